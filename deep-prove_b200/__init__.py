@@ -1,0 +1,314 @@
+"""ctypes binding of libdpb.so, the C-ABI library of the B200 sumcheck /
+multilinear-fold / logup-GKR back end (declarations: include/dpb.h).
+
+The directory name is not a Python identifier; load it by path under the name
+`deep_prove_b200` (tests/conftest.py and bench.py show how).  There is no CPU
+path: importing works without a GPU (so the exported symbols can be checked),
+but creating a Context raises when no CUDA device is usable, and a missing
+library raises at import.
+"""
+import ctypes
+import os
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libdpb.so")
+
+GL_BASE, GL_EXT, FR = 0, 1, 2
+FORM_NATIVE, FORM_CANONICAL, FORM_I64 = 0, 1, 2
+LOGUP_LOOKUP, LOGUP_TABLE = 0, 1
+MAX_FACTORS = 8
+
+OK, EINVAL, ENOMEM, ECUDA, ETIMEOUT, ESTATE, ENCCL = 0, -1, -2, -3, -4, -5, -6
+
+
+class DpbError(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__(f"dpb error {code}: {msg}")
+        self.code = code
+
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} is missing: build it with `python deep-prove_b200/build.py` "
+        "(nvcc, sm_100a). There is no fallback implementation.")
+
+lib = ctypes.CDLL(LIB_PATH)
+
+
+class Term(ctypes.Structure):
+    _fields_ = [("coeff", ctypes.c_uint8 * 32), ("n_factors", ctypes.c_uint32),
+                ("idx", ctypes.c_uint16 * MAX_FACTORS)]
+
+
+_vp, _u32, _u64, _int = ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_int
+_pp = ctypes.POINTER(ctypes.c_void_p)
+
+SIGNATURES = {
+    "dpb_init": (_int, [_int, _pp]),
+    "dpb_shutdown": (None, [_vp]),
+    "dpb_last_error": (ctypes.c_char_p, []),
+    "dpb_sync": (_int, [_vp]),
+    "dpb_stream": (_vp, [_vp]),
+    "dpb_mle_from_host": (_int, [_vp, _int, _vp, _u64, _int, _pp]),
+    "dpb_mle_from_device": (_int, [_vp, _int, _vp, _u64, _pp]),
+    "dpb_mle_alloc": (_int, [_vp, _int, _u64, _pp]),
+    "dpb_mle_free": (_int, [_vp]),
+    "dpb_mle_to_host": (_int, [_vp, _vp, _u64, _int]),
+    "dpb_mle_len": (_u64, [_vp]),
+    "dpb_mle_dtype": (_int, [_vp]),
+    "dpb_mle_device_ptr": (_vp, [_vp]),
+    "dpb_mle_view": (_int, [_vp, _u64, _u64, _pp]),
+    "dpb_eq_table": (_int, [_vp, _int, _vp, _u32, _pp]),
+    "dpb_fix_high": (_int, [_vp, _vp, _vp, _u32, _pp]),
+    "dpb_fix_low": (_int, [_vp, _vp, _vp, _u32, _pp]),
+    "dpb_mle_evaluate": (_int, [_vp, _vp, _vp, _u32, _vp]),
+    "dpb_sumcheck_begin": (_int, [_vp, _u32, _pp, _u32, ctypes.POINTER(Term), _u32, _pp]),
+    "dpb_sumcheck_degree": (_u32, [_vp]),
+    "dpb_sumcheck_round": (_int, [_vp, _vp, _vp, ctypes.POINTER(_u32)]),
+    "dpb_sumcheck_finish": (_int, [_vp, _vp, _vp]),
+    "dpb_sumcheck_free": (None, [_vp]),
+    "dpb_logup_build": (_int, [_vp, _int, _pp, _u32, _vp, _vp, _vp, _pp]),
+    "dpb_logup_num_levels": (_u32, [_vp]),
+    "dpb_logup_level": (_int, [_vp, _u32, _pp]),
+    "dpb_logup_outputs": (_int, [_vp, _vp]),
+    "dpb_logup_free": (None, [_vp]),
+}
+
+
+def _bind():
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+
+
+_bind()
+
+
+def check(rc):
+    if rc != OK:
+        raise DpbError(rc, lib.dpb_last_error().decode(errors="replace"))
+
+
+def elem_words(dtype):
+    return {GL_BASE: 1, GL_EXT: 2, FR: 4}[dtype]
+
+
+def chal_dtype(dtype):
+    return FR if dtype == FR else GL_EXT
+
+
+def _buf(a):
+    return ctypes.c_void_p(a.ctypes.data)
+
+
+def dtype_of_array(a, family):
+    """family 'gl': uint64[n] -> base, uint64[n,2] -> extension; 'fr': uint64[n,4]."""
+    a = np.asarray(a)
+    if family == "fr":
+        return FR
+    return GL_BASE if a.ndim == 1 else GL_EXT
+
+
+class Context:
+    """One GPU, one stream (dpb_init / dpb_shutdown)."""
+
+    def __init__(self, device=0):
+        h = ctypes.c_void_p()
+        check(lib.dpb_init(device, ctypes.byref(h)))
+        self.h = h
+        self.device = device
+
+    def close(self):
+        if self.h:
+            lib.dpb_shutdown(self.h)
+            self.h = None
+
+    def sync(self):
+        check(lib.dpb_sync(self.h))
+
+    @property
+    def stream(self):
+        return lib.dpb_stream(self.h)
+
+    # ---- tables
+    def upload(self, array, dtype, form=FORM_NATIVE):
+        a = np.ascontiguousarray(array)
+        n = a.shape[0]
+        h = ctypes.c_void_p()
+        check(lib.dpb_mle_from_host(self.h, dtype, _buf(a), n, form, ctypes.byref(h)))
+        return Mle(self, h)
+
+    def upload_i64(self, array, dtype):
+        a = np.ascontiguousarray(array, dtype=np.int64)
+        h = ctypes.c_void_p()
+        check(lib.dpb_mle_from_host(self.h, dtype, _buf(a), a.size, FORM_I64, ctypes.byref(h)))
+        return Mle(self, h)
+
+    def alloc(self, dtype, n):
+        h = ctypes.c_void_p()
+        check(lib.dpb_mle_alloc(self.h, dtype, n, ctypes.byref(h)))
+        return Mle(self, h)
+
+    def wrap_device(self, dev_ptr, dtype, n):
+        h = ctypes.c_void_p()
+        check(lib.dpb_mle_from_device(self.h, dtype, ctypes.c_void_p(dev_ptr), n, ctypes.byref(h)))
+        return Mle(self, h)
+
+    def eq_table(self, family_dtype, point_array):
+        """point_array: challenge elements, uint64[m, words]"""
+        p = np.ascontiguousarray(point_array, dtype=np.uint64)
+        m = p.shape[0] if p.size else 0
+        h = ctypes.c_void_p()
+        check(lib.dpb_eq_table(self.h, family_dtype, _buf(p) if m else None, m, ctypes.byref(h)))
+        return Mle(self, h)
+
+    def fix_high(self, mle, point_array):
+        p = np.ascontiguousarray(point_array, dtype=np.uint64)
+        h = ctypes.c_void_p()
+        check(lib.dpb_fix_high(self.h, mle.h, _buf(p), p.shape[0], ctypes.byref(h)))
+        return Mle(self, h)
+
+    def fix_low(self, mle, point_array):
+        p = np.ascontiguousarray(point_array, dtype=np.uint64)
+        h = ctypes.c_void_p()
+        check(lib.dpb_fix_low(self.h, mle.h, _buf(p), p.shape[0], ctypes.byref(h)))
+        return Mle(self, h)
+
+    def evaluate(self, mle, point_array):
+        p = np.ascontiguousarray(point_array, dtype=np.uint64)
+        n = p.shape[0] if p.size else 0
+        out = np.zeros(elem_words(chal_dtype(mle.dtype)), dtype=np.uint64)
+        check(lib.dpb_mle_evaluate(self.h, mle.h, _buf(p) if n else None, n, _buf(out)))
+        return out
+
+    def sumcheck(self, num_vars, mles, terms):
+        return Sumcheck(self, num_vars, mles, terms)
+
+    def logup(self, kind, columns, constant, sep, mult=None):
+        return Logup(self, kind, columns, constant, sep, mult)
+
+
+class Mle:
+    """A multilinear table on the device (dpb_mle)."""
+
+    def __init__(self, ctx, h):
+        self.ctx, self.h = ctx, h
+
+    @property
+    def len(self):
+        return lib.dpb_mle_len(self.h)
+
+    @property
+    def dtype(self):
+        return lib.dpb_mle_dtype(self.h)
+
+    @property
+    def device_ptr(self):
+        return lib.dpb_mle_device_ptr(self.h)
+
+    def to_host(self, form=FORM_NATIVE, n=None):
+        n = self.len if n is None else n
+        w = elem_words(self.dtype)
+        out = np.empty((n, w) if w > 1 else (n,), dtype=np.uint64)
+        check(lib.dpb_mle_to_host(self.h, _buf(out), n, form))
+        return out
+
+    def view(self, offset, n):
+        h = ctypes.c_void_p()
+        check(lib.dpb_mle_view(self.h, offset, n, ctypes.byref(h)))
+        return Mle(self.ctx, h)
+
+    def free(self):
+        if self.h:
+            lib.dpb_mle_free(self.h)
+            self.h = None
+
+
+def make_terms(terms, coeff_bytes):
+    """terms: list of (coeff, [table ids]); coeff_bytes(coeff) -> native bytes."""
+    arr = (Term * len(terms))()
+    for t, (c, idx) in enumerate(terms):
+        raw = coeff_bytes(c)
+        for i, b in enumerate(raw):
+            arr[t].coeff[i] = b
+        arr[t].n_factors = len(idx)
+        if len(idx) > MAX_FACTORS:
+            raise ValueError("too many factors")
+        for j, v in enumerate(idx):
+            arr[t].idx[j] = v
+    return arr
+
+
+class Sumcheck:
+    """dpb_sumcheck_begin / round / finish."""
+
+    def __init__(self, ctx, num_vars, mles, term_array):
+        self.ctx = ctx
+        k = len(mles)
+        hs = (ctypes.c_void_p * k)(*[m.h for m in mles])
+        h = ctypes.c_void_p()
+        check(lib.dpb_sumcheck_begin(ctx.h, num_vars, hs, k, term_array, len(term_array), ctypes.byref(h)))
+        self.h = h
+        self.k = k
+        self.num_vars = num_vars
+        self.words = elem_words(chal_dtype(mles[0].dtype))
+        self.degree = lib.dpb_sumcheck_degree(h)
+        self._out = np.zeros((self.degree + 1, self.words), dtype=np.uint64)
+
+    def round(self, prev_challenge=None):
+        n = ctypes.c_uint32()
+        pc = None
+        if prev_challenge is not None:
+            self._pc = np.ascontiguousarray(prev_challenge, dtype=np.uint64)
+            pc = _buf(self._pc)
+        check(lib.dpb_sumcheck_round(self.h, pc, _buf(self._out), ctypes.byref(n)))
+        return self._out.copy()
+
+    def finish(self, last_challenge):
+        lc = np.ascontiguousarray(last_challenge, dtype=np.uint64)
+        out = np.zeros((self.k, self.words), dtype=np.uint64)
+        check(lib.dpb_sumcheck_finish(self.h, _buf(lc), _buf(out)))
+        return out
+
+    def free(self):
+        if self.h:
+            lib.dpb_sumcheck_free(self.h)
+            self.h = None
+
+
+class Logup:
+    """dpb_logup_build and accessors."""
+
+    def __init__(self, ctx, kind, columns, constant, sep, mult=None):
+        self.ctx = ctx
+        k = len(columns)
+        hs = (ctypes.c_void_p * k)(*[m.h for m in columns])
+        c = np.ascontiguousarray(constant, dtype=np.uint64)
+        s = np.ascontiguousarray(sep, dtype=np.uint64)
+        h = ctypes.c_void_p()
+        check(lib.dpb_logup_build(ctx.h, kind, hs, k, mult.h if mult is not None else None, _buf(c), _buf(s),
+                                  ctypes.byref(h)))
+        self.h = h
+        self.words = elem_words(chal_dtype(columns[0].dtype))
+
+    @property
+    def num_levels(self):
+        return lib.dpb_logup_num_levels(self.h)
+
+    def level(self, l):
+        out = (ctypes.c_void_p * 4)()
+        check(lib.dpb_logup_level(self.h, l, out))
+        return [Mle(self.ctx, ctypes.c_void_p(v)) for v in out]
+
+    def outputs(self):
+        out = np.zeros((4, self.words), dtype=np.uint64)
+        check(lib.dpb_logup_outputs(self.h, _buf(out)))
+        return out
+
+    def free(self):
+        if self.h:
+            lib.dpb_logup_free(self.h)
+            self.h = None

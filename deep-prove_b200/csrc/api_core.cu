@@ -1,0 +1,400 @@
+// C ABI: context, table handles, layout conversion, eq tables and partial
+// evaluation (fix_high / fix_low / evaluate).
+#include "common.cuh"
+#include "poly_kernels.cuh"
+
+namespace dpb {
+
+std::string& last_error_slot() {
+    static thread_local std::string s;
+    return s;
+}
+
+int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    last_error_slot() = buf;
+    return code;
+}
+
+int device_alloc(dpb_ctx* ctx, size_t bytes, void** out) {
+    if (bytes == 0) bytes = 16;
+    DPB_CUDA(cudaMallocAsync(out, bytes, ctx->stream));
+    return DPB_OK;
+}
+void device_free(dpb_ctx* ctx, void* p) {
+    if (p) cudaFreeAsync(p, ctx->stream);
+}
+
+int new_mle(dpb_ctx* ctx, int dtype, uint64_t len, dpb_mle** out) {
+    dpb_mle* m = new (std::nothrow) dpb_mle();
+    if (!m) return fail(DPB_ENOMEM, "host allocation failed");
+    m->ctx = ctx;
+    m->dtype = dtype;
+    m->len = len;
+    m->owns = true;
+    int rc = device_alloc(ctx, len * dtype_size(dtype), &m->ptr);
+    if (rc != DPB_OK) {
+        delete m;
+        return rc;
+    }
+    *out = m;
+    return DPB_OK;
+}
+
+int stage_to_device(dpb_ctx* ctx, const void* host, size_t bytes, size_t offset, void** dev) {
+    if (offset + bytes > ctx->stage_bytes)
+        return fail(DPB_EINVAL, "staging area too small (%zu + %zu > %zu)", offset, bytes,
+                    ctx->stage_bytes);
+    *dev = (char*)ctx->stage_dev + offset;
+    DPB_CUDA(cudaMemcpyAsync(*dev, host, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    return DPB_OK;
+}
+
+// eq(x, pt) table over m variables into freshly allocated device memory.
+template <class F>
+static int eq_table_dev(dpb_ctx* ctx, const typename F::E* pt_dev, uint32_t m,
+                        typename F::E** out) {
+    typedef typename F::E E;
+    const uint64_t n = 1ull << m;
+    E* res = nullptr;
+    DPB_TRY(device_alloc(ctx, n * sizeof(E), (void**)&res));
+    constexpr uint32_t kDirect = 10;
+    if (m <= kDirect) {
+        eq_direct<F><<<grid_for(ctx, n), kThreads, 0, ctx->stream>>>(pt_dev, m, res);
+    } else {
+        E* lo = nullptr;
+        E* hi = nullptr;
+        DPB_TRY(device_alloc(ctx, sizeof(E) << kDirect, (void**)&lo));
+        eq_direct<F><<<grid_for(ctx, 1ull << kDirect), kThreads, 0, ctx->stream>>>(pt_dev, kDirect, lo);
+        int rc = eq_table_dev<F>(ctx, pt_dev + kDirect, m - kDirect, &hi);
+        if (rc != DPB_OK) {
+            device_free(ctx, lo);
+            device_free(ctx, res);
+            return rc;
+        }
+        eq_combine<F><<<grid_for(ctx, n), kThreads, 0, ctx->stream>>>(lo, kDirect, hi, n, res);
+        device_free(ctx, lo);
+        device_free(ctx, hi);
+    }
+    DPB_CUDA(cudaGetLastError());
+    *out = res;
+    return DPB_OK;
+}
+
+template <class F>
+static int eq_table_impl(dpb_ctx* ctx, const void* point, uint32_t m, dpb_mle** out) {
+    typedef typename F::E E;
+    void* pt_dev = nullptr;
+    if (m > 0) DPB_TRY(stage_to_device(ctx, point, m * sizeof(E), 0, &pt_dev));
+    E* res = nullptr;
+    DPB_TRY(eq_table_dev<F>(ctx, (const E*)pt_dev, m, &res));
+    dpb_mle* h = new (std::nothrow) dpb_mle();
+    if (!h) return fail(DPB_ENOMEM, "host allocation failed");
+    h->ctx = ctx;
+    h->dtype = F::kChalDtype;
+    h->len = 1ull << m;
+    h->ptr = res;
+    h->owns = true;
+    *out = h;
+    return DPB_OK;
+}
+
+// Binds k variables from the top (high = true) or the bottom, at most 5 per
+// pass so every pass keeps the whole device busy.
+template <class F>
+static int fix_vars_impl(dpb_ctx* ctx, const void* in, int dtype_in, uint64_t len,
+                         const void* point_host, uint32_t k, bool high, void** out_ptr) {
+    typedef typename F::E E;
+    void* pt_dev = nullptr;
+    DPB_TRY(stage_to_device(ctx, point_host, k * sizeof(E), 0, &pt_dev));
+    const E* pt = (const E*)pt_dev;
+    const void* cur = in;
+    int cur_dtype = dtype_in;
+    uint64_t cur_len = len;
+    void* owned = nullptr;  // intermediate we must free
+    uint32_t done = 0;
+    E* w = nullptr;
+    DPB_TRY(device_alloc(ctx, sizeof(E) * 32, (void**)&w));
+    while (done < k) {
+        const uint32_t g = (k - done) < 5 ? (k - done) : 5;
+        // high: bind the top g of the variables still free, i.e. point[k-done-g .. k-done)
+        // low : bind the bottom g, i.e. point[done .. done+g)
+        const E* sub = high ? pt + (k - done - g) : pt + done;
+        eq_direct<F><<<1, 32, 0, ctx->stream>>>(sub, g, w);
+        const uint64_t n_out = cur_len >> g;
+        E* nxt = nullptr;
+        int rc = device_alloc(ctx, n_out * sizeof(E), (void**)&nxt);
+        if (rc != DPB_OK) {
+            device_free(ctx, owned);
+            device_free(ctx, w);
+            return rc;
+        }
+        if (high)
+            fix_high_pass<F><<<grid_for(ctx, n_out), kThreads, 0, ctx->stream>>>(cur, cur_dtype, w, g, n_out, nxt);
+        else
+            fix_low_pass<F><<<grid_for(ctx, cur_len), kThreads, 0, ctx->stream>>>(cur, cur_dtype, w, g, cur_len, nxt);
+        device_free(ctx, owned);
+        owned = nxt;
+        cur = nxt;
+        cur_dtype = F::kChalDtype;
+        cur_len = n_out;
+        done += g;
+    }
+    device_free(ctx, w);
+    DPB_CUDA(cudaGetLastError());
+    *out_ptr = owned;
+    return DPB_OK;
+}
+
+static int fix_common(dpb_ctx* ctx, const dpb_mle* mle, const void* point, uint32_t k, bool high,
+                      dpb_mle** out) {
+    if (!ctx || !mle || !out || (!point && k)) return fail(DPB_EINVAL, "null argument");
+    const uint32_t n = log2u(mle->len);
+    if (k == 0 || k > n) return fail(DPB_EINVAL, "cannot bind %u of %u variables", k, n);
+    if (k * dtype_size(chal_dtype(mle->dtype)) > ctx->stage_bytes)
+        return fail(DPB_EINVAL, "point too long");
+    void* res = nullptr;
+    int rc = is_gl(mle->dtype)
+                 ? fix_vars_impl<GlFam>(ctx, mle->ptr, mle->dtype, mle->len, point, k, high, &res)
+                 : fix_vars_impl<FrFam>(ctx, mle->ptr, mle->dtype, mle->len, point, k, high, &res);
+    if (rc != DPB_OK) return rc;
+    dpb_mle* h = new (std::nothrow) dpb_mle();
+    if (!h) return fail(DPB_ENOMEM, "host allocation failed");
+    h->ctx = ctx;
+    h->dtype = chal_dtype(mle->dtype);
+    h->len = mle->len >> k;
+    h->ptr = res;
+    h->owns = true;
+    *out = h;
+    return DPB_OK;
+}
+
+}  // namespace dpb
+
+using namespace dpb;
+
+extern "C" {
+
+const char* dpb_last_error(void) { return last_error_slot().c_str(); }
+
+int dpb_init(int device, dpb_ctx** out) {
+    if (!out) return fail(DPB_EINVAL, "null argument");
+    int n_dev = 0;
+    cudaError_t e = cudaGetDeviceCount(&n_dev);
+    if (e != cudaSuccess || n_dev == 0)
+        return fail(DPB_ECUDA, "no CUDA device available (%s); this library has no CPU path",
+                    e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e));
+    if (device < 0 || device >= n_dev) return fail(DPB_EINVAL, "device %d out of range", device);
+    DPB_CUDA(cudaSetDevice(device));
+    dpb_ctx* ctx = new (std::nothrow) dpb_ctx();
+    if (!ctx) return fail(DPB_ENOMEM, "host allocation failed");
+    ctx->device = device;
+    cudaDeviceProp prop;
+    DPB_CUDA(cudaGetDeviceProperties(&prop, device));
+    ctx->sm_count = prop.multiProcessorCount;
+    DPB_CUDA(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
+    // keep freed blocks in the stream-ordered pool instead of returning them to the driver
+    cudaMemPool_t pool;
+    DPB_CUDA(cudaDeviceGetDefaultMemPool(&pool, device));
+    uint64_t thresh = UINT64_MAX;
+    DPB_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &thresh));
+    ctx->max_blocks = (uint32_t)ctx->sm_count * 8;
+    DPB_CUDA(cudaMalloc(&ctx->partials, (size_t)ctx->max_blocks * kMaxAcc * sizeof(Fr)));
+    DPB_CUDA(cudaMalloc((void**)&ctx->counter, 256));
+    DPB_CUDA(cudaMemset(ctx->counter, 0, 256));
+    ctx->result_bytes = 64 * 1024;
+    DPB_CUDA(cudaHostAlloc(&ctx->result_host, ctx->result_bytes, cudaHostAllocMapped));
+    DPB_CUDA(cudaHostGetDevicePointer(&ctx->result_dev, ctx->result_host, 0));
+    ctx->stage_bytes = 64 * 1024;
+    DPB_CUDA(cudaMalloc(&ctx->stage_dev, ctx->stage_bytes));
+    *out = ctx;
+    return DPB_OK;
+}
+
+void dpb_shutdown(dpb_ctx* ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    cudaFree(ctx->partials);
+    cudaFree(ctx->counter);
+    cudaFree(ctx->stage_dev);
+    cudaFreeHost(ctx->result_host);
+    cudaStreamDestroy(ctx->stream);
+    delete ctx;
+}
+
+int dpb_sync(dpb_ctx* ctx) {
+    if (!ctx) return fail(DPB_EINVAL, "null context");
+    DPB_CUDA(cudaStreamSynchronize(ctx->stream));
+    return DPB_OK;
+}
+
+void* dpb_stream(dpb_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+
+int dpb_mle_alloc(dpb_ctx* ctx, int dtype, uint64_t len, dpb_mle** out) {
+    if (!ctx || !out) return fail(DPB_EINVAL, "null argument");
+    if (!valid_dtype(dtype)) return fail(DPB_EINVAL, "unknown dtype %d", dtype);
+    if (!is_pow2(len)) return fail(DPB_EINVAL, "length %llu is not a power of two", (unsigned long long)len);
+    return new_mle(ctx, dtype, len, out);
+}
+
+int dpb_mle_from_host(dpb_ctx* ctx, int dtype, const void* evals, uint64_t len, int form,
+                      dpb_mle** out) {
+    if (!ctx || !out || !evals) return fail(DPB_EINVAL, "null argument");
+    if (!valid_dtype(dtype)) return fail(DPB_EINVAL, "unknown dtype %d", dtype);
+    if (!is_pow2(len)) return fail(DPB_EINVAL, "length %llu is not a power of two", (unsigned long long)len);
+    if (form == DPB_FORM_CANONICAL && dtype != DPB_FR)
+        return fail(DPB_EINVAL, "canonical form applies to DPB_FR tables only");
+    if (form == DPB_FORM_I64 && dtype == DPB_GL_EXT)
+        return fail(DPB_EINVAL, "i64 input yields base-field or Fr tables");
+    if (form < DPB_FORM_NATIVE || form > DPB_FORM_I64) return fail(DPB_EINVAL, "unknown form %d", form);
+    dpb_mle* m = nullptr;
+    DPB_TRY(new_mle(ctx, dtype, len, &m));
+    int rc = DPB_OK;
+    if (form == DPB_FORM_NATIVE) {
+        cudaError_t e = cudaMemcpyAsync(m->ptr, evals, len * dtype_size(dtype), cudaMemcpyHostToDevice, ctx->stream);
+        if (e != cudaSuccess) rc = fail(DPB_ECUDA, "upload: %s", cudaGetErrorString(e));
+    } else if (form == DPB_FORM_CANONICAL) {
+        cudaError_t e = cudaMemcpyAsync(m->ptr, evals, len * 32, cudaMemcpyHostToDevice, ctx->stream);
+        if (e != cudaSuccess) rc = fail(DPB_ECUDA, "upload: %s", cudaGetErrorString(e));
+        else fr_canonical_to_mont<<<grid_for(ctx, len), kThreads, 0, ctx->stream>>>((const Fr*)m->ptr, (Fr*)m->ptr, len);
+    } else {
+        void* tmp = nullptr;
+        rc = device_alloc(ctx, len * 8, &tmp);
+        if (rc == DPB_OK) {
+            cudaError_t e = cudaMemcpyAsync(tmp, evals, len * 8, cudaMemcpyHostToDevice, ctx->stream);
+            if (e != cudaSuccess) rc = fail(DPB_ECUDA, "upload: %s", cudaGetErrorString(e));
+            else if (dtype == DPB_FR)
+                fr_from_i64_kernel<<<grid_for(ctx, len), kThreads, 0, ctx->stream>>>((const int64_t*)tmp, (Fr*)m->ptr, len);
+            else
+                gl_from_i64_kernel<<<grid_for(ctx, len), kThreads, 0, ctx->stream>>>((const int64_t*)tmp, (uint64_t*)m->ptr, len);
+            device_free(ctx, tmp);
+        }
+    }
+    if (rc == DPB_OK) {
+        // the host buffer may be pageable and reused by the caller right away
+        cudaError_t e = cudaStreamSynchronize(ctx->stream);
+        if (e == cudaSuccess) e = cudaGetLastError();
+        if (e != cudaSuccess) rc = fail(DPB_ECUDA, "upload: %s", cudaGetErrorString(e));
+    }
+    if (rc != DPB_OK) {
+        dpb_mle_free(m);
+        return rc;
+    }
+    *out = m;
+    return DPB_OK;
+}
+
+int dpb_mle_from_device(dpb_ctx* ctx, int dtype, void* dev_ptr, uint64_t len, dpb_mle** out) {
+    if (!ctx || !out || !dev_ptr) return fail(DPB_EINVAL, "null argument");
+    if (!valid_dtype(dtype)) return fail(DPB_EINVAL, "unknown dtype %d", dtype);
+    if (!is_pow2(len)) return fail(DPB_EINVAL, "length %llu is not a power of two", (unsigned long long)len);
+    if (((uintptr_t)dev_ptr & 15) != 0) return fail(DPB_EINVAL, "device pointer must be 16-byte aligned");
+    dpb_mle* m = new (std::nothrow) dpb_mle();
+    if (!m) return fail(DPB_ENOMEM, "host allocation failed");
+    m->ctx = ctx;
+    m->dtype = dtype;
+    m->len = len;
+    m->ptr = dev_ptr;
+    m->owns = false;
+    *out = m;
+    return DPB_OK;
+}
+
+int dpb_mle_view(const dpb_mle* mle, uint64_t offset, uint64_t len, dpb_mle** out) {
+    if (!mle || !out) return fail(DPB_EINVAL, "null argument");
+    if (!is_pow2(len) || offset + len > mle->len)
+        return fail(DPB_EINVAL, "view [%llu, +%llu) outside a table of %llu", (unsigned long long)offset,
+                    (unsigned long long)len, (unsigned long long)mle->len);
+    const size_t byte_off = offset * dtype_size(mle->dtype);
+    if (byte_off & 15) return fail(DPB_EINVAL, "view must start on a 16-byte boundary");
+    dpb_mle* m = new (std::nothrow) dpb_mle();
+    if (!m) return fail(DPB_ENOMEM, "host allocation failed");
+    m->ctx = mle->ctx;
+    m->dtype = mle->dtype;
+    m->len = len;
+    m->ptr = (char*)mle->ptr + byte_off;
+    m->owns = false;
+    *out = m;
+    return DPB_OK;
+}
+
+int dpb_mle_free(dpb_mle* mle) {
+    if (!mle) return DPB_OK;
+    if (mle->owns) device_free(mle->ctx, mle->ptr);
+    delete mle;
+    return DPB_OK;
+}
+
+int dpb_mle_to_host(const dpb_mle* mle, void* out, uint64_t len, int form) {
+    if (!mle || !out) return fail(DPB_EINVAL, "null argument");
+    if (len > mle->len) return fail(DPB_EINVAL, "asked for %llu of %llu entries", (unsigned long long)len,
+                                    (unsigned long long)mle->len);
+    dpb_ctx* ctx = mle->ctx;
+    if (form == DPB_FORM_NATIVE) {
+        DPB_CUDA(cudaMemcpyAsync(out, mle->ptr, len * dtype_size(mle->dtype), cudaMemcpyDeviceToHost, ctx->stream));
+    } else if (form == DPB_FORM_CANONICAL && mle->dtype == DPB_FR) {
+        void* tmp = nullptr;
+        DPB_TRY(device_alloc(ctx, len * 32, &tmp));
+        fr_mont_to_canonical<<<grid_for(ctx, len), kThreads, 0, ctx->stream>>>((const Fr*)mle->ptr, (Fr*)tmp, len);
+        cudaError_t e = cudaMemcpyAsync(out, tmp, len * 32, cudaMemcpyDeviceToHost, ctx->stream);
+        device_free(ctx, tmp);
+        if (e != cudaSuccess) return fail(DPB_ECUDA, "download: %s", cudaGetErrorString(e));
+    } else {
+        return fail(DPB_EINVAL, "form %d not available for dtype %d", form, mle->dtype);
+    }
+    DPB_CUDA(cudaStreamSynchronize(ctx->stream));
+    DPB_CUDA(cudaGetLastError());
+    return DPB_OK;
+}
+
+uint64_t dpb_mle_len(const dpb_mle* mle) { return mle ? mle->len : 0; }
+int dpb_mle_dtype(const dpb_mle* mle) { return mle ? mle->dtype : DPB_EINVAL; }
+void* dpb_mle_device_ptr(const dpb_mle* mle) { return mle ? mle->ptr : nullptr; }
+
+int dpb_eq_table(dpb_ctx* ctx, int family_dtype, const void* point, uint32_t m, dpb_mle** out) {
+    if (!ctx || !out || (!point && m)) return fail(DPB_EINVAL, "null argument");
+    if (!valid_dtype(family_dtype)) return fail(DPB_EINVAL, "unknown dtype %d", family_dtype);
+    if (m > 34) return fail(DPB_EINVAL, "eq table over %u variables is too large", m);
+    return is_gl(family_dtype) ? eq_table_impl<GlFam>(ctx, point, m, out)
+                               : eq_table_impl<FrFam>(ctx, point, m, out);
+}
+
+int dpb_fix_high(dpb_ctx* ctx, const dpb_mle* mle, const void* point, uint32_t k, dpb_mle** out) {
+    return fix_common(ctx, mle, point, k, true, out);
+}
+
+int dpb_fix_low(dpb_ctx* ctx, const dpb_mle* mle, const void* point, uint32_t k, dpb_mle** out) {
+    return fix_common(ctx, mle, point, k, false, out);
+}
+
+int dpb_mle_evaluate(dpb_ctx* ctx, const dpb_mle* mle, const void* point, uint32_t n, void* out) {
+    if (!ctx || !mle || !out) return fail(DPB_EINVAL, "null argument");
+    if ((1ull << n) != mle->len)
+        return fail(DPB_EINVAL, "point of %u coordinates for a table of %llu entries", n,
+                    (unsigned long long)mle->len);
+    if (n == 0) {
+        // a constant: widen the single entry
+        if (mle->dtype == DPB_GL_BASE) {
+            uint64_t v[2] = {0, 0};
+            DPB_CUDA(cudaMemcpyAsync(v, mle->ptr, 8, cudaMemcpyDeviceToHost, ctx->stream));
+            DPB_CUDA(cudaStreamSynchronize(ctx->stream));
+            memcpy(out, v, 16);
+            return DPB_OK;
+        }
+        DPB_CUDA(cudaMemcpyAsync(out, mle->ptr, dtype_size(mle->dtype), cudaMemcpyDeviceToHost, ctx->stream));
+        DPB_CUDA(cudaStreamSynchronize(ctx->stream));
+        return DPB_OK;
+    }
+    dpb_mle* res = nullptr;
+    DPB_TRY(fix_common(ctx, mle, point, n, false, &res));
+    int rc = dpb_mle_to_host(res, out, 1, DPB_FORM_NATIVE);
+    dpb_mle_free(res);
+    return rc;
+}
+
+}  // extern "C"

@@ -1,0 +1,302 @@
+// C ABI: the sumcheck prover state machine (begin / round / finish).
+//
+// All device buffers and the per-round table descriptors are laid out when the
+// sumcheck begins, so a round is: [fold with the previous challenge] + one
+// evaluation launch + one stream synchronisation.  The evaluation kernel's
+// last block writes the round polynomial straight into mapped host memory.
+#include "common.cuh"
+#include "fused_kernels.cuh"
+
+namespace dpb {
+
+struct MleTrack {
+    const void* orig;
+    int dtype;
+    uint32_t nv;
+    void* buf[2];  // ping-pong targets of the folds (challenge-element layout)
+};
+
+}  // namespace dpb
+
+using namespace dpb;
+
+struct dpb_sc {
+    dpb_ctx* ctx = nullptr;
+    bool gl = false;
+    uint32_t n = 0, k = 0, d = 0, n_terms = 0;
+    uint32_t round = 0;  // next round to run
+    bool finished = false;
+    std::vector<MleTrack> tr;
+    void* slab = nullptr;        // fold buffers
+    MleDesc* d_desc = nullptr;   // [n][k]
+    FoldDesc* d_fold = nullptr;  // [n][k]   folds that run before round i (i >= 1)
+    std::vector<uint32_t> n_fold;  // per round
+    std::vector<uint64_t> max_fold_out;
+    void* d_terms = nullptr;
+    void* d_final = nullptr;  // k challenge elements
+    int fused_shape = 0;      // see fused_kernels.cuh
+    std::vector<MleDesc> h_desc;
+    std::vector<FoldDesc> h_fold;
+};
+
+namespace dpb {
+
+// the table MLE j presents in round i: where it lives and in which layout
+static void table_at_round(const dpb_sc* sc, uint32_t j, uint32_t i, const void** ptr, int* dtype,
+                           bool* active) {
+    const MleTrack& t = sc->tr[j];
+    const uint32_t first_active = sc->n - t.nv;
+    if (i < first_active) {
+        *ptr = t.orig;
+        *dtype = t.dtype;
+        *active = false;
+        return;
+    }
+    *active = true;
+    const uint32_t folds = i - first_active;
+    if (folds == 0) {
+        *ptr = t.orig;
+        *dtype = t.dtype;
+    } else {
+        *ptr = t.buf[(folds - 1) & 1];
+        *dtype = chal_dtype(t.dtype);
+    }
+}
+
+template <class F>
+static int upload_terms(dpb_sc* sc, const dpb_term* terms) {
+    typedef typename F::E E;
+    std::vector<TermDev<F>> h(sc->n_terms);
+    for (uint32_t t = 0; t < sc->n_terms; t++) {
+        memcpy(&h[t].coeff, terms[t].coeff, sizeof(E));
+        h[t].n_factors = terms[t].n_factors;
+        h[t].coeff_is_one = F::is_one(h[t].coeff) ? 1u : 0u;
+        for (int j = 0; j < DPB_MAX_FACTORS; j++) h[t].idx[j] = terms[t].idx[j];
+    }
+    DPB_TRY(device_alloc(sc->ctx, h.size() * sizeof(TermDev<F>), &sc->d_terms));
+    DPB_CUDA(cudaMemcpyAsync(sc->d_terms, h.data(), h.size() * sizeof(TermDev<F>), cudaMemcpyHostToDevice,
+                             sc->ctx->stream));
+    // h is pageable: the copy has been staged by the driver when the call returns
+    DPB_CUDA(cudaStreamSynchronize(sc->ctx->stream));
+    return DPB_OK;
+}
+
+template <class F, int D>
+static void launch_eval(dpb_sc* sc, uint32_t round, uint64_t n_pairs) {
+    dpb_ctx* ctx = sc->ctx;
+    sc_eval_generic<F, D><<<grid_for(ctx, n_pairs, 4), kThreads, 0, ctx->stream>>>(
+        sc->d_desc + (size_t)round * sc->k, (const TermDev<F>*)sc->d_terms, sc->n_terms, n_pairs,
+        reduce_scratch<F>(ctx), (typename F::E*)ctx->result_dev);
+}
+
+template <class F>
+static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
+    typedef typename F::E E;
+    dpb_ctx* ctx = sc->ctx;
+    const uint32_t i = sc->round;
+    const uint64_t n_pairs = 1ull << (sc->n - i - 1);
+    E r = F::zero();
+    if (i > 0) memcpy(&r, prev_challenge, sizeof(E));
+
+    bool done = false;
+    if (sc->fused_shape != 0) {
+        int rc = fused_round<F>(sc->fused_shape, ctx, sc->h_desc.data() + (size_t)i * sc->k,
+                                i > 0 ? sc->h_fold.data() + (size_t)i * sc->k : nullptr, sc->k, i, r,
+                                n_pairs, &done);
+        if (rc != DPB_OK) return rc;
+    }
+    if (!done) {
+        if (i > 0 && sc->n_fold[i] > 0) {
+            dim3 grid(grid_for(ctx, sc->max_fold_out[i], 4), sc->n_fold[i]);
+            sc_fold_generic<F><<<grid, kThreads, 0, ctx->stream>>>(sc->d_fold + (size_t)i * sc->k, r);
+        }
+        switch (sc->d) {
+            case 1: launch_eval<F, 1>(sc, i, n_pairs); break;
+            case 2: launch_eval<F, 2>(sc, i, n_pairs); break;
+            case 3: launch_eval<F, 3>(sc, i, n_pairs); break;
+            case 4: launch_eval<F, 4>(sc, i, n_pairs); break;
+            case 5: launch_eval<F, 5>(sc, i, n_pairs); break;
+            case 6: launch_eval<F, 6>(sc, i, n_pairs); break;
+            default: return fail(DPB_EINVAL, "degree %u not supported", sc->d);
+        }
+    }
+    DPB_CUDA(cudaGetLastError());
+    DPB_CUDA(cudaStreamSynchronize(ctx->stream));
+    memcpy(out_evals, ctx->result_host, (sc->d + 1) * sizeof(E));
+    return DPB_OK;
+}
+
+template <class F>
+static int run_finish(dpb_sc* sc, const void* last_challenge, void* out) {
+    typedef typename F::E E;
+    dpb_ctx* ctx = sc->ctx;
+    E r;
+    memcpy(&r, last_challenge, sizeof(E));
+    sc_final_evals<F><<<(sc->k + 127) / 128, 128, 0, ctx->stream>>>(
+        sc->d_desc + (size_t)(sc->n - 1) * sc->k, sc->k, r, (E*)sc->d_final);
+    DPB_CUDA(cudaGetLastError());
+    DPB_CUDA(cudaMemcpyAsync(out, sc->d_final, sc->k * sizeof(E), cudaMemcpyDeviceToHost, ctx->stream));
+    DPB_CUDA(cudaStreamSynchronize(ctx->stream));
+    return DPB_OK;
+}
+
+}  // namespace dpb
+
+extern "C" {
+
+int dpb_sumcheck_begin(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, uint32_t k,
+                       const dpb_term* terms, uint32_t n_terms, dpb_sc** out) {
+    if (!ctx || !mles || !terms || !out) return fail(DPB_EINVAL, "null argument");
+    if (num_vars < 1 || num_vars > 40) return fail(DPB_EINVAL, "num_vars %u out of range", num_vars);
+    if (k < 1 || k > 65535) return fail(DPB_EINVAL, "table count %u out of range", k);
+    if (n_terms < 1) return fail(DPB_EINVAL, "no terms");
+    const bool gl = is_gl(mles[0] ? mles[0]->dtype : -1);
+    uint32_t d = 0;
+    for (uint32_t t = 0; t < n_terms; t++) {
+        if (terms[t].n_factors > DPB_MAX_FACTORS)
+            return fail(DPB_EINVAL, "term %u has %u factors (max %d)", t, terms[t].n_factors, DPB_MAX_FACTORS);
+        for (uint32_t j = 0; j < terms[t].n_factors; j++)
+            if (terms[t].idx[j] >= k) return fail(DPB_EINVAL, "term %u refers to table %u of %u", t, terms[t].idx[j], k);
+        if (terms[t].n_factors > d) d = terms[t].n_factors;
+    }
+    if (d < 1 || d > 6) return fail(DPB_EINVAL, "degree %u outside 1..6", d);
+
+    dpb_sc* sc = new (std::nothrow) dpb_sc();
+    if (!sc) return fail(DPB_ENOMEM, "host allocation failed");
+    sc->ctx = ctx;
+    sc->gl = gl;
+    sc->n = num_vars;
+    sc->k = k;
+    sc->d = d;
+    sc->n_terms = n_terms;
+    sc->tr.resize(k);
+    const size_t es = gl ? 16 : 32;
+    size_t slab_elems = 0;
+    for (uint32_t j = 0; j < k; j++) {
+        const dpb_mle* m = mles[j];
+        if (!m || m->ctx != ctx || !valid_dtype(m->dtype) || is_gl(m->dtype) != gl) {
+            delete sc;
+            return fail(DPB_EINVAL, "table %u is null, foreign or of another field", j);
+        }
+        const uint32_t nv = log2u(m->len);
+        if (nv < 1 || nv > num_vars) {
+            delete sc;
+            return fail(DPB_EINVAL, "table %u has %u variables, sumcheck has %u", j, nv, num_vars);
+        }
+        sc->tr[j].orig = m->ptr;
+        sc->tr[j].dtype = m->dtype;
+        sc->tr[j].nv = nv;
+        slab_elems += (1ull << (nv - 1)) + (nv >= 2 ? (1ull << (nv - 2)) : 0);
+    }
+    int rc = device_alloc(ctx, slab_elems * es, &sc->slab);
+    if (rc != DPB_OK) {
+        delete sc;
+        return rc;
+    }
+    {
+        char* p = (char*)sc->slab;
+        for (uint32_t j = 0; j < k; j++) {
+            const uint32_t nv = sc->tr[j].nv;
+            sc->tr[j].buf[0] = p;
+            p += (es << (nv - 1));
+            sc->tr[j].buf[1] = nv >= 2 ? p : nullptr;
+            if (nv >= 2) p += (es << (nv - 2));
+        }
+    }
+    // descriptors for every round
+    sc->h_desc.resize((size_t)num_vars * k);
+    sc->h_fold.resize((size_t)num_vars * k);
+    sc->n_fold.assign(num_vars, 0);
+    sc->max_fold_out.assign(num_vars, 0);
+    for (uint32_t i = 0; i < num_vars; i++) {
+        const uint32_t v = num_vars - i;
+        for (uint32_t j = 0; j < k; j++) {
+            const void* ptr;
+            int dt;
+            bool active;
+            table_at_round(sc, j, i, &ptr, &dt, &active);
+            MleDesc& md = sc->h_desc[(size_t)i * k + j];
+            md.ptr = ptr;
+            md.dtype = dt;
+            md.shift = active ? -1 : (int32_t)(v - 1 - sc->tr[j].nv);
+            // fold that must run before round i: tables that were active in round i-1
+            if (i >= 1) {
+                const void* pptr;
+                int pdt;
+                bool pactive;
+                table_at_round(sc, j, i - 1, &pptr, &pdt, &pactive);
+                if (pactive) {
+                    FoldDesc& fd = sc->h_fold[(size_t)i * k + sc->n_fold[i]];
+                    fd.in = pptr;
+                    fd.out = (void*)ptr;
+                    fd.dtype_in = pdt;
+                    fd.pad = 0;
+                    fd.n_out = 1ull << (sc->tr[j].nv - (i - (num_vars - sc->tr[j].nv)));
+                    if (fd.n_out > sc->max_fold_out[i]) sc->max_fold_out[i] = fd.n_out;
+                    sc->n_fold[i]++;
+                }
+            }
+        }
+    }
+    auto cleanup = [&](int code) {
+        dpb_sumcheck_free(sc);
+        return code;
+    };
+    rc = device_alloc(ctx, sc->h_desc.size() * sizeof(MleDesc), (void**)&sc->d_desc);
+    if (rc != DPB_OK) return cleanup(rc);
+    rc = device_alloc(ctx, sc->h_fold.size() * sizeof(FoldDesc), (void**)&sc->d_fold);
+    if (rc != DPB_OK) return cleanup(rc);
+    rc = device_alloc(ctx, k * es, &sc->d_final);
+    if (rc != DPB_OK) return cleanup(rc);
+    cudaError_t e = cudaMemcpyAsync(sc->d_desc, sc->h_desc.data(), sc->h_desc.size() * sizeof(MleDesc),
+                                    cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(sc->d_fold, sc->h_fold.data(), sc->h_fold.size() * sizeof(FoldDesc),
+                            cudaMemcpyHostToDevice, ctx->stream);
+    if (e != cudaSuccess) return cleanup(fail(DPB_ECUDA, "descriptor upload: %s", cudaGetErrorString(e)));
+    rc = gl ? upload_terms<GlFam>(sc, terms) : upload_terms<FrFam>(sc, terms);
+    if (rc != DPB_OK) return cleanup(rc);
+    sc->fused_shape = detect_fused_shape(sc->h_desc.data(), sc->tr.size(), num_vars, terms, n_terms, gl,
+                                         [&](uint32_t j) { return sc->tr[j].nv; },
+                                         [&](uint32_t j) { return sc->tr[j].dtype; });
+    *out = sc;
+    return DPB_OK;
+}
+
+uint32_t dpb_sumcheck_degree(const dpb_sc* sc) { return sc ? sc->d : 0; }
+
+int dpb_sumcheck_round(dpb_sc* sc, const void* prev_challenge, void* out_evals, uint32_t* n_evals) {
+    if (!sc || !out_evals) return fail(DPB_EINVAL, "null argument");
+    if (sc->finished || sc->round >= sc->n) return fail(DPB_ESTATE, "all %u rounds already ran", sc->n);
+    if (sc->round == 0 && prev_challenge) return fail(DPB_ESTATE, "the first round takes no challenge");
+    if (sc->round > 0 && !prev_challenge) return fail(DPB_ESTATE, "round %u needs the previous challenge", sc->round);
+    int rc = sc->gl ? run_round<GlFam>(sc, prev_challenge, out_evals)
+                    : run_round<FrFam>(sc, prev_challenge, out_evals);
+    if (rc != DPB_OK) return rc;
+    if (n_evals) *n_evals = sc->d + 1;
+    sc->round++;
+    return DPB_OK;
+}
+
+int dpb_sumcheck_finish(dpb_sc* sc, const void* last_challenge, void* out_final_evals) {
+    if (!sc || !last_challenge || !out_final_evals) return fail(DPB_EINVAL, "null argument");
+    if (sc->finished) return fail(DPB_ESTATE, "already finished");
+    if (sc->round != sc->n) return fail(DPB_ESTATE, "only %u of %u rounds ran", sc->round, sc->n);
+    int rc = sc->gl ? run_finish<GlFam>(sc, last_challenge, out_final_evals)
+                    : run_finish<FrFam>(sc, last_challenge, out_final_evals);
+    if (rc != DPB_OK) return rc;
+    sc->finished = true;
+    return DPB_OK;
+}
+
+void dpb_sumcheck_free(dpb_sc* sc) {
+    if (!sc) return;
+    device_free(sc->ctx, sc->slab);
+    device_free(sc->ctx, sc->d_desc);
+    device_free(sc->ctx, sc->d_fold);
+    device_free(sc->ctx, sc->d_terms);
+    device_free(sc->ctx, sc->d_final);
+    delete sc;
+}
+
+}  // extern "C"

@@ -1,0 +1,100 @@
+// Host-side plumbing shared by the C-ABI translation units: error reporting,
+// the context, table handles and launch-size helpers.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "family.cuh"
+#include "sumcheck_kernels.cuh"
+
+namespace dpb {
+
+// Message of the last failing call on this host thread.
+std::string& last_error_slot();
+int fail(int code, const char* fmt, ...);
+
+#define DPB_CUDA(call)                                                                  \
+    do {                                                                                \
+        cudaError_t e__ = (call);                                                       \
+        if (e__ != cudaSuccess)                                                         \
+            return ::dpb::fail(e__ == cudaErrorMemoryAllocation ? DPB_ENOMEM : DPB_ECUDA, \
+                               "%s: %s", #call, cudaGetErrorString(e__));               \
+    } while (0)
+
+#define DPB_TRY(call)            \
+    do {                         \
+        int rc__ = (call);       \
+        if (rc__ != DPB_OK) return rc__; \
+    } while (0)
+
+inline bool is_gl(int dtype) { return dtype == DPB_GL_BASE || dtype == DPB_GL_EXT; }
+inline bool valid_dtype(int dtype) { return dtype >= DPB_GL_BASE && dtype <= DPB_FR; }
+inline size_t dtype_size(int dtype) { return dtype == DPB_GL_BASE ? 8 : dtype == DPB_GL_EXT ? 16 : 32; }
+inline int chal_dtype(int dtype) { return is_gl(dtype) ? DPB_GL_EXT : DPB_FR; }
+inline bool is_pow2(uint64_t x) { return x && !(x & (x - 1)); }
+inline uint32_t log2u(uint64_t x) {
+    uint32_t l = 0;
+    while ((1ull << l) < x) l++;
+    return l;
+}
+
+constexpr int kMaxAcc = 8;  // round-polynomial evaluations per launch (degree <= 7)
+
+}  // namespace dpb
+
+struct dpb_ctx {
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;
+    // per-launch reduction scratch (partials are sized for the widest element)
+    void* partials = nullptr;
+    unsigned int* counter = nullptr;
+    uint32_t max_blocks = 0;
+    // mapped pinned buffer the last block of a round writes its result to
+    void* result_host = nullptr;
+    void* result_dev = nullptr;
+    size_t result_bytes = 0;
+    // small device staging area for points / challenges
+    void* stage_dev = nullptr;
+    size_t stage_bytes = 0;
+};
+
+struct dpb_mle {
+    dpb_ctx* ctx = nullptr;
+    int dtype = 0;
+    uint64_t len = 0;
+    void* ptr = nullptr;
+    bool owns = false;
+};
+
+namespace dpb {
+
+inline uint32_t grid_for(const dpb_ctx* ctx, uint64_t work_items, uint32_t per_sm = 8) {
+    uint64_t b = (work_items + kThreads - 1) / kThreads;
+    const uint64_t cap = (uint64_t)ctx->sm_count * per_sm;
+    if (b > cap) b = cap;
+    if (b < 1) b = 1;
+    if (b > ctx->max_blocks) b = ctx->max_blocks;
+    return (uint32_t)b;
+}
+
+template <class F>
+inline ReduceScratch<F> reduce_scratch(const dpb_ctx* ctx) {
+    ReduceScratch<F> rs;
+    rs.partials = (typename F::E*)ctx->partials;
+    rs.counter = ctx->counter;
+    return rs;
+}
+
+int device_alloc(dpb_ctx* ctx, size_t bytes, void** out);
+void device_free(dpb_ctx* ctx, void* p);
+int new_mle(dpb_ctx* ctx, int dtype, uint64_t len, dpb_mle** out);
+// copies `n` challenge elements from host memory to the staging area and returns the device pointer
+int stage_to_device(dpb_ctx* ctx, const void* host, size_t bytes, size_t offset, void** dev);
+
+}  // namespace dpb

@@ -1,0 +1,210 @@
+// BN254 scalar field Fr (the field the reference prover is instantiated on,
+// zkml/src/lookup/logup_gkr/mod.rs:22 `type F = ark_bn254::Fr`), host and device.
+//
+// Storage form: four 64-bit little-endian limbs holding a*R mod r with
+// R = 2^256 (Montgomery form), the in-memory form of arkworks' 4-limb
+// Montgomery backend. Canonical form (plain integer < r, 32 bytes LE) is what
+// ark_serialize writes; conversions are provided.
+//
+// r = 21888242871839275222246405745257275088548364400416034343698204186575808495617
+#pragma once
+#include <cstdint>
+
+#include "field_gl.cuh"  // DPB_HD, mul64wide
+
+namespace dpb {
+
+struct alignas(16) Fr {
+    uint64_t l[4];
+};
+
+// Constants as macros so both host and device code inline them as immediates.
+#define DPB_FR_P0 0x43e1f593f0000001ULL
+#define DPB_FR_P1 0x2833e84879b97091ULL
+#define DPB_FR_P2 0xb85045b68181585dULL
+#define DPB_FR_P3 0x30644e72e131a029ULL
+#define DPB_FR_INV 0xc2e1f593efffffffULL  // -r^{-1} mod 2^64
+// R mod r (Montgomery form of 1)
+#define DPB_FR_R0 0xac96341c4ffffffbULL
+#define DPB_FR_R1 0x36fc76959f60cd29ULL
+#define DPB_FR_R2_ 0x666ea36f7879462eULL
+#define DPB_FR_R3 0x0e0a77c19a07df2fULL
+// R^2 mod r
+#define DPB_FR_RR0 0x1bb8e645ae216da7ULL
+#define DPB_FR_RR1 0x53fe3ab1e35c59e3ULL
+#define DPB_FR_RR2 0x8c49833d53bb8085ULL
+#define DPB_FR_RR3 0x0216d0b17f4e44a5ULL
+
+DPB_HD Fr fr_zero() {
+    Fr r;
+    r.l[0] = r.l[1] = r.l[2] = r.l[3] = 0;
+    return r;
+}
+DPB_HD Fr fr_one() {
+    Fr r;
+    r.l[0] = DPB_FR_R0;
+    r.l[1] = DPB_FR_R1;
+    r.l[2] = DPB_FR_R2_;
+    r.l[3] = DPB_FR_R3;
+    return r;
+}
+DPB_HD Fr fr_rr() {
+    Fr r;
+    r.l[0] = DPB_FR_RR0;
+    r.l[1] = DPB_FR_RR1;
+    r.l[2] = DPB_FR_RR2;
+    r.l[3] = DPB_FR_RR3;
+    return r;
+}
+DPB_HD bool fr_eq(const Fr& a, const Fr& b) {
+    return a.l[0] == b.l[0] && a.l[1] == b.l[1] && a.l[2] == b.l[2] && a.l[3] == b.l[3];
+}
+DPB_HD bool fr_is_zero(const Fr& a) { return (a.l[0] | a.l[1] | a.l[2] | a.l[3]) == 0; }
+
+// a + b + carry_in -> sum, carry_out
+DPB_HD uint64_t adc(uint64_t a, uint64_t b, uint64_t& carry) {
+    uint64_t s = a + b;
+    uint64_t c1 = s < a;
+    uint64_t t = s + carry;
+    uint64_t c2 = t < s;
+    carry = c1 + c2;
+    return t;
+}
+// a - b - borrow_in -> diff, borrow_out
+DPB_HD uint64_t sbb(uint64_t a, uint64_t b, uint64_t& borrow) {
+    uint64_t d = a - b;
+    uint64_t b1 = a < b;
+    uint64_t t = d - borrow;
+    uint64_t b2 = d < borrow;
+    borrow = b1 + b2;
+    return t;
+}
+// acc + x*y + carry -> low 64 bits; carry <- high 64 bits
+DPB_HD uint64_t mac(uint64_t acc, uint64_t x, uint64_t y, uint64_t& carry) {
+    uint64_t lo, hi;
+    mul64wide(x, y, lo, hi);
+    uint64_t s = lo + acc;
+    hi += (s < lo);
+    uint64_t t = s + carry;
+    hi += (t < s);
+    carry = hi;
+    return t;
+}
+
+// Conditionally subtract r so the result is < r (input < 2r).
+DPB_HD Fr fr_reduce_once(const Fr& a) {
+    uint64_t bw = 0;
+    Fr d;
+    d.l[0] = sbb(a.l[0], DPB_FR_P0, bw);
+    d.l[1] = sbb(a.l[1], DPB_FR_P1, bw);
+    d.l[2] = sbb(a.l[2], DPB_FR_P2, bw);
+    d.l[3] = sbb(a.l[3], DPB_FR_P3, bw);
+    return bw ? a : d;
+}
+
+DPB_HD Fr fr_add(const Fr& a, const Fr& b) {
+    uint64_t c = 0;
+    Fr s;
+    s.l[0] = adc(a.l[0], b.l[0], c);
+    s.l[1] = adc(a.l[1], b.l[1], c);
+    s.l[2] = adc(a.l[2], b.l[2], c);
+    s.l[3] = adc(a.l[3], b.l[3], c);  // r < 2^254: no carry out
+    return fr_reduce_once(s);
+}
+
+DPB_HD Fr fr_sub(const Fr& a, const Fr& b) {
+    uint64_t bw = 0;
+    Fr d;
+    d.l[0] = sbb(a.l[0], b.l[0], bw);
+    d.l[1] = sbb(a.l[1], b.l[1], bw);
+    d.l[2] = sbb(a.l[2], b.l[2], bw);
+    d.l[3] = sbb(a.l[3], b.l[3], bw);
+    if (bw) {
+        uint64_t c = 0;
+        d.l[0] = adc(d.l[0], DPB_FR_P0, c);
+        d.l[1] = adc(d.l[1], DPB_FR_P1, c);
+        d.l[2] = adc(d.l[2], DPB_FR_P2, c);
+        d.l[3] = adc(d.l[3], DPB_FR_P3, c);
+    }
+    return d;
+}
+
+DPB_HD Fr fr_neg(const Fr& a) { return fr_is_zero(a) ? a : fr_sub(fr_zero(), a); }
+
+// Montgomery product a*b/R mod r (coarsely integrated operand scanning; the
+// top limb of r leaves two spare bits so the running sum fits five limbs).
+DPB_HD Fr fr_mul(const Fr& a, const Fr& b) {
+    const uint64_t p[4] = {DPB_FR_P0, DPB_FR_P1, DPB_FR_P2, DPB_FR_P3};
+    uint64_t t0 = 0, t1 = 0, t2 = 0, t3 = 0, t4 = 0;
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
+    for (int i = 0; i < 4; i++) {
+        uint64_t c = 0;
+        uint64_t bi = b.l[i];
+        t0 = mac(t0, a.l[0], bi, c);
+        t1 = mac(t1, a.l[1], bi, c);
+        t2 = mac(t2, a.l[2], bi, c);
+        t3 = mac(t3, a.l[3], bi, c);
+        t4 += c;
+        uint64_t m = t0 * DPB_FR_INV;
+        c = 0;
+        (void)mac(t0, m, p[0], c);
+        t0 = mac(t1, m, p[1], c);
+        t1 = mac(t2, m, p[2], c);
+        t2 = mac(t3, m, p[3], c);
+        t3 = t4 + c;
+        t4 = 0;
+    }
+    Fr r;
+    r.l[0] = t0;
+    r.l[1] = t1;
+    r.l[2] = t2;
+    r.l[3] = t3;
+    return fr_reduce_once(r);
+}
+
+DPB_HD Fr fr_sqr(const Fr& a) { return fr_mul(a, a); }
+DPB_HD Fr fr_double(const Fr& a) { return fr_add(a, a); }
+
+// canonical integer (< r) -> Montgomery form
+DPB_HD Fr fr_to_mont(const Fr& a) { return fr_mul(a, fr_rr()); }
+// Montgomery form -> canonical integer
+DPB_HD Fr fr_from_mont(const Fr& a) {
+    Fr one;
+    one.l[0] = 1;
+    one.l[1] = one.l[2] = one.l[3] = 0;
+    return fr_mul(a, one);
+}
+// Signed 64-bit integer -> field element; negative x maps to r - |x|, the
+// rule of the reference's Element -> field conversion
+// (zkml/src/quantization/mod.rs:220-267).
+DPB_HD Fr fr_from_i64(int64_t x) {
+    Fr a;
+    uint64_t mag = x < 0 ? (uint64_t)0 - (uint64_t)x : (uint64_t)x;
+    a.l[0] = mag;
+    a.l[1] = a.l[2] = a.l[3] = 0;
+    a = fr_to_mont(a);
+    return x < 0 ? fr_neg(a) : a;
+}
+DPB_HD Fr fr_from_u64(uint64_t x) {
+    Fr a;
+    a.l[0] = x;
+    a.l[1] = a.l[2] = a.l[3] = 0;
+    return fr_to_mont(a);
+}
+
+inline Fr fr_pow(Fr a, const uint64_t e[4]) {
+    Fr r = fr_one();
+    for (int i = 255; i >= 0; i--) {
+        r = fr_mul(r, r);
+        if ((e[i / 64] >> (i % 64)) & 1) r = fr_mul(r, a);
+    }
+    return r;
+}
+inline Fr fr_inv(const Fr& a) {
+    const uint64_t e[4] = {DPB_FR_P0 - 2, DPB_FR_P1, DPB_FR_P2, DPB_FR_P3};
+    return fr_pow(a, e);
+}
+
+}  // namespace dpb

@@ -1,0 +1,238 @@
+// Fused sumcheck rounds for the shape that dominates the byte count: a single
+// product term  f_1 * f_2 * ... * f_K  (coefficient one) over K tables that all
+// have every variable of the sumcheck and share one storage layout.  This is
+// the f*g*h microbenchmark shape and the v1*v2*eq shape of the Hadamard
+// prover (zkml/src/layers/hadamard.rs:106-115).
+//
+// Round 0 only evaluates.  Every later round reads the previous tables ONCE,
+// binds the previous variable with the challenge, writes the half-size tables
+// and evaluates the new round polynomial from the values it still holds in
+// registers — the minimum traffic a sumcheck with host-side challenges allows:
+// per table 2*s0 + 2*s1 bytes per entry of the input (s0, s1 = entry size
+// before / after the first fold).
+#pragma once
+#include <functional>
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace dpb {
+
+constexpr int kFusedNone = 0;
+constexpr int kFusedProduct = 1;  // single product of K = k full-size tables, coefficient one
+
+// ---- input adaptors --------------------------------------------------------
+// Goldilocks tables that still hold base-field entries are multiplied in the
+// base field (one 64-bit multiply instead of three).
+template <class F, bool BASE>
+struct FusedIn;
+
+template <>
+struct FusedIn<GlFam, true> {
+    typedef uint64_t T;
+    __device__ __forceinline__ static void load4(const void* p, uint64_t q, T (&a)[4]) {
+        const ulonglong2* s = (const ulonglong2*)p + 2 * q;
+        const ulonglong2 u = s[0], v = s[1];
+        a[0] = u.x; a[1] = u.y; a[2] = v.x; a[3] = v.y;
+    }
+    __device__ __forceinline__ static void load2(const void* p, uint64_t q, T (&a)[2]) {
+        const ulonglong2 u = ((const ulonglong2*)p)[q];
+        a[0] = u.x; a[1] = u.y;
+    }
+    __device__ __forceinline__ static Gl2 fold(T a0, T a1, const Gl2& r) {
+        const uint64_t d = gl_sub(a1, a0);
+        return gl2_make(gl_add(a0, gl_mul(r.c0, d)), gl_mul(r.c1, d));
+    }
+    __device__ __forceinline__ static T add(T a, T b) { return gl_add(a, b); }
+    __device__ __forceinline__ static T sub(T a, T b) { return gl_sub(a, b); }
+    __device__ __forceinline__ static T mul(T a, T b) { return gl_mul(a, b); }
+    __device__ __forceinline__ static T zero() { return 0; }
+    __device__ __forceinline__ static Gl2 widen(T a) { return gl2_from_base(a); }
+};
+
+template <class F>
+struct FusedIn<F, false> {
+    typedef typename F::E T;
+    __device__ __forceinline__ static void load4(const void* p, uint64_t q, T (&a)[4]) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) a[i] = F::load(p, F::kChalDtype, 4 * q + i);
+    }
+    __device__ __forceinline__ static void load2(const void* p, uint64_t q, T (&a)[2]) {
+        a[0] = F::load(p, F::kChalDtype, 2 * q);
+        a[1] = F::load(p, F::kChalDtype, 2 * q + 1);
+    }
+    __device__ __forceinline__ static T fold(const T& a0, const T& a1, const T& r) {
+        return F::add(a0, F::mul(r, F::sub(a1, a0)));
+    }
+    __device__ __forceinline__ static T add(const T& a, const T& b) { return F::add(a, b); }
+    __device__ __forceinline__ static T sub(const T& a, const T& b) { return F::sub(a, b); }
+    __device__ __forceinline__ static T mul(const T& a, const T& b) { return F::mul(a, b); }
+    __device__ __forceinline__ static T zero() { return F::zero(); }
+    __device__ __forceinline__ static T widen(const T& a) { return a; }
+};
+
+template <int K>
+struct FusedPtrs {
+    const void* in[K];
+    void* out[K];
+};
+
+// Round 0: acc[x] = sum_p prod_j (f_j[2p] + x (f_j[2p+1] - f_j[2p])),  x = 0..K.
+template <class F, int K, bool BASE>
+__global__ void __launch_bounds__(kThreads)
+    fused_product_eval0(FusedPtrs<K> ptrs, uint64_t n_pairs, ReduceScratch<F> rs,
+                        typename F::E* out) {
+    typedef FusedIn<F, BASE> In;
+    typedef typename In::T T;
+    typedef typename F::E E;
+    T acc[K + 1];
+#pragma unroll
+    for (int x = 0; x <= K; x++) acc[x] = In::zero();
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t p = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; p < n_pairs; p += stride) {
+        T val[K], delta[K];
+#pragma unroll
+        for (int j = 0; j < K; j++) {
+            T a[2];
+            In::load2(ptrs.in[j], p, a);
+            val[j] = a[0];
+            delta[j] = In::sub(a[1], a[0]);
+        }
+#pragma unroll
+        for (int x = 0; x <= K; x++) {
+            T prod = val[0];
+#pragma unroll
+            for (int j = 1; j < K; j++) prod = In::mul(prod, val[j]);
+            acc[x] = In::add(acc[x], prod);
+            if (x < K) {
+#pragma unroll
+                for (int j = 0; j < K; j++) val[j] = In::add(val[j], delta[j]);
+            }
+        }
+    }
+    E wide[K + 1];
+#pragma unroll
+    for (int x = 0; x <= K; x++) wide[x] = In::widen(acc[x]);
+    grid_sum_publish<F, K + 1>(wide, rs, out);
+}
+
+// Rounds >= 1: bind the previous variable with r, write the folded tables,
+// evaluate the new round polynomial.  One thread per OUTPUT pair: it reads
+// entries 4p..4p+3 of every input table and writes entries 2p, 2p+1.
+template <class F, int K, bool BASE_IN>
+__global__ void __launch_bounds__(kThreads)
+    fused_product_fold_eval(FusedPtrs<K> ptrs, typename F::E r, uint64_t n_pairs,
+                            ReduceScratch<F> rs, typename F::E* out) {
+    typedef FusedIn<F, BASE_IN> In;
+    typedef typename In::T T;
+    typedef typename F::E E;
+    E acc[K + 1];
+#pragma unroll
+    for (int x = 0; x <= K; x++) acc[x] = F::zero();
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t p = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; p < n_pairs; p += stride) {
+        E val[K], delta[K];
+#pragma unroll
+        for (int j = 0; j < K; j++) {
+            T a[4];
+            In::load4(ptrs.in[j], p, a);
+            const E f0 = In::fold(a[0], a[1], r);
+            const E f1 = In::fold(a[2], a[3], r);
+            F::store(ptrs.out[j], 2 * p, f0);
+            F::store(ptrs.out[j], 2 * p + 1, f1);
+            val[j] = f0;
+            delta[j] = F::sub(f1, f0);
+        }
+#pragma unroll
+        for (int x = 0; x <= K; x++) {
+            E prod = val[0];
+#pragma unroll
+            for (int j = 1; j < K; j++) prod = F::mul(prod, val[j]);
+            acc[x] = F::add(acc[x], prod);
+            if (x < K) {
+#pragma unroll
+                for (int j = 0; j < K; j++) val[j] = F::add(val[j], delta[j]);
+            }
+        }
+    }
+    grid_sum_publish<F, K + 1>(acc, rs, out);
+}
+
+// ---- host side ---------------------------------------------------------------
+// Returns kFusedProduct when the term list is one coefficient-one product of
+// all k (2..4) tables, each used once, all full-size and in one layout.
+inline int detect_fused_shape(const MleDesc*, size_t k, uint32_t num_vars, const dpb_term* terms,
+                              uint32_t n_terms, bool gl, const std::function<uint32_t(uint32_t)>& nv,
+                              const std::function<int(uint32_t)>& dtype) {
+    if (n_terms != 1 || k < 2 || k > 4 || terms[0].n_factors != k || num_vars < 2) return kFusedNone;
+    bool seen[4] = {false, false, false, false};
+    for (uint32_t j = 0; j < k; j++) {
+        const uint32_t id = terms[0].idx[j];
+        if (id >= k || seen[id]) return kFusedNone;
+        seen[id] = true;
+        if (nv(j) != num_vars || dtype(j) != dtype(0)) return kFusedNone;
+    }
+    if (gl) {
+        Gl2 c;
+        memcpy(&c, terms[0].coeff, sizeof c);
+        if (!GlFam::is_one(c)) return kFusedNone;
+    } else {
+        Fr c;
+        memcpy(&c, terms[0].coeff, sizeof c);
+        if (!FrFam::is_one(c)) return kFusedNone;
+    }
+    return kFusedProduct;
+}
+
+template <class F, int K>
+static int fused_product_round(dpb_ctx* ctx, const MleDesc* desc, const FoldDesc* folds, uint32_t round,
+                               typename F::E r, uint64_t n_pairs) {
+    typedef typename F::E E;
+    FusedPtrs<K> ptrs;
+    const ReduceScratch<F> rs = reduce_scratch<F>(ctx);
+    E* out = (E*)ctx->result_dev;
+    const uint32_t grid = grid_for(ctx, n_pairs, 4);
+    if (round == 0) {
+        for (int j = 0; j < K; j++) {
+            ptrs.in[j] = desc[j].ptr;
+            ptrs.out[j] = nullptr;
+        }
+        if (desc[0].dtype == DPB_GL_BASE) {
+            if constexpr (std::is_same<F, GlFam>::value)
+                fused_product_eval0<F, K, true><<<grid, kThreads, 0, ctx->stream>>>(ptrs, n_pairs, rs, out);
+        } else {
+            fused_product_eval0<F, K, false><<<grid, kThreads, 0, ctx->stream>>>(ptrs, n_pairs, rs, out);
+        }
+    } else {
+        // folds[] lists the tables in registration order (all are active)
+        for (int j = 0; j < K; j++) {
+            ptrs.in[j] = folds[j].in;
+            ptrs.out[j] = folds[j].out;
+        }
+        if (folds[0].dtype_in == DPB_GL_BASE) {
+            if constexpr (std::is_same<F, GlFam>::value)
+                fused_product_fold_eval<F, K, true><<<grid, kThreads, 0, ctx->stream>>>(ptrs, r, n_pairs, rs, out);
+        } else {
+            fused_product_fold_eval<F, K, false><<<grid, kThreads, 0, ctx->stream>>>(ptrs, r, n_pairs, rs, out);
+        }
+    }
+    return DPB_OK;
+}
+
+template <class F>
+static int fused_round(int shape, dpb_ctx* ctx, const MleDesc* desc, const FoldDesc* folds, uint32_t k,
+                       uint32_t round, typename F::E r, uint64_t n_pairs, bool* done) {
+    *done = false;
+    if (shape != kFusedProduct) return DPB_OK;
+    int rc = DPB_OK;
+    switch (k) {
+        case 2: rc = fused_product_round<F, 2>(ctx, desc, folds, round, r, n_pairs); break;
+        case 3: rc = fused_product_round<F, 3>(ctx, desc, folds, round, r, n_pairs); break;
+        case 4: rc = fused_product_round<F, 4>(ctx, desc, folds, round, r, n_pairs); break;
+        default: return DPB_OK;
+    }
+    *done = (rc == DPB_OK);
+    return rc;
+}
+
+}  // namespace dpb

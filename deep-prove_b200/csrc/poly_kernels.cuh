@@ -1,0 +1,102 @@
+// Multilinear-table kernels outside the sumcheck loop: layout conversion, eq
+// tables, partial evaluation of the top / bottom variables.
+#pragma once
+#include "family.cuh"
+
+namespace dpb {
+
+// ---- layout conversion ---------------------------------------------------
+// in and out may be the same array
+__global__ void fr_canonical_to_mont(const Fr* in, Fr* out, uint64_t n) {
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        FrFam::store(out, i, fr_to_mont(FrFam::load(in, DPB_FR, i)));
+}
+__global__ void fr_mont_to_canonical(const Fr* in, Fr* out, uint64_t n) {
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        FrFam::store(out, i, fr_from_mont(FrFam::load(in, DPB_FR, i)));
+}
+__global__ void fr_from_i64_kernel(const int64_t* __restrict__ in, Fr* __restrict__ out,
+                                   uint64_t n) {
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        FrFam::store(out, i, fr_from_i64(in[i]));
+}
+__global__ void gl_from_i64_kernel(const int64_t* __restrict__ in, uint64_t* __restrict__ out,
+                                   uint64_t n) {
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const int64_t x = in[i];
+        // |x| < 2^63 < p, so the magnitude is already canonical
+        out[i] = x < 0 ? GL_P - ((uint64_t)0 - (uint64_t)x) : (uint64_t)x;
+    }
+}
+
+// ---- eq tables -------------------------------------------------------------
+// out[i] = prod_j (bit_j(i) ? pt[j] : 1 - pt[j]),  i < 2^m, directly (m small).
+template <class F>
+__global__ void eq_direct(const typename F::E* __restrict__ pt, uint32_t m,
+                          typename F::E* __restrict__ out) {
+    typedef typename F::E E;
+    const uint64_t n = 1ull << m;
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        E acc = F::one();
+        for (uint32_t j = 0; j < m; j++) {
+            const E r = pt[j];
+            acc = F::mul(acc, ((i >> j) & 1) ? r : F::sub(F::one(), r));
+        }
+        F::store(out, i, acc);
+    }
+}
+// out[i] = hi[i >> lo_bits] * lo[i & (2^lo_bits - 1)]
+template <class F>
+__global__ void eq_combine(const typename F::E* __restrict__ lo, uint32_t lo_bits,
+                           const typename F::E* __restrict__ hi, uint64_t n,
+                           typename F::E* __restrict__ out) {
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    const uint64_t mask = (1ull << lo_bits) - 1;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        F::store(out, i,
+                 F::mul(F::load(hi, F::kChalDtype, i >> lo_bits), F::load(lo, F::kChalDtype, i & mask)));
+}
+
+// ---- partial evaluation ----------------------------------------------------
+// Top g variables: out[j] = sum_{h < 2^g} w[h] * in[h * n_out + j].
+template <class F>
+__global__ void fix_high_pass(const void* __restrict__ in, int dtype_in,
+                              const typename F::E* __restrict__ w, uint32_t g, uint64_t n_out,
+                              typename F::E* __restrict__ out) {
+    typedef typename F::E E;
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    const uint32_t H = 1u << g;
+    for (uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; j < n_out; j += stride) {
+        E acc = F::zero();
+        for (uint32_t h = 0; h < H; h++)
+            acc = F::add(acc, F::mul(w[h], F::load(in, dtype_in, (uint64_t)h * n_out + j)));
+        F::store(out, j, acc);
+    }
+}
+
+// Bottom g variables (g <= 5): out[j] = sum_{l < 2^g} w[l] * in[j * 2^g + l].
+// One thread per input entry; groups of 2^g lanes add up with shuffles.
+// blockDim.x must be a multiple of 32; n_in is a multiple of 2^g.
+template <class F>
+__global__ void fix_low_pass(const void* __restrict__ in, int dtype_in,
+                             const typename F::E* __restrict__ w, uint32_t g, uint64_t n_in,
+                             typename F::E* __restrict__ out) {
+    typedef typename F::E E;
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    const uint32_t G = 1u << g;
+    // every lane of a warp runs the same number of iterations: round n_in up to a warp multiple
+    const uint64_t n_round = (n_in + 31) & ~31ull;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_round; i += stride) {
+        E v = F::zero();
+        if (i < n_in) v = F::mul(w[i & (G - 1)], F::load(in, dtype_in, i));
+        for (uint32_t off = G >> 1; off > 0; off >>= 1) v = F::add(v, F::shfl_down(v, off));
+        if (i < n_in && (i & (G - 1)) == 0) F::store(out, i >> g, v);
+    }
+}
+
+}  // namespace dpb

@@ -1,0 +1,208 @@
+// Sumcheck prover kernels: per-round evaluation of product terms over the
+// remaining hypercube, and the fold that binds one variable.
+//
+// Round i of a sumcheck over n variables sees every table with n-i variables;
+// entries 2p and 2p+1 differ in the variable being bound.  The round
+// polynomial is returned as its evaluations at 0..=D.
+#pragma once
+#include "family.cuh"
+
+namespace dpb {
+
+// One registered table as a round sees it.
+struct MleDesc {
+    const void* ptr;
+    int32_t dtype;  // storage layout of `ptr`
+    int32_t shift;  // < 0: table has all remaining variables (entries 2p, 2p+1);
+                    // >= 0: table is constant in this round, entry p >> shift
+};
+
+struct FoldDesc {
+    const void* in;
+    void* out;
+    int32_t dtype_in;
+    uint32_t pad;
+    uint64_t n_out;
+};
+
+template <class F>
+struct TermDev {
+    typename F::E coeff;
+    uint32_t n_factors;
+    uint32_t coeff_is_one;
+    uint16_t idx[DPB_MAX_FACTORS];
+};
+
+// Scratch a round reduction needs: per-block partial sums and a ticket counter.
+template <class F>
+struct ReduceScratch {
+    typename F::E* partials;  // [max_blocks][NACC]
+    unsigned int* counter;    // zero between launches
+};
+
+constexpr int kThreads = 256;
+constexpr int kMaxWarps = kThreads / 32;
+
+// Sums acc[] over the block; thread 0 ends up holding the totals.
+template <class F, int NACC>
+__device__ __forceinline__ void block_sum(typename F::E (&acc)[NACC]) {
+    typedef typename F::E E;
+    __shared__ E sm[NACC][kMaxWarps];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+        for (int i = 0; i < NACC; i++) acc[i] = F::add(acc[i], F::shfl_down(acc[i], off));
+    }
+    __syncthreads();  // protects sm[] when block_sum is called twice
+    if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < NACC; i++) sm[i][warp] = acc[i];
+    }
+    __syncthreads();
+    if (warp == 0) {
+        const int nwarps = (blockDim.x + 31) >> 5;
+#pragma unroll
+        for (int i = 0; i < NACC; i++) acc[i] = lane < nwarps ? sm[i][lane] : F::zero();
+#pragma unroll
+        for (int off = kMaxWarps / 2; off > 0; off >>= 1) {
+#pragma unroll
+            for (int i = 0; i < NACC; i++) acc[i] = F::add(acc[i], F::shfl_down(acc[i], off));
+        }
+    }
+}
+
+// Grid-wide sum of per-thread accumulators.  Every block publishes its partial
+// sums; the block that draws the last ticket adds them up and writes NACC
+// elements to `out` (device memory or mapped host memory).  The counter is
+// left at zero for the next launch.
+template <class F, int NACC>
+__device__ __forceinline__ void grid_sum_publish(typename F::E (&acc)[NACC], ReduceScratch<F> rs,
+                                                 typename F::E* out) {
+    typedef typename F::E E;
+    __shared__ bool is_last;
+    block_sum<F, NACC>(acc);
+    if (gridDim.x == 1) {
+        if (threadIdx.x == 0) {
+#pragma unroll
+            for (int i = 0; i < NACC; i++) out[i] = acc[i];
+            __threadfence_system();
+        }
+        return;
+    }
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int i = 0; i < NACC; i++) rs.partials[(size_t)blockIdx.x * NACC + i] = acc[i];
+        __threadfence();
+        const unsigned int t = atomicAdd(rs.counter, 1u);
+        is_last = (t == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    E tot[NACC];
+#pragma unroll
+    for (int i = 0; i < NACC; i++) tot[i] = F::zero();
+    const volatile uint64_t* pw = (const volatile uint64_t*)rs.partials;
+    constexpr int W = sizeof(E) / 8;
+    for (unsigned int b = threadIdx.x; b < gridDim.x; b += blockDim.x) {
+#pragma unroll
+        for (int i = 0; i < NACC; i++) {
+            E v;
+            uint64_t* vw = (uint64_t*)&v;
+#pragma unroll
+            for (int w = 0; w < W; w++) vw[w] = pw[((size_t)b * NACC + i) * W + w];
+            tot[i] = F::add(tot[i], v);
+        }
+    }
+    block_sum<F, NACC>(tot);
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int i = 0; i < NACC; i++) out[i] = tot[i];
+        *rs.counter = 0;
+        __threadfence_system();
+    }
+}
+
+// Generic round evaluation: any list of product terms over any tables.
+// acc[x] = sum_p sum_t coeff_t * prod_j f_tj(x; p),  f(x; p) = f[2p] + x (f[2p+1] - f[2p]).
+template <class F, int D>
+__global__ void __launch_bounds__(kThreads)
+    sc_eval_generic(const MleDesc* __restrict__ mles, const TermDev<F>* __restrict__ terms,
+                    uint32_t n_terms, uint64_t n_pairs, ReduceScratch<F> rs,
+                    typename F::E* out) {
+    typedef typename F::E E;
+    E acc[D + 1];
+#pragma unroll
+    for (int x = 0; x <= D; x++) acc[x] = F::zero();
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t p = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; p < n_pairs; p += stride) {
+        for (uint32_t t = 0; t < n_terms; t++) {
+            const TermDev<F>& tm = terms[t];
+            E prod[D + 1];
+            const uint32_t nf = tm.n_factors;
+            for (uint32_t j = 0; j < nf; j++) {
+                const MleDesc md = mles[tm.idx[j]];
+                E f0, f1;
+                if (md.shift < 0) {
+                    F::load_pair(md.ptr, md.dtype, p, f0, f1);
+                } else {
+                    f0 = F::load(md.ptr, md.dtype, p >> md.shift);
+                    f1 = f0;
+                }
+                if (j == 0 && !tm.coeff_is_one) {
+                    f0 = F::mul(f0, tm.coeff);
+                    f1 = F::mul(f1, tm.coeff);
+                }
+                const E delta = F::sub(f1, f0);
+                E val = f0;
+#pragma unroll
+                for (int x = 0; x <= D; x++) {
+                    prod[x] = (j == 0) ? val : F::mul(prod[x], val);
+                    if (x < D) val = F::add(val, delta);
+                }
+            }
+            if (nf == 0) {
+                // constant term: contributes coeff once per point of the pair (x-independent)
+#pragma unroll
+                for (int x = 0; x <= D; x++) acc[x] = F::add(acc[x], tm.coeff);
+            } else {
+#pragma unroll
+                for (int x = 0; x <= D; x++) acc[x] = F::add(acc[x], prod[x]);
+            }
+        }
+    }
+    grid_sum_publish<F, D + 1>(acc, rs, out);
+}
+
+// Binds the lowest remaining variable of several tables in one launch:
+// out[p] = in[2p] + r * (in[2p+1] - in[2p]).   blockIdx.y selects the table.
+template <class F>
+__global__ void __launch_bounds__(kThreads)
+    sc_fold_generic(const FoldDesc* __restrict__ descs, typename F::E r) {
+    typedef typename F::E E;
+    const FoldDesc d = descs[blockIdx.y];
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t p = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; p < d.n_out; p += stride) {
+        E f0, f1;
+        F::load_pair(d.in, d.dtype_in, p, f0, f1);
+        F::store(d.out, p, F::add(f0, F::mul(r, F::sub(f1, f0))));
+    }
+}
+
+// Last step of a sumcheck: every table has two entries left; bind the final
+// variable and collect one value per table.
+template <class F>
+__global__ void sc_final_evals(const MleDesc* __restrict__ mles, uint32_t k, typename F::E r,
+                               typename F::E* out) {
+    typedef typename F::E E;
+    const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= k) return;
+    const MleDesc md = mles[j];
+    E f0, f1;
+    F::load_pair(md.ptr, md.dtype, 0, f0, f1);
+    out[j] = F::add(f0, F::mul(r, F::sub(f1, f0)));
+    if (j == 0) __threadfence_system();
+}
+
+}  // namespace dpb

@@ -1,0 +1,173 @@
+/*
+ * dpb — C ABI of the B200 (sm_100a) sumcheck / multilinear-fold / logup-GKR
+ * prover back end.
+ *
+ * The reference reaches this path through ordinary Rust calls into the
+ * `dp-crypto` crate (Cargo.toml:42); there is no FFI in the reference.  Each
+ * entry point below names the reference call (file:line, paths relative to the
+ * reference repository) that a thin Rust shim inside `dp-crypto` would forward
+ * to it.  The Fiat-Shamir transcript never crosses this boundary: the host
+ * drives a sumcheck one challenge at a time.
+ *
+ * Conventions
+ *  - Every function returns DPB_OK (0) or a negative status and never aborts,
+ *    traps or throws.  dpb_last_error() gives a message for the calling thread.
+ *  - Handles are owned by the caller and freed explicitly.  A dpb_ctx is used
+ *    from one host thread at a time; kernels run on a stream private to it.
+ *  - Host buffers are only read or written for the duration of the call.
+ *  - Field elements cross the boundary in these layouts (all little-endian):
+ *      DPB_GL_BASE  Goldilocks base element, canonical uint64          (8 B)
+ *      DPB_GL_EXT   Goldilocks quadratic extension c0 + c1*X, X^2 = 7  (16 B)
+ *      DPB_FR       BN254 Fr, 4 x uint64 Montgomery limbs (a*2^256 mod r),
+ *                   the in-memory form of ark_ff's 4-limb Montgomery backend
+ *                   (32 B)
+ *    "challenge element" means DPB_GL_EXT for the Goldilocks family and
+ *    DPB_FR for BN254.
+ *  - Multilinear tables are indexed little-endian: bit i of the index is
+ *    variable i (zkml/src/lib.rs:357-369).  Sumcheck round i binds variable i.
+ */
+#ifndef DPB_H
+#define DPB_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DPB_OK 0
+#define DPB_EINVAL (-1)   /* bad argument, size or handle */
+#define DPB_ENOMEM (-2)   /* device or host allocation failed */
+#define DPB_ECUDA (-3)    /* CUDA runtime error */
+#define DPB_ETIMEOUT (-4) /* a bounded device-side wait ran out */
+#define DPB_ESTATE (-5)   /* call made in the wrong state */
+#define DPB_ENCCL (-6)    /* NCCL error or library unavailable */
+
+/* element layouts */
+#define DPB_GL_BASE 0
+#define DPB_GL_EXT 1
+#define DPB_FR 2
+
+/* forms accepted by dpb_mle_from_host for DPB_FR tables */
+#define DPB_FORM_NATIVE 0    /* already in the layout of `dtype` */
+#define DPB_FORM_CANONICAL 1 /* DPB_FR only: 32-byte canonical integers */
+#define DPB_FORM_I64 2       /* signed 64-bit integers, negative x -> p - |x|
+                                (zkml/src/quantization/mod.rs:220-267) */
+
+typedef struct dpb_ctx dpb_ctx;
+typedef struct dpb_mle dpb_mle;
+typedef struct dpb_sc dpb_sc;
+typedef struct dpb_logup dpb_logup;
+
+/* One product term  coeff * prod_j mle[idx[j]]  of a virtual polynomial, the
+ * monomial form `VirtualPolynomialsBuilder::to_virtual_polys` produces
+ * (zkml/src/layers/einsum/prove.rs:171-182).  `coeff` is a challenge element
+ * stored in the first 16 (Goldilocks) or 32 (BN254) bytes. */
+#define DPB_MAX_FACTORS 8
+typedef struct dpb_term {
+    uint8_t coeff[32];
+    uint32_t n_factors;
+    uint16_t idx[DPB_MAX_FACTORS];
+} dpb_term;
+
+/* ---- context ----------------------------------------------------------- */
+/* Creates a context on CUDA device `device`.  Fails with DPB_ECUDA when no
+ * usable GPU is present: there is no CPU fallback. */
+int dpb_init(int device, dpb_ctx** out);
+void dpb_shutdown(dpb_ctx* ctx);
+const char* dpb_last_error(void);
+/* Blocks until all work queued on the context's stream has finished. */
+int dpb_sync(dpb_ctx* ctx);
+/* The context's CUDA stream (a cudaStream_t), for callers that time with
+ * CUDA events or order their own copies against it. */
+void* dpb_stream(dpb_ctx* ctx);
+
+/* ---- multilinear tables (dp_crypto::poly::dense::DensePolynomial) ------ */
+/* Uploads `len` (a power of two) evaluations from host memory.
+ * Replaces DensePolynomial::new / new_from_smart_slice
+ * (zkml/src/lookup/logup_gkr/circuit.rs:262-269) and Tensor::to_field_mle
+ * (zkml/src/layers/hadamard.rs:104-105) for DPB_FORM_I64. */
+int dpb_mle_from_host(dpb_ctx* ctx, int dtype, const void* evals, uint64_t len, int form,
+                      dpb_mle** out);
+/* Wraps device memory the caller already owns (no copy, not freed). */
+int dpb_mle_from_device(dpb_ctx* ctx, int dtype, void* dev_ptr, uint64_t len, dpb_mle** out);
+/* Allocates an uninitialised device table. */
+int dpb_mle_alloc(dpb_ctx* ctx, int dtype, uint64_t len, dpb_mle** out);
+int dpb_mle_free(dpb_mle* mle);
+/* Copies the table back (DensePolynomial::evals). `form` as above; DPB_FORM_I64 is invalid. */
+int dpb_mle_to_host(const dpb_mle* mle, void* out, uint64_t len, int form);
+uint64_t dpb_mle_len(const dpb_mle* mle);
+int dpb_mle_dtype(const dpb_mle* mle);
+void* dpb_mle_device_ptr(const dpb_mle* mle);
+/* A borrowed view of `len` elements starting at `offset` (DensePolynomial::as_view_chunks,
+ * and the low/high half split of zkml/src/lookup/logup_gkr/circuit.rs:260-261). */
+int dpb_mle_view(const dpb_mle* mle, uint64_t offset, uint64_t len, dpb_mle** out);
+
+/* eq(x, point) for all x in {0,1}^m, little-endian index
+ * (dp_crypto::poly::eq::evals; call sites zkml/src/lookup/logup_gkr/prover.rs:247-249,
+ * zkml/src/layers/hadamard.rs:103).  `point` holds m challenge elements on the host. */
+int dpb_eq_table(dpb_ctx* ctx, int family_dtype, const void* point, uint32_t m, dpb_mle** out);
+
+/* Binds the top k variables (variable n-k+j := point[j]) -> table of len/2^k.
+ * DensePolynomial::fix_high_variables{,_parallel}
+ * (zkml/src/layers/transformer/positional/rope.rs:556, zkml/src/iop/prover.rs:448). */
+int dpb_fix_high(dpb_ctx* ctx, const dpb_mle* mle, const void* point, uint32_t k, dpb_mle** out);
+/* Binds the bottom k variables (variable j := point[j]).
+ * DensePolynomial::fix_low_variables{,_in_place_parallel}
+ * (zkml/src/layers/transformer/embeddings.rs:432, zkml/src/layers/pooling.rs:933). */
+int dpb_fix_low(dpb_ctx* ctx, const dpb_mle* mle, const void* point, uint32_t k, dpb_mle** out);
+/* Full evaluation at an n-variable point (DensePolynomial::evaluate,
+ * zkml/src/iop/mod.rs:196-207).  Result: one challenge element on the host. */
+int dpb_mle_evaluate(dpb_ctx* ctx, const dpb_mle* mle, const void* point, uint32_t n, void* out);
+
+/* ---- sumcheck (dp_crypto::structs::IOPProverState) --------------------- */
+/* Starts a sumcheck over `num_vars` variables of  sum_t coeff_t * prod_j mle[idx_tj].
+ * Tables are borrowed and never modified.  A table with fewer than num_vars
+ * variables is a function of the LAST variables only (constant in the early
+ * rounds), the convention the batched logup prover relies on
+ * (zkml/src/lookup/logup_gkr/prover.rs:217-249).
+ * Replaces IOPProverState::prove's set-up; call sites
+ * zkml/src/layers/einsum/prove.rs:184, zkml/src/lookup/logup_gkr/prover.rs:275,
+ * zkml/src/layers/hadamard.rs:115, zkml/src/iop/same_poly.rs:105. */
+int dpb_sumcheck_begin(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, uint32_t k,
+                       const dpb_term* terms, uint32_t n_terms, dpb_sc** out);
+/* Degree of the round polynomial (max factors per term). */
+uint32_t dpb_sumcheck_degree(const dpb_sc* sc);
+/* One prover round.  `prev_challenge` is NULL on the first round, otherwise the
+ * challenge the host sampled after the previous round (one challenge element).
+ * Writes the round polynomial's evaluations at 0..=degree (degree+1 challenge
+ * elements) to `out_evals`. */
+int dpb_sumcheck_round(dpb_sc* sc, const void* prev_challenge, void* out_evals, uint32_t* n_evals);
+/* Binds the last variable and returns every table's evaluation at the full
+ * point, in registration order (IOPProverState::get_mle_flatten_final_evaluations,
+ * zkml/src/lookup/logup_gkr/prover.rs:281). */
+int dpb_sumcheck_finish(dpb_sc* sc, const void* last_challenge, void* out_final_evals);
+void dpb_sumcheck_free(dpb_sc* sc);
+
+/* ---- logup-GKR fraction tree ------------------------------------------- */
+#define DPB_LOGUP_LOOKUP 0
+#define DPB_LOGUP_TABLE 1
+/* Builds every level of the fraction tree of one instance on the device
+ * (LogUpCircuit::new, zkml/src/lookup/logup_gkr/circuit.rs:512-516;
+ * LogUpLayer::next_layer, :88-184).  `columns` are n_cols tables of 2^m
+ * entries; `mult` (tables only) the multiplicities.  constant_chal / sep_chal
+ * are challenge elements on the host. */
+int dpb_logup_build(dpb_ctx* ctx, int kind, dpb_mle* const* columns, uint32_t n_cols,
+                    const dpb_mle* mult, const void* constant_chal, const void* sep_chal,
+                    dpb_logup** out);
+/* Number of levels above the input (m-1 ... down to the 2-element level). */
+uint32_t dpb_logup_num_levels(const dpb_logup* lu);
+/* Borrowed views [num_lo, num_hi, den_lo, den_hi] of tree level `level`
+ * (1 = first computed level, arrays of 2^(m-1); num_levels = top, arrays of 2),
+ * the MLEs LogUpLayer::layer_proving_info hands to the sumcheck
+ * (zkml/src/lookup/logup_gkr/circuit.rs:255-271). Views must be freed with dpb_mle_free. */
+int dpb_logup_level(const dpb_logup* lu, uint32_t level, dpb_mle* out_views[4]);
+/* [num[0], num[1], den[0], den[1]] of the top level (LogUpCircuit::outputs, :558-560). */
+int dpb_logup_outputs(const dpb_logup* lu, void* out4);
+void dpb_logup_free(dpb_logup* lu);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DPB_H */

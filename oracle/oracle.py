@@ -1,0 +1,942 @@
+"""CPU oracle for the sumcheck / multilinear-fold / logup-GKR path.
+
+TEST INFRASTRUCTURE ONLY.  Only the tests, the smoke check and the benchmark's
+CPU-baseline legs may import this module; the library never does.
+
+PARITY UNPINNED at the byte level (see the header of oracle.c): the
+reference's sumcheck core and transcript live in the absent third-party crate
+dp-crypto 0.1.0 (rev 22e8e93), and the reference ships no golden proof.  The
+protocol logic below restates the reference's in-repo code step by step
+(file:line beside each function, paths relative to the reference repository);
+the heavy loops are in oracle.c (plain C + OpenMP), scalars are Python ints.
+
+Conventions shared with the library:
+  * tables are little-endian (bit i of the index = variable i,
+    zkml/src/lib.rs:357-369); sumcheck round i binds variable i;
+  * a round message is the round polynomial's evaluations at 0..=d;
+  * the transcript is the BLAKE3 construction of `Transcript` below.
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+from . import blake3_py
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "_build", "liboracle.so")
+
+DT_GL_BASE, DT_GL_EXT, DT_FR = 0, 1, 2
+
+FR_MOD = 21888242871839275222246405745257275088548364400416034343698204186575808495617
+GL_MOD = 2**64 - 2**32 + 1
+GL_NONRES = 7
+
+
+def build(force=False):
+    """Compiles oracle.c into oracle/_build/liboracle.so with gcc."""
+    src = os.path.join(HERE, "oracle.c")
+    if not force and os.path.exists(LIB_PATH) and os.path.getmtime(LIB_PATH) >= os.path.getmtime(src):
+        return LIB_PATH
+    os.makedirs(os.path.dirname(LIB_PATH), exist_ok=True)
+    subprocess.run(["gcc", "-O3", "-fopenmp", "-shared", "-fPIC", "-o", LIB_PATH, src], check=True)
+    return LIB_PATH
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        build()
+        _lib = ctypes.CDLL(LIB_PATH)
+    return _lib
+
+
+class OrcTerm(ctypes.Structure):
+    _fields_ = [("coeff", ctypes.c_uint8 * 32), ("n_factors", ctypes.c_uint32), ("idx", ctypes.c_uint16 * 8)]
+
+
+def _ptr(a):
+    return ctypes.c_void_p(a.ctypes.data)
+
+
+# --------------------------------------------------------------------- fields
+class FrField:
+    """BN254 Fr.  Scalars are Python ints in [0, r); tables are uint64[n, 4]
+    Montgomery limbs (the library's DPB_FR layout)."""
+    name = "fr"
+    chal_dtype = DT_FR
+    elem_words = 4
+    R = (1 << 256) % FR_MOD
+    RINV = pow((1 << 256) % FR_MOD, -1, FR_MOD)
+
+    zero, one = 0, 1
+
+    @staticmethod
+    def add(a, b): return (a + b) % FR_MOD
+    @staticmethod
+    def sub(a, b): return (a - b) % FR_MOD
+    @staticmethod
+    def mul(a, b): return (a * b) % FR_MOD
+    @staticmethod
+    def neg(a): return (-a) % FR_MOD
+    @staticmethod
+    def inv(a): return pow(a, -1, FR_MOD)
+    @staticmethod
+    def from_int(x): return x % FR_MOD
+
+    @classmethod
+    def pow(cls, a, e):
+        return pow(a, e, FR_MOD)
+
+    # scalar <-> native bytes (Montgomery limbs)
+    @classmethod
+    def to_native(cls, a):
+        return ((a * cls.R) % FR_MOD).to_bytes(32, "little")
+
+    @classmethod
+    def from_native(cls, b):
+        return (int.from_bytes(bytes(b), "little") * cls.RINV) % FR_MOD
+
+    # scalar <-> canonical bytes (what ark_serialize writes: 32 bytes LE)
+    @staticmethod
+    def to_canonical(a):
+        return int(a).to_bytes(32, "little")
+
+    @classmethod
+    def table_from_ints(cls, vals):
+        buf = b"".join(cls.to_native(v % FR_MOD) for v in vals)
+        return np.frombuffer(buf, dtype=np.uint64).reshape(-1, 4).copy()
+
+    @classmethod
+    def table_to_ints(cls, t):
+        raw = np.ascontiguousarray(t).tobytes()
+        return [cls.from_native(raw[i:i + 32]) for i in range(0, len(raw), 32)]
+
+    @classmethod
+    def table_from_i64(cls, x):
+        x = np.ascontiguousarray(x, dtype=np.int64)
+        out = np.empty((x.size, 4), dtype=np.uint64)
+        lib().orc_fr_from_i64(_ptr(x), _ptr(out), ctypes.c_uint64(x.size))
+        return out
+
+    @classmethod
+    def random_table(cls, rng, n):
+        """n uniform elements (512 random bits reduced mod r)."""
+        vals = [int.from_bytes(rng.bytes(64), "little") % FR_MOD for _ in range(n)]
+        return cls.table_from_ints(vals)
+
+    @classmethod
+    def random_table_fast(cls, rng, n):
+        """n pseudo-random elements for large tables: random limbs with the top
+        limb masked below the modulus' top limb, taken as Montgomery residues."""
+        t = rng.integers(0, 2**64, size=(n, 4), dtype=np.uint64)
+        t[:, 3] &= np.uint64((1 << 60) - 1)
+        return t
+
+    @classmethod
+    def random_scalar(cls, rng):
+        return int.from_bytes(rng.bytes(64), "little") % FR_MOD
+
+    @staticmethod
+    def dtype_of(table):
+        return DT_FR
+
+    @classmethod
+    def challenge_from_bytes(cls, b64):
+        return int.from_bytes(b64, "little") % FR_MOD
+
+
+class GlField:
+    """Goldilocks with its quadratic extension X^2 = 7.  Scalars are (c0, c1)
+    tuples; tables are uint64[n] (base) or uint64[n, 2] (extension)."""
+    name = "gl"
+    chal_dtype = DT_GL_EXT
+    elem_words = 2
+    zero, one = (0, 0), (1, 0)
+
+    @staticmethod
+    def add(a, b): return ((a[0] + b[0]) % GL_MOD, (a[1] + b[1]) % GL_MOD)
+    @staticmethod
+    def sub(a, b): return ((a[0] - b[0]) % GL_MOD, (a[1] - b[1]) % GL_MOD)
+    @staticmethod
+    def mul(a, b):
+        return ((a[0] * b[0] + GL_NONRES * a[1] * b[1]) % GL_MOD, (a[0] * b[1] + a[1] * b[0]) % GL_MOD)
+    @staticmethod
+    def neg(a): return ((-a[0]) % GL_MOD, (-a[1]) % GL_MOD)
+    @staticmethod
+    def inv(a):
+        n = pow((a[0] * a[0] - GL_NONRES * a[1] * a[1]) % GL_MOD, -1, GL_MOD)
+        return ((a[0] * n) % GL_MOD, (-a[1] * n) % GL_MOD)
+    @staticmethod
+    def from_int(x): return (x % GL_MOD, 0)
+
+    @classmethod
+    def pow(cls, a, e):
+        r = cls.one
+        while e:
+            if e & 1:
+                r = cls.mul(r, a)
+            a = cls.mul(a, a)
+            e >>= 1
+        return r
+
+    @staticmethod
+    def to_native(a):
+        return int(a[0]).to_bytes(8, "little") + int(a[1]).to_bytes(8, "little")
+
+    @staticmethod
+    def from_native(b):
+        b = bytes(b)
+        return (int.from_bytes(b[:8], "little"), int.from_bytes(b[8:16], "little"))
+
+    to_canonical = to_native
+
+    @classmethod
+    def table_from_ints(cls, vals):
+        """vals: ints -> base table; tuples -> extension table."""
+        if len(vals) and isinstance(vals[0], tuple):
+            return np.array([[v[0] % GL_MOD, v[1] % GL_MOD] for v in vals], dtype=np.uint64).reshape(-1, 2)
+        return np.array([v % GL_MOD for v in vals], dtype=np.uint64)
+
+    @classmethod
+    def table_to_ints(cls, t):
+        t = np.asarray(t)
+        if t.ndim == 1:
+            return [(int(v), 0) for v in t]
+        return [(int(a), int(b)) for a, b in t]
+
+    @classmethod
+    def table_from_i64(cls, x):
+        x = np.ascontiguousarray(x, dtype=np.int64)
+        out = np.empty(x.size, dtype=np.uint64)
+        lib().orc_gl_from_i64(_ptr(x), _ptr(out), ctypes.c_uint64(x.size))
+        return out
+
+    @classmethod
+    def random_table(cls, rng, n):
+        """n uniform base-field values by rejection sampling below p."""
+        out = rng.integers(0, 2**64, size=n, dtype=np.uint64)
+        while True:
+            bad = out >= np.uint64(GL_MOD)
+            k = int(bad.sum())
+            if k == 0:
+                return out
+            out[bad] = rng.integers(0, 2**64, size=k, dtype=np.uint64)
+
+    random_table_fast = random_table
+
+    @classmethod
+    def random_ext_table(cls, rng, n):
+        return np.stack([cls.random_table(rng, n), cls.random_table(rng, n)], axis=1).copy()
+
+    @classmethod
+    def random_scalar(cls, rng):
+        return (int.from_bytes(rng.bytes(16), "little") % GL_MOD, int.from_bytes(rng.bytes(16), "little") % GL_MOD)
+
+    @staticmethod
+    def dtype_of(table):
+        return DT_GL_BASE if np.asarray(table).ndim == 1 else DT_GL_EXT
+
+    @classmethod
+    def challenge_from_bytes(cls, b64):
+        return (int.from_bytes(b64[:16], "little") % GL_MOD, int.from_bytes(b64[32:48], "little") % GL_MOD)
+
+
+FIELDS = {"fr": FrField, "gl": GlField}
+
+
+def scalars_to_array(F, vals):
+    buf = b"".join(F.to_native(v) for v in vals)
+    return np.frombuffer(buf, dtype=np.uint64).reshape(-1, F.elem_words).copy()
+
+
+def array_to_scalars(F, arr):
+    raw = np.ascontiguousarray(arr).tobytes()
+    w = F.elem_words * 8
+    return [F.from_native(raw[i:i + w]) for i in range(0, len(raw), w)]
+
+
+def table_len(t):
+    return np.asarray(t).shape[0]
+
+
+# ----------------------------------------------------------------- transcript
+class Transcript:
+    """Fiat-Shamir transcript over BLAKE3 with the method names the reference
+    uses (`Blake3Transcript::new(b"m2vec")`, zkml/src/lib.rs:106-108;
+    append_scalars / append_and_sample / challenge_scalar,
+    zkml/src/lookup/logup_gkr/prover.rs:163-173).  The reference's byte format is
+    defined in the absent dp-crypto crate; this one is the library's own:
+
+      state_0      = BLAKE3("dpb-transcript-v1" || label)
+      absorb(t, m) : state = BLAKE3(state || u32le(round) || u32le(len t) || t || m); round += 1
+      append_scalars(v)      = absorb("scalars", u64le(len v) || canonical bytes of each v)
+      append_and_sample(l)   = absorb("label", l); challenge_scalar()
+      challenge_scalar()     = absorb("challenge", ""); 64 bytes = BLAKE3(state||0) || BLAKE3(state||1)
+                               Fr: the 64 bytes as an LE integer mod r
+                               Goldilocks ext: c0 = bytes[0:16] mod p, c1 = bytes[32:48] mod p
+    """
+
+    def __init__(self, F, label=b"m2vec", hash_fn=None):
+        self.F = F
+        self.h = hash_fn or blake3_py.blake3
+        self.state = self.h(b"dpb-transcript-v1" + bytes(label))
+        self.round = 0
+
+    def clone(self):
+        t = Transcript.__new__(Transcript)
+        t.F, t.h, t.state, t.round = self.F, self.h, self.state, self.round
+        return t
+
+    def _absorb(self, tag, msg):
+        self.state = self.h(self.state + self.round.to_bytes(4, "little") + len(tag).to_bytes(4, "little") + tag + msg)
+        self.round += 1
+
+    def append_scalars(self, vals):
+        self._absorb(b"scalars", len(vals).to_bytes(8, "little") + b"".join(self.F.to_canonical(v) for v in vals))
+
+    def challenge_scalar(self):
+        self._absorb(b"challenge", b"")
+        return self.F.challenge_from_bytes(self.h(self.state + b"\0") + self.h(self.state + b"\1"))
+
+    def append_and_sample(self, label):
+        self._absorb(b"label", bytes(label))
+        return self.challenge_scalar()
+
+    def read_challenges(self, n):
+        """zkml/src/lib.rs:176-184"""
+        return [self.challenge_scalar() for _ in range(n)]
+
+
+# ----------------------------------------------------------------- expressions
+class Expr:
+    """dp_crypto::Expression as zkml uses it: WitIn(id), Constant(c),
+    Challenge(id, pow, scalar, offset) = scalar * ch[id]^pow + offset, closed
+    under + - * and negation (zkml/src/lookup/logup_gkr/circuit.rs:245-284)."""
+
+    def __init__(self, kind, *args):
+        self.kind, self.args = kind, args
+
+    @staticmethod
+    def wit(i): return Expr("wit", i)
+    @staticmethod
+    def const(c): return Expr("const", c)
+    @staticmethod
+    def chal(i, p, scalar, offset): return Expr("chal", i, p, scalar, offset)
+
+    def __add__(self, o): return Expr("add", self, o)
+    def __sub__(self, o): return Expr("add", self, Expr("neg", o))
+    def __mul__(self, o): return Expr("mul", self, o)
+    def __neg__(self): return Expr("neg", self)
+
+
+def expr_to_terms(F, e, challenges):
+    """Expands an expression into {sorted tuple of table ids: coefficient}
+    (what VirtualPolynomialsBuilder::to_virtual_polys hands the prover)."""
+    k = e.kind
+    if k == "wit":
+        return {(e.args[0],): F.one}
+    if k == "const":
+        return {(): e.args[0]} if e.args[0] != F.zero else {}
+    if k == "chal":
+        i, p, s, off = e.args
+        v = F.add(F.mul(s, F.pow(challenges[i], p)), off)
+        return {(): v} if v != F.zero else {}
+    if k == "neg":
+        return {m: F.neg(c) for m, c in expr_to_terms(F, e.args[0], challenges).items()}
+    a = expr_to_terms(F, e.args[0], challenges)
+    b = expr_to_terms(F, e.args[1], challenges)
+    out = {}
+    if k == "add":
+        for src in (a, b):
+            for m, c in src.items():
+                out[m] = F.add(out.get(m, F.zero), c)
+    elif k == "mul":
+        for ma, ca in a.items():
+            for mb, cb in b.items():
+                m = tuple(sorted(ma + mb))
+                out[m] = F.add(out.get(m, F.zero), F.mul(ca, cb))
+    else:
+        raise ValueError(k)
+    return {m: c for m, c in out.items() if c != F.zero}
+
+
+def eval_expr(F, e, wit_evals, challenges):
+    """dp_crypto::utils::eval_by_expr_with_instance with only witness values
+    and challenges populated (zkml/src/lookup/logup_gkr/prover.rs:50-57)."""
+    k = e.kind
+    if k == "wit":
+        return wit_evals[e.args[0]]
+    if k == "const":
+        return e.args[0]
+    if k == "chal":
+        i, p, s, off = e.args
+        return F.add(F.mul(s, F.pow(challenges[i], p)), off)
+    if k == "neg":
+        return F.neg(eval_expr(F, e.args[0], wit_evals, challenges))
+    a = eval_expr(F, e.args[0], wit_evals, challenges)
+    b = eval_expr(F, e.args[1], wit_evals, challenges)
+    return F.add(a, b) if k == "add" else F.mul(a, b)
+
+
+# ------------------------------------------------------------------- poly ops
+def eq_evals(F, point):
+    """dp_crypto::poly::eq::evals: eq(x, point) for all x, little-endian."""
+    m = len(point)
+    out = np.empty((1 << m, F.elem_words), dtype=np.uint64)
+    pt = scalars_to_array(F, point) if m else np.zeros((1, F.elem_words), dtype=np.uint64)
+    fn = lib().orc_eq_gl if F is GlField else lib().orc_eq_fr
+    fn(_ptr(pt), ctypes.c_uint32(m), _ptr(out))
+    return out
+
+
+def identity_eval(F, r1, r2):
+    """zkml/src/poly_commit/mod.rs:184-192"""
+    acc = F.one
+    for a, b in zip(r1, r2):
+        acc = F.mul(acc, F.add(F.mul(a, b), F.mul(F.sub(F.one, a), F.sub(F.one, b))))
+    return acc
+
+
+def fold_low(F, table, r):
+    """Binds variable 0 of `table` to r."""
+    t = np.ascontiguousarray(table)
+    n_out = t.shape[0] // 2
+    out = np.empty((n_out, F.elem_words), dtype=np.uint64)
+    rr = scalars_to_array(F, [r])
+    fn = lib().orc_fold_gl if F is GlField else lib().orc_fold_fr
+    fn(_ptr(t), ctypes.c_int(F.dtype_of(t)), ctypes.c_uint64(n_out), _ptr(rr), _ptr(out))
+    return out
+
+
+def fold_high(F, table, r):
+    """Binds the top variable of `table` to r."""
+    t = np.ascontiguousarray(table)
+    n_out = t.shape[0] // 2
+    out = np.empty((n_out, F.elem_words), dtype=np.uint64)
+    rr = scalars_to_array(F, [r])
+    fn = lib().orc_fold_high_gl if F is GlField else lib().orc_fold_high_fr
+    fn(_ptr(t), ctypes.c_int(F.dtype_of(t)), ctypes.c_uint64(n_out), _ptr(rr), _ptr(out))
+    return out
+
+
+def fix_low_variables(F, table, point):
+    """DensePolynomial::fix_low_variables: variable j := point[j], one pass
+    per variable (zkml/src/layers/transformer/attention_mask/prove.rs:431-436)."""
+    t = table
+    for r in point:
+        t = fold_low(F, t, r)
+    return t
+
+
+def fix_high_variables(F, table, point):
+    """DensePolynomial::fix_high_variables: the top len(point) variables, with
+    point[j] the value of variable n - len(point) + j
+    (zkml/src/layers/transformer/attention_mask/prove.rs:419-426,
+    zkml/src/tensor/mod.rs:1889-1895)."""
+    t = table
+    for r in reversed(point):
+        t = fold_high(F, t, r)
+    return t
+
+
+def evaluate(F, table, point):
+    """DensePolynomial::evaluate, little-endian (zkml/src/lib.rs:357-369)."""
+    assert table_len(table) == 1 << len(point)
+    if not point:
+        return array_to_scalars(F, _widen(F, table))[0]
+    return array_to_scalars(F, fix_low_variables(F, table, point))[0]
+
+
+def _widen(F, table):
+    t = np.asarray(table)
+    if F is GlField and t.ndim == 1:
+        return np.stack([t, np.zeros_like(t)], axis=1).copy()
+    return t
+
+
+# -------------------------------------------------------------------- sumcheck
+def terms_degree(terms):
+    return max(len(m) for m in terms)
+
+
+def _terms_array(F, terms):
+    items = sorted(terms.items())
+    arr = (OrcTerm * len(items))()
+    for t, (m, c) in enumerate(items):
+        raw = F.to_native(c)
+        for i, b in enumerate(raw):
+            arr[t].coeff[i] = b
+        arr[t].n_factors = len(m)
+        for j, idx in enumerate(m):
+            arr[t].idx[j] = idx
+    return arr, len(items)
+
+
+def sumcheck_round(F, vars_left, tables, terms, d):
+    """Round polynomial evaluations at 0..=d over tables that have `vars_left`
+    (or fewer) variables."""
+    k = len(tables)
+    tabs = [np.ascontiguousarray(t) for t in tables]
+    # fast path: first round of a coefficient-one product of base tables
+    if (F is GlField and len(terms) == 1 and all(t.ndim == 1 for t in tabs)
+            and all(table_len(t) == 1 << vars_left for t in tabs)):
+        (m, c), = terms.items()
+        if c == F.one and sorted(m) == list(range(k)) and d == k:
+            ptrs = (ctypes.c_void_p * k)(*[t.ctypes.data for t in tabs])
+            out = np.empty((d + 1, 2), dtype=np.uint64)
+            lib().orc_round_gl_base_product(ctypes.c_uint32(vars_left), ptrs, ctypes.c_uint32(k), _ptr(out))
+            return array_to_scalars(F, out)
+    ptrs = (ctypes.c_void_p * k)(*[t.ctypes.data for t in tabs])
+    dts = (ctypes.c_int * k)(*[F.dtype_of(t) for t in tabs])
+    tv = (ctypes.c_uint32 * k)(*[table_len(t).bit_length() - 1 for t in tabs])
+    arr, n_terms = _terms_array(F, terms)
+    out = np.empty((d + 1, F.elem_words), dtype=np.uint64)
+    fn = lib().orc_round_gl if F is GlField else lib().orc_round_fr
+    fn(ctypes.c_uint32(vars_left), ptrs, dts, tv, ctypes.c_uint32(k), arr, ctypes.c_uint32(n_terms),
+       ctypes.c_uint32(d), _ptr(out))
+    return array_to_scalars(F, out)
+
+
+ROUND_LABEL = b"sumcheck_round"
+
+
+def sumcheck_prove(F, num_vars, tables, terms, transcript, degree=None):
+    """IOPProverState::prove as its call sites use it
+    (zkml/src/layers/hadamard.rs:115-130): returns (proof, point, final_evals)
+    with proof = list of per-round evaluation lists, point[j] the challenge of
+    variable j (collect_raw_challenges) and final_evals[i] = table i at the
+    point (get_mle_flatten_final_evaluations).  A table with fewer variables
+    is a function of the last variables and starts folding when its turn comes."""
+    d = degree if degree is not None else terms_degree(terms)
+    cur = list(tables)
+    nv = [table_len(t).bit_length() - 1 for t in cur]
+    transcript.append_scalars([F.from_int(num_vars), F.from_int(d)])
+    proof, point = [], []
+    for i in range(num_vars):
+        left = num_vars - i
+        evals = sumcheck_round(F, left, cur, terms, d)
+        transcript.append_scalars(evals)
+        r = transcript.append_and_sample(ROUND_LABEL)
+        proof.append(evals)
+        point.append(r)
+        for j in range(len(cur)):
+            if nv[j] >= left:
+                cur[j] = fold_low(F, cur[j], r)
+                nv[j] -= 1
+    finals = [array_to_scalars(F, _widen(F, t))[0] for t in cur]
+    return proof, point, finals
+
+
+def interpolate_eval(F, evals, r):
+    """Value at r of the polynomial with the given values at 0..len-1."""
+    n = len(evals)
+    tot = F.zero
+    for i in range(n):
+        num, den = F.one, F.one
+        for j in range(n):
+            if j != i:
+                num = F.mul(num, F.sub(r, F.from_int(j)))
+                den = F.mul(den, F.sub(F.from_int(i), F.from_int(j)))
+        tot = F.add(tot, F.mul(evals[i], F.mul(num, F.inv(den))))
+    return tot
+
+
+def sumcheck_verify(F, claimed_sum, proof, num_vars, degree, transcript):
+    """IOPVerifierState::verify (zkml/src/lookup/logup_gkr/verifier.rs:186-191):
+    returns (point, expected_evaluation)."""
+    transcript.append_scalars([F.from_int(num_vars), F.from_int(degree)])
+    claim = claimed_sum
+    point = []
+    assert len(proof) == num_vars
+    for evals in proof:
+        assert len(evals) == degree + 1
+        if F.add(evals[0], evals[1]) != claim:
+            raise ValueError("sumcheck round check failed")
+        transcript.append_scalars(evals)
+        r = transcript.append_and_sample(ROUND_LABEL)
+        claim = interpolate_eval(F, evals, r)
+        point.append(r)
+    return point, claim
+
+
+def extract_sum(F, proof):
+    """IOPProof::extract_sum (zkml/src/layers/hadamard.rs:118)."""
+    return F.add(proof[0][0], proof[0][1])
+
+
+# ----------------------------------------------------------------- logup-GKR
+def logup_next(F, kind, cols, mult, constant, sep):
+    """One LogUpLayer::next_layer step (zkml/src/lookup/logup_gkr/circuit.rs:88-184).
+    kind 0 lookup / 1 table: cols = denominator columns; kind 2: cols = [num, den]."""
+    cols = [np.ascontiguousarray(c) for c in cols]
+    half = table_len(cols[0]) // 2
+    num = np.empty((half, F.elem_words), dtype=np.uint64)
+    den = np.empty((half, F.elem_words), dtype=np.uint64)
+    k = len(cols)
+    ptrs = (ctypes.c_void_p * k)(*[c.ctypes.data for c in cols])
+    dts = (ctypes.c_int * k)(*[F.dtype_of(c) for c in cols])
+    cst = scalars_to_array(F, [constant if constant is not None else F.zero])
+    sp = scalars_to_array(F, [sep if sep is not None else F.zero])
+    m = np.ascontiguousarray(mult) if mult is not None else None
+    fn = lib().orc_logup_next_gl if F is GlField else lib().orc_logup_next_fr
+    fn(ctypes.c_int(kind), ptrs, dts, ctypes.c_uint32(k), _ptr(m) if m is not None else None,
+       ctypes.c_int(F.dtype_of(m) if m is not None else 0), _ptr(cst), _ptr(sp), ctypes.c_uint64(half),
+       _ptr(num), _ptr(den))
+    return num, den
+
+
+class LogUpCircuit:
+    """LogUpCircuit::new (zkml/src/lookup/logup_gkr/circuit.rs:512-516): all
+    levels, bottom to top.  levels[0] describes the input layer; levels[l] for
+    l >= 1 are (num, den) arrays of 2^(m-l) entries."""
+
+    def __init__(self, F, kind, columns, mult, constant, sep):
+        self.F, self.kind = F, kind  # 0 lookup, 1 table
+        self.columns, self.mult, self.constant, self.sep = columns, mult, constant, sep
+        m = table_len(columns[0]).bit_length() - 1
+        assert m >= 2
+        self.m = m
+        self.levels = [None]
+        num, den = logup_next(F, kind, columns, mult, constant, sep)
+        self.levels.append((num, den))
+        while table_len(num) > 2:
+            num, den = logup_next(F, 2, [num, den], None, None, None)
+            self.levels.append((num, den))
+
+    def num_vars(self):
+        """circuit.rs:564-566: the input layer's num_vars = m - 1"""
+        return self.m - 1
+
+    def outputs(self):
+        """circuit.rs:558-560: [num[0], num[1], den[0], den[1]] of the top level"""
+        num, den = self.levels[-1]
+        return array_to_scalars(self.F, num) + array_to_scalars(self.F, den)
+
+    def final_eval_count(self):
+        """circuit.rs:414-426"""
+        return 2 * len(self.columns) + (2 if self.kind == 1 else 0)
+
+    def layer_tables(self, layer_vars):
+        """The MLEs LogUpLayer::layer_proving_info registers for the layer whose
+        halves have `layer_vars` variables (circuit.rs:255-271, 298-353, 360-409)."""
+        half = 1 << layer_vars
+        if layer_vars == self.m - 1:  # the input layer
+            lo = [np.ascontiguousarray(c[:half]) for c in self.columns]
+            hi = [np.ascontiguousarray(c[half:]) for c in self.columns]
+            if self.kind == 1:
+                return [np.ascontiguousarray(self.mult[:half]), np.ascontiguousarray(self.mult[half:])] + lo + hi
+            return lo + hi
+        num, den = self.levels[self.m - 1 - layer_vars]
+        return [num[:half], num[half:], den[:half], den[half:]]
+
+    def layer_exprs(self, layer_vars, layer_count, wit0):
+        """(sumcheck_expression, claim_expression, n_witnesses) of
+        layer_proving_info (circuit.rs:231-412)."""
+        F = self.F
+        one, zero = F.one, F.zero
+        W, C = Expr.wit, Expr.chal
+        b = layer_count * 4
+        claim = C(0, layer_count, one, zero) * (
+            C(2, 1, one, zero) * (W(b + 1) - W(b)) + W(b)
+            + C(1, 1, one, zero) * (C(2, 1, one, zero) * (W(b + 3) - W(b + 2)) + W(b + 2)))
+        alpha_j = C(0, layer_count, one, zero)
+        lam = C(1, 1, one, zero)
+        if layer_vars != self.m - 1:
+            n_lo, n_hi, d_lo, d_hi = W(wit0), W(wit0 + 1), W(wit0 + 2), W(wit0 + 3)
+            sc = alpha_j * (n_lo * d_hi + n_hi * d_lo + lam * d_lo * d_hi)
+            return sc, claim, 4
+        ncol = len(self.columns)
+        first = wit0 + (2 if self.kind == 1 else 0)
+        d_lo, d_hi = Expr.const(self.constant), Expr.const(self.constant)
+        pw = one
+        for i in range(ncol):
+            d_lo = d_lo + Expr.const(pw) * W(first + i)
+            d_hi = d_hi + Expr.const(pw) * W(first + ncol + i)
+            pw = F.mul(pw, self.sep)
+        if self.kind == 1:
+            sc = alpha_j * (W(wit0) * d_hi + W(wit0 + 1) * d_lo + lam * d_lo * d_hi)
+            return sc, claim, 2 + 2 * ncol
+        sc = alpha_j * (-d_hi - d_lo + lam * d_lo * d_hi)
+        return sc, claim, 2 * ncol
+
+    def combine_final_evals(self, evals, rho):
+        """circuit.rs:442-500"""
+        F = self.F
+        ncol = len(self.columns)
+        out = []
+        if self.kind == 1:
+            out.append(F.add(F.mul(rho, F.sub(evals[1], evals[0])), evals[0]))
+            evals = evals[2:]
+        lo, hi = evals[:ncol], evals[ncol:]
+        out += [F.add(F.mul(rho, F.sub(h, l)), l) for l, h in zip(lo, hi)]
+        return out
+
+
+class LogUpInput:
+    """zkml/src/lookup/logup_gkr/structs.rs:138-231.  kind 0 = Lookup with
+    `columns_per_instance` columns per circuit, kind 1 = Table."""
+
+    def __init__(self, F, kind, columns, constant, sep, columns_per_instance=None, mult=None):
+        if not columns:
+            raise ValueError("No column evals were provided for Lookup input")
+        n = table_len(columns[0])
+        if n & (n - 1) or n == 0:
+            raise ValueError(f"Need a power of two number of evaluations got: {n}")
+        if any(table_len(c) != n for c in columns):
+            raise ValueError("All sets of evaluations should be the same length")
+        if kind == 1 and table_len(mult) != n:
+            raise ValueError("Multiplicities length was not equal to column evaluations length")
+        self.F, self.kind, self.columns, self.constant, self.sep = F, kind, columns, constant, sep
+        self.columns_per_instance = columns_per_instance if kind == 0 else len(columns)
+        self.mult = mult
+
+    def make_new_circuits(self):
+        """structs.rs:241-272"""
+        if self.kind == 1:
+            return [LogUpCircuit(self.F, 1, self.columns, self.mult, self.constant, self.sep)]
+        c = self.columns_per_instance
+        return [LogUpCircuit(self.F, 0, self.columns[i:i + c], None, self.constant, self.sep)
+                for i in range(0, len(self.columns), c)]
+
+
+def logup_batch_prove(F, inputs, transcript):
+    """new_batch_multiple_sizes_prove (zkml/src/lookup/logup_gkr/prover.rs:91-344).
+    Returns a dict with the fields of LogUpBatchProof (structs.rs:555-578)."""
+    if not inputs:
+        raise ValueError("No inputs provided for LogUp")
+    if any(i.kind != inputs[0].kind for i in inputs):
+        raise ValueError("Not all proof types matched")
+    circuits = [c for i in inputs for c in i.make_new_circuits()]
+    for a, b in zip(circuits, circuits[1:]):
+        if a.num_vars() < b.num_vars():
+            raise ValueError("Circuits were not in decreasing size order")
+    total_layers = max(c.num_vars() for c in circuits)
+    sizes = sorted({c.num_vars() for c in circuits}, reverse=True)
+    by_size = {s: [c for c in circuits if c.num_vars() == s] for s in sizes}
+    circuit_outputs = [c.outputs() for c in circuits]
+
+    transcript.append_scalars([F.from_int(len(circuits))])
+    for o in circuit_outputs:
+        transcript.append_scalars(o)
+    rho = transcript.append_and_sample(b"initial_batching")
+    alpha = transcript.append_and_sample(b"initial_alpha")
+    lam = transcript.append_and_sample(b"initial_lambda")
+    point = [rho]
+    sumcheck_proofs, round_evaluations = [], []
+
+    for v in range(1, total_layers + 1):
+        remaining = total_layers - (v - 1)
+        joining = [e for c in by_size.get(remaining, []) for e in c.outputs()]
+        wit_evals = (round_evaluations[-1] if round_evaluations else []) + joining
+        if not wit_evals:
+            raise ValueError("Proving failed: No previous evals and no evals for this number of variables")
+        tables, eq_tables, group_exprs = [], [], []
+        claim_expr = Expr.const(F.zero)
+        layer_count, wit_off = 0, 0
+        for size in sizes:
+            if size < remaining:
+                continue
+            mult = Expr.const(F.from_int(1 << (total_layers - size)))
+            layer_vars = size - remaining + 1  # variables of this group's halves in this step
+            group = Expr.const(F.zero)
+            for c in by_size[size]:
+                sc, cl, nw = c.layer_exprs(layer_vars, layer_count, wit_off)
+                tables += c.layer_tables(layer_vars)
+                layer_count += 1
+                wit_off += nw
+                group = group + sc
+                claim_expr = claim_expr + mult * cl
+            eq_tables.append(eq_evals(F, point[len(point) - layer_vars:]))
+            group_exprs.append(group)
+        current_claim = eval_expr(F, claim_expr, wit_evals, [alpha, lam, rho])
+        transcript.append_scalars([current_claim])
+        full = Expr.const(F.zero)
+        for i, g in enumerate(group_exprs):
+            full = full + g * Expr.wit(wit_off + i)
+        terms = expr_to_terms(F, full, [alpha, lam])
+        proof, point, finals = sumcheck_prove(F, v, tables + eq_tables, terms, transcript)
+        evals = finals[:wit_off]
+        rho = transcript.append_and_sample(b"logup_batching")
+        if v != total_layers:
+            alpha = transcript.append_and_sample(b"logup_alpha")
+            lam = transcript.append_and_sample(b"logup_lambda")
+        point = point + [rho]
+        sumcheck_proofs.append(proof)
+        round_evaluations.append(evals)
+
+    output_claims, ncols = [], []
+    skip = 0
+    last = round_evaluations[-1]
+    for c in circuits:
+        n = c.final_eval_count()
+        ev = c.combine_final_evals(last[skip:skip + n], rho)
+        skip += n
+        pt = point[len(point) - (c.num_vars() + 1):]
+        output_claims += [(pt, e) for e in ev]
+        ncols.append(len(c.columns))
+    return dict(sumcheck_proofs=sumcheck_proofs, round_evaluations=round_evaluations,
+                output_claims=output_claims, circuit_outputs=circuit_outputs, proof_type=inputs[0].kind,
+                num_vars_per_instance=[c.num_vars() for c in circuits],
+                num_denominator_columns_per_instance=ncols)
+
+
+def _verifier_instance_exprs(F, inst, layer_count, wit0, is_final):
+    """LogUpVerifierInstance::instance_expressions (structs.rs:427-553).
+    inst = dict(constant, sep, num_columns, kind, num_vars)."""
+    one, zero = F.one, F.zero
+    W, C = Expr.wit, Expr.chal
+    b = layer_count * 4
+    claim = C(0, layer_count, one, zero) * (
+        C(2, 1, one, zero) * (W(b + 1) - W(b)) + W(b)
+        + C(1, 1, one, zero) * (C(2, 1, one, zero) * (W(b + 3) - W(b + 2)) + W(b + 2)))
+    alpha_j, lam = C(0, layer_count, one, zero), C(1, 1, one, zero)
+    if not is_final:
+        sc = alpha_j * (W(wit0) * W(wit0 + 3) + W(wit0 + 1) * W(wit0 + 2) + lam * W(wit0 + 2) * W(wit0 + 3))
+        return sc, claim, 4
+    ncol = inst["num_columns"]
+    first = wit0 + (2 if inst["kind"] == 1 else 0)
+    d_lo, d_hi = Expr.const(inst["constant"]), Expr.const(inst["constant"])
+    pw = one
+    for i in range(ncol):
+        d_lo = d_lo + Expr.const(pw) * W(first + i)
+        d_hi = d_hi + Expr.const(pw) * W(first + ncol + i)
+        pw = F.mul(pw, inst["sep"])
+    if inst["kind"] == 1:
+        return alpha_j * (W(wit0) * d_hi + W(wit0 + 1) * d_lo + lam * d_lo * d_hi), claim, 2 + 2 * ncol
+    return alpha_j * (-d_hi - d_lo + lam * d_lo * d_hi), claim, 2 * ncol
+
+
+def logup_batch_verify(F, proof, instances, transcript):
+    """new_verify_logup_proof_multiple_sizes (zkml/src/lookup/logup_gkr/verifier.rs:77-256).
+    Returns dict(output_claims, point, numerators, denominators); raises on failure."""
+    transcript.append_scalars([F.from_int(len(instances))])
+    for o in proof["circuit_outputs"]:
+        transcript.append_scalars(o)
+    numer = [F.add(F.mul(e[0], e[3]), F.mul(e[1], e[2])) for e in proof["circuit_outputs"]]
+    denom = [F.mul(e[2], e[3]) for e in proof["circuit_outputs"]]
+    out_by_size = {}
+    for inst, o in zip(instances, proof["circuit_outputs"]):
+        out_by_size.setdefault(inst["num_vars"], []).append(o)
+    sizes = sorted({i["num_vars"] for i in instances}, reverse=True)
+    total_layers = len(proof["sumcheck_proofs"])
+    rho = transcript.append_and_sample(b"initial_batching")
+    alpha = transcript.append_and_sample(b"initial_alpha")
+    lam = transcript.append_and_sample(b"initial_lambda")
+    point = [rho]
+    for i, (sc_proof, round_evals) in enumerate(zip(proof["sumcheck_proofs"], proof["round_evaluations"])):
+        remaining = total_layers - i
+        joining = [e for o in out_by_size.get(remaining, []) for e in o]
+        wit_evals = (proof["round_evaluations"][i - 1] if i else []) + joining
+        layer_count, wit_off = 0, 0
+        claim_expr = Expr.const(F.zero)
+        group_exprs, eq_points = [], []
+        for size in sizes:
+            if size < remaining:
+                continue
+            mult = Expr.const(F.from_int(1 << (total_layers - size)))
+            group = Expr.const(F.zero)
+            cur_vars = size + 1 - remaining
+            for inst in instances:
+                if inst["num_vars"] == size:
+                    sc, cl, nw = _verifier_instance_exprs(F, inst, layer_count, wit_off, i + 1 == total_layers)
+                    layer_count += 1
+                    wit_off += nw
+                    group = group + sc
+                    claim_expr = claim_expr + mult * cl
+            eq_points.append(point[len(point) - cur_vars:])
+            group_exprs.append(group)
+        current_claim = eval_expr(F, claim_expr, wit_evals, [alpha, lam, rho])
+        transcript.append_scalars([current_claim])
+        cur_point, expected = sumcheck_verify(F, current_claim, sc_proof, i + 1, 3, transcript)
+        rho = transcript.append_and_sample(b"logup_batching")
+        full = Expr.const(F.zero)
+        for g_i, g in enumerate(group_exprs):
+            full = full + g * Expr.wit(wit_off + g_i)
+        eq_vals = [identity_eval(F, cur_point[len(cur_point) - len(p):], p) for p in eq_points]
+        calc = eval_expr(F, full, list(round_evals) + eq_vals, [alpha, lam])
+        if i + 1 != total_layers:
+            alpha = transcript.append_and_sample(b"logup_alpha")
+            lam = transcript.append_and_sample(b"logup_lambda")
+        if calc != expected:
+            raise ValueError(f"LogUp Verifier error at round {i}")
+        point = cur_point + [rho]
+    last = proof["round_evaluations"][-1]
+    skip, claims = 0, []
+    for inst in instances:
+        ncol = inst["num_columns"]
+        n = 2 * ncol + (2 if inst["kind"] == 1 else 0)
+        ev = last[skip:skip + n]
+        skip += n
+        pt = point[len(point) - 1 - inst["num_vars"]:]
+        if inst["kind"] == 1:
+            claims.append((pt, F.add(F.mul(rho, F.sub(ev[1], ev[0])), ev[0])))
+            ev = ev[2:]
+        claims += [(pt, F.add(F.mul(rho, F.sub(h, l)), l)) for l, h in zip(ev[:ncol], ev[ncol:])]
+    return dict(output_claims=claims, point=point, numerators=numer, denominators=denom)
+
+
+# --------------------------------------------------------- layer-level provers
+def hadamard_prove(F, transcript, claim_point, v1, v2):
+    """zkml/src/layers/hadamard.rs:93-131: sum_x v1(x) v2(x) eq(r, x)."""
+    beta = eq_evals(F, claim_point)
+    terms = {(0, 1, 2): F.one}
+    proof, point, finals = sumcheck_prove(F, len(claim_point), [v1, v2, beta], terms, transcript)
+    return dict(sumcheck=proof, individual_claim=finals[:2], point=point)
+
+
+def same_poly_prove(F, transcript, poly, claims):
+    """same_poly::Prover::prove (zkml/src/iop/same_poly.rs:84-114):
+    sum_x f(x) * sum_i a_i eq_i(x)."""
+    chal = transcript.read_challenges(len(claims))
+    betas = [eq_evals(F, pt) for pt, _ in claims]
+    e = Expr.const(F.zero)
+    for i in range(len(claims)):
+        e = e + Expr.chal(i, 1, F.one, F.zero) * Expr.wit(1 + i)
+    terms = expr_to_terms(F, Expr.wit(0) * e, chal)
+    n = len(claims[0][0])
+    proof, point, finals = sumcheck_prove(F, n, [poly] + betas, terms, transcript)
+    return dict(sumcheck=proof, eval=finals[0], point=point, challenges=chal)
+
+
+# -------------------------------------------------------------- serialization
+def serialize_scalars(F, vals):
+    return b"".join(F.to_canonical(v) for v in vals)
+
+
+def serialize_sumcheck_proof(F, proof):
+    return b"".join(serialize_scalars(F, ev) for ev in proof)
+
+
+def serialize_logup_proof(F, p):
+    """A flat canonical encoding used to compare proofs byte for byte:
+    u32 counts (LE) followed by canonical scalars, field order of
+    LogUpBatchProof (zkml/src/lookup/logup_gkr/structs.rs:561-578)."""
+    out = bytearray()
+    u32 = lambda x: int(x).to_bytes(4, "little")
+    out += u32(len(p["sumcheck_proofs"]))
+    for sp in p["sumcheck_proofs"]:
+        out += u32(len(sp))
+        for ev in sp:
+            out += u32(len(ev)) + serialize_scalars(F, ev)
+    out += u32(len(p["round_evaluations"]))
+    for ev in p["round_evaluations"]:
+        out += u32(len(ev)) + serialize_scalars(F, ev)
+    out += u32(len(p["output_claims"]))
+    for pt, e in p["output_claims"]:
+        out += u32(len(pt)) + serialize_scalars(F, pt) + serialize_scalars(F, [e])
+    out += u32(len(p["circuit_outputs"]))
+    for o in p["circuit_outputs"]:
+        out += u32(len(o)) + serialize_scalars(F, o)
+    out += u32(p["proof_type"])
+    out += u32(len(p["num_vars_per_instance"]))
+    for v in p["num_vars_per_instance"]:
+        out += u32(v)
+    out += u32(len(p["num_denominator_columns_per_instance"]))
+    for v in p["num_denominator_columns_per_instance"]:
+        out += u32(v)
+    return bytes(out)
