@@ -1,0 +1,331 @@
+"""Benchmark of the sumcheck hot path on B200.
+
+Workload: the standalone sumcheck microbenchmark — prove sum_x f(x) g(x) h(x)
+over three random multilinear tables of 2^n Goldilocks base-field values, the
+verifier challenges being quadratic-extension elements drawn from the host
+transcript.  One "step" is one complete proof (all n rounds).  The metric is
+sumcheck GB/s: algorithmic bytes B_alg = k (2 s0 + 2 s1) 2^n = 144 * 2^n (k = 3
+tables, s0 = 8 B before and s1 = 16 B after the first fold) divided by the time
+of a whole proof, host transcript turn-arounds included.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--log2-size n] [--field gl|fr]
+    python bench.py --impl reference ...   times the CPU restatement of the same prover
+
+Prints one JSON line (see the keys below).  Inputs are seeded synthetic data.
+"""
+import argparse
+import importlib
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+GL_MOD = 2**64 - 2**32 + 1
+FALLBACK_HBM_GBS = 6650.0
+
+# DRAM traffic of the dominant launch from the ncu capture summarised under
+# profiles/ (bytes per table entry of the launch's input); None until captured.
+NCU_TRAFFIC_BYTES_PER_INPUT_ENTRY = None
+
+
+def alg_bytes(field, n, k=3):
+    s0, s1 = (8, 16) if field == "gl" else (32, 32)
+    return k * (2 * s0 + 2 * s1) * (1 << n)
+
+
+def load_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return FALLBACK_HBM_GBS, "fallback (6.65 TB/s)"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device):
+        self.device = device
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.device), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                parts = [x.strip() for x in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    mx.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        os.unlink(self.path)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def host_tables(field, n, seed, pinned):
+    """Three seeded tables of 2^n entries in host memory (pinned when asked)."""
+    import torch
+    N = 1 << n
+    words = 1 if field == "gl" else 4
+    t = torch.empty((3, N, words), dtype=torch.int64, pin_memory=pinned)
+    a = t.numpy().view(np.uint64)
+    rng = np.random.default_rng(seed)
+    chunk = 1 << 22
+    for j in range(3):
+        for off in range(0, N, chunk):
+            m = min(chunk, N - off)
+            if field == "gl":
+                a[j, off:off + m, 0] = rng.integers(0, GL_MOD, size=m, dtype=np.uint64)
+            else:
+                blk = rng.integers(0, 2**64, size=(m, 4), dtype=np.uint64)
+                blk[:, 3] &= np.uint64((1 << 60) - 1)  # below the modulus: valid Montgomery residues
+                a[j, off:off + m] = blk
+    return t, (a[:, :, 0] if field == "gl" else a)
+
+
+def cpu_prove(orc, F, n, tabs):
+    return orc.sumcheck_prove(F, n, tabs, {(0, 1, 2): F.one}, orc.Transcript(F))
+
+
+def cpu_baseline(field, n_sample, seed):
+    """The CPU restatement (oracle) of the same prover on the host cores."""
+    from oracle import oracle as orc
+    F = orc.GlField if field == "gl" else orc.FrField
+    rng = np.random.default_rng(seed)
+    tabs = [F.random_table_fast(rng, 1 << n_sample) for _ in range(3)]
+    cpu_prove(orc, F, min(n_sample, 16), [t[: 1 << min(n_sample, 16)] for t in tabs])  # warm up threads
+    t0 = time.perf_counter()
+    cpu_prove(orc, F, n_sample, tabs)
+    dt = time.perf_counter() - t0
+    return {"value": alg_bytes(field, n_sample) / dt / 1e9, "unit": "GB/s", "cores": orc.lib().orc_num_threads(),
+            "kind": "port", "seconds": dt,
+            "sample": f"one full proof at 2^{n_sample} entries per table (same shape and field, smaller size); "
+                      "C/OpenMP restatement of the prover, not the reference's Rust binary"}
+
+
+def metric_name(field):
+    return "sumcheck_GBps_" + ("goldilocks" if field == "gl" else "bn254")
+
+
+def workload_config(field, n, n_gpus):
+    name = "Goldilocks base tables, Ext2 challenges" if field == "gl" else "BN254 Fr"
+    return {"workload": f"standalone sumcheck microbench f*g*h, 2^{n} entries per table, {name} "
+                        "(BASELINE.json configs[1])",
+            "log2_size": n, "field": field, "tables": 3, "degree": 3, "sharding": f"top log2({n_gpus}) variables",
+            "l2": "inputs per step exceed the 126 MB L2; no flush needed"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle as orc
+    F = orc.GlField if args.field == "gl" else orc.FrField
+    n_s = args.cpu_sample_log2
+    rng = np.random.default_rng(args.seed)
+    tabs = [F.random_table_fast(rng, 1 << n_s) for _ in range(3)]
+    for _ in range(args.warmup):
+        cpu_prove(orc, F, n_s, tabs)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_prove(orc, F, n_s, tabs)
+    dt = (time.perf_counter() - t0) / args.steps
+    val = alg_bytes(args.field, n_s) / dt / 1e9
+    cores = orc.lib().orc_num_threads()
+    sample = (f"each step is one full proof at 2^{n_s} entries per table (bounded sample of the 2^{args.log2_size} "
+              "workload; throughput is size-independent on the CPU)")
+    print(json.dumps({
+        "impl": "reference", "metric": metric_name(args.field), "value": val, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "u64" if args.field == "gl" else "u256", "data": "synthetic",
+        "config": workload_config(args.field, args.log2_size, args.gpus),
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference's Rust prover cannot be built here (no Rust toolchain, dp-crypto not vendored); "
+                "this is the C/OpenMP restatement in oracle/ on the host cores",
+    }))
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from __graft_entry__ import load_package
+    dpb = load_package()
+    prover = importlib.import_module("deep_prove_b200.prover")
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    torch.cuda.set_device(local_rank)
+    field, n = args.field, args.log2_size
+    base_dtype = dpb.GL_BASE if field == "gl" else dpb.FR
+    fam = dpb.GL_EXT if field == "gl" else dpb.FR
+    ctx = dpb.Context(local_rank)
+    stream = torch.cuda.ExternalStream(ctx.stream, device=torch.device("cuda", local_rank))
+
+    if world > 1:
+        raise SystemExit("multi-GPU sharding is wired in deep-prove_b200.sharded; see --gpus handling there")
+
+    pinned, host = host_tables(field, n, args.seed + rank, pinned=True)
+    mles = [ctx.upload(host[j], base_dtype) for j in range(3)]
+    terms = dpb.make_terms([(dpb.one_bytes(fam), [0, 1, 2])], bytes)
+
+    def step_device():
+        t = prover.Blake3Transcript(fam)
+        st = prover.IOPProverState.prove(ctx, n, mles, terms, t)
+        t.free()
+        return st
+
+    def step_e2e():
+        ms = [ctx.upload(host[j], base_dtype) for j in range(3)]
+        t = prover.Blake3Transcript(fam)
+        st = prover.IOPProverState.prove(ctx, n, ms, terms, t)
+        t.free()
+        for m in ms:
+            m.free()
+        return st
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        ctx.sync()
+        torch.cuda.synchronize()
+
+    # ---- device-resident throughput
+    for _ in range(args.warmup):
+        step_device()
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    ctx.profile(True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        st = step_device()
+    e1.record(stream)
+    barrier()
+    ctx.profile(False)
+    clocks = sampler.stop()
+    ms_total = e0.elapsed_time(e1)
+    if world > 1:
+        tt = torch.tensor([ms_total], device="cuda")
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms_total = float(tt.item())
+    ms_step = ms_total / args.steps
+    n_global = n + (world.bit_length() - 1)
+    value = alg_bytes(field, n_global) / (ms_step * 1e-3) / 1e9
+    prof = ctx.profile_read()
+
+    # ---- end to end: host buffers in, proof out, copies inside the timed region
+    for _ in range(min(args.warmup, 2)):
+        step_e2e()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        st = step_e2e()
+    barrier()
+    e2e_s = (time.perf_counter() - t0) / args.steps
+    words = 2 if field == "gl" else 4
+    h2d = 3 * (1 << n) * (8 if field == "gl" else 32)
+    d2h = (n * 4 + n + 3) * words * 8
+
+    if rank != 0:
+        return
+    peak, peak_src = load_peak()
+    top = max(prof, key=lambda e: e["total_ms"]) if prof else None
+    roofline = None
+    if top:
+        per_launch_ms = top["total_ms"] / top["launches"]
+        ach = top["alg_bytes_per_launch"] / (per_launch_ms * 1e-3) / 1e9
+        traffic = None
+        if NCU_TRAFFIC_BYTES_PER_INPUT_ENTRY is not None:
+            traffic = NCU_TRAFFIC_BYTES_PER_INPUT_ENTRY * 3 * (1 << (n - max(top["round"] - 1, 0)))
+        roofline = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                    "traffic": traffic, "kernel": top["kernel"], "round": top["round"],
+                    "launch_ms": per_launch_ms, "alg_bytes_per_launch": top["alg_bytes_per_launch"],
+                    "peak_source": peak_src}
+    kernels = [{"kernel": e["kernel"], "round": e["round"], "launches": e["launches"],
+                "ms_per_launch": e["total_ms"] / e["launches"],
+                "GBps": e["alg_bytes_per_launch"] / (e["total_ms"] / e["launches"] * 1e-3) / 1e9}
+               for e in sorted(prof, key=lambda e: e["round"])[:6]]
+    out = {
+        "metric": metric_name(field), "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "u64" if field == "gl" else "u256", "data": "synthetic",
+        "config": workload_config(field, n_global, world),
+        "frac_of_hbm_peak": value / (peak * world),
+        "roofline": roofline,
+        "kernels": kernels,
+        "e2e": {"value": alg_bytes(field, n_global) / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3},
+        "gpu_launches": args.steps * (n + 1) * world,
+        "clocks": clocks,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        out["cpu_baseline"] = cpu_baseline(field, args.cpu_sample_log2, args.seed)
+    print(json.dumps(out))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--log2-size", type=int, default=28)
+    ap.add_argument("--field", default="gl", choices=["gl", "fr"])
+    ap.add_argument("--cpu-sample-log2", type=int, default=24)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -42,10 +42,17 @@ class Term(ctypes.Structure):
                 ("idx", ctypes.c_uint16 * MAX_FACTORS)]
 
 
+class ProfileEntry(ctypes.Structure):
+    _fields_ = [("kernel", ctypes.c_char * 48), ("round", ctypes.c_uint32), ("launches", ctypes.c_uint32),
+                ("total_ms", ctypes.c_double), ("alg_bytes_per_launch", ctypes.c_uint64)]
+
+
 _vp, _u32, _u64, _int = ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_int
 _pp = ctypes.POINTER(ctypes.c_void_p)
 
 SIGNATURES = {
+    "dpb_profile_enable": (_int, [_vp, _int]),
+    "dpb_profile_read": (_int, [_vp, ctypes.POINTER(ProfileEntry), _u32, ctypes.POINTER(_u32)]),
     "dpb_init": (_int, [_int, _pp]),
     "dpb_shutdown": (None, [_vp]),
     "dpb_last_error": (ctypes.c_char_p, []),
@@ -100,6 +107,16 @@ def chal_dtype(dtype):
     return FR if dtype == FR else GL_EXT
 
 
+FR_MODULUS = 21888242871839275222246405745257275088548364400416034343698204186575808495617
+
+
+def one_bytes(dtype):
+    """The field's one as native challenge-element bytes (Fr: Montgomery form)."""
+    if dtype == FR:
+        return ((1 << 256) % FR_MODULUS).to_bytes(32, "little")
+    return (1).to_bytes(8, "little") + bytes(8)
+
+
 def _buf(a):
     return ctypes.c_void_p(a.ctypes.data)
 
@@ -132,6 +149,18 @@ class Context:
     @property
     def stream(self):
         return lib.dpb_stream(self.h)
+
+    def profile(self, on):
+        check(lib.dpb_profile_enable(self.h, 1 if on else 0))
+
+    def profile_read(self):
+        n = ctypes.c_uint32()
+        check(lib.dpb_profile_read(self.h, None, 0, ctypes.byref(n)))
+        arr = (ProfileEntry * max(n.value, 1))()
+        check(lib.dpb_profile_read(self.h, arr, n.value, ctypes.byref(n)))
+        return [dict(kernel=arr[i].kernel.decode(), round=arr[i].round, launches=arr[i].launches,
+                     total_ms=arr[i].total_ms, alg_bytes_per_launch=arr[i].alg_bytes_per_launch)
+                for i in range(n.value)]
 
     # ---- tables
     def upload(self, array, dtype, form=FORM_NATIVE):

@@ -211,6 +211,8 @@ int dpb_init(int device, dpb_ctx** out) {
     DPB_CUDA(cudaHostGetDevicePointer(&ctx->result_dev, ctx->result_host, 0));
     ctx->stage_bytes = 64 * 1024;
     DPB_CUDA(cudaMalloc(&ctx->stage_dev, ctx->stage_bytes));
+    DPB_CUDA(cudaEventCreate(&ctx->prof_ev[0]));
+    DPB_CUDA(cudaEventCreate(&ctx->prof_ev[1]));
     *out = ctx;
     return DPB_OK;
 }
@@ -223,6 +225,8 @@ void dpb_shutdown(dpb_ctx* ctx) {
     cudaFree(ctx->counter);
     cudaFree(ctx->stage_dev);
     cudaFreeHost(ctx->result_host);
+    cudaEventDestroy(ctx->prof_ev[0]);
+    cudaEventDestroy(ctx->prof_ev[1]);
     cudaStreamDestroy(ctx->stream);
     delete ctx;
 }
@@ -234,6 +238,20 @@ int dpb_sync(dpb_ctx* ctx) {
 }
 
 void* dpb_stream(dpb_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+
+int dpb_profile_enable(dpb_ctx* ctx, int on) {
+    if (!ctx) return fail(DPB_EINVAL, "null context");
+    if (on) ctx->prof_log.clear();
+    ctx->profile = on != 0;
+    return DPB_OK;
+}
+
+int dpb_profile_read(dpb_ctx* ctx, dpb_profile_entry* out, uint32_t cap, uint32_t* n) {
+    if (!ctx || !n || (!out && cap)) return fail(DPB_EINVAL, "null argument");
+    *n = (uint32_t)ctx->prof_log.size();
+    for (uint32_t i = 0; i < *n && i < cap; i++) out[i] = ctx->prof_log[i];
+    return DPB_OK;
+}
 
 int dpb_mle_alloc(dpb_ctx* ctx, int dtype, uint64_t len, dpb_mle** out) {
     if (!ctx || !out) return fail(DPB_EINVAL, "null argument");

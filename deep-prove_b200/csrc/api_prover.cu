@@ -1,0 +1,346 @@
+// C ABI of the host-side prover layer (include/dpb_prover.h): transcript,
+// expression expansion, IOPProverState::prove and the batched logup prover.
+// Exceptions of the C++ layer are caught here and turned into status codes.
+#include "../../include/dpb_prover.h"
+
+#include "common.cuh"
+#include "host/logup.hpp"
+#include "host/prover.hpp"
+#include "host/transcript.hpp"
+
+using namespace dpb;
+
+struct dpb_transcript {
+    bool gl;
+    Blake3Transcript<GlFam>* g = nullptr;
+    Blake3Transcript<FrFam>* f = nullptr;
+    ~dpb_transcript() {
+        delete g;
+        delete f;
+    }
+};
+
+struct dpb_logup_proof {
+    std::vector<uint8_t> bytes;
+};
+
+namespace {
+
+template <class Fn>
+int guarded(Fn&& fn) {
+    try {
+        return fn();
+    } catch (const dp_crypto::Error& e) {
+        return fail(e.code, "%s", e.what());
+    } catch (const std::bad_alloc&) {
+        return fail(DPB_ENOMEM, "host allocation failed");
+    } catch (const std::exception& e) {
+        return fail(DPB_EINVAL, "%s", e.what());
+    }
+}
+
+template <class F>
+dp_crypto::Expression<F> build_expr(const dpb_expr_node* nodes, uint32_t n) {
+    typedef dp_crypto::Expression<F> X;
+    typedef typename F::E E;
+    std::vector<X> st;
+    for (uint32_t i = 0; i < n; i++) {
+        const dpb_expr_node& nd = nodes[i];
+        E c0, c1;
+        memcpy(&c0, nd.c0, sizeof(E));
+        memcpy(&c1, nd.c1, sizeof(E));
+        auto pop = [&]() {
+            if (st.empty()) throw dp_crypto::Error(DPB_EINVAL, "malformed expression: stack underflow");
+            X x = st.back();
+            st.pop_back();
+            return x;
+        };
+        switch (nd.op) {
+            case DPB_EXPR_WITIN: st.push_back(X::WitIn((uint16_t)nd.a)); break;
+            case DPB_EXPR_CONSTANT: st.push_back(X::Constant(c0)); break;
+            case DPB_EXPR_CHALLENGE: st.push_back(X::Challenge((uint16_t)nd.a, nd.b, c0, c1)); break;
+            case DPB_EXPR_ADD: { X r = pop(), l = pop(); st.push_back(l + r); break; }
+            case DPB_EXPR_SUB: { X r = pop(), l = pop(); st.push_back(l - r); break; }
+            case DPB_EXPR_MUL: { X r = pop(), l = pop(); st.push_back(l * r); break; }
+            case DPB_EXPR_NEG: { X x = pop(); st.push_back(-x); break; }
+            default: throw dp_crypto::Error(DPB_EINVAL, "malformed expression: unknown opcode");
+        }
+    }
+    if (st.size() != 1) throw dp_crypto::Error(DPB_EINVAL, "malformed expression: it must leave one value");
+    return st[0];
+}
+
+template <class F>
+std::vector<typename F::E> elems(const void* p, uint32_t n) {
+    std::vector<typename F::E> v(n);
+    if (n) memcpy(v.data(), p, n * sizeof(typename F::E));
+    return v;
+}
+
+template <class F>
+int expr_to_terms_impl(const dpb_expr_node* nodes, uint32_t n_nodes, const void* challenges, uint32_t n_ch,
+                       dpb_term* out, uint32_t cap, uint32_t* n_out) {
+    auto e = build_expr<F>(nodes, n_nodes);
+    dp_crypto::VirtualPolynomialsBuilder<F> b(1, 0);
+    auto vp = b.to_virtual_polys({e}, elems<F>(challenges, n_ch));
+    *n_out = (uint32_t)vp.terms.size();
+    for (uint32_t i = 0; i < vp.terms.size() && i < cap; i++) out[i] = vp.terms[i];
+    return DPB_OK;
+}
+
+template <class F, class T>
+int prove_sumcheck_impl(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, uint32_t k, const dpb_term* terms,
+                        uint32_t n_terms, T& tr, void* out_round_evals, uint32_t cap, void* out_point,
+                        void* out_final, uint32_t* out_degree) {
+    typedef typename F::E E;
+    dp_crypto::VirtualPolynomials<F> vp;
+    vp.num_vars = num_vars;
+    vp.mles.assign(mles, mles + k);
+    vp.terms.assign(terms, terms + n_terms);
+    for (const auto& t : vp.terms) vp.max_degree = std::max(vp.max_degree, t.n_factors);
+    if ((uint64_t)num_vars * (vp.max_degree + 1) > cap)
+        return fail(DPB_EINVAL, "round-evaluation buffer holds %u elements, %llu needed", cap,
+                    (unsigned long long)num_vars * (vp.max_degree + 1));
+    auto res = dp_crypto::IOPProverState<F>::prove(ctx, vp, tr);
+    E* o = (E*)out_round_evals;
+    for (const auto& m : res.first.proofs)
+        for (const auto& v : m.evaluations) *o++ = v;
+    memcpy(out_point, res.second.collect_raw_challenges().data(), num_vars * sizeof(E));
+    memcpy(out_final, res.second.get_mle_flatten_final_evaluations().data(), k * sizeof(E));
+    if (out_degree) *out_degree = vp.max_degree;
+    return DPB_OK;
+}
+
+// hadamard.rs:93-131
+template <class F, class T>
+int hadamard_impl(dpb_ctx* ctx, dpb_mle* v1, dpb_mle* v2, const void* point, uint32_t n, T& tr, void* out_evals,
+                  void* out_point, void* out_claims) {
+    typedef typename F::E E;
+    typedef dp_crypto::Expression<F> X;
+    if (dpb_mle_len(v1) != (1ull << n) || dpb_mle_len(v2) != (1ull << n))
+        return fail(DPB_EINVAL, "claim point has %u coordinates but the tables have %llu and %llu entries", n,
+                    (unsigned long long)dpb_mle_len(v1), (unsigned long long)dpb_mle_len(v2));
+    dpb_mle* beta = nullptr;
+    dp_crypto::check(dpb_eq_table(ctx, F::kChalDtype, point, n, &beta));
+    struct G { dpb_mle* m; ~G() { dpb_mle_free(m); } } g{beta};
+    dp_crypto::VirtualPolynomialsBuilder<F> b(1, n);
+    X expr = X::Constant(F::one());
+    for (dpb_mle* p : {v1, v2, beta}) expr = expr * b.lift(p);
+    auto vp = b.to_virtual_polys({expr}, {});
+    auto res = dp_crypto::IOPProverState<F>::prove(ctx, vp, tr);
+    E* o = (E*)out_evals;
+    for (const auto& m : res.first.proofs)
+        for (const auto& v : m.evaluations) *o++ = v;
+    memcpy(out_point, res.second.collect_raw_challenges().data(), n * sizeof(E));
+    memcpy(out_claims, res.second.get_mle_flatten_final_evaluations().data(), 2 * sizeof(E));
+    return DPB_OK;
+}
+
+// same_poly.rs:84-114
+template <class F, class T>
+int same_poly_impl(dpb_ctx* ctx, dpb_mle* poly, const void* points, uint32_t n_claims, uint32_t n, T& tr,
+                   void* out_evals, void* out_point, void* out_eval) {
+    typedef typename F::E E;
+    typedef dp_crypto::Expression<F> X;
+    if (dpb_mle_len(poly) != (1ull << n)) return fail(DPB_EINVAL, "invalid input len wrt to poly");
+    if (n_claims == 0) return fail(DPB_EINVAL, "no claims");
+    const std::vector<E> chal = tr.read_challenges(n_claims);
+    std::vector<dpb_mle*> betas(n_claims, nullptr);
+    struct G {
+        std::vector<dpb_mle*>& v;
+        ~G() { for (auto* m : v) dpb_mle_free(m); }
+    } g{betas};
+    for (uint32_t i = 0; i < n_claims; i++)
+        dp_crypto::check(dpb_eq_table(ctx, F::kChalDtype, (const E*)points + (size_t)i * n, n, &betas[i]));
+    dp_crypto::VirtualPolynomialsBuilder<F> b(1, n);
+    X poly_expr = b.lift(poly);
+    X sum = X::Constant(F::zero());
+    for (uint32_t i = 0; i < n_claims; i++)
+        sum = sum + X::Challenge((uint16_t)i, 1, F::one(), F::zero()) * b.lift(betas[i]);
+    auto vp = b.to_virtual_polys({poly_expr * sum}, chal);
+    auto res = dp_crypto::IOPProverState<F>::prove(ctx, vp, tr);
+    E* o = (E*)out_evals;
+    for (const auto& m : res.first.proofs)
+        for (const auto& v : m.evaluations) *o++ = v;
+    memcpy(out_point, res.second.collect_raw_challenges().data(), n * sizeof(E));
+    memcpy(out_eval, res.second.get_mle_flatten_final_evaluations().data(), sizeof(E));
+    return DPB_OK;
+}
+
+template <class F, class T>
+int logup_impl(dpb_ctx* ctx, const dpb_logup_input* inputs, uint32_t n_inputs, T& tr, dpb_logup_proof** out) {
+    typedef typename F::E E;
+    using namespace zkml::logup_gkr;
+    std::vector<LogUpInput<F>> in;
+    for (uint32_t i = 0; i < n_inputs; i++) {
+        const dpb_logup_input& s = inputs[i];
+        if (!s.columns || !s.constant_challenge || !s.column_separation_challenge)
+            return fail(DPB_EINVAL, "input %u has a null field", i);
+        std::vector<dpb_mle*> cols(s.columns, s.columns + s.n_columns);
+        for (auto* c : cols)
+            if (!c) return fail(DPB_EINVAL, "input %u has a null column", i);
+        E cst, sep;
+        memcpy(&cst, s.constant_challenge, sizeof(E));
+        memcpy(&sep, s.column_separation_challenge, sizeof(E));
+        if (s.kind == DPB_LOGUP_TABLE) in.push_back(LogUpInput<F>::new_table(cols, s.multiplicities, cst, sep));
+        else if (s.kind == DPB_LOGUP_LOOKUP) in.push_back(LogUpInput<F>::new_lookup(cols, cst, sep, s.columns_per_instance));
+        else return fail(DPB_EINVAL, "input %u has unknown kind %d", i, s.kind);
+    }
+    auto proof = new_batch_multiple_sizes_prove<F>(ctx, in, tr);
+    dpb_logup_proof* p = new dpb_logup_proof();
+    p->bytes = proof.serialize();
+    *out = p;
+    return DPB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int dpb_transcript_new(int family_dtype, const void* label, size_t label_len, dpb_transcript** out) {
+    if (!out || (!label && label_len)) return fail(DPB_EINVAL, "null argument");
+    if (!valid_dtype(family_dtype)) return fail(DPB_EINVAL, "unknown dtype %d", family_dtype);
+    return guarded([&] {
+        dpb_transcript* t = new dpb_transcript();
+        t->gl = is_gl(family_dtype);
+        if (t->gl) t->g = new Blake3Transcript<GlFam>(label, label_len);
+        else t->f = new Blake3Transcript<FrFam>(label, label_len);
+        *out = t;
+        return DPB_OK;
+    });
+}
+
+int dpb_transcript_clone(const dpb_transcript* t, dpb_transcript** out) {
+    if (!t || !out) return fail(DPB_EINVAL, "null argument");
+    return guarded([&] {
+        dpb_transcript* c = new dpb_transcript();
+        c->gl = t->gl;
+        if (t->gl) c->g = new Blake3Transcript<GlFam>(*t->g);
+        else c->f = new Blake3Transcript<FrFam>(*t->f);
+        *out = c;
+        return DPB_OK;
+    });
+}
+
+void dpb_transcript_free(dpb_transcript* t) { delete t; }
+
+int dpb_transcript_append_scalars(dpb_transcript* t, const void* scalars, uint32_t n) {
+    if (!t || (!scalars && n)) return fail(DPB_EINVAL, "null argument");
+    return guarded([&] {
+        if (t->gl) t->g->append_scalars((const Gl2*)scalars, n);
+        else t->f->append_scalars(elems<FrFam>(scalars, n));
+        return DPB_OK;
+    });
+}
+
+int dpb_transcript_append_and_sample(dpb_transcript* t, const void* label, size_t label_len, void* out) {
+    if (!t || !out || (!label && label_len)) return fail(DPB_EINVAL, "null argument");
+    return guarded([&] {
+        if (t->gl) { Gl2 c = t->g->append_and_sample(label, label_len); memcpy(out, &c, sizeof c); }
+        else { Fr c = t->f->append_and_sample(label, label_len); memcpy(out, &c, sizeof c); }
+        return DPB_OK;
+    });
+}
+
+int dpb_transcript_challenge_scalar(dpb_transcript* t, void* out) {
+    if (!t || !out) return fail(DPB_EINVAL, "null argument");
+    return guarded([&] {
+        if (t->gl) { Gl2 c = t->g->challenge_scalar(); memcpy(out, &c, sizeof c); }
+        else { Fr c = t->f->challenge_scalar(); memcpy(out, &c, sizeof c); }
+        return DPB_OK;
+    });
+}
+
+int dpb_transcript_state(const dpb_transcript* t, uint8_t out_state[32], uint32_t* out_round) {
+    if (!t || !out_state) return fail(DPB_EINVAL, "null argument");
+    memcpy(out_state, t->gl ? t->g->state() : t->f->state(), 32);
+    if (out_round) *out_round = t->gl ? t->g->round() : t->f->round();
+    return DPB_OK;
+}
+
+int dpb_expr_to_terms(int family_dtype, const dpb_expr_node* nodes, uint32_t n_nodes, const void* challenges,
+                      uint32_t n_challenges, dpb_term* out, uint32_t cap, uint32_t* n_out) {
+    if (!nodes || !n_out || (!out && cap) || (!challenges && n_challenges)) return fail(DPB_EINVAL, "null argument");
+    if (!valid_dtype(family_dtype)) return fail(DPB_EINVAL, "unknown dtype %d", family_dtype);
+    return guarded([&] {
+        return is_gl(family_dtype)
+                   ? expr_to_terms_impl<GlFam>(nodes, n_nodes, challenges, n_challenges, out, cap, n_out)
+                   : expr_to_terms_impl<FrFam>(nodes, n_nodes, challenges, n_challenges, out, cap, n_out);
+    });
+}
+
+int dpb_expr_eval(int family_dtype, const dpb_expr_node* nodes, uint32_t n_nodes, const void* wit_evals,
+                  uint32_t n_wit, const void* challenges, uint32_t n_challenges, void* out) {
+    if (!nodes || !out || (!wit_evals && n_wit) || (!challenges && n_challenges))
+        return fail(DPB_EINVAL, "null argument");
+    if (!valid_dtype(family_dtype)) return fail(DPB_EINVAL, "unknown dtype %d", family_dtype);
+    return guarded([&] {
+        if (is_gl(family_dtype)) {
+            Gl2 v = build_expr<GlFam>(nodes, n_nodes).evaluate(elems<GlFam>(wit_evals, n_wit), elems<GlFam>(challenges, n_challenges));
+            memcpy(out, &v, sizeof v);
+        } else {
+            Fr v = build_expr<FrFam>(nodes, n_nodes).evaluate(elems<FrFam>(wit_evals, n_wit), elems<FrFam>(challenges, n_challenges));
+            memcpy(out, &v, sizeof v);
+        }
+        return DPB_OK;
+    });
+}
+
+int dpb_prove_sumcheck(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, uint32_t k, const dpb_term* terms,
+                       uint32_t n_terms, dpb_transcript* t, void* out_round_evals, uint32_t round_evals_cap,
+                       void* out_point, void* out_final_evals, uint32_t* out_degree) {
+    if (!ctx || !mles || !terms || !t || !out_round_evals || !out_point || !out_final_evals)
+        return fail(DPB_EINVAL, "null argument");
+    if (k == 0 || !mles[0]) return fail(DPB_EINVAL, "no tables");
+    if (is_gl(mles[0]->dtype) != t->gl) return fail(DPB_EINVAL, "transcript and tables are of different fields");
+    return guarded([&] {
+        return t->gl ? prove_sumcheck_impl<GlFam>(ctx, num_vars, mles, k, terms, n_terms, *t->g, out_round_evals,
+                                                  round_evals_cap, out_point, out_final_evals, out_degree)
+                     : prove_sumcheck_impl<FrFam>(ctx, num_vars, mles, k, terms, n_terms, *t->f, out_round_evals,
+                                                  round_evals_cap, out_point, out_final_evals, out_degree);
+    });
+}
+
+int dpb_hadamard_prove(dpb_ctx* ctx, dpb_mle* v1, dpb_mle* v2, const void* claim_point, uint32_t n,
+                       dpb_transcript* t, void* out_round_evals, void* out_point, void* out_claims) {
+    if (!ctx || !v1 || !v2 || !claim_point || !t || !out_round_evals || !out_point || !out_claims)
+        return fail(DPB_EINVAL, "null argument");
+    if (is_gl(v1->dtype) != t->gl || is_gl(v2->dtype) != t->gl)
+        return fail(DPB_EINVAL, "transcript and tables are of different fields");
+    return guarded([&] {
+        return t->gl ? hadamard_impl<GlFam>(ctx, v1, v2, claim_point, n, *t->g, out_round_evals, out_point, out_claims)
+                     : hadamard_impl<FrFam>(ctx, v1, v2, claim_point, n, *t->f, out_round_evals, out_point, out_claims);
+    });
+}
+
+int dpb_same_poly_prove(dpb_ctx* ctx, dpb_mle* poly, const void* points, uint32_t n_claims, uint32_t n,
+                        dpb_transcript* t, void* out_round_evals, void* out_point, void* out_eval) {
+    if (!ctx || !poly || !points || !t || !out_round_evals || !out_point || !out_eval)
+        return fail(DPB_EINVAL, "null argument");
+    if (is_gl(poly->dtype) != t->gl) return fail(DPB_EINVAL, "transcript and table are of different fields");
+    return guarded([&] {
+        return t->gl ? same_poly_impl<GlFam>(ctx, poly, points, n_claims, n, *t->g, out_round_evals, out_point, out_eval)
+                     : same_poly_impl<FrFam>(ctx, poly, points, n_claims, n, *t->f, out_round_evals, out_point, out_eval);
+    });
+}
+
+int dpb_logup_batch_prove(dpb_ctx* ctx, const dpb_logup_input* inputs, uint32_t n_inputs, dpb_transcript* t,
+                          dpb_logup_proof** out) {
+    if (!ctx || !t || !out || (!inputs && n_inputs)) return fail(DPB_EINVAL, "null argument");
+    if (n_inputs == 0) return fail(DPB_EINVAL, "No inputs provided for LogUp");
+    return guarded([&] {
+        return t->gl ? logup_impl<GlFam>(ctx, inputs, n_inputs, *t->g, out)
+                     : logup_impl<FrFam>(ctx, inputs, n_inputs, *t->f, out);
+    });
+}
+
+int dpb_logup_proof_serialize(const dpb_logup_proof* p, void* buf, size_t cap, size_t* len) {
+    if (!p || !len || (!buf && cap)) return fail(DPB_EINVAL, "null argument");
+    *len = p->bytes.size();
+    if (cap >= p->bytes.size()) memcpy(buf, p->bytes.data(), p->bytes.size());
+    return DPB_OK;
+}
+
+void dpb_logup_proof_free(dpb_logup_proof* p) { delete p; }
+
+}  // extern "C"

@@ -98,6 +98,7 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
     E r = F::zero();
     if (i > 0) memcpy(&r, prev_challenge, sizeof(E));
 
+    if (ctx->profile) DPB_CUDA(cudaEventRecord(ctx->prof_ev[0], ctx->stream));
     bool done = false;
     if (sc->fused_shape != 0) {
         int rc = fused_round<F>(sc->fused_shape, ctx, sc->h_desc.data() + (size_t)i * sc->k,
@@ -121,8 +122,47 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
         }
     }
     DPB_CUDA(cudaGetLastError());
+    if (ctx->profile) DPB_CUDA(cudaEventRecord(ctx->prof_ev[1], ctx->stream));
     DPB_CUDA(cudaStreamSynchronize(ctx->stream));
     memcpy(out_evals, ctx->result_host, (sc->d + 1) * sizeof(E));
+    if (ctx->profile) {
+        float ms = 0.f;
+        DPB_CUDA(cudaEventElapsedTime(&ms, ctx->prof_ev[0], ctx->prof_ev[1]));
+        // minimum traffic of this round: every table read once, folded tables written once
+        uint64_t bytes = 0;
+        const char* name;
+        if (i == 0) {
+            for (uint32_t j = 0; j < sc->k; j++) bytes += dtype_size(sc->tr[j].dtype) << sc->tr[j].nv;
+            name = done ? (sc->tr[0].dtype == DPB_GL_BASE ? "fused_product_eval0<base>" : "fused_product_eval0") : "sc_eval_generic";
+        } else {
+            const FoldDesc* fd = sc->h_fold.data() + (size_t)i * sc->k;
+            for (uint32_t j = 0; j < sc->n_fold[i]; j++)
+                bytes += fd[j].n_out * (2 * dtype_size(fd[j].dtype_in) + sizeof(E));
+            for (uint32_t j = 0; j < sc->k; j++)
+                if (sc->h_desc[(size_t)i * sc->k + j].shift >= 0) bytes += dtype_size(sc->tr[j].dtype) << sc->tr[j].nv;
+            name = done ? (fd[0].dtype_in == DPB_GL_BASE ? "fused_product_fold_eval<base>" : "fused_product_fold_eval")
+                        : "sc_fold_generic+sc_eval_generic";
+        }
+        bool found = false;
+        for (auto& e : ctx->prof_log) {
+            if (e.round == i && e.alg_bytes_per_launch == bytes && strcmp(e.kernel, name) == 0) {
+                e.launches++;
+                e.total_ms += ms;
+                found = true;
+                break;
+            }
+        }
+        if (!found) {
+            dpb_profile_entry e;
+            memset(&e, 0, sizeof e);
+            strncpy(e.kernel, name, sizeof(e.kernel) - 1);
+            e.round = i;
+            e.launches = 1;
+            e.total_ms = ms;
+            e.alg_bytes_per_launch = bytes;
+            ctx->prof_log.push_back(e);
+        }
+    }
     return DPB_OK;
 }
 

@@ -62,6 +62,10 @@ struct dpb_ctx {
     // small device staging area for points / challenges
     void* stage_dev = nullptr;
     size_t stage_bytes = 0;
+    // optional per-kernel timing log (dpb_profile_enable)
+    bool profile = false;
+    cudaEvent_t prof_ev[2] = {nullptr, nullptr};
+    std::vector<dpb_profile_entry> prof_log;
 };
 
 struct dpb_mle {

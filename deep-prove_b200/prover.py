@@ -1,0 +1,262 @@
+"""Python face of the host-side prover layer (include/dpb_prover.h), with the
+names the reference's callers use: Blake3Transcript, Expression,
+IOPProverState.prove, hadamard / same_poly provers, LogUpInput and
+new_batch_multiple_sizes_prove.  Everything here forwards to libdpb.so; the
+transcript and the expression algebra run in its C++ host code, the rounds on
+the GPU.
+"""
+import ctypes
+
+import numpy as np
+
+from . import (FR, GL_EXT, LOGUP_LOOKUP, LOGUP_TABLE, Term, _buf, _int, _pp, _u32, _vp, chal_dtype, check,
+               elem_words, lib)
+
+
+class ExprNode(ctypes.Structure):
+    _fields_ = [("op", ctypes.c_uint32), ("a", ctypes.c_uint32), ("b", ctypes.c_uint32), ("pad", ctypes.c_uint32),
+                ("c0", ctypes.c_uint8 * 32), ("c1", ctypes.c_uint8 * 32)]
+
+
+class LogupInputStruct(ctypes.Structure):
+    _fields_ = [("kind", ctypes.c_int), ("columns", _pp), ("n_columns", ctypes.c_uint32),
+                ("columns_per_instance", ctypes.c_uint32), ("multiplicities", ctypes.c_void_p),
+                ("constant_challenge", ctypes.c_void_p), ("column_separation_challenge", ctypes.c_void_p)]
+
+
+_size_t = ctypes.c_size_t
+PROVER_SIGNATURES = {
+    "dpb_transcript_new": (_int, [_int, _vp, _size_t, _pp]),
+    "dpb_transcript_clone": (_int, [_vp, _pp]),
+    "dpb_transcript_free": (None, [_vp]),
+    "dpb_transcript_append_scalars": (_int, [_vp, _vp, _u32]),
+    "dpb_transcript_append_and_sample": (_int, [_vp, _vp, _size_t, _vp]),
+    "dpb_transcript_challenge_scalar": (_int, [_vp, _vp]),
+    "dpb_transcript_state": (_int, [_vp, _vp, ctypes.POINTER(_u32)]),
+    "dpb_expr_to_terms": (_int, [_int, ctypes.POINTER(ExprNode), _u32, _vp, _u32, ctypes.POINTER(Term), _u32,
+                                 ctypes.POINTER(_u32)]),
+    "dpb_expr_eval": (_int, [_int, ctypes.POINTER(ExprNode), _u32, _vp, _u32, _vp, _u32, _vp]),
+    "dpb_prove_sumcheck": (_int, [_vp, _u32, _pp, _u32, ctypes.POINTER(Term), _u32, _vp, _vp, _u32, _vp, _vp,
+                                  ctypes.POINTER(_u32)]),
+    "dpb_hadamard_prove": (_int, [_vp, _vp, _vp, _vp, _u32, _vp, _vp, _vp, _vp]),
+    "dpb_same_poly_prove": (_int, [_vp, _vp, _vp, _u32, _u32, _vp, _vp, _vp, _vp]),
+    "dpb_logup_batch_prove": (_int, [_vp, ctypes.POINTER(LogupInputStruct), _u32, _vp, _pp]),
+    "dpb_logup_proof_serialize": (_int, [_vp, _vp, _size_t, ctypes.POINTER(_size_t)]),
+    "dpb_logup_proof_free": (None, [_vp]),
+}
+for _name, (_res, _args) in PROVER_SIGNATURES.items():
+    _fn = getattr(lib, _name)
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+def _scalars(a):
+    return np.ascontiguousarray(a, dtype=np.uint64)
+
+
+class Blake3Transcript:
+    """Blake3Transcript::new(label); challenges are uint64 arrays in the
+    library's challenge-element layout of `family_dtype` (GL_EXT or FR)."""
+
+    def __init__(self, family_dtype, label=b"m2vec", _h=None):
+        self.family = chal_dtype(family_dtype)
+        self.words = elem_words(self.family)
+        if _h is None:
+            _h = ctypes.c_void_p()
+            check(lib.dpb_transcript_new(self.family, label, len(label), ctypes.byref(_h)))
+        self.h = _h
+
+    def clone(self):
+        h = ctypes.c_void_p()
+        check(lib.dpb_transcript_clone(self.h, ctypes.byref(h)))
+        return Blake3Transcript(self.family, _h=h)
+
+    def append_scalars(self, scalars):
+        s = _scalars(scalars).reshape(-1, self.words)
+        check(lib.dpb_transcript_append_scalars(self.h, _buf(s) if s.size else None, s.shape[0]))
+
+    def append_and_sample(self, label):
+        out = np.zeros(self.words, dtype=np.uint64)
+        check(lib.dpb_transcript_append_and_sample(self.h, label, len(label), _buf(out)))
+        return out
+
+    def challenge_scalar(self):
+        out = np.zeros(self.words, dtype=np.uint64)
+        check(lib.dpb_transcript_challenge_scalar(self.h, _buf(out)))
+        return out
+
+    def state(self):
+        st = (ctypes.c_uint8 * 32)()
+        rnd = ctypes.c_uint32()
+        check(lib.dpb_transcript_state(self.h, st, ctypes.byref(rnd)))
+        return bytes(st), rnd.value
+
+    def free(self):
+        if self.h:
+            lib.dpb_transcript_free(self.h)
+            self.h = None
+
+
+class Expression:
+    """dp_crypto::Expression: WitIn / Constant / Challenge closed under + - *
+    and negation, kept as a postfix program for the C ABI.  Constants and
+    challenge scalars are native challenge-element bytes."""
+    WITIN, CONSTANT, CHALLENGE, ADD, SUB, MUL, NEG = range(7)
+
+    def __init__(self, nodes):
+        self.nodes = nodes
+
+    @staticmethod
+    def WitIn(i):
+        return Expression([(Expression.WITIN, i, 0, b"", b"")])
+
+    @staticmethod
+    def Constant(c):
+        return Expression([(Expression.CONSTANT, 0, 0, bytes(c), b"")])
+
+    @staticmethod
+    def Challenge(i, power, scalar, offset):
+        return Expression([(Expression.CHALLENGE, i, power, bytes(scalar), bytes(offset))])
+
+    def _bin(self, o, op):
+        return Expression(self.nodes + o.nodes + [(op, 0, 0, b"", b"")])
+
+    def __add__(self, o): return self._bin(o, Expression.ADD)
+    def __sub__(self, o): return self._bin(o, Expression.SUB)
+    def __mul__(self, o): return self._bin(o, Expression.MUL)
+    def __neg__(self): return Expression(self.nodes + [(Expression.NEG, 0, 0, b"", b"")])
+
+    def _array(self):
+        arr = (ExprNode * len(self.nodes))()
+        for i, (op, a, b, c0, c1) in enumerate(self.nodes):
+            arr[i].op, arr[i].a, arr[i].b = op, a, b
+            for j, v in enumerate(c0):
+                arr[i].c0[j] = v
+            for j, v in enumerate(c1):
+                arr[i].c1[j] = v
+        return arr
+
+    def to_terms(self, family_dtype, challenges):
+        """VirtualPolynomialsBuilder::to_virtual_polys: a ctypes array of Term."""
+        ch = _scalars(challenges)
+        n_ch = 0 if ch.size == 0 else ch.reshape(-1, elem_words(chal_dtype(family_dtype))).shape[0]
+        arr = self._array()
+        n = ctypes.c_uint32()
+        check(lib.dpb_expr_to_terms(family_dtype, arr, len(arr), _buf(ch) if n_ch else None, n_ch, None, 0,
+                                    ctypes.byref(n)))
+        out = (Term * max(n.value, 1))()
+        check(lib.dpb_expr_to_terms(family_dtype, arr, len(arr), _buf(ch) if n_ch else None, n_ch, out, n.value,
+                                    ctypes.byref(n)))
+        return (Term * n.value).from_buffer_copy(bytes(out)[:ctypes.sizeof(Term) * n.value]) if n.value else (Term * 0)()
+
+    def evaluate(self, family_dtype, wit_evals, challenges):
+        """eval_by_expr_with_instance"""
+        w = elem_words(chal_dtype(family_dtype))
+        we = _scalars(wit_evals).reshape(-1, w)
+        ch = _scalars(challenges).reshape(-1, w)
+        out = np.zeros(w, dtype=np.uint64)
+        arr = self._array()
+        check(lib.dpb_expr_eval(family_dtype, arr, len(arr), _buf(we) if we.size else None, we.shape[0],
+                                _buf(ch) if ch.size else None, ch.shape[0], _buf(out)))
+        return out
+
+
+class IOPProverState:
+    """Result of IOPProverState::prove: `proof` (round evaluations,
+    [num_vars, degree+1, words]), collect_raw_challenges(),
+    get_mle_flatten_final_evaluations()."""
+
+    def __init__(self, proof, point, finals):
+        self.proof, self._point, self._finals = proof, point, finals
+
+    @staticmethod
+    def prove(ctx, num_vars, mles, term_array, transcript):
+        k = len(mles)
+        w = elem_words(chal_dtype(mles[0].dtype))
+        d = max(t.n_factors for t in term_array)
+        hs = (ctypes.c_void_p * k)(*[m.h for m in mles])
+        evals = np.zeros((num_vars, d + 1, w), dtype=np.uint64)
+        point = np.zeros((num_vars, w), dtype=np.uint64)
+        finals = np.zeros((k, w), dtype=np.uint64)
+        deg = ctypes.c_uint32()
+        check(lib.dpb_prove_sumcheck(ctx.h, num_vars, hs, k, term_array, len(term_array), transcript.h, _buf(evals),
+                                     num_vars * (d + 1), _buf(point), _buf(finals), ctypes.byref(deg)))
+        return IOPProverState(evals, point, finals)
+
+    def collect_raw_challenges(self):
+        return self._point
+
+    def get_mle_flatten_final_evaluations(self):
+        return self._finals
+
+    def extract_sum(self):
+        raise NotImplementedError("add proof[0][0] and proof[0][1] in the field of your choice")
+
+
+def hadamard_prove(ctx, transcript, claim_point, v1, v2):
+    """zkml/src/layers/hadamard.rs:93-131 -> (round evals [n,4,w], point [n,w], claims [2,w])"""
+    p = _scalars(claim_point)
+    w = elem_words(chal_dtype(v1.dtype))
+    p = p.reshape(-1, w)
+    n = p.shape[0]
+    evals = np.zeros((n, 4, w), dtype=np.uint64)
+    point = np.zeros((n, w), dtype=np.uint64)
+    claims = np.zeros((2, w), dtype=np.uint64)
+    check(lib.dpb_hadamard_prove(ctx.h, v1.h, v2.h, _buf(p), n, transcript.h, _buf(evals), _buf(point), _buf(claims)))
+    return evals, point, claims
+
+
+def same_poly_prove(ctx, transcript, poly, points):
+    """zkml/src/iop/same_poly.rs:84-114; points: [n_claims, n, w]"""
+    w = elem_words(chal_dtype(poly.dtype))
+    p = _scalars(points).reshape(len(points), -1, w)
+    m, n = p.shape[0], p.shape[1]
+    evals = np.zeros((n, 3, w), dtype=np.uint64)
+    point = np.zeros((n, w), dtype=np.uint64)
+    ev = np.zeros(w, dtype=np.uint64)
+    check(lib.dpb_same_poly_prove(ctx.h, poly.h, _buf(p), m, n, transcript.h, _buf(evals), _buf(point), _buf(ev)))
+    return evals, point, ev
+
+
+class LogUpInput:
+    """zkml/src/lookup/logup_gkr/structs.rs:138-231"""
+
+    def __init__(self, kind, columns, constant, sep, columns_per_instance=1, multiplicities=None):
+        self.kind, self.columns, self.mult = kind, list(columns), multiplicities
+        self.constant, self.sep = _scalars(constant), _scalars(sep)
+        self.cpi = columns_per_instance
+
+    @staticmethod
+    def new_lookup(columns, constant, sep, columns_per_instance):
+        return LogUpInput(LOGUP_LOOKUP, columns, constant, sep, columns_per_instance)
+
+    @staticmethod
+    def new_table(columns, multiplicities, constant, sep):
+        return LogUpInput(LOGUP_TABLE, columns, constant, sep, len(columns), multiplicities)
+
+
+def new_batch_multiple_sizes_prove(ctx, inputs, transcript):
+    """zkml/src/lookup/logup_gkr/prover.rs:91-344.  Returns the flat canonical
+    encoding of the LogUpBatchProof (see include/dpb_prover.h)."""
+    arr = (LogupInputStruct * max(len(inputs), 1))()
+    keep = []
+    for i, inp in enumerate(inputs):
+        hs = (ctypes.c_void_p * len(inp.columns))(*[m.h for m in inp.columns])
+        keep.append(hs)
+        arr[i].kind = inp.kind
+        arr[i].columns = hs
+        arr[i].n_columns = len(inp.columns)
+        arr[i].columns_per_instance = inp.cpi
+        arr[i].multiplicities = inp.mult.h if inp.mult is not None else None
+        arr[i].constant_challenge = inp.constant.ctypes.data
+        arr[i].column_separation_challenge = inp.sep.ctypes.data
+    h = ctypes.c_void_p()
+    check(lib.dpb_logup_batch_prove(ctx.h, arr, len(inputs), transcript.h, ctypes.byref(h)))
+    try:
+        n = ctypes.c_size_t()
+        check(lib.dpb_logup_proof_serialize(h, None, 0, ctypes.byref(n)))
+        buf = (ctypes.c_uint8 * n.value)()
+        check(lib.dpb_logup_proof_serialize(h, buf, n.value, ctypes.byref(n)))
+        return bytes(buf)
+    finally:
+        lib.dpb_logup_proof_free(h)

@@ -83,6 +83,23 @@ int dpb_sync(dpb_ctx* ctx);
  * CUDA events or order their own copies against it. */
 void* dpb_stream(dpb_ctx* ctx);
 
+/* ---- per-kernel timing (no counterpart in the reference) ---------------- */
+/* When enabled, every sumcheck round brackets its kernel launches with CUDA
+ * events on the context's stream and adds the elapsed device time to a log
+ * keyed by (kernel, round).  alg_bytes_per_launch is the minimum traffic of
+ * that round: tables read once, folded tables written once. */
+typedef struct dpb_profile_entry {
+    char kernel[48];
+    uint32_t round;
+    uint32_t launches;
+    double total_ms;
+    uint64_t alg_bytes_per_launch;
+} dpb_profile_entry;
+/* on != 0 clears the log and starts recording; 0 stops. */
+int dpb_profile_enable(dpb_ctx* ctx, int on);
+/* Copies at most cap entries; *n is the number available. */
+int dpb_profile_read(dpb_ctx* ctx, dpb_profile_entry* out, uint32_t cap, uint32_t* n);
+
 /* ---- multilinear tables (dp_crypto::poly::dense::DensePolynomial) ------ */
 /* Uploads `len` (a power of two) evaluations from host memory.
  * Replaces DensePolynomial::new / new_from_smart_slice

@@ -1,0 +1,107 @@
+/*
+ * dpb_prover — whole-protocol entry points above include/dpb.h: the host-side
+ * transcript and the provers that drive the GPU rounds with it.  These are the
+ * calls a binding at the level of zkml's layer provers would use (one FFI call
+ * per sumcheck or per logup batch instead of one per round).
+ *
+ * Element layouts, status codes and threading rules are those of dpb.h.
+ * "challenge element" = DPB_GL_EXT (16 B) or DPB_FR (32 B, Montgomery).
+ */
+#ifndef DPB_PROVER_H
+#define DPB_PROVER_H
+
+#include "dpb.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- transcript (dp_crypto::arkyper::transcript::blake3::Blake3Transcript) ---- */
+typedef struct dpb_transcript dpb_transcript;
+/* Blake3Transcript::new(label) (zkml/src/lib.rs:106-108).  family_dtype picks
+ * the field the challenges are drawn from. */
+int dpb_transcript_new(int family_dtype, const void* label, size_t label_len, dpb_transcript** out);
+int dpb_transcript_clone(const dpb_transcript* t, dpb_transcript** out);
+void dpb_transcript_free(dpb_transcript* t);
+/* Transcript::append_scalars (zkml/src/lookup/logup_gkr/prover.rs:163-166) */
+int dpb_transcript_append_scalars(dpb_transcript* t, const void* scalars, uint32_t n);
+/* Transcript::append_and_sample (zkml/src/lookup/logup_gkr/prover.rs:171-173) */
+int dpb_transcript_append_and_sample(dpb_transcript* t, const void* label, size_t label_len, void* out);
+/* Transcript::challenge_scalar (zkml/src/lib.rs:176-184) */
+int dpb_transcript_challenge_scalar(dpb_transcript* t, void* out);
+/* 32-byte running state and the absorb counter, for comparing two transcripts. */
+int dpb_transcript_state(const dpb_transcript* t, uint8_t out_state[32], uint32_t* out_round);
+
+/* ---- expressions (dp_crypto::Expression) ---------------------------------- */
+/* An expression as a postfix program: leaves push, operators pop. */
+#define DPB_EXPR_WITIN 0     /* a = table id */
+#define DPB_EXPR_CONSTANT 1  /* c0 = value */
+#define DPB_EXPR_CHALLENGE 2 /* a = challenge id, b = power, c0 = scalar, c1 = offset */
+#define DPB_EXPR_ADD 3
+#define DPB_EXPR_SUB 4
+#define DPB_EXPR_MUL 5
+#define DPB_EXPR_NEG 6
+typedef struct dpb_expr_node {
+    uint32_t op;
+    uint32_t a;
+    uint32_t b;
+    uint32_t pad;
+    uint8_t c0[32];
+    uint8_t c1[32];
+} dpb_expr_node;
+/* VirtualPolynomialsBuilder::to_virtual_polys (zkml/src/layers/einsum/prove.rs:177-182):
+ * expands the expression under the challenge values into product terms.
+ * Writes at most `cap` terms; *n_out is the number needed. */
+int dpb_expr_to_terms(int family_dtype, const dpb_expr_node* nodes, uint32_t n_nodes,
+                      const void* challenges, uint32_t n_challenges, dpb_term* out, uint32_t cap,
+                      uint32_t* n_out);
+/* eval_by_expr_with_instance with witness values and challenges
+ * (zkml/src/lookup/logup_gkr/prover.rs:50-57). */
+int dpb_expr_eval(int family_dtype, const dpb_expr_node* nodes, uint32_t n_nodes, const void* wit_evals,
+                  uint32_t n_wit, const void* challenges, uint32_t n_challenges, void* out);
+
+/* ---- IOPProverState::prove -------------------------------------------------- */
+/* Runs all num_vars rounds (zkml/src/layers/hadamard.rs:115-130).  Outputs, all
+ * challenge elements: out_round_evals[num_vars * (degree+1)] (IOPProof),
+ * out_point[num_vars] (collect_raw_challenges), out_final_evals[k]
+ * (get_mle_flatten_final_evaluations).  *out_degree receives the degree. */
+int dpb_prove_sumcheck(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, uint32_t k,
+                       const dpb_term* terms, uint32_t n_terms, dpb_transcript* t, void* out_round_evals,
+                       uint32_t round_evals_cap, void* out_point, void* out_final_evals, uint32_t* out_degree);
+
+/* hadamard::prove (zkml/src/layers/hadamard.rs:93-131): sum_x v1 v2 eq(point, x).
+ * out_round_evals[n*4], out_point[n], out_claims[2] = (v1, v2) at the point. */
+int dpb_hadamard_prove(dpb_ctx* ctx, dpb_mle* v1, dpb_mle* v2, const void* claim_point, uint32_t n,
+                       dpb_transcript* t, void* out_round_evals, void* out_point, void* out_claims);
+
+/* same_poly::Prover::prove (zkml/src/iop/same_poly.rs:84-114): merges n_claims
+ * claims (points of n coordinates, row-major in `points`) on one table.
+ * out_round_evals[n*3], out_point[n], out_eval[1]. */
+int dpb_same_poly_prove(dpb_ctx* ctx, dpb_mle* poly, const void* points, uint32_t n_claims, uint32_t n,
+                        dpb_transcript* t, void* out_round_evals, void* out_point, void* out_eval);
+
+/* ---- batched logup-GKR ------------------------------------------------------- */
+/* LogUpInput (zkml/src/lookup/logup_gkr/structs.rs:138-154) */
+typedef struct dpb_logup_input {
+    int kind; /* DPB_LOGUP_LOOKUP or DPB_LOGUP_TABLE */
+    dpb_mle* const* columns;
+    uint32_t n_columns;
+    uint32_t columns_per_instance; /* lookups: columns per circuit */
+    dpb_mle* multiplicities;       /* tables only */
+    const void* constant_challenge;
+    const void* column_separation_challenge;
+} dpb_logup_input;
+typedef struct dpb_logup_proof dpb_logup_proof;
+/* new_batch_multiple_sizes_prove (zkml/src/lookup/logup_gkr/prover.rs:91-344) */
+int dpb_logup_batch_prove(dpb_ctx* ctx, const dpb_logup_input* inputs, uint32_t n_inputs, dpb_transcript* t,
+                          dpb_logup_proof** out);
+/* Flat encoding of LogUpBatchProof (field order of
+ * zkml/src/lookup/logup_gkr/structs.rs:561-578): u32 counts and canonical
+ * scalars.  Writes at most cap bytes; *len is the size needed. */
+int dpb_logup_proof_serialize(const dpb_logup_proof* p, void* buf, size_t cap, size_t* len);
+void dpb_logup_proof_free(dpb_logup_proof* p);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DPB_PROVER_H */
