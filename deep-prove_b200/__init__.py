@@ -81,6 +81,7 @@ SIGNATURES = {
     "dpb_logup_level": (_int, [_vp, _u32, _pp]),
     "dpb_logup_outputs": (_int, [_vp, _vp]),
     "dpb_logup_free": (None, [_vp]),
+    "dpb_product_round_noalloc": (_int, [_vp, _int, _pp, _u32, _u64, _vp]),
 }
 
 
@@ -218,6 +219,16 @@ class Context:
 
     def logup(self, kind, columns, constant, sep, mult=None):
         return Logup(self, kind, columns, constant, sep, mult)
+
+
+def product_round_noalloc(stream, dtype, table_ptrs, length, out_ptr):
+    """dpb_product_round_noalloc: first sumcheck round of a product of tables
+    for callers that may not allocate device memory.  `table_ptrs` and
+    `out_ptr` are device addresses the caller owns; the kernel is queued on
+    `stream` (a cudaStream_t value) and the caller synchronises."""
+    k = len(table_ptrs)
+    arr = (ctypes.c_void_p * k)(*table_ptrs)
+    check(lib.dpb_product_round_noalloc(ctypes.c_void_p(stream), dtype, arr, k, length, ctypes.c_void_p(out_ptr)))
 
 
 class Mle:

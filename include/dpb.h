@@ -162,6 +162,36 @@ int dpb_sumcheck_round(dpb_sc* sc, const void* prev_challenge, void* out_evals, 
 int dpb_sumcheck_finish(dpb_sc* sc, const void* last_challenge, void* out_final_evals);
 void dpb_sumcheck_free(dpb_sc* sc);
 
+/* First sumcheck round of a product of k tables without any allocation.
+ * (No counterpart in the reference: its prover is CPU code and never had to
+ * care who owns device memory.)
+ *
+ * Meant for callers that must not allocate on the device when they call in:
+ * code running inside a region an outer runtime records for later replay, a
+ * host that gave all device memory to its own pool, or a worker with a fixed
+ * device-memory budget.  It needs no dpb_ctx.  The caller passes k (2..4)
+ * device pointers to tables of `len` entries of layout `dtype`, all 16-byte
+ * aligned, and a device buffer for k+1 challenge elements; on return the
+ * kernel has been queued on `cuda_stream` (a cudaStream_t, on the current
+ * device) and will write there the round polynomial's evaluations at 0..=k,
+ * the same values dpb_sumcheck_begin + dpb_sumcheck_round return for the
+ * term  table_0 * ... * table_{k-1}.  The caller synchronises.
+ *
+ * Limits and rules:
+ *  - len is a power of two, 2 <= len <= 2^30; larger tables are rejected with
+ *    DPB_EINVAL, as are k outside 2..4 and unaligned pointers.
+ *  - The per-block partial sums live in a fixed scratch array inside the
+ *    library's device image, about 160 KiB on every GPU that loads the
+ *    library, kept until the process exits.  The first call on a device looks
+ *    up that array's device address; make that first call outside any stream
+ *    capture.
+ *  - All calls on a device share the scratch array.  Each call zeroes the part
+ *    that must start at zero, but two calls whose kernels can overlap on the
+ *    GPU (different streams, no ordering between them) race on it: order them.
+ *  - It calls no cudaMalloc / cudaFree and no allocating library routine. */
+int dpb_product_round_noalloc(void* cuda_stream, int dtype, const void* const* tables_dev, uint32_t k,
+                              uint64_t len, void* out_evals_dev);
+
 /* ---- logup-GKR fraction tree ------------------------------------------- */
 #define DPB_LOGUP_LOOKUP 0
 #define DPB_LOGUP_TABLE 1
