@@ -6,6 +6,7 @@
 // last block writes the round polynomial straight into mapped host memory.
 #include "common.cuh"
 #include "fused_kernels.cuh"
+#include "fused_v2.cuh"
 
 namespace dpb {
 
@@ -35,6 +36,7 @@ struct dpb_sc {
     void* d_terms = nullptr;
     void* d_final = nullptr;  // k challenge elements
     int fused_shape = 0;      // see fused_kernels.cuh
+    alignas(16) uint8_t prev_coeffs[5 * 32] = {0};  // previous round polynomial, low to high (fused rounds)
     std::vector<MleDesc> h_desc;
     std::vector<FoldDesc> h_fold;
 };
@@ -89,6 +91,64 @@ static void launch_eval(dpb_sc* sc, uint32_t round, uint64_t n_pairs) {
         reduce_scratch<F>(ctx), (typename F::E*)ctx->result_dev);
 }
 
+// Fused product rounds (fused_v2.cuh).  The kernels leave SAMPLES of the round
+// polynomial in the result buffer; run_round converts them.
+template <int K>
+static void launch_fused_gl(dpb_ctx* ctx, const MleDesc* desc, const FoldDesc* folds, uint32_t round, const Gl2& r,
+                            uint64_t n_pairs) {
+    V2Ptrs<K> ptrs;
+    const ReduceScratch<GlFam> rs = reduce_scratch<GlFam>(ctx);
+    Gl2* out = (Gl2*)ctx->result_dev;
+    const uint32_t grid = grid_for(ctx, n_pairs, 4);
+    if (round == 0) {
+        for (int j = 0; j < K; j++) {
+            ptrs.in[j] = desc[j].ptr;
+            ptrs.out[j] = nullptr;
+        }
+        if (desc[0].dtype == DPB_GL_BASE) v2_eval0<OpsGlBase, K><<<grid, kThreads, 0, ctx->stream>>>(ptrs, n_pairs, rs, out);
+        else v2_eval0<OpsGlExt, K><<<grid, kThreads, 0, ctx->stream>>>(ptrs, n_pairs, rs, out);
+        return;
+    }
+    for (int j = 0; j < K; j++) {  // folds[] lists the tables in registration order (all are active)
+        ptrs.in[j] = folds[j].in;
+        ptrs.out[j] = folds[j].out;
+    }
+    GlChal c;
+    c.r0 = r.c0;
+    c.r1 = r.c1;
+    c.r1x7 = gl_mul_small(r.c1, (uint32_t)GL_NONRES);
+    if (folds[0].dtype_in == DPB_GL_BASE) v2_fold_eval_gl<K, true><<<grid, kThreads, 0, ctx->stream>>>(ptrs, c, n_pairs, rs, out);
+    else v2_fold_eval_gl<K, false><<<grid, kThreads, 0, ctx->stream>>>(ptrs, c, n_pairs, rs, out);
+}
+
+template <int K>
+static void launch_fused_fr(dpb_ctx* ctx, const MleDesc* desc, const FoldDesc* folds, uint32_t round, const Fr& r,
+                            uint64_t n_pairs) {
+    V2Ptrs<K> ptrs;
+    const ReduceScratch<FrFam> rs = reduce_scratch<FrFam>(ctx);
+    Fr* out = (Fr*)ctx->result_dev;
+    const uint32_t grid = grid_for(ctx, n_pairs, 4);
+    for (int j = 0; j < K; j++) {
+        ptrs.in[j] = round == 0 ? desc[j].ptr : folds[j].in;
+        ptrs.out[j] = round == 0 ? nullptr : folds[j].out;
+    }
+    if (round == 0) v2_eval0<OpsFr, K><<<grid, kThreads, 0, ctx->stream>>>(ptrs, n_pairs, rs, out);
+    else v2_fold_eval_fr<K><<<grid, kThreads, 0, ctx->stream>>>(ptrs, r, n_pairs, rs, out);
+}
+
+static void launch_fused(dpb_ctx* ctx, const MleDesc* desc, const FoldDesc* folds, uint32_t k, uint32_t round,
+                         const Gl2& r, uint64_t n_pairs) {
+    if (k == 2) launch_fused_gl<2>(ctx, desc, folds, round, r, n_pairs);
+    else if (k == 3) launch_fused_gl<3>(ctx, desc, folds, round, r, n_pairs);
+    else launch_fused_gl<4>(ctx, desc, folds, round, r, n_pairs);
+}
+static void launch_fused(dpb_ctx* ctx, const MleDesc* desc, const FoldDesc* folds, uint32_t k, uint32_t round,
+                         const Fr& r, uint64_t n_pairs) {
+    if (k == 2) launch_fused_fr<2>(ctx, desc, folds, round, r, n_pairs);
+    else if (k == 3) launch_fused_fr<3>(ctx, desc, folds, round, r, n_pairs);
+    else launch_fused_fr<4>(ctx, desc, folds, round, r, n_pairs);
+}
+
 template <class F>
 static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
     typedef typename F::E E;
@@ -100,11 +160,10 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
 
     if (ctx->profile) DPB_CUDA(cudaEventRecord(ctx->prof_ev[0], ctx->stream));
     bool done = false;
-    if (sc->fused_shape != 0) {
-        int rc = fused_round<F>(sc->fused_shape, ctx, sc->h_desc.data() + (size_t)i * sc->k,
-                                i > 0 ? sc->h_fold.data() + (size_t)i * sc->k : nullptr, sc->k, i, r,
-                                n_pairs, &done);
-        if (rc != DPB_OK) return rc;
+    if (sc->fused_shape == kFusedProduct) {
+        launch_fused(ctx, sc->h_desc.data() + (size_t)i * sc->k, i > 0 ? sc->h_fold.data() + (size_t)i * sc->k : nullptr,
+                     sc->k, i, r, n_pairs);
+        done = true;
     }
     if (!done) {
         if (i > 0 && sc->n_fold[i] > 0) {
@@ -124,7 +183,15 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
     DPB_CUDA(cudaGetLastError());
     if (ctx->profile) DPB_CUDA(cudaEventRecord(ctx->prof_ev[1], ctx->stream));
     DPB_CUDA(cudaStreamSynchronize(ctx->stream));
-    memcpy(out_evals, ctx->result_host, (sc->d + 1) * sizeof(E));
+    if (done) {
+        // samples -> evaluations at 0..=d; P(1) of later rounds comes from the previous round's polynomial
+        E* coeffs = (E*)sc->prev_coeffs;
+        E claim = F::zero();
+        if (i > 0) claim = eval_coeffs<F>((int)sc->d, coeffs, r);
+        samples_to_evals<F>((int)sc->d, (const E*)ctx->result_host, i == 0, claim, (E*)out_evals, coeffs);
+    } else {
+        memcpy(out_evals, ctx->result_host, (sc->d + 1) * sizeof(E));
+    }
     if (ctx->profile) {
         float ms = 0.f;
         DPB_CUDA(cudaEventElapsedTime(&ms, ctx->prof_ev[0], ctx->prof_ev[1]));
@@ -133,14 +200,14 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
         const char* name;
         if (i == 0) {
             for (uint32_t j = 0; j < sc->k; j++) bytes += dtype_size(sc->tr[j].dtype) << sc->tr[j].nv;
-            name = done ? (sc->tr[0].dtype == DPB_GL_BASE ? "fused_product_eval0<base>" : "fused_product_eval0") : "sc_eval_generic";
+            name = done ? (sc->tr[0].dtype == DPB_GL_BASE ? "v2_eval0<base>" : "v2_eval0") : "sc_eval_generic";
         } else {
             const FoldDesc* fd = sc->h_fold.data() + (size_t)i * sc->k;
             for (uint32_t j = 0; j < sc->n_fold[i]; j++)
                 bytes += fd[j].n_out * (2 * dtype_size(fd[j].dtype_in) + sizeof(E));
             for (uint32_t j = 0; j < sc->k; j++)
                 if (sc->h_desc[(size_t)i * sc->k + j].shift >= 0) bytes += dtype_size(sc->tr[j].dtype) << sc->tr[j].nv;
-            name = done ? (fd[0].dtype_in == DPB_GL_BASE ? "fused_product_fold_eval<base>" : "fused_product_fold_eval")
+            name = done ? (fd[0].dtype_in == DPB_GL_BASE ? "v2_fold_eval<base>" : "v2_fold_eval")
                         : "sc_fold_generic+sc_eval_generic";
         }
         bool found = false;

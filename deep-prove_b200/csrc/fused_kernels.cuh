@@ -183,56 +183,4 @@ inline int detect_fused_shape(const MleDesc*, size_t k, uint32_t num_vars, const
     }
     return kFusedProduct;
 }
-
-template <class F, int K>
-static int fused_product_round(dpb_ctx* ctx, const MleDesc* desc, const FoldDesc* folds, uint32_t round,
-                               typename F::E r, uint64_t n_pairs) {
-    typedef typename F::E E;
-    FusedPtrs<K> ptrs;
-    const ReduceScratch<F> rs = reduce_scratch<F>(ctx);
-    E* out = (E*)ctx->result_dev;
-    const uint32_t grid = grid_for(ctx, n_pairs, 4);
-    if (round == 0) {
-        for (int j = 0; j < K; j++) {
-            ptrs.in[j] = desc[j].ptr;
-            ptrs.out[j] = nullptr;
-        }
-        if (desc[0].dtype == DPB_GL_BASE) {
-            if constexpr (std::is_same<F, GlFam>::value)
-                fused_product_eval0<F, K, true><<<grid, kThreads, 0, ctx->stream>>>(ptrs, n_pairs, rs, out);
-        } else {
-            fused_product_eval0<F, K, false><<<grid, kThreads, 0, ctx->stream>>>(ptrs, n_pairs, rs, out);
-        }
-    } else {
-        // folds[] lists the tables in registration order (all are active)
-        for (int j = 0; j < K; j++) {
-            ptrs.in[j] = folds[j].in;
-            ptrs.out[j] = folds[j].out;
-        }
-        if (folds[0].dtype_in == DPB_GL_BASE) {
-            if constexpr (std::is_same<F, GlFam>::value)
-                fused_product_fold_eval<F, K, true><<<grid, kThreads, 0, ctx->stream>>>(ptrs, r, n_pairs, rs, out);
-        } else {
-            fused_product_fold_eval<F, K, false><<<grid, kThreads, 0, ctx->stream>>>(ptrs, r, n_pairs, rs, out);
-        }
-    }
-    return DPB_OK;
-}
-
-template <class F>
-static int fused_round(int shape, dpb_ctx* ctx, const MleDesc* desc, const FoldDesc* folds, uint32_t k,
-                       uint32_t round, typename F::E r, uint64_t n_pairs, bool* done) {
-    *done = false;
-    if (shape != kFusedProduct) return DPB_OK;
-    int rc = DPB_OK;
-    switch (k) {
-        case 2: rc = fused_product_round<F, 2>(ctx, desc, folds, round, r, n_pairs); break;
-        case 3: rc = fused_product_round<F, 3>(ctx, desc, folds, round, r, n_pairs); break;
-        case 4: rc = fused_product_round<F, 4>(ctx, desc, folds, round, r, n_pairs); break;
-        default: return DPB_OK;
-    }
-    *done = (rc == DPB_OK);
-    return rc;
-}
-
 }  // namespace dpb
