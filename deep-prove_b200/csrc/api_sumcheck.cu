@@ -7,6 +7,7 @@
 #include "common.cuh"
 #include "fused_kernels.cuh"
 #include "fused_v2.cuh"
+#include "fused_v3.cuh"
 
 namespace dpb {
 
@@ -99,14 +100,33 @@ static void launch_fused_gl(dpb_ctx* ctx, const MleDesc* desc, const FoldDesc* f
     V2Ptrs<K> ptrs;
     const ReduceScratch<GlFam> rs = reduce_scratch<GlFam>(ctx);
     Gl2* out = (Gl2*)ctx->result_dev;
-    const uint32_t grid = grid_for(ctx, n_pairs, 4);
+    static const int per_sm = getenv("DPB_GRID_PER_SM") ? atoi(getenv("DPB_GRID_PER_SM")) : 4;
+    static const int minb = getenv("DPB_MINB") ? atoi(getenv("DPB_MINB")) : 1;
+    const uint32_t grid = grid_for(ctx, n_pairs, per_sm);
+    // staged kernels (fused_v3.cuh) once a launch has enough items per thread to pipeline
+    static const int use_v3 = getenv("DPB_V3") ? atoi(getenv("DPB_V3")) : 1;
+    const bool staged = use_v3 && n_pairs >= (uint64_t)grid * kStageThreads * 2;
     if (round == 0) {
         for (int j = 0; j < K; j++) {
             ptrs.in[j] = desc[j].ptr;
             ptrs.out[j] = nullptr;
         }
-        if (desc[0].dtype == DPB_GL_BASE) v2_eval0<OpsGlBase, K><<<grid, kThreads, 0, ctx->stream>>>(ptrs, n_pairs, rs, out);
-        else v2_eval0<OpsGlExt, K><<<grid, kThreads, 0, ctx->stream>>>(ptrs, n_pairs, rs, out);
+        const bool base = desc[0].dtype == DPB_GL_BASE;
+        if (staged) {
+            if (base) {
+                constexpr size_t sm = Stager<K, 1, 4>::bytes();
+                cudaFuncSetAttribute(v3_eval0_gl<K, true, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+                v3_eval0_gl<K, true, 4><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, n_pairs, rs, out);
+            } else {
+                constexpr size_t sm = Stager<K, 2, 3>::bytes();
+                cudaFuncSetAttribute(v3_eval0_gl<K, false, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+                v3_eval0_gl<K, false, 3><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, n_pairs, rs, out);
+            }
+        } else if (base) {
+            v2_eval0<OpsGlBase, K><<<grid, kThreads, 0, ctx->stream>>>(ptrs, n_pairs, rs, out);
+        } else {
+            v2_eval0<OpsGlExt, K><<<grid, kThreads, 0, ctx->stream>>>(ptrs, n_pairs, rs, out);
+        }
         return;
     }
     for (int j = 0; j < K; j++) {  // folds[] lists the tables in registration order (all are active)
@@ -117,8 +137,29 @@ static void launch_fused_gl(dpb_ctx* ctx, const MleDesc* desc, const FoldDesc* f
     c.r0 = r.c0;
     c.r1 = r.c1;
     c.r1x7 = gl_mul_small(r.c1, (uint32_t)GL_NONRES);
-    if (folds[0].dtype_in == DPB_GL_BASE) v2_fold_eval_gl<K, true><<<grid, kThreads, 0, ctx->stream>>>(ptrs, c, n_pairs, rs, out);
-    else v2_fold_eval_gl<K, false><<<grid, kThreads, 0, ctx->stream>>>(ptrs, c, n_pairs, rs, out);
+    const bool base = folds[0].dtype_in == DPB_GL_BASE;
+    if (staged) {
+        if (base) {
+            constexpr size_t sm = Stager<K, 2, 3>::bytes();
+            cudaFuncSetAttribute(v3_fold_eval_gl<K, true, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+            v3_fold_eval_gl<K, true, 3><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, c, n_pairs, rs, out);
+        } else {
+            constexpr size_t sm = Stager<K, 4, 2>::bytes();
+            cudaFuncSetAttribute(v3_fold_eval_gl<K, false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+            v3_fold_eval_gl<K, false, 2><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, c, n_pairs, rs, out);
+        }
+        return;
+    }
+#define DPB_LAUNCH_FOLD(MB)                                                                                  \
+    do {                                                                                                      \
+        if (base) v2_fold_eval_gl<K, true, MB><<<grid, kThreads, 0, ctx->stream>>>(ptrs, c, n_pairs, rs, out); \
+        else v2_fold_eval_gl<K, false, MB><<<grid, kThreads, 0, ctx->stream>>>(ptrs, c, n_pairs, rs, out);     \
+    } while (0)
+    if (minb == 2) DPB_LAUNCH_FOLD(2);
+    else if (minb == 3) DPB_LAUNCH_FOLD(3);
+    else if (minb == 4) DPB_LAUNCH_FOLD(4);
+    else DPB_LAUNCH_FOLD(1);
+#undef DPB_LAUNCH_FOLD
 }
 
 template <int K>

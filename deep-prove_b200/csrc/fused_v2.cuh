@@ -194,8 +194,8 @@ struct GlChal {
 
 // Rounds >= 1 over Goldilocks.  BASE_IN: the input tables hold base elements
 // (round 1); otherwise extension elements.  One thread per output pair.
-template <int K, bool BASE_IN>
-__global__ void __launch_bounds__(kThreads)
+template <int K, bool BASE_IN, int MINB>
+__global__ void __launch_bounds__(kThreads, MINB)
     v2_fold_eval_gl(V2Ptrs<K> ptrs, GlChal r, uint64_t n_pairs, ReduceScratch<GlFam> rs, Gl2* out) {
     typedef OpsGlExt Ops;
     typedef glf::L2 T;
