@@ -205,7 +205,13 @@ def run_ours(args):
     stream = torch.cuda.ExternalStream(ctx.stream, device=torch.device("cuda", local_rank))
 
     if world > 1:
-        raise SystemExit("multi-GPU sharding is wired in deep-prove_b200.sharded; see --gpus handling there")
+        # the library's own communicator; torch.distributed only carries the 128-byte id
+        box = [dpb.comm_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        ctx.comm_init(box[0], rank, world)
+    sharded = world > 1
+    log2_world = world.bit_length() - 1
+    n_global = n + log2_world  # weak scaling: every rank holds a 2^n shard of a 2^(n + log2 G) hypercube
 
     pinned, host = host_tables(field, n, args.seed + rank, pinned=True)
     mles = [ctx.upload(host[j], base_dtype) for j in range(3)]
@@ -213,14 +219,14 @@ def run_ours(args):
 
     def step_device():
         t = prover.Blake3Transcript(fam)
-        st = prover.IOPProverState.prove(ctx, n, mles, terms, t)
+        st = prover.IOPProverState.prove(ctx, n_global, mles, terms, t, sharded=sharded)
         t.free()
         return st
 
     def step_e2e():
         ms = [ctx.upload(host[j], base_dtype) for j in range(3)]
         t = prover.Blake3Transcript(fam)
-        st = prover.IOPProverState.prove(ctx, n, ms, terms, t)
+        st = prover.IOPProverState.prove(ctx, n_global, ms, terms, t, sharded=sharded)
         t.free()
         for m in ms:
             m.free()
@@ -253,7 +259,6 @@ def run_ours(args):
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         ms_total = float(tt.item())
     ms_step = ms_total / args.steps
-    n_global = n + (world.bit_length() - 1)
     value = alg_bytes(field, n_global) / (ms_step * 1e-3) / 1e9
     prof = ctx.profile_read()
 
@@ -268,8 +273,15 @@ def run_ours(args):
     e2e_s = (time.perf_counter() - t0) / args.steps
     words = 2 if field == "gl" else 4
     h2d = 3 * (1 << n) * (8 if field == "gl" else 32)
-    d2h = (n * 4 + n + 3) * words * 8
+    d2h = (n_global * 4 + n_global + 3) * words * 8
 
+    if world > 1:
+        tt = torch.tensor([e2e_s], device="cuda")
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        e2e_s = float(tt.item())
+        ctx.comm_free()
+        dist.barrier()
+        dist.destroy_process_group()
     if rank != 0:
         return
     peak, peak_src = load_peak()
@@ -299,7 +311,8 @@ def run_ours(args):
         "kernels": kernels,
         "e2e": {"value": alg_bytes(field, n_global) / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3},
-        "gpu_launches": args.steps * (n + 1) * world,
+        # per rank and step: n local rounds, the last local fold, 2 launches per tail round, the final evaluation
+        "gpu_launches": args.steps * (n + 2 + 2 * log2_world) * world,
         "clocks": clocks,
     }
     if world == 1 and not args.no_cpu_baseline:

@@ -82,7 +82,22 @@ SIGNATURES = {
     "dpb_logup_outputs": (_int, [_vp, _vp]),
     "dpb_logup_free": (None, [_vp]),
     "dpb_product_round_noalloc": (_int, [_vp, _int, _pp, _u32, _u64, _vp]),
+    "dpb_comm_unique_id": (_int, [_vp]),
+    "dpb_comm_init": (_int, [_vp, _vp, _int, _int]),
+    "dpb_comm_rank": (_int, [_vp]),
+    "dpb_comm_size": (_int, [_vp]),
+    "dpb_comm_free": (_int, [_vp]),
+    "dpb_sumcheck_begin_sharded": (_int, [_vp, _u32, _pp, _u32, ctypes.POINTER(Term), _u32, _pp]),
 }
+
+COMM_ID_BYTES = 128
+
+
+def comm_unique_id():
+    """dpb_comm_unique_id: 128 bytes to hand to every rank's Context.comm_init."""
+    buf = (ctypes.c_uint8 * COMM_ID_BYTES)()
+    check(lib.dpb_comm_unique_id(buf))
+    return bytes(buf)
 
 
 def _bind():
@@ -151,6 +166,14 @@ class Context:
     def stream(self):
         return lib.dpb_stream(self.h)
 
+    def comm_init(self, unique_id, rank, nranks):
+        """Joins the NCCL communicator of sharded sumchecks (collective over all ranks)."""
+        buf = (ctypes.c_uint8 * COMM_ID_BYTES).from_buffer_copy(unique_id)
+        check(lib.dpb_comm_init(self.h, buf, rank, nranks))
+
+    def comm_free(self):
+        check(lib.dpb_comm_free(self.h))
+
     def profile(self, on):
         check(lib.dpb_profile_enable(self.h, 1 if on else 0))
 
@@ -214,8 +237,8 @@ class Context:
         check(lib.dpb_mle_evaluate(self.h, mle.h, _buf(p) if n else None, n, _buf(out)))
         return out
 
-    def sumcheck(self, num_vars, mles, terms):
-        return Sumcheck(self, num_vars, mles, terms)
+    def sumcheck(self, num_vars, mles, terms, sharded=False):
+        return Sumcheck(self, num_vars, mles, terms, sharded)
 
     def logup(self, kind, columns, constant, sep, mult=None):
         return Logup(self, kind, columns, constant, sep, mult)
@@ -285,12 +308,13 @@ def make_terms(terms, coeff_bytes):
 class Sumcheck:
     """dpb_sumcheck_begin / round / finish."""
 
-    def __init__(self, ctx, num_vars, mles, term_array):
+    def __init__(self, ctx, num_vars, mles, term_array, sharded=False):
         self.ctx = ctx
         k = len(mles)
         hs = (ctypes.c_void_p * k)(*[m.h for m in mles])
         h = ctypes.c_void_p()
-        check(lib.dpb_sumcheck_begin(ctx.h, num_vars, hs, k, term_array, len(term_array), ctypes.byref(h)))
+        begin = lib.dpb_sumcheck_begin_sharded if sharded else lib.dpb_sumcheck_begin
+        check(begin(ctx.h, num_vars, hs, k, term_array, len(term_array), ctypes.byref(h)))
         self.h = h
         self.k = k
         self.num_vars = num_vars

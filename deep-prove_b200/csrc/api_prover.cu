@@ -91,7 +91,7 @@ int expr_to_terms_impl(const dpb_expr_node* nodes, uint32_t n_nodes, const void*
 template <class F, class T>
 int prove_sumcheck_impl(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, uint32_t k, const dpb_term* terms,
                         uint32_t n_terms, T& tr, void* out_round_evals, uint32_t cap, void* out_point,
-                        void* out_final, uint32_t* out_degree) {
+                        void* out_final, uint32_t* out_degree, bool sharded = false) {
     typedef typename F::E E;
     dp_crypto::VirtualPolynomials<F> vp;
     vp.num_vars = num_vars;
@@ -101,7 +101,7 @@ int prove_sumcheck_impl(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, u
     if ((uint64_t)num_vars * (vp.max_degree + 1) > cap)
         return fail(DPB_EINVAL, "round-evaluation buffer holds %u elements, %llu needed", cap,
                     (unsigned long long)num_vars * (vp.max_degree + 1));
-    auto res = dp_crypto::IOPProverState<F>::prove(ctx, vp, tr);
+    auto res = dp_crypto::IOPProverState<F>::prove(ctx, vp, tr, sharded);
     E* o = (E*)out_round_evals;
     for (const auto& m : res.first.proofs)
         for (const auto& v : m.evaluations) *o++ = v;
@@ -298,6 +298,21 @@ int dpb_prove_sumcheck(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, ui
                                                   round_evals_cap, out_point, out_final_evals, out_degree)
                      : prove_sumcheck_impl<FrFam>(ctx, num_vars, mles, k, terms, n_terms, *t->f, out_round_evals,
                                                   round_evals_cap, out_point, out_final_evals, out_degree);
+    });
+}
+
+int dpb_prove_sumcheck_sharded(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, uint32_t k,
+                               const dpb_term* terms, uint32_t n_terms, dpb_transcript* t, void* out_round_evals,
+                               uint32_t round_evals_cap, void* out_point, void* out_final_evals, uint32_t* out_degree) {
+    if (!ctx || !mles || !terms || !t || !out_round_evals || !out_point || !out_final_evals)
+        return fail(DPB_EINVAL, "null argument");
+    if (k == 0 || !mles[0]) return fail(DPB_EINVAL, "no tables");
+    if (is_gl(mles[0]->dtype) != t->gl) return fail(DPB_EINVAL, "transcript and tables are of different fields");
+    return guarded([&] {
+        return t->gl ? prove_sumcheck_impl<GlFam>(ctx, num_vars, mles, k, terms, n_terms, *t->g, out_round_evals,
+                                                  round_evals_cap, out_point, out_final_evals, out_degree, true)
+                     : prove_sumcheck_impl<FrFam>(ctx, num_vars, mles, k, terms, n_terms, *t->f, out_round_evals,
+                                                  round_evals_cap, out_point, out_final_evals, out_degree, true);
     });
 }
 

@@ -8,6 +8,7 @@
 #include "fused_kernels.cuh"
 #include "fused_v2.cuh"
 #include "fused_v3.cuh"
+#include "comm.cuh"
 
 namespace dpb {
 
@@ -38,6 +39,13 @@ struct dpb_sc {
     void* d_final = nullptr;  // k challenge elements
     int fused_shape = 0;      // see fused_kernels.cuh
     alignas(16) uint8_t prev_coeffs[5 * 32] = {0};  // previous round polynomial, low to high (fused rounds)
+    // sharded sumchecks: the local part has n variables, the whole sumcheck n + log2_ranks
+    uint32_t log2_ranks = 0;
+    uint32_t global_round = 0;
+    std::vector<dpb_term> terms_copy;
+    dpb_sc* tail = nullptr;             // the last log2_ranks rounds, identical on every rank
+    std::vector<dpb_mle*> tail_mles;
+    void* tail_dev = nullptr;
     std::vector<MleDesc> h_desc;
     std::vector<FoldDesc> h_fold;
 };
@@ -89,7 +97,7 @@ static void launch_eval(dpb_sc* sc, uint32_t round, uint64_t n_pairs) {
     dpb_ctx* ctx = sc->ctx;
     sc_eval_generic<F, D><<<grid_for(ctx, n_pairs, 4), kThreads, 0, ctx->stream>>>(
         sc->d_desc + (size_t)round * sc->k, (const TermDev<F>*)sc->d_terms, sc->n_terms, n_pairs,
-        reduce_scratch<F>(ctx), (typename F::E*)ctx->result_dev);
+        reduce_scratch<F>(ctx), (typename F::E*)ctx->round_out);
 }
 
 // Fused product rounds (fused_v2.cuh).  The kernels leave SAMPLES of the round
@@ -99,7 +107,7 @@ static void launch_fused_gl(dpb_ctx* ctx, const MleDesc* desc, const FoldDesc* f
                             uint64_t n_pairs) {
     V2Ptrs<K> ptrs;
     const ReduceScratch<GlFam> rs = reduce_scratch<GlFam>(ctx);
-    Gl2* out = (Gl2*)ctx->result_dev;
+    Gl2* out = (Gl2*)ctx->round_out;
     static const int per_sm = getenv("DPB_GRID_PER_SM") ? atoi(getenv("DPB_GRID_PER_SM")) : 4;
     static const int minb = getenv("DPB_MINB") ? atoi(getenv("DPB_MINB")) : 1;
     const uint32_t grid = grid_for(ctx, n_pairs, per_sm);
@@ -167,7 +175,7 @@ static void launch_fused_fr(dpb_ctx* ctx, const MleDesc* desc, const FoldDesc* f
                             uint64_t n_pairs) {
     V2Ptrs<K> ptrs;
     const ReduceScratch<FrFam> rs = reduce_scratch<FrFam>(ctx);
-    Fr* out = (Fr*)ctx->result_dev;
+    Fr* out = (Fr*)ctx->round_out;
     const uint32_t grid = grid_for(ctx, n_pairs, 4);
     for (int j = 0; j < K; j++) {
         ptrs.in[j] = round == 0 ? desc[j].ptr : folds[j].in;
@@ -199,6 +207,10 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
     E r = F::zero();
     if (i > 0) memcpy(&r, prev_challenge, sizeof(E));
 
+    // A sharded sumcheck publishes into this rank's slot of the exchange area (in-place all-gather).
+    const size_t msg_bytes = (sc->d + 1) * sizeof(E);
+    const bool sharded = sc->log2_ranks > 0;
+    ctx->round_out = sharded ? (void*)((char*)ctx->gather_dev + (size_t)ctx->rank * msg_bytes) : ctx->result_dev;
     if (ctx->profile) DPB_CUDA(cudaEventRecord(ctx->prof_ev[0], ctx->stream));
     bool done = false;
     if (sc->fused_shape == kFusedProduct) {
@@ -223,15 +235,28 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
     }
     DPB_CUDA(cudaGetLastError());
     if (ctx->profile) DPB_CUDA(cudaEventRecord(ctx->prof_ev[1], ctx->stream));
-    DPB_CUDA(cudaStreamSynchronize(ctx->stream));
+    E raw[kMaxAcc];
+    if (sharded) {
+        // every rank's partial sums -> all hosts; add them mod p (NCCL has no modular sum)
+        DPB_TRY(allgather_to_host(ctx, ctx->round_out, msg_bytes));
+        const E* g = (const E*)ctx->gather_host;
+        for (uint32_t x = 0; x <= sc->d; x++) {
+            E tot = g[x];
+            for (int q = 1; q < ctx->nranks; q++) tot = F::add(tot, g[(size_t)q * (sc->d + 1) + x]);
+            raw[x] = tot;
+        }
+    } else {
+        DPB_CUDA(cudaStreamSynchronize(ctx->stream));
+        memcpy(raw, ctx->result_host, msg_bytes);
+    }
     if (done) {
         // samples -> evaluations at 0..=d; P(1) of later rounds comes from the previous round's polynomial
         E* coeffs = (E*)sc->prev_coeffs;
         E claim = F::zero();
         if (i > 0) claim = eval_coeffs<F>((int)sc->d, coeffs, r);
-        samples_to_evals<F>((int)sc->d, (const E*)ctx->result_host, i == 0, claim, (E*)out_evals, coeffs);
+        samples_to_evals<F>((int)sc->d, raw, i == 0, claim, (E*)out_evals, coeffs);
     } else {
-        memcpy(out_evals, ctx->result_host, (sc->d + 1) * sizeof(E));
+        memcpy(out_evals, raw, msg_bytes);
     }
     if (ctx->profile) {
         float ms = 0.f;
@@ -286,6 +311,37 @@ static int run_finish(dpb_sc* sc, const void* last_challenge, void* out) {
     DPB_CUDA(cudaMemcpyAsync(out, sc->d_final, sc->k * sizeof(E), cudaMemcpyDeviceToHost, ctx->stream));
     DPB_CUDA(cudaStreamSynchronize(ctx->stream));
     return DPB_OK;
+}
+
+// Sharded sumcheck, first tail round: bind the last local variable, gather the
+// one-entry shards from every rank and start the (replicated) tail sumcheck.
+template <class F>
+static int start_tail(dpb_sc* sc, const void* prev_challenge) {
+    typedef typename F::E E;
+    dpb_ctx* ctx = sc->ctx;
+    const int G = ctx->nranks;
+    const size_t bytes = sc->k * sizeof(E);
+    E r;
+    memcpy(&r, prev_challenge, sizeof(E));
+    E* slot = (E*)((char*)ctx->gather_dev + (size_t)ctx->rank * bytes);
+    sc_final_evals<F><<<(sc->k + 127) / 128, 128, 0, ctx->stream>>>(sc->d_desc + (size_t)(sc->n - 1) * sc->k, sc->k, r, slot);
+    DPB_CUDA(cudaGetLastError());
+    DPB_TRY(allgather_to_host(ctx, slot, bytes));
+    // gathered[g][j] -> table j entry g (rank g owns the top-variable block g)
+    const E* g = (const E*)ctx->gather_host;
+    E* stage = (E*)ctx->result_host;
+    for (uint32_t j = 0; j < sc->k; j++)
+        for (int q = 0; q < G; q++) stage[(size_t)j * G + q] = g[(size_t)q * sc->k + j];
+    DPB_TRY(device_alloc(ctx, (size_t)sc->k * G * sizeof(E), &sc->tail_dev));
+    DPB_CUDA(cudaMemcpyAsync(sc->tail_dev, stage, (size_t)sc->k * G * sizeof(E), cudaMemcpyHostToDevice, ctx->stream));
+    DPB_CUDA(cudaStreamSynchronize(ctx->stream));
+    for (uint32_t j = 0; j < sc->k; j++) {
+        dpb_mle* m = nullptr;
+        DPB_TRY(dpb_mle_from_device(ctx, F::kChalDtype, (char*)sc->tail_dev + (size_t)j * G * sizeof(E), (uint64_t)G, &m));
+        sc->tail_mles.push_back(m);
+    }
+    return dpb_sumcheck_begin(ctx, sc->log2_ranks, sc->tail_mles.data(), sc->k, sc->terms_copy.data(),
+                              (uint32_t)sc->terms_copy.size(), &sc->tail);
 }
 
 }  // namespace dpb
@@ -413,25 +469,60 @@ int dpb_sumcheck_begin(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, ui
 
 uint32_t dpb_sumcheck_degree(const dpb_sc* sc) { return sc ? sc->d : 0; }
 
+int dpb_sumcheck_begin_sharded(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, uint32_t k,
+                               const dpb_term* terms, uint32_t n_terms, dpb_sc** out) {
+    if (!ctx || !mles || !terms || !out) return fail(DPB_EINVAL, "null argument");
+    uint32_t c = 0;
+    while ((1 << c) < ctx->nranks) c++;
+    if (c == 0) return dpb_sumcheck_begin(ctx, num_vars, mles, k, terms, n_terms, out);
+    if (!ctx->nccl_comm) return fail(DPB_ESTATE, "the context has no communicator (dpb_comm_init)");
+    if (num_vars <= c) return fail(DPB_EINVAL, "%u variables cannot be sharded over %d ranks", num_vars, ctx->nranks);
+    const uint32_t n_loc = num_vars - c;
+    for (uint32_t j = 0; j < k; j++)
+        if (!mles[j] || mles[j]->len != (1ull << n_loc))
+            return fail(DPB_EINVAL, "a sharded sumcheck needs every table to hold its 2^%u-entry shard (table %u)", n_loc, j);
+    if ((size_t)k * ctx->nranks * 32 > ctx->result_bytes || (size_t)k * ctx->nranks * 32 > ctx->gather_bytes)
+        return fail(DPB_EINVAL, "too many tables (%u) for the tail exchange", k);
+    dpb_sc* sc = nullptr;
+    DPB_TRY(dpb_sumcheck_begin(ctx, n_loc, mles, k, terms, n_terms, &sc));
+    sc->log2_ranks = c;
+    sc->terms_copy.assign(terms, terms + n_terms);
+    *out = sc;
+    return DPB_OK;
+}
+
 int dpb_sumcheck_round(dpb_sc* sc, const void* prev_challenge, void* out_evals, uint32_t* n_evals) {
     if (!sc || !out_evals) return fail(DPB_EINVAL, "null argument");
-    if (sc->finished || sc->round >= sc->n) return fail(DPB_ESTATE, "all %u rounds already ran", sc->n);
-    if (sc->round == 0 && prev_challenge) return fail(DPB_ESTATE, "the first round takes no challenge");
-    if (sc->round > 0 && !prev_challenge) return fail(DPB_ESTATE, "round %u needs the previous challenge", sc->round);
-    int rc = sc->gl ? run_round<GlFam>(sc, prev_challenge, out_evals)
-                    : run_round<FrFam>(sc, prev_challenge, out_evals);
+    const uint32_t total = sc->n + sc->log2_ranks;
+    if (sc->finished || sc->global_round >= total) return fail(DPB_ESTATE, "all %u rounds already ran", total);
+    if (sc->global_round == 0 && prev_challenge) return fail(DPB_ESTATE, "the first round takes no challenge");
+    if (sc->global_round > 0 && !prev_challenge)
+        return fail(DPB_ESTATE, "round %u needs the previous challenge", sc->global_round);
+    int rc;
+    if (sc->global_round < sc->n) {
+        rc = sc->gl ? run_round<GlFam>(sc, prev_challenge, out_evals) : run_round<FrFam>(sc, prev_challenge, out_evals);
+        if (rc == DPB_OK) sc->round++;
+    } else if (sc->global_round == sc->n) {
+        rc = sc->gl ? start_tail<GlFam>(sc, prev_challenge) : start_tail<FrFam>(sc, prev_challenge);
+        if (rc == DPB_OK) rc = dpb_sumcheck_round(sc->tail, nullptr, out_evals, nullptr);
+    } else {
+        rc = dpb_sumcheck_round(sc->tail, prev_challenge, out_evals, nullptr);
+    }
     if (rc != DPB_OK) return rc;
     if (n_evals) *n_evals = sc->d + 1;
-    sc->round++;
+    sc->global_round++;
     return DPB_OK;
 }
 
 int dpb_sumcheck_finish(dpb_sc* sc, const void* last_challenge, void* out_final_evals) {
     if (!sc || !last_challenge || !out_final_evals) return fail(DPB_EINVAL, "null argument");
     if (sc->finished) return fail(DPB_ESTATE, "already finished");
-    if (sc->round != sc->n) return fail(DPB_ESTATE, "only %u of %u rounds ran", sc->round, sc->n);
-    int rc = sc->gl ? run_finish<GlFam>(sc, last_challenge, out_final_evals)
-                    : run_finish<FrFam>(sc, last_challenge, out_final_evals);
+    const uint32_t total = sc->n + sc->log2_ranks;
+    if (sc->global_round != total) return fail(DPB_ESTATE, "only %u of %u rounds ran", sc->global_round, total);
+    int rc;
+    if (sc->log2_ranks > 0) rc = dpb_sumcheck_finish(sc->tail, last_challenge, out_final_evals);
+    else rc = sc->gl ? run_finish<GlFam>(sc, last_challenge, out_final_evals)
+                     : run_finish<FrFam>(sc, last_challenge, out_final_evals);
     if (rc != DPB_OK) return rc;
     sc->finished = true;
     return DPB_OK;
@@ -439,6 +530,9 @@ int dpb_sumcheck_finish(dpb_sc* sc, const void* last_challenge, void* out_final_
 
 void dpb_sumcheck_free(dpb_sc* sc) {
     if (!sc) return;
+    if (sc->tail) dpb_sumcheck_free(sc->tail);
+    for (auto* m : sc->tail_mles) dpb_mle_free(m);
+    device_free(sc->ctx, sc->tail_dev);
     device_free(sc->ctx, sc->slab);
     device_free(sc->ctx, sc->d_desc);
     device_free(sc->ctx, sc->d_fold);

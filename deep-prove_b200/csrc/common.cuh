@@ -59,9 +59,16 @@ struct dpb_ctx {
     void* result_host = nullptr;
     void* result_dev = nullptr;
     size_t result_bytes = 0;
+    void* round_out = nullptr;  // where the current round's kernel publishes (result_dev or the exchange area)
     // small device staging area for points / challenges
     void* stage_dev = nullptr;
     size_t stage_bytes = 0;
+    // communicator of sharded sumchecks (dpb_comm_init); nranks == 1 without one
+    void* nccl_comm = nullptr;
+    int rank = 0, nranks = 1;
+    void* gather_dev = nullptr;   // send area (first half) and all-gather result (second half is unused slack)
+    void* gather_host = nullptr;  // pinned copy of the all-gather result
+    size_t gather_bytes = 0;
     // optional per-kernel timing log (dpb_profile_enable)
     bool profile = false;
     cudaEvent_t prof_ev[2] = {nullptr, nullptr};

@@ -253,13 +253,14 @@ class IOPProverState {
     // Runs every round on the GPU behind `ctx`; the transcript is only touched here, on the host.
     template <class T>
     static std::pair<IOPProof<F>, IOPProverState> prove(dpb_ctx* ctx, const VirtualPolynomials<F>& vp,
-                                                        T& transcript) {
+                                                        T& transcript, bool sharded = false) {
         if (vp.terms.empty()) throw Error(DPB_EINVAL, "virtual polynomial has no terms");
         IOPProverState st;
         IOPProof<F> proof;
         dpb_sc* sc = nullptr;
-        check(dpb_sumcheck_begin(ctx, vp.num_vars, vp.mles.data(), (uint32_t)vp.mles.size(), vp.terms.data(),
-                                 (uint32_t)vp.terms.size(), &sc));
+        // sharded: the tables are this rank's slices and every rank runs this same loop
+        check((sharded ? dpb_sumcheck_begin_sharded : dpb_sumcheck_begin)(
+            ctx, vp.num_vars, vp.mles.data(), (uint32_t)vp.mles.size(), vp.terms.data(), (uint32_t)vp.terms.size(), &sc));
         struct Guard {
             dpb_sc* s;
             ~Guard() { dpb_sumcheck_free(s); }

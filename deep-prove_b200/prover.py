@@ -38,6 +38,8 @@ PROVER_SIGNATURES = {
     "dpb_expr_eval": (_int, [_int, ctypes.POINTER(ExprNode), _u32, _vp, _u32, _vp, _u32, _vp]),
     "dpb_prove_sumcheck": (_int, [_vp, _u32, _pp, _u32, ctypes.POINTER(Term), _u32, _vp, _vp, _u32, _vp, _vp,
                                   ctypes.POINTER(_u32)]),
+    "dpb_prove_sumcheck_sharded": (_int, [_vp, _u32, _pp, _u32, ctypes.POINTER(Term), _u32, _vp, _vp, _u32, _vp, _vp,
+                                          ctypes.POINTER(_u32)]),
     "dpb_hadamard_prove": (_int, [_vp, _vp, _vp, _vp, _u32, _vp, _vp, _vp, _vp]),
     "dpb_same_poly_prove": (_int, [_vp, _vp, _vp, _u32, _u32, _vp, _vp, _vp, _vp]),
     "dpb_logup_batch_prove": (_int, [_vp, ctypes.POINTER(LogupInputStruct), _u32, _vp, _pp]),
@@ -170,7 +172,9 @@ class IOPProverState:
         self.proof, self._point, self._finals = proof, point, finals
 
     @staticmethod
-    def prove(ctx, num_vars, mles, term_array, transcript):
+    def prove(ctx, num_vars, mles, term_array, transcript, sharded=False):
+        """sharded=True: `mles` are this rank's shards, num_vars counts all
+        variables, and every rank of the context's communicator makes this call."""
         k = len(mles)
         w = elem_words(chal_dtype(mles[0].dtype))
         d = max(t.n_factors for t in term_array)
@@ -179,7 +183,8 @@ class IOPProverState:
         point = np.zeros((num_vars, w), dtype=np.uint64)
         finals = np.zeros((k, w), dtype=np.uint64)
         deg = ctypes.c_uint32()
-        check(lib.dpb_prove_sumcheck(ctx.h, num_vars, hs, k, term_array, len(term_array), transcript.h, _buf(evals),
+        fn = lib.dpb_prove_sumcheck_sharded if sharded else lib.dpb_prove_sumcheck
+        check(fn(ctx.h, num_vars, hs, k, term_array, len(term_array), transcript.h, _buf(evals),
                                      num_vars * (d + 1), _buf(point), _buf(finals), ctypes.byref(deg)))
         return IOPProverState(evals, point, finals)
 

@@ -83,6 +83,23 @@ int dpb_sync(dpb_ctx* ctx);
  * CUDA events or order their own copies against it. */
 void* dpb_stream(dpb_ctx* ctx);
 
+/* ---- multi-GPU (no counterpart in the reference, which has no collective) -- */
+/* One process per GPU.  A sumcheck over n variables is sharded on its top
+ * log2(G) variables: rank g holds entries [g*2^(n-c), (g+1)*2^(n-c)) of every
+ * table, c = log2 G.  Rounds 0..n-c-1 fold locally; each rank's partial round
+ * evaluations travel through one small NCCL all-gather and are added mod p on
+ * every host, so all ranks drive identical transcripts.  When c variables are
+ * left the one-entry shards are gathered and every rank finishes the same tail.
+ * Waits on collectives are bounded (DPB_ETIMEOUT). */
+#define DPB_COMM_ID_BYTES 128
+/* ncclGetUniqueId; call on one rank and distribute the bytes to the others. */
+int dpb_comm_unique_id(void* out_id);
+/* ncclCommInitRank on the context's device; collective over all ranks.  nranks a power of two. */
+int dpb_comm_init(dpb_ctx* ctx, const void* id, int rank, int nranks);
+int dpb_comm_rank(const dpb_ctx* ctx);
+int dpb_comm_size(const dpb_ctx* ctx);
+int dpb_comm_free(dpb_ctx* ctx);
+
 /* ---- per-kernel timing (no counterpart in the reference) ---------------- */
 /* When enabled, every sumcheck round brackets its kernel launches with CUDA
  * events on the context's stream and adds the elapsed device time to a log
@@ -149,6 +166,14 @@ int dpb_mle_evaluate(dpb_ctx* ctx, const dpb_mle* mle, const void* point, uint32
  * zkml/src/layers/hadamard.rs:115, zkml/src/iop/same_poly.rs:105. */
 int dpb_sumcheck_begin(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, uint32_t k,
                        const dpb_term* terms, uint32_t n_terms, dpb_sc** out);
+/* The same over a communicator (dpb_comm_init): num_vars counts ALL variables,
+ * every table handle holds this rank's shard of 2^(num_vars - log2 G) entries
+ * (the slice selected by the top log2 G index bits = the rank).  Every rank must
+ * make the same sequence of calls with the same challenges; rounds and finish
+ * return identical values on all ranks.  Without a communicator this is
+ * dpb_sumcheck_begin. */
+int dpb_sumcheck_begin_sharded(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, uint32_t k,
+                               const dpb_term* terms, uint32_t n_terms, dpb_sc** out);
 /* Degree of the round polynomial (max factors per term). */
 uint32_t dpb_sumcheck_degree(const dpb_sc* sc);
 /* One prover round.  `prev_challenge` is NULL on the first round, otherwise the

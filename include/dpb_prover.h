@@ -69,6 +69,14 @@ int dpb_prove_sumcheck(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, ui
                        const dpb_term* terms, uint32_t n_terms, dpb_transcript* t, void* out_round_evals,
                        uint32_t round_evals_cap, void* out_point, void* out_final_evals, uint32_t* out_degree);
 
+/* The same over the context's communicator: tables are this rank's shards (see
+ * dpb_sumcheck_begin_sharded), num_vars counts all variables, every rank passes a
+ * transcript in the same state and all ranks return the same proof. */
+int dpb_prove_sumcheck_sharded(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, uint32_t k,
+                               const dpb_term* terms, uint32_t n_terms, dpb_transcript* t, void* out_round_evals,
+                               uint32_t round_evals_cap, void* out_point, void* out_final_evals,
+                               uint32_t* out_degree);
+
 /* hadamard::prove (zkml/src/layers/hadamard.rs:93-131): sum_x v1 v2 eq(point, x).
  * out_round_evals[n*4], out_point[n], out_claims[2] = (v1, v2) at the point. */
 int dpb_hadamard_prove(dpb_ctx* ctx, dpb_mle* v1, dpb_mle* v2, const void* claim_point, uint32_t n,

@@ -1,0 +1,75 @@
+"""Multi-rank sumcheck: the hypercube is sharded on its top log2(G) variables,
+each rank folds its shard locally and contributes its partial round
+evaluations through an all-gather; all ranks must produce the proof a single
+process produces for the whole tables."""
+import json
+import os
+import socket
+import subprocess
+import sys
+import tempfile
+
+import pytest
+
+from oracle import oracle as orc
+from tests import sharded_worker as W
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def launch(mode, field, n, seed, world):
+    tmp = tempfile.mkdtemp()
+    out = os.path.join(tmp, "res")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(free_port()), OMP_NUM_THREADS="2",
+               NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "sharded_worker.py"), mode, field, str(n),
+                               str(seed), str(r), str(world), out], env=env, cwd=ROOT,
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT) for r in range(world)]
+    logs = []
+    for p in procs:
+        try:
+            o, _ = p.communicate(timeout=300)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            o, _ = p.communicate()
+        logs.append(o.decode(errors="replace"))
+    for r, p in enumerate(procs):
+        assert p.returncode == 0, f"rank {r} failed:\n{logs[r][-3000:]}"
+    return [json.load(open(f"{out}.{r}.json")) for r in range(world)]
+
+
+def oracle_proof(F, n, seed):
+    tabs = W.full_tables(F, n, seed)
+    proof, point, finals = orc.sumcheck_prove(F, n, tabs, {(0, 1, 2): F.one}, orc.Transcript(F))
+    hx = lambda v: orc.serialize_scalars(F, v).hex()
+    return dict(proof=orc.serialize_sumcheck_proof(F, proof).hex(), point=hx(point), finals=hx(finals))
+
+
+@pytest.mark.parametrize("field", ["gl", "fr"])
+@pytest.mark.parametrize("world,n", [(2, 7), (4, 6)])
+def test_sharding_protocol_on_cpu_gloo(field, world, n):
+    """world_size > 1 on CPU: gloo ranks run the sharding protocol with the oracle."""
+    want = oracle_proof(orc.FIELDS[field], n, 11)
+    for got in launch("cpu", field, n, 11, world):
+        assert got == want
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("field", ["gl", "fr"])
+@pytest.mark.parametrize("n", [4, 14])
+def test_sharded_sumcheck_on_gpus(field, n):
+    """The library's sharded path over NCCL on as many GPUs as the box has (2, 4 or 8)."""
+    import torch
+    g = torch.cuda.device_count()
+    world = 8 if g >= 8 else 4 if g >= 4 else 2 if g >= 2 else 0
+    if world == 0:
+        pytest.skip("needs at least 2 GPUs")
+    want = oracle_proof(orc.FIELDS[field], n, 12)
+    for got in launch("gpu", field, n, 12, world):
+        assert got == want
