@@ -18,6 +18,7 @@ LIB_PATH = os.path.join(HERE, "libdpb.so")
 GL_BASE, GL_EXT, FR = 0, 1, 2
 FORM_NATIVE, FORM_CANONICAL, FORM_I64 = 0, 1, 2
 LOGUP_LOOKUP, LOGUP_TABLE = 0, 1
+AXIS_CONTRACTED, AXIS_OUTER, AXIS_STACKED = 0, 1, 2
 MAX_FACTORS = 8
 
 OK, EINVAL, ENOMEM, ECUDA, ETIMEOUT, ESTATE, ENCCL = 0, -1, -2, -3, -4, -5, -6
@@ -82,6 +83,7 @@ SIGNATURES = {
     "dpb_logup_outputs": (_int, [_vp, _vp]),
     "dpb_logup_free": (None, [_vp]),
     "dpb_product_round_noalloc": (_int, [_vp, _int, _pp, _u32, _u64, _vp]),
+    "dpb_einsum_fix_axes": (_int, [_vp, _int, _vp, _int, _vp, _vp, _pp, _vp, _u32, _pp, _pp, _u32, ctypes.POINTER(_u32)]),
     "dpb_comm_unique_id": (_int, [_vp]),
     "dpb_comm_init": (_int, [_vp, _vp, _int, _int]),
     "dpb_comm_rank": (_int, [_vp]),
@@ -236,6 +238,28 @@ class Context:
         out = np.zeros(elem_words(chal_dtype(mle.dtype)), dtype=np.uint64)
         check(lib.dpb_mle_evaluate(self.h, mle.h, _buf(p) if n else None, n, _buf(out)))
         return out
+
+    def einsum_fix_axes(self, family_dtype, tensor, kinds, points):
+        """dpb_einsum_fix_axes.  tensor: int64 ndarray (unpadded); kinds[a] in
+        AXIS_*; points[a]: challenge elements uint64[len, words] for outer axes,
+        None otherwise.  Returns (owner, [views])."""
+        t = np.ascontiguousarray(tensor, dtype=np.int64)
+        rank = t.ndim
+        shape = (ctypes.c_uint64 * rank)(*t.shape)
+        kd = (ctypes.c_uint8 * rank)(*kinds)
+        keep = [np.ascontiguousarray(p, dtype=np.uint64) if p is not None else None for p in points]
+        pts = (ctypes.c_void_p * rank)(*[k.ctypes.data if k is not None and k.size else None for k in keep])
+        lens = (ctypes.c_uint32 * rank)(*[0 if k is None else (k.shape[0] if k.size else 0) for k in keep])
+        cap = 1
+        for a in range(rank):
+            if kinds[a] == AXIS_STACKED:
+                cap *= t.shape[a]
+        views = (ctypes.c_void_p * cap)()
+        owner = ctypes.c_void_p()
+        n = ctypes.c_uint32()
+        check(lib.dpb_einsum_fix_axes(self.h, family_dtype, _buf(t), 0, shape, kd, pts, lens, rank, ctypes.byref(owner),
+                                      views, cap, ctypes.byref(n)))
+        return Mle(self, owner), [Mle(self, ctypes.c_void_p(views[i])) for i in range(n.value)]
 
     def sumcheck(self, num_vars, mles, terms, sharded=False):
         return Sumcheck(self, num_vars, mles, terms, sharded)

@@ -1,0 +1,132 @@
+"""Times the other pieces of the path on one GPU (the sumcheck itself is
+bench.py's job): eq tables, fix_high / fix_low, the logup fraction tree, the
+batched logup-GKR prover, einsum axis fixing and the generic (term-list)
+sumcheck.  Prints one line per measurement with the algorithmic bytes it is
+divided by, so each figure can be read against the HBM peak.
+
+    python deep-prove_b200/microbench.py [--field fr|gl] [--log2 22] [--reps 5]
+"""
+import argparse
+import importlib
+import importlib.util
+import os
+import sys
+import time
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def load():
+    name = "deep_prove_b200"
+    if name not in sys.modules:
+        spec = importlib.util.spec_from_file_location(name, os.path.join(HERE, "__init__.py"),
+                                                      submodule_search_locations=[HERE])
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules[name] = mod
+        spec.loader.exec_module(mod)
+    return sys.modules[name], importlib.import_module(name + ".prover")
+
+
+def timed(ctx, fn, reps):
+    fn()
+    ctx.sync()
+    best = 1e30
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        r = fn()
+        ctx.sync()
+        best = min(best, time.perf_counter() - t0)
+        del r
+    return best
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--field", default="fr", choices=["fr", "gl"])
+    ap.add_argument("--log2", type=int, default=22)
+    ap.add_argument("--reps", type=int, default=5)
+    args = ap.parse_args()
+    dpb, prover = load()
+    ctx = dpb.Context(0)
+    rng = np.random.default_rng(0)
+    n, N = args.log2, 1 << args.log2
+    fr = args.field == "fr"
+    base, fam, w = (dpb.FR, dpb.FR, 4) if fr else (dpb.GL_BASE, dpb.GL_EXT, 2)
+    s0, s1 = (32, 32) if fr else (8, 16)
+    one = np.frombuffer(dpb.one_bytes(fam), dtype=np.uint64)
+
+    def table(m):
+        if fr:
+            t = rng.integers(0, 2**64, size=(m, 4), dtype=np.uint64)
+            t[:, 3] &= np.uint64((1 << 60) - 1)
+            return t
+        return rng.integers(0, 2**64 - 2**32 + 1, size=m, dtype=np.uint64)
+
+    def chal(k):
+        return table(k) if fr else np.stack([table(k), table(k)], axis=1)
+
+    def report(name, seconds, nbytes):
+        print(f"{name:44s} {seconds * 1e3:9.3f} ms  {nbytes / 1e9:8.3f} GB  {nbytes / seconds / 1e9:8.1f} GB/s")
+
+    print(f"# field={args.field} log2={n} (one B200, best of {args.reps}, wall clock around a stream sync)")
+    pt = chal(n)
+    t = timed(ctx, lambda: ctx.eq_table(fam, pt).free(), args.reps)
+    report(f"eq_table 2^{n}", t, N * s1)
+
+    m = ctx.upload(table(N), base)
+    for k in (1, 10, n):
+        t = timed(ctx, lambda: ctx.fix_low(m, pt[:k]).free(), args.reps)
+        report(f"fix_low  k={k}", t, N * s0 + (N >> k) * s1)
+        t = timed(ctx, lambda: ctx.fix_high(m, pt[:k]).free(), args.reps)
+        report(f"fix_high k={k}", t, N * s0 + (N >> k) * s1)
+
+    cols = [ctx.upload(table(N), base) for _ in range(2)]
+    c, sep = chal(1)[0], chal(1)[0]
+    t = timed(ctx, lambda: ctx.logup(dpb.LOGUP_LOOKUP, cols[:1], c, sep).free(), args.reps)
+    report("logup tree, lookup, 1 column", t, (1 + 4) * N * s1 if fr else N * s0 + 4 * N * s1)
+    t = timed(ctx, lambda: ctx.logup(dpb.LOGUP_LOOKUP, cols, c, sep).free(), args.reps)
+    report("logup tree, lookup, 2 columns", t, 2 * N * s0 + 4 * N * s1)
+
+    def logup_prove(columns, cpi):
+        tr = prover.Blake3Transcript(fam)
+        inp = prover.LogUpInput.new_lookup(columns, c, sep, cpi)
+        out = prover.new_batch_multiple_sizes_prove(ctx, [inp], tr)
+        tr.free()
+        return out
+
+    t = timed(ctx, lambda: logup_prove(cols, 1), max(1, args.reps // 2))
+    # tree build for both instances + one sumcheck per level over 4 tables per instance + eq
+    tree = 2 * (N * s0 + 4 * N * s1)
+    sc = sum((4 * 2 + 1) * (4 * s1) * (1 << v) for v in range(1, n)) // 2
+    report(f"logup-GKR batch prove, 2 x 2^{n} lookups", t, tree + sc)
+
+    # generic sumcheck: two product terms with coefficients over four tables (einsum-like shape)
+    tabs = [ctx.upload(table(N), base) for _ in range(4)]
+    cb = chal(2)
+    terms = dpb.make_terms([(cb[0].tobytes(), [0, 1]), (cb[1].tobytes(), [2, 3])], bytes)
+
+    def generic():
+        tr = prover.Blake3Transcript(fam)
+        st = prover.IOPProverState.prove(ctx, n, tabs, terms, tr)
+        tr.free()
+        return st
+
+    t = timed(ctx, generic, max(1, args.reps // 2))
+    report(f"generic sumcheck, 4 tables, 2 terms, 2^{n}", t, 4 * (2 * s0 + 2 * s1) * N)
+
+    x = rng.integers(-2048, 2048, size=(512, 768), dtype=np.int64)
+    wt = rng.integers(-2048, 2048, size=(768, 3072), dtype=np.int64)
+    p9, p12 = chal(9), chal(12)
+    K = (dpb.AXIS_OUTER, dpb.AXIS_CONTRACTED)
+    t = timed(ctx, lambda: [h.free() for h in ctx.einsum_fix_axes(fam, x, K, [p9, None])[1]], args.reps)
+    report("einsum fix_axes x[512,768], bind rows", t, x.size * 8)
+    K2 = (dpb.AXIS_CONTRACTED, dpb.AXIS_OUTER)
+    t = timed(ctx, lambda: [h.free() for h in ctx.einsum_fix_axes(fam, wt, K2, [None, p12])[1]], args.reps)
+    report("einsum fix_axes W[768,3072], bind columns", t, wt.size * 8)
+    ctx.close()
+
+
+if __name__ == "__main__":
+    main()

@@ -155,6 +155,26 @@ int dpb_fix_low(dpb_ctx* ctx, const dpb_mle* mle, const void* point, uint32_t k,
  * zkml/src/iop/mod.rs:196-207).  Result: one challenge element on the host. */
 int dpb_mle_evaluate(dpb_ctx* ctx, const dpb_mle* mle, const void* point, uint32_t n, void* out);
 
+/* ---- einsum axis fixing --------------------------------------------------- */
+#define DPB_AXIS_CONTRACTED 0 /* summed over by the sumcheck: kept */
+#define DPB_AXIS_OUTER 1      /* bound to a point: contracted against eq(point)[..size] */
+#define DPB_AXIS_STACKED 2    /* kept; one output table per index */
+/* AxesMapping::fix_axes -> FixedAxesMapping::mles_from_tensor
+ * (zkml/src/layers/einsum/axis.rs:478-500, 1142-1234): `tensor` is the UNPADDED
+ * row-major tensor of signed 64-bit quantised values (the reference's Element,
+ * widened with the rule of zkml/src/quantization/mod.rs:220-267), in host memory
+ * or, with tensor_on_device != 0, in device memory.  Every OUTER axis a is bound
+ * to axis_points[a] (axis_point_len[a] challenge elements on the host, with
+ * 2^len >= shape[a]); STACKED and CONTRACTED axes are kept in row-major order.
+ * Produces one table per stacked index (S = product of the stacked sizes), each
+ * holding the contracted axes' entries zero-padded to the next power of two.
+ * out_mles receives S borrowed views (free each with dpb_mle_free) into
+ * *out_owner, which owns the memory (free it last).  *n_out = S. */
+int dpb_einsum_fix_axes(dpb_ctx* ctx, int family_dtype, const int64_t* tensor, int tensor_on_device,
+                        const uint64_t* shape, const uint8_t* axis_kind, const void* const* axis_points,
+                        const uint32_t* axis_point_len, uint32_t rank, dpb_mle** out_owner, dpb_mle** out_mles,
+                        uint32_t out_cap, uint32_t* n_out);
+
 /* ---- sumcheck (dp_crypto::structs::IOPProverState) --------------------- */
 /* Starts a sumcheck over `num_vars` variables of  sum_t coeff_t * prod_j mle[idx_tj].
  * Tables are borrowed and never modified.  A table with fewer than num_vars

@@ -940,3 +940,45 @@ def serialize_logup_proof(F, p):
     for v in p["num_denominator_columns_per_instance"]:
         out += u32(v)
     return bytes(out)
+
+
+# ------------------------------------------------------------ einsum axis fixing
+AXIS_CONTRACTED, AXIS_OUTER, AXIS_STACKED = 0, 1, 2
+
+
+def mles_from_tensor(F, tensor_i64, kinds, points):
+    """FixedAxesMapping::mles_from_tensor (zkml/src/layers/einsum/axis.rs:1142-1234),
+    axis by axis from the innermost one as the reference does: an Outer axis is
+    contracted against evals(point)[..size] (a plain dot product when nothing
+    kept lies inside it, a strided one otherwise), Stacked and Contracted axes
+    are kept; the result is cut into chunks of the contraction size, each
+    zero-padded to a power of two.  Scalars are Python ints (small tensors only).
+    Returns a list of tables (one per stacked index)."""
+    shape = list(tensor_i64.shape)
+    cur = [F.from_int(int(v)) for v in np.asarray(tensor_i64).reshape(-1)]
+    chunk, contraction = 1, 1
+    for axis in reversed(range(len(shape))):
+        size = shape[axis]
+        if kinds[axis] == AXIS_OUTER:
+            beta = array_to_scalars(F, eq_evals(F, points[axis]))[:size]
+            nxt = []
+            for start in range(0, len(cur), chunk * size):
+                full = cur[start:start + chunk * size]
+                for i in range(chunk):
+                    acc = F.zero
+                    for b, v in zip(beta, full[i::chunk]):
+                        acc = F.add(acc, F.mul(v, b))
+                    nxt.append(acc)
+            cur = nxt
+        elif kinds[axis] == AXIS_STACKED:
+            chunk *= size
+        else:
+            chunk *= size
+            contraction *= size
+    n_vars = max(contraction - 1, 0).bit_length()
+    pad = (1 << n_vars) - contraction
+    out = []
+    for start in range(0, len(cur), contraction):
+        vals = cur[start:start + contraction] + [F.zero] * pad
+        out.append(scalars_to_array(F, vals))
+    return out
