@@ -147,15 +147,22 @@ static void launch_fused_gl(dpb_ctx* ctx, const MleDesc* desc, const FoldDesc* f
     c.r1x7 = gl_mul_small(r.c1, (uint32_t)GL_NONRES);
     const bool base = folds[0].dtype_in == DPB_GL_BASE;
     if (staged) {
-        if (base) {
-            constexpr size_t sm = Stager<K, 2, 3>::bytes();
-            cudaFuncSetAttribute(v3_fold_eval_gl<K, true, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
-            v3_fold_eval_gl<K, true, 3><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, c, n_pairs, rs, out);
-        } else {
-            constexpr size_t sm = Stager<K, 4, 2>::bytes();
-            cudaFuncSetAttribute(v3_fold_eval_gl<K, false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
-            v3_fold_eval_gl<K, false, 2><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, c, n_pairs, rs, out);
-        }
+#define DPB_LAUNCH_V3(MB)                                                                                          \
+    do {                                                                                                           \
+        if (base) {                                                                                                \
+            constexpr size_t sm = Stager<K, 2, 3>::bytes();                                                        \
+            cudaFuncSetAttribute(v3_fold_eval_gl<K, true, 3, MB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); \
+            v3_fold_eval_gl<K, true, 3, MB><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, c, n_pairs, rs, out);  \
+        } else {                                                                                                   \
+            constexpr size_t sm = Stager<K, 4, 2>::bytes();                                                        \
+            cudaFuncSetAttribute(v3_fold_eval_gl<K, false, 2, MB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); \
+            v3_fold_eval_gl<K, false, 2, MB><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, c, n_pairs, rs, out); \
+        }                                                                                                          \
+    } while (0)
+        if (minb == 2) DPB_LAUNCH_V3(2);
+        else if (minb == 3) DPB_LAUNCH_V3(3);
+        else DPB_LAUNCH_V3(1);
+#undef DPB_LAUNCH_V3
         return;
     }
 #define DPB_LAUNCH_FOLD(MB)                                                                                  \

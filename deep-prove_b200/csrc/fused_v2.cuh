@@ -94,6 +94,29 @@ struct OpsGlExt {
     }
 };
 
+// Extension arithmetic with two accumulators per sample: the non-residue is
+// folded into the left operand of the lazy product (one small multiply per
+// product) instead of keeping a third 160-bit sum alive.
+struct OpsGlExt2 : OpsGlExt {
+    struct Acc {
+        glf::Acc160 s0, s1;
+    };
+    __device__ __forceinline__ static Acc acc_zero() {
+        Acc a;
+        a.s0 = a.s1 = glf::acc_zero();
+        return a;
+    }
+    __device__ __forceinline__ static void mac(Acc& acc, const T& a, const T& b) {
+        glf::acc_mac(acc.s0, a.c0, b.c0);
+        glf::acc_mac(acc.s0, glf::mul7(a.c1), b.c1);
+        glf::acc_mac(acc.s1, a.c0, b.c1);
+        glf::acc_mac(acc.s1, a.c1, b.c0);
+    }
+    __device__ __forceinline__ static Gl2 finish(const Acc& acc) {
+        return gl2_make(glf::canon(glf::acc_reduce(acc.s0)), glf::canon(glf::acc_reduce(acc.s1)));
+    }
+};
+
 struct OpsFr {
     typedef FrFam F;
     typedef Fr T;
@@ -147,6 +170,41 @@ __device__ __forceinline__ void sample_pair(typename Ops::Acc (&acc)[K + 1], con
         mac_product<Ops, K>(acc[K], g);
     }
 }
+
+// The same sampling, fed one table at a time: keeps only the running products
+// of the K-1 tables seen so far (fewer live registers than holding every
+// table's pair).  Call absorb<J>() for J = 0..K-1 in order.
+template <class Ops, int K, bool WITH_P1>
+struct Sampler {
+    typedef typename Ops::T T;
+    T p0, p1, pinf, pm1, p2;
+    template <int J>
+    __device__ __forceinline__ void absorb(typename Ops::Acc (&acc)[K + 1], const T& f0, const T& f1) {
+        const T e = Ops::sub_c(f0, f1);
+        T m = e, g = e;
+        if (K >= 3) m = Ops::add_c(e, f0);
+        if (K >= 4) g = Ops::add_c(Ops::sub_c(f1, f0), f1);
+        if (J == 0) {
+            p0 = f0;
+            p1 = f1;
+            pinf = e;
+            pm1 = m;
+            p2 = g;
+        } else if (J < K - 1) {
+            p0 = Ops::mul(p0, f0);
+            if (WITH_P1) p1 = Ops::mul(p1, f1);
+            pinf = Ops::mul(pinf, e);
+            if (K >= 3) pm1 = Ops::mul(pm1, m);
+            if (K >= 4) p2 = Ops::mul(p2, g);
+        } else {
+            Ops::mac(acc[0], p0, f0);
+            if (WITH_P1) Ops::mac(acc[1], p1, f1);
+            Ops::mac(acc[2], pinf, e);
+            if (K >= 3) Ops::mac(acc[3], pm1, m);
+            if (K >= 4) Ops::mac(acc[K], p2, g);
+        }
+    }
+};
 
 template <int K>
 struct V2Ptrs {

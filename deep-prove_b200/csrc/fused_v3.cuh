@@ -119,15 +119,16 @@ __global__ void __launch_bounds__(kStageThreads)
     publish<Ops, K>(acc, rs, out);
 }
 
-// Rounds >= 1 over Goldilocks, staged.
-template <int K, bool BASE_IN, int STAGES>
-__global__ void __launch_bounds__(kStageThreads)
+// Rounds >= 1 over Goldilocks, staged.  Tables are folded, stored and fed to
+// the sampler one at a time.
+template <int K, bool BASE_IN, int STAGES, int MINB>
+__global__ void __launch_bounds__(kStageThreads, MINB)
     v3_fold_eval_gl(V2Ptrs<K> ptrs, GlChal r, uint64_t n_pairs, ReduceScratch<GlFam> rs, Gl2* out) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int CH = BASE_IN ? 2 : 4;
     Stager<K, CH, STAGES> st;
     st.base = (uint4*)smem_raw;
-    typedef OpsGlExt Ops;
+    typedef OpsGlExt2 Ops;
     typedef glf::L2 T;
     Ops::Acc acc[K + 1];
 #pragma unroll
@@ -143,9 +144,9 @@ __global__ void __launch_bounds__(kStageThreads)
         if (nxt >= STAGES) nxt -= STAGES;
         st.issue(nxt, ptrs.in, pn, pn < n_pairs);
         cp_async_wait<STAGES - 1>();
-        T f0[K], f1[K];
-#pragma unroll
-        for (int j = 0; j < K; j++) {
+        Sampler<Ops, K, false> smp;
+        auto one_table = [&](auto jc) {
+            constexpr int j = decltype(jc)::value;
             T f[2];
             if constexpr (BASE_IN) {
                 const uint4 u = st.get(cur, j, 0), v = st.get(cur, j, 1);
@@ -159,10 +160,12 @@ __global__ void __launch_bounds__(kStageThreads)
             ulonglong2* o = (ulonglong2*)ptrs.out[j] + 2 * p;
             o[0] = make_ulonglong2(f[0].c0, f[0].c1);
             o[1] = make_ulonglong2(f[1].c0, f[1].c1);
-            f0[j] = f[0];
-            f1[j] = f[1];
-        }
-        sample_pair<Ops, K, false>(acc, f0, f1);
+            smp.template absorb<j>(acc, f[0], f[1]);
+        };
+        one_table(std::integral_constant<int, 0>());
+        one_table(std::integral_constant<int, 1>());
+        if constexpr (K >= 3) one_table(std::integral_constant<int, 2>());
+        if constexpr (K >= 4) one_table(std::integral_constant<int, 3>());
         if (++cur == STAGES) cur = 0;
     }
     cp_async_wait<0>();
