@@ -4,6 +4,9 @@
 // sumcheck begins, so a round is: [fold with the previous challenge] + one
 // evaluation launch + one stream synchronisation.  The evaluation kernel's
 // last block writes the round polynomial straight into mapped host memory.
+#include <atomic>
+#include <chrono>
+
 #include "common.cuh"
 #include "fused_kernels.cuh"
 #include "fused_v2.cuh"
@@ -205,6 +208,33 @@ static void launch_fused(dpb_ctx* ctx, const MleDesc* desc, const FoldDesc* fold
     else launch_fused_fr<4>(ctx, desc, folds, round, r, n_pairs);
 }
 
+// Polls the completion flag of the round just launched.  The kernel's last
+// block stores the sequence number after the result, so the host sees the
+// result without paying a stream synchronisation; the stream is queried now and
+// then so that a failed launch surfaces, and the wait is bounded.
+static int wait_round_flag(dpb_ctx* ctx) {
+    const unsigned int want = ctx->done_seq;
+    uint64_t spins = 0;
+    std::chrono::steady_clock::time_point t0;
+    while (*ctx->flag_host != want) {
+        if ((++spins & 0xFFF) == 0) {
+            cudaError_t e = cudaStreamQuery(ctx->stream);
+            if (e != cudaSuccess && e != cudaErrorNotReady) return fail(DPB_ECUDA, "round kernel: %s", cudaGetErrorString(e));
+            if (e == cudaSuccess && *ctx->flag_host != want) {
+                // the stream drained without the flag: the launch itself failed
+                e = cudaGetLastError();
+                if (*ctx->flag_host == want) break;
+                return fail(DPB_ECUDA, "round kernel did not signal completion (%s)", cudaGetErrorString(e));
+            }
+            if (spins == 0x1000) t0 = std::chrono::steady_clock::now();
+            else if (std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() > 120.0)
+                return fail(DPB_ETIMEOUT, "round kernel did not finish within 120 s");
+        }
+    }
+    std::atomic_thread_fence(std::memory_order_acquire);
+    return DPB_OK;
+}
+
 template <class F>
 static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
     typedef typename F::E E;
@@ -218,6 +248,9 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
     const size_t msg_bytes = (sc->d + 1) * sizeof(E);
     const bool sharded = sc->log2_ranks > 0;
     ctx->round_out = sharded ? (void*)((char*)ctx->gather_dev + (size_t)ctx->rank * msg_bytes) : ctx->result_dev;
+    // unsharded rounds signal completion through a flag in mapped host memory that the host polls
+    ctx->done_seq++;
+    ctx->done_flag_dev = sharded ? nullptr : ctx->flag_dev;
     if (ctx->profile) DPB_CUDA(cudaEventRecord(ctx->prof_ev[0], ctx->stream));
     bool done = false;
     if (sc->fused_shape == kFusedProduct) {
@@ -253,7 +286,7 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
             raw[x] = tot;
         }
     } else {
-        DPB_CUDA(cudaStreamSynchronize(ctx->stream));
+        DPB_TRY(wait_round_flag(ctx));
         memcpy(raw, ctx->result_host, msg_bytes);
     }
     if (done) {
@@ -267,6 +300,7 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
     }
     if (ctx->profile) {
         float ms = 0.f;
+        DPB_CUDA(cudaEventSynchronize(ctx->prof_ev[1]));
         DPB_CUDA(cudaEventElapsedTime(&ms, ctx->prof_ev[0], ctx->prof_ev[1]));
         // minimum traffic of this round: every table read once, folded tables written once
         uint64_t bytes = 0;

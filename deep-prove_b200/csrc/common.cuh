@@ -59,6 +59,12 @@ struct dpb_ctx {
     void* result_host = nullptr;
     void* result_dev = nullptr;
     size_t result_bytes = 0;
+    // completion flag of the current round (last word of the mapped result buffer); null when the
+    // round is followed by a collective on the stream
+    unsigned int* done_flag_dev = nullptr;            // what the next launch signals (or null)
+    unsigned int* flag_dev = nullptr;                 // device view of the flag word
+    volatile unsigned int* flag_host = nullptr;       // host view of the same word
+    unsigned int done_seq = 0;
     void* round_out = nullptr;  // where the current round's kernel publishes (result_dev or the exchange area)
     // small device staging area for points / challenges
     void* stage_dev = nullptr;
@@ -99,6 +105,8 @@ inline ReduceScratch<F> reduce_scratch(const dpb_ctx* ctx) {
     ReduceScratch<F> rs;
     rs.partials = (typename F::E*)ctx->partials;
     rs.counter = ctx->counter;
+    rs.done_flag = ctx->done_flag_dev;
+    rs.done_value = ctx->done_seq;
     return rs;
 }
 

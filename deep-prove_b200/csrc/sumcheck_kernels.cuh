@@ -38,7 +38,21 @@ template <class F>
 struct ReduceScratch {
     typename F::E* partials;  // [max_blocks][NACC]
     unsigned int* counter;    // zero between launches
+    // Optional completion flag (mapped host memory): after the result is
+    // written, done_value is stored there so the host can poll for it instead
+    // of synchronising the stream.  nullptr: no flag.
+    unsigned int* done_flag;
+    unsigned int done_value;
 };
+
+template <class F>
+__device__ __forceinline__ void signal_done(const ReduceScratch<F>& rs) {
+    __threadfence_system();
+    if (rs.done_flag) {
+        *(volatile unsigned int*)rs.done_flag = rs.done_value;
+        __threadfence_system();
+    }
+}
 
 constexpr int kThreads = 256;
 constexpr int kMaxWarps = kThreads / 32;
@@ -86,7 +100,7 @@ __device__ __forceinline__ void grid_sum_publish(typename F::E (&acc)[NACC], Red
         if (threadIdx.x == 0) {
 #pragma unroll
             for (int i = 0; i < NACC; i++) out[i] = acc[i];
-            __threadfence_system();
+            signal_done<F>(rs);
         }
         return;
     }
@@ -120,7 +134,7 @@ __device__ __forceinline__ void grid_sum_publish(typename F::E (&acc)[NACC], Red
 #pragma unroll
         for (int i = 0; i < NACC; i++) out[i] = tot[i];
         *rs.counter = 0;
-        __threadfence_system();
+        signal_done<F>(rs);
     }
 }
 
