@@ -11,6 +11,7 @@
 #include "fused_kernels.cuh"
 #include "fused_v2.cuh"
 #include "fused_v3.cuh"
+#include "fused_v4.cuh"
 #include "comm.cuh"
 
 namespace dpb {
@@ -123,7 +124,18 @@ static void launch_fused_gl(dpb_ctx* ctx, const MleDesc* desc, const FoldDesc* f
             ptrs.out[j] = nullptr;
         }
         const bool base = desc[0].dtype == DPB_GL_BASE;
-        if (staged) {
+        static const int use_v4 = getenv("DPB_V4") ? atoi(getenv("DPB_V4")) : 1;
+        if (staged && use_v4) {
+            if (base) {
+                constexpr size_t sm = Stager<K, 1, 4>::bytes();
+                cudaFuncSetAttribute(v4_eval0_gl<K, true, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+                v4_eval0_gl<K, true, 4><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, n_pairs, rs, out);
+            } else {
+                constexpr size_t sm = Stager<K, 2, 3>::bytes();
+                cudaFuncSetAttribute(v4_eval0_gl<K, false, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+                v4_eval0_gl<K, false, 3><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, n_pairs, rs, out);
+            }
+        } else if (staged) {
             if (base) {
                 constexpr size_t sm = Stager<K, 1, 4>::bytes();
                 cudaFuncSetAttribute(v3_eval0_gl<K, true, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
@@ -149,6 +161,30 @@ static void launch_fused_gl(dpb_ctx* ctx, const MleDesc* desc, const FoldDesc* f
     c.r1 = r.c1;
     c.r1x7 = gl_mul_small(r.c1, (uint32_t)GL_NONRES);
     const bool base = folds[0].dtype_in == DPB_GL_BASE;
+    static const int use_v4f = getenv("DPB_V4") ? atoi(getenv("DPB_V4")) : 1;
+    if (staged && use_v4f) {
+        glw::Chal wc;
+        wc.r0 = glw::make_w((uint32_t)c.r0, (uint32_t)(c.r0 >> 32));
+        wc.r1 = glw::make_w((uint32_t)c.r1, (uint32_t)(c.r1 >> 32));
+        wc.r1x7 = glw::make_w((uint32_t)c.r1x7, (uint32_t)(c.r1x7 >> 32));
+#define DPB_LAUNCH_V4(MB)                                                                                          \
+    do {                                                                                                           \
+        if (base) {                                                                                                \
+            constexpr size_t sm = Stager<K, 2, 3>::bytes();                                                        \
+            cudaFuncSetAttribute(v4_fold_eval_gl<K, true, 3, MB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); \
+            v4_fold_eval_gl<K, true, 3, MB><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, wc, n_pairs, rs, out); \
+        } else {                                                                                                   \
+            constexpr size_t sm = Stager<K, 4, 2>::bytes();                                                        \
+            cudaFuncSetAttribute(v4_fold_eval_gl<K, false, 2, MB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); \
+            v4_fold_eval_gl<K, false, 2, MB><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, wc, n_pairs, rs, out); \
+        }                                                                                                          \
+    } while (0)
+        if (minb == 2) DPB_LAUNCH_V4(2);
+        else if (minb == 3) DPB_LAUNCH_V4(3);
+        else DPB_LAUNCH_V4(1);
+#undef DPB_LAUNCH_V4
+        return;
+    }
     if (staged) {
 #define DPB_LAUNCH_V3(MB)                                                                                          \
     do {                                                                                                           \

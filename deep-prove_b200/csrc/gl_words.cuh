@@ -1,0 +1,216 @@
+// Goldilocks arithmetic on explicit 32-bit words, for the hottest kernels.
+//
+// Instruction counts measured on sm_100a show that a 64-bit formulation pays
+// for packing and unpacking register pairs around every multiply: the C
+// version of a 64x64 product issues ten multiply-pipe instructions where four
+// are needed.  The integer pipes dispatch an IADD3 per cycle but an IMAD (or
+// LOP3 / SHF / ISETP) every other cycle, so the cheapest code is: exactly four
+// mul.wide.u32 per product, and everything else as carry-chained 32-bit adds,
+// with corrections driven by the carry flag and a mask — no compares, no
+// predicates, no shifts.
+//
+// Values are "loose" (any 64-bit representative of the residue) unless a
+// comment says canonical.  p = 2^64 - 2^32 + 1, EPS = 2^32 - 1 = 2^64 mod p,
+// 2^96 = -1, 2^128 = -2^32 (mod p).
+#pragma once
+#include <cstdint>
+
+#include "field_gl.cuh"
+
+namespace dpb {
+namespace glw {
+
+struct W {
+    uint32_t lo, hi;
+};
+__host__ __device__ __forceinline__ W make_w(uint32_t lo, uint32_t hi) {
+    W r;
+    r.lo = lo;
+    r.hi = hi;
+    return r;
+}
+__device__ __forceinline__ uint64_t to_u64(const W& a) { return (uint64_t)a.lo | ((uint64_t)a.hi << 32); }
+
+// a loose, c canonical -> loose.  A carry means the true sum is s + 2^64 = s + EPS;
+// s < p then, so adding EPS cannot carry again.
+__device__ __forceinline__ W add_c(const W& a, const W& c) {
+    W d;
+    asm("{ .reg .u32 m;\n\t"
+        "add.cc.u32 %0, %2, %4; addc.cc.u32 %1, %3, %5; addc.u32 m, 0, 0; neg.s32 m, m;\n\t"
+        "add.cc.u32 %0, %0, m; addc.u32 %1, %1, 0; }"
+        : "=&r"(d.lo), "=&r"(d.hi)
+        : "r"(a.lo), "r"(a.hi), "r"(c.lo), "r"(c.hi));
+    return d;
+}
+// a loose, c canonical -> loose.  A borrow means the true difference is d - 2^64 = d - EPS;
+// d >= 2^32 then, so subtracting EPS cannot borrow again.
+__device__ __forceinline__ W sub_c(const W& a, const W& c) {
+    W d;
+    asm("{ .reg .u32 m;\n\t"
+        "sub.cc.u32 %0, %2, %4; subc.cc.u32 %1, %3, %5; subc.u32 m, 0, 0;\n\t"
+        "sub.cc.u32 %0, %0, m; subc.u32 %1, %1, 0; }"
+        : "=&r"(d.lo), "=&r"(d.hi)
+        : "r"(a.lo), "r"(a.hi), "r"(c.lo), "r"(c.hi));
+    return d;
+}
+// loose -> canonical: a >= p  <=>  a + EPS carries; then a + EPS (mod 2^64) = a - p
+__device__ __forceinline__ W canon(const W& a) {
+    W d;
+    asm("{ .reg .u32 t, m;\n\t"
+        "add.cc.u32 t, %2, 0xffffffff; addc.cc.u32 t, %3, 0; addc.u32 m, 0, 0; neg.s32 m, m;\n\t"
+        "add.cc.u32 %0, %2, m; addc.u32 %1, %3, 0; }"
+        : "=&r"(d.lo), "=&r"(d.hi)
+        : "r"(a.lo), "r"(a.hi));
+    return d;
+}
+
+// 160-bit accumulator of 128-bit products: five words, little-endian.
+struct A5 {
+    uint32_t w0, w1, w2, w3, w4;
+};
+__device__ __forceinline__ A5 acc_zero() {
+    A5 a;
+    a.w0 = a.w1 = a.w2 = a.w3 = a.w4 = 0;
+    return a;
+}
+// accumulator that starts at the value v
+__device__ __forceinline__ A5 acc_from(const W& v) {
+    A5 a;
+    a.w0 = v.lo;
+    a.w1 = v.hi;
+    a.w2 = a.w3 = a.w4 = 0;
+    return a;
+}
+
+// The 128-bit product a * b as four words: four 32x32 products and six adds.
+// It does not depend on any accumulator, so the adds that do (acc_add below)
+// form a short chain.
+struct P4 {
+    uint32_t x0, x1, x2, x3;
+};
+__device__ __forceinline__ P4 prod(const W& a, const W& b) {
+    P4 r;
+    asm("{ .reg .u32 q0,q1,r0,r1; .reg .u64 t;\n\t"
+        "mul.wide.u32 t, %4, %6; mov.b64 {%0,%1}, t;\n\t"
+        "mul.wide.u32 t, %5, %7; mov.b64 {%2,%3}, t;\n\t"
+        "mul.wide.u32 t, %4, %7; mov.b64 {q0,q1}, t;\n\t"
+        "mul.wide.u32 t, %5, %6; mov.b64 {r0,r1}, t;\n\t"
+        "add.cc.u32 %1, %1, q0; addc.cc.u32 %2, %2, q1; addc.u32 %3, %3, 0;\n\t"
+        "add.cc.u32 %1, %1, r0; addc.cc.u32 %2, %2, r1; addc.u32 %3, %3, 0; }"
+        : "=&r"(r.x0), "=&r"(r.x1), "=&r"(r.x2), "=&r"(r.x3)
+        : "r"(a.lo), "r"(a.hi), "r"(b.lo), "r"(b.hi));
+    return r;
+}
+__device__ __forceinline__ void acc_add(A5& s, const P4& p) {
+    asm("add.cc.u32 %0, %0, %5; addc.cc.u32 %1, %1, %6; addc.cc.u32 %2, %2, %7; addc.cc.u32 %3, %3, %8; addc.u32 %4, %4, 0;"
+        : "+r"(s.w0), "+r"(s.w1), "+r"(s.w2), "+r"(s.w3), "+r"(s.w4)
+        : "r"(p.x0), "r"(p.x1), "r"(p.x2), "r"(p.x3));
+}
+// acc += a * b
+__device__ __forceinline__ void acc_mac(A5& s, const W& a, const W& b) { acc_add(s, prod(a, b)); }
+
+// Loose residue of the accumulator.  With x = w0 + 2^32 w1, the value is
+//   x + 2^64 w2 + 2^96 w3 + 2^128 w4 = x - (w3 + 2^32 w4) + w2 * EPS   (mod p).
+// w4 counts overflows of a thread's sums and stays far below 2^31, so
+// w3 + 2^32 w4 is canonical and the first step is a sub_c; w2 * EPS is
+// (w2 << 32) - w2, built with one sub / subc, and added with the add_c fix.
+__device__ __forceinline__ W acc_reduce(const A5& s) {
+    W d;
+    asm("{ .reg .u32 m, y0, y1;\n\t"
+        "sub.cc.u32 %0, %2, %5; subc.cc.u32 %1, %3, %6; subc.u32 m, 0, 0;\n\t"
+        "sub.cc.u32 %0, %0, m; subc.u32 %1, %1, 0;\n\t"
+        "sub.cc.u32 y0, 0, %4; subc.u32 y1, %4, 0;\n\t"
+        "add.cc.u32 %0, %0, y0; addc.cc.u32 %1, %1, y1; addc.u32 m, 0, 0; neg.s32 m, m;\n\t"
+        "add.cc.u32 %0, %0, m; addc.u32 %1, %1, 0; }"
+        : "=&r"(d.lo), "=&r"(d.hi)
+        : "r"(s.w0), "r"(s.w1), "r"(s.w2), "r"(s.w3), "r"(s.w4));
+    return d;
+}
+
+// a * b as a loose residue
+__device__ __forceinline__ W mul(const W& a, const W& b) {
+    const P4 p = prod(a, b);
+    A5 s;
+    s.w0 = p.x0;
+    s.w1 = p.x1;
+    s.w2 = p.x2;
+    s.w3 = p.x3;
+    s.w4 = 0;
+    return acc_reduce(s);
+}
+
+// 7 * a as a loose residue: 7a = x0 + 2^32 x1 + 2^64 x2 with x2 < 7, and 2^64 x2 = x2 * EPS
+__device__ __forceinline__ W mul7(const W& a) {
+    W d;
+    asm("{ .reg .u32 x0, c0, y0, y1, x2, m, z0, z1; .reg .u64 t;\n\t"
+        "mul.wide.u32 t, %2, 7; mov.b64 {x0,c0}, t;\n\t"
+        "mul.wide.u32 t, %3, 7; mov.b64 {y0,y1}, t;\n\t"
+        "add.cc.u32 y0, y0, c0; addc.u32 x2, y1, 0;\n\t"
+        "sub.cc.u32 z0, 0, x2; subc.u32 z1, x2, 0;\n\t"
+        "add.cc.u32 %0, x0, z0; addc.cc.u32 %1, y0, z1; addc.u32 m, 0, 0; neg.s32 m, m;\n\t"
+        "add.cc.u32 %0, %0, m; addc.u32 %1, %1, 0; }"
+        : "=&r"(d.lo), "=&r"(d.hi)
+        : "r"(a.lo), "r"(a.hi));
+    return d;
+}
+
+// ---- quadratic extension X^2 = 7, loose components ------------------------------
+struct W2 {
+    W c0, c1;
+};
+__device__ __forceinline__ W2 add_c(const W2& a, const W2& c) {
+    W2 r;
+    r.c0 = add_c(a.c0, c.c0);
+    r.c1 = add_c(a.c1, c.c1);
+    return r;
+}
+__device__ __forceinline__ W2 sub_c(const W2& a, const W2& c) {
+    W2 r;
+    r.c0 = sub_c(a.c0, c.c0);
+    r.c1 = sub_c(a.c1, c.c1);
+    return r;
+}
+// (a0 + a1 X)(b0 + b1 X): c0 = a0 b0 + (7 a1) b1, c1 = a0 b1 + a1 b0; two lazy sums, two reductions
+__device__ __forceinline__ W2 mul(const W2& a, const W2& b) {
+    A5 s0 = acc_zero(), s1 = acc_zero();
+    acc_mac(s0, a.c0, b.c0);
+    acc_mac(s0, mul7(a.c1), b.c1);
+    acc_mac(s1, a.c0, b.c1);
+    acc_mac(s1, a.c1, b.c0);
+    W2 r;
+    r.c0 = acc_reduce(s0);
+    r.c1 = acc_reduce(s1);
+    return r;
+}
+
+// What a fold needs of the challenge r = r0 + r1 X: r0, r1 and 7 r1, canonical.
+struct Chal {
+    W r0, r1, r1x7;
+};
+// canonical a0 + r (a1 - a0), a0 and a1 canonical extension elements
+__device__ __forceinline__ W2 fold_ext(const W2& a0, const W2& a1, const Chal& r) {
+    const W2 d = sub_c(a1, a0);
+    A5 s0 = acc_from(a0.c0), s1 = acc_from(a0.c1);
+    acc_mac(s0, d.c0, r.r0);
+    acc_mac(s0, d.c1, r.r1x7);
+    acc_mac(s1, d.c0, r.r1);
+    acc_mac(s1, d.c1, r.r0);
+    W2 f;
+    f.c0 = canon(acc_reduce(s0));
+    f.c1 = canon(acc_reduce(s1));
+    return f;
+}
+// canonical a0 + r (a1 - a0), a0 and a1 canonical base elements
+__device__ __forceinline__ W2 fold_base(const W& a0, const W& a1, const Chal& r) {
+    const W d = sub_c(a1, a0);
+    A5 s0 = acc_from(a0), s1 = acc_zero();
+    acc_mac(s0, d, r.r0);
+    acc_mac(s1, d, r.r1);
+    W2 f;
+    f.c0 = canon(acc_reduce(s0));
+    f.c1 = canon(acc_reduce(s1));
+    return f;
+}
+
+}  // namespace glw
+}  // namespace dpb
