@@ -112,39 +112,23 @@ static void launch_fused_gl(dpb_ctx* ctx, const MleDesc* desc, const FoldDesc* f
     V2Ptrs<K> ptrs;
     const ReduceScratch<GlFam> rs = reduce_scratch<GlFam>(ctx);
     Gl2* out = (Gl2*)ctx->round_out;
-    static const int per_sm = getenv("DPB_GRID_PER_SM") ? atoi(getenv("DPB_GRID_PER_SM")) : 4;
-    static const int minb = getenv("DPB_MINB") ? atoi(getenv("DPB_MINB")) : 1;
-    const uint32_t grid = grid_for(ctx, n_pairs, per_sm);
-    // staged kernels (fused_v3.cuh) once a launch has enough items per thread to pipeline
-    static const int use_v3 = getenv("DPB_V3") ? atoi(getenv("DPB_V3")) : 1;
-    const bool staged = use_v3 && n_pairs >= (uint64_t)grid * kStageThreads * 2;
+    const uint32_t grid = grid_for(ctx, n_pairs, 4);
+    // staged kernels (fused_v4.cuh) once a launch has enough items per thread to pipeline
+    const bool staged = n_pairs >= (uint64_t)grid * kStageThreads * 2;
     if (round == 0) {
         for (int j = 0; j < K; j++) {
             ptrs.in[j] = desc[j].ptr;
             ptrs.out[j] = nullptr;
         }
         const bool base = desc[0].dtype == DPB_GL_BASE;
-        static const int use_v4 = getenv("DPB_V4") ? atoi(getenv("DPB_V4")) : 1;
-        if (staged && use_v4) {
-            if (base) {
-                constexpr size_t sm = Stager<K, 1, 4>::bytes();
-                cudaFuncSetAttribute(v4_eval0_gl<K, true, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
-                v4_eval0_gl<K, true, 4><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, n_pairs, rs, out);
-            } else {
-                constexpr size_t sm = Stager<K, 2, 3>::bytes();
-                cudaFuncSetAttribute(v4_eval0_gl<K, false, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
-                v4_eval0_gl<K, false, 3><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, n_pairs, rs, out);
-            }
+        if (staged && base) {
+            constexpr size_t sm = Stager<K, 1, 4>::bytes();
+            cudaFuncSetAttribute(v4_eval0_gl<K, true, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+            v4_eval0_gl<K, true, 4><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, n_pairs, rs, out);
         } else if (staged) {
-            if (base) {
-                constexpr size_t sm = Stager<K, 1, 4>::bytes();
-                cudaFuncSetAttribute(v3_eval0_gl<K, true, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
-                v3_eval0_gl<K, true, 4><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, n_pairs, rs, out);
-            } else {
-                constexpr size_t sm = Stager<K, 2, 3>::bytes();
-                cudaFuncSetAttribute(v3_eval0_gl<K, false, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
-                v3_eval0_gl<K, false, 3><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, n_pairs, rs, out);
-            }
+            constexpr size_t sm = Stager<K, 2, 3>::bytes();
+            cudaFuncSetAttribute(v4_eval0_gl<K, false, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+            v4_eval0_gl<K, false, 3><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, n_pairs, rs, out);
         } else if (base) {
             v2_eval0<OpsGlBase, K><<<grid, kThreads, 0, ctx->stream>>>(ptrs, n_pairs, rs, out);
         } else {
@@ -161,59 +145,24 @@ static void launch_fused_gl(dpb_ctx* ctx, const MleDesc* desc, const FoldDesc* f
     c.r1 = r.c1;
     c.r1x7 = gl_mul_small(r.c1, (uint32_t)GL_NONRES);
     const bool base = folds[0].dtype_in == DPB_GL_BASE;
-    static const int use_v4f = getenv("DPB_V4") ? atoi(getenv("DPB_V4")) : 1;
-    if (staged && use_v4f) {
+    if (staged) {
         glw::Chal wc;
         wc.r0 = glw::make_w((uint32_t)c.r0, (uint32_t)(c.r0 >> 32));
         wc.r1 = glw::make_w((uint32_t)c.r1, (uint32_t)(c.r1 >> 32));
         wc.r1x7 = glw::make_w((uint32_t)c.r1x7, (uint32_t)(c.r1x7 >> 32));
-#define DPB_LAUNCH_V4(MB)                                                                                          \
-    do {                                                                                                           \
-        if (base) {                                                                                                \
-            constexpr size_t sm = Stager<K, 2, 3>::bytes();                                                        \
-            cudaFuncSetAttribute(v4_fold_eval_gl<K, true, 3, MB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); \
-            v4_fold_eval_gl<K, true, 3, MB><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, wc, n_pairs, rs, out); \
-        } else {                                                                                                   \
-            constexpr size_t sm = Stager<K, 4, 2>::bytes();                                                        \
-            cudaFuncSetAttribute(v4_fold_eval_gl<K, false, 2, MB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); \
-            v4_fold_eval_gl<K, false, 2, MB><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, wc, n_pairs, rs, out); \
-        }                                                                                                          \
-    } while (0)
-        if (minb == 2) DPB_LAUNCH_V4(2);
-        else if (minb == 3) DPB_LAUNCH_V4(3);
-        else DPB_LAUNCH_V4(1);
-#undef DPB_LAUNCH_V4
+        if (base) {
+            constexpr size_t sm = Stager<K, 2, 3>::bytes();
+            cudaFuncSetAttribute(v4_fold_eval_gl<K, true, 3, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+            v4_fold_eval_gl<K, true, 3, 1><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, wc, n_pairs, rs, out);
+        } else {
+            constexpr size_t sm = Stager<K, 4, 2>::bytes();
+            cudaFuncSetAttribute(v4_fold_eval_gl<K, false, 2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+            v4_fold_eval_gl<K, false, 2, 1><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, wc, n_pairs, rs, out);
+        }
         return;
     }
-    if (staged) {
-#define DPB_LAUNCH_V3(MB)                                                                                          \
-    do {                                                                                                           \
-        if (base) {                                                                                                \
-            constexpr size_t sm = Stager<K, 2, 3>::bytes();                                                        \
-            cudaFuncSetAttribute(v3_fold_eval_gl<K, true, 3, MB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); \
-            v3_fold_eval_gl<K, true, 3, MB><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, c, n_pairs, rs, out);  \
-        } else {                                                                                                   \
-            constexpr size_t sm = Stager<K, 4, 2>::bytes();                                                        \
-            cudaFuncSetAttribute(v3_fold_eval_gl<K, false, 2, MB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); \
-            v3_fold_eval_gl<K, false, 2, MB><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, c, n_pairs, rs, out); \
-        }                                                                                                          \
-    } while (0)
-        if (minb == 2) DPB_LAUNCH_V3(2);
-        else if (minb == 3) DPB_LAUNCH_V3(3);
-        else DPB_LAUNCH_V3(1);
-#undef DPB_LAUNCH_V3
-        return;
-    }
-#define DPB_LAUNCH_FOLD(MB)                                                                                  \
-    do {                                                                                                      \
-        if (base) v2_fold_eval_gl<K, true, MB><<<grid, kThreads, 0, ctx->stream>>>(ptrs, c, n_pairs, rs, out); \
-        else v2_fold_eval_gl<K, false, MB><<<grid, kThreads, 0, ctx->stream>>>(ptrs, c, n_pairs, rs, out);     \
-    } while (0)
-    if (minb == 2) DPB_LAUNCH_FOLD(2);
-    else if (minb == 3) DPB_LAUNCH_FOLD(3);
-    else if (minb == 4) DPB_LAUNCH_FOLD(4);
-    else DPB_LAUNCH_FOLD(1);
-#undef DPB_LAUNCH_FOLD
+    if (base) v2_fold_eval_gl<K, true, 1><<<grid, kThreads, 0, ctx->stream>>>(ptrs, c, n_pairs, rs, out);
+    else v2_fold_eval_gl<K, false, 1><<<grid, kThreads, 0, ctx->stream>>>(ptrs, c, n_pairs, rs, out);
 }
 
 template <int K>
@@ -343,14 +292,14 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
         const char* name;
         if (i == 0) {
             for (uint32_t j = 0; j < sc->k; j++) bytes += dtype_size(sc->tr[j].dtype) << sc->tr[j].nv;
-            name = done ? (sc->tr[0].dtype == DPB_GL_BASE ? "v2_eval0<base>" : "v2_eval0") : "sc_eval_generic";
+            name = done ? (sc->tr[0].dtype == DPB_GL_BASE ? "fused_eval0<base>" : "fused_eval0") : "sc_eval_generic";
         } else {
             const FoldDesc* fd = sc->h_fold.data() + (size_t)i * sc->k;
             for (uint32_t j = 0; j < sc->n_fold[i]; j++)
                 bytes += fd[j].n_out * (2 * dtype_size(fd[j].dtype_in) + sizeof(E));
             for (uint32_t j = 0; j < sc->k; j++)
                 if (sc->h_desc[(size_t)i * sc->k + j].shift >= 0) bytes += dtype_size(sc->tr[j].dtype) << sc->tr[j].nv;
-            name = done ? (fd[0].dtype_in == DPB_GL_BASE ? "v2_fold_eval<base>" : "v2_fold_eval")
+            name = done ? (fd[0].dtype_in == DPB_GL_BASE ? "fused_fold_eval<base>" : "fused_fold_eval")
                         : "sc_fold_generic+sc_eval_generic";
         }
         bool found = false;

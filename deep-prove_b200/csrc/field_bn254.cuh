@@ -35,6 +35,12 @@ struct alignas(16) Fr {
 #define DPB_FR_RR2 0x8c49833d53bb8085ULL
 #define DPB_FR_RR3 0x0216d0b17f4e44a5ULL
 
+}  // namespace dpb
+#if defined(__CUDACC__)
+#include "fr_words.cuh"
+#endif
+namespace dpb {
+
 DPB_HD Fr fr_zero() {
     Fr r;
     r.l[0] = r.l[1] = r.l[2] = r.l[3] = 0;
@@ -102,7 +108,7 @@ DPB_HD Fr fr_reduce_once(const Fr& a) {
     return bw ? a : d;
 }
 
-DPB_HD Fr fr_add(const Fr& a, const Fr& b) {
+DPB_HD Fr fr_add_portable(const Fr& a, const Fr& b) {
     uint64_t c = 0;
     Fr s;
     s.l[0] = adc(a.l[0], b.l[0], c);
@@ -112,7 +118,7 @@ DPB_HD Fr fr_add(const Fr& a, const Fr& b) {
     return fr_reduce_once(s);
 }
 
-DPB_HD Fr fr_sub(const Fr& a, const Fr& b) {
+DPB_HD Fr fr_sub_portable(const Fr& a, const Fr& b) {
     uint64_t bw = 0;
     Fr d;
     d.l[0] = sbb(a.l[0], b.l[0], bw);
@@ -129,11 +135,28 @@ DPB_HD Fr fr_sub(const Fr& a, const Fr& b) {
     return d;
 }
 
+// Device code uses the 32-bit word routines of fr_words.cuh; host code the
+// portable 64-bit limb ones above.  Same values either way.
+DPB_HD Fr fr_add(const Fr& a, const Fr& b) {
+#if defined(__CUDA_ARCH__)
+    return frw::to_fr(frw::add(frw::from_fr(a), frw::from_fr(b)));
+#else
+    return fr_add_portable(a, b);
+#endif
+}
+DPB_HD Fr fr_sub(const Fr& a, const Fr& b) {
+#if defined(__CUDA_ARCH__)
+    return frw::to_fr(frw::sub(frw::from_fr(a), frw::from_fr(b)));
+#else
+    return fr_sub_portable(a, b);
+#endif
+}
+
 DPB_HD Fr fr_neg(const Fr& a) { return fr_is_zero(a) ? a : fr_sub(fr_zero(), a); }
 
 // Montgomery product a*b/R mod r (coarsely integrated operand scanning; the
 // top limb of r leaves two spare bits so the running sum fits five limbs).
-DPB_HD Fr fr_mul(const Fr& a, const Fr& b) {
+DPB_HD Fr fr_mul_portable(const Fr& a, const Fr& b) {
     const uint64_t p[4] = {DPB_FR_P0, DPB_FR_P1, DPB_FR_P2, DPB_FR_P3};
     uint64_t t0 = 0, t1 = 0, t2 = 0, t3 = 0, t4 = 0;
 #if defined(__CUDA_ARCH__)
@@ -162,6 +185,14 @@ DPB_HD Fr fr_mul(const Fr& a, const Fr& b) {
     r.l[2] = t2;
     r.l[3] = t3;
     return fr_reduce_once(r);
+}
+
+DPB_HD Fr fr_mul(const Fr& a, const Fr& b) {
+#if defined(__CUDA_ARCH__)
+    return frw::to_fr(frw::mul(frw::from_fr(a), frw::from_fr(b)));
+#else
+    return fr_mul_portable(a, b);
+#endif
 }
 
 DPB_HD Fr fr_sqr(const Fr& a) { return fr_mul(a, a); }
