@@ -4,11 +4,12 @@
 // each 64x64 product expands into a long sequence of 32-bit multiply-adds and
 // register shuffles.  Here a field element is eight 32-bit words and the
 // Montgomery product is coarsely integrated operand scanning over words: per
-// word of b, eight 32x32 products accumulate into the running sum through two
-// carry chains (low halves, high halves), then eight more for the reduction
-// step.  Multiplies are mul.wide.u32 (one per limb product), everything else is
-// carry-chained 32-bit addition: the instruction mix the sm_100a integer pipes
-// dispatch fastest (an add per cycle, a multiply every other cycle).
+// word of b, eight 32x32 products accumulate into the running sum, then eight
+// more for the reduction step.  Every product is a wide multiply-add that adds
+// its 64-bit result to an aligned word pair with carry in and out, so the 128
+// multiplies carry almost all of the additions; measured on sm_100a a wide
+// multiply-add costs about four issue cycles and a carry-chained add about one,
+// which makes the multiply count the floor.
 //
 // The word layout is the little-endian split of the four 64-bit limbs, so a
 // conversion is a register reinterpretation.
@@ -50,49 +51,67 @@ __device__ __forceinline__ Fr to_fr(const F8& a) {
 #define DPB_FRW_P7 0x30644e72u
 #define DPB_FRW_INV 0xefffffffu  // -r^{-1} mod 2^32
 
-// t (10 words) += a (8 words) * b (one word)
-__device__ __forceinline__ void row_mac(uint32_t (&t)[10], const F8& a, uint32_t b) {
-    asm("{ .reg .u32 l0,l1,l2,l3,l4,l5,l6,l7,h0,h1,h2,h3,h4,h5,h6,h7; .reg .u64 x;\n\t"
-        "mul.wide.u32 x, %10, %18; mov.b64 {l0,h0}, x;\n\t"
-        "mul.wide.u32 x, %11, %18; mov.b64 {l1,h1}, x;\n\t"
-        "mul.wide.u32 x, %12, %18; mov.b64 {l2,h2}, x;\n\t"
-        "mul.wide.u32 x, %13, %18; mov.b64 {l3,h3}, x;\n\t"
-        "mul.wide.u32 x, %14, %18; mov.b64 {l4,h4}, x;\n\t"
-        "mul.wide.u32 x, %15, %18; mov.b64 {l5,h5}, x;\n\t"
-        "mul.wide.u32 x, %16, %18; mov.b64 {l6,h6}, x;\n\t"
-        "mul.wide.u32 x, %17, %18; mov.b64 {l7,h7}, x;\n\t"
-        "add.cc.u32 %0, %0, l0; addc.cc.u32 %1, %1, l1; addc.cc.u32 %2, %2, l2; addc.cc.u32 %3, %3, l3;\n\t"
-        "addc.cc.u32 %4, %4, l4; addc.cc.u32 %5, %5, l5; addc.cc.u32 %6, %6, l6; addc.cc.u32 %7, %7, l7;\n\t"
-        "addc.cc.u32 %8, %8, 0; addc.u32 %9, %9, 0;\n\t"
-        "add.cc.u32 %1, %1, h0; addc.cc.u32 %2, %2, h1; addc.cc.u32 %3, %3, h2; addc.cc.u32 %4, %4, h3;\n\t"
-        "addc.cc.u32 %5, %5, h4; addc.cc.u32 %6, %6, h5; addc.cc.u32 %7, %7, h6; addc.cc.u32 %8, %8, h7;\n\t"
-        "addc.u32 %9, %9, 0; }"
-        : "+r"(t[0]), "+r"(t[1]), "+r"(t[2]), "+r"(t[3]), "+r"(t[4]), "+r"(t[5]), "+r"(t[6]), "+r"(t[7]), "+r"(t[8]),
-          "+r"(t[9])
-        : "r"(a.w[0]), "r"(a.w[1]), "r"(a.w[2]), "r"(a.w[3]), "r"(a.w[4]), "r"(a.w[5]), "r"(a.w[6]), "r"(a.w[7]),
-          "r"(b));
+// Four wide multiply-adds on one carry chain: the four aligned word pairs
+// (c0,c1) .. (c6,c7) += (x0, x1, x2, x3) * y, the carry out goes into top.  Each
+// mad.lo.cc / madc.hi.cc pair with the same operands is one 32x32+64 multiply-add
+// with carry in and out on the device, so a chain is four multiply instructions
+// and one add.  With LEAD the chain starts with a carry in of (lead != 0).
+#define DPB_FRW_CHAIN_BODY(FIRST, X0, X1, X2, X3)                                      \
+    FIRST ".lo.cc.u32 %0, " X0 ", %9, %0; madc.hi.cc.u32 %1, " X0 ", %9, %1;\n\t"      \
+    "madc.lo.cc.u32 %2, " X1 ", %9, %2; madc.hi.cc.u32 %3, " X1 ", %9, %3;\n\t"        \
+    "madc.lo.cc.u32 %4, " X2 ", %9, %4; madc.hi.cc.u32 %5, " X2 ", %9, %5;\n\t"        \
+    "madc.lo.cc.u32 %6, " X3 ", %9, %6; madc.hi.cc.u32 %7, " X3 ", %9, %7;\n\t"        \
+    "addc.u32 %8, %8, 0;"
+#define DPB_FRW_CHAIN_OUT(c, top)                                                                           \
+    "+r"((c)[0]), "+r"((c)[1]), "+r"((c)[2]), "+r"((c)[3]), "+r"((c)[4]), "+r"((c)[5]), "+r"((c)[6]), \
+        "+r"((c)[7]), "+r"(top)
+
+// c points at the first word of the first pair; x are four words of a
+__device__ __forceinline__ void chain_mul(uint32_t* c, uint32_t& top, uint32_t x0, uint32_t x1, uint32_t x2,
+                                          uint32_t x3, uint32_t y) {
+    asm(DPB_FRW_CHAIN_BODY("mad", "%10", "%11", "%12", "%13")
+        : DPB_FRW_CHAIN_OUT(c, top)
+        : "r"(y), "r"(x0), "r"(x1), "r"(x2), "r"(x3));
+}
+// the same with the even words of the modulus
+__device__ __forceinline__ void chain_mod_even(uint32_t* c, uint32_t& top, uint32_t y) {
+    asm(DPB_FRW_CHAIN_BODY("mad", "0xf0000001", "0x79b97091", "0x8181585d", "0xe131a029")
+        : DPB_FRW_CHAIN_OUT(c, top)
+        : "r"(y));
+}
+// the odd words of the modulus; LEAD: carry in of (lead != 0)
+template <bool LEAD>
+__device__ __forceinline__ void chain_mod_odd(uint32_t* c, uint32_t& top, uint32_t y, uint32_t lead) {
+    if (LEAD) {
+        asm("{ .reg .u32 t;\n\t"
+            "add.cc.u32 t, %10, 0xffffffff;\n\t" DPB_FRW_CHAIN_BODY("madc", "0x43e1f593", "0x2833e848", "0xb85045b6",
+                                                                   "0x30644e72") " }"
+            : DPB_FRW_CHAIN_OUT(c, top)
+            : "r"(y), "r"(lead));
+    } else {
+        asm(DPB_FRW_CHAIN_BODY("mad", "0x43e1f593", "0x2833e848", "0xb85045b6", "0x30644e72")
+            : DPB_FRW_CHAIN_OUT(c, top)
+            : "r"(y));
+    }
 }
 
-// t += m * r with m chosen so that word 0 becomes zero; the caller then drops word 0.
-__device__ __forceinline__ void row_reduce(uint32_t (&t)[10]) {
-    asm("{ .reg .u32 m,l0,l1,l2,l3,l4,l5,l6,l7,h0,h1,h2,h3,h4,h5,h6,h7; .reg .u64 x;\n\t"
-        "mul.lo.u32 m, %0, 0xefffffff;\n\t"
-        "mul.wide.u32 x, m, 0xf0000001; mov.b64 {l0,h0}, x;\n\t"
-        "mul.wide.u32 x, m, 0x43e1f593; mov.b64 {l1,h1}, x;\n\t"
-        "mul.wide.u32 x, m, 0x79b97091; mov.b64 {l2,h2}, x;\n\t"
-        "mul.wide.u32 x, m, 0x2833e848; mov.b64 {l3,h3}, x;\n\t"
-        "mul.wide.u32 x, m, 0x8181585d; mov.b64 {l4,h4}, x;\n\t"
-        "mul.wide.u32 x, m, 0xb85045b6; mov.b64 {l5,h5}, x;\n\t"
-        "mul.wide.u32 x, m, 0xe131a029; mov.b64 {l6,h6}, x;\n\t"
-        "mul.wide.u32 x, m, 0x30644e72; mov.b64 {l7,h7}, x;\n\t"
-        "add.cc.u32 %0, %0, l0; addc.cc.u32 %1, %1, l1; addc.cc.u32 %2, %2, l2; addc.cc.u32 %3, %3, l3;\n\t"
-        "addc.cc.u32 %4, %4, l4; addc.cc.u32 %5, %5, l5; addc.cc.u32 %6, %6, l6; addc.cc.u32 %7, %7, l7;\n\t"
-        "addc.cc.u32 %8, %8, 0; addc.u32 %9, %9, 0;\n\t"
-        "add.cc.u32 %1, %1, h0; addc.cc.u32 %2, %2, h1; addc.cc.u32 %3, %3, h2; addc.cc.u32 %4, %4, h3;\n\t"
-        "addc.cc.u32 %5, %5, h4; addc.cc.u32 %6, %6, h5; addc.cc.u32 %7, %7, h6; addc.cc.u32 %8, %8, h7;\n\t"
-        "addc.u32 %9, %9, 0; }"
-        : "+r"(t[0]), "+r"(t[1]), "+r"(t[2]), "+r"(t[3]), "+r"(t[4]), "+r"(t[5]), "+r"(t[6]), "+r"(t[7]), "+r"(t[8]),
-          "+r"(t[9]));
+// One word of b: the running sum is held as two arrays indexed by absolute word
+// position.  P holds 64-bit pairs that start at positions of the parity of I, Q
+// pairs that start at the other parity; the true sum is P + Q.  Products of the
+// even words of a with b_I start at position I (in P), those of the odd words at
+// I + 1 (in Q), so every multiply-add lands on an aligned pair.  The reduction
+// word m clears position I of the sum: P[I] becomes -Q[I] mod 2^32, and the carry
+// that P[I] + Q[I] sends to position I + 1 is exactly (Q[I] != 0); it enters the
+// odd-word chain of the modulus.  Position I is never looked at again.
+template <int I>
+__device__ __forceinline__ void mont_step(uint32_t* P, uint32_t* Q, const uint32_t* a, uint32_t bi) {
+    chain_mul(P + I, P[I + 8], a[0], a[2], a[4], a[6], bi);
+    chain_mul(Q + I + 1, Q[I + 9], a[1], a[3], a[5], a[7], bi);
+    const uint32_t w = I ? P[I] + Q[I] : P[I];
+    const uint32_t m = w * DPB_FRW_INV;
+    chain_mod_even(P + I, P[I + 8], m);
+    if (I) chain_mod_odd<true>(Q + I + 1, Q[I + 9], m, Q[I]);
+    else chain_mod_odd<false>(Q + I + 1, Q[I + 9], m, 0);
 }
 
 // a < 2r -> a mod r: subtract r; on a borrow add it back through a mask
@@ -114,22 +133,26 @@ __device__ __forceinline__ F8 reduce_once(const F8& a) {
 
 // Montgomery product a * b / 2^256 mod r
 __device__ __forceinline__ F8 mul(const F8& a, const F8& b) {
-    uint32_t t[10];
+    uint32_t E[18], O[18];  // pairs at even / odd positions; only a window of ten words is live at a time
 #pragma unroll
-    for (int i = 0; i < 10; i++) t[i] = 0;
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        row_mac(t, a, b.w[i]);
-        row_reduce(t);
-        // word 0 is zero now: shift down one word
-#pragma unroll
-        for (int j = 0; j < 9; j++) t[j] = t[j + 1];
-        t[9] = 0;
-    }
-    F8 r;
-#pragma unroll
-    for (int i = 0; i < 8; i++) r.w[i] = t[i];
-    return reduce_once(r);  // the running sum stays below 2r (r has two spare top bits)
+    for (int i = 0; i < 18; i++) E[i] = O[i] = 0;
+    mont_step<0>(E, O, a.w, b.w[0]);
+    mont_step<1>(O, E, a.w, b.w[1]);
+    mont_step<2>(E, O, a.w, b.w[2]);
+    mont_step<3>(O, E, a.w, b.w[3]);
+    mont_step<4>(E, O, a.w, b.w[4]);
+    mont_step<5>(O, E, a.w, b.w[5]);
+    mont_step<6>(E, O, a.w, b.w[6]);
+    mont_step<7>(O, E, a.w, b.w[7]);
+    // positions 0..7 of the sum are clear; positions 8..15 hold a value below 2r
+    F8 s;
+    asm("add.cc.u32 %0, %8, %16; addc.cc.u32 %1, %9, %17; addc.cc.u32 %2, %10, %18; addc.cc.u32 %3, %11, %19;\n\t"
+        "addc.cc.u32 %4, %12, %20; addc.cc.u32 %5, %13, %21; addc.cc.u32 %6, %14, %22; addc.u32 %7, %15, %23;"
+        : "=&r"(s.w[0]), "=&r"(s.w[1]), "=&r"(s.w[2]), "=&r"(s.w[3]), "=&r"(s.w[4]), "=&r"(s.w[5]), "=&r"(s.w[6]),
+          "=&r"(s.w[7])
+        : "r"(E[8]), "r"(E[9]), "r"(E[10]), "r"(E[11]), "r"(E[12]), "r"(E[13]), "r"(E[14]), "r"(E[15]), "r"(O[8]),
+          "r"(O[9]), "r"(O[10]), "r"(O[11]), "r"(O[12]), "r"(O[13]), "r"(O[14]), "r"(O[15]));
+    return reduce_once(s);
 }
 
 __device__ __forceinline__ F8 add(const F8& a, const F8& b) {
