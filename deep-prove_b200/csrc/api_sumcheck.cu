@@ -122,13 +122,16 @@ static void launch_fused_gl(dpb_ctx* ctx, const MleDesc* desc, const FoldDesc* f
         }
         const bool base = desc[0].dtype == DPB_GL_BASE;
         if (staged && base) {
+            // three resident blocks per SM leave this kernel the registers it wants
             constexpr size_t sm = Stager<K, 1, 4>::bytes();
-            cudaFuncSetAttribute(v4_eval0_gl<K, true, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
-            v4_eval0_gl<K, true, 4><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, n_pairs, rs, out);
+            const uint32_t grid3 = grid_for(ctx, n_pairs, 3);
+            cudaFuncSetAttribute(v4_eval0_gl<K, true, 4, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+            v4_eval0_gl<K, true, 4, 3><<<grid3, kStageThreads, sm, ctx->stream>>>(ptrs, n_pairs, rs, out);
         } else if (staged) {
             constexpr size_t sm = Stager<K, 2, 3>::bytes();
-            cudaFuncSetAttribute(v4_eval0_gl<K, false, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
-            v4_eval0_gl<K, false, 3><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, n_pairs, rs, out);
+            constexpr int minb = K <= 3 ? 2 : 1;
+            cudaFuncSetAttribute(v4_eval0_gl<K, false, 3, minb>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+            v4_eval0_gl<K, false, 3, minb><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, n_pairs, rs, out);
         } else if (base) {
             v2_eval0<OpsGlBase, K><<<grid, kThreads, 0, ctx->stream>>>(ptrs, n_pairs, rs, out);
         } else {
@@ -152,12 +155,14 @@ static void launch_fused_gl(dpb_ctx* ctx, const MleDesc* desc, const FoldDesc* f
         wc.r1x7 = glw::make_w((uint32_t)c.r1x7, (uint32_t)(c.r1x7 >> 32));
         if (base) {
             constexpr size_t sm = Stager<K, 2, 3>::bytes();
-            cudaFuncSetAttribute(v4_fold_eval_gl<K, true, 3, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
-            v4_fold_eval_gl<K, true, 3, 1><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, wc, n_pairs, rs, out);
+            constexpr int minb = K <= 3 ? 2 : 1;
+            cudaFuncSetAttribute(v4_fold_eval_gl<K, true, 3, minb>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+            v4_fold_eval_gl<K, true, 3, minb><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, wc, n_pairs, rs, out);
         } else {
             constexpr size_t sm = Stager<K, 4, 2>::bytes();
-            cudaFuncSetAttribute(v4_fold_eval_gl<K, false, 2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
-            v4_fold_eval_gl<K, false, 2, 1><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, wc, n_pairs, rs, out);
+            constexpr int minb = K <= 3 ? 2 : 1;
+            cudaFuncSetAttribute(v4_fold_eval_gl<K, false, 2, minb>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+            v4_fold_eval_gl<K, false, 2, minb><<<grid, kStageThreads, sm, ctx->stream>>>(ptrs, wc, n_pairs, rs, out);
         }
         return;
     }

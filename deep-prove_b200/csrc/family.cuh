@@ -9,17 +9,52 @@
 #include "../../include/dpb.h"
 #include "field_bn254.cuh"
 #include "field_gl.cuh"
+#if defined(__CUDACC__)
+#include "gl_words.cuh"
+#endif
 
 namespace dpb {
+
+#if defined(__CUDACC__)
+// canonical extension elements to and from the word-level form of gl_words.cuh
+__device__ __forceinline__ glw::W2 gl2_words(const Gl2& a) {
+    glw::W2 r;
+    r.c0 = glw::make_w((uint32_t)a.c0, (uint32_t)(a.c0 >> 32));
+    r.c1 = glw::make_w((uint32_t)a.c1, (uint32_t)(a.c1 >> 32));
+    return r;
+}
+__device__ __forceinline__ Gl2 gl2_canonical(const glw::W2& a) {
+    return gl2_make(glw::to_u64(glw::canon(a.c0)), glw::to_u64(glw::canon(a.c1)));
+}
+#endif
 
 struct GlFam {
     typedef Gl2 E;
     static constexpr int kChalDtype = DPB_GL_EXT;
     DPB_HD static E zero() { return gl2_zero(); }
     DPB_HD static E one() { return gl2_one(); }
-    DPB_HD static E add(const E& a, const E& b) { return gl2_add(a, b); }
-    DPB_HD static E sub(const E& a, const E& b) { return gl2_sub(a, b); }
-    DPB_HD static E mul(const E& a, const E& b) { return gl2_mul(a, b); }
+    // on the device the operations run on the word-level arithmetic; results are canonical either way
+    DPB_HD static E add(const E& a, const E& b) {
+#if defined(__CUDA_ARCH__)
+        return gl2_canonical(glw::add_c(gl2_words(a), gl2_words(b)));
+#else
+        return gl2_add(a, b);
+#endif
+    }
+    DPB_HD static E sub(const E& a, const E& b) {
+#if defined(__CUDA_ARCH__)
+        return gl2_canonical(glw::sub_c(gl2_words(a), gl2_words(b)));
+#else
+        return gl2_sub(a, b);
+#endif
+    }
+    DPB_HD static E mul(const E& a, const E& b) {
+#if defined(__CUDA_ARCH__)
+        return gl2_canonical(glw::mul(gl2_words(a), gl2_words(b)));
+#else
+        return gl2_mul(a, b);
+#endif
+    }
     DPB_HD static E neg(const E& a) { return gl2_neg(a); }
     DPB_HD static bool is_one(const E& a) { return a.c0 == 1 && a.c1 == 0; }
     DPB_HD static bool is_zero(const E& a) { return a.c0 == 0 && a.c1 == 0; }

@@ -10,7 +10,7 @@ namespace dpb {
 struct OpsWBase {
     typedef GlFam F;
     typedef glw::W T;
-    typedef glw::A5 Acc;
+    typedef glw::A8 Acc;
     __device__ __forceinline__ static T sub_c(const T& a, const T& c) { return glw::sub_c(a, c); }
     __device__ __forceinline__ static T add_c(const T& a, const T& c) { return glw::add_c(a, c); }
     __device__ __forceinline__ static T mul(const T& a, const T& b) { return glw::mul(a, b); }
@@ -25,7 +25,7 @@ struct OpsWExt {
     typedef GlFam F;
     typedef glw::W2 T;
     struct Acc {
-        glw::A5 s0, s1;
+        glw::A8 s0, s1;
     };
     __device__ __forceinline__ static T sub_c(const T& a, const T& c) { return glw::sub_c(a, c); }
     __device__ __forceinline__ static T add_c(const T& a, const T& c) { return glw::add_c(a, c); }
@@ -54,8 +54,8 @@ __device__ __forceinline__ glw::W2 as_w2(const uint4& v) {
 }
 
 // Round 0, staged.
-template <int K, bool BASE, int STAGES>
-__global__ void __launch_bounds__(kStageThreads)
+template <int K, bool BASE, int STAGES, int MINB>
+__global__ void __launch_bounds__(kStageThreads, MINB)
     v4_eval0_gl(V2Ptrs<K> ptrs, uint64_t n_pairs, ReduceScratch<GlFam> rs, Gl2* out) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int CH = BASE ? 1 : 2;

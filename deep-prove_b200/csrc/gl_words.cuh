@@ -3,11 +3,14 @@
 // Instruction counts measured on sm_100a show that a 64-bit formulation pays
 // for packing and unpacking register pairs around every multiply: the C
 // version of a 64x64 product issues ten multiply-pipe instructions where four
-// are needed.  The integer pipes dispatch an IADD3 per cycle but an IMAD (or
-// LOP3 / SHF / ISETP) every other cycle, so the cheapest code is: exactly four
-// mul.wide.u32 per product, and everything else as carry-chained 32-bit adds,
-// with corrections driven by the carry flag and a mask — no compares, no
-// predicates, no shifts.
+// are needed.  Measured issue costs per warp instruction: a 32x32->64 multiply
+// (with or without a 64-bit addend and carry) about four cycles, a 32-bit
+// multiply, logic op, shift or compare about two, a carry-chained add about
+// one.  So the cheapest code is: exactly four wide multiplies per product, the
+// additions of a sum of products folded into the multiplies' addends
+// (mad.lo.cc / madc.hi.cc pairs on aligned word pairs become one instruction),
+// everything else carry-chained 32-bit adds with corrections driven by the
+// carry flag and a mask — no compares, no predicates, no shifts.
 //
 // Values are "loose" (any 64-bit representative of the residue) unless a
 // comment says canonical.  p = 2^64 - 2^32 + 1, EPS = 2^32 - 1 = 2^64 mod p,
@@ -64,22 +67,48 @@ __device__ __forceinline__ W canon(const W& a) {
     return d;
 }
 
-// 160-bit accumulator of 128-bit products: five words, little-endian.
+// 160-bit value, five words little-endian: what a reduction consumes.
 struct A5 {
     uint32_t w0, w1, w2, w3, w4;
 };
-__device__ __forceinline__ A5 acc_zero() {
-    A5 a;
-    a.w0 = a.w1 = a.w2 = a.w3 = a.w4 = 0;
+
+// Accumulator of 128-bit products, split so that every 64-bit partial product
+// is added to an aligned word pair: e0..e4 hold the pairs at word positions
+// (0,1), (2,3) and the carries out of them; o1..o3 hold the pair at (1,2) and
+// its carries.  The value is e0 + 2^32 e1 + 2^64 e2 + 2^96 e3 + 2^128 e4
+// + 2^32 o1 + 2^64 o2 + 2^96 o3.
+struct A8 {
+    uint32_t e0, e1, e2, e3, e4, o1, o2, o3;
+};
+__device__ __forceinline__ A8 acc_zero() {
+    A8 a;
+    a.e0 = a.e1 = a.e2 = a.e3 = a.e4 = a.o1 = a.o2 = a.o3 = 0;
     return a;
 }
 // accumulator that starts at the value v
-__device__ __forceinline__ A5 acc_from(const W& v) {
-    A5 a;
-    a.w0 = v.lo;
-    a.w1 = v.hi;
-    a.w2 = a.w3 = a.w4 = 0;
+__device__ __forceinline__ A8 acc_from(const W& v) {
+    A8 a = acc_zero();
+    a.e0 = v.lo;
+    a.e1 = v.hi;
     return a;
+}
+// acc += a * b: four wide multiply-adds and three carry adds
+__device__ __forceinline__ void acc_mac(A8& s, const W& a, const W& b) {
+    asm("mad.lo.cc.u32 %0, %8, %10, %0; madc.hi.cc.u32 %1, %8, %10, %1;\n\t"
+        "madc.lo.cc.u32 %2, %9, %11, %2; madc.hi.cc.u32 %3, %9, %11, %3; addc.u32 %4, %4, 0;\n\t"
+        "mad.lo.cc.u32 %5, %8, %11, %5; madc.hi.cc.u32 %6, %8, %11, %6; addc.u32 %7, %7, 0;\n\t"
+        "mad.lo.cc.u32 %5, %9, %10, %5; madc.hi.cc.u32 %6, %9, %10, %6; addc.u32 %7, %7, 0;"
+        : "+r"(s.e0), "+r"(s.e1), "+r"(s.e2), "+r"(s.e3), "+r"(s.e4), "+r"(s.o1), "+r"(s.o2), "+r"(s.o3)
+        : "r"(a.lo), "r"(a.hi), "r"(b.lo), "r"(b.hi));
+}
+// the accumulator as one 160-bit value
+__device__ __forceinline__ A5 acc_merge(const A8& s) {
+    A5 r;
+    r.w0 = s.e0;
+    asm("add.cc.u32 %0, %4, %8; addc.cc.u32 %1, %5, %9; addc.cc.u32 %2, %6, %10; addc.u32 %3, %7, 0;"
+        : "=&r"(r.w1), "=&r"(r.w2), "=&r"(r.w3), "=&r"(r.w4)
+        : "r"(s.e1), "r"(s.e2), "r"(s.e3), "r"(s.e4), "r"(s.o1), "r"(s.o2), "r"(s.o3));
+    return r;
 }
 
 // The 128-bit product a * b as four words: four 32x32 products and six adds.
@@ -101,14 +130,6 @@ __device__ __forceinline__ P4 prod(const W& a, const W& b) {
         : "r"(a.lo), "r"(a.hi), "r"(b.lo), "r"(b.hi));
     return r;
 }
-__device__ __forceinline__ void acc_add(A5& s, const P4& p) {
-    asm("add.cc.u32 %0, %0, %5; addc.cc.u32 %1, %1, %6; addc.cc.u32 %2, %2, %7; addc.cc.u32 %3, %3, %8; addc.u32 %4, %4, 0;"
-        : "+r"(s.w0), "+r"(s.w1), "+r"(s.w2), "+r"(s.w3), "+r"(s.w4)
-        : "r"(p.x0), "r"(p.x1), "r"(p.x2), "r"(p.x3));
-}
-// acc += a * b
-__device__ __forceinline__ void acc_mac(A5& s, const W& a, const W& b) { acc_add(s, prod(a, b)); }
-
 // Loose residue of the accumulator.  With x = w0 + 2^32 w1, the value is
 //   x + 2^64 w2 + 2^96 w3 + 2^128 w4 = x - (w3 + 2^32 w4) + w2 * EPS   (mod p).
 // w4 counts overflows of a thread's sums and stays far below 2^31, so
@@ -126,6 +147,8 @@ __device__ __forceinline__ W acc_reduce(const A5& s) {
         : "r"(s.w0), "r"(s.w1), "r"(s.w2), "r"(s.w3), "r"(s.w4));
     return d;
 }
+
+__device__ __forceinline__ W acc_reduce(const A8& s) { return acc_reduce(acc_merge(s)); }
 
 // a * b as a loose residue
 __device__ __forceinline__ W mul(const W& a, const W& b) {
@@ -172,7 +195,7 @@ __device__ __forceinline__ W2 sub_c(const W2& a, const W2& c) {
 }
 // (a0 + a1 X)(b0 + b1 X): c0 = a0 b0 + (7 a1) b1, c1 = a0 b1 + a1 b0; two lazy sums, two reductions
 __device__ __forceinline__ W2 mul(const W2& a, const W2& b) {
-    A5 s0 = acc_zero(), s1 = acc_zero();
+    A8 s0 = acc_zero(), s1 = acc_zero();
     acc_mac(s0, a.c0, b.c0);
     acc_mac(s0, mul7(a.c1), b.c1);
     acc_mac(s1, a.c0, b.c1);
@@ -190,7 +213,7 @@ struct Chal {
 // canonical a0 + r (a1 - a0), a0 and a1 canonical extension elements
 __device__ __forceinline__ W2 fold_ext(const W2& a0, const W2& a1, const Chal& r) {
     const W2 d = sub_c(a1, a0);
-    A5 s0 = acc_from(a0.c0), s1 = acc_from(a0.c1);
+    A8 s0 = acc_from(a0.c0), s1 = acc_from(a0.c1);
     acc_mac(s0, d.c0, r.r0);
     acc_mac(s0, d.c1, r.r1x7);
     acc_mac(s1, d.c0, r.r1);
@@ -203,7 +226,7 @@ __device__ __forceinline__ W2 fold_ext(const W2& a0, const W2& a1, const Chal& r
 // canonical a0 + r (a1 - a0), a0 and a1 canonical base elements
 __device__ __forceinline__ W2 fold_base(const W& a0, const W& a1, const Chal& r) {
     const W d = sub_c(a1, a0);
-    A5 s0 = acc_from(a0), s1 = acc_zero();
+    A8 s0 = acc_from(a0), s1 = acc_zero();
     acc_mac(s0, d, r.r0);
     acc_mac(s1, d, r.r1);
     W2 f;
