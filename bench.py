@@ -33,9 +33,16 @@ if ROOT not in sys.path:
 GL_MOD = 2**64 - 2**32 + 1
 FALLBACK_HBM_GBS = 6650.0
 
-# DRAM traffic of the dominant launch from the ncu capture summarised under
-# profiles/ (bytes per table entry of the launch's input); None until captured.
-NCU_TRAFFIC_BYTES_PER_INPUT_ENTRY = None
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per table entry of a
+# launch's input, from the ncu capture at 2^24 summarised in
+# profiles/sumcheck_goldilocks_product3_2p24_fused_rounds.md.  Traffic grows in
+# proportion to the entries processed, so a full launch is this figure times
+# its input entries.  Keyed by (field, profile label, round).
+NCU_TRAFFIC_BYTES_PER_INPUT_ENTRY = {
+    ("gl", "fused_eval0<base>", 0): (402.744064e6 + 6.582016e6) / (3 << 24),
+    ("gl", "fused_fold_eval<base>", 1): (402.845952e6 + 359.348736e6) / (3 << 24),
+    ("gl", "fused_fold_eval", 2): (402.789632e6 + 169.018880e6) / (3 << 23),
+}
 
 
 def alg_bytes(field, n, k=3):
@@ -296,8 +303,9 @@ def run_ours(args):
         per_launch_ms = top["total_ms"] / top["launches"]
         ach = top["alg_bytes_per_launch"] / (per_launch_ms * 1e-3) / 1e9
         traffic = None
-        if NCU_TRAFFIC_BYTES_PER_INPUT_ENTRY is not None:
-            traffic = NCU_TRAFFIC_BYTES_PER_INPUT_ENTRY * 3 * (1 << (n - max(top["round"] - 1, 0)))
+        per_entry = NCU_TRAFFIC_BYTES_PER_INPUT_ENTRY.get((field, top["kernel"], top["round"]))
+        if per_entry is not None:
+            traffic = per_entry * 3 * (1 << (n - max(top["round"] - 1, 0)))
         roofline = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
                     "traffic": traffic, "kernel": top["kernel"], "round": top["round"],
                     "launch_ms": per_launch_ms, "alg_bytes_per_launch": top["alg_bytes_per_launch"],
