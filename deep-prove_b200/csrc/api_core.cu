@@ -216,6 +216,12 @@ int dpb_init(int device, dpb_ctx** out) {
     DPB_CUDA(cudaMalloc(&ctx->stage_dev, ctx->stage_bytes));
     DPB_CUDA(cudaEventCreate(&ctx->prof_ev[0]));
     DPB_CUDA(cudaEventCreate(&ctx->prof_ev[1]));
+    DPB_CUDA(cudaHostAlloc(&ctx->tail_box_host, 8192, cudaHostAllocMapped));
+    DPB_CUDA(cudaHostGetDevicePointer(&ctx->tail_box_dev, ctx->tail_box_host, 0));
+    memset(ctx->tail_box_host, 0, 8192);
+    DPB_CUDA(cudaStreamCreateWithFlags(&ctx->tail_stream, cudaStreamNonBlocking));
+    DPB_CUDA(cudaEventCreateWithFlags(&ctx->tail_ev[0], cudaEventDisableTiming));
+    DPB_CUDA(cudaEventCreateWithFlags(&ctx->tail_ev[1], cudaEventDisableTiming));
     *out = ctx;
     return DPB_OK;
 }
@@ -224,6 +230,11 @@ void dpb_shutdown(dpb_ctx* ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
+    cudaStreamSynchronize(ctx->tail_stream);
+    cudaStreamDestroy(ctx->tail_stream);
+    cudaEventDestroy(ctx->tail_ev[0]);
+    cudaEventDestroy(ctx->tail_ev[1]);
+    cudaFreeHost(ctx->tail_box_host);
     cudaFree(ctx->partials);
     cudaFree(ctx->counter);
     cudaFree(ctx->stage_dev);
@@ -241,6 +252,13 @@ int dpb_sync(dpb_ctx* ctx) {
 }
 
 void* dpb_stream(dpb_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+
+int dpb_resident_rounds(dpb_ctx* ctx, int enable, uint32_t wait_ms) {
+    if (!ctx) return fail(DPB_EINVAL, "null context");
+    ctx->tail_enabled = enable != 0;
+    if (wait_ms) ctx->tail_wait_ns = (unsigned long long)wait_ms * 1000000ull;
+    return DPB_OK;
+}
 
 int dpb_profile_enable(dpb_ctx* ctx, int on) {
     if (!ctx) return fail(DPB_EINVAL, "null context");

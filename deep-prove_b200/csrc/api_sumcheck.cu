@@ -1,20 +1,25 @@
 // C ABI: the sumcheck prover state machine (begin / round / finish).
 //
 // All device buffers and the per-round table descriptors are laid out when the
-// sumcheck begins, so a round is: [fold with the previous challenge] + one
-// evaluation launch + one stream synchronisation.  The evaluation kernel's
-// last block writes the round polynomial straight into mapped host memory.
+// sumcheck begins, so a round is one launch that binds the previous challenge
+// and evaluates (two launches on the fallback path for very many tables).  The
+// kernel's last block writes the round polynomial straight into mapped host
+// memory and raises a flag the host polls.
 #include <atomic>
 #include <chrono>
+#include <mutex>
 
 #include "common.cuh"
 #include "fused_kernels.cuh"
 #include "fused_v2.cuh"
 #include "fused_v3.cuh"
 #include "fused_v4.cuh"
+#include "generic_round.cuh"
 #include "comm.cuh"
 
 namespace dpb {
+
+constexpr int kOnePassMaxSmem = 200 * 1024;  // dynamic shared memory the one-pass generic rounds may use
 
 struct MleTrack {
     const void* orig;
@@ -42,6 +47,23 @@ struct dpb_sc {
     void* d_terms = nullptr;
     void* d_final = nullptr;  // k challenge elements
     int fused_shape = 0;      // see fused_kernels.cuh
+    // one-pass generic rounds (generic_round.cuh); off when the tables' slots do not fit in shared memory
+    bool one_pass = false;       // large generic rounds run sc_round_generic
+    bool has_prog = false;       // d_rtab / d_groups / d_prog are laid out (every shape that fits)
+    uint32_t tail_start = ~0u;   // first round the resident last-rounds kernel may take over
+    bool tail_active = false;    // that kernel is running for this sumcheck
+    uint32_t n_prog_terms = 0;
+    bool tail_prog_in_smem = false;
+    uint32_t tail_slots_offset = 0;
+    size_t tail_smem = 0;
+    RoundTab* d_rtab = nullptr;  // [n][k]
+    void* d_groups = nullptr;
+    void* d_prog = nullptr;
+    uint32_t n_groups = 0;
+    uint32_t op_threads = 0;
+    size_t op_smem = 0;
+    alignas(16) uint8_t prev_evals[7 * 32] = {0};  // previous round message (one-pass rounds derive s(1) from it)
+    alignas(16) uint8_t lag_w[7 * 32] = {0};       // interpolation weights for the nodes 0..d
     alignas(16) uint8_t prev_coeffs[5 * 32] = {0};  // previous round polynomial, low to high (fused rounds)
     // sharded sumchecks: the local part has n variables, the whole sumcheck n + log2_ranks
     uint32_t log2_ranks = 0;
@@ -102,6 +124,260 @@ static void launch_eval(dpb_sc* sc, uint32_t round, uint64_t n_pairs) {
     sc_eval_generic<F, D><<<grid_for(ctx, n_pairs, 4), kThreads, 0, ctx->stream>>>(
         sc->d_desc + (size_t)round * sc->k, (const TermDev<F>*)sc->d_terms, sc->n_terms, n_pairs,
         reduce_scratch<F>(ctx), (typename F::E*)ctx->round_out);
+}
+
+template <class F, int D>
+static int launch_one_pass(dpb_sc* sc, uint32_t round, uint64_t n_pairs, const typename F::E& r) {
+    dpb_ctx* ctx = sc->ctx;
+    const bool skip = round > 0;
+    if (skip)
+        DPB_CUDA(cudaFuncSetAttribute(sc_round_generic<F, D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kOnePassMaxSmem));
+    else
+        DPB_CUDA(cudaFuncSetAttribute(sc_round_generic<F, D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kOnePassMaxSmem));
+    uint64_t blocks = (n_pairs + sc->op_threads - 1) / sc->op_threads;
+    const uint64_t cap = (uint64_t)ctx->sm_count * (kOnePassMaxSmem / sc->op_smem ? kOnePassMaxSmem / sc->op_smem : 1);
+    if (blocks > cap) blocks = cap;
+    if (blocks > ctx->max_blocks) blocks = ctx->max_blocks;
+    const RoundTab* tabs = sc->d_rtab + (size_t)round * sc->k;
+    if (skip)
+        sc_round_generic<F, D, true><<<(uint32_t)blocks, sc->op_threads, sc->op_smem, ctx->stream>>>(
+            tabs, sc->k, (const ProgGroup*)sc->d_groups, sc->n_groups, (const ProgTerm<F>*)sc->d_prog, r, n_pairs,
+            reduce_scratch<F>(ctx), (typename F::E*)ctx->round_out);
+    else
+        sc_round_generic<F, D, false><<<(uint32_t)blocks, sc->op_threads, sc->op_smem, ctx->stream>>>(
+            tabs, sc->k, (const ProgGroup*)sc->d_groups, sc->n_groups, (const ProgTerm<F>*)sc->d_prog, r, n_pairs,
+            reduce_scratch<F>(ctx), (typename F::E*)ctx->round_out);
+    return DPB_OK;
+}
+
+// Lays out what the one-pass rounds need: per-round table descriptors that say
+// which tables are bound inside the round's kernel, and the grouped term program.
+template <class F>
+static int setup_one_pass(dpb_sc* sc, const dpb_term* terms) {
+    typedef typename F::E E;
+    dpb_ctx* ctx = sc->ctx;
+    const size_t per_thread = (size_t)sc->k * 2 * sizeof(E);
+    uint32_t threads = 256;
+    while (threads >= 64 && per_thread * threads > (size_t)kOnePassMaxSmem) threads /= 2;
+    if (threads < 64) return DPB_OK;  // too many tables: the two-pass kernels run
+    sc->op_threads = threads;
+    sc->op_smem = per_thread * threads;
+    std::vector<RoundTab> rt((size_t)sc->n * sc->k);
+    for (uint32_t i = 0; i < sc->n; i++) {
+        for (uint32_t j = 0; j < sc->k; j++) {
+            const MleDesc& md = sc->h_desc[(size_t)i * sc->k + j];
+            RoundTab& t = rt[(size_t)i * sc->k + j];
+            t.in = md.ptr;
+            t.out = nullptr;
+            t.dtype_in = md.dtype;
+            t.shift = md.shift;
+            if (i >= 1) {
+                const void* pptr;
+                int pdt;
+                bool pactive;
+                table_at_round(sc, j, i - 1, &pptr, &pdt, &pactive);
+                if (pactive) {
+                    t.in = pptr;
+                    t.dtype_in = pdt;
+                    t.out = (void*)md.ptr;
+                }
+            }
+        }
+    }
+    std::vector<ProgGroup> groups;
+    std::vector<ProgTerm<F>> prog;
+    compile_program<F>(terms, sc->n_terms, sc->k, groups, prog);
+    sc->n_groups = (uint32_t)groups.size();
+    DPB_TRY(device_alloc(ctx, rt.size() * sizeof(RoundTab), (void**)&sc->d_rtab));
+    DPB_TRY(device_alloc(ctx, groups.size() * sizeof(ProgGroup), &sc->d_groups));
+    DPB_TRY(device_alloc(ctx, prog.size() * sizeof(ProgTerm<F>), &sc->d_prog));
+    DPB_CUDA(cudaMemcpyAsync(sc->d_rtab, rt.data(), rt.size() * sizeof(RoundTab), cudaMemcpyHostToDevice, ctx->stream));
+    DPB_CUDA(cudaMemcpyAsync(sc->d_groups, groups.data(), groups.size() * sizeof(ProgGroup), cudaMemcpyHostToDevice,
+                             ctx->stream));
+    DPB_CUDA(cudaMemcpyAsync(sc->d_prog, prog.data(), prog.size() * sizeof(ProgTerm<F>), cudaMemcpyHostToDevice,
+                             ctx->stream));
+    // the vectors are pageable: the copies have been staged when the synchronisation returns
+    DPB_CUDA(cudaStreamSynchronize(ctx->stream));
+    // interpolation weights per degree, computed once per process (field inversions are slow on the host)
+    static E weights[7][7];
+    static bool have[7] = {false, false, false, false, false, false, false};
+    static std::mutex mu;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!have[sc->d]) {
+            lagrange_weights<F>((int)sc->d, weights[sc->d]);
+            have[sc->d] = true;
+        }
+        memcpy(sc->lag_w, weights[sc->d], (sc->d + 1) * sizeof(E));
+    }
+    sc->has_prog = true;
+    sc->one_pass = sc->fused_shape == kFusedNone;
+    sc->n_prog_terms = (uint32_t)prog.size();
+    if (sc->k <= kTailMaxTables) {
+        // shared memory of the resident kernel: [program copy | round descriptors | slots or sum tree]
+        const size_t prog_bytes = prog.size() * sizeof(ProgTerm<F>) + groups.size() * sizeof(ProgGroup);
+        sc->tail_prog_in_smem = prog_bytes <= (size_t)kTailProgBytes;
+        size_t off = sc->tail_prog_in_smem ? prog_bytes : 0;
+        off = (off + 15) & ~(size_t)15;
+        off += 2 * (size_t)sc->k * sizeof(RoundTab);  // descriptors of the current and the next round
+        off = (off + 15) & ~(size_t)15;
+        sc->tail_slots_offset = (uint32_t)off;
+        // pairs per round the kernel can take: two items per thread in the evaluation phase, and the slots must fit
+        uint64_t max_pairs = 256;
+        while (max_pairs * (sc->d + 1) > 2 * (uint64_t)kTailThreads) max_pairs >>= 1;
+        const size_t per_pair = std::max<size_t>((size_t)sc->k * 2, sc->d + 1) * sizeof(E);
+        while (max_pairs >= 1 && off + per_pair * max_pairs > (size_t)kOnePassMaxSmem) max_pairs >>= 1;
+        if (max_pairs >= 1) {
+            sc->tail_smem = off + per_pair * max_pairs;
+            uint32_t i = 0;
+            while (i < sc->n && (1ull << (sc->n - i - 1)) > max_pairs) i++;
+            sc->tail_start = i;
+        }
+    }
+    return DPB_OK;
+}
+
+// ---- resident last-rounds kernel: host side -------------------------------------
+
+
+// Polls the mailbox until `ready` holds; bounded, and the stream is queried now and then so that a
+// kernel that died or returned early surfaces as an error.
+template <class Ready>
+static int tail_wait_host(dpb_ctx* ctx, TailBox* box, Ready ready) {
+    uint64_t spins = 0;
+    std::chrono::steady_clock::time_point t0;
+    while (!ready()) {
+        if (box->status == 2) return fail(DPB_ETIMEOUT, "the resident round kernel gave up waiting for a challenge");
+        if ((++spins & 0xFFF) == 0) {
+            cudaError_t e = cudaStreamQuery(ctx->tail_stream);
+            if (e != cudaSuccess && e != cudaErrorNotReady)
+                return fail(DPB_ECUDA, "resident round kernel: %s", cudaGetErrorString(e));
+            if (e == cudaSuccess && box->status != 2 && !ready())
+                return fail(DPB_ECUDA, "the resident round kernel returned without a result (%s)",
+                            cudaGetErrorString(cudaGetLastError()));
+            if (spins == 0x1000) t0 = std::chrono::steady_clock::now();
+            else if (std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() > 120.0)
+                return fail(DPB_ETIMEOUT, "the resident round kernel did not answer within 120 s");
+        }
+    }
+    std::atomic_thread_fence(std::memory_order_acquire);
+    return DPB_OK;
+}
+
+template <class F, int D>
+static int launch_tail(dpb_sc* sc, uint32_t round, const typename F::E& r) {
+    dpb_ctx* ctx = sc->ctx;
+    DPB_CUDA(cudaFuncSetAttribute(sc_tail_generic<F, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, kOnePassMaxSmem));
+    sc_tail_generic<F, D><<<1, kTailThreads, sc->tail_smem, ctx->tail_stream>>>(
+        sc->d_rtab, sc->k, (const ProgGroup*)sc->d_groups, sc->n_groups, (const ProgTerm<F>*)sc->d_prog,
+        sc->n_prog_terms, r, round, sc->n, (TailBox*)ctx->tail_box_dev, ctx->tail_wait_ns, sc->tail_prog_in_smem ? 1u : 0u,
+        sc->tail_slots_offset);
+    DPB_CUDA(cudaGetLastError());
+    return DPB_OK;
+}
+
+// the challenge as chunks: data first, then the sequence numbers
+template <class E>
+static void tail_post(TailBox* box, const void* chal, uint32_t seq) {
+    const uint64_t* w = (const uint64_t*)chal;
+    constexpr int W8 = sizeof(E) / 8;
+    for (int i = 0; i < W8; i++) ((volatile TailChunk*)box->chal)[i].data = w[i];
+    std::atomic_thread_fence(std::memory_order_release);
+    for (int i = 0; i < W8; i++) ((volatile TailChunk*)box->chal)[i].seq = seq;
+}
+// element `idx` of a chunk array, once every chunk of it carries `seq`
+template <class E>
+static bool tail_take(const TailChunk* base, uint32_t idx, uint32_t seq, E* out) {
+    constexpr int W8 = sizeof(E) / 8;
+    const volatile TailChunk* c = (const volatile TailChunk*)base + (size_t)idx * W8;
+    uint64_t* w = (uint64_t*)out;
+    for (int i = 0; i < W8; i++) {
+        if (c[i].seq != seq) return false;
+        std::atomic_thread_fence(std::memory_order_acquire);
+        w[i] = c[i].data;
+    }
+    return true;
+}
+
+// Round i through the resident kernel: start it (first use) or post the challenge
+// that ends round i - 1, then wait for the sums of round i.
+template <class F>
+static int tail_round(dpb_sc* sc, uint32_t i, const typename F::E& r, typename F::E* raw) {
+    typedef typename F::E E;
+    dpb_ctx* ctx = sc->ctx;
+    TailBox* box = (TailBox*)ctx->tail_box_host;
+    if (!sc->tail_active) {
+        memset(box, 0, sizeof(TailBox));  // sequence numbers of an earlier sumcheck must not be mistaken for ours
+        std::atomic_thread_fence(std::memory_order_seq_cst);
+        // the kernel runs on its own stream, after everything this context has queued so far
+        DPB_CUDA(cudaEventRecord(ctx->tail_ev[0], ctx->stream));
+        DPB_CUDA(cudaStreamWaitEvent(ctx->tail_stream, ctx->tail_ev[0], 0));
+        int rc;
+        switch (sc->d) {
+            case 1: rc = launch_tail<F, 1>(sc, i, r); break;
+            case 2: rc = launch_tail<F, 2>(sc, i, r); break;
+            case 3: rc = launch_tail<F, 3>(sc, i, r); break;
+            case 4: rc = launch_tail<F, 4>(sc, i, r); break;
+            case 5: rc = launch_tail<F, 5>(sc, i, r); break;
+            case 6: rc = launch_tail<F, 6>(sc, i, r); break;
+            default: return fail(DPB_EINVAL, "degree %u not supported", sc->d);
+        }
+        if (rc != DPB_OK) return rc;
+        DPB_CUDA(cudaEventRecord(ctx->tail_ev[1], ctx->tail_stream));
+        sc->tail_active = true;
+        ctx->tail_owner = sc;
+    } else {
+        tail_post<E>(box, &r, i);
+    }
+    const uint32_t want = i + 1;
+    uint32_t x = 0;  // sums taken so far; the sum at 1 is not sent after round 0
+    DPB_TRY(tail_wait_host(ctx, box, [&] {
+        while (x <= sc->d) {
+            if (i > 0 && x == 1) {
+                x++;
+                continue;
+            }
+            if (!tail_take<E>(box->evals, x, want, &raw[x])) return false;
+            x++;
+        }
+        return true;
+    }));
+    return DPB_OK;
+}
+
+// Posts the last challenge, collects the final evaluations and releases the kernel's slot.
+template <class F>
+static int tail_finish(dpb_sc* sc, const void* last_challenge, void* out) {
+    typedef typename F::E E;
+    dpb_ctx* ctx = sc->ctx;
+    TailBox* box = (TailBox*)ctx->tail_box_host;
+    tail_post<E>(box, last_challenge, sc->n);
+    uint32_t j = 0;
+    int rc = tail_wait_host(ctx, box, [&] {
+        while (j < sc->k) {
+            if (!tail_take<E>(box->finals, j, sc->n + 1, (E*)out + j)) return false;
+            j++;
+        }
+        return true;
+    });
+    // later work of this context (frees, the next sumcheck) is ordered after the kernel's end
+    cudaStreamWaitEvent(ctx->stream, ctx->tail_ev[1], 0);
+    sc->tail_active = false;
+    ctx->tail_owner = nullptr;
+    return rc;
+}
+
+// A sumcheck that is dropped before its last round: tell the kernel to leave and wait for it.
+static void tail_abort(dpb_sc* sc) {
+    dpb_ctx* ctx = sc->ctx;
+    TailBox* box = (TailBox*)ctx->tail_box_host;
+    for (int i = 0; i < 4; i++) ((volatile TailChunk*)box->chal)[i].seq = kTailAbort;
+    std::atomic_thread_fence(std::memory_order_seq_cst);
+    cudaStreamSynchronize(ctx->tail_stream);  // bounded by the kernel's own wait limit
+    sc->tail_active = false;
+    ctx->tail_owner = nullptr;
 }
 
 // Fused product rounds (fused_v2.cuh).  The kernels leave SAMPLES of the round
@@ -241,14 +517,36 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
     // unsharded rounds signal completion through a flag in mapped host memory that the host polls
     ctx->done_seq++;
     ctx->done_flag_dev = sharded ? nullptr : ctx->flag_dev;
-    if (ctx->profile) DPB_CUDA(cudaEventRecord(ctx->prof_ev[0], ctx->stream));
+    // the last rounds go to the resident kernel (one per context at a time; not while profiling per launch)
+    const bool use_tail = sc->tail_active || (sc->has_prog && ctx->tail_enabled && !sharded && !ctx->profile &&
+                                              i >= sc->tail_start && ctx->tail_owner == nullptr);
+    const bool profiled = ctx->profile && !use_tail;
+    E raw[kMaxAcc];
+    if (profiled) DPB_CUDA(cudaEventRecord(ctx->prof_ev[0], ctx->stream));
     bool done = false;
-    if (sc->fused_shape == kFusedProduct) {
+    if (use_tail) {
+        DPB_TRY(tail_round<F>(sc, i, r, raw));
+    } else if (sc->fused_shape == kFusedProduct) {
         launch_fused(ctx, sc->h_desc.data() + (size_t)i * sc->k, i > 0 ? sc->h_fold.data() + (size_t)i * sc->k : nullptr,
                      sc->k, i, r, n_pairs);
         done = true;
     }
-    if (!done) {
+    bool one_pass = use_tail;
+    if (!use_tail && !done && sc->one_pass) {
+        int rc = DPB_OK;
+        switch (sc->d) {
+            case 1: rc = launch_one_pass<F, 1>(sc, i, n_pairs, r); break;
+            case 2: rc = launch_one_pass<F, 2>(sc, i, n_pairs, r); break;
+            case 3: rc = launch_one_pass<F, 3>(sc, i, n_pairs, r); break;
+            case 4: rc = launch_one_pass<F, 4>(sc, i, n_pairs, r); break;
+            case 5: rc = launch_one_pass<F, 5>(sc, i, n_pairs, r); break;
+            case 6: rc = launch_one_pass<F, 6>(sc, i, n_pairs, r); break;
+            default: return fail(DPB_EINVAL, "degree %u not supported", sc->d);
+        }
+        if (rc != DPB_OK) return rc;
+        one_pass = true;
+    }
+    if (!done && !one_pass) {
         if (i > 0 && sc->n_fold[i] > 0) {
             dim3 grid(grid_for(ctx, sc->max_fold_out[i], 4), sc->n_fold[i]);
             sc_fold_generic<F><<<grid, kThreads, 0, ctx->stream>>>(sc->d_fold + (size_t)i * sc->k, r);
@@ -264,9 +562,10 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
         }
     }
     DPB_CUDA(cudaGetLastError());
-    if (ctx->profile) DPB_CUDA(cudaEventRecord(ctx->prof_ev[1], ctx->stream));
-    E raw[kMaxAcc];
-    if (sharded) {
+    if (profiled) DPB_CUDA(cudaEventRecord(ctx->prof_ev[1], ctx->stream));
+    if (use_tail) {
+        // the sums are already in raw
+    } else if (sharded) {
         // every rank's partial sums -> all hosts; add them mod p (NCCL has no modular sum)
         DPB_TRY(allgather_to_host(ctx, ctx->round_out, msg_bytes));
         const E* g = (const E*)ctx->gather_host;
@@ -285,10 +584,17 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
         E claim = F::zero();
         if (i > 0) claim = eval_coeffs<F>((int)sc->d, coeffs, r);
         samples_to_evals<F>((int)sc->d, raw, i == 0, claim, (E*)out_evals, coeffs);
+        memcpy(sc->prev_evals, out_evals, msg_bytes);
     } else {
+        if (one_pass && i > 0) {
+            // s(1) = previous s(r) - s(0)
+            const E claim = lagrange_eval<F>((int)sc->d, (const E*)sc->prev_evals, (const E*)sc->lag_w, r);
+            raw[1] = F::sub(claim, raw[0]);
+        }
         memcpy(out_evals, raw, msg_bytes);
+        memcpy(sc->prev_evals, raw, msg_bytes);
     }
-    if (ctx->profile) {
+    if (profiled) {
         float ms = 0.f;
         DPB_CUDA(cudaEventSynchronize(ctx->prof_ev[1]));
         DPB_CUDA(cudaEventElapsedTime(&ms, ctx->prof_ev[0], ctx->prof_ev[1]));
@@ -297,7 +603,8 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
         const char* name;
         if (i == 0) {
             for (uint32_t j = 0; j < sc->k; j++) bytes += dtype_size(sc->tr[j].dtype) << sc->tr[j].nv;
-            name = done ? (sc->tr[0].dtype == DPB_GL_BASE ? "fused_eval0<base>" : "fused_eval0") : "sc_eval_generic";
+            name = done ? (sc->tr[0].dtype == DPB_GL_BASE ? "fused_eval0<base>" : "fused_eval0")
+                        : one_pass ? "sc_round_generic" : "sc_eval_generic";
         } else {
             const FoldDesc* fd = sc->h_fold.data() + (size_t)i * sc->k;
             for (uint32_t j = 0; j < sc->n_fold[i]; j++)
@@ -305,7 +612,7 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
             for (uint32_t j = 0; j < sc->k; j++)
                 if (sc->h_desc[(size_t)i * sc->k + j].shift >= 0) bytes += dtype_size(sc->tr[j].dtype) << sc->tr[j].nv;
             name = done ? (fd[0].dtype_in == DPB_GL_BASE ? "fused_fold_eval<base>" : "fused_fold_eval")
-                        : "sc_fold_generic+sc_eval_generic";
+                        : one_pass ? "sc_round_generic" : "sc_fold_generic+sc_eval_generic";
         }
         bool found = false;
         for (auto& e : ctx->prof_log) {
@@ -494,6 +801,8 @@ int dpb_sumcheck_begin(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, ui
     sc->fused_shape = detect_fused_shape(sc->h_desc.data(), sc->tr.size(), num_vars, terms, n_terms, gl,
                                          [&](uint32_t j) { return sc->tr[j].nv; },
                                          [&](uint32_t j) { return sc->tr[j].dtype; });
+    rc = gl ? setup_one_pass<GlFam>(sc, terms) : setup_one_pass<FrFam>(sc, terms);
+    if (rc != DPB_OK) return cleanup(rc);
     *out = sc;
     return DPB_OK;
 }
@@ -552,6 +861,8 @@ int dpb_sumcheck_finish(dpb_sc* sc, const void* last_challenge, void* out_final_
     if (sc->global_round != total) return fail(DPB_ESTATE, "only %u of %u rounds ran", sc->global_round, total);
     int rc;
     if (sc->log2_ranks > 0) rc = dpb_sumcheck_finish(sc->tail, last_challenge, out_final_evals);
+    else if (sc->tail_active) rc = sc->gl ? tail_finish<GlFam>(sc, last_challenge, out_final_evals)
+                                          : tail_finish<FrFam>(sc, last_challenge, out_final_evals);
     else rc = sc->gl ? run_finish<GlFam>(sc, last_challenge, out_final_evals)
                      : run_finish<FrFam>(sc, last_challenge, out_final_evals);
     if (rc != DPB_OK) return rc;
@@ -561,6 +872,7 @@ int dpb_sumcheck_finish(dpb_sc* sc, const void* last_challenge, void* out_final_
 
 void dpb_sumcheck_free(dpb_sc* sc) {
     if (!sc) return;
+    if (sc->tail_active) tail_abort(sc);
     if (sc->tail) dpb_sumcheck_free(sc->tail);
     for (auto* m : sc->tail_mles) dpb_mle_free(m);
     device_free(sc->ctx, sc->tail_dev);
@@ -569,6 +881,9 @@ void dpb_sumcheck_free(dpb_sc* sc) {
     device_free(sc->ctx, sc->d_fold);
     device_free(sc->ctx, sc->d_terms);
     device_free(sc->ctx, sc->d_final);
+    device_free(sc->ctx, sc->d_rtab);
+    device_free(sc->ctx, sc->d_groups);
+    device_free(sc->ctx, sc->d_prog);
     delete sc;
 }
 

@@ -75,6 +75,15 @@ struct dpb_ctx {
     void* gather_dev = nullptr;   // send area (first half) and all-gather result (second half is unused slack)
     void* gather_host = nullptr;  // pinned copy of the all-gather result
     size_t gather_bytes = 0;
+    // resident last-rounds kernel (generic_round.cuh): its mailbox in mapped pinned memory, the stream it
+    // runs on (so that it never blocks other work of this context) and the sumcheck that owns it right now
+    void* tail_box_host = nullptr;
+    void* tail_box_dev = nullptr;
+    cudaStream_t tail_stream = nullptr;
+    cudaEvent_t tail_ev[2] = {nullptr, nullptr};
+    const void* tail_owner = nullptr;
+    bool tail_enabled = true;
+    unsigned long long tail_wait_ns = 5ull * 1000 * 1000 * 1000;
     // optional per-kernel timing log (dpb_profile_enable)
     bool profile = false;
     cudaEvent_t prof_ev[2] = {nullptr, nullptr};

@@ -337,7 +337,7 @@ inline void samples_to_evals(int K, const typename F::E* raw, bool have_p1, cons
     const E p1 = have_p1 ? raw[1] : F::sub(claim, p0);
     const E lead = (K & 1) ? F::neg(raw[2]) : raw[2];
     const E two = F::from_u64(2);
-    const E inv2 = F::inv(two);
+    static const E inv2 = F::inv(F::from_u64(2)), inv6 = F::inv(F::from_u64(6));  // inversions are slow: once per process
     E c[5];
     for (int i = 0; i < 5; i++) c[i] = F::zero();
     c[0] = p0;
@@ -358,7 +358,7 @@ inline void samples_to_evals(int K, const typename F::E* raw, bool have_p1, cons
         t = F::sub(t, F::mul(F::from_u64(4), c[2]));
         t = F::sub(t, F::mul(F::from_u64(16), lead));
         t = F::sub(t, F::mul(two, s));
-        c[3] = F::mul(t, F::inv(F::from_u64(6)));
+        c[3] = F::mul(t, inv6);
         c[1] = F::sub(s, c[3]);
     }
     for (int x = 0; x <= K; x++) {

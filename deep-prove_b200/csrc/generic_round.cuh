@@ -1,0 +1,507 @@
+// One-pass sumcheck round for any list of product terms.
+//
+// A round of the generic prover used to be two launches: bind the previous
+// challenge into every table (read 2^v, write 2^(v-1)), then evaluate the terms
+// (read 2^(v-1) again).  Here one kernel does both: a thread that owns pair p
+// of this round reads the four previous-round entries 4p..4p+3 of every table,
+// binds the challenge, stores the two new entries and evaluates the terms on
+// them while they are still on chip.
+//
+// Three things cut the multiplies per pair:
+//  * every table is loaded and bound once per pair, whatever the number of
+//    terms that use it: the pair (value at 0, difference) of each table sits in
+//    a per-thread slot of shared memory, and moving to the next evaluation point
+//    is one addition per table;
+//  * after round 0 the value at 1 is not computed: the host gets it from the
+//    previous round polynomial (s(0) + s(1) = previous s(r));
+//  * terms that share a table are grouped on the host, and that table
+//    multiplies the group's sum once per point instead of once per term.
+// Results are exact field sums, so they equal the two-pass kernels' bit for bit.
+#pragma once
+#include "sumcheck_kernels.cuh"
+
+namespace dpb {
+
+// A table as one round's kernel sees it.
+struct RoundTab {
+    const void* in;    // fold mode: the table of the previous round; otherwise this round's table
+    void* out;         // fold mode: where the bound table goes (2 entries per pair); else nullptr
+    int32_t dtype_in;  // layout of `in`
+    int32_t shift;     // < 0: entries 2p, 2p+1 (4p..4p+3 in fold mode); >= 0: constant this round, entry p >> shift
+};
+
+constexpr uint16_t kNoOuter = 0xFFFF;
+constexpr int kMaxAccTail = 8;  // sums a round publishes (degree <= 7)
+
+// Terms [term_begin, term_end) multiplied by table `outer` (kNoOuter: by nothing).
+struct ProgGroup {
+    uint16_t outer, term_begin, term_end, pad;
+};
+
+// coeff * product of idx[0..n_factors) (the group's outer table is not listed)
+template <class F>
+struct ProgTerm {
+    typename F::E coeff;
+    uint16_t n_factors;
+    uint16_t coeff_is_one;
+    uint16_t idx[DPB_MAX_FACTORS];
+};
+
+// Per-thread slots in shared memory: slot s (= 2 * table + {0: value, 1: difference}) is W 16-byte words,
+// word w of thread t at ((s * W + w) * blockDim + t): consecutive threads touch consecutive words.
+template <class F>
+struct Slots {
+    typedef typename F::E E;
+    static constexpr int W = sizeof(E) / 16;
+    uint4* base;
+    __device__ __forceinline__ E get(uint32_t s) const {
+        E v;
+        uint4* q = (uint4*)&v;
+#pragma unroll
+        for (int w = 0; w < W; w++) q[w] = base[((size_t)s * W + w) * blockDim.x + threadIdx.x];
+        return v;
+    }
+    __device__ __forceinline__ void put(uint32_t s, const E& v) const {
+        const uint4* q = (const uint4*)&v;
+#pragma unroll
+        for (int w = 0; w < W; w++) base[((size_t)s * W + w) * blockDim.x + threadIdx.x] = q[w];
+    }
+};
+
+// sum over groups of outer * sum over terms of coeff * product, at the tables' current values
+template <class F>
+__device__ __noinline__ typename F::E eval_program(const Slots<F>& sl, const ProgGroup* __restrict__ groups,
+                                                   uint32_t n_groups, const ProgTerm<F>* __restrict__ terms) {
+    typedef typename F::E E;
+    E total = F::zero();
+    for (uint32_t g = 0; g < n_groups; g++) {
+        const ProgGroup pg = groups[g];
+        E inner = F::zero();
+        for (uint32_t t = pg.term_begin; t < pg.term_end; t++) {
+            const ProgTerm<F>& tm = terms[t];
+            const uint32_t nf = tm.n_factors;
+            E prod;
+            if (nf == 0) {
+                prod = tm.coeff;
+            } else {
+                prod = sl.get(2 * tm.idx[0]);
+                for (uint32_t j = 1; j < nf; j++) prod = F::mul(prod, sl.get(2 * tm.idx[j]));
+                if (!tm.coeff_is_one) prod = F::mul(prod, tm.coeff);
+            }
+            inner = F::add(inner, prod);
+        }
+        if (pg.outer != kNoOuter) inner = F::mul(inner, sl.get(2 * pg.outer));
+        total = F::add(total, inner);
+    }
+    return total;
+}
+
+// every table's current value moves one evaluation point on
+template <class F>
+__device__ __noinline__ void advance_point(const Slots<F>& sl, const RoundTab* __restrict__ tabs, uint32_t k) {
+    for (uint32_t j = 0; j < k; j++) {
+        if (tabs[j].shift >= 0) continue;  // constant in this round
+        sl.put(2 * j, F::add(sl.get(2 * j), sl.get(2 * j + 1)));
+    }
+}
+
+// acc[x] = sum over pairs of the program at point x, for x = 0..D; with SKIP_ONE, x = 1 is left at zero.
+template <class F, int D, bool SKIP_ONE>
+__global__ void __launch_bounds__(kThreads)
+    sc_round_generic(const RoundTab* __restrict__ tabs, uint32_t k, const ProgGroup* __restrict__ groups,
+                     uint32_t n_groups, const ProgTerm<F>* __restrict__ terms, typename F::E r, uint64_t n_pairs,
+                     ReduceScratch<F> rs, typename F::E* out) {
+    typedef typename F::E E;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    Slots<F> sl;
+    sl.base = (uint4*)smem_raw;
+    E acc[D + 1];
+#pragma unroll
+    for (int x = 0; x <= D; x++) acc[x] = F::zero();
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t p = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; p < n_pairs; p += stride) {
+        for (uint32_t j = 0; j < k; j++) {
+            const RoundTab t = tabs[j];
+            E f0, f1;
+            if (t.out) {
+                E a0, a1, b0, b1;
+                F::load_pair(t.in, t.dtype_in, 2 * p, a0, a1);
+                F::load_pair(t.in, t.dtype_in, 2 * p + 1, b0, b1);
+                f0 = F::add(a0, F::mul(r, F::sub(a1, a0)));
+                f1 = F::add(b0, F::mul(r, F::sub(b1, b0)));
+                F::store(t.out, 2 * p, f0);
+                F::store(t.out, 2 * p + 1, f1);
+            } else if (t.shift < 0) {
+                F::load_pair(t.in, t.dtype_in, p, f0, f1);
+            } else {
+                f0 = F::load(t.in, t.dtype_in, p >> t.shift);
+                f1 = f0;
+            }
+            sl.put(2 * j, f0);
+            sl.put(2 * j + 1, F::sub(f1, f0));
+        }
+#pragma unroll
+        for (int x = 0; x <= D; x++) {
+            if (!(SKIP_ONE && x == 1)) acc[x] = F::add(acc[x], eval_program<F>(sl, groups, n_groups, terms));
+            if (x < D) advance_point<F>(sl, tabs, k);
+        }
+    }
+    grid_sum_publish<F, D + 1>(acc, rs, out);
+}
+
+// ---- resident kernel for the last rounds ---------------------------------------
+//
+// Once a round has only a few hundred pairs, launching a kernel per round costs
+// more than the round.  sc_tail_generic stays resident instead: one block runs
+// every remaining round, hands each round's sums to the host through mapped
+// memory and waits there for the challenge (about 4 us per exchange, measured).
+// With so little work per round the latency of one thread's chain of
+// multiplications is what counts, so the block spreads a round as widely as it
+// can: binding over (pair, table), evaluation over (pair, point).  Every wait
+// is bounded: when the host does not answer within wait_ns the kernel records
+// that in the mailbox and returns.
+
+constexpr uint32_t kTailAbort = 0xFFFFFFFFu;
+constexpr uint32_t kTailMaxTables = 96;
+
+// Mailbox in mapped pinned host memory.  Everything travels as 16-byte chunks
+// {8 bytes of data, sequence number, pad}: a chunk is written and read as one
+// transaction, so a reader that sees the sequence number it waits for has the
+// data that belongs to it, and neither side needs a system-wide fence (those
+// cost more than a microsecond each on the device).
+struct TailChunk {
+    uint64_t data;
+    uint32_t seq;
+    uint32_t pad;
+};
+struct TailBox {
+    // host -> device: the challenge that ends round i carries sequence number i + 1; kTailAbort: leave now
+    TailChunk chal[4];
+    // device -> host
+    volatile uint32_t status;  // 0 running, 2 gave up waiting for the host
+    uint32_t pad[15];
+    TailChunk evals[kMaxAccTail * 4];      // sums of round i: sequence number i + 1
+    TailChunk finals[kTailMaxTables * 4];  // final evaluations: sequence number n_rounds + 1
+};
+
+static_assert(sizeof(TailBox) <= 8192, "the context reserves 8 KiB for the mailbox");
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void chunk_store(TailChunk* c, uint64_t data, uint32_t seq) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(c), "r"((uint32_t)data),
+                 "r"((uint32_t)(data >> 32)), "r"(seq), "r"(0u)
+                 : "memory");
+}
+__device__ __forceinline__ void chunk_load(const TailChunk* c, uint64_t& data, uint32_t& seq) {
+    uint32_t lo, hi, unused = 0;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(lo), "=r"(hi), "=r"(seq), "+r"(unused) : "l"(c) : "memory");
+    data = (uint64_t)lo | ((uint64_t)hi << 32);
+}
+// an element as chunks with one sequence number
+template <class E>
+__device__ __forceinline__ void chunks_store(TailChunk* c, const E& v, uint32_t seq) {
+    const uint64_t* w = (const uint64_t*)&v;
+#pragma unroll
+    for (int i = 0; i < (int)(sizeof(E) / 8); i++) chunk_store(c + i, w[i], seq);
+}
+
+// Waits for the challenge with sequence number `want`.  true: it is in r; false: abort or time-out.
+template <class E>
+__device__ __forceinline__ bool tail_wait(TailBox* box, uint32_t want, unsigned long long wait_ns, E& r) {
+    const unsigned long long t0 = global_ns();
+    uint64_t* rw = (uint64_t*)&r;
+    for (int i = 0; i < (int)(sizeof(E) / 8); i++) {
+        for (;;) {
+            uint32_t s;
+            chunk_load(&box->chal[i], rw[i], s);
+            if (s == want) break;
+            if (s == kTailAbort) return false;
+            if (global_ns() - t0 > wait_ns) {
+                box->status = 2;
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+constexpr int kTailThreads = 512;
+constexpr int kTailProgBytes = 8 * 1024;  // the term program is staged in shared memory when it fits
+
+// Shared-memory slots addressed by pair instead of by thread: slot s of pair p, n pairs in the round.
+template <class F>
+struct PairSlots {
+    typedef typename F::E E;
+    static constexpr int W = sizeof(E) / 16;
+    uint4* base;
+    uint32_t n;
+    __device__ __forceinline__ E get(uint32_t s, uint32_t p) const {
+        E v;
+        uint4* q = (uint4*)&v;
+#pragma unroll
+        for (int w = 0; w < W; w++) q[w] = base[((size_t)s * W + w) * n + p];
+        return v;
+    }
+    __device__ __forceinline__ void put(uint32_t s, uint32_t p, const E& v) const {
+        const uint4* q = (const uint4*)&v;
+#pragma unroll
+        for (int w = 0; w < W; w++) base[((size_t)s * W + w) * n + p] = q[w];
+    }
+    // value of table j at the integer point x: f(0) + x * (f(1) - f(0)) by repeated addition
+    __device__ __forceinline__ E at(uint32_t j, uint32_t p, uint32_t x) const {
+        E v = get(2 * j, p);
+        if (x) {
+            const E d = get(2 * j + 1, p);
+            for (uint32_t q = 0; q < x; q++) v = F::add(v, d);
+        }
+        return v;
+    }
+};
+
+template <class F>
+__device__ __noinline__ typename F::E eval_program_at(const PairSlots<F>& sl, uint32_t p, uint32_t x,
+                                                      const ProgGroup* groups, uint32_t n_groups,
+                                                      const ProgTerm<F>* terms) {
+    typedef typename F::E E;
+    E total = F::zero();
+    for (uint32_t g = 0; g < n_groups; g++) {
+        const ProgGroup pg = groups[g];
+        E inner = F::zero();
+        for (uint32_t t = pg.term_begin; t < pg.term_end; t++) {
+            const ProgTerm<F>& tm = terms[t];
+            const uint32_t nf = tm.n_factors;
+            E prod;
+            if (nf == 0) {
+                prod = tm.coeff;
+            } else {
+                prod = sl.at(tm.idx[0], p, x);
+                for (uint32_t j = 1; j < nf; j++) prod = F::mul(prod, sl.at(tm.idx[j], p, x));
+                if (!tm.coeff_is_one) prod = F::mul(prod, tm.coeff);
+            }
+            inner = F::add(inner, prod);
+        }
+        if (pg.outer != kNoOuter) inner = F::mul(inner, sl.at(pg.outer, p, x));
+        total = F::add(total, inner);
+    }
+    return total;
+}
+
+// One block; round `round` has n_pairs = 2^(n_rounds - round - 1) <= max_pairs pairs.  Per round:
+//   A. items (pair, table): load, bind the previous challenge, store, fill the pair's slots;
+//   B. items (pair, point): evaluate the program at that point;
+//   C. tree sum over the pairs of each point; thread 0 posts the sums and waits for the challenge.
+// Dynamic shared memory: [program copy | round descriptors | slots (reused for the tree sum)].
+template <class F, int D>
+__global__ void __launch_bounds__(kTailThreads)
+    sc_tail_generic(const RoundTab* __restrict__ tabs_all, uint32_t k, const ProgGroup* __restrict__ groups_g,
+                    uint32_t n_groups, const ProgTerm<F>* __restrict__ terms_g, uint32_t n_prog_terms,
+                    typename F::E r, uint32_t first_round, uint32_t n_rounds, TailBox* box,
+                    unsigned long long wait_ns, uint32_t prog_in_smem, uint32_t slots_offset) {
+    typedef typename F::E E;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ E sh_r;
+    __shared__ int sh_stop;
+    const ProgGroup* groups = groups_g;
+    const ProgTerm<F>* terms = terms_g;
+    unsigned char* cursor = smem_raw;
+    if (prog_in_smem) {
+        ProgTerm<F>* st = (ProgTerm<F>*)cursor;
+        cursor += (size_t)n_prog_terms * sizeof(ProgTerm<F>);
+        ProgGroup* sg = (ProgGroup*)cursor;
+        for (uint32_t i = threadIdx.x; i < n_prog_terms; i += blockDim.x) st[i] = terms_g[i];
+        for (uint32_t i = threadIdx.x; i < n_groups; i += blockDim.x) sg[i] = groups_g[i];
+        groups = sg;
+        terms = st;
+    }
+    // round descriptors, double-buffered: the next round's are fetched while this round computes
+    RoundTab* tabs_buf[2] = {(RoundTab*)(smem_raw + slots_offset - 2 * (size_t)k * sizeof(RoundTab)),
+                             (RoundTab*)(smem_raw + slots_offset - (size_t)k * sizeof(RoundTab))};
+    for (uint32_t j = threadIdx.x; j < k; j += blockDim.x) tabs_buf[0][j] = tabs_all[(size_t)first_round * k + j];
+    const RoundTab* tabs = tabs_buf[0];
+    PairSlots<F> sl;
+    sl.base = (uint4*)(smem_raw + slots_offset);
+    E* tree = (E*)(smem_raw + slots_offset);  // [point][pair], after the slots have been consumed
+    for (uint32_t round = first_round; round < n_rounds; round++) {
+        const uint32_t n_pairs = 1u << (n_rounds - round - 1);
+        sl.n = n_pairs;
+        tabs = tabs_buf[(round - first_round) & 1];
+        if (round + 1 < n_rounds) {
+            RoundTab* nxt = tabs_buf[(round + 1 - first_round) & 1];
+            for (uint32_t j = threadIdx.x; j < k; j += blockDim.x) nxt[j] = tabs_all[(size_t)(round + 1) * k + j];
+        }
+        __syncthreads();
+        // A
+        for (uint32_t w = threadIdx.x; w < n_pairs * k; w += blockDim.x) {
+            const uint32_t j = w / n_pairs, p = w % n_pairs;
+            const RoundTab t = tabs[j];
+            E f0, f1;
+            if (t.out) {
+                E a0, a1, b0, b1;
+                F::load_pair(t.in, t.dtype_in, 2 * (uint64_t)p, a0, a1);
+                F::load_pair(t.in, t.dtype_in, 2 * (uint64_t)p + 1, b0, b1);
+                f0 = F::add(a0, F::mul(r, F::sub(a1, a0)));
+                f1 = F::add(b0, F::mul(r, F::sub(b1, b0)));
+                F::store(t.out, 2 * (uint64_t)p, f0);
+                F::store(t.out, 2 * (uint64_t)p + 1, f1);
+            } else if (t.shift < 0) {
+                F::load_pair(t.in, t.dtype_in, p, f0, f1);
+            } else {
+                f0 = F::load(t.in, t.dtype_in, p >> t.shift);
+                f1 = f0;
+            }
+            sl.put(2 * j, p, f0);
+            sl.put(2 * j + 1, p, F::sub(f1, f0));
+        }
+        __syncthreads();
+        // B: the points are 0, 1, .., D in round 0 and 0, 2, .., D later (index 1 is left out)
+        const uint32_t n_points = round > 0 ? D : D + 1;
+        E mine[2];  // at most two items per thread: n_pairs * n_points <= 2 * blockDim
+        uint32_t n_mine = 0;
+        for (uint32_t w = threadIdx.x; w < n_pairs * n_points; w += blockDim.x) {
+            const uint32_t xi = w / n_pairs, p = w % n_pairs;
+            const uint32_t x = (round > 0 && xi >= 1) ? xi + 1 : xi;
+            mine[n_mine++] = eval_program_at<F>(sl, p, x, groups, n_groups, terms);
+        }
+        __syncthreads();  // every slot has been read: the region becomes the tree
+        n_mine = 0;
+        for (uint32_t w = threadIdx.x; w < n_pairs * n_points; w += blockDim.x) tree[w] = mine[n_mine++];
+        __syncthreads();
+        // C
+        for (uint32_t s = n_pairs >> 1; s > 0; s >>= 1) {
+            for (uint32_t w = threadIdx.x; w < s * n_points; w += blockDim.x) {
+                const uint32_t xi = w / s, p = w % s;
+                tree[xi * n_pairs + p] = F::add(tree[xi * n_pairs + p], tree[xi * n_pairs + p + s]);
+            }
+            __syncthreads();
+        }
+        if (threadIdx.x == 0) {
+            constexpr int W8 = sizeof(E) / 8;
+            for (uint32_t xi = 0; xi < n_points; xi++) {
+                const uint32_t x = (round > 0 && xi >= 1) ? xi + 1 : xi;
+                chunks_store<E>(&box->evals[x * W8], tree[xi * n_pairs], round + 1);
+            }
+            E rr;
+            const bool ok = tail_wait<E>(box, round + 1, wait_ns, rr);
+            if (ok) sh_r = rr;
+            sh_stop = ok ? 0 : 1;
+        }
+        __syncthreads();  // also orders this round's table stores before the next round's loads
+        if (sh_stop) return;
+        r = sh_r;
+    }
+    // r ends the last round: one value per table (tabs still holds the last round's descriptors)
+    for (uint32_t j = threadIdx.x; j < k; j += blockDim.x) {
+        const RoundTab t = tabs[j];
+        E a0, a1;
+        if (t.out) F::load_pair(t.out, F::kChalDtype, 0, a0, a1);
+        else F::load_pair(t.in, t.dtype_in, 0, a0, a1);
+        chunks_store<E>(&box->finals[j * (sizeof(E) / 8)], F::add(a0, F::mul(r, F::sub(a1, a0))), n_rounds + 1);
+    }
+}
+
+// ---- host side ---------------------------------------------------------------
+
+// Groups terms by a shared table, greedily: the table that occurs in most of the
+// still ungrouped terms (at least two) becomes the outer factor of those terms.
+template <class F>
+inline void compile_program(const dpb_term* terms, uint32_t n_terms, uint32_t k, std::vector<ProgGroup>& groups,
+                            std::vector<ProgTerm<F>>& prog) {
+    typedef typename F::E E;
+    std::vector<bool> used(n_terms, false);
+    uint32_t left = n_terms;
+    auto emit = [&](uint32_t t, int drop) {  // drop: position of the factor that became the outer table, or -1
+        ProgTerm<F> pt;
+        memset(&pt, 0, sizeof pt);
+        memcpy(&pt.coeff, terms[t].coeff, sizeof(E));
+        pt.coeff_is_one = F::is_one(pt.coeff) ? 1 : 0;
+        uint16_t n = 0;
+        for (uint32_t j = 0; j < terms[t].n_factors; j++)
+            if ((int)j != drop) pt.idx[n++] = terms[t].idx[j];
+        pt.n_factors = n;
+        if (n == 0 && drop >= 0) {
+            // the term was the outer table alone: its inner part is the coefficient itself
+        }
+        prog.push_back(pt);
+    };
+    while (left > 0) {
+        std::vector<uint32_t> count(k, 0);
+        for (uint32_t t = 0; t < n_terms; t++) {
+            if (used[t]) continue;
+            for (uint32_t j = 0; j < terms[t].n_factors; j++) {
+                bool first = true;
+                for (uint32_t q = 0; q < j; q++)
+                    if (terms[t].idx[q] == terms[t].idx[j]) first = false;
+                if (first) count[terms[t].idx[j]]++;
+            }
+        }
+        uint32_t best = 0, best_n = 0;
+        for (uint32_t j = 0; j < k; j++)
+            if (count[j] > best_n) {
+                best_n = count[j];
+                best = j;
+            }
+        ProgGroup g;
+        g.pad = 0;
+        g.term_begin = (uint16_t)prog.size();
+        if (best_n >= 2) {
+            g.outer = (uint16_t)best;
+            for (uint32_t t = 0; t < n_terms; t++) {
+                if (used[t]) continue;
+                int pos = -1;
+                for (uint32_t j = 0; j < terms[t].n_factors; j++)
+                    if (terms[t].idx[j] == best) {
+                        pos = (int)j;
+                        break;
+                    }
+                if (pos < 0) continue;
+                emit(t, pos);
+                used[t] = true;
+                left--;
+            }
+        } else {
+            g.outer = kNoOuter;
+            for (uint32_t t = 0; t < n_terms; t++) {
+                if (used[t]) continue;
+                emit(t, -1);
+                used[t] = true;
+                left--;
+            }
+        }
+        g.term_end = (uint16_t)prog.size();
+        groups.push_back(g);
+    }
+}
+
+// Value at x of the polynomial of degree <= D with the given values at 0..D.
+// w[j] = 1 / prod_{m != j} (j - m), computed once by lagrange_weights.
+template <class F>
+inline void lagrange_weights(int D, typename F::E* w) {
+    typedef typename F::E E;
+    for (int j = 0; j <= D; j++) {
+        E den = F::one();
+        for (int m = 0; m <= D; m++) {
+            if (m == j) continue;
+            const E diff = j > m ? F::from_u64((uint64_t)(j - m)) : F::neg(F::from_u64((uint64_t)(m - j)));
+            den = F::mul(den, diff);
+        }
+        w[j] = F::inv(den);
+    }
+}
+template <class F>
+inline typename F::E lagrange_eval(int D, const typename F::E* evals, const typename F::E* w, const typename F::E& x) {
+    typedef typename F::E E;
+    E total = F::zero();
+    for (int j = 0; j <= D; j++) {
+        E term = F::mul(evals[j], w[j]);
+        for (int m = 0; m <= D; m++)
+            if (m != j) term = F::mul(term, F::sub(x, F::from_u64((uint64_t)m)));
+        total = F::add(total, term);
+    }
+    return total;
+}
+
+}  // namespace dpb

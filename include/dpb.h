@@ -117,6 +117,15 @@ int dpb_profile_enable(dpb_ctx* ctx, int on);
 /* Copies at most cap entries; *n is the number available. */
 int dpb_profile_read(dpb_ctx* ctx, dpb_profile_entry* out, uint32_t cap, uint32_t* n);
 
+/* The last rounds of a sumcheck (a few hundred pairs or fewer) run in one
+ * resident kernel that exchanges round sums and challenges with the host
+ * through mapped memory instead of one launch per round.  enable = 0 turns
+ * that off (every round is a launch); wait_ms bounds how long the kernel
+ * waits for the next challenge before it gives up, after which the sumcheck's
+ * next call returns DPB_ETIMEOUT (default 5000; 0 keeps the current value).
+ * No reference counterpart: the reference's rounds are CPU loops. */
+int dpb_resident_rounds(dpb_ctx* ctx, int enable, uint32_t wait_ms);
+
 /* ---- multilinear tables (dp_crypto::poly::dense::DensePolynomial) ------ */
 /* Uploads `len` (a power of two) evaluations from host memory.
  * Replaces DensePolynomial::new / new_from_smart_slice
