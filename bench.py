@@ -252,11 +252,13 @@ def run_ours(args):
     barrier()
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = ctx.sumcheck_launches()
     e0.record(stream)
     for _ in range(args.steps):
         st = step_device()
     e1.record(stream)
     barrier()
+    launches = ctx.sumcheck_launches() - launches0
     ms_total = e0.elapsed_time(e1)
     # per-kernel CUDA-event times: the same steps once more with the library's per-round events on
     # (they cost about 10 us per round, so they stay out of the timed region above)
@@ -324,8 +326,9 @@ def run_ours(args):
         "kernels": kernels,
         "e2e": {"value": alg_bytes(field, n_global) / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3},
-        # per rank and step: n local rounds, the last local fold, 2 launches per tail round, the final evaluation
-        "gpu_launches": args.steps * (n + 2 + 2 * log2_world) * world,
+        # counted by the library on rank 0 over the timed steps (every rank launches the same kernels): one
+        # launch per large round, one resident kernel for the last rounds and the final evaluations
+        "gpu_launches": launches * world,
         "clocks": clocks,
     }
     if world == 1 and not args.no_cpu_baseline:

@@ -53,6 +53,7 @@ _pp = ctypes.POINTER(ctypes.c_void_p)
 
 SIGNATURES = {
     "dpb_resident_rounds": (_int, [_vp, _int, _u32]),
+    "dpb_sumcheck_launches": (_u64, [_vp]),
     "dpb_profile_enable": (_int, [_vp, _int]),
     "dpb_profile_read": (_int, [_vp, ctypes.POINTER(ProfileEntry), _u32, ctypes.POINTER(_u32)]),
     "dpb_init": (_int, [_int, _pp]),
@@ -180,6 +181,9 @@ class Context:
     def resident_rounds(self, enable=True, wait_ms=0):
         """Last rounds in one resident kernel (default) or one launch per round; wait_ms bounds the kernel's waits."""
         check(lib.dpb_resident_rounds(self.h, 1 if enable else 0, int(wait_ms)))
+
+    def sumcheck_launches(self):
+        return int(lib.dpb_sumcheck_launches(self.h))
 
     def profile(self, on):
         check(lib.dpb_profile_enable(self.h, 1 if on else 0))

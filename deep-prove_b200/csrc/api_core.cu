@@ -1,5 +1,7 @@
 // C ABI: context, table handles, layout conversion, eq tables and partial
 // evaluation (fix_high / fix_low / evaluate).
+#include <algorithm>
+
 #include "common.cuh"
 #include "poly_kernels.cuh"
 
@@ -29,6 +31,24 @@ void device_free(dpb_ctx* ctx, void* p) {
     if (p) cudaFreeAsync(p, ctx->stream);
 }
 
+int upload_small(dpb_ctx* ctx, void* dst, const void* src, size_t bytes) {
+    size_t done = 0;
+    while (done < bytes) {
+        const int slot = ctx->up_next;
+        ctx->up_next = (slot + 1) % dpb_ctx::kStageSlots;
+        // a slot is reused only after the copy that last read it has run (long ago, as a rule)
+        if (ctx->up_used[slot]) DPB_CUDA(cudaEventSynchronize(ctx->up_ev[slot]));
+        const size_t n = std::min(bytes - done, dpb_ctx::kStageSlotBytes);
+        char* stage = (char*)ctx->up_host + (size_t)slot * dpb_ctx::kStageSlotBytes;
+        memcpy(stage, (const char*)src + done, n);
+        DPB_CUDA(cudaMemcpyAsync((char*)dst + done, stage, n, cudaMemcpyHostToDevice, ctx->stream));
+        DPB_CUDA(cudaEventRecord(ctx->up_ev[slot], ctx->stream));
+        ctx->up_used[slot] = true;
+        done += n;
+    }
+    return DPB_OK;
+}
+
 int new_mle(dpb_ctx* ctx, int dtype, uint64_t len, dpb_mle** out) {
     dpb_mle* m = new (std::nothrow) dpb_mle();
     if (!m) return fail(DPB_ENOMEM, "host allocation failed");
@@ -50,8 +70,7 @@ int stage_to_device(dpb_ctx* ctx, const void* host, size_t bytes, size_t offset,
         return fail(DPB_EINVAL, "staging area too small (%zu + %zu > %zu)", offset, bytes,
                     ctx->stage_bytes);
     *dev = (char*)ctx->stage_dev + offset;
-    DPB_CUDA(cudaMemcpyAsync(*dev, host, bytes, cudaMemcpyHostToDevice, ctx->stream));
-    return DPB_OK;
+    return upload_small(ctx, *dev, host, bytes);
 }
 
 // eq(x, pt) table over m variables into freshly allocated device memory.
@@ -216,6 +235,9 @@ int dpb_init(int device, dpb_ctx** out) {
     DPB_CUDA(cudaMalloc(&ctx->stage_dev, ctx->stage_bytes));
     DPB_CUDA(cudaEventCreate(&ctx->prof_ev[0]));
     DPB_CUDA(cudaEventCreate(&ctx->prof_ev[1]));
+    DPB_CUDA(cudaHostAlloc(&ctx->up_host, dpb_ctx::kStageSlots * dpb_ctx::kStageSlotBytes, cudaHostAllocDefault));
+    for (int i = 0; i < dpb_ctx::kStageSlots; i++)
+        DPB_CUDA(cudaEventCreateWithFlags(&ctx->up_ev[i], cudaEventDisableTiming));
     DPB_CUDA(cudaHostAlloc(&ctx->tail_box_host, 8192, cudaHostAllocMapped));
     DPB_CUDA(cudaHostGetDevicePointer(&ctx->tail_box_dev, ctx->tail_box_host, 0));
     memset(ctx->tail_box_host, 0, 8192);
@@ -235,6 +257,8 @@ void dpb_shutdown(dpb_ctx* ctx) {
     cudaEventDestroy(ctx->tail_ev[0]);
     cudaEventDestroy(ctx->tail_ev[1]);
     cudaFreeHost(ctx->tail_box_host);
+    cudaFreeHost(ctx->up_host);
+    for (int i = 0; i < dpb_ctx::kStageSlots; i++) cudaEventDestroy(ctx->up_ev[i]);
     cudaFree(ctx->partials);
     cudaFree(ctx->counter);
     cudaFree(ctx->stage_dev);
@@ -252,6 +276,8 @@ int dpb_sync(dpb_ctx* ctx) {
 }
 
 void* dpb_stream(dpb_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+
+uint64_t dpb_sumcheck_launches(const dpb_ctx* ctx) { return ctx ? ctx->sumcheck_launches : 0; }
 
 int dpb_resident_rounds(dpb_ctx* ctx, int enable, uint32_t wait_ms) {
     if (!ctx) return fail(DPB_EINVAL, "null context");

@@ -100,10 +100,14 @@ static int einsum_impl(dpb_ctx* ctx, const int64_t* tensor, int tensor_on_device
         free_eqs();
         return cleanup(rc);
     }
-    cudaMemcpyAsync(d_off, off.data(), O * 8, cudaMemcpyHostToDevice, ctx->stream);
-    if (n_outer) {
-        cudaMemcpyAsync(d_wptr, w_ptrs.data(), n_outer * sizeof(void*), cudaMemcpyHostToDevice, ctx->stream);
-        cudaMemcpyAsync(d_dims, outer_dims, n_outer * 8, cudaMemcpyHostToDevice, ctx->stream);
+    rc = upload_small(ctx, d_off, off.data(), O * 8);
+    if (rc == DPB_OK && n_outer) {
+        rc = upload_small(ctx, d_wptr, w_ptrs.data(), n_outer * sizeof(void*));
+        if (rc == DPB_OK) rc = upload_small(ctx, d_dims, outer_dims, n_outer * 8);
+    }
+    if (rc != DPB_OK) {
+        free_eqs();
+        return cleanup(rc);
     }
     einsum_outer_weights<F><<<grid_for(ctx, O), kThreads, 0, ctx->stream>>>((const E* const*)d_wptr, (const uint64_t*)d_dims,
                                                                               n_outer, O, (E*)d_w);
@@ -133,7 +137,8 @@ static int einsum_impl(dpb_ctx* ctx, const int64_t* tensor, int tensor_on_device
         einsum_contract_thread<F><<<grid_for(ctx, n_outputs), kThreads, 0, ctx->stream>>>(
             t_dev, kept, (const uint64_t*)d_off, (const E*)d_w, O, n_outputs, C, c_pad, (E*)owner->ptr);
     cudaError_t e = cudaGetLastError();
-    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);  // host staging vectors go out of scope
+    // a host tensor is only read during the call: wait for its copy (device tensors need no wait)
+    if (e == cudaSuccess && !tensor_on_device) e = cudaStreamSynchronize(ctx->stream);
     free_eqs();
     cleanup(DPB_OK);
     if (e != cudaSuccess) {

@@ -100,8 +100,9 @@ static void table_at_round(const dpb_sc* sc, uint32_t j, uint32_t i, const void*
     }
 }
 
+// the term list in the layout the two-pass evaluation kernel reads
 template <class F>
-static int upload_terms(dpb_sc* sc, const dpb_term* terms) {
+static void build_terms(const dpb_sc* sc, const dpb_term* terms, std::vector<uint8_t>& out) {
     typedef typename F::E E;
     std::vector<TermDev<F>> h(sc->n_terms);
     for (uint32_t t = 0; t < sc->n_terms; t++) {
@@ -110,12 +111,7 @@ static int upload_terms(dpb_sc* sc, const dpb_term* terms) {
         h[t].coeff_is_one = F::is_one(h[t].coeff) ? 1u : 0u;
         for (int j = 0; j < DPB_MAX_FACTORS; j++) h[t].idx[j] = terms[t].idx[j];
     }
-    DPB_TRY(device_alloc(sc->ctx, h.size() * sizeof(TermDev<F>), &sc->d_terms));
-    DPB_CUDA(cudaMemcpyAsync(sc->d_terms, h.data(), h.size() * sizeof(TermDev<F>), cudaMemcpyHostToDevice,
-                             sc->ctx->stream));
-    // h is pageable: the copy has been staged by the driver when the call returns
-    DPB_CUDA(cudaStreamSynchronize(sc->ctx->stream));
-    return DPB_OK;
+    out.assign((const uint8_t*)h.data(), (const uint8_t*)h.data() + h.size() * sizeof(TermDev<F>));
 }
 
 template <class F, int D>
@@ -152,19 +148,67 @@ static int launch_one_pass(dpb_sc* sc, uint32_t round, uint64_t n_pairs, const t
     return DPB_OK;
 }
 
-// Lays out what the one-pass rounds need: per-round table descriptors that say
-// which tables are bound inside the round's kernel, and the grouped term program.
+// Host-side plan of the one-pass rounds and the resident kernel: the grouped term
+// program, launch shapes and shared-memory layouts.  No device work.
 template <class F>
-static int setup_one_pass(dpb_sc* sc, const dpb_term* terms) {
+static void plan_program(dpb_sc* sc, const dpb_term* terms, std::vector<uint8_t>& h_groups, std::vector<uint8_t>& h_prog) {
     typedef typename F::E E;
-    dpb_ctx* ctx = sc->ctx;
+    if (sc->k > 4096) return;  // very many tables: the two-pass kernels run every round
+    std::vector<ProgGroup> groups;
+    std::vector<ProgTerm<F>> prog;
+    compile_program<F>(terms, sc->n_terms, sc->k, groups, prog);
+    sc->n_groups = (uint32_t)groups.size();
+    sc->n_prog_terms = (uint32_t)prog.size();
+    h_groups.assign((const uint8_t*)groups.data(), (const uint8_t*)groups.data() + groups.size() * sizeof(ProgGroup));
+    h_prog.assign((const uint8_t*)prog.data(), (const uint8_t*)prog.data() + prog.size() * sizeof(ProgTerm<F>));
+    sc->has_prog = true;
+    // one-pass rounds: every thread keeps (value, difference) of every table in shared memory
     const size_t per_thread = (size_t)sc->k * 2 * sizeof(E);
     uint32_t threads = 256;
     while (threads >= 64 && per_thread * threads > (size_t)kOnePassMaxSmem) threads /= 2;
-    if (threads < 64) return DPB_OK;  // too many tables: the two-pass kernels run
-    sc->op_threads = threads;
-    sc->op_smem = per_thread * threads;
-    std::vector<RoundTab> rt((size_t)sc->n * sc->k);
+    if (threads >= 64) {
+        sc->op_threads = threads;
+        sc->op_smem = per_thread * threads;
+        sc->one_pass = sc->fused_shape == kFusedNone;
+    }
+    // interpolation weights per degree, computed once per process (field inversions are slow on the host)
+    static E weights[7][7];
+    static bool have[7] = {false, false, false, false, false, false, false};
+    static std::mutex mu;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!have[sc->d]) {
+            lagrange_weights<F>((int)sc->d, weights[sc->d]);
+            have[sc->d] = true;
+        }
+        memcpy(sc->lag_w, weights[sc->d], (sc->d + 1) * sizeof(E));
+    }
+    if (sc->k <= kTailMaxTables) {
+        // shared memory of the resident kernel: [program copy | round descriptors | slots or sum tree]
+        const size_t prog_bytes = h_prog.size() + h_groups.size();
+        sc->tail_prog_in_smem = prog_bytes <= (size_t)kTailProgBytes;
+        size_t off = sc->tail_prog_in_smem ? prog_bytes : 0;
+        off = (off + 15) & ~(size_t)15;
+        off += 2 * (size_t)sc->k * sizeof(RoundTab);  // descriptors of the current and the next round
+        off = (off + 15) & ~(size_t)15;
+        sc->tail_slots_offset = (uint32_t)off;
+        // pairs per round the kernel can take: two items per thread in the evaluation phase, and the slots must fit
+        uint64_t max_pairs = 256;
+        while (max_pairs * (sc->d + 1) > 2 * (uint64_t)kTailThreads) max_pairs >>= 1;
+        const size_t per_pair = std::max<size_t>((size_t)sc->k * 2, sc->d + 1) * sizeof(E);
+        while (max_pairs >= 1 && off + per_pair * max_pairs > (size_t)kOnePassMaxSmem) max_pairs >>= 1;
+        if (max_pairs >= 1) {
+            sc->tail_smem = off + per_pair * max_pairs;
+            uint32_t i = 0;
+            while (i < sc->n && (1ull << (sc->n - i - 1)) > max_pairs) i++;
+            sc->tail_start = i;
+        }
+    }
+}
+
+// per-round descriptors of the one-pass kernels: which tables are bound inside the round's kernel
+static void build_round_tabs(const dpb_sc* sc, std::vector<RoundTab>& rt) {
+    rt.resize((size_t)sc->n * sc->k);
     for (uint32_t i = 0; i < sc->n; i++) {
         for (uint32_t j = 0; j < sc->k; j++) {
             const MleDesc& md = sc->h_desc[(size_t)i * sc->k + j];
@@ -186,57 +230,6 @@ static int setup_one_pass(dpb_sc* sc, const dpb_term* terms) {
             }
         }
     }
-    std::vector<ProgGroup> groups;
-    std::vector<ProgTerm<F>> prog;
-    compile_program<F>(terms, sc->n_terms, sc->k, groups, prog);
-    sc->n_groups = (uint32_t)groups.size();
-    DPB_TRY(device_alloc(ctx, rt.size() * sizeof(RoundTab), (void**)&sc->d_rtab));
-    DPB_TRY(device_alloc(ctx, groups.size() * sizeof(ProgGroup), &sc->d_groups));
-    DPB_TRY(device_alloc(ctx, prog.size() * sizeof(ProgTerm<F>), &sc->d_prog));
-    DPB_CUDA(cudaMemcpyAsync(sc->d_rtab, rt.data(), rt.size() * sizeof(RoundTab), cudaMemcpyHostToDevice, ctx->stream));
-    DPB_CUDA(cudaMemcpyAsync(sc->d_groups, groups.data(), groups.size() * sizeof(ProgGroup), cudaMemcpyHostToDevice,
-                             ctx->stream));
-    DPB_CUDA(cudaMemcpyAsync(sc->d_prog, prog.data(), prog.size() * sizeof(ProgTerm<F>), cudaMemcpyHostToDevice,
-                             ctx->stream));
-    // the vectors are pageable: the copies have been staged when the synchronisation returns
-    DPB_CUDA(cudaStreamSynchronize(ctx->stream));
-    // interpolation weights per degree, computed once per process (field inversions are slow on the host)
-    static E weights[7][7];
-    static bool have[7] = {false, false, false, false, false, false, false};
-    static std::mutex mu;
-    {
-        std::lock_guard<std::mutex> lock(mu);
-        if (!have[sc->d]) {
-            lagrange_weights<F>((int)sc->d, weights[sc->d]);
-            have[sc->d] = true;
-        }
-        memcpy(sc->lag_w, weights[sc->d], (sc->d + 1) * sizeof(E));
-    }
-    sc->has_prog = true;
-    sc->one_pass = sc->fused_shape == kFusedNone;
-    sc->n_prog_terms = (uint32_t)prog.size();
-    if (sc->k <= kTailMaxTables) {
-        // shared memory of the resident kernel: [program copy | round descriptors | slots or sum tree]
-        const size_t prog_bytes = prog.size() * sizeof(ProgTerm<F>) + groups.size() * sizeof(ProgGroup);
-        sc->tail_prog_in_smem = prog_bytes <= (size_t)kTailProgBytes;
-        size_t off = sc->tail_prog_in_smem ? prog_bytes : 0;
-        off = (off + 15) & ~(size_t)15;
-        off += 2 * (size_t)sc->k * sizeof(RoundTab);  // descriptors of the current and the next round
-        off = (off + 15) & ~(size_t)15;
-        sc->tail_slots_offset = (uint32_t)off;
-        // pairs per round the kernel can take: two items per thread in the evaluation phase, and the slots must fit
-        uint64_t max_pairs = 256;
-        while (max_pairs * (sc->d + 1) > 2 * (uint64_t)kTailThreads) max_pairs >>= 1;
-        const size_t per_pair = std::max<size_t>((size_t)sc->k * 2, sc->d + 1) * sizeof(E);
-        while (max_pairs >= 1 && off + per_pair * max_pairs > (size_t)kOnePassMaxSmem) max_pairs >>= 1;
-        if (max_pairs >= 1) {
-            sc->tail_smem = off + per_pair * max_pairs;
-            uint32_t i = 0;
-            while (i < sc->n && (1ull << (sc->n - i - 1)) > max_pairs) i++;
-            sc->tail_start = i;
-        }
-    }
-    return DPB_OK;
 }
 
 // ---- resident last-rounds kernel: host side -------------------------------------
@@ -326,6 +319,7 @@ static int tail_round(dpb_sc* sc, uint32_t i, const typename F::E& r, typename F
         }
         if (rc != DPB_OK) return rc;
         DPB_CUDA(cudaEventRecord(ctx->tail_ev[1], ctx->tail_stream));
+        ctx->sumcheck_launches++;
         sc->tail_active = true;
         ctx->tail_owner = sc;
     } else {
@@ -562,6 +556,7 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
         }
     }
     DPB_CUDA(cudaGetLastError());
+    if (!use_tail) ctx->sumcheck_launches += (!done && !one_pass && i > 0 && sc->n_fold[i] > 0) ? 2 : 1;
     if (profiled) DPB_CUDA(cudaEventRecord(ctx->prof_ev[1], ctx->stream));
     if (use_tail) {
         // the sums are already in raw
@@ -646,6 +641,7 @@ static int run_finish(dpb_sc* sc, const void* last_challenge, void* out) {
     sc_final_evals<F><<<(sc->k + 127) / 128, 128, 0, ctx->stream>>>(
         sc->d_desc + (size_t)(sc->n - 1) * sc->k, sc->k, r, (E*)sc->d_final);
     DPB_CUDA(cudaGetLastError());
+    ctx->sumcheck_launches++;
     DPB_CUDA(cudaMemcpyAsync(out, sc->d_final, sc->k * sizeof(E), cudaMemcpyDeviceToHost, ctx->stream));
     DPB_CUDA(cudaStreamSynchronize(ctx->stream));
     return DPB_OK;
@@ -664,6 +660,7 @@ static int start_tail(dpb_sc* sc, const void* prev_challenge) {
     E* slot = (E*)((char*)ctx->gather_dev + (size_t)ctx->rank * bytes);
     sc_final_evals<F><<<(sc->k + 127) / 128, 128, 0, ctx->stream>>>(sc->d_desc + (size_t)(sc->n - 1) * sc->k, sc->k, r, slot);
     DPB_CUDA(cudaGetLastError());
+    ctx->sumcheck_launches++;
     DPB_TRY(allgather_to_host(ctx, slot, bytes));
     // gathered[g][j] -> table j entry g (rank g owns the top-variable block g)
     const E* g = (const E*)ctx->gather_host;
@@ -730,13 +727,45 @@ int dpb_sumcheck_begin(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, ui
         sc->tr[j].nv = nv;
         slab_elems += (1ull << (nv - 1)) + (nv >= 2 ? (1ull << (nv - 2)) : 0);
     }
-    int rc = device_alloc(ctx, slab_elems * es, &sc->slab);
+    sc->fused_shape = detect_fused_shape(nullptr, sc->tr.size(), num_vars, terms, n_terms, gl,
+                                         [&](uint32_t j) { return sc->tr[j].nv; },
+                                         [&](uint32_t j) { return sc->tr[j].dtype; });
+    // host-side plan, then ONE device allocation and ONE upload:
+    // [fold buffers | table descriptors | fold descriptors | terms | final values | round tables | groups | program]
+    std::vector<uint8_t> h_terms, h_groups, h_prog;
+    if (gl) {
+        build_terms<GlFam>(sc, terms, h_terms);
+        plan_program<GlFam>(sc, terms, h_groups, h_prog);
+    } else {
+        build_terms<FrFam>(sc, terms, h_terms);
+        plan_program<FrFam>(sc, terms, h_groups, h_prog);
+    }
+    size_t off = (slab_elems * es + 255) & ~(size_t)255;
+    auto take = [&](size_t bytes) {
+        const size_t o = off;
+        off = (off + bytes + 15) & ~(size_t)15;
+        return o;
+    };
+    const size_t nk = (size_t)num_vars * k;
+    const size_t o_desc = take(nk * sizeof(MleDesc)), o_fold = take(nk * sizeof(FoldDesc)), o_terms = take(h_terms.size()),
+                 o_final = take(k * es), o_rtab = take(sc->has_prog ? nk * sizeof(RoundTab) : 0),
+                 o_groups = take(h_groups.size()), o_prog = take(h_prog.size());
+    int rc = device_alloc(ctx, off, &sc->slab);
     if (rc != DPB_OK) {
         delete sc;
         return rc;
     }
     {
-        char* p = (char*)sc->slab;
+        char* base = (char*)sc->slab;
+        sc->d_desc = (MleDesc*)(base + o_desc);
+        sc->d_fold = (FoldDesc*)(base + o_fold);
+        sc->d_terms = base + o_terms;
+        sc->d_final = base + o_final;
+        sc->d_rtab = (RoundTab*)(base + o_rtab);
+        sc->d_groups = base + o_groups;
+        sc->d_prog = base + o_prog;
+        // ping-pong fold buffers of every table, at the front of the block
+        char* p = base;
         for (uint32_t j = 0; j < k; j++) {
             const uint32_t nv = sc->tr[j].nv;
             sc->tr[j].buf[0] = p;
@@ -784,25 +813,24 @@ int dpb_sumcheck_begin(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, ui
         dpb_sumcheck_free(sc);
         return code;
     };
-    rc = device_alloc(ctx, sc->h_desc.size() * sizeof(MleDesc), (void**)&sc->d_desc);
-    if (rc != DPB_OK) return cleanup(rc);
-    rc = device_alloc(ctx, sc->h_fold.size() * sizeof(FoldDesc), (void**)&sc->d_fold);
-    if (rc != DPB_OK) return cleanup(rc);
-    rc = device_alloc(ctx, k * es, &sc->d_final);
-    if (rc != DPB_OK) return cleanup(rc);
-    cudaError_t e = cudaMemcpyAsync(sc->d_desc, sc->h_desc.data(), sc->h_desc.size() * sizeof(MleDesc),
-                                    cudaMemcpyHostToDevice, ctx->stream);
-    if (e == cudaSuccess)
-        e = cudaMemcpyAsync(sc->d_fold, sc->h_fold.data(), sc->h_fold.size() * sizeof(FoldDesc),
-                            cudaMemcpyHostToDevice, ctx->stream);
-    if (e != cudaSuccess) return cleanup(fail(DPB_ECUDA, "descriptor upload: %s", cudaGetErrorString(e)));
-    rc = gl ? upload_terms<GlFam>(sc, terms) : upload_terms<FrFam>(sc, terms);
-    if (rc != DPB_OK) return cleanup(rc);
-    sc->fused_shape = detect_fused_shape(sc->h_desc.data(), sc->tr.size(), num_vars, terms, n_terms, gl,
-                                         [&](uint32_t j) { return sc->tr[j].nv; },
-                                         [&](uint32_t j) { return sc->tr[j].dtype; });
-    rc = gl ? setup_one_pass<GlFam>(sc, terms) : setup_one_pass<FrFam>(sc, terms);
-    if (rc != DPB_OK) return cleanup(rc);
+    {
+        std::vector<uint8_t> blob(off - o_desc, 0);
+        auto put = [&](size_t o, const void* src, size_t bytes) {
+            if (bytes) memcpy(blob.data() + (o - o_desc), src, bytes);
+        };
+        put(o_desc, sc->h_desc.data(), nk * sizeof(MleDesc));
+        put(o_fold, sc->h_fold.data(), nk * sizeof(FoldDesc));
+        put(o_terms, h_terms.data(), h_terms.size());
+        if (sc->has_prog) {
+            std::vector<RoundTab> rt;
+            build_round_tabs(sc, rt);
+            put(o_rtab, rt.data(), rt.size() * sizeof(RoundTab));
+        }
+        put(o_groups, h_groups.data(), h_groups.size());
+        put(o_prog, h_prog.data(), h_prog.size());
+        rc = upload_small(ctx, (char*)sc->slab + o_desc, blob.data(), blob.size());
+        if (rc != DPB_OK) return cleanup(rc);
+    }
     *out = sc;
     return DPB_OK;
 }
@@ -876,14 +904,7 @@ void dpb_sumcheck_free(dpb_sc* sc) {
     if (sc->tail) dpb_sumcheck_free(sc->tail);
     for (auto* m : sc->tail_mles) dpb_mle_free(m);
     device_free(sc->ctx, sc->tail_dev);
-    device_free(sc->ctx, sc->slab);
-    device_free(sc->ctx, sc->d_desc);
-    device_free(sc->ctx, sc->d_fold);
-    device_free(sc->ctx, sc->d_terms);
-    device_free(sc->ctx, sc->d_final);
-    device_free(sc->ctx, sc->d_rtab);
-    device_free(sc->ctx, sc->d_groups);
-    device_free(sc->ctx, sc->d_prog);
+    device_free(sc->ctx, sc->slab);  // the fold buffers and every descriptor array live in this one block
     delete sc;
 }
 

@@ -82,7 +82,15 @@ struct dpb_ctx {
     cudaStream_t tail_stream = nullptr;
     cudaEvent_t tail_ev[2] = {nullptr, nullptr};
     const void* tail_owner = nullptr;
+    // ring of pinned staging slots for small host-to-device copies that must not block (upload_small)
+    static constexpr int kStageSlots = 8;
+    static constexpr size_t kStageSlotBytes = 64 * 1024;
+    void* up_host = nullptr;
+    cudaEvent_t up_ev[kStageSlots] = {};
+    bool up_used[kStageSlots] = {};
+    int up_next = 0;
     bool tail_enabled = true;
+    uint64_t sumcheck_launches = 0;  // kernels launched by the sumcheck entry points
     unsigned long long tail_wait_ns = 5ull * 1000 * 1000 * 1000;
     // optional per-kernel timing log (dpb_profile_enable)
     bool profile = false;
@@ -121,6 +129,9 @@ inline ReduceScratch<F> reduce_scratch(const dpb_ctx* ctx) {
 
 int device_alloc(dpb_ctx* ctx, size_t bytes, void** out);
 void device_free(dpb_ctx* ctx, void* p);
+// Queues a copy of a (small) host buffer to device memory on the context's stream and returns at once: the
+// bytes are taken now, into pinned staging slots, so the caller may free or reuse `src` immediately.
+int upload_small(dpb_ctx* ctx, void* dst, const void* src, size_t bytes);
 int new_mle(dpb_ctx* ctx, int dtype, uint64_t len, dpb_mle** out);
 // copies `n` challenge elements from host memory to the staging area and returns the device pointer
 int stage_to_device(dpb_ctx* ctx, const void* host, size_t bytes, size_t offset, void** dev);

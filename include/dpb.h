@@ -126,6 +126,10 @@ int dpb_profile_read(dpb_ctx* ctx, dpb_profile_entry* out, uint32_t cap, uint32_
  * No reference counterpart: the reference's rounds are CPU loops. */
 int dpb_resident_rounds(dpb_ctx* ctx, int enable, uint32_t wait_ms);
 
+/* Kernels the sumcheck entry points (begin / round / finish) have launched on
+ * this context so far.  No reference counterpart. */
+uint64_t dpb_sumcheck_launches(const dpb_ctx* ctx);
+
 /* ---- multilinear tables (dp_crypto::poly::dense::DensePolynomial) ------ */
 /* Uploads `len` (a power of two) evaluations from host memory.
  * Replaces DensePolynomial::new / new_from_smart_slice
