@@ -451,8 +451,9 @@ static void launch_fused_fr(dpb_ctx* ctx, const MleDesc* desc, const FoldDesc* f
         ptrs.in[j] = round == 0 ? desc[j].ptr : folds[j].in;
         ptrs.out[j] = round == 0 ? nullptr : folds[j].out;
     }
-    if (round == 0) v2_eval0<OpsFr, K><<<grid, kThreads, 0, ctx->stream>>>(ptrs, n_pairs, rs, out);
-    else v2_fold_eval_fr<K><<<grid, kThreads, 0, ctx->stream>>>(ptrs, r, n_pairs, rs, out);
+    // two resident blocks per SM: these kernels wait on their multiply chains, more warps hide that
+    if (round == 0) v2_eval0<OpsFr, K, 2><<<grid, kThreads, 0, ctx->stream>>>(ptrs, n_pairs, rs, out);
+    else v2_fold_eval_fr<K, 2><<<grid, kThreads, 0, ctx->stream>>>(ptrs, r, n_pairs, rs, out);
 }
 
 static void launch_fused(dpb_ctx* ctx, const MleDesc* desc, const FoldDesc* folds, uint32_t k, uint32_t round,

@@ -222,8 +222,8 @@ __device__ __forceinline__ void publish(typename Ops::Acc (&acc)[K + 1], ReduceS
 }
 
 // Round 0: samples only.
-template <class Ops, int K>
-__global__ void __launch_bounds__(kThreads)
+template <class Ops, int K, int MINB = 1>
+__global__ void __launch_bounds__(kThreads, MINB)
     v2_eval0(V2Ptrs<K> ptrs, uint64_t n_pairs, ReduceScratch<typename Ops::F> rs, typename Ops::F::E* out) {
     typedef typename Ops::T T;
     typename Ops::Acc acc[K + 1];
@@ -300,8 +300,8 @@ __global__ void __launch_bounds__(kThreads, MINB)
 }
 
 // Rounds >= 1 over BN254.
-template <int K>
-__global__ void __launch_bounds__(kThreads)
+template <int K, int MINB = 1>
+__global__ void __launch_bounds__(kThreads, MINB)
     v2_fold_eval_fr(V2Ptrs<K> ptrs, Fr r, uint64_t n_pairs, ReduceScratch<FrFam> rs, Fr* out) {
     typedef OpsFr Ops;
     Fr acc[K + 1];
