@@ -70,6 +70,8 @@ SIGNATURES = {
     "dpb_mle_dtype": (_int, [_vp]),
     "dpb_mle_device_ptr": (_vp, [_vp]),
     "dpb_mle_view": (_int, [_vp, _u64, _u64, _pp]),
+    "dpb_mle_zero_padded": (_int, [_vp, _pp]),
+    "dpb_linear_combination": (_int, [_vp, _pp, _vp, _u32, _pp]),
     "dpb_eq_table": (_int, [_vp, _int, _vp, _u32, _pp]),
     "dpb_fix_high": (_int, [_vp, _vp, _vp, _u32, _pp]),
     "dpb_fix_low": (_int, [_vp, _vp, _vp, _u32, _pp]),
@@ -317,10 +319,26 @@ class Mle:
         check(lib.dpb_mle_view(self.h, offset, n, ctypes.byref(h)))
         return Mle(self.ctx, h)
 
+    def zero_padded(self):
+        """A view that a sumcheck over more variables treats as zero above this table's length."""
+        h = ctypes.c_void_p()
+        check(lib.dpb_mle_zero_padded(self.h, ctypes.byref(h)))
+        return Mle(self.ctx, h)
+
     def free(self):
         if self.h:
             lib.dpb_mle_free(self.h)
             self.h = None
+
+
+def linear_combination(ctx, mles, coeffs):
+    """DensePolynomial::linear_combination: sum_j coeffs[j] * mles[j]; shorter tables are zero-padded."""
+    k = len(mles)
+    hs = (ctypes.c_void_p * k)(*[m.h for m in mles])
+    c = np.ascontiguousarray(coeffs, dtype=np.uint64)
+    h = ctypes.c_void_p()
+    check(lib.dpb_linear_combination(ctx.h, hs, _buf(c), k, ctypes.byref(h)))
+    return Mle(ctx, h)
 
 
 def make_terms(terms, coeff_bytes):

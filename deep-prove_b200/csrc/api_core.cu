@@ -388,6 +388,61 @@ int dpb_mle_view(const dpb_mle* mle, uint64_t offset, uint64_t len, dpb_mle** ou
     return DPB_OK;
 }
 
+int dpb_mle_zero_padded(const dpb_mle* mle, dpb_mle** out) {
+    if (!mle || !out) return fail(DPB_EINVAL, "null argument");
+    dpb_mle* m = new (std::nothrow) dpb_mle();
+    if (!m) return fail(DPB_ENOMEM, "host allocation failed");
+    *m = *mle;
+    m->owns = false;
+    m->zero_pad = true;
+    *out = m;
+    return DPB_OK;
+}
+
+int dpb_linear_combination(dpb_ctx* ctx, dpb_mle* const* mles, const void* coeffs, uint32_t n, dpb_mle** out) {
+    if (!ctx || !mles || !coeffs || !out) return fail(DPB_EINVAL, "null argument");
+    if (n < 1) return fail(DPB_EINVAL, "no tables");
+    const bool gl = mles[0] && is_gl(mles[0]->dtype);
+    uint64_t max_len = 0;
+    std::vector<LinCombSrc> src(n);
+    for (uint32_t j = 0; j < n; j++) {
+        const dpb_mle* m = mles[j];
+        if (!m || m->ctx != ctx || !valid_dtype(m->dtype) || is_gl(m->dtype) != gl)
+            return fail(DPB_EINVAL, "table %u is null, foreign or of another field", j);
+        src[j].ptr = m->ptr;
+        src[j].len = m->len;
+        src[j].dtype = m->dtype;
+        src[j].pad = 0;
+        if (m->len > max_len) max_len = m->len;
+    }
+    const size_t es = gl ? 16 : 32;
+    void *d_src = nullptr, *d_coef = nullptr;
+    DPB_TRY(device_alloc(ctx, n * sizeof(LinCombSrc), &d_src));
+    int rc = device_alloc(ctx, n * es, &d_coef);
+    if (rc == DPB_OK) rc = upload_small(ctx, d_src, src.data(), n * sizeof(LinCombSrc));
+    if (rc == DPB_OK) rc = upload_small(ctx, d_coef, coeffs, n * es);
+    dpb_mle* res = nullptr;
+    if (rc == DPB_OK) rc = new_mle(ctx, gl ? DPB_GL_EXT : DPB_FR, max_len, &res);
+    if (rc == DPB_OK) {
+        if (gl)
+            linear_combination_kernel<GlFam><<<grid_for(ctx, max_len), kThreads, 0, ctx->stream>>>(
+                (const LinCombSrc*)d_src, (const Gl2*)d_coef, n, max_len, (Gl2*)res->ptr);
+        else
+            linear_combination_kernel<FrFam><<<grid_for(ctx, max_len), kThreads, 0, ctx->stream>>>(
+                (const LinCombSrc*)d_src, (const Fr*)d_coef, n, max_len, (Fr*)res->ptr);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) rc = fail(DPB_ECUDA, "linear combination: %s", cudaGetErrorString(e));
+    }
+    device_free(ctx, d_src);
+    device_free(ctx, d_coef);
+    if (rc != DPB_OK) {
+        if (res) dpb_mle_free(res);
+        return rc;
+    }
+    *out = res;
+    return DPB_OK;
+}
+
 int dpb_mle_free(dpb_mle* mle) {
     if (!mle) return DPB_OK;
     if (mle->owns) device_free(mle->ctx, mle->ptr);

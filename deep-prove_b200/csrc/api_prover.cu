@@ -4,6 +4,7 @@
 #include "../../include/dpb_prover.h"
 
 #include "common.cuh"
+#include "host/claims.hpp"
 #include "host/logup.hpp"
 #include "host/prover.hpp"
 #include "host/transcript.hpp"
@@ -164,6 +165,48 @@ int same_poly_impl(dpb_ctx* ctx, dpb_mle* poly, const void* points, uint32_t n_c
         for (const auto& v : m.evaluations) *o++ = v;
     memcpy(out_point, res.second.collect_raw_challenges().data(), n * sizeof(E));
     memcpy(out_eval, res.second.get_mle_flatten_final_evaluations().data(), sizeof(E));
+    return DPB_OK;
+}
+
+// prover.rs:113-122, 140-255
+template <class F, class T>
+int claims_impl(dpb_ctx* ctx, const dpb_committed_poly* polys, uint32_t n_polys, T& tr, void* out_evals,
+                uint32_t evals_room, void* out_point, uint32_t* out_num_vars, void* out_sc_evals, uint32_t sc_room,
+                void* out_chal, dpb_mle** out_rlc) {
+    typedef typename F::E E;
+    using namespace zkml::poly_commit;
+    std::vector<CommittedPoly<F>> in(n_polys);
+    for (uint32_t i = 0; i < n_polys; i++) {
+        const dpb_committed_poly& s = polys[i];
+        if (!s.chunks || s.n_chunks == 0) return fail(DPB_EINVAL, "polynomial %u has no chunks", i);
+        if (s.n_claims && (!s.claim_points || !s.claim_evals)) return fail(DPB_EINVAL, "polynomial %u has null claims", i);
+        in[i].chunks.assign(s.chunks, s.chunks + s.n_chunks);
+        for (auto* c : in[i].chunks)
+            if (!c || c->ctx != ctx) return fail(DPB_EINVAL, "polynomial %u has a null or foreign chunk", i);
+        if (s.n_chunks & (s.n_chunks - 1)) return fail(DPB_EINVAL, "polynomial %u: the chunk count must be a power of two", i);
+        const size_t pt_len = in[i].num_vars_for_chunk() + in[i].batching_vars();
+        for (uint32_t c = 0; c < s.n_claims; c++) {
+            Claim<F> cl;
+            cl.point.assign((const E*)s.claim_points + (size_t)c * pt_len, (const E*)s.claim_points + (size_t)(c + 1) * pt_len);
+            memcpy(&cl.eval, (const E*)s.claim_evals + c, sizeof(E));
+            in[i].claims.push_back(std::move(cl));
+        }
+    }
+    auto proof = claims_batching_sumcheck<F>(ctx, in, tr);
+    const size_t n = proof.max_num_vars;
+    if (out_num_vars) *out_num_vars = (uint32_t)n;
+    if (evals_room < n * 3) return fail(DPB_EINVAL, "room for %u round evaluations, %zu needed", evals_room, n * 3);
+    if (sc_room < proof.sumcheck_evals.size())
+        return fail(DPB_EINVAL, "room for %u evaluations, %zu needed", sc_room, proof.sumcheck_evals.size());
+    E* o = (E*)out_evals;
+    for (const auto& m : proof.sumcheck_proof.proofs)
+        for (const auto& v : m.evaluations) *o++ = v;
+    memcpy(out_point, proof.sumcheck_point.data(), n * sizeof(E));
+    memcpy(out_sc_evals, proof.sumcheck_evals.data(), proof.sumcheck_evals.size() * sizeof(E));
+    if (out_rlc) {
+        const std::vector<E> ch = batching_rlc<F>(ctx, proof, tr, out_rlc);
+        if (out_chal) memcpy(out_chal, ch.data(), ch.size() * sizeof(E));
+    }
     return DPB_OK;
 }
 
@@ -336,6 +379,22 @@ int dpb_same_poly_prove(dpb_ctx* ctx, dpb_mle* poly, const void* points, uint32_
     return guarded([&] {
         return t->gl ? same_poly_impl<GlFam>(ctx, poly, points, n_claims, n, *t->g, out_round_evals, out_point, out_eval)
                      : same_poly_impl<FrFam>(ctx, poly, points, n_claims, n, *t->f, out_round_evals, out_point, out_eval);
+    });
+}
+
+int dpb_claims_batching_prove(dpb_ctx* ctx, const dpb_committed_poly* polys, uint32_t n_polys, dpb_transcript* t,
+                              void* out_round_evals, uint32_t round_evals_cap, void* out_point,
+                              uint32_t* out_num_vars, void* out_sumcheck_evals, uint32_t evals_cap,
+                              void* out_rlc_challenges, dpb_mle** out_rlc) {
+    if (!ctx || !polys || !t || !out_round_evals || !out_point || !out_sumcheck_evals) return fail(DPB_EINVAL, "null argument");
+    if (n_polys == 0) return fail(DPB_EINVAL, "no committed polynomials");
+    if (!polys[0].chunks || !polys[0].chunks[0]) return fail(DPB_EINVAL, "polynomial 0 has no chunks");
+    if (is_gl(polys[0].chunks[0]->dtype) != t->gl) return fail(DPB_EINVAL, "transcript and tables are of different fields");
+    return guarded([&] {
+        return t->gl ? claims_impl<GlFam>(ctx, polys, n_polys, *t->g, out_round_evals, round_evals_cap, out_point,
+                                          out_num_vars, out_sumcheck_evals, evals_cap, out_rlc_challenges, out_rlc)
+                     : claims_impl<FrFam>(ctx, polys, n_polys, *t->f, out_round_evals, round_evals_cap, out_point,
+                                          out_num_vars, out_sumcheck_evals, evals_cap, out_rlc_challenges, out_rlc);
     });
 }
 

@@ -25,6 +25,7 @@ struct MleTrack {
     const void* orig;
     int dtype;
     uint32_t nv;
+    bool padded;   // fewer variables than the sumcheck and zero above its length (else: constant in early rounds)
     void* buf[2];  // ping-pong targets of the folds (challenge-element layout)
 };
 
@@ -48,6 +49,11 @@ struct dpb_sc {
     void* d_final = nullptr;  // k challenge elements
     int fused_shape = 0;      // see fused_kernels.cuh
     // one-pass generic rounds (generic_round.cuh); off when the tables' slots do not fit in shared memory
+    // zero-padded tables: each term is evaluated over the pairs where all its padded factors hold data
+    bool ranged = false;
+    uint64_t* d_tile_prefix = nullptr;  // [n][n_terms + 1]
+    uint64_t* d_term_pairs = nullptr;   // [n][n_terms]
+    std::vector<uint64_t> total_tiles;  // per round
     bool one_pass = false;       // large generic rounds run sc_round_generic
     bool has_prog = false;       // d_rtab / d_groups / d_prog are laid out (every shape that fits)
     uint32_t tail_start = ~0u;   // first round the resident last-rounds kernel may take over
@@ -82,7 +88,7 @@ namespace dpb {
 static void table_at_round(const dpb_sc* sc, uint32_t j, uint32_t i, const void** ptr, int* dtype,
                            bool* active) {
     const MleTrack& t = sc->tr[j];
-    const uint32_t first_active = sc->n - t.nv;
+    const uint32_t first_active = t.padded ? 0 : sc->n - t.nv;
     if (i < first_active) {
         *ptr = t.orig;
         *dtype = t.dtype;
@@ -112,6 +118,23 @@ static void build_terms(const dpb_sc* sc, const dpb_term* terms, std::vector<uin
         for (int j = 0; j < DPB_MAX_FACTORS; j++) h[t].idx[j] = terms[t].idx[j];
     }
     out.assign((const uint8_t*)h.data(), (const uint8_t*)h.data() + h.size() * sizeof(TermDev<F>));
+}
+
+// entries a zero-padded table holds in round i (it keeps one entry once all its own variables are bound)
+static uint64_t padded_entries(const MleTrack& t, uint32_t i) { return t.nv > i ? 1ull << (t.nv - i) : 1ull; }
+
+template <class F, int D>
+static void launch_eval_ranged(dpb_sc* sc, uint32_t round) {
+    dpb_ctx* ctx = sc->ctx;
+    const uint64_t tiles = sc->total_tiles[round];
+    uint64_t blocks = std::min<uint64_t>(tiles ? tiles : 1, (uint64_t)ctx->sm_count * 8);
+    if (blocks > ctx->max_blocks) blocks = ctx->max_blocks;
+    const size_t prefix_bytes = ((size_t)sc->n_terms + 1) * 8;
+    const bool in_smem = prefix_bytes <= 40 * 1024;
+    sc_eval_ranged<F, D><<<(uint32_t)blocks, kThreads, in_smem ? prefix_bytes : 0, ctx->stream>>>(
+        sc->d_desc + (size_t)round * sc->k, (const TermDev<F>*)sc->d_terms, sc->n_terms,
+        sc->d_tile_prefix + (size_t)round * (sc->n_terms + 1), sc->d_term_pairs + (size_t)round * sc->n_terms,
+        in_smem ? 1u : 0u, reduce_scratch<F>(ctx), (typename F::E*)ctx->round_out);
 }
 
 template <class F, int D>
@@ -546,14 +569,26 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
             dim3 grid(grid_for(ctx, sc->max_fold_out[i], 4), sc->n_fold[i]);
             sc_fold_generic<F><<<grid, kThreads, 0, ctx->stream>>>(sc->d_fold + (size_t)i * sc->k, r);
         }
-        switch (sc->d) {
-            case 1: launch_eval<F, 1>(sc, i, n_pairs); break;
-            case 2: launch_eval<F, 2>(sc, i, n_pairs); break;
-            case 3: launch_eval<F, 3>(sc, i, n_pairs); break;
-            case 4: launch_eval<F, 4>(sc, i, n_pairs); break;
-            case 5: launch_eval<F, 5>(sc, i, n_pairs); break;
-            case 6: launch_eval<F, 6>(sc, i, n_pairs); break;
-            default: return fail(DPB_EINVAL, "degree %u not supported", sc->d);
+        if (sc->ranged) {
+            switch (sc->d) {
+                case 1: launch_eval_ranged<F, 1>(sc, i); break;
+                case 2: launch_eval_ranged<F, 2>(sc, i); break;
+                case 3: launch_eval_ranged<F, 3>(sc, i); break;
+                case 4: launch_eval_ranged<F, 4>(sc, i); break;
+                case 5: launch_eval_ranged<F, 5>(sc, i); break;
+                case 6: launch_eval_ranged<F, 6>(sc, i); break;
+                default: return fail(DPB_EINVAL, "degree %u not supported", sc->d);
+            }
+        } else {
+            switch (sc->d) {
+                case 1: launch_eval<F, 1>(sc, i, n_pairs); break;
+                case 2: launch_eval<F, 2>(sc, i, n_pairs); break;
+                case 3: launch_eval<F, 3>(sc, i, n_pairs); break;
+                case 4: launch_eval<F, 4>(sc, i, n_pairs); break;
+                case 5: launch_eval<F, 5>(sc, i, n_pairs); break;
+                case 6: launch_eval<F, 6>(sc, i, n_pairs); break;
+                default: return fail(DPB_EINVAL, "degree %u not supported", sc->d);
+            }
         }
     }
     DPB_CUDA(cudaGetLastError());
@@ -726,20 +761,48 @@ int dpb_sumcheck_begin(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, ui
         sc->tr[j].orig = m->ptr;
         sc->tr[j].dtype = m->dtype;
         sc->tr[j].nv = nv;
-        slab_elems += (1ull << (nv - 1)) + (nv >= 2 ? (1ull << (nv - 2)) : 0);
+        sc->tr[j].padded = m->zero_pad && nv < num_vars;
+        if (sc->tr[j].padded) sc->ranged = true;
+        // a zero-padded table keeps folding (as one entry) after its own variables are bound: both buffers exist
+        slab_elems += (1ull << (nv - 1)) + (nv >= 2 ? (1ull << (nv - 2)) : (sc->tr[j].padded ? 1 : 0));
     }
-    sc->fused_shape = detect_fused_shape(nullptr, sc->tr.size(), num_vars, terms, n_terms, gl,
-                                         [&](uint32_t j) { return sc->tr[j].nv; },
-                                         [&](uint32_t j) { return sc->tr[j].dtype; });
+    sc->fused_shape = sc->ranged ? kFusedNone
+                                 : detect_fused_shape(nullptr, sc->tr.size(), num_vars, terms, n_terms, gl,
+                                                      [&](uint32_t j) { return sc->tr[j].nv; },
+                                                      [&](uint32_t j) { return sc->tr[j].dtype; });
     // host-side plan, then ONE device allocation and ONE upload:
     // [fold buffers | table descriptors | fold descriptors | terms | final values | round tables | groups | program]
     std::vector<uint8_t> h_terms, h_groups, h_prog;
     if (gl) {
         build_terms<GlFam>(sc, terms, h_terms);
-        plan_program<GlFam>(sc, terms, h_groups, h_prog);
+        if (!sc->ranged) plan_program<GlFam>(sc, terms, h_groups, h_prog);
     } else {
         build_terms<FrFam>(sc, terms, h_terms);
-        plan_program<FrFam>(sc, terms, h_groups, h_prog);
+        if (!sc->ranged) plan_program<FrFam>(sc, terms, h_groups, h_prog);
+    }
+    // ranged evaluation: per round and term, the pairs to visit and the tiles that cover them
+    std::vector<uint64_t> h_tile_prefix, h_term_pairs;
+    if (sc->ranged) {
+        h_tile_prefix.resize((size_t)num_vars * (n_terms + 1));
+        h_term_pairs.resize((size_t)num_vars * n_terms);
+        sc->total_tiles.assign(num_vars, 0);
+        for (uint32_t i = 0; i < num_vars; i++) {
+            uint64_t run = 0;
+            for (uint32_t t = 0; t < n_terms; t++) {
+                uint64_t pairs = 1ull << (num_vars - i - 1);
+                for (uint32_t j = 0; j < terms[t].n_factors; j++) {
+                    const MleTrack& tk = sc->tr[terms[t].idx[j]];
+                    if (!tk.padded) continue;
+                    const uint64_t e = padded_entries(tk, i);
+                    pairs = std::min(pairs, e >= 2 ? e / 2 : 1);
+                }
+                h_term_pairs[(size_t)i * n_terms + t] = pairs;
+                h_tile_prefix[(size_t)i * (n_terms + 1) + t] = run;
+                run += (pairs + kThreads - 1) / kThreads;
+            }
+            h_tile_prefix[(size_t)i * (n_terms + 1) + n_terms] = run;
+            sc->total_tiles[i] = run;
+        }
     }
     size_t off = (slab_elems * es + 255) & ~(size_t)255;
     auto take = [&](size_t bytes) {
@@ -750,7 +813,8 @@ int dpb_sumcheck_begin(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, ui
     const size_t nk = (size_t)num_vars * k;
     const size_t o_desc = take(nk * sizeof(MleDesc)), o_fold = take(nk * sizeof(FoldDesc)), o_terms = take(h_terms.size()),
                  o_final = take(k * es), o_rtab = take(sc->has_prog ? nk * sizeof(RoundTab) : 0),
-                 o_groups = take(h_groups.size()), o_prog = take(h_prog.size());
+                 o_groups = take(h_groups.size()), o_prog = take(h_prog.size()),
+                 o_tiles = take(h_tile_prefix.size() * 8), o_pairs = take(h_term_pairs.size() * 8);
     int rc = device_alloc(ctx, off, &sc->slab);
     if (rc != DPB_OK) {
         delete sc;
@@ -765,14 +829,17 @@ int dpb_sumcheck_begin(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, ui
         sc->d_rtab = (RoundTab*)(base + o_rtab);
         sc->d_groups = base + o_groups;
         sc->d_prog = base + o_prog;
+        sc->d_tile_prefix = (uint64_t*)(base + o_tiles);
+        sc->d_term_pairs = (uint64_t*)(base + o_pairs);
         // ping-pong fold buffers of every table, at the front of the block
         char* p = base;
         for (uint32_t j = 0; j < k; j++) {
             const uint32_t nv = sc->tr[j].nv;
             sc->tr[j].buf[0] = p;
             p += (es << (nv - 1));
-            sc->tr[j].buf[1] = nv >= 2 ? p : nullptr;
-            if (nv >= 2) p += (es << (nv - 2));
+            const bool second = nv >= 2 || sc->tr[j].padded;
+            sc->tr[j].buf[1] = second ? p : nullptr;
+            if (second) p += nv >= 2 ? (es << (nv - 2)) : es;
         }
     }
     // descriptors for every round
@@ -791,6 +858,7 @@ int dpb_sumcheck_begin(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, ui
             md.ptr = ptr;
             md.dtype = dt;
             md.shift = active ? -1 : (int32_t)(v - 1 - sc->tr[j].nv);
+            md.limit = sc->tr[j].padded ? padded_entries(sc->tr[j], i) : kNoLimit;
             // fold that must run before round i: tables that were active in round i-1
             if (i >= 1) {
                 const void* pptr;
@@ -803,7 +871,12 @@ int dpb_sumcheck_begin(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, ui
                     fd.out = (void*)ptr;
                     fd.dtype_in = pdt;
                     fd.pad = 0;
-                    fd.n_out = 1ull << (sc->tr[j].nv - (i - (num_vars - sc->tr[j].nv)));
+                    fd.limit_in = kNoLimit;
+                    if (sc->tr[j].padded) {
+                        fd.limit_in = padded_entries(sc->tr[j], i - 1);
+                        fd.n_out = padded_entries(sc->tr[j], i);
+                    } else
+                        fd.n_out = 1ull << (sc->tr[j].nv - (i - (num_vars - sc->tr[j].nv)));
                     if (fd.n_out > sc->max_fold_out[i]) sc->max_fold_out[i] = fd.n_out;
                     sc->n_fold[i]++;
                 }
@@ -829,6 +902,8 @@ int dpb_sumcheck_begin(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, ui
         }
         put(o_groups, h_groups.data(), h_groups.size());
         put(o_prog, h_prog.data(), h_prog.size());
+        put(o_tiles, h_tile_prefix.data(), h_tile_prefix.size() * 8);
+        put(o_pairs, h_term_pairs.data(), h_term_pairs.size() * 8);
         rc = upload_small(ctx, (char*)sc->slab + o_desc, blob.data(), blob.size());
         if (rc != DPB_OK) return cleanup(rc);
     }
@@ -847,6 +922,8 @@ int dpb_sumcheck_begin_sharded(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* 
     if (!ctx->nccl_comm) return fail(DPB_ESTATE, "the context has no communicator (dpb_comm_init)");
     if (num_vars <= c) return fail(DPB_EINVAL, "%u variables cannot be sharded over %d ranks", num_vars, ctx->nranks);
     const uint32_t n_loc = num_vars - c;
+    for (uint32_t j = 0; j < k; j++)
+        if (mles[j] && mles[j]->zero_pad) return fail(DPB_EINVAL, "zero-padded tables cannot be sharded (table %u)", j);
     for (uint32_t j = 0; j < k; j++)
         if (!mles[j] || mles[j]->len != (1ull << n_loc))
             return fail(DPB_EINVAL, "a sharded sumcheck needs every table to hold its 2^%u-entry shard (table %u)", n_loc, j);

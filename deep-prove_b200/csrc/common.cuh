@@ -104,6 +104,7 @@ struct dpb_mle {
     uint64_t len = 0;
     void* ptr = nullptr;
     bool owns = false;
+    bool zero_pad = false;  // in a sumcheck over more variables: zero above its length (else: constant in the early rounds)
 };
 
 namespace dpb {

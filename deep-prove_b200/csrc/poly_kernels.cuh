@@ -99,4 +99,30 @@ __global__ void fix_low_pass(const void* __restrict__ in, int dtype_in,
     }
 }
 
+// One source table of a linear combination.
+struct LinCombSrc {
+    const void* ptr;
+    uint64_t len;
+    int32_t dtype;
+    int32_t pad;
+};
+
+// out[i] = sum_j coeff[j] * table_j[i], tables shorter than the output read as zero beyond their length.
+// Consecutive threads read consecutive entries of each table in turn.
+template <class F>
+__global__ void __launch_bounds__(kThreads)
+    linear_combination_kernel(const LinCombSrc* __restrict__ src, const typename F::E* __restrict__ coeff, uint32_t n,
+                              uint64_t len, typename F::E* __restrict__ out) {
+    typedef typename F::E E;
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < len; i += stride) {
+        E acc = F::zero();
+        for (uint32_t j = 0; j < n; j++) {
+            const LinCombSrc s = src[j];
+            if (i < s.len) acc = F::add(acc, F::mul(coeff[j], F::load(s.ptr, s.dtype, i)));
+        }
+        F::store(out, i, acc);
+    }
+}
+
 }  // namespace dpb

@@ -12,10 +12,13 @@ namespace dpb {
 // One registered table as a round sees it.
 struct MleDesc {
     const void* ptr;
-    int32_t dtype;  // storage layout of `ptr`
-    int32_t shift;  // < 0: table has all remaining variables (entries 2p, 2p+1);
-                    // >= 0: table is constant in this round, entry p >> shift
+    int32_t dtype;   // storage layout of `ptr`
+    int32_t shift;   // < 0: table has all remaining variables (entries 2p, 2p+1);
+                     // >= 0: table is constant in this round, entry p >> shift
+    uint64_t limit;  // entries the table really holds; entries from `limit` on read as zero
+                     // (zero-padded tables); kNoLimit for every other table
 };
+constexpr uint64_t kNoLimit = ~0ull;
 
 struct FoldDesc {
     const void* in;
@@ -23,7 +26,23 @@ struct FoldDesc {
     int32_t dtype_in;
     uint32_t pad;
     uint64_t n_out;
+    uint64_t limit_in;  // entries `in` really holds (kNoLimit: all)
 };
+
+// entries 2p and 2p+1 of a table that reads as zero from `limit` on
+template <class F>
+__device__ __forceinline__ void load_pair_limited(const void* ptr, int dtype, uint64_t limit, uint64_t p,
+                                                  typename F::E& a, typename F::E& b) {
+    if (2 * p + 1 < limit) {
+        F::load_pair(ptr, dtype, p, a, b);
+    } else if (2 * p < limit) {
+        a = F::load(ptr, dtype, 2 * p);
+        b = F::zero();
+    } else {
+        a = F::zero();
+        b = F::zero();
+    }
+}
 
 template <class F>
 struct TermDev {
@@ -159,7 +178,7 @@ __global__ void __launch_bounds__(kThreads)
                 const MleDesc md = mles[tm.idx[j]];
                 E f0, f1;
                 if (md.shift < 0) {
-                    F::load_pair(md.ptr, md.dtype, p, f0, f1);
+                    load_pair_limited<F>(md.ptr, md.dtype, md.limit, p, f0, f1);
                 } else {
                     f0 = F::load(md.ptr, md.dtype, p >> md.shift);
                     f1 = f0;
@@ -189,6 +208,74 @@ __global__ void __launch_bounds__(kThreads)
     grid_sum_publish<F, D + 1>(acc, rs, out);
 }
 
+// Round evaluation when tables are zero-padded: a term is zero wherever one of
+// its padded factors is, so each term is evaluated only over the pairs where all
+// of them hold data (`term_pairs[t]`).  Work is cut into tiles of one block's
+// width; `tile_prefix[t]` is the first tile of term t (n_terms + 1 entries), and a
+// block finds the term of a tile by binary search.
+template <class F, int D>
+__global__ void __launch_bounds__(kThreads)
+    sc_eval_ranged(const MleDesc* __restrict__ mles, const TermDev<F>* __restrict__ terms, uint32_t n_terms,
+                   const uint64_t* __restrict__ tile_prefix_g, const uint64_t* __restrict__ term_pairs,
+                   uint32_t prefix_in_smem, ReduceScratch<F> rs, typename F::E* out) {
+    typedef typename F::E E;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const uint64_t* tile_prefix = tile_prefix_g;
+    if (prefix_in_smem) {  // the search below runs per tile: keep its table on chip when it fits
+        uint64_t* sp = (uint64_t*)smem_raw;
+        for (uint32_t i = threadIdx.x; i <= n_terms; i += blockDim.x) sp[i] = tile_prefix_g[i];
+        __syncthreads();
+        tile_prefix = sp;
+    }
+    E acc[D + 1];
+#pragma unroll
+    for (int x = 0; x <= D; x++) acc[x] = F::zero();
+    const uint64_t total_tiles = tile_prefix[n_terms];
+    for (uint64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        uint32_t lo = 0, hi = n_terms;  // the term t with tile_prefix[t] <= tile < tile_prefix[t + 1]
+        while (hi - lo > 1) {
+            const uint32_t mid = (lo + hi) >> 1;
+            if (tile_prefix[mid] <= tile) lo = mid;
+            else hi = mid;
+        }
+        const uint32_t t = lo;
+        const uint64_t p = (tile - tile_prefix[t]) * kThreads + threadIdx.x;
+        if (p >= term_pairs[t]) continue;
+        const TermDev<F>& tm = terms[t];
+        const uint32_t nf = tm.n_factors;
+        E prod[D + 1];
+        for (uint32_t j = 0; j < nf; j++) {
+            const MleDesc md = mles[tm.idx[j]];
+            E f0, f1;
+            if (md.shift < 0) {
+                load_pair_limited<F>(md.ptr, md.dtype, md.limit, p, f0, f1);
+            } else {
+                f0 = F::load(md.ptr, md.dtype, p >> md.shift);
+                f1 = f0;
+            }
+            if (j == 0 && !tm.coeff_is_one) {
+                f0 = F::mul(f0, tm.coeff);
+                f1 = F::mul(f1, tm.coeff);
+            }
+            const E delta = F::sub(f1, f0);
+            E val = f0;
+#pragma unroll
+            for (int x = 0; x <= D; x++) {
+                prod[x] = (j == 0) ? val : F::mul(prod[x], val);
+                if (x < D) val = F::add(val, delta);
+            }
+        }
+        if (nf == 0) {
+#pragma unroll
+            for (int x = 0; x <= D; x++) acc[x] = F::add(acc[x], tm.coeff);
+        } else {
+#pragma unroll
+            for (int x = 0; x <= D; x++) acc[x] = F::add(acc[x], prod[x]);
+        }
+    }
+    grid_sum_publish<F, D + 1>(acc, rs, out);
+}
+
 // Binds the lowest remaining variable of several tables in one launch:
 // out[p] = in[2p] + r * (in[2p+1] - in[2p]).   blockIdx.y selects the table.
 template <class F>
@@ -199,7 +286,7 @@ __global__ void __launch_bounds__(kThreads)
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
     for (uint64_t p = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; p < d.n_out; p += stride) {
         E f0, f1;
-        F::load_pair(d.in, d.dtype_in, p, f0, f1);
+        load_pair_limited<F>(d.in, d.dtype_in, d.limit_in, p, f0, f1);
         F::store(d.out, p, F::add(f0, F::mul(r, F::sub(f1, f0))));
     }
 }
@@ -214,7 +301,7 @@ __global__ void sc_final_evals(const MleDesc* __restrict__ mles, uint32_t k, typ
     if (j >= k) return;
     const MleDesc md = mles[j];
     E f0, f1;
-    F::load_pair(md.ptr, md.dtype, 0, f0, f1);
+    load_pair_limited<F>(md.ptr, md.dtype, md.limit, 0, f0, f1);
     out[j] = F::add(f0, F::mul(r, F::sub(f1, f0)));
     if (j == 0) __threadfence_system();
 }

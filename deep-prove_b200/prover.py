@@ -24,6 +24,11 @@ class LogupInputStruct(ctypes.Structure):
                 ("constant_challenge", ctypes.c_void_p), ("column_separation_challenge", ctypes.c_void_p)]
 
 
+class CommittedPolyStruct(ctypes.Structure):
+    _fields_ = [("chunks", _pp), ("n_chunks", ctypes.c_uint32), ("n_claims", ctypes.c_uint32),
+                ("claim_points", ctypes.c_void_p), ("claim_evals", ctypes.c_void_p)]
+
+
 _size_t = ctypes.c_size_t
 PROVER_SIGNATURES = {
     "dpb_transcript_new": (_int, [_int, _vp, _size_t, _pp]),
@@ -42,6 +47,8 @@ PROVER_SIGNATURES = {
                                           ctypes.POINTER(_u32)]),
     "dpb_hadamard_prove": (_int, [_vp, _vp, _vp, _vp, _u32, _vp, _vp, _vp, _vp]),
     "dpb_same_poly_prove": (_int, [_vp, _vp, _vp, _u32, _u32, _vp, _vp, _vp, _vp]),
+    "dpb_claims_batching_prove": (_int, [_vp, ctypes.POINTER(CommittedPolyStruct), _u32, _vp, _vp, _u32, _vp,
+                                         ctypes.POINTER(_u32), _vp, _u32, _vp, _pp]),
     "dpb_logup_batch_prove": (_int, [_vp, ctypes.POINTER(LogupInputStruct), _u32, _vp, _pp]),
     "dpb_logup_proof_serialize": (_int, [_vp, _vp, _size_t, ctypes.POINTER(_size_t)]),
     "dpb_logup_proof_free": (None, [_vp]),
@@ -221,6 +228,50 @@ def same_poly_prove(ctx, transcript, poly, points):
     ev = np.zeros(w, dtype=np.uint64)
     check(lib.dpb_same_poly_prove(ctx.h, poly.h, _buf(p), m, n, transcript.h, _buf(evals), _buf(point), _buf(ev)))
     return evals, point, ev
+
+
+class CommittedPoly:
+    """A committed polynomial as its chunk tables (a power of two of them, equal lengths) and the claims
+    (point, eval) to batch for it (zkml/src/poly_commit/mod.rs:32-93)."""
+
+    def __init__(self, chunks, claims):
+        self.chunks = list(chunks)
+        self.claims = list(claims)
+
+
+def claims_batching_prove(ctx, transcript, polys, with_rlc=True):
+    """CommitmentProver::claims_batching_sumcheck and the random linear combination that follows it
+    (zkml/src/poly_commit/prover.rs:113-131, 140-255).
+    Returns dict(sumcheck [n,3,w], point [n,w], sumcheck_evals [chunks,w], rlc_challenges, rlc Mle)."""
+    from . import Mle
+    w = elem_words(chal_dtype(polys[0].chunks[0].dtype))
+    arr = (CommittedPolyStruct * len(polys))()
+    keep = []
+    total_chunks, max_vars = 0, 0
+    for i, p in enumerate(polys):
+        hs = (ctypes.c_void_p * len(p.chunks))(*[m.h for m in p.chunks])
+        pts = _scalars([c[0] for c in p.claims]).reshape(len(p.claims), -1, w) if p.claims else np.zeros((0, 0, w), np.uint64)
+        evs = _scalars([c[1] for c in p.claims]).reshape(len(p.claims), w) if p.claims else np.zeros((0, w), np.uint64)
+        keep += [hs, pts, evs]
+        arr[i].chunks = hs
+        arr[i].n_chunks = len(p.chunks)
+        arr[i].n_claims = len(p.claims)
+        arr[i].claim_points = pts.ctypes.data if p.claims else None
+        arr[i].claim_evals = evs.ctypes.data if p.claims else None
+        total_chunks += len(p.chunks)
+        max_vars = max(max_vars, int(p.chunks[0].len).bit_length() - 1)
+    evals = np.zeros((max_vars, 3, w), dtype=np.uint64)
+    point = np.zeros((max_vars, w), dtype=np.uint64)
+    sc_evals = np.zeros((total_chunks, w), dtype=np.uint64)
+    chal = np.zeros((total_chunks, w), dtype=np.uint64)
+    nv = ctypes.c_uint32()
+    h = ctypes.c_void_p()
+    check(lib.dpb_claims_batching_prove(ctx.h, arr, len(polys), transcript.h, _buf(evals), max_vars * 3, _buf(point),
+                                        ctypes.byref(nv), _buf(sc_evals), total_chunks,
+                                        _buf(chal) if with_rlc else None, ctypes.byref(h) if with_rlc else None))
+    assert nv.value == max_vars
+    return dict(sumcheck=evals, point=point, sumcheck_evals=sc_evals, rlc_challenges=chal if with_rlc else None,
+                rlc=Mle(ctx, h) if with_rlc else None)
 
 
 class LogUpInput:

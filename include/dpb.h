@@ -150,6 +150,18 @@ void* dpb_mle_device_ptr(const dpb_mle* mle);
 /* A borrowed view of `len` elements starting at `offset` (DensePolynomial::as_view_chunks,
  * and the low/high half split of zkml/src/lookup/logup_gkr/circuit.rs:260-261). */
 int dpb_mle_view(const dpb_mle* mle, uint64_t offset, uint64_t len, dpb_mle** out);
+/* A borrowed view that a sumcheck over MORE variables treats as zero-padded:
+ * the table keeps its entries at indices below its length and reads as zero
+ * above, i.e. it is a function of the FIRST variables times (1 - x_j) for every
+ * added variable j (DensePolynomial::as_view + zero_pad_num_vars,
+ * zkml/src/poly_commit/prover.rs:216-226; the verifier's formula for the padded
+ * eq tables, zkml/src/poly_commit/verifier.rs:300-311, pins the convention).
+ * Without this flag a smaller table is a function of the LAST variables. */
+int dpb_mle_zero_padded(const dpb_mle* mle, dpb_mle** out);
+/* out = sum_j coeffs[j] * mles[j] over challenge elements; shorter tables count
+ * as zero-padded; the result has the length of the longest
+ * (DensePolynomial::linear_combination, zkml/src/poly_commit/prover.rs:122). */
+int dpb_linear_combination(dpb_ctx* ctx, dpb_mle* const* mles, const void* coeffs, uint32_t n, dpb_mle** out);
 
 /* eq(x, point) for all x in {0,1}^m, little-endian index
  * (dp_crypto::poly::eq::evals; call sites zkml/src/lookup/logup_gkr/prover.rs:247-249,

@@ -88,6 +88,35 @@ int dpb_hadamard_prove(dpb_ctx* ctx, dpb_mle* v1, dpb_mle* v2, const void* claim
 int dpb_same_poly_prove(dpb_ctx* ctx, dpb_mle* poly, const void* points, uint32_t n_claims, uint32_t n,
                         dpb_transcript* t, void* out_round_evals, void* out_point, void* out_eval);
 
+/* ---- claim batching of the opening proof ------------------------------------- */
+/* One committed polynomial: its n_chunks (a power of two) chunk tables of equal
+ * length, and the claims to batch for it.  A claim's point has
+ * log2(chunk length) + log2(n_chunks) coordinates (ChunkedCommitment,
+ * zkml/src/poly_commit/mod.rs:32-93). */
+typedef struct dpb_committed_poly {
+    dpb_mle* const* chunks;
+    uint32_t n_chunks;
+    uint32_t n_claims;
+    const void* claim_points; /* n_claims points, row-major */
+    const void* claim_evals;  /* n_claims elements */
+} dpb_committed_poly;
+
+/* CommitmentProver::claims_batching_sumcheck (zkml/src/poly_commit/prover.rs:140-255)
+ * and, when out_rlc is not NULL, the step that follows it in
+ * CommitmentProver::prove (prover.rs:113-122): point and evaluations go into the
+ * transcript, one challenge per committed chunk is drawn, and the random linear
+ * combination of the chunks is built (the polynomial the commitment scheme
+ * opens; the scheme itself is outside this library).  `polys` in the order the
+ * reference visits them: model commitments, then witness commitments.
+ * out_round_evals[num_vars*3] (round_evals_cap elements of room),
+ * out_point[num_vars], out_sumcheck_evals[total chunks] (evals_cap elements of
+ * room), out_rlc_challenges[total chunks] (may be NULL with out_rlc);
+ * *out_num_vars = the largest chunk's variables.  The caller frees *out_rlc. */
+int dpb_claims_batching_prove(dpb_ctx* ctx, const dpb_committed_poly* polys, uint32_t n_polys, dpb_transcript* t,
+                              void* out_round_evals, uint32_t round_evals_cap, void* out_point,
+                              uint32_t* out_num_vars, void* out_sumcheck_evals, uint32_t evals_cap,
+                              void* out_rlc_challenges, dpb_mle** out_rlc);
+
 /* ---- batched logup-GKR ------------------------------------------------------- */
 /* LogUpInput (zkml/src/lookup/logup_gkr/structs.rs:138-154) */
 typedef struct dpb_logup_input {

@@ -903,6 +903,125 @@ def same_poly_prove(F, transcript, poly, claims):
     return dict(sumcheck=proof, eval=finals[0], point=point, challenges=chal)
 
 
+# ------------------------------------------------ claim batching (opening proof)
+def zero_pad_table(F, table, num_vars):
+    """DensePolynomial::zero_pad_num_vars, materialised: entries above the table's length are zero, i.e. the
+    padded polynomial is p(x_0..x_{m-1}) * prod_{j >= m} (1 - x_j) (the verifier's formula for padded eq tables,
+    zkml/src/poly_commit/verifier.rs:300-311, pins this convention)."""
+    t = _widen(F, table)
+    out = np.zeros((1 << num_vars, F.elem_words), dtype=np.uint64)
+    out[: t.shape[0]] = t
+    return out
+
+
+def linear_combination(F, tables, coeffs):
+    """DensePolynomial::linear_combination (zkml/src/poly_commit/prover.rs:122); shorter tables are zero-padded."""
+    n = max(table_len(t) for t in tables)
+    acc = [F.zero] * n
+    for t, c in zip(tables, coeffs):
+        for i, v in enumerate(array_to_scalars(F, _widen(F, t))):
+            acc[i] = F.add(acc[i], F.mul(c, v))
+    return scalars_to_array(F, acc)
+
+
+class CommittedPoly:
+    """A committed polynomial as its M = 2^b chunk tables of equal length (ChunkedCommitment,
+    zkml/src/poly_commit/mod.rs:32-93) with the claims to batch for it."""
+
+    def __init__(self, chunks, claims):
+        self.chunks = chunks
+        self.claims = claims  # [(point over chunk_vars + b coordinates, eval)]
+        self.num_chunks = len(chunks)
+        self.batch_vars = (self.num_chunks - 1).bit_length()
+        assert 1 << self.batch_vars == self.num_chunks
+        self.chunk_vars = (table_len(chunks[0]) - 1).bit_length()
+
+    def eq_point_per_chunk(self, point):
+        return point[: len(point) - self.batch_vars]
+
+    def batching_coefficients_for_chunks(self, F, point):
+        coords = point[len(point) - self.batch_vars:]
+        return [identity_eval(F, coords, [F.from_int((i >> b) & 1) for b in range(self.batch_vars)])
+                for i in range(self.num_chunks)]
+
+
+def claims_batching_expression(F, polys, coeffs_per_poly):
+    """build_sumcheck_expression (zkml/src/poly_commit/mod.rs:96-148)."""
+    eq_offset = sum(p.num_chunks for p in polys)
+    e = Expr.const(F.zero)
+    total_terms = total_polys = 0
+    for p, per_claim in zip(polys, coeffs_per_poly):
+        for i, chunk_coeffs in enumerate(per_claim):
+            inner = Expr.const(F.zero)
+            for ci, c in enumerate(chunk_coeffs):
+                inner = inner + Expr.const(c) * Expr.wit(total_polys + ci)
+            e = e + Expr.chal(0, total_terms + i, F.one, F.zero) * inner * Expr.wit(total_terms + i + eq_offset)
+        total_terms += len(per_claim)
+        total_polys += p.num_chunks
+    return e
+
+
+def claims_batching_prove(F, polys, transcript):
+    """CommitmentProver::claims_batching_sumcheck + the random linear combination that follows it
+    (zkml/src/poly_commit/prover.rs:113-131, 140-255).  `polys` in the order the reference visits them
+    (model commitments, then witness commitments)."""
+    eq_tables, committed, coeffs_per_poly = [], [], []
+    max_vars = 0
+    for p in polys:
+        per_claim = []
+        for point, ev in p.claims:
+            transcript.append_scalars([ev])
+            eq_tables.append(eq_evals(F, p.eq_point_per_chunk(point)))
+            per_claim.append(p.batching_coefficients_for_chunks(F, point))
+        coeffs_per_poly.append(per_claim)
+        committed.extend(p.chunks)
+        max_vars = max(max_vars, p.chunk_vars)
+    expr = claims_batching_expression(F, polys, coeffs_per_poly)
+    challenge = transcript.append_and_sample(b"model_batching")
+    terms = expr_to_terms(F, expr, [challenge])
+    tables = [zero_pad_table(F, t, max_vars) for t in committed + eq_tables]
+    proof, point, finals = sumcheck_prove(F, max_vars, tables, terms, transcript, degree=2)
+    evals = finals[: len(committed)]
+    transcript.append_scalars(point)
+    transcript.append_scalars(evals)
+    rlc_challenges = [transcript.challenge_scalar() for _ in committed]
+    rlc = linear_combination(F, committed, rlc_challenges)
+    return dict(sumcheck=proof, sumcheck_evals=evals, point=point, rlc_challenges=rlc_challenges, rlc=rlc)
+
+
+def claims_batching_verify(F, proof, polys_info, transcript):
+    """CommitmentVerifier::claims_batching_sumcheck (zkml/src/poly_commit/verifier.rs:203-330).
+    polys_info: CommittedPoly objects whose chunks may be None (only sizes and claims are used)."""
+    eq_points, evals, coeffs_per_poly = [], [], []
+    max_vars = 0
+    for p in polys_info:
+        per_claim = []
+        for point, ev in p.claims:
+            transcript.append_scalars([ev])
+            eq_points.append(p.eq_point_per_chunk(point))
+            evals.append(ev)
+            per_claim.append(p.batching_coefficients_for_chunks(F, point))
+        coeffs_per_poly.append(per_claim)
+        max_vars = max(max_vars, p.chunk_vars)
+    expr = claims_batching_expression(F, polys_info, coeffs_per_poly)
+    challenge = transcript.append_and_sample(b"model_batching")
+    claimed, acc = F.zero, F.one
+    for e in evals:
+        claimed = F.add(claimed, F.mul(acc, e))
+        acc = F.mul(acc, challenge)
+    try:
+        point, expected = sumcheck_verify(F, claimed, proof["sumcheck"], max_vars, 2, transcript)
+    except ValueError:
+        return False
+    wit = list(proof["sumcheck_evals"])
+    for eq_point in eq_points:
+        v = identity_eval(F, point[: len(eq_point)], eq_point)
+        for pcoord in point[len(eq_point):]:
+            v = F.mul(v, F.sub(F.one, pcoord))
+        wit.append(v)
+    return eval_expr(F, expr, wit, [challenge]) == expected
+
+
 # -------------------------------------------------------------- serialization
 def serialize_scalars(F, vals):
     return b"".join(F.to_canonical(v) for v in vals)
