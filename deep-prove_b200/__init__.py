@@ -71,6 +71,7 @@ SIGNATURES = {
     "dpb_mle_device_ptr": (_vp, [_vp]),
     "dpb_mle_view": (_int, [_vp, _u64, _u64, _pp]),
     "dpb_mle_zero_padded": (_int, [_vp, _pp]),
+    "dpb_eq_tables": (_int, [_vp, _int, _vp, ctypes.POINTER(_u32), _u32, _pp, _pp]),
     "dpb_linear_combination": (_int, [_vp, _pp, _vp, _u32, _pp]),
     "dpb_eq_table": (_int, [_vp, _int, _vp, _u32, _pp]),
     "dpb_fix_high": (_int, [_vp, _vp, _vp, _u32, _pp]),
@@ -329,6 +330,20 @@ class Mle:
         if self.h:
             lib.dpb_mle_free(self.h)
             self.h = None
+
+
+def eq_tables(ctx, family_dtype, points):
+    """One eq table per point (a list of [m_t, w] arrays) in a single call.  Returns (owner, [tables]): the tables
+    are views into the owner's memory; free the owner last."""
+    n = len(points)
+    nv = (ctypes.c_uint32 * n)(*[int(np.asarray(p).shape[0]) for p in points])
+    w = elem_words(chal_dtype(family_dtype))
+    flat = np.ascontiguousarray(np.concatenate([np.asarray(p, dtype=np.uint64).reshape(-1, w) for p in points])
+                                if n else np.zeros((0, w), np.uint64))
+    owner = ctypes.c_void_p()
+    outs = (ctypes.c_void_p * n)()
+    check(lib.dpb_eq_tables(ctx.h, family_dtype, _buf(flat), nv, n, ctypes.byref(owner), outs))
+    return Mle(ctx, owner), [Mle(ctx, ctypes.c_void_p(outs[i])) for i in range(n)]
 
 
 def linear_combination(ctx, mles, coeffs):

@@ -196,6 +196,75 @@ static int fix_common(dpb_ctx* ctx, const dpb_mle* mle, const void* point, uint3
 
 using namespace dpb;
 
+template <class F>
+int eq_tables_impl(dpb_ctx* ctx, const void* points, const uint32_t* num_vars, uint32_t n, dpb_mle** out_owner,
+                          dpb_mle** out_tables) {
+    typedef typename F::E E;
+    std::vector<EqBatchDesc> desc(n);
+    std::vector<uint64_t> part_prefix(n + 1), out_prefix(n + 1);
+    uint64_t pt = 0, parts = 0, outs = 0;
+    for (uint32_t t = 0; t < n; t++) {
+        const uint32_t m = num_vars[t], h = (m + 1) / 2;
+        if (m > 34) return fail(DPB_EINVAL, "eq table %u over %u variables is too large", t, m);
+        desc[t].m = m;
+        desc[t].pt_off = (uint32_t)pt;
+        desc[t].part_off = parts;
+        desc[t].out_off = outs;
+        part_prefix[t] = parts;
+        out_prefix[t] = outs;
+        pt += m;
+        parts += (1ull << h) + (1ull << (m - h));
+        outs += 1ull << m;
+    }
+    part_prefix[n] = parts;
+    out_prefix[n] = outs;
+    if (pt > 0xFFFFFFFFull) return fail(DPB_EINVAL, "too many coordinates");
+    // one scratch block: [descriptors | part prefix | table prefix | points | parts]
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        const size_t o = off;
+        off = (off + bytes + 31) & ~(size_t)31;
+        return o;
+    };
+    const size_t o_desc = take(n * sizeof(EqBatchDesc)), o_pp = take((n + 1) * 8), o_op = take((n + 1) * 8),
+                 o_pts = take((size_t)pt * sizeof(E)), meta = off, o_parts = take(parts * sizeof(E));
+    void* scratch = nullptr;
+    DPB_TRY(device_alloc(ctx, off, &scratch));
+    std::vector<uint8_t> blob(meta, 0);
+    memcpy(blob.data() + o_desc, desc.data(), n * sizeof(EqBatchDesc));
+    memcpy(blob.data() + o_pp, part_prefix.data(), (n + 1) * 8);
+    memcpy(blob.data() + o_op, out_prefix.data(), (n + 1) * 8);
+    if (pt) memcpy(blob.data() + o_pts, points, (size_t)pt * sizeof(E));
+    int rc = upload_small(ctx, scratch, blob.data(), meta);
+    dpb_mle* owner = nullptr;
+    if (rc == DPB_OK) rc = new_mle(ctx, F::kChalDtype, outs, &owner);
+    if (rc != DPB_OK) {
+        device_free(ctx, scratch);
+        return rc;
+    }
+    char* sb = (char*)scratch;
+    eq_batch_parts<F><<<grid_for(ctx, parts), kThreads, 0, ctx->stream>>>(
+        (const EqBatchDesc*)(sb + o_desc), (const uint64_t*)(sb + o_pp), n, (const E*)(sb + o_pts), (E*)(sb + o_parts));
+    eq_batch_combine<F><<<grid_for(ctx, outs), kThreads, 0, ctx->stream>>>(
+        (const EqBatchDesc*)(sb + o_desc), (const uint64_t*)(sb + o_op), n, (const E*)(sb + o_parts), (E*)owner->ptr);
+    cudaError_t e = cudaGetLastError();
+    device_free(ctx, scratch);
+    if (e != cudaSuccess) {
+        dpb_mle_free(owner);
+        return fail(DPB_ECUDA, "eq tables: %s", cudaGetErrorString(e));
+    }
+    for (uint32_t t = 0; t < n; t++) {
+        rc = dpb_mle_view(owner, out_prefix[t], 1ull << num_vars[t], &out_tables[t]);
+        if (rc != DPB_OK) {
+            for (uint32_t q = 0; q < t; q++) dpb_mle_free(out_tables[q]);
+            dpb_mle_free(owner);
+            return rc;
+        }
+    }
+    *out_owner = owner;
+    return DPB_OK;
+}
+
 extern "C" {
 
 const char* dpb_last_error(void) { return last_error_slot().c_str(); }
@@ -482,6 +551,18 @@ int dpb_eq_table(dpb_ctx* ctx, int family_dtype, const void* point, uint32_t m, 
     if (m > 34) return fail(DPB_EINVAL, "eq table over %u variables is too large", m);
     return is_gl(family_dtype) ? eq_table_impl<GlFam>(ctx, point, m, out)
                                : eq_table_impl<FrFam>(ctx, point, m, out);
+}
+
+int dpb_eq_tables(dpb_ctx* ctx, int family_dtype, const void* points, const uint32_t* num_vars, uint32_t n,
+                  dpb_mle** out_owner, dpb_mle** out_tables) {
+    if (!ctx || !num_vars || !out_owner || !out_tables) return fail(DPB_EINVAL, "null argument");
+    if (n == 0) return fail(DPB_EINVAL, "no tables");
+    if (!valid_dtype(family_dtype)) return fail(DPB_EINVAL, "unknown dtype %d", family_dtype);
+    bool any = false;
+    for (uint32_t t = 0; t < n; t++) any = any || num_vars[t] > 0;
+    if (any && !points) return fail(DPB_EINVAL, "null argument");
+    return is_gl(family_dtype) ? eq_tables_impl<GlFam>(ctx, points, num_vars, n, out_owner, out_tables)
+                               : eq_tables_impl<FrFam>(ctx, points, num_vars, n, out_owner, out_tables);
 }
 
 int dpb_fix_high(dpb_ctx* ctx, const dpb_mle* mle, const void* point, uint32_t k, dpb_mle** out) {

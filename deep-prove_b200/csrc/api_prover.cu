@@ -147,12 +147,18 @@ int same_poly_impl(dpb_ctx* ctx, dpb_mle* poly, const void* points, uint32_t n_c
     if (n_claims == 0) return fail(DPB_EINVAL, "no claims");
     const std::vector<E> chal = tr.read_challenges(n_claims);
     std::vector<dpb_mle*> betas(n_claims, nullptr);
+    dpb_mle* beta_owner = nullptr;
     struct G {
         std::vector<dpb_mle*>& v;
-        ~G() { for (auto* m : v) dpb_mle_free(m); }
-    } g{betas};
-    for (uint32_t i = 0; i < n_claims; i++)
-        dp_crypto::check(dpb_eq_table(ctx, F::kChalDtype, (const E*)points + (size_t)i * n, n, &betas[i]));
+        dpb_mle*& owner;
+        ~G() {
+            for (auto* m : v) dpb_mle_free(m);
+            dpb_mle_free(owner);
+        }
+    } g{betas, beta_owner};
+    // one eq table per claim, all built in one call
+    const std::vector<uint32_t> vars(n_claims, n);
+    dp_crypto::check(dpb_eq_tables(ctx, F::kChalDtype, points, vars.data(), n_claims, &beta_owner, betas.data()));
     dp_crypto::VirtualPolynomialsBuilder<F> b(1, n);
     X poly_expr = b.lift(poly);
     X sum = X::Constant(F::zero());

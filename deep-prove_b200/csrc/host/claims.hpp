@@ -124,8 +124,9 @@ ClaimsBatchingProof<F> claims_batching_sumcheck(dpb_ctx* ctx, const std::vector<
         std::vector<dpb_mle*>& v;
         ~Guard() { for (auto* m : v) dpb_mle_free(m); }
     } guard{owned};
-    std::vector<dpb_mle*> eq_polys;
     std::vector<std::vector<std::vector<E>>> coeffs;
+    std::vector<E> eq_points;       // the eq point of every claim, end to end
+    std::vector<uint32_t> eq_vars;  // and its length
     size_t total_chunks = 0, total_claims = 0;
     for (size_t pi = 0; pi < polys.size(); pi++) {
         const auto& p = polys[pi];
@@ -133,10 +134,9 @@ ClaimsBatchingProof<F> claims_batching_sumcheck(dpb_ctx* ctx, const std::vector<
         std::vector<std::vector<E>> per_claim;
         for (const auto& c : p.claims) {
             transcript.append_scalars(&c.eval, 1);
-            dpb_mle* eq = nullptr;
-            check(dpb_eq_table(ctx, F::kChalDtype, c.point.data(), (uint32_t)p.num_vars_for_chunk(), &eq));
-            owned.push_back(eq);
-            eq_polys.push_back(eq);
+            // eq_point_per_chunk (mod.rs:61-69): the point without its last log2(chunks) coordinates
+            eq_points.insert(eq_points.end(), c.point.begin(), c.point.begin() + p.num_vars_for_chunk());
+            eq_vars.push_back((uint32_t)p.num_vars_for_chunk());
             per_claim.push_back(p.batching_coefficients_for_chunks(c.point));
         }
         total_claims += p.claims.size();
@@ -146,6 +146,14 @@ ClaimsBatchingProof<F> claims_batching_sumcheck(dpb_ctx* ctx, const std::vector<
         out.max_num_vars = std::max(out.max_num_vars, p.num_vars_for_chunk());
     }
     if (total_chunks + total_claims > 65535) throw Error(DPB_EINVAL, "more than 65535 tables in one batching sumcheck");
+    if (total_claims == 0) throw Error(DPB_EINVAL, "no claims to batch");
+    // all eq tables in one call (one block of device memory, two launches)
+    std::vector<dpb_mle*> eq_polys(total_claims, nullptr);
+    dpb_mle* eq_owner = nullptr;
+    check(dpb_eq_tables(ctx, F::kChalDtype, eq_points.data(), eq_vars.data(), (uint32_t)total_claims, &eq_owner,
+                        eq_polys.data()));
+    for (auto* m : eq_polys) owned.push_back(m);
+    owned.push_back(eq_owner);  // freed last
     const Expression<F> expr = build_sumcheck_expression<F>(polys, coeffs);
     // every table enters as a zero-padded view of max_num_vars variables (prover.rs:214-226)
     std::vector<dpb_mle*> views;

@@ -62,6 +62,76 @@ __global__ void eq_combine(const typename F::E* __restrict__ lo, uint32_t lo_bit
                  F::mul(F::load(hi, F::kChalDtype, i >> lo_bits), F::load(lo, F::kChalDtype, i & mask)));
 }
 
+// ---- many eq tables at once -----------------------------------------------------
+// Table t has m_t variables and its point at pts[pt_off[t] ..].  Its table is
+// the outer product of a "low" part over the first h_t = ceil(m_t / 2) variables
+// and a "high" part over the rest, each computed directly (at most m_t / 2 + 1
+// multiplies per entry of tables of about sqrt(2^m_t) entries), then one
+// multiply per output entry.  Work items of all tables are laid end to end;
+// `prefix` holds the first item of every table (n + 1 entries) and a thread
+// finds its table by binary search.
+struct EqBatchDesc {
+    uint32_t m;        // variables
+    uint32_t pt_off;   // first coordinate in the points array
+    uint64_t part_off; // low part at parts[part_off], high part right after it
+    uint64_t out_off;  // table at out[out_off]
+};
+
+__device__ __forceinline__ uint32_t find_segment(const uint64_t* __restrict__ prefix, uint32_t n, uint64_t item) {
+    uint32_t lo = 0, hi = n;
+    while (hi - lo > 1) {
+        const uint32_t mid = (lo + hi) >> 1;
+        if (prefix[mid] <= item) lo = mid;
+        else hi = mid;
+    }
+    return lo;
+}
+
+template <class F>
+__global__ void __launch_bounds__(kThreads)
+    eq_batch_parts(const EqBatchDesc* __restrict__ desc, const uint64_t* __restrict__ prefix, uint32_t n,
+                   const typename F::E* __restrict__ pts, typename F::E* __restrict__ parts) {
+    typedef typename F::E E;
+    const uint64_t total = prefix[n];
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t w = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; w < total; w += stride) {
+        const uint32_t t = find_segment(prefix, n, w);
+        const EqBatchDesc d = desc[t];
+        const uint32_t h = (d.m + 1) / 2;
+        uint64_t i = w - prefix[t];
+        uint32_t first = 0, bits = h;  // low part: coordinates [0, h)
+        if (i >= (1ull << h)) {        // high part: coordinates [h, m)
+            i -= 1ull << h;
+            first = h;
+            bits = d.m - h;
+        }
+        E acc = F::one();
+        for (uint32_t j = 0; j < bits; j++) {
+            const E r = pts[d.pt_off + first + j];
+            acc = F::mul(acc, ((i >> j) & 1) ? r : F::sub(F::one(), r));
+        }
+        F::store(parts, d.part_off + (w - prefix[t]), acc);
+    }
+}
+
+template <class F>
+__global__ void __launch_bounds__(kThreads)
+    eq_batch_combine(const EqBatchDesc* __restrict__ desc, const uint64_t* __restrict__ prefix, uint32_t n,
+                     const typename F::E* __restrict__ parts, typename F::E* __restrict__ out) {
+    const uint64_t total = prefix[n];
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t w = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; w < total; w += stride) {
+        const uint32_t t = find_segment(prefix, n, w);
+        const EqBatchDesc d = desc[t];
+        const uint32_t h = (d.m + 1) / 2;
+        const uint64_t i = w - prefix[t];
+        const uint64_t lo = i & ((1ull << h) - 1), hi = i >> h;
+        F::store(out, d.out_off + i,
+                 F::mul(F::load(parts, F::kChalDtype, d.part_off + lo),
+                        F::load(parts, F::kChalDtype, d.part_off + (1ull << h) + hi)));
+    }
+}
+
 // ---- partial evaluation ----------------------------------------------------
 // Top g variables: out[j] = sum_{h < 2^g} w[h] * in[h * n_out + j].
 template <class F>

@@ -125,6 +125,28 @@ def main():
     K2 = (dpb.AXIS_CONTRACTED, dpb.AXIS_OUTER)
     t = timed(ctx, lambda: [h.free() for h in ctx.einsum_fix_axes(fam, wt, K2, [None, p12])[1]], args.reps)
     report("einsum fix_axes W[768,3072], bind columns", t, wt.size * 8)
+
+    # claim batching of the opening proof: many committed polynomials of mixed sizes, one claim each, all
+    # zero-padded to the largest; bytes = sumcheck traffic of every polynomial and its eq table at its own size
+    sizes = [min(n, 16)] * 64 + [min(n, 12)] * 192 + [n] * 4
+    polys, nbytes = [], 0
+    for m in sizes:
+        tab = ctx.upload(table(1 << m), base)
+        polys.append(prover.CommittedPoly([tab], [(chal(m), chal(1)[0])]))
+        nbytes += ((2 * s0 + 2 * s1) + 4 * s1) * (1 << m)
+
+    def claims():
+        tr = prover.Blake3Transcript(fam)
+        out = prover.claims_batching_prove(ctx, tr, polys, with_rlc=False)
+        tr.free()
+        return out
+
+    t = timed(ctx, claims, max(1, args.reps // 2))
+    report(f"claim batching, {len(sizes)} polys up to 2^{n}", t, nbytes)
+    mles = [p.chunks[0] for p in polys]
+    cf = chal(len(mles))
+    t = timed(ctx, lambda: dpb.linear_combination(ctx, mles, cf).free(), args.reps)
+    report(f"linear combination of {len(mles)} polys", t, sum((1 << m) * s0 for m in sizes) + (1 << n) * s1)
     ctx.close()
 
 

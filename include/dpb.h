@@ -167,6 +167,13 @@ int dpb_linear_combination(dpb_ctx* ctx, dpb_mle* const* mles, const void* coeff
  * (dp_crypto::poly::eq::evals; call sites zkml/src/lookup/logup_gkr/prover.rs:247-249,
  * zkml/src/layers/hadamard.rs:103).  `point` holds m challenge elements on the host. */
 int dpb_eq_table(dpb_ctx* ctx, int family_dtype, const void* point, uint32_t m, dpb_mle** out);
+/* n eq tables in one call: table t is over num_vars[t] variables and its point
+ * is the next num_vars[t] elements of `points`.  All tables live in one block
+ * owned by *out_owner (free it last); out_tables[t] are views.  For callers that
+ * build one eq table per claim (zkml/src/poly_commit/prover.rs:172,201;
+ * zkml/src/iop/same_poly.rs:90). */
+int dpb_eq_tables(dpb_ctx* ctx, int family_dtype, const void* points, const uint32_t* num_vars, uint32_t n,
+                  dpb_mle** out_owner, dpb_mle** out_tables);
 
 /* Binds the top k variables (variable n-k+j := point[j]) -> table of len/2^k.
  * DensePolynomial::fix_high_variables{,_parallel}

@@ -26,7 +26,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 def golden_inputs(F, name):
     """Seeded inputs shared by the generator and the GPU parity tests."""
     seed = {"prod3": 101, "hadamard": 102, "logup_lookup": 103, "logup_table": 104, "fix": 105,
-            "mixed": 106}[name]
+            "mixed": 106, "claims": 107}[name]
     rng = np.random.default_rng(seed)
     if name == "prod3":
         n = 6
@@ -55,6 +55,18 @@ def golden_inputs(F, name):
         return dict(n=n, tables=[F.random_table(rng, 1 << n), F.random_table(rng, 1 << n),
                                  F.random_table(rng, 1 << (n - 2)), F.random_table(rng, 1 << (n - 2))],
                     coeffs=[F.random_scalar(rng) for _ in range(3)])
+    if name == "claims":
+        # committed polynomials (num_vars, chunks, claims): one unchunked with two claims, one in four chunks, one small
+        polys = []
+        for nv, nchunks, nclaims in ((5, 1, 2), (6, 4, 1), (3, 1, 1)):
+            full = F.random_table(rng, 1 << nv)
+            m = nv - (nchunks.bit_length() - 1)
+            claims = []
+            for _ in range(nclaims):
+                pt = [F.random_scalar(rng) for _ in range(nv)]
+                claims.append((pt, orc.evaluate(F, full, pt)))
+            polys.append(orc.CommittedPoly([full[i << m:(i + 1) << m] for i in range(nchunks)], claims))
+        return polys
     raise KeyError(name)
 
 
@@ -89,6 +101,11 @@ def generate(F):
     g = golden_inputs(F, "logup_table")
     inp = orc.LogUpInput(F, 1, g["columns"], g["constant"], g["sep"], mult=g["mult"])
     out["logup_table"] = orc.serialize_logup_proof(F, orc.logup_batch_prove(F, [inp], orc.Transcript(F))).hex()
+
+    pr = orc.claims_batching_prove(F, golden_inputs(F, "claims"), orc.Transcript(F))
+    out["claims"] = dict(proof=orc.serialize_sumcheck_proof(F, pr["sumcheck"]).hex(), point=hx(pr["point"]),
+                         evals=hx(pr["sumcheck_evals"]), rlc_challenges=hx(pr["rlc_challenges"]),
+                         rlc=hx(orc.array_to_scalars(F, pr["rlc"])))
 
     g = golden_inputs(F, "fix")
     out["eq"] = hx(orc.array_to_scalars(F, orc.eq_evals(F, g["point"][:4])))

@@ -62,6 +62,21 @@ def test_linear_combination(dpb, ctx, F):
     assert got.len == 1 << 9
 
 
+@pytest.mark.parametrize("F", FIELDS)
+def test_eq_tables_batch(dpb, ctx, F):
+    """Many eq tables in one call equal the oracle's, table by table (sizes 0 .. 13 variables, odd and even)."""
+    rng = np.random.default_rng(8250)
+    sizes = [5, 0, 1, 12, 3, 13, 2, 8, 8, 1, 7]
+    pts = [[F.random_scalar(rng) for _ in range(m)] for m in sizes]
+    arrs = [orc.scalars_to_array(F, p) if p else np.zeros((0, F.elem_words), np.uint64) for p in pts]
+    owner, tabs = dpb.eq_tables(ctx, family_dtype(dpb, F), arrs)
+    for t, p in zip(tabs, pts):
+        assert (t.to_host() == orc.eq_evals(F, p)).all()
+    for t in tabs:
+        t.free()
+    owner.free()
+
+
 def make_polys(F, rng, shapes):
     """shapes: (num_vars, num_chunks, num_claims) per polynomial -> oracle-side CommittedPoly list"""
     polys = []
@@ -112,6 +127,28 @@ def test_claims_batching_prove(dpb, ctx, F, chunked):
     got["rlc"].free()
     for m in owned:
         m.free()
+
+
+@pytest.mark.parametrize("F", FIELDS)
+def test_claims_batching_golden(dpb, ctx, F):
+    """The committed fixture (tests/golden/oracle_*.json, key "claims")."""
+    import json
+    import os
+    from deep_prove_b200 import prover
+    from tests.golden import make_golden
+    with open(os.path.join(os.path.dirname(__file__), "golden", f"oracle_{F.name}.json")) as f:
+        want = json.load(f)["claims"]
+    hx = lambda arr: orc.serialize_scalars(F, orc.array_to_scalars(F, arr)).hex()
+    gpu_polys = []
+    for p in make_golden.golden_inputs(F, "claims"):
+        chunks = [upload(dpb, ctx, F, c) for c in p.chunks]
+        claims = [(orc.scalars_to_array(F, pt), orc.scalars_to_array(F, [ev])[0]) for pt, ev in p.claims]
+        gpu_polys.append(prover.CommittedPoly(chunks, claims))
+    tr = prover.Blake3Transcript(family_dtype(dpb, F))
+    got = prover.claims_batching_prove(ctx, tr, gpu_polys)
+    assert hx(got["sumcheck"].reshape(-1, got["sumcheck"].shape[-1])) == want["proof"]
+    assert hx(got["point"]) == want["point"] and hx(got["sumcheck_evals"]) == want["evals"]
+    assert hx(got["rlc_challenges"]) == want["rlc_challenges"] and hx(got["rlc"].to_host()) == want["rlc"]
 
 
 def test_claims_batching_argument_errors(dpb, ctx):

@@ -330,6 +330,61 @@ def test_logup_table_and_lookup_fractions_cancel(F):
 
 
 @pytest.mark.parametrize("F", FIELDS)
+def test_zero_padding_convention(F):
+    """A zero-padded table is its polynomial over the FIRST variables times (1 - x_j) for every added variable:
+    the formula the reference's verifier uses for the padded eq tables (zkml/src/poly_commit/verifier.rs:300-311)."""
+    rng = np.random.default_rng(14)
+    m, n = 3, 6
+    eq_point = [F.random_scalar(rng) for _ in range(m)]
+    point = [F.random_scalar(rng) for _ in range(n)]
+    padded = orc.zero_pad_table(F, orc.eq_evals(F, eq_point), n)
+    want = orc.identity_eval(F, point[:m], eq_point)
+    for p in point[m:]:
+        want = F.mul(want, F.sub(F.one, p))
+    assert orc.evaluate(F, padded, point) == want
+
+
+@pytest.mark.parametrize("F", FIELDS)
+@pytest.mark.parametrize("chunked", [False, True])
+def test_claims_batching_prove_verify(F, chunked):
+    """The reference's own test of this path (zkml/src/poly_commit/mod.rs:224-398) at reduced sizes: polynomials
+    of different sizes, one or two claims each, unchunked and cut into chunks; the prover's output passes the
+    restated verifier (verifier.rs:203-330), the linear combination opens to sum_j c_j * eval_j at the sumcheck
+    point, and a changed evaluation is rejected."""
+    rng = np.random.default_rng(15 + int(chunked))
+    polys = []
+    for nv, nclaims in ((6, 1), (8, 2), (5, 1), (7, 2), (6, 1)):
+        nchunks = 1 << max(nv - 5, 0) if chunked else 1
+        full = F.random_table_fast(rng, 1 << nv)
+        mv = nv - (nchunks.bit_length() - 1)
+        claims = []
+        for _ in range(nclaims):
+            pt = [F.random_scalar(rng) for _ in range(nv)]
+            claims.append((pt, orc.evaluate(F, full, pt)))
+        polys.append(orc.CommittedPoly([full[i << mv:(i + 1) << mv] for i in range(nchunks)], claims))
+    proof = orc.claims_batching_prove(F, polys, orc.Transcript(F))
+    assert orc.claims_batching_verify(F, proof, polys, orc.Transcript(F))
+    # the chunk coefficients rebuild a claim from the chunks' evaluations (mod.rs:38-45)
+    p = polys[1]
+    pt, ev = p.claims[0]
+    acc = F.zero
+    for c, chunk in zip(p.batching_coefficients_for_chunks(F, pt), p.chunks):
+        acc = F.add(acc, F.mul(c, orc.evaluate(F, chunk, p.eq_point_per_chunk(pt))))
+    assert acc == ev
+    # the combined polynomial at the sumcheck point
+    point, n_rlc = proof["point"], (len(proof["rlc"]) - 1).bit_length()
+    lhs = orc.evaluate(F, proof["rlc"], point[:n_rlc])
+    rhs = F.zero
+    for c, e in zip(proof["rlc_challenges"], proof["sumcheck_evals"]):
+        rhs = F.add(rhs, F.mul(c, e))
+    assert lhs == rhs
+    bad = dict(proof)
+    bad["sumcheck_evals"] = list(proof["sumcheck_evals"])
+    bad["sumcheck_evals"][0] = F.add(bad["sumcheck_evals"][0], F.one)
+    assert not orc.claims_batching_verify(F, bad, polys, orc.Transcript(F))
+
+
+@pytest.mark.parametrize("F", FIELDS)
 def test_golden_fixture(F):
     """The oracle's outputs on seeded inputs are frozen in tests/golden."""
     from tests.golden import make_golden
