@@ -260,17 +260,20 @@ static void build_round_tabs(const dpb_sc* sc, std::vector<RoundTab>& rt) {
 
 // Polls the mailbox until `ready` holds; bounded, and the stream is queried now and then so that a
 // kernel that died or returned early surfaces as an error.
+constexpr int kTailNoHost = 1;  // internal: the kernel found that launches block the host; fall back to launches
+
 template <class Ready>
 static int tail_wait_host(dpb_ctx* ctx, TailBox* box, Ready ready) {
     uint64_t spins = 0;
     std::chrono::steady_clock::time_point t0;
     while (!ready()) {
+        if (box->status == 3) return kTailNoHost;
         if (box->status == 2) return fail(DPB_ETIMEOUT, "the resident round kernel gave up waiting for a challenge");
         if ((++spins & 0xFFF) == 0) {
             cudaError_t e = cudaStreamQuery(ctx->tail_stream);
             if (e != cudaSuccess && e != cudaErrorNotReady)
                 return fail(DPB_ECUDA, "resident round kernel: %s", cudaGetErrorString(e));
-            if (e == cudaSuccess && box->status != 2 && !ready())
+            if (e == cudaSuccess && box->status != 2 && box->status != 3 && !ready())
                 return fail(DPB_ECUDA, "the resident round kernel returned without a result (%s)",
                             cudaGetErrorString(cudaGetLastError()));
             if (spins == 0x1000) t0 = std::chrono::steady_clock::now();
@@ -341,6 +344,8 @@ static int tail_round(dpb_sc* sc, uint32_t i, const typename F::E& r, typename F
             default: return fail(DPB_EINVAL, "degree %u not supported", sc->d);
         }
         if (rc != DPB_OK) return rc;
+        // first sign of life, as soon as the launch call is back (the kernel waits 50 ms for it)
+        ((volatile TailChunk*)&box->hello)->seq = 1;
         DPB_CUDA(cudaEventRecord(ctx->tail_ev[1], ctx->tail_stream));
         ctx->sumcheck_launches++;
         sc->tail_active = true;
@@ -350,7 +355,7 @@ static int tail_round(dpb_sc* sc, uint32_t i, const typename F::E& r, typename F
     }
     const uint32_t want = i + 1;
     uint32_t x = 0;  // sums taken so far; the sum at 1 is not sent after round 0
-    DPB_TRY(tail_wait_host(ctx, box, [&] {
+    const int rc_wait = tail_wait_host(ctx, box, [&] {
         while (x <= sc->d) {
             if (i > 0 && x == 1) {
                 x++;
@@ -360,8 +365,16 @@ static int tail_round(dpb_sc* sc, uint32_t i, const typename F::E& r, typename F
             x++;
         }
         return true;
-    }));
-    return DPB_OK;
+    });
+    if (rc_wait == kTailNoHost) {
+        // launches block this host thread (a profiler that serialises them, or blocking launches): the kernel has
+        // left without touching anything; this context runs one launch per round from now on
+        cudaStreamSynchronize(ctx->tail_stream);
+        ctx->tail_enabled = false;
+        sc->tail_active = false;
+        ctx->tail_owner = nullptr;
+    }
+    return rc_wait;
 }
 
 // Posts the last challenge, collects the final evaluations and releases the kernel's slot.
@@ -536,14 +549,19 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
     ctx->done_seq++;
     ctx->done_flag_dev = sharded ? nullptr : ctx->flag_dev;
     // the last rounds go to the resident kernel (one per context at a time; not while profiling per launch)
-    const bool use_tail = sc->tail_active || (sc->has_prog && ctx->tail_enabled && !sharded && !ctx->profile &&
-                                              i >= sc->tail_start && ctx->tail_owner == nullptr);
-    const bool profiled = ctx->profile && !use_tail;
+    bool use_tail = sc->tail_active || (sc->has_prog && ctx->tail_enabled && !sharded && !ctx->profile &&
+                                        i >= sc->tail_start && ctx->tail_owner == nullptr);
     E raw[kMaxAcc];
+    if (use_tail) {
+        const int rc = tail_round<F>(sc, i, r, raw);
+        if (rc == kTailNoHost) use_tail = false;  // only possible right after the kernel's launch: nothing has run
+        else if (rc != DPB_OK) return rc;
+    }
+    const bool profiled = ctx->profile && !use_tail;
     if (profiled) DPB_CUDA(cudaEventRecord(ctx->prof_ev[0], ctx->stream));
     bool done = false;
     if (use_tail) {
-        DPB_TRY(tail_round<F>(sc, i, r, raw));
+        // the sums are already in raw
     } else if (sc->fused_shape == kFusedProduct) {
         launch_fused(ctx, sc->h_desc.data() + (size_t)i * sc->k, i > 0 ? sc->h_fold.data() + (size_t)i * sc->k : nullptr,
                      sc->k, i, r, n_pairs);

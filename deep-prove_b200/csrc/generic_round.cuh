@@ -162,6 +162,7 @@ __global__ void __launch_bounds__(kThreads)
 // that in the mailbox and returns.
 
 constexpr uint32_t kTailAbort = 0xFFFFFFFFu;
+constexpr unsigned long long kTailHelloNs = 50ull * 1000 * 1000;  // 50 ms for the host's first sign of life
 constexpr uint32_t kTailMaxTables = 96;
 
 // Mailbox in mapped pinned host memory.  Everything travels as 16-byte chunks
@@ -177,8 +178,11 @@ struct TailChunk {
 struct TailBox {
     // host -> device: the challenge that ends round i carries sequence number i + 1; kTailAbort: leave now
     TailChunk chal[4];
+    // host -> device, written right after the launch call returns: sequence number 1 = "the host runs beside you"
+    TailChunk hello;
+    uint32_t pad0[12];
     // device -> host
-    volatile uint32_t status;  // 0 running, 2 gave up waiting for the host
+    volatile uint32_t status;  // 0 running, 2 gave up waiting for a challenge, 3 no hello: launches block the host
     uint32_t pad[15];
     TailChunk evals[kMaxAccTail * 4];      // sums of round i: sequence number i + 1
     TailChunk finals[kTailMaxTables * 4];  // final evaluations: sequence number n_rounds + 1
@@ -207,6 +211,24 @@ __device__ __forceinline__ void chunks_store(TailChunk* c, const E& v, uint32_t 
     const uint64_t* w = (const uint64_t*)&v;
 #pragma unroll
     for (int i = 0; i < (int)(sizeof(E) / 8); i++) chunk_store(c + i, w[i], seq);
+}
+
+// The kernel can only trade messages with a host that runs while it does.  Under a profiler that serialises
+// launches, or with blocking launches, the launch call returns only when the kernel has ended: the hello never
+// comes, the kernel says so and leaves at once, and the host goes back to one launch per round.
+__device__ __forceinline__ bool tail_hello(TailBox* box, unsigned long long limit_ns) {
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+        uint64_t d;
+        uint32_t s;
+        chunk_load(&box->hello, d, s);
+        if (s == 1) return true;
+        if (s == kTailAbort) return false;
+        if (global_ns() - t0 > limit_ns) {
+            box->status = 3;
+            return false;
+        }
+    }
 }
 
 // Waits for the challenge with sequence number `want`.  true: it is in r; false: abort or time-out.
@@ -325,6 +347,9 @@ __global__ void __launch_bounds__(kTailThreads)
     PairSlots<F> sl;
     sl.base = (uint4*)(smem_raw + slots_offset);
     E* tree = (E*)(smem_raw + slots_offset);  // [point][pair], after the slots have been consumed
+    if (threadIdx.x == 0) sh_stop = tail_hello(box, kTailHelloNs) ? 0 : 1;
+    __syncthreads();
+    if (sh_stop) return;
     for (uint32_t round = first_round; round < n_rounds; round++) {
         const uint32_t n_pairs = 1u << (n_rounds - round - 1);
         sl.n = n_pairs;

@@ -114,3 +114,38 @@ def test_host_that_does_not_answer(dpb, ctx):
     # the context is usable afterwards
     want = orc.sumcheck_prove(F, n, tabs, terms, orc.Transcript(F))
     assert gpu_sumcheck_prove(dpb, ctx, F, n, mles, terms, orc.Transcript(F)) == want
+
+
+def test_blocking_launches_fall_back_to_one_launch_per_round():
+    """With launches that block the host (CUDA_LAUNCH_BLOCKING=1; a profiler that serialises kernels behaves the
+    same) the resident kernel cannot talk to the host: it notices within 50 ms, leaves, and the context runs one
+    launch per round.  Results are unchanged and nothing waits for a time-out."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = r"""
+import sys, time
+sys.path.insert(0, {root!r}); sys.path.insert(0, {root!r} + '/tests')
+import numpy as np
+from conftest import load_package
+from oracle import oracle as orc
+from tests.helpers import gpu_sumcheck_prove, upload
+dpb = load_package()
+ctx = dpb.Context(0)
+F = orc.GlField
+rng = np.random.default_rng(7400)
+n = 7
+tabs = [F.random_table_fast(rng, 1 << n) for _ in range(3)]
+terms = {{(0, 1, 2): F.one}}
+want = orc.sumcheck_prove(F, n, tabs, terms, orc.Transcript(F))
+mles = [upload(dpb, ctx, F, t) for t in tabs]
+t0 = time.perf_counter()
+for _ in range(3):
+    assert gpu_sumcheck_prove(dpb, ctx, F, n, mles, terms, orc.Transcript(F)) == want
+assert time.perf_counter() - t0 < 3.0
+print('FALLBACK-OK')
+""".format(root=root)
+    env = dict(os.environ, CUDA_LAUNCH_BLOCKING="1")
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert "FALLBACK-OK" in out.stdout, out.stdout + out.stderr
