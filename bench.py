@@ -155,10 +155,13 @@ def metric_name(field):
 
 def workload_config(field, n, n_gpus):
     name = "Goldilocks base tables, Ext2 challenges" if field == "gl" else "BN254 Fr"
+    in_bytes = 3 * (1 << (n - (n_gpus.bit_length() - 1))) * (8 if field == "gl" else 32)  # per GPU
+    l2 = ("inputs per step exceed the 126 MB L2; no flush needed" if in_bytes > 126e6
+          else "inputs fit in the 126 MB L2: a small-size run, not a roofline measurement")
     return {"workload": f"standalone sumcheck microbench f*g*h, 2^{n} entries per table, {name} "
                         "(BASELINE.json configs[1])",
             "log2_size": n, "field": field, "tables": 3, "degree": 3, "sharding": f"top log2({n_gpus}) variables",
-            "l2": "inputs per step exceed the 126 MB L2; no flush needed"}
+            "l2": l2}
 
 
 def run_reference(args):
@@ -216,6 +219,10 @@ def run_ours(args):
         box = [dpb.comm_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
         ctx.comm_init(box[0], rank, world)
+    exchange = None
+    if world > 1:
+        exchange = ("per-round sums through a shared host segment every rank's kernel writes and every host polls"
+                    if ctx.comm_shared_exchange() else "per-round sums through ncclAllGather + copy to the host")
     sharded = world > 1
     log2_world = world.bit_length() - 1
     n_global = n + log2_world  # weak scaling: every rank holds a 2^n shard of a 2^(n + log2 G) hypercube
@@ -320,7 +327,7 @@ def run_ours(args):
         "metric": metric_name(field), "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "u64" if field == "gl" else "u256", "data": "synthetic",
-        "config": workload_config(field, n_global, world),
+        "config": dict(workload_config(field, n_global, world), **({"exchange": exchange} if exchange else {})),
         "frac_of_hbm_peak": value / (peak * world),
         "roofline": roofline,
         "kernels": kernels,

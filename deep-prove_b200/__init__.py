@@ -52,6 +52,7 @@ _vp, _u32, _u64, _int = ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint64, ctype
 _pp = ctypes.POINTER(ctypes.c_void_p)
 
 SIGNATURES = {
+    "dpb_comm_shared_exchange": (_int, [_vp]),
     "dpb_resident_rounds": (_int, [_vp, _int, _u32]),
     "dpb_sumcheck_launches": (_u64, [_vp]),
     "dpb_profile_enable": (_int, [_vp, _int]),
@@ -180,6 +181,10 @@ class Context:
 
     def comm_free(self):
         check(lib.dpb_comm_free(self.h))
+
+    def comm_shared_exchange(self):
+        """True when sharded rounds exchange their sums through the shared host segment, False for ncclAllGather."""
+        return bool(lib.dpb_comm_shared_exchange(self.h))
 
     def resident_rounds(self, enable=True, wait_ms=0):
         """Last rounds in one resident kernel (default) or one launch per round; wait_ms bounds the kernel's waits."""

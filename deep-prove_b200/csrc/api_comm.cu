@@ -3,12 +3,23 @@
 // One process per GPU.  The library does not link NCCL: libnccl.so.2 is opened
 // on first use, so single-GPU users carry no dependency and a process that has
 // already loaded an NCCL (e.g. through torch) shares that copy.  The exchange
-// per round is tiny (d+1 field elements per rank): one ncclAllGather over
-// NVLink, then each rank adds the partial sums mod p on the host, where the
-// transcript lives anyway (NCCL has no modular sum).
+// per round is tiny (d+1 field elements per rank) and its readers are the
+// HOSTS (each adds the partial sums mod p and runs the transcript; NCCL has no
+// modular sum).  On one node the ranks therefore share a small POSIX
+// shared-memory segment that each process registers with CUDA: a rank's round
+// kernel writes its sums and a sequence number straight into it and every host
+// polls it — no collective and no device-to-host copy on the per-round path.
+// When the ranks are not on one host, or the set-up fails anywhere, the
+// exchange is one ncclAllGather over NVLink followed by a copy to the host.
+// NCCL also carries the once-per-proof gather of the one-entry shards.
 #include <dlfcn.h>
+#include <fcntl.h>
 #include <nccl.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
 
+#include <atomic>
 #include <chrono>
 #include <thread>
 
@@ -62,6 +73,115 @@ int sync_bounded(dpb_ctx* ctx, double seconds) {
     }
 }
 
+int xch_collect(dpb_ctx* ctx, unsigned int seq, size_t msg_bytes, void* out, double seconds) {
+    const auto t0 = std::chrono::steady_clock::now();
+    uint64_t spins = 0;
+    for (int q = 0; q < ctx->nranks; q++) {
+        const char* slot = (const char*)ctx->xch_host + xch_slot_offset(q, seq);
+        const volatile unsigned int* flag = (const volatile unsigned int*)slot;
+        while (*flag != seq) {
+            if ((++spins & 0xFFF) == 0) {
+                cudaError_t e = cudaStreamQuery(ctx->stream);  // our own launch may have failed
+                if (e != cudaSuccess && e != cudaErrorNotReady) return fail(DPB_ECUDA, "round kernel: %s", cudaGetErrorString(e));
+                const double dt = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+                if (dt > seconds) return fail(DPB_ETIMEOUT, "waited %.1f s for the partial sums of rank %d", dt, q);
+            }
+        }
+        std::atomic_thread_fence(std::memory_order_acquire);
+        memcpy((char*)out + (size_t)q * msg_bytes, slot + 64, msg_bytes);
+    }
+    return DPB_OK;
+}
+
+// FNV-1a over the host name and the boot id: equal on two ranks exactly when they share a host
+static uint64_t host_fingerprint() {
+    char buf[512];
+    memset(buf, 0, sizeof buf);
+    gethostname(buf, 255);
+    if (FILE* f = fopen("/proc/sys/kernel/random/boot_id", "r")) {
+        const size_t used = strlen(buf);
+        if (!fgets(buf + used, (int)(sizeof buf - used - 1), f)) buf[used] = 0;
+        fclose(f);
+    }
+    uint64_t h = 1469598103934665603ull;
+    for (const char* p = buf; *p; p++) h = (h ^ (unsigned char)*p) * 1099511628211ull;
+    return h;
+}
+
+// every rank contributes one 64-bit word; true when all are equal to ours
+static int all_ranks_agree(dpb_ctx* ctx, uint64_t mine, bool* agree) {
+    uint64_t* slot = (uint64_t*)((char*)ctx->gather_dev + (size_t)ctx->rank * 8);
+    DPB_CUDA(cudaMemcpyAsync(slot, &mine, 8, cudaMemcpyHostToDevice, ctx->stream));
+    DPB_TRY(allgather_to_host(ctx, slot, 8));
+    *agree = true;
+    for (int q = 0; q < ctx->nranks; q++)
+        if (((const uint64_t*)ctx->gather_host)[q] != mine) *agree = false;
+    return DPB_OK;
+}
+
+// Tries to set the shared exchange segment up; leaves ctx->xch_host null when it cannot.  Every rank ends with
+// the same answer (the last step is an agreement over NCCL).
+static int xch_setup(dpb_ctx* ctx, const void* unique_id) {
+    bool same_host = false;
+    DPB_TRY(all_ranks_agree(ctx, host_fingerprint(), &same_host));
+    bool ok = same_host;
+    void* map = MAP_FAILED;
+    const size_t bytes = (xch_bytes_for(ctx->nranks) + 4095) & ~(size_t)4095;
+    char name[64];
+    {
+        uint64_t h = 1469598103934665603ull;
+        for (size_t i = 0; i < sizeof(ncclUniqueId); i++) h = (h ^ ((const unsigned char*)unique_id)[i]) * 1099511628211ull;
+        snprintf(name, sizeof name, "/dpb-xch-%016llx", (unsigned long long)h);
+    }
+    if (ok) {
+        int fd = -1;
+        if (ctx->rank == 0) {
+            shm_unlink(name);  // a leftover of a crashed run with the same id
+            fd = shm_open(name, O_CREAT | O_EXCL | O_RDWR, 0600);
+            if (fd >= 0 && ftruncate(fd, (off_t)bytes) != 0) {
+                close(fd);
+                fd = -1;
+            }
+        } else {
+            const auto t0 = std::chrono::steady_clock::now();
+            while (std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() < 10.0) {
+                fd = shm_open(name, O_RDWR, 0600);
+                struct stat st;
+                if (fd >= 0 && fstat(fd, &st) == 0 && (size_t)st.st_size >= bytes) break;
+                if (fd >= 0) close(fd);
+                fd = -1;
+                std::this_thread::sleep_for(std::chrono::milliseconds(1));
+            }
+        }
+        if (fd >= 0) {
+            map = mmap(nullptr, bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+            close(fd);
+        }
+        ok = map != MAP_FAILED;
+    }
+    bool registered = false;
+    void* dev = nullptr;
+    if (ok) {
+        // rank 0 created the segment zero-filled (ftruncate); nobody writes before the agreement below
+        registered = cudaHostRegister(map, bytes, cudaHostRegisterMapped | cudaHostRegisterPortable) == cudaSuccess;
+        ok = registered && cudaHostGetDevicePointer(&dev, map, 0) == cudaSuccess;
+        if (!ok) cudaGetLastError();  // clear the sticky-free error of a refused registration
+    }
+    bool all_ok = false;
+    int rc = all_ranks_agree(ctx, ok ? 1 : 0, &all_ok);
+    if (ctx->rank == 0 && same_host) shm_unlink(name);  // every rank that could has mapped it by now
+    if (rc == DPB_OK && ok && all_ok) {
+        ctx->xch_host = map;
+        ctx->xch_dev = dev;
+        ctx->xch_bytes = bytes;
+        ctx->xseq = 0;
+        return DPB_OK;
+    }
+    if (registered) cudaHostUnregister(map);
+    if (map != MAP_FAILED) munmap(map, bytes);
+    return rc;
+}
+
 }  // namespace dpb
 
 using namespace dpb;
@@ -96,8 +216,11 @@ int dpb_comm_init(dpb_ctx* ctx, const void* id, int rank, int nranks) {
     ctx->gather_bytes = 64 * 1024;
     DPB_CUDA(cudaMalloc(&ctx->gather_dev, 2 * ctx->gather_bytes));
     DPB_CUDA(cudaHostAlloc(&ctx->gather_host, ctx->gather_bytes, cudaHostAllocDefault));
+    if (nranks > 1 && !getenv("DPB_NO_SHARED_EXCHANGE")) DPB_TRY(xch_setup(ctx, id));
     return DPB_OK;
 }
+
+int dpb_comm_shared_exchange(const dpb_ctx* ctx) { return ctx && ctx->xch_host ? 1 : 0; }
 
 int dpb_comm_rank(const dpb_ctx* ctx) { return ctx ? ctx->rank : -1; }
 int dpb_comm_size(const dpb_ctx* ctx) { return ctx ? ctx->nranks : 0; }
@@ -105,6 +228,11 @@ int dpb_comm_size(const dpb_ctx* ctx) { return ctx ? ctx->nranks : 0; }
 int dpb_comm_free(dpb_ctx* ctx) {
     if (!ctx || !ctx->nccl_comm) return DPB_OK;
     cudaStreamSynchronize(ctx->stream);
+    if (ctx->xch_host) {
+        cudaHostUnregister(ctx->xch_host);
+        munmap(ctx->xch_host, ctx->xch_bytes);
+        ctx->xch_host = ctx->xch_dev = nullptr;
+    }
     nccl_api().ncclCommDestroy((ncclComm_t)ctx->nccl_comm);
     ctx->nccl_comm = nullptr;
     ctx->nranks = 1;

@@ -544,10 +544,21 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
     // A sharded sumcheck publishes into this rank's slot of the exchange area (in-place all-gather).
     const size_t msg_bytes = (sc->d + 1) * sizeof(E);
     const bool sharded = sc->log2_ranks > 0;
-    ctx->round_out = sharded ? (void*)((char*)ctx->gather_dev + (size_t)ctx->rank * msg_bytes) : ctx->result_dev;
-    // unsharded rounds signal completion through a flag in mapped host memory that the host polls
-    ctx->done_seq++;
-    ctx->done_flag_dev = sharded ? nullptr : ctx->flag_dev;
+    const bool shared_xch = sharded && ctx->xch_host != nullptr;
+    if (shared_xch) {
+        // this rank's slot of the shared host segment: the kernel's last block writes the sums, then the sequence number
+        ctx->xseq++;
+        char* slot = (char*)ctx->xch_dev + xch_slot_offset(ctx->rank, ctx->xseq);
+        ctx->round_out = slot + 64;
+        ctx->done_flag_dev = (unsigned int*)slot;
+        ctx->done_value = ctx->xseq;
+    } else {
+        ctx->round_out = sharded ? (void*)((char*)ctx->gather_dev + (size_t)ctx->rank * msg_bytes) : ctx->result_dev;
+        // unsharded rounds signal completion through a flag in mapped host memory that the host polls
+        ctx->done_seq++;
+        ctx->done_value = ctx->done_seq;
+        ctx->done_flag_dev = sharded ? nullptr : ctx->flag_dev;
+    }
     // the last rounds go to the resident kernel (one per context at a time; not while profiling per launch)
     bool use_tail = sc->tail_active || (sc->has_prog && ctx->tail_enabled && !sharded && !ctx->profile &&
                                         i >= sc->tail_start && ctx->tail_owner == nullptr);
@@ -616,7 +627,8 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
         // the sums are already in raw
     } else if (sharded) {
         // every rank's partial sums -> all hosts; add them mod p (NCCL has no modular sum)
-        DPB_TRY(allgather_to_host(ctx, ctx->round_out, msg_bytes));
+        if (shared_xch) DPB_TRY(xch_collect(ctx, ctx->xseq, msg_bytes, ctx->gather_host, 60.0));
+        else DPB_TRY(allgather_to_host(ctx, ctx->round_out, msg_bytes));
         const E* g = (const E*)ctx->gather_host;
         for (uint32_t x = 0; x <= sc->d; x++) {
             E tot = g[x];

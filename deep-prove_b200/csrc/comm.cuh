@@ -17,6 +17,15 @@ struct NcclApi {
     ncclResult_t (*ncclCommGetAsyncError)(ncclComm_t, ncclResult_t*) = nullptr;
 };
 
+// Layout of the shared exchange segment: a header line, then per rank two slots (used in turn, so that a rank may
+// publish round s + 1 while a slower host still reads round s): [flag line | up to kMaxAcc elements of 32 bytes].
+constexpr size_t kXchHeader = 256;
+constexpr size_t kXchSlot = 64 + kMaxAcc * 32;
+inline size_t xch_slot_offset(int rank, unsigned int seq) { return kXchHeader + ((size_t)rank * 2 + (seq & 1)) * kXchSlot; }
+inline size_t xch_bytes_for(int nranks) { return kXchHeader + (size_t)nranks * 2 * kXchSlot; }
+// Waits until every rank's slot of exchange `seq` is published, then copies the messages to out[rank][msg_bytes].
+int xch_collect(dpb_ctx* ctx, unsigned int seq, size_t msg_bytes, void* out, double seconds);
+
 NcclApi& nccl_api();
 int nccl_load();
 int sync_bounded(dpb_ctx* ctx, double seconds);

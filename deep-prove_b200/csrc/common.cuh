@@ -75,6 +75,14 @@ struct dpb_ctx {
     void* gather_dev = nullptr;   // send area (first half) and all-gather result (second half is unused slack)
     void* gather_host = nullptr;  // pinned copy of the all-gather result
     size_t gather_bytes = 0;
+    // Single-node exchange of the per-round partial sums: a POSIX shared-memory segment that every rank maps and
+    // registers with CUDA, so each rank's round kernel publishes straight into memory all hosts poll
+    // (api_comm.cu).  Off (nullptr) when the ranks are not on one host or the set-up failed: NCCL all-gather then.
+    void* xch_host = nullptr;
+    void* xch_dev = nullptr;
+    size_t xch_bytes = 0;
+    unsigned int xseq = 0;     // exchanges made so far; every rank counts the same
+    unsigned int done_value = 0;  // what the next launch writes into its completion flag
     // resident last-rounds kernel (generic_round.cuh): its mailbox in mapped pinned memory, the stream it
     // runs on (so that it never blocks other work of this context) and the sumcheck that owns it right now
     void* tail_box_host = nullptr;
@@ -124,7 +132,7 @@ inline ReduceScratch<F> reduce_scratch(const dpb_ctx* ctx) {
     rs.partials = (typename F::E*)ctx->partials;
     rs.counter = ctx->counter;
     rs.done_flag = ctx->done_flag_dev;
-    rs.done_value = ctx->done_seq;
+    rs.done_value = ctx->done_value;
     return rs;
 }
 

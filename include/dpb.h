@@ -96,6 +96,11 @@ void* dpb_stream(dpb_ctx* ctx);
 int dpb_comm_unique_id(void* out_id);
 /* ncclCommInitRank on the context's device; collective over all ranks.  nranks a power of two. */
 int dpb_comm_init(dpb_ctx* ctx, const void* id, int rank, int nranks);
+/* 1 when the ranks of this context's communicator exchange the per-round sums
+ * through a shared host segment (all on one host), 0 when they use
+ * ncclAllGather.  The environment variable DPB_NO_SHARED_EXCHANGE, set on every
+ * rank before dpb_comm_init, forces the NCCL path. */
+int dpb_comm_shared_exchange(const dpb_ctx* ctx);
 int dpb_comm_rank(const dpb_ctx* ctx);
 int dpb_comm_size(const dpb_ctx* ctx);
 int dpb_comm_free(dpb_ctx* ctx);

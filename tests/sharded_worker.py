@@ -63,7 +63,7 @@ def run_gpu(field, n, seed, rank, world, out):
     st = prover.IOPProverState.prove(ctx, n, mles, terms, prover.Blake3Transcript(fam), sharded=True)
     flat = lambda a: orc.serialize_scalars(F, orc.array_to_scalars(F, np.asarray(a).reshape(-1, F.elem_words))).hex()
     res = dict(proof=flat(st.proof), point=flat(st.collect_raw_challenges()),
-               finals=flat(st.get_mle_flatten_final_evaluations()))
+               finals=flat(st.get_mle_flatten_final_evaluations()), shared_exchange=ctx.comm_shared_exchange())
     ctx.comm_free()
     ctx.close()
     with open(f"{out}.{rank}.json", "w") as f:

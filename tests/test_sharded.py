@@ -23,11 +23,12 @@ def free_port():
         return s.getsockname()[1]
 
 
-def launch(mode, field, n, seed, world):
+def launch(mode, field, n, seed, world, extra_env=None):
     tmp = tempfile.mkdtemp()
     out = os.path.join(tmp, "res")
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(free_port()), OMP_NUM_THREADS="2",
                NCCL_NVLS_ENABLE="0")
+    env.update(extra_env or {})
     procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "sharded_worker.py"), mode, field, str(n),
                                str(seed), str(r), str(world), out], env=env, cwd=ROOT,
                               stdout=subprocess.PIPE, stderr=subprocess.STDOUT) for r in range(world)]
@@ -63,13 +64,19 @@ def test_sharding_protocol_on_cpu_gloo(field, world, n):
 @pytest.mark.gpu
 @pytest.mark.parametrize("field", ["gl", "fr"])
 @pytest.mark.parametrize("n", [4, 14])
-def test_sharded_sumcheck_on_gpus(field, n):
-    """The library's sharded path over NCCL on as many GPUs as the box has (2, 4 or 8)."""
+@pytest.mark.parametrize("exchange", ["shared", "nccl"])
+def test_sharded_sumcheck_on_gpus(field, n, exchange):
+    """The library's sharded path on as many GPUs as the box has (2, 4 or 8), with the per-round sums exchanged
+    through the shared host segment and through ncclAllGather."""
     import torch
     g = torch.cuda.device_count()
     world = 8 if g >= 8 else 4 if g >= 4 else 2 if g >= 2 else 0
     if world == 0:
         pytest.skip("needs at least 2 GPUs")
     want = oracle_proof(orc.FIELDS[field], n, 12)
-    for got in launch("gpu", field, n, 12, world):
+    env = {"DPB_NO_SHARED_EXCHANGE": "1"} if exchange == "nccl" else {}
+    for got in launch("gpu", field, n, 12, world, env):
+        shared = got.pop("shared_exchange")
+        if exchange == "nccl":
+            assert not shared
         assert got == want
