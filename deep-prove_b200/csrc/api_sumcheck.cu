@@ -160,13 +160,14 @@ static int launch_one_pass(dpb_sc* sc, uint32_t round, uint64_t n_pairs, const t
     if (blocks > cap) blocks = cap;
     if (blocks > ctx->max_blocks) blocks = ctx->max_blocks;
     const RoundTab* tabs = sc->d_rtab + (size_t)round * sc->k;
+    const typename F::FoldKey rk = F::fold_key(r);
     if (skip)
         sc_round_generic<F, D, true><<<(uint32_t)blocks, sc->op_threads, sc->op_smem, ctx->stream>>>(
-            tabs, sc->k, (const ProgGroup*)sc->d_groups, sc->n_groups, (const ProgTerm<F>*)sc->d_prog, r, n_pairs,
+            tabs, sc->k, (const ProgGroup*)sc->d_groups, sc->n_groups, (const ProgTerm<F>*)sc->d_prog, rk, n_pairs,
             reduce_scratch<F>(ctx), (typename F::E*)ctx->round_out);
     else
         sc_round_generic<F, D, false><<<(uint32_t)blocks, sc->op_threads, sc->op_smem, ctx->stream>>>(
-            tabs, sc->k, (const ProgGroup*)sc->d_groups, sc->n_groups, (const ProgTerm<F>*)sc->d_prog, r, n_pairs,
+            tabs, sc->k, (const ProgGroup*)sc->d_groups, sc->n_groups, (const ProgTerm<F>*)sc->d_prog, rk, n_pairs,
             reduce_scratch<F>(ctx), (typename F::E*)ctx->round_out);
     return DPB_OK;
 }
@@ -488,8 +489,13 @@ static void launch_fused_fr(dpb_ctx* ctx, const MleDesc* desc, const FoldDesc* f
         ptrs.out[j] = round == 0 ? nullptr : folds[j].out;
     }
     // two resident blocks per SM: these kernels wait on their multiply chains, more warps hide that
-    if (round == 0) v2_eval0<OpsFr, K, 2><<<grid, kThreads, 0, ctx->stream>>>(ptrs, n_pairs, rs, out);
-    else v2_fold_eval_fr<K, 2><<<grid, kThreads, 0, ctx->stream>>>(ptrs, r, n_pairs, rs, out);
+    if (round == 0) {
+        v2_eval0<OpsFr, K, 2><<<grid, kThreads, 0, ctx->stream>>>(ptrs, n_pairs, rs, out);
+    } else {
+        frw::FixedMul rk;  // the fold multiplies everything by this round's challenge: precomputed rows
+        fr_fixed_table(r, rk);
+        v2_fold_eval_fr<K, 2><<<grid, kThreads, 0, ctx->stream>>>(ptrs, rk, n_pairs, rs, out);
+    }
 }
 
 static void launch_fused(dpb_ctx* ctx, const MleDesc* desc, const FoldDesc* folds, uint32_t k, uint32_t round,
@@ -596,7 +602,7 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
     if (!done && !one_pass) {
         if (i > 0 && sc->n_fold[i] > 0) {
             dim3 grid(grid_for(ctx, sc->max_fold_out[i], 4), sc->n_fold[i]);
-            sc_fold_generic<F><<<grid, kThreads, 0, ctx->stream>>>(sc->d_fold + (size_t)i * sc->k, r);
+            sc_fold_generic<F><<<grid, kThreads, 0, ctx->stream>>>(sc->d_fold + (size_t)i * sc->k, F::fold_key(r));
         }
         if (sc->ranged) {
             switch (sc->d) {

@@ -62,6 +62,14 @@ struct GlFam {
     static E inv(const E& a) { return gl2_inv(a); }
     DPB_HD static size_t elem_size(int dtype) { return dtype == DPB_GL_BASE ? 8 : 16; }
 #if defined(__CUDACC__)
+    // What a launch needs to multiply many values by one challenge (the fold of a round).
+    typedef Gl2 FoldKey;
+    static FoldKey fold_key(const E& r) { return r; }
+    __device__ __forceinline__ static E mul_key(const FoldKey& k, const E& a) { return mul(k, a); }
+    // the same key, made by the threads of a block into *out (shared memory); the caller synchronises
+    __device__ __forceinline__ static void fold_key_block(const E& r, FoldKey* out) {
+        if (threadIdx.x == 0) *out = r;
+    }
     __device__ __forceinline__ static E load(const void* p, int dtype, uint64_t i) {
         if (dtype == DPB_GL_BASE) return gl2_from_base(((const uint64_t*)p)[i]);
         const ulonglong2 v = ((const ulonglong2*)p)[i];
@@ -108,6 +116,17 @@ struct FrFam {
     static E inv(const E& a) { return fr_inv(a); }
     DPB_HD static size_t elem_size(int) { return 32; }
 #if defined(__CUDACC__)
+    // The challenge as the eight precomputed rows of frw::mul_fixed: 80 wide multiply-adds per product instead of 128.
+    typedef frw::FixedMul FoldKey;
+    static FoldKey fold_key(const E& r) {
+        FoldKey k;
+        fr_fixed_table(r, k);
+        return k;
+    }
+    __device__ __forceinline__ static E mul_key(const FoldKey& k, const E& a) { return fr_mul_fixed(k, a); }
+    __device__ __forceinline__ static void fold_key_block(const E& r, FoldKey* out) {
+        if (threadIdx.x < 8) fr_fixed_row(r, (int)threadIdx.x, out->c[threadIdx.x]);
+    }
     __device__ __forceinline__ static E load(const void* p, int, uint64_t i) {
         const ulonglong2* q = (const ulonglong2*)p + 2 * i;
         const ulonglong2 a = q[0], b = q[1];

@@ -195,6 +195,42 @@ DPB_HD Fr fr_mul(const Fr& a, const Fr& b) {
 #endif
 }
 
+#if defined(__CUDACC__)
+// a * c for the multiplicand c whose constants `k` were made by fr_fixed_table (device only)
+__device__ __forceinline__ Fr fr_mul_fixed(const frw::FixedMul& k, const Fr& a) {
+    return frw::to_fr(frw::mul_fixed(frw::from_fr(a), k));
+}
+// 2^(32 i + 64) mod r as a plain integer, i = 0..7
+DPB_HD Fr fr_fixed_power(int i) {
+    Fr x;
+    x.l[0] = x.l[1] = x.l[2] = x.l[3] = 0;
+    const int e = 32 * i + 64;
+    if (e < 254) {
+        x.l[e / 64] = 1ull << (e % 64);
+    } else if (e == 256) {
+        x = fr_one();  // 2^256 mod r
+    } else {  // 2^288 mod r
+        x.l[0] = 0x93e7886515b8b9daULL;
+        x.l[1] = 0x16df2426b05ea154ULL;
+        x.l[2] = 0x1271b743302ab839ULL;
+        x.l[3] = 0x06bc037eec6c226eULL;
+    }
+    return x;
+}
+// Constants of frw::mul_fixed for the multiplicand c (Montgomery form): row i is
+// c * 2^(32 i + 64) / 2^256 mod r (a Montgomery product of c with the plain power).
+DPB_HD void fr_fixed_row(const Fr& c, int i, uint32_t* row) {
+    const Fr ci = fr_mul(c, fr_fixed_power(i));
+    for (int w = 0; w < 4; w++) {
+        row[2 * w] = (uint32_t)ci.l[w];
+        row[2 * w + 1] = (uint32_t)(ci.l[w] >> 32);
+    }
+}
+inline void fr_fixed_table(const Fr& c, frw::FixedMul& out) {
+    for (int i = 0; i < 8; i++) fr_fixed_row(c, i, out.c[i]);
+}
+#endif
+
 DPB_HD Fr fr_sqr(const Fr& a) { return fr_mul(a, a); }
 DPB_HD Fr fr_double(const Fr& a) { return fr_add(a, a); }
 

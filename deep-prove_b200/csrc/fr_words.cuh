@@ -155,6 +155,42 @@ __device__ __forceinline__ F8 mul(const F8& a, const F8& b) {
     return reduce_once(s);
 }
 
+// Product by a multiplicand that is fixed for a whole launch (the challenge of a fold).
+// With a = sum_i a_i 2^(32 i), a * c / 2^256 = sum_i a_i * C_i for the eight constants
+// C_i = c * 2^(32 i) / 2^256 mod r, which the host computes once per round.  The sum of
+// the eight rows needs no interleaved reduction: 64 multiply-adds, all landing on the
+// same aligned pairs, give a 289-bit value; two reduction words bring it below 2r (the
+// host folds their factor 2^-64 into the constants).  80 wide multiply-adds instead
+// of 128.
+struct FixedMul {
+    uint32_t c[8][8];  // C_i * 2^64 mod r, words little-endian
+};
+__device__ __forceinline__ F8 mul_fixed(const F8& a, const FixedMul& k) {
+    uint32_t E[12], O[12];  // pairs at even / odd positions
+#pragma unroll
+    for (int i = 0; i < 12; i++) E[i] = O[i] = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        chain_mul(E, E[8], k.c[i][0], k.c[i][2], k.c[i][4], k.c[i][6], a.w[i]);
+        chain_mul(O + 1, O[9], k.c[i][1], k.c[i][3], k.c[i][5], k.c[i][7], a.w[i]);
+    }
+    // reduction word for position 0 (only E holds it), then for position 1 (O's pair and E's left-over word)
+    const uint32_t m0 = E[0] * DPB_FRW_INV;
+    chain_mod_even(E, E[8], m0);
+    chain_mod_odd<false>(O + 1, O[9], m0, 0);
+    const uint32_t m1 = (O[1] + E[1]) * DPB_FRW_INV;
+    chain_mod_even(O + 1, O[9], m1);
+    chain_mod_odd<true>(E + 2, E[10], m1, E[1]);
+    F8 s;
+    asm("add.cc.u32 %0, %8, %16; addc.cc.u32 %1, %9, %17; addc.cc.u32 %2, %10, %18; addc.cc.u32 %3, %11, %19;\n\t"
+        "addc.cc.u32 %4, %12, %20; addc.cc.u32 %5, %13, %21; addc.cc.u32 %6, %14, %22; addc.u32 %7, %15, %23;"
+        : "=&r"(s.w[0]), "=&r"(s.w[1]), "=&r"(s.w[2]), "=&r"(s.w[3]), "=&r"(s.w[4]), "=&r"(s.w[5]), "=&r"(s.w[6]),
+          "=&r"(s.w[7])
+        : "r"(E[2]), "r"(E[3]), "r"(E[4]), "r"(E[5]), "r"(E[6]), "r"(E[7]), "r"(E[8]), "r"(E[9]), "r"(O[2]),
+          "r"(O[3]), "r"(O[4]), "r"(O[5]), "r"(O[6]), "r"(O[7]), "r"(O[8]), "r"(O[9]));
+    return reduce_once(s);
+}
+
 __device__ __forceinline__ F8 add(const F8& a, const F8& b) {
     F8 s;
     asm("add.cc.u32 %0, %8, %16; addc.cc.u32 %1, %9, %17; addc.cc.u32 %2, %10, %18; addc.cc.u32 %3, %11, %19;\n\t"

@@ -302,7 +302,7 @@ __global__ void __launch_bounds__(kThreads, MINB)
 // Rounds >= 1 over BN254.
 template <int K, int MINB = 1>
 __global__ void __launch_bounds__(kThreads, MINB)
-    v2_fold_eval_fr(V2Ptrs<K> ptrs, Fr r, uint64_t n_pairs, ReduceScratch<FrFam> rs, Fr* out) {
+    v2_fold_eval_fr(V2Ptrs<K> ptrs, frw::FixedMul rk, uint64_t n_pairs, ReduceScratch<FrFam> rs, Fr* out) {
     typedef OpsFr Ops;
     Fr acc[K + 1];
 #pragma unroll
@@ -316,7 +316,7 @@ __global__ void __launch_bounds__(kThreads, MINB)
             for (int h = 0; h < 2; h++) {
                 const Fr a0 = FrFam::load(ptrs.in[j], DPB_FR, 4 * p + 2 * h);
                 const Fr a1 = FrFam::load(ptrs.in[j], DPB_FR, 4 * p + 2 * h + 1);
-                f[h][j] = fr_add(a0, fr_mul(r, fr_sub(a1, a0)));
+                f[h][j] = fr_add(a0, fr_mul_fixed(rk, fr_sub(a1, a0)));  // the challenge is fixed for the launch
                 FrFam::store(ptrs.out[j], 2 * p + h, f[h][j]);
             }
         }

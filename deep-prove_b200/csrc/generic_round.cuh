@@ -109,7 +109,7 @@ __device__ __noinline__ void advance_point(const Slots<F>& sl, const RoundTab* _
 template <class F, int D, bool SKIP_ONE>
 __global__ void __launch_bounds__(kThreads)
     sc_round_generic(const RoundTab* __restrict__ tabs, uint32_t k, const ProgGroup* __restrict__ groups,
-                     uint32_t n_groups, const ProgTerm<F>* __restrict__ terms, typename F::E r, uint64_t n_pairs,
+                     uint32_t n_groups, const ProgTerm<F>* __restrict__ terms, typename F::FoldKey rk, uint64_t n_pairs,
                      ReduceScratch<F> rs, typename F::E* out) {
     typedef typename F::E E;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -127,8 +127,8 @@ __global__ void __launch_bounds__(kThreads)
                 E a0, a1, b0, b1;
                 F::load_pair(t.in, t.dtype_in, 2 * p, a0, a1);
                 F::load_pair(t.in, t.dtype_in, 2 * p + 1, b0, b1);
-                f0 = F::add(a0, F::mul(r, F::sub(a1, a0)));
-                f1 = F::add(b0, F::mul(r, F::sub(b1, b0)));
+                f0 = F::add(a0, F::mul_key(rk, F::sub(a1, a0)));
+                f1 = F::add(b0, F::mul_key(rk, F::sub(b1, b0)));
                 F::store(t.out, 2 * p, f0);
                 F::store(t.out, 2 * p + 1, f1);
             } else if (t.shift < 0) {
@@ -327,6 +327,7 @@ __global__ void __launch_bounds__(kTailThreads)
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ E sh_r;
     __shared__ int sh_stop;
+    __shared__ typename F::FoldKey sh_key;  // the current challenge in the form the folds multiply by
     const ProgGroup* groups = groups_g;
     const ProgTerm<F>* terms = terms_g;
     unsigned char* cursor = smem_raw;
@@ -348,6 +349,7 @@ __global__ void __launch_bounds__(kTailThreads)
     sl.base = (uint4*)(smem_raw + slots_offset);
     E* tree = (E*)(smem_raw + slots_offset);  // [point][pair], after the slots have been consumed
     if (threadIdx.x == 0) sh_stop = tail_hello(box, kTailHelloNs) ? 0 : 1;
+    F::fold_key_block(r, &sh_key);
     __syncthreads();
     if (sh_stop) return;
     for (uint32_t round = first_round; round < n_rounds; round++) {
@@ -368,8 +370,8 @@ __global__ void __launch_bounds__(kTailThreads)
                 E a0, a1, b0, b1;
                 F::load_pair(t.in, t.dtype_in, 2 * (uint64_t)p, a0, a1);
                 F::load_pair(t.in, t.dtype_in, 2 * (uint64_t)p + 1, b0, b1);
-                f0 = F::add(a0, F::mul(r, F::sub(a1, a0)));
-                f1 = F::add(b0, F::mul(r, F::sub(b1, b0)));
+                f0 = F::add(a0, F::mul_key(sh_key, F::sub(a1, a0)));
+                f1 = F::add(b0, F::mul_key(sh_key, F::sub(b1, b0)));
                 F::store(t.out, 2 * (uint64_t)p, f0);
                 F::store(t.out, 2 * (uint64_t)p + 1, f1);
             } else if (t.shift < 0) {
@@ -417,6 +419,7 @@ __global__ void __launch_bounds__(kTailThreads)
         __syncthreads();  // also orders this round's table stores before the next round's loads
         if (sh_stop) return;
         r = sh_r;
+        F::fold_key_block(r, &sh_key);  // visible after the barrier that follows the descriptor fetch of the next round
     }
     // r ends the last round: one value per table (tabs still holds the last round's descriptors)
     for (uint32_t j = threadIdx.x; j < k; j += blockDim.x) {

@@ -280,14 +280,14 @@ __global__ void __launch_bounds__(kThreads)
 // out[p] = in[2p] + r * (in[2p+1] - in[2p]).   blockIdx.y selects the table.
 template <class F>
 __global__ void __launch_bounds__(kThreads)
-    sc_fold_generic(const FoldDesc* __restrict__ descs, typename F::E r) {
+    sc_fold_generic(const FoldDesc* __restrict__ descs, typename F::FoldKey rk) {
     typedef typename F::E E;
     const FoldDesc d = descs[blockIdx.y];
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
     for (uint64_t p = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; p < d.n_out; p += stride) {
         E f0, f1;
         load_pair_limited<F>(d.in, d.dtype_in, d.limit_in, p, f0, f1);
-        F::store(d.out, p, F::add(f0, F::mul(r, F::sub(f1, f0))));
+        F::store(d.out, p, F::add(f0, F::mul_key(rk, F::sub(f1, f0))));
     }
 }
 
