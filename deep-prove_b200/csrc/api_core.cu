@@ -118,6 +118,7 @@ static int eq_table_impl(dpb_ctx* ctx, const void* point, uint32_t m, dpb_mle** 
     h->len = 1ull << m;
     h->ptr = res;
     h->owns = true;
+    if (m) h->eq_point.assign((const uint8_t*)point, (const uint8_t*)point + m * sizeof(E));
     *out = h;
     return DPB_OK;
 }
@@ -255,6 +256,9 @@ int eq_tables_impl(dpb_ctx* ctx, const void* points, const uint32_t* num_vars, u
     }
     for (uint32_t t = 0; t < n; t++) {
         rc = dpb_mle_view(owner, out_prefix[t], 1ull << num_vars[t], &out_tables[t]);
+        if (rc == DPB_OK && num_vars[t])
+            out_tables[t]->eq_point.assign((const uint8_t*)points + (size_t)desc[t].pt_off * sizeof(E),
+                                           (const uint8_t*)points + (size_t)(desc[t].pt_off + num_vars[t]) * sizeof(E));
         if (rc != DPB_OK) {
             for (uint32_t q = 0; q < t; q++) dpb_mle_free(out_tables[q]);
             dpb_mle_free(owner);

@@ -54,6 +54,22 @@ struct dpb_sc {
     uint64_t* d_tile_prefix = nullptr;  // [n][n_terms + 1]
     uint64_t* d_term_pairs = nullptr;   // [n][n_terms]
     std::vector<uint64_t> total_tiles;  // per round
+    // split-eq form of the large rounds (generic_round.cuh): every group of the program is led by an eq table
+    struct EqLead {
+        uint32_t table = 0;         // table id of the eq table
+        uint32_t first_active = 0;  // round in which it starts to move
+        uint32_t vars = 0;
+        std::vector<uint8_t> q;       // its point (vars elements)
+        std::vector<uint8_t> inv_zp;  // vars + 1 elements: 1 / prod_{k < j} (1 - q_k)
+        alignas(16) uint8_t S[32] = {0}, S_prev[32] = {0};  // prod eq(q_k, c_k) over the bound variables, now / one round ago
+    };
+    bool spliteq = false;
+    bool eq_unbound = false;      // split-eq rounds ran: the eq tables' bound copies do not exist
+    std::vector<EqLead> eq_leads;
+    std::vector<uint32_t> group_lead;  // per program group: index into eq_leads
+    std::vector<uint8_t> round_q, round_inv_q;  // per round: the active groups' shared coordinate and its inverse
+    RoundTab* d_rtab_eq = nullptr;  // [n][k] descriptors of split-eq rounds
+    alignas(16) uint8_t lag_w_h[7 * 32] = {0};  // interpolation weights for the nodes 0..d-1
     bool one_pass = false;       // large generic rounds run sc_round_generic
     bool has_prog = false;       // d_rtab / d_groups / d_prog are laid out (every shape that fits)
     uint32_t tail_start = ~0u;   // first round the resident last-rounds kernel may take over
@@ -172,15 +188,118 @@ static int launch_one_pass(dpb_sc* sc, uint32_t round, uint64_t n_pairs, const t
     return DPB_OK;
 }
 
+// Decides whether the large rounds can run in split-eq form and precomputes what they need.  Conditions: one-pass
+// rounds, degree >= 2, at most 32 groups, every group led by an eq table (tagged by dpb_eq_table / dpb_eq_tables,
+// full point, at most kMaxSplitEq of them) that no term uses as an inner factor, in every round the eq tables
+// that move share their coordinate, and no coordinate is 0 or 1 (their inverses are needed).
+template <class F>
+static void plan_spliteq(dpb_sc* sc, dpb_mle* const* mles, const std::vector<ProgGroup>& groups,
+                         const std::vector<ProgTerm<F>>& prog) {
+    typedef typename F::E E;
+    if (!sc->one_pass || sc->d < 2 || groups.size() > 32) return;
+    std::vector<dpb_sc::EqLead> leads;
+    std::vector<uint32_t> group_lead(groups.size());
+    for (size_t g = 0; g < groups.size(); g++) {
+        const uint32_t j = groups[g].outer;
+        if (j == kNoOuter || mles[j]->eq_point.size() != (size_t)sc->tr[j].nv * sizeof(E) || sc->tr[j].padded) return;
+        size_t at = leads.size();
+        for (size_t q = 0; q < leads.size(); q++)
+            if (leads[q].table == j) at = q;
+        if (at == leads.size()) {
+            if (leads.size() == (size_t)kMaxSplitEq) return;
+            dpb_sc::EqLead l;
+            l.table = j;
+            l.vars = sc->tr[j].nv;
+            l.first_active = sc->n - l.vars;
+            l.q = mles[j]->eq_point;
+            leads.push_back(l);
+        }
+        group_lead[g] = (uint32_t)at;
+    }
+    for (const auto& t : prog)
+        for (uint32_t f = 0; f < t.n_factors; f++)
+            for (const auto& l : leads)
+                if (t.idx[f] == l.table) return;  // an eq table inside a product: not of the form eq * G
+    // while a group's eq table does not move, nothing else in the group may: no factor with more variables
+    for (size_t g = 0; g < groups.size(); g++)
+        for (uint32_t t = groups[g].term_begin; t < groups[g].term_end; t++)
+            for (uint32_t f = 0; f < prog[t].n_factors; f++)
+                if (sc->tr[prog[t].idx[f]].nv > leads[group_lead[g]].vars) return;
+    // per round: the shared coordinate of the eq tables that move
+    const E one = F::one();
+    std::vector<E> rq(sc->n, F::zero());
+    for (uint32_t i = 0; i < sc->n; i++) {
+        bool have = false;
+        for (const auto& l : leads) {
+            if (i < l.first_active) continue;
+            E q;
+            memcpy(&q, l.q.data() + (size_t)(i - l.first_active) * sizeof(E), sizeof(E));
+            if (have && memcmp(&q, &rq[i], sizeof(E)) != 0) return;
+            rq[i] = q;
+            have = true;
+        }
+        if (!have) return;  // nothing moves in some round: leave it to the direct kernels
+        if (F::is_zero(rq[i]) || F::is_zero(F::sub(one, rq[i]))) return;
+    }
+    // inverses: one field inversion for all of them (Montgomery's trick)
+    std::vector<E> vals;  // the values to invert: per round q, per lead the prefix products of (1 - q_k)
+    for (uint32_t i = 0; i < sc->n; i++) vals.push_back(rq[i]);
+    for (auto& l : leads) {
+        E zp = one;
+        vals.push_back(zp);
+        for (uint32_t k = 0; k < l.vars; k++) {
+            E q;
+            memcpy(&q, l.q.data() + (size_t)k * sizeof(E), sizeof(E));
+            zp = F::mul(zp, F::sub(one, q));
+            vals.push_back(zp);
+        }
+    }
+    std::vector<E> pre(vals.size() + 1, one);
+    for (size_t a = 0; a < vals.size(); a++) pre[a + 1] = F::mul(pre[a], vals[a]);
+    E inv_all = F::inv(pre[vals.size()]);
+    std::vector<E> inv(vals.size());
+    for (size_t a = vals.size(); a-- > 0;) {
+        inv[a] = F::mul(inv_all, pre[a]);
+        inv_all = F::mul(inv_all, vals[a]);
+    }
+    sc->round_q.assign((const uint8_t*)rq.data(), (const uint8_t*)rq.data() + sc->n * sizeof(E));
+    sc->round_inv_q.assign((const uint8_t*)inv.data(), (const uint8_t*)inv.data() + sc->n * sizeof(E));
+    size_t at = sc->n;
+    for (auto& l : leads) {
+        l.inv_zp.assign((const uint8_t*)(inv.data() + at), (const uint8_t*)(inv.data() + at) + (l.vars + 1) * sizeof(E));
+        at += l.vars + 1;
+        memcpy(l.S, &one, sizeof(E));
+        memcpy(l.S_prev, &one, sizeof(E));
+    }
+    // interpolation weights for H (degree d - 1, nodes 0..d-1), once per process and degree
+    static E weights[7][7];
+    static bool have_w[7] = {false, false, false, false, false, false, false};
+    static std::mutex mu;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!have_w[sc->d]) {
+            lagrange_weights<F>((int)sc->d - 1, weights[sc->d]);
+            have_w[sc->d] = true;
+        }
+        memcpy(sc->lag_w_h, weights[sc->d], sc->d * sizeof(E));
+    }
+    sc->eq_leads = std::move(leads);
+    sc->group_lead = std::move(group_lead);
+    sc->spliteq = true;
+}
+
 // Host-side plan of the one-pass rounds and the resident kernel: the grouped term
 // program, launch shapes and shared-memory layouts.  No device work.
 template <class F>
-static void plan_program(dpb_sc* sc, const dpb_term* terms, std::vector<uint8_t>& h_groups, std::vector<uint8_t>& h_prog) {
+static void plan_program(dpb_sc* sc, const dpb_term* terms, dpb_mle* const* mles, std::vector<uint8_t>& h_groups,
+                         std::vector<uint8_t>& h_prog) {
     typedef typename F::E E;
     if (sc->k > 4096) return;  // very many tables: the two-pass kernels run every round
     std::vector<ProgGroup> groups;
     std::vector<ProgTerm<F>> prog;
-    compile_program<F>(terms, sc->n_terms, sc->k, groups, prog);
+    std::vector<bool> is_eq(sc->k);
+    for (uint32_t j = 0; j < sc->k; j++) is_eq[j] = mles[j]->eq_point.size() == (size_t)sc->tr[j].nv * sizeof(E);
+    compile_program<F>(terms, sc->n_terms, sc->k, groups, prog, is_eq);
     sc->n_groups = (uint32_t)groups.size();
     sc->n_prog_terms = (uint32_t)prog.size();
     h_groups.assign((const uint8_t*)groups.data(), (const uint8_t*)groups.data() + groups.size() * sizeof(ProgGroup));
@@ -228,6 +347,9 @@ static void plan_program(dpb_sc* sc, const dpb_term* terms, std::vector<uint8_t>
             sc->tail_start = i;
         }
     }
+    // split-eq form for the rounds before the resident kernel's; a sumcheck that is all "last rounds" skips the
+    // planning (it costs a field inversion on the host)
+    if (sc->tail_start > 0) plan_spliteq<F>(sc, mles, groups, prog);
 }
 
 // per-round descriptors of the one-pass kernels: which tables are bound inside the round's kernel
@@ -254,6 +376,127 @@ static void build_round_tabs(const dpb_sc* sc, std::vector<RoundTab>& rt) {
             }
         }
     }
+}
+
+// ---- split-eq rounds: host side ---------------------------------------------------
+
+// eq(q, c) = q c + (1 - q)(1 - c)
+template <class F>
+static typename F::E eq_scalar(const typename F::E& q, const typename F::E& c) {
+    const typename F::E one = F::one();
+    return F::add(F::mul(q, c), F::mul(F::sub(one, q), F::sub(one, c)));
+}
+
+// Called at the start of round i >= 1 with the challenge that ended round i - 1.
+template <class F>
+static void spliteq_advance(dpb_sc* sc, uint32_t i, const typename F::E& r) {
+    typedef typename F::E E;
+    for (auto& l : sc->eq_leads) {
+        memcpy(l.S_prev, l.S, sizeof(E));
+        if (i - 1 < l.first_active) continue;
+        E q, S;
+        memcpy(&q, l.q.data() + (size_t)(i - 1 - l.first_active) * sizeof(E), sizeof(E));
+        memcpy(&S, l.S, sizeof(E));
+        S = F::mul(S, eq_scalar<F>(q, r));
+        memcpy(l.S, &S, sizeof(E));
+    }
+}
+
+template <class F, int D>
+static int launch_spliteq(dpb_sc* sc, uint32_t round, uint64_t n_pairs, const typename F::E& r) {
+    typedef typename F::E E;
+    dpb_ctx* ctx = sc->ctx;
+    SplitEqArgs<F> eq;
+    memset(&eq, 0, sizeof eq);
+    for (size_t a = 0; a < sc->eq_leads.size(); a++) {
+        const auto& l = sc->eq_leads[a];
+        if (round < l.first_active) {
+            for (size_t g = 0; g < sc->group_lead.size(); g++)
+                if (sc->group_lead[g] == a) eq.const_groups |= 1u << g;
+            continue;
+        }
+        const uint32_t ip = round - l.first_active;
+        E S, iz;
+        memcpy(&S, l.S, sizeof(E));
+        memcpy(&iz, l.inv_zp.data() + (size_t)(ip + 1) * sizeof(E), sizeof(E));
+        eq.table[eq.n_eq] = l.table;
+        eq.stride_log2[eq.n_eq] = ip + 1;
+        eq.scale[eq.n_eq] = F::mul(S, iz);
+        eq.n_eq++;
+    }
+    const bool skip = round > 0;
+    if (skip)
+        DPB_CUDA(cudaFuncSetAttribute(sc_round_spliteq<F, D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kOnePassMaxSmem));
+    else
+        DPB_CUDA(cudaFuncSetAttribute(sc_round_spliteq<F, D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kOnePassMaxSmem));
+    uint64_t blocks = (n_pairs + sc->op_threads - 1) / sc->op_threads;
+    const uint64_t cap = (uint64_t)ctx->sm_count * (kOnePassMaxSmem / sc->op_smem ? kOnePassMaxSmem / sc->op_smem : 1);
+    if (blocks > cap) blocks = cap;
+    if (blocks > ctx->max_blocks) blocks = ctx->max_blocks;
+    const RoundTab* tabs = sc->d_rtab_eq + (size_t)round * sc->k;
+    const typename F::FoldKey rk = F::fold_key(r);
+    if (skip)
+        sc_round_spliteq<F, D, true><<<(uint32_t)blocks, sc->op_threads, sc->op_smem, ctx->stream>>>(
+            tabs, sc->k, (const ProgGroup*)sc->d_groups, sc->n_groups, (const ProgTerm<F>*)sc->d_prog, rk, eq, n_pairs,
+            reduce_scratch<F>(ctx), (E*)ctx->round_out);
+    else
+        sc_round_spliteq<F, D, false><<<(uint32_t)blocks, sc->op_threads, sc->op_smem, ctx->stream>>>(
+            tabs, sc->k, (const ProgGroup*)sc->d_groups, sc->n_groups, (const ProgTerm<F>*)sc->d_prog, rk, eq, n_pairs,
+            reduce_scratch<F>(ctx), (E*)ctx->round_out);
+    return DPB_OK;
+}
+
+// raw = H(0), [H(1)], .., H(d-1), C  ->  the round message s(0..d).  `claim` = s(0) + s(1), used after round 0.
+template <class F>
+static void spliteq_message(const dpb_sc* sc, uint32_t i, const typename F::E* raw, const typename F::E& claim,
+                            typename F::E* out) {
+    typedef typename F::E E;
+    const uint32_t d = sc->d;
+    E H[8];
+    for (uint32_t x = 0; x < d; x++) H[x] = raw[x];
+    const E C = raw[d], one = F::one();
+    E q, inv_q;
+    memcpy(&q, sc->round_q.data() + (size_t)i * sizeof(E), sizeof(E));
+    memcpy(&inv_q, sc->round_inv_q.data() + (size_t)i * sizeof(E), sizeof(E));
+    if (i > 0)  // s(0) + s(1) = (1 - q) H(0) + q H(1) + 2 C
+        H[1] = F::mul(F::sub(F::sub(claim, F::add(C, C)), F::mul(F::sub(one, q), H[0])), inv_q);
+    H[d] = lagrange_eval<F>((int)d - 1, H, (const E*)sc->lag_w_h, F::from_u64(d));
+    const E slope = F::sub(F::add(q, q), one);  // (1 - q) + (2 q - 1) x
+    E l = F::sub(one, q);
+    for (uint32_t x = 0; x <= d; x++) {
+        out[x] = F::add(F::mul(l, H[x]), C);
+        l = F::add(l, slope);
+    }
+}
+
+// The direct kernels (the resident one) are about to take over at round i: give every eq table that split-eq
+// rounds left unbound the bound copy those kernels expect as their input, the table of round i - 1.
+template <class F>
+static int spliteq_materialize(dpb_sc* sc, uint32_t i) {
+    typedef typename F::E E;
+    dpb_ctx* ctx = sc->ctx;
+    if (i == 0) return DPB_OK;
+    for (const auto& l : sc->eq_leads) {
+        if (i - 1 < l.first_active) continue;
+        const uint32_t f = i - 1 - l.first_active;  // variables bound in the table of round i - 1
+        if (f == 0) continue;                       // that table is the original
+        const void* ptr;
+        int dt;
+        bool active;
+        table_at_round(sc, l.table, i - 1, &ptr, &dt, &active);
+        E S, iz;
+        memcpy(&S, l.S_prev, sizeof(E));
+        memcpy(&iz, l.inv_zp.data() + (size_t)f * sizeof(E), sizeof(E));
+        const uint64_t n = 1ull << (l.vars - f);
+        eq_materialize<F><<<grid_for(ctx, n), kThreads, 0, ctx->stream>>>(sc->tr[l.table].orig, sc->tr[l.table].dtype, f,
+                                                                         F::mul(S, iz), n, (E*)ptr);
+        DPB_CUDA(cudaGetLastError());
+        ctx->sumcheck_launches++;
+    }
+    sc->eq_unbound = false;
+    return DPB_OK;
 }
 
 // ---- resident last-rounds kernel: host side -------------------------------------
@@ -329,6 +572,7 @@ static int tail_round(dpb_sc* sc, uint32_t i, const typename F::E& r, typename F
     dpb_ctx* ctx = sc->ctx;
     TailBox* box = (TailBox*)ctx->tail_box_host;
     if (!sc->tail_active) {
+        if (sc->eq_unbound) DPB_TRY(spliteq_materialize<F>(sc, i));
         memset(box, 0, sizeof(TailBox));  // sequence numbers of an earlier sumcheck must not be mistaken for ours
         std::atomic_thread_fence(std::memory_order_seq_cst);
         // the kernel runs on its own stream, after everything this context has queued so far
@@ -565,6 +809,7 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
         ctx->done_value = ctx->done_seq;
         ctx->done_flag_dev = sharded ? nullptr : ctx->flag_dev;
     }
+    if (sc->spliteq && i > 0) spliteq_advance<F>(sc, i, r);
     // the last rounds go to the resident kernel (one per context at a time; not while profiling per launch)
     bool use_tail = sc->tail_active || (sc->has_prog && ctx->tail_enabled && !sharded && !ctx->profile &&
                                         i >= sc->tail_start && ctx->tail_owner == nullptr);
@@ -585,7 +830,22 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
         done = true;
     }
     bool one_pass = use_tail;
-    if (!use_tail && !done && sc->one_pass) {
+    bool split = false;
+    if (!use_tail && !done && sc->spliteq) {
+        int rc = DPB_OK;
+        switch (sc->d) {
+            case 2: rc = launch_spliteq<F, 2>(sc, i, n_pairs, r); break;
+            case 3: rc = launch_spliteq<F, 3>(sc, i, n_pairs, r); break;
+            case 4: rc = launch_spliteq<F, 4>(sc, i, n_pairs, r); break;
+            case 5: rc = launch_spliteq<F, 5>(sc, i, n_pairs, r); break;
+            case 6: rc = launch_spliteq<F, 6>(sc, i, n_pairs, r); break;
+            default: return fail(DPB_EINVAL, "degree %u not supported", sc->d);
+        }
+        if (rc != DPB_OK) return rc;
+        one_pass = split = true;
+        sc->eq_unbound = true;
+    }
+    if (!use_tail && !done && !split && sc->one_pass) {
         int rc = DPB_OK;
         switch (sc->d) {
             case 1: rc = launch_one_pass<F, 1>(sc, i, n_pairs, r); break;
@@ -653,7 +913,13 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
         samples_to_evals<F>((int)sc->d, raw, i == 0, claim, (E*)out_evals, coeffs);
         memcpy(sc->prev_evals, out_evals, msg_bytes);
     } else {
-        if (one_pass && i > 0) {
+        if (split) {
+            // raw holds H at 0..d-1 (without 1 after round 0) and the constant part: rebuild the message
+            E claim = F::zero(), msg[kMaxAcc];
+            if (i > 0) claim = lagrange_eval<F>((int)sc->d, (const E*)sc->prev_evals, (const E*)sc->lag_w, r);
+            spliteq_message<F>(sc, i, raw, claim, msg);
+            memcpy(raw, msg, msg_bytes);
+        } else if (one_pass && i > 0) {
             // s(1) = previous s(r) - s(0)
             const E claim = lagrange_eval<F>((int)sc->d, (const E*)sc->prev_evals, (const E*)sc->lag_w, r);
             raw[1] = F::sub(claim, raw[0]);
@@ -671,7 +937,7 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
         if (i == 0) {
             for (uint32_t j = 0; j < sc->k; j++) bytes += dtype_size(sc->tr[j].dtype) << sc->tr[j].nv;
             name = done ? (sc->tr[0].dtype == DPB_GL_BASE ? "fused_eval0<base>" : "fused_eval0")
-                        : one_pass ? "sc_round_generic" : "sc_eval_generic";
+                        : split ? "sc_round_spliteq" : one_pass ? "sc_round_generic" : "sc_eval_generic";
         } else {
             const FoldDesc* fd = sc->h_fold.data() + (size_t)i * sc->k;
             for (uint32_t j = 0; j < sc->n_fold[i]; j++)
@@ -679,7 +945,7 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
             for (uint32_t j = 0; j < sc->k; j++)
                 if (sc->h_desc[(size_t)i * sc->k + j].shift >= 0) bytes += dtype_size(sc->tr[j].dtype) << sc->tr[j].nv;
             name = done ? (fd[0].dtype_in == DPB_GL_BASE ? "fused_fold_eval<base>" : "fused_fold_eval")
-                        : one_pass ? "sc_round_generic" : "sc_fold_generic+sc_eval_generic";
+                        : split ? "sc_round_spliteq" : one_pass ? "sc_round_generic" : "sc_fold_generic+sc_eval_generic";
         }
         bool found = false;
         for (auto& e : ctx->prof_log) {
@@ -716,6 +982,15 @@ static int run_finish(dpb_sc* sc, const void* last_challenge, void* out) {
     ctx->sumcheck_launches++;
     DPB_CUDA(cudaMemcpyAsync(out, sc->d_final, sc->k * sizeof(E), cudaMemcpyDeviceToHost, ctx->stream));
     DPB_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (sc->eq_unbound) {
+        // split-eq rounds never bound the eq tables: their value at the point is the running product of eq(q_k, c_k)
+        for (const auto& l : sc->eq_leads) {
+            E q, S;
+            memcpy(&q, l.q.data() + (size_t)(sc->n - 1 - l.first_active) * sizeof(E), sizeof(E));
+            memcpy(&S, l.S, sizeof(E));
+            ((E*)out)[l.table] = F::mul(S, eq_scalar<F>(q, r));
+        }
+    }
     return DPB_OK;
 }
 
@@ -811,10 +1086,10 @@ int dpb_sumcheck_begin(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, ui
     std::vector<uint8_t> h_terms, h_groups, h_prog;
     if (gl) {
         build_terms<GlFam>(sc, terms, h_terms);
-        if (!sc->ranged) plan_program<GlFam>(sc, terms, h_groups, h_prog);
+        if (!sc->ranged) plan_program<GlFam>(sc, terms, mles, h_groups, h_prog);
     } else {
         build_terms<FrFam>(sc, terms, h_terms);
-        if (!sc->ranged) plan_program<FrFam>(sc, terms, h_groups, h_prog);
+        if (!sc->ranged) plan_program<FrFam>(sc, terms, mles, h_groups, h_prog);
     }
     // ranged evaluation: per round and term, the pairs to visit and the tiles that cover them
     std::vector<uint64_t> h_tile_prefix, h_term_pairs;
@@ -850,7 +1125,8 @@ int dpb_sumcheck_begin(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, ui
     const size_t o_desc = take(nk * sizeof(MleDesc)), o_fold = take(nk * sizeof(FoldDesc)), o_terms = take(h_terms.size()),
                  o_final = take(k * es), o_rtab = take(sc->has_prog ? nk * sizeof(RoundTab) : 0),
                  o_groups = take(h_groups.size()), o_prog = take(h_prog.size()),
-                 o_tiles = take(h_tile_prefix.size() * 8), o_pairs = take(h_term_pairs.size() * 8);
+                 o_tiles = take(h_tile_prefix.size() * 8), o_pairs = take(h_term_pairs.size() * 8),
+                 o_rtab_eq = take(sc->spliteq ? nk * sizeof(RoundTab) : 0);
     int rc = device_alloc(ctx, off, &sc->slab);
     if (rc != DPB_OK) {
         delete sc;
@@ -865,6 +1141,7 @@ int dpb_sumcheck_begin(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, ui
         sc->d_rtab = (RoundTab*)(base + o_rtab);
         sc->d_groups = base + o_groups;
         sc->d_prog = base + o_prog;
+        sc->d_rtab_eq = (RoundTab*)(base + o_rtab_eq);
         sc->d_tile_prefix = (uint64_t*)(base + o_tiles);
         sc->d_term_pairs = (uint64_t*)(base + o_pairs);
         // ping-pong fold buffers of every table, at the front of the block
@@ -935,6 +1212,19 @@ int dpb_sumcheck_begin(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, ui
             std::vector<RoundTab> rt;
             build_round_tabs(sc, rt);
             put(o_rtab, rt.data(), rt.size() * sizeof(RoundTab));
+            if (sc->spliteq) {
+                // split-eq rounds read a leading eq table from its original, strided: no fold, marked constant
+                for (uint32_t i = 0; i < num_vars; i++)
+                    for (const auto& l : sc->eq_leads) {
+                        if (i < l.first_active) continue;
+                        RoundTab& t = rt[(size_t)i * k + l.table];
+                        t.in = sc->tr[l.table].orig;
+                        t.out = nullptr;
+                        t.dtype_in = sc->tr[l.table].dtype;
+                        t.shift = 0;
+                    }
+                put(o_rtab_eq, rt.data(), rt.size() * sizeof(RoundTab));
+            }
         }
         put(o_groups, h_groups.data(), h_groups.size());
         put(o_prog, h_prog.data(), h_prog.size());
@@ -968,6 +1258,7 @@ int dpb_sumcheck_begin_sharded(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* 
     dpb_sc* sc = nullptr;
     DPB_TRY(dpb_sumcheck_begin(ctx, n_loc, mles, k, terms, n_terms, &sc));
     sc->log2_ranks = c;
+    sc->spliteq = false;  // the shards of an eq table are not eq tables
     sc->terms_copy.assign(terms, terms + n_terms);
     *out = sc;
     return DPB_OK;

@@ -113,6 +113,9 @@ struct dpb_mle {
     void* ptr = nullptr;
     bool owns = false;
     bool zero_pad = false;  // in a sumcheck over more variables: zero above its length (else: constant in the early rounds)
+    // Set on the tables dpb_eq_table / dpb_eq_tables return: the point (challenge elements, native bytes) the table
+    // is the eq table of.  A sumcheck whose terms all carry such a table runs its large rounds in split-eq form.
+    std::vector<uint8_t> eq_point;
 };
 
 namespace dpb {

@@ -69,12 +69,15 @@ struct Slots {
 };
 
 // sum over groups of outer * sum over terms of coeff * product, at the tables' current values
+// (only the groups g with bit g of `mask` equal to `want`; mask = want = 0 takes all)
 template <class F>
 __device__ __noinline__ typename F::E eval_program(const Slots<F>& sl, const ProgGroup* __restrict__ groups,
-                                                   uint32_t n_groups, const ProgTerm<F>* __restrict__ terms) {
+                                                   uint32_t n_groups, const ProgTerm<F>* __restrict__ terms,
+                                                   uint32_t mask = 0, uint32_t want = 0) {
     typedef typename F::E E;
     E total = F::zero();
     for (uint32_t g = 0; g < n_groups; g++) {
+        if (((mask >> (g & 31)) & 1u) != want) continue;
         const ProgGroup pg = groups[g];
         E inner = F::zero();
         for (uint32_t t = pg.term_begin; t < pg.term_end; t++) {
@@ -147,6 +150,93 @@ __global__ void __launch_bounds__(kThreads)
         }
     }
     grid_sum_publish<F, D + 1>(acc, rs, out);
+}
+
+// ---- rounds in split-eq form -----------------------------------------------------
+//
+// When every group of the program is "an eq table times a sum of products", the
+// round polynomial factors.  After the first i' variables of an eq table over the
+// point q are bound to challenges c, its pair p is S * W[p] * ((1 - q_i'), q_i') with
+// S = prod_k eq(q_k, c_k) and W the eq table of the remaining coordinates, and W[p] is
+// the ORIGINAL table's entry p << (i' + 1) divided by prod_{k <= i'} (1 - q_k).  So
+//     s(X) = ((1 - q) + (2 q - 1) X) * H(X) + C,    H(X) = sum_p kappa * eq[p << (i' + 1)] * G(X, p),
+// with G the group's sum of products (one degree less than s), kappa a host-side scalar,
+// and C the groups whose tables do not move in this round.  The kernel accumulates H at
+// 0, 1, .., D - 1 (without 1 after round 0: the host gets H(1) from s(0) + s(1)) and C
+// once per pair; the eq tables are neither bound nor stored.  One evaluation point and
+// the eq table's folds less than the direct form; results are the same field elements.
+constexpr int kMaxSplitEq = 4;
+template <class F>
+struct SplitEqArgs {
+    uint32_t n_eq;                         // eq tables read in strided form this round
+    uint32_t const_groups;                 // bit g: group g does not depend on this round's variable
+    uint32_t table[kMaxSplitEq];           // their table ids
+    uint32_t stride_log2[kMaxSplitEq];     // pair p reads entry p << stride_log2 of the original table
+    typename F::E scale[kMaxSplitEq];      // kappa
+};
+
+// acc[x] = H(x) for x = 0..D-1 (x = 1 left at zero with SKIP_ONE), acc[D] = C.
+template <class F, int D, bool SKIP_ONE>
+__global__ void __launch_bounds__(kThreads)
+    sc_round_spliteq(const RoundTab* __restrict__ tabs, uint32_t k, const ProgGroup* __restrict__ groups,
+                     uint32_t n_groups, const ProgTerm<F>* __restrict__ terms, typename F::FoldKey rk,
+                     SplitEqArgs<F> eq, uint64_t n_pairs, ReduceScratch<F> rs, typename F::E* out) {
+    typedef typename F::E E;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    Slots<F> sl;
+    sl.base = (uint4*)smem_raw;
+    E acc[D + 1];
+#pragma unroll
+    for (int x = 0; x <= D; x++) acc[x] = F::zero();
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t p = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; p < n_pairs; p += stride) {
+        for (uint32_t j = 0; j < k; j++) {
+            const RoundTab t = tabs[j];
+            E f0, f1;
+            int e = -1;
+            for (uint32_t q = 0; q < eq.n_eq; q++)
+                if (eq.table[q] == j) e = (int)q;
+            if (e >= 0) {
+                // descriptors mark these tables constant (shift >= 0), so advance_point leaves them alone
+                f0 = F::mul(eq.scale[e], F::load(t.in, t.dtype_in, p << eq.stride_log2[e]));
+                f1 = f0;
+            } else if (t.out) {
+                E a0, a1, b0, b1;
+                F::load_pair(t.in, t.dtype_in, 2 * p, a0, a1);
+                F::load_pair(t.in, t.dtype_in, 2 * p + 1, b0, b1);
+                f0 = F::add(a0, F::mul_key(rk, F::sub(a1, a0)));
+                f1 = F::add(b0, F::mul_key(rk, F::sub(b1, b0)));
+                F::store(t.out, 2 * p, f0);
+                F::store(t.out, 2 * p + 1, f1);
+            } else if (t.shift < 0) {
+                F::load_pair(t.in, t.dtype_in, p, f0, f1);
+            } else {
+                f0 = F::load(t.in, t.dtype_in, p >> t.shift);
+                f1 = f0;
+            }
+            sl.put(2 * j, f0);
+            sl.put(2 * j + 1, F::sub(f1, f0));
+        }
+        if (eq.const_groups) acc[D] = F::add(acc[D], eval_program<F>(sl, groups, n_groups, terms, eq.const_groups, 1u));
+#pragma unroll
+        for (int x = 0; x < D; x++) {
+            if (!(SKIP_ONE && x == 1))
+                acc[x] = F::add(acc[x], eval_program<F>(sl, groups, n_groups, terms, eq.const_groups, 0u));
+            if (x < D - 1) advance_point<F>(sl, tabs, k);
+        }
+    }
+    grid_sum_publish<F, D + 1>(acc, rs, out);
+}
+
+// out[i] = scale * in[i << stride_log2]: an eq table in the bound form the direct kernels expect, made from the
+// original when a sumcheck leaves the split-eq form (the resident last-rounds kernel takes over).
+template <class F>
+__global__ void __launch_bounds__(kThreads)
+    eq_materialize(const void* __restrict__ in, int dtype_in, uint32_t stride_log2, typename F::E scale, uint64_t n,
+                   typename F::E* __restrict__ out) {
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        F::store(out, i, F::mul(scale, F::load(in, dtype_in, i << stride_log2)));
 }
 
 // ---- resident kernel for the last rounds ---------------------------------------
@@ -435,9 +525,10 @@ __global__ void __launch_bounds__(kTailThreads)
 
 // Groups terms by a shared table, greedily: the table that occurs in most of the
 // still ungrouped terms (at least two) becomes the outer factor of those terms.
+// Tables listed in `prefer` (eq tables) become outer factors first, whatever their counts.
 template <class F>
 inline void compile_program(const dpb_term* terms, uint32_t n_terms, uint32_t k, std::vector<ProgGroup>& groups,
-                            std::vector<ProgTerm<F>>& prog) {
+                            std::vector<ProgTerm<F>>& prog, const std::vector<bool>& prefer = std::vector<bool>()) {
     typedef typename F::E E;
     std::vector<bool> used(n_terms, false);
     uint32_t left = n_terms;
@@ -467,11 +558,16 @@ inline void compile_program(const dpb_term* terms, uint32_t n_terms, uint32_t k,
             }
         }
         uint32_t best = 0, best_n = 0;
-        for (uint32_t j = 0; j < k; j++)
-            if (count[j] > best_n) {
+        bool best_pref = false;
+        for (uint32_t j = 0; j < k; j++) {
+            const bool pref = j < prefer.size() && prefer[j] && count[j] > 0;
+            if ((pref && !best_pref) || (pref == best_pref && count[j] > best_n)) {
                 best_n = count[j];
                 best = j;
+                best_pref = pref;
             }
+        }
+        if (best_pref && best_n < 2) best_n = 2;  // an eq table leads its group even when a single term uses it
         ProgGroup g;
         g.pad = 0;
         g.term_begin = (uint16_t)prog.size();
