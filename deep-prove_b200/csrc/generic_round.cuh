@@ -38,12 +38,14 @@ struct ProgGroup {
     uint16_t outer, term_begin, term_end, pad;
 };
 
-// coeff * product of idx[0..n_factors) (the group's outer table is not listed)
+// coeff * product of idx[0..n_factors) (the group's outer table is not listed).  Terms of a group with the same
+// coefficient are stored next to each other; the coefficient multiplies their sum, at the term with run_last set.
 template <class F>
 struct ProgTerm {
     typename F::E coeff;
     uint16_t n_factors;
-    uint16_t coeff_is_one;
+    uint8_t coeff_is_one;
+    uint8_t run_last;
     uint16_t idx[DPB_MAX_FACTORS];
 };
 
@@ -79,19 +81,22 @@ __device__ __noinline__ typename F::E eval_program(const Slots<F>& sl, const Pro
     for (uint32_t g = 0; g < n_groups; g++) {
         if (((mask >> (g & 31)) & 1u) != want) continue;
         const ProgGroup pg = groups[g];
-        E inner = F::zero();
+        E inner = F::zero(), run = F::zero();
         for (uint32_t t = pg.term_begin; t < pg.term_end; t++) {
             const ProgTerm<F>& tm = terms[t];
             const uint32_t nf = tm.n_factors;
             E prod;
             if (nf == 0) {
-                prod = tm.coeff;
+                prod = F::one();
             } else {
                 prod = sl.get(2 * tm.idx[0]);
                 for (uint32_t j = 1; j < nf; j++) prod = F::mul(prod, sl.get(2 * tm.idx[j]));
-                if (!tm.coeff_is_one) prod = F::mul(prod, tm.coeff);
             }
-            inner = F::add(inner, prod);
+            run = F::add(run, prod);
+            if (tm.run_last) {
+                inner = F::add(inner, tm.coeff_is_one ? run : F::mul(run, tm.coeff));
+                run = F::zero();
+            }
         }
         if (pg.outer != kNoOuter) inner = F::mul(inner, sl.get(2 * pg.outer));
         total = F::add(total, inner);
@@ -382,19 +387,22 @@ __device__ __noinline__ typename F::E eval_program_at(const PairSlots<F>& sl, ui
     E total = F::zero();
     for (uint32_t g = 0; g < n_groups; g++) {
         const ProgGroup pg = groups[g];
-        E inner = F::zero();
+        E inner = F::zero(), run = F::zero();
         for (uint32_t t = pg.term_begin; t < pg.term_end; t++) {
             const ProgTerm<F>& tm = terms[t];
             const uint32_t nf = tm.n_factors;
             E prod;
             if (nf == 0) {
-                prod = tm.coeff;
+                prod = F::one();
             } else {
                 prod = sl.at(tm.idx[0], p, x);
                 for (uint32_t j = 1; j < nf; j++) prod = F::mul(prod, sl.at(tm.idx[j], p, x));
-                if (!tm.coeff_is_one) prod = F::mul(prod, tm.coeff);
             }
-            inner = F::add(inner, prod);
+            run = F::add(run, prod);
+            if (tm.run_last) {
+                inner = F::add(inner, tm.coeff_is_one ? run : F::mul(run, tm.coeff));
+                run = F::zero();
+            }
         }
         if (pg.outer != kNoOuter) inner = F::mul(inner, sl.at(pg.outer, p, x));
         total = F::add(total, inner);
@@ -596,6 +604,11 @@ inline void compile_program(const dpb_term* terms, uint32_t n_terms, uint32_t k,
             }
         }
         g.term_end = (uint16_t)prog.size();
+        // equal coefficients next to each other (stable: otherwise the caller's order), the last of each run marked
+        std::stable_sort(prog.begin() + g.term_begin, prog.begin() + g.term_end,
+                         [](const ProgTerm<F>& a, const ProgTerm<F>& b) { return memcmp(&a.coeff, &b.coeff, sizeof(E)) < 0; });
+        for (uint32_t t = g.term_begin; t < g.term_end; t++)
+            prog[t].run_last = (t + 1 == g.term_end || memcmp(&prog[t].coeff, &prog[t + 1].coeff, sizeof(E)) != 0) ? 1 : 0;
         groups.push_back(g);
     }
 }
