@@ -187,7 +187,8 @@ class Context:
         return bool(lib.dpb_comm_shared_exchange(self.h))
 
     def resident_rounds(self, enable=True, wait_ms=0):
-        """Last rounds in one resident kernel (default) or one launch per round; wait_ms bounds the kernel's waits."""
+        """Last rounds in one resident kernel (default) or one launch per round; wait_ms bounds the kernel's waits
+        for a challenge (a kernel that returned is started again by the next call)."""
         check(lib.dpb_resident_rounds(self.h, 1 if enable else 0, int(wait_ms)))
 
     def sumcheck_launches(self):

@@ -505,6 +505,7 @@ static int spliteq_materialize(dpb_sc* sc, uint32_t i) {
 // Polls the mailbox until `ready` holds; bounded, and the stream is queried now and then so that a
 // kernel that died or returned early surfaces as an error.
 constexpr int kTailNoHost = 1;  // internal: the kernel found that launches block the host; fall back to launches
+constexpr int kTailGaveUp = 2;  // internal: the kernel's wait for a challenge ran out and it returned
 
 template <class Ready>
 static int tail_wait_host(dpb_ctx* ctx, TailBox* box, Ready ready) {
@@ -512,7 +513,7 @@ static int tail_wait_host(dpb_ctx* ctx, TailBox* box, Ready ready) {
     std::chrono::steady_clock::time_point t0;
     while (!ready()) {
         if (box->status == 3) return kTailNoHost;
-        if (box->status == 2) return fail(DPB_ETIMEOUT, "the resident round kernel gave up waiting for a challenge");
+        if (box->status == 2) return kTailGaveUp;
         if ((++spins & 0xFFF) == 0) {
             cudaError_t e = cudaStreamQuery(ctx->tail_stream);
             if (e != cudaSuccess && e != cudaErrorNotReady)
@@ -566,63 +567,90 @@ static bool tail_take(const TailChunk* base, uint32_t idx, uint32_t seq, E* out)
 
 // Round i through the resident kernel: start it (first use) or post the challenge
 // that ends round i - 1, then wait for the sums of round i.
+// (Re)starts the resident kernel at round i; r is the challenge that ended round i - 1.
+template <class F>
+static int tail_start_kernel(dpb_sc* sc, uint32_t i, const typename F::E& r) {
+    dpb_ctx* ctx = sc->ctx;
+    TailBox* box = (TailBox*)ctx->tail_box_host;
+    memset(box, 0, sizeof(TailBox));  // sequence numbers of an earlier run must not be mistaken for this one's
+    std::atomic_thread_fence(std::memory_order_seq_cst);
+    // the kernel runs on its own stream, after everything this context has queued so far
+    DPB_CUDA(cudaEventRecord(ctx->tail_ev[0], ctx->stream));
+    DPB_CUDA(cudaStreamWaitEvent(ctx->tail_stream, ctx->tail_ev[0], 0));
+    int rc;
+    switch (sc->d) {
+        case 1: rc = launch_tail<F, 1>(sc, i, r); break;
+        case 2: rc = launch_tail<F, 2>(sc, i, r); break;
+        case 3: rc = launch_tail<F, 3>(sc, i, r); break;
+        case 4: rc = launch_tail<F, 4>(sc, i, r); break;
+        case 5: rc = launch_tail<F, 5>(sc, i, r); break;
+        case 6: rc = launch_tail<F, 6>(sc, i, r); break;
+        default: return fail(DPB_EINVAL, "degree %u not supported", sc->d);
+    }
+    if (rc != DPB_OK) return rc;
+    // first sign of life, as soon as the launch call is back (the kernel waits 50 ms for it)
+    ((volatile TailChunk*)&box->hello)->seq = 1;
+    DPB_CUDA(cudaEventRecord(ctx->tail_ev[1], ctx->tail_stream));
+    ctx->sumcheck_launches++;
+    return DPB_OK;
+}
+
+// Round i through the resident kernel: start it (first use) or post the challenge that ends round i - 1, then
+// wait for the sums of round i.  A kernel that gave up waiting for that challenge (the host was held up for longer
+// than the kernel's limit, e.g. by a device-wide synchronisation elsewhere in the process) has left every table as
+// round i - 1 made it, so it is started again at round i; only a second give-up in the same round is an error.
 template <class F>
 static int tail_round(dpb_sc* sc, uint32_t i, const typename F::E& r, typename F::E* raw) {
     typedef typename F::E E;
     dpb_ctx* ctx = sc->ctx;
     TailBox* box = (TailBox*)ctx->tail_box_host;
-    if (!sc->tail_active) {
+    const bool first = !sc->tail_active;
+    if (first) {
         if (sc->eq_unbound) DPB_TRY(spliteq_materialize<F>(sc, i));
-        memset(box, 0, sizeof(TailBox));  // sequence numbers of an earlier sumcheck must not be mistaken for ours
-        std::atomic_thread_fence(std::memory_order_seq_cst);
-        // the kernel runs on its own stream, after everything this context has queued so far
-        DPB_CUDA(cudaEventRecord(ctx->tail_ev[0], ctx->stream));
-        DPB_CUDA(cudaStreamWaitEvent(ctx->tail_stream, ctx->tail_ev[0], 0));
-        int rc;
-        switch (sc->d) {
-            case 1: rc = launch_tail<F, 1>(sc, i, r); break;
-            case 2: rc = launch_tail<F, 2>(sc, i, r); break;
-            case 3: rc = launch_tail<F, 3>(sc, i, r); break;
-            case 4: rc = launch_tail<F, 4>(sc, i, r); break;
-            case 5: rc = launch_tail<F, 5>(sc, i, r); break;
-            case 6: rc = launch_tail<F, 6>(sc, i, r); break;
-            default: return fail(DPB_EINVAL, "degree %u not supported", sc->d);
-        }
-        if (rc != DPB_OK) return rc;
-        // first sign of life, as soon as the launch call is back (the kernel waits 50 ms for it)
-        ((volatile TailChunk*)&box->hello)->seq = 1;
-        DPB_CUDA(cudaEventRecord(ctx->tail_ev[1], ctx->tail_stream));
-        ctx->sumcheck_launches++;
+        DPB_TRY(tail_start_kernel<F>(sc, i, r));
         sc->tail_active = true;
         ctx->tail_owner = sc;
     } else {
         tail_post<E>(box, &r, i);
     }
     const uint32_t want = i + 1;
-    uint32_t x = 0;  // sums taken so far; the sum at 1 is not sent after round 0
-    const int rc_wait = tail_wait_host(ctx, box, [&] {
-        while (x <= sc->d) {
-            if (i > 0 && x == 1) {
+    for (int attempt = 0;; attempt++) {
+        uint32_t x = 0;  // sums taken so far; the sum at 1 is not sent after round 0
+        const int rc_wait = tail_wait_host(ctx, box, [&] {
+            while (x <= sc->d) {
+                if (i > 0 && x == 1) {
+                    x++;
+                    continue;
+                }
+                if (!tail_take<E>(box->evals, x, want, &raw[x])) return false;
                 x++;
-                continue;
             }
-            if (!tail_take<E>(box->evals, x, want, &raw[x])) return false;
-            x++;
+            return true;
+        });
+        if (rc_wait == kTailNoHost) {
+            // launches block this host thread (a profiler that serialises them, or blocking launches): the kernel
+            // has left without touching anything; this context runs one launch per round from now on
+            cudaStreamSynchronize(ctx->tail_stream);
+            ctx->tail_enabled = false;
+            sc->tail_active = false;
+            ctx->tail_owner = nullptr;
+            return rc_wait;
         }
-        return true;
-    });
-    if (rc_wait == kTailNoHost) {
-        // launches block this host thread (a profiler that serialises them, or blocking launches): the kernel has
-        // left without touching anything; this context runs one launch per round from now on
-        cudaStreamSynchronize(ctx->tail_stream);
-        ctx->tail_enabled = false;
-        sc->tail_active = false;
-        ctx->tail_owner = nullptr;
+        if (rc_wait == kTailGaveUp && !first && attempt == 0) {
+            DPB_CUDA(cudaStreamSynchronize(ctx->tail_stream));  // it has returned; make that certain
+            DPB_TRY(tail_start_kernel<F>(sc, i, r));
+            continue;
+        }
+        if (rc_wait == kTailGaveUp)
+            return fail(DPB_ETIMEOUT, "the resident round kernel gave up waiting for a challenge");
+        return rc_wait;
     }
-    return rc_wait;
 }
 
 // Posts the last challenge, collects the final evaluations and releases the kernel's slot.
+template <class F>
+static int run_finish(dpb_sc* sc, const void* last_challenge, void* out);
+
 template <class F>
 static int tail_finish(dpb_sc* sc, const void* last_challenge, void* out) {
     typedef typename F::E E;
@@ -641,6 +669,11 @@ static int tail_finish(dpb_sc* sc, const void* last_challenge, void* out) {
     cudaStreamWaitEvent(ctx->stream, ctx->tail_ev[1], 0);
     sc->tail_active = false;
     ctx->tail_owner = nullptr;
+    if (rc == kTailGaveUp) {
+        // the kernel left after the last round without the last challenge: its tables are in place, one small launch
+        DPB_CUDA(cudaStreamSynchronize(ctx->tail_stream));
+        return run_finish<F>(sc, last_challenge, out);
+    }
     return rc;
 }
 

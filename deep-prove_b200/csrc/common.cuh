@@ -99,7 +99,7 @@ struct dpb_ctx {
     int up_next = 0;
     bool tail_enabled = true;
     uint64_t sumcheck_launches = 0;  // kernels launched by the sumcheck entry points
-    unsigned long long tail_wait_ns = 5ull * 1000 * 1000 * 1000;
+    unsigned long long tail_wait_ns = 1ull * 1000 * 1000 * 1000;
     // optional per-kernel timing log (dpb_profile_enable)
     bool profile = false;
     cudaEvent_t prof_ev[2] = {nullptr, nullptr};

@@ -126,8 +126,10 @@ int dpb_profile_read(dpb_ctx* ctx, dpb_profile_entry* out, uint32_t cap, uint32_
  * resident kernel that exchanges round sums and challenges with the host
  * through mapped memory instead of one launch per round.  enable = 0 turns
  * that off (every round is a launch); wait_ms bounds how long the kernel
- * waits for the next challenge before it gives up, after which the sumcheck's
- * next call returns DPB_ETIMEOUT (default 5000; 0 keeps the current value).
+ * waits for the next challenge before it returns (default 1000; 0 keeps the
+ * current value).  A kernel that returned this way is started again by the
+ * sumcheck's next call, so a host that was held up only loses time; a caller
+ * that synchronises the whole device between two rounds waits for that limit.
  * No reference counterpart: the reference's rounds are CPU loops. */
 int dpb_resident_rounds(dpb_ctx* ctx, int enable, uint32_t wait_ms);
 

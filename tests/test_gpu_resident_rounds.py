@@ -2,8 +2,10 @@
 sums for challenges with the host through mapped memory.  These tests pin
 that path against the one-launch-per-round path and the oracle, and check the
 ways out of the kernel that are not the normal one: a sumcheck that is dropped
-half way, two sumchecks advanced in turns on one context, and a host that does
-not answer (the kernel's wait is bounded and the next call reports it)."""
+half way, two sumchecks advanced in turns on one context, a host that is held
+up past the kernel's bounded wait (the kernel returns and is started again), and
+launches that block the host (the kernel leaves at once and rounds become
+launches)."""
 import time
 
 import numpy as np
@@ -92,28 +94,37 @@ def test_two_sumchecks_in_turns(dpb, ctx, F):
         assert (proofs[q], points[q], finals) == want[q]
 
 
-def test_host_that_does_not_answer(dpb, ctx):
-    """The kernel's wait for a challenge is bounded: it gives up, and the sumcheck's next call says so."""
-    F = orc.GlField
+@pytest.mark.parametrize("F", FIELDS)
+def test_host_that_is_held_up(dpb, ctx, F):
+    """The kernel's wait for a challenge is bounded: when the host takes longer (here: sleeps past a 200 ms limit,
+    twice, and once more before the last challenge) the kernel returns, the next call starts it again where it
+    stopped, and the proof is the same."""
     rng = np.random.default_rng(7300)
-    n = 5
-    tabs = [F.random_table_fast(rng, 1 << n) for _ in range(3)]
+    n = 6
+    tabs, terms = mixed_case(F, rng, n)
+    want = orc.sumcheck_prove(F, n, tabs, terms, orc.Transcript(F))
     mles = [upload(dpb, ctx, F, t) for t in tabs]
-    terms = {(0, 1, 2): F.one}
     ctx.resident_rounds(True, wait_ms=200)
     try:
         sc = ctx.sumcheck(n, mles, terms_array(dpb, F, terms))
-        sc.round(None)
-        time.sleep(0.6)  # well past the 200 ms the kernel waits
-        with pytest.raises(dpb.DpbError) as e:
-            sc.round(orc.scalars_to_array(F, [F.random_scalar(rng)]))
-        assert e.value.code == dpb.ETIMEOUT
+        tr = orc.Transcript(F)
+        tr.append_scalars([F.from_int(n), F.from_int(sc.degree)])
+        proof, point, r_arr = [], [], None
+        for i in range(n):
+            if i in (1, 4):
+                time.sleep(0.5)  # well past the 200 ms the kernel waits
+            ev = orc.array_to_scalars(F, sc.round(r_arr))
+            tr.append_scalars(ev)
+            r = tr.append_and_sample(orc.ROUND_LABEL)
+            proof.append(ev)
+            point.append(r)
+            r_arr = orc.scalars_to_array(F, [r])
+        time.sleep(0.5)
+        finals = orc.array_to_scalars(F, sc.finish(r_arr))
         sc.free()
     finally:
-        ctx.resident_rounds(True, wait_ms=5000)
-    # the context is usable afterwards
-    want = orc.sumcheck_prove(F, n, tabs, terms, orc.Transcript(F))
-    assert gpu_sumcheck_prove(dpb, ctx, F, n, mles, terms, orc.Transcript(F)) == want
+        ctx.resident_rounds(True, wait_ms=1000)
+    assert (proof, point, finals) == want
 
 
 def test_blocking_launches_fall_back_to_one_launch_per_round():
