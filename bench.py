@@ -60,7 +60,7 @@ def load_peak():
 
 class ClockSampler:
     """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
@@ -68,6 +68,11 @@ class ClockSampler:
         self.device = device
         self.proc = None
         self.path = None
+        self.window = None
+
+    def mark(self, t0, t1):
+        """Wall-clock bounds (time.time()) of the timed region; samples outside are dropped when enough lie inside."""
+        self.window = (t0, t1)
 
     def start(self):
         try:
@@ -88,24 +93,30 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        import datetime
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = []
         with open(self.path) as f:
             for line in f:
                 parts = [x.strip() for x in line.split(",")]
                 if len(parts) < 9:
                     continue
                 try:
-                    sm.append(float(parts[1]))
-                    mx.append(float(parts[2]))
+                    ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                    rows.append((ts, float(parts[1]), float(parts[2]),
+                                 [n for n, v in zip(names, parts[5:9]) if v.lower().startswith("active")]))
                 except ValueError:
                     continue
-                for name, val in zip(names, parts[5:9]):
-                    if val.lower().startswith("active"):
-                        reasons.add(name)
         os.unlink(self.path)
+        scope = "warm-up, timed and profiled steps (all under the same load)"
+        if self.window:
+            inside = [r for r in rows if self.window[0] - 0.05 <= r[0] <= self.window[1] + 0.05]
+            if len(inside) >= 3:
+                rows, scope = inside, "timed steps"
+        sm, mx = [r[1] for r in rows], [r[2] for r in rows]
+        reasons = sorted({n for r in rows for n in r[3]})
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": reasons, "samples": len(sm), "window": scope}
 
 
 def host_tables(field, n, seed, pinned):
@@ -253,18 +264,20 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     # ---- device-resident throughput
+    sampler = ClockSampler(local_rank)
+    sampler.start()  # before the warm-up: nvidia-smi takes a moment to deliver its first sample
     for _ in range(args.warmup):
         step_device()
-    sampler = ClockSampler(local_rank)
     barrier()
-    sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches0 = ctx.sumcheck_launches()
+    wall0 = time.time()
     e0.record(stream)
     for _ in range(args.steps):
         st = step_device()
     e1.record(stream)
     barrier()
+    sampler.mark(wall0, time.time())
     launches = ctx.sumcheck_launches() - launches0
     ms_total = e0.elapsed_time(e1)
     # per-kernel CUDA-event times: the same steps once more with the library's per-round events on
