@@ -257,13 +257,29 @@ class Context:
         check(lib.dpb_mle_evaluate(self.h, mle.h, _buf(p) if n else None, n, _buf(out)))
         return out
 
-    def einsum_fix_axes(self, family_dtype, tensor, kinds, points):
+    def upload_tensor_i64(self, tensor):
+        """An int64 tensor kept on the device as raw 64-bit words, for einsum_fix_axes(device_tensor=...)."""
+        t = np.ascontiguousarray(tensor, dtype=np.int64)
+        n = 1
+        while n < t.size:
+            n *= 2
+        flat = np.zeros(n, dtype=np.uint64)
+        flat[: t.size] = t.reshape(-1).view(np.uint64)
+        return self.upload(flat, GL_BASE), tuple(t.shape)
+
+    def einsum_fix_axes(self, family_dtype, tensor, kinds, points, device_tensor=None):
         """dpb_einsum_fix_axes.  tensor: int64 ndarray (unpadded); kinds[a] in
         AXIS_*; points[a]: challenge elements uint64[len, words] for outer axes,
-        None otherwise.  Returns (owner, [views])."""
-        t = np.ascontiguousarray(tensor, dtype=np.int64)
-        rank = t.ndim
-        shape = (ctypes.c_uint64 * rank)(*t.shape)
+        None otherwise.  device_tensor = upload_tensor_i64(...) uses a tensor that
+        is already on the device instead.  Returns (owner, [views])."""
+        if device_tensor is not None:
+            mle, tshape = device_tensor
+            t = None
+        else:
+            t = np.ascontiguousarray(tensor, dtype=np.int64)
+            tshape = t.shape
+        rank = len(tshape)
+        shape = (ctypes.c_uint64 * rank)(*tshape)
         kd = (ctypes.c_uint8 * rank)(*kinds)
         keep = [np.ascontiguousarray(p, dtype=np.uint64) if p is not None else None for p in points]
         pts = (ctypes.c_void_p * rank)(*[k.ctypes.data if k is not None and k.size else None for k in keep])
@@ -271,12 +287,13 @@ class Context:
         cap = 1
         for a in range(rank):
             if kinds[a] == AXIS_STACKED:
-                cap *= t.shape[a]
+                cap *= tshape[a]
         views = (ctypes.c_void_p * cap)()
         owner = ctypes.c_void_p()
         n = ctypes.c_uint32()
-        check(lib.dpb_einsum_fix_axes(self.h, family_dtype, _buf(t), 0, shape, kd, pts, lens, rank, ctypes.byref(owner),
-                                      views, cap, ctypes.byref(n)))
+        src = _buf(t) if t is not None else ctypes.c_void_p(lib.dpb_mle_device_ptr(mle.h))
+        check(lib.dpb_einsum_fix_axes(self.h, family_dtype, src, 0 if t is not None else 1, shape, kd, pts, lens, rank,
+                                      ctypes.byref(owner), views, cap, ctypes.byref(n)))
         return Mle(self, owner), [Mle(self, ctypes.c_void_p(views[i])) for i in range(n.value)]
 
     def sumcheck(self, num_vars, mles, terms, sharded=False):

@@ -3,6 +3,7 @@
 #include <algorithm>
 
 #include "common.cuh"
+#include "fix_kernels.cuh"
 #include "poly_kernels.cuh"
 
 namespace dpb {
@@ -154,9 +155,9 @@ static int fix_vars_impl(dpb_ctx* ctx, const void* in, int dtype_in, uint64_t le
             return rc;
         }
         if (high)
-            fix_high_pass<F><<<grid_for(ctx, n_out), kThreads, 0, ctx->stream>>>(cur, cur_dtype, w, g, n_out, nxt);
+            fix_high_sum<F><<<grid_for(ctx, n_out), kThreads, 0, ctx->stream>>>(cur, cur_dtype, w, g, n_out, nxt);
         else
-            fix_low_pass<F><<<grid_for(ctx, cur_len), kThreads, 0, ctx->stream>>>(cur, cur_dtype, w, g, cur_len, nxt);
+            fix_low_sum<F><<<grid_for(ctx, n_out), kThreads, 0, ctx->stream>>>(cur, cur_dtype, w, g, n_out, nxt);
         device_free(ctx, owned);
         owned = nxt;
         cur = nxt;

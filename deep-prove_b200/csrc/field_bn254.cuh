@@ -200,6 +200,30 @@ DPB_HD Fr fr_mul(const Fr& a, const Fr& b) {
 __device__ __forceinline__ Fr fr_mul_fixed(const frw::FixedMul& k, const Fr& a) {
     return frw::to_fr(frw::mul_fixed(frw::from_fr(a), k));
 }
+// Sum of integer * field-element products, lazily: see frw::IntAcc.  `w` in Montgomery form; the result is the
+// Montgomery form of sum x_o * w_o.  A negative x adds |x| * (r - w).
+struct FrIntAcc {
+    frw::IntAcc a;
+};
+__device__ __forceinline__ FrIntAcc fr_intacc_zero() {
+    FrIntAcc r;
+    r.a = frw::intacc_zero();
+    return r;
+}
+__device__ __forceinline__ void fr_intacc_mac(FrIntAcc& acc, const Fr& w, int64_t x) {
+    const uint64_t mag = x < 0 ? (uint64_t)0 - (uint64_t)x : (uint64_t)x;
+    frw::intacc_mac(acc.a, frw::from_fr(x < 0 ? fr_neg(w) : w), mag);
+}
+__device__ __forceinline__ Fr fr_intacc_finish(const FrIntAcc& acc) {
+    // S = lo + 2^256 hi: lo * R / R = lo mod r, hi * R^2 / R = hi * 2^256 mod r (inputs below 2^256 are fine: the
+    // other factor is below r, so the Montgomery product stays below 2 r before its last subtraction)
+    frw::F8 lo, hi;
+    frw::intacc_split(acc.a, lo, hi);
+    const Fr a = frw::to_fr(frw::mul(lo, frw::from_fr(fr_one())));
+    const Fr b = frw::to_fr(frw::mul(hi, frw::from_fr(fr_rr())));
+    return fr_add(a, b);
+}
+
 // 2^(32 i + 64) mod r as a plain integer, i = 0..7
 DPB_HD Fr fr_fixed_power(int i) {
     Fr x;

@@ -191,6 +191,67 @@ __device__ __forceinline__ F8 mul_fixed(const F8& a, const FixedMul& k) {
     return reduce_once(s);
 }
 
+// Sum of (64-bit integer) * (field element) products kept as one unreduced integer: what the contraction of an
+// integer tensor against eq weights is made of.  A term is 16 wide multiply-adds and no reduction; the sum of up to
+// 2^24 terms stays below 2^352 and is reduced once (two Montgomery products).  Layout as in mul: E holds word pairs
+// at even positions, O at odd positions, value = E + O; words 0..11.
+struct IntAcc {
+    uint32_t E[12], O[12];
+};
+__device__ __forceinline__ IntAcc intacc_zero() {
+    IntAcc a;
+#pragma unroll
+    for (int i = 0; i < 12; i++) a.E[i] = a.O[i] = 0;
+    return a;
+}
+// four pairs starting at c += (x0..x3) * y, the carry runs on through three more words
+__device__ __forceinline__ void chain_mul_long(uint32_t* c, uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3, uint32_t y) {
+    asm("mad.lo.cc.u32 %0, %12, %11, %0; madc.hi.cc.u32 %1, %12, %11, %1;\n\t"
+        "madc.lo.cc.u32 %2, %13, %11, %2; madc.hi.cc.u32 %3, %13, %11, %3;\n\t"
+        "madc.lo.cc.u32 %4, %14, %11, %4; madc.hi.cc.u32 %5, %14, %11, %5;\n\t"
+        "madc.lo.cc.u32 %6, %15, %11, %6; madc.hi.cc.u32 %7, %15, %11, %7;\n\t"
+        "addc.cc.u32 %8, %8, 0; addc.cc.u32 %9, %9, 0; addc.u32 %10, %10, 0;"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]), "+r"(c[4]), "+r"(c[5]), "+r"(c[6]), "+r"(c[7]), "+r"(c[8]),
+          "+r"(c[9]), "+r"(c[10])
+        : "r"(y), "r"(x0), "r"(x1), "r"(x2), "r"(x3));
+}
+// acc += mag * w, mag a 64-bit magnitude, w any 256-bit value
+__device__ __forceinline__ void intacc_mac(IntAcc& a, const F8& w, uint64_t mag) {
+    const uint32_t m0 = (uint32_t)mag, m1 = (uint32_t)(mag >> 32);
+    chain_mul_long(a.E, w.w[0], w.w[2], w.w[4], w.w[6], m0);      // positions (0,1) .. (6,7)
+    chain_mul_long(a.O + 1, w.w[1], w.w[3], w.w[5], w.w[7], m0);  // positions (1,2) .. (7,8)
+    if (m1) {  // quantised values seldom need the upper word
+        chain_mul_long(a.O + 1, w.w[0], w.w[2], w.w[4], w.w[6], m1);  // one word up: (1,2) .. (7,8)
+        // two words up: (2,3) .. (8,9); the carry has one word of room left (the sum stays below 2^352)
+        asm("mad.lo.cc.u32 %0, %10, %9, %0; madc.hi.cc.u32 %1, %10, %9, %1;\n\t"
+            "madc.lo.cc.u32 %2, %11, %9, %2; madc.hi.cc.u32 %3, %11, %9, %3;\n\t"
+            "madc.lo.cc.u32 %4, %12, %9, %4; madc.hi.cc.u32 %5, %12, %9, %5;\n\t"
+            "madc.lo.cc.u32 %6, %13, %9, %6; madc.hi.cc.u32 %7, %13, %9, %7;\n\t"
+            "addc.cc.u32 %8, %8, 0;"
+            : "+r"(a.E[2]), "+r"(a.E[3]), "+r"(a.E[4]), "+r"(a.E[5]), "+r"(a.E[6]), "+r"(a.E[7]), "+r"(a.E[8]),
+              "+r"(a.E[9]), "+r"(a.E[10])
+            : "r"(m1), "r"(w.w[1]), "r"(w.w[3]), "r"(w.w[5]), "r"(w.w[7]));
+    }
+}
+// the sum as words 0..10 (E + O), low 8 words and the words above them
+__device__ __forceinline__ void intacc_split(const IntAcc& a, F8& lo, F8& hi) {
+    uint32_t s[12];
+    asm("add.cc.u32 %0, %12, %24; addc.cc.u32 %1, %13, %25; addc.cc.u32 %2, %14, %26; addc.cc.u32 %3, %15, %27;\n\t"
+        "addc.cc.u32 %4, %16, %28; addc.cc.u32 %5, %17, %29; addc.cc.u32 %6, %18, %30; addc.cc.u32 %7, %19, %31;\n\t"
+        "addc.cc.u32 %8, %20, %32; addc.cc.u32 %9, %21, %33; addc.cc.u32 %10, %22, %34; addc.u32 %11, %23, %35;"
+        : "=&r"(s[0]), "=&r"(s[1]), "=&r"(s[2]), "=&r"(s[3]), "=&r"(s[4]), "=&r"(s[5]), "=&r"(s[6]), "=&r"(s[7]),
+          "=&r"(s[8]), "=&r"(s[9]), "=&r"(s[10]), "=&r"(s[11])
+        : "r"(a.E[0]), "r"(a.E[1]), "r"(a.E[2]), "r"(a.E[3]), "r"(a.E[4]), "r"(a.E[5]), "r"(a.E[6]), "r"(a.E[7]),
+          "r"(a.E[8]), "r"(a.E[9]), "r"(a.E[10]), "r"(a.E[11]), "r"(a.O[0]), "r"(a.O[1]), "r"(a.O[2]), "r"(a.O[3]),
+          "r"(a.O[4]), "r"(a.O[5]), "r"(a.O[6]), "r"(a.O[7]), "r"(a.O[8]), "r"(a.O[9]), "r"(a.O[10]), "r"(a.O[11]));
+#pragma unroll
+    for (int i = 0; i < 8; i++) lo.w[i] = s[i];
+#pragma unroll
+    for (int i = 0; i < 4; i++) hi.w[i] = s[8 + i];
+#pragma unroll
+    for (int i = 4; i < 8; i++) hi.w[i] = 0;
+}
+
 __device__ __forceinline__ F8 add(const F8& a, const F8& b) {
     F8 s;
     asm("add.cc.u32 %0, %8, %16; addc.cc.u32 %1, %9, %17; addc.cc.u32 %2, %10, %18; addc.cc.u32 %3, %11, %19;\n\t"

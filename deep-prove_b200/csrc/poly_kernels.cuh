@@ -132,43 +132,6 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
-// ---- partial evaluation ----------------------------------------------------
-// Top g variables: out[j] = sum_{h < 2^g} w[h] * in[h * n_out + j].
-template <class F>
-__global__ void fix_high_pass(const void* __restrict__ in, int dtype_in,
-                              const typename F::E* __restrict__ w, uint32_t g, uint64_t n_out,
-                              typename F::E* __restrict__ out) {
-    typedef typename F::E E;
-    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
-    const uint32_t H = 1u << g;
-    for (uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; j < n_out; j += stride) {
-        E acc = F::zero();
-        for (uint32_t h = 0; h < H; h++)
-            acc = F::add(acc, F::mul(w[h], F::load(in, dtype_in, (uint64_t)h * n_out + j)));
-        F::store(out, j, acc);
-    }
-}
-
-// Bottom g variables (g <= 5): out[j] = sum_{l < 2^g} w[l] * in[j * 2^g + l].
-// One thread per input entry; groups of 2^g lanes add up with shuffles.
-// blockDim.x must be a multiple of 32; n_in is a multiple of 2^g.
-template <class F>
-__global__ void fix_low_pass(const void* __restrict__ in, int dtype_in,
-                             const typename F::E* __restrict__ w, uint32_t g, uint64_t n_in,
-                             typename F::E* __restrict__ out) {
-    typedef typename F::E E;
-    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
-    const uint32_t G = 1u << g;
-    // every lane of a warp runs the same number of iterations: round n_in up to a warp multiple
-    const uint64_t n_round = (n_in + 31) & ~31ull;
-    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_round; i += stride) {
-        E v = F::zero();
-        if (i < n_in) v = F::mul(w[i & (G - 1)], F::load(in, dtype_in, i));
-        for (uint32_t off = G >> 1; off > 0; off >>= 1) v = F::add(v, F::shfl_down(v, off));
-        if (i < n_in && (i & (G - 1)) == 0) F::store(out, i >> g, v);
-    }
-}
-
 // One source table of a linear combination.
 struct LinCombSrc {
     const void* ptr;

@@ -125,6 +125,11 @@ def main():
     K2 = (dpb.AXIS_CONTRACTED, dpb.AXIS_OUTER)
     t = timed(ctx, lambda: [h.free() for h in ctx.einsum_fix_axes(fam, wt, K2, [None, p12])[1]], args.reps)
     report("einsum fix_axes W[768,3072], bind columns", t, wt.size * 8)
+    dx, dw = ctx.upload_tensor_i64(x), ctx.upload_tensor_i64(wt)
+    t = timed(ctx, lambda: [h.free() for h in ctx.einsum_fix_axes(fam, None, K, [p9, None], device_tensor=dx)[1]], args.reps)
+    report("  the same, tensor already on the device", t, x.size * 8)
+    t = timed(ctx, lambda: [h.free() for h in ctx.einsum_fix_axes(fam, None, K2, [None, p12], device_tensor=dw)[1]], args.reps)
+    report("  the same, tensor already on the device", t, wt.size * 8)
 
     # claim batching of the opening proof: many committed polynomials of mixed sizes, one claim each, all
     # zero-padded to the largest; bytes = sumcheck traffic of every polynomial and its eq table at its own size

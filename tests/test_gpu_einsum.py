@@ -45,6 +45,35 @@ def test_fix_axes_matches_oracle(dpb, ctx, F, shape, kinds):
         assert (v.to_host().reshape(w.shape) == w).all()
         v.free()
     owner.free()
+    # the same from a tensor that is already on the device
+    owner, views = ctx.einsum_fix_axes(family_dtype(dpb, F), None, kinds,
+                                       [orc.scalars_to_array(F, p) if p is not None else None for p in pts],
+                                       device_tensor=ctx.upload_tensor_i64(t))
+    for v, w in zip(views, want):
+        assert (v.to_host().reshape(w.shape) == w).all()
+        v.free()
+    owner.free()
+
+
+@pytest.mark.parametrize("F", FIELDS)
+def test_fix_axes_full_range_entries(dpb, ctx, F):
+    """Entries over the whole int64 range (both 32-bit halves of the magnitude in use, both signs, the extremes):
+    the contraction adds integer * weight products up unreduced, so the wide cases must be exact too."""
+    rng = np.random.default_rng(4242)
+    shape, kinds = (37, 20), (O, C)
+    t = rng.integers(-2**63, 2**63 - 1, size=shape, dtype=np.int64)
+    t[0, 0], t[1, 0], t[2, 0], t[3, 0] = -2**63, 2**63 - 1, 0, -1
+    pts = points_for(F, rng, shape, kinds)
+    want = orc.mles_from_tensor(F, t, kinds, pts)
+    for k2, t2 in ((kinds, t), ((C, O), np.ascontiguousarray(t.T))):
+        pts2 = pts if k2 == kinds else pts[::-1]
+        want = orc.mles_from_tensor(F, t2, k2, pts2)
+        owner, views = ctx.einsum_fix_axes(family_dtype(dpb, F), t2, k2,
+                                           [orc.scalars_to_array(F, p) if p is not None else None for p in pts2])
+        for v, w in zip(views, want):
+            assert (v.to_host().reshape(w.shape) == w).all()
+            v.free()
+        owner.free()
 
 
 @pytest.mark.parametrize("F", FIELDS)
