@@ -76,19 +76,23 @@ int sync_bounded(dpb_ctx* ctx, double seconds) {
 int xch_collect(dpb_ctx* ctx, unsigned int seq, size_t msg_bytes, void* out, double seconds) {
     const auto t0 = std::chrono::steady_clock::now();
     uint64_t spins = 0;
+    const size_t words = msg_bytes / 8;
     for (int q = 0; q < ctx->nranks; q++) {
-        const char* slot = (const char*)ctx->xch_host + xch_slot_offset(q, seq);
-        const volatile unsigned int* flag = (const volatile unsigned int*)slot;
-        while (*flag != seq) {
-            if ((++spins & 0xFFF) == 0) {
-                cudaError_t e = cudaStreamQuery(ctx->stream);  // our own launch may have failed
-                if (e != cudaSuccess && e != cudaErrorNotReady) return fail(DPB_ECUDA, "round kernel: %s", cudaGetErrorString(e));
-                const double dt = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
-                if (dt > seconds) return fail(DPB_ETIMEOUT, "waited %.1f s for the partial sums of rank %d", dt, q);
+        const volatile TailChunk* c = (const volatile TailChunk*)((const char*)ctx->xch_host + xch_slot_offset(q, seq));
+        uint64_t* dst = (uint64_t*)((char*)out + (size_t)q * msg_bytes);
+        for (size_t w = 0; w < words; w++) {
+            while (c[w].seq != seq) {
+                if ((++spins & 0xFFF) == 0) {
+                    cudaError_t e = cudaStreamQuery(ctx->stream);  // our own launch may have failed
+                    if (e != cudaSuccess && e != cudaErrorNotReady)
+                        return fail(DPB_ECUDA, "round kernel: %s", cudaGetErrorString(e));
+                    const double dt = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+                    if (dt > seconds) return fail(DPB_ETIMEOUT, "waited %.1f s for the partial sums of rank %d", dt, q);
+                }
             }
+            std::atomic_thread_fence(std::memory_order_acquire);
+            dst[w] = c[w].data;
         }
-        std::atomic_thread_fence(std::memory_order_acquire);
-        memcpy((char*)out + (size_t)q * msg_bytes, slot + 64, msg_bytes);
     }
     return DPB_OK;
 }

@@ -303,8 +303,6 @@ int dpb_init(int device, dpb_ctx** out) {
     DPB_CUDA(cudaHostAlloc(&ctx->result_host, ctx->result_bytes, cudaHostAllocMapped));
     DPB_CUDA(cudaHostGetDevicePointer(&ctx->result_dev, ctx->result_host, 0));
     memset(ctx->result_host, 0, ctx->result_bytes);
-    ctx->flag_host = (volatile unsigned int*)((char*)ctx->result_host + ctx->result_bytes - 64);
-    ctx->flag_dev = (unsigned int*)((char*)ctx->result_dev + ctx->result_bytes - 64);
     ctx->stage_bytes = 64 * 1024;
     DPB_CUDA(cudaMalloc(&ctx->stage_dev, ctx->stage_bytes));
     DPB_CUDA(cudaEventCreate(&ctx->prof_ev[0]));

@@ -788,30 +788,34 @@ static void launch_fused(dpb_ctx* ctx, const MleDesc* desc, const FoldDesc* fold
     else launch_fused_fr<4>(ctx, desc, folds, round, r, n_pairs);
 }
 
-// Polls the completion flag of the round just launched.  The kernel's last
-// block stores the sequence number after the result, so the host sees the
-// result without paying a stream synchronisation; the stream is queried now and
-// then so that a failed launch surfaces, and the wait is bounded.
-static int wait_round_flag(dpb_ctx* ctx) {
-    const unsigned int want = ctx->done_seq;
+// Collects the sums of the round just launched from the chunk area in mapped host memory: every chunk carries
+// the launch's sequence number once it has arrived.  The stream is queried now and then so that a failed launch
+// surfaces, and the wait is bounded.
+static int wait_round_chunks(dpb_ctx* ctx, size_t msg_bytes, void* out) {
+    const unsigned int want = ctx->done_value;
+    const volatile TailChunk* c = (const volatile TailChunk*)ctx->result_host;
+    uint64_t* dst = (uint64_t*)out;
     uint64_t spins = 0;
     std::chrono::steady_clock::time_point t0;
-    while (*ctx->flag_host != want) {
-        if ((++spins & 0xFFF) == 0) {
-            cudaError_t e = cudaStreamQuery(ctx->stream);
-            if (e != cudaSuccess && e != cudaErrorNotReady) return fail(DPB_ECUDA, "round kernel: %s", cudaGetErrorString(e));
-            if (e == cudaSuccess && *ctx->flag_host != want) {
-                // the stream drained without the flag: the launch itself failed
-                e = cudaGetLastError();
-                if (*ctx->flag_host == want) break;
-                return fail(DPB_ECUDA, "round kernel did not signal completion (%s)", cudaGetErrorString(e));
+    for (size_t w = 0; w < msg_bytes / 8; w++) {
+        while (c[w].seq != want) {
+            if ((++spins & 0xFFF) == 0) {
+                cudaError_t e = cudaStreamQuery(ctx->stream);
+                if (e != cudaSuccess && e != cudaErrorNotReady) return fail(DPB_ECUDA, "round kernel: %s", cudaGetErrorString(e));
+                if (e == cudaSuccess && c[w].seq != want) {
+                    // the stream drained without the result: the launch itself failed
+                    e = cudaGetLastError();
+                    if (c[w].seq == want) break;
+                    return fail(DPB_ECUDA, "round kernel did not deliver its result (%s)", cudaGetErrorString(e));
+                }
+                if (spins == 0x1000) t0 = std::chrono::steady_clock::now();
+                else if (std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() > 120.0)
+                    return fail(DPB_ETIMEOUT, "round kernel did not finish within 120 s");
             }
-            if (spins == 0x1000) t0 = std::chrono::steady_clock::now();
-            else if (std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() > 120.0)
-                return fail(DPB_ETIMEOUT, "round kernel did not finish within 120 s");
         }
+        std::atomic_thread_fence(std::memory_order_acquire);
+        dst[w] = c[w].data;
     }
-    std::atomic_thread_fence(std::memory_order_acquire);
     return DPB_OK;
 }
 
@@ -831,16 +835,15 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
     if (shared_xch) {
         // this rank's slot of the shared host segment: the kernel's last block writes the sums, then the sequence number
         ctx->xseq++;
-        char* slot = (char*)ctx->xch_dev + xch_slot_offset(ctx->rank, ctx->xseq);
-        ctx->round_out = slot + 64;
-        ctx->done_flag_dev = (unsigned int*)slot;
+        ctx->chunk_out_dev = (char*)ctx->xch_dev + xch_slot_offset(ctx->rank, ctx->xseq);
+        ctx->round_out = nullptr;
         ctx->done_value = ctx->xseq;
     } else {
         ctx->round_out = sharded ? (void*)((char*)ctx->gather_dev + (size_t)ctx->rank * msg_bytes) : ctx->result_dev;
         // unsharded rounds signal completion through a flag in mapped host memory that the host polls
         ctx->done_seq++;
         ctx->done_value = ctx->done_seq;
-        ctx->done_flag_dev = sharded ? nullptr : ctx->flag_dev;
+        ctx->chunk_out_dev = sharded ? nullptr : ctx->result_dev;
     }
     if (sc->spliteq && i > 0) spliteq_advance<F>(sc, i, r);
     // the last rounds go to the resident kernel (one per context at a time; not while profiling per launch)
@@ -935,8 +938,7 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
             raw[x] = tot;
         }
     } else {
-        DPB_TRY(wait_round_flag(ctx));
-        memcpy(raw, ctx->result_host, msg_bytes);
+        DPB_TRY(wait_round_chunks(ctx, msg_bytes, raw));
     }
     if (done) {
         // samples -> evaluations at 0..=d; P(1) of later rounds comes from the previous round's polynomial
@@ -1044,12 +1046,11 @@ static int start_tail(dpb_sc* sc, const void* prev_challenge) {
     DPB_TRY(allgather_to_host(ctx, slot, bytes));
     // gathered[g][j] -> table j entry g (rank g owns the top-variable block g)
     const E* g = (const E*)ctx->gather_host;
-    E* stage = (E*)ctx->result_host;
+    std::vector<E> stage((size_t)sc->k * G);
     for (uint32_t j = 0; j < sc->k; j++)
         for (int q = 0; q < G; q++) stage[(size_t)j * G + q] = g[(size_t)q * sc->k + j];
-    DPB_TRY(device_alloc(ctx, (size_t)sc->k * G * sizeof(E), &sc->tail_dev));
-    DPB_CUDA(cudaMemcpyAsync(sc->tail_dev, stage, (size_t)sc->k * G * sizeof(E), cudaMemcpyHostToDevice, ctx->stream));
-    DPB_CUDA(cudaStreamSynchronize(ctx->stream));
+    DPB_TRY(device_alloc(ctx, stage.size() * sizeof(E), &sc->tail_dev));
+    DPB_TRY(upload_small(ctx, sc->tail_dev, stage.data(), stage.size() * sizeof(E)));
     for (uint32_t j = 0; j < sc->k; j++) {
         dpb_mle* m = nullptr;
         DPB_TRY(dpb_mle_from_device(ctx, F::kChalDtype, (char*)sc->tail_dev + (size_t)j * G * sizeof(E), (uint64_t)G, &m));

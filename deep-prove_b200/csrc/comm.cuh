@@ -18,9 +18,10 @@ struct NcclApi {
 };
 
 // Layout of the shared exchange segment: a header line, then per rank two slots (used in turn, so that a rank may
-// publish round s + 1 while a slower host still reads round s): [flag line | up to kMaxAcc elements of 32 bytes].
+// publish round s + 1 while a slower host still reads round s).  A slot holds up to kMaxAcc elements as 16-byte
+// chunks {8 bytes of data, sequence number, pad} (see ReduceScratch::chunk_out).
 constexpr size_t kXchHeader = 256;
-constexpr size_t kXchSlot = 64 + kMaxAcc * 32;
+constexpr size_t kXchSlot = (size_t)kMaxAcc * 4 * 16;
 inline size_t xch_slot_offset(int rank, unsigned int seq) { return kXchHeader + ((size_t)rank * 2 + (seq & 1)) * kXchSlot; }
 inline size_t xch_bytes_for(int nranks) { return kXchHeader + (size_t)nranks * 2 * kXchSlot; }
 // Waits until every rank's slot of exchange `seq` is published, then copies the messages to out[rank][msg_bytes].

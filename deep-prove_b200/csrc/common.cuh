@@ -55,15 +55,14 @@ struct dpb_ctx {
     void* partials = nullptr;
     unsigned int* counter = nullptr;
     uint32_t max_blocks = 0;
-    // mapped pinned buffer the last block of a round writes its result to
+    // mapped pinned buffer the last block of a round writes its sums to, as sequence-numbered 16-byte chunks
+    // that the host polls (ReduceScratch::chunk_out)
     void* result_host = nullptr;
     void* result_dev = nullptr;
     size_t result_bytes = 0;
-    // completion flag of the current round (last word of the mapped result buffer); null when the
-    // round is followed by a collective on the stream
-    unsigned int* done_flag_dev = nullptr;            // what the next launch signals (or null)
-    unsigned int* flag_dev = nullptr;                 // device view of the flag word
-    volatile unsigned int* flag_host = nullptr;       // host view of the same word
+    // where the next launch publishes for the host: result_dev, this rank's slot of the shared exchange segment,
+    // or null when the round is followed by a collective on the stream (the sums then go to round_out)
+    void* chunk_out_dev = nullptr;
     unsigned int done_seq = 0;
     void* round_out = nullptr;  // where the current round's kernel publishes (result_dev or the exchange area)
     // small device staging area for points / challenges
@@ -134,7 +133,7 @@ inline ReduceScratch<F> reduce_scratch(const dpb_ctx* ctx) {
     ReduceScratch<F> rs;
     rs.partials = (typename F::E*)ctx->partials;
     rs.counter = ctx->counter;
-    rs.done_flag = ctx->done_flag_dev;
+    rs.chunk_out = ctx->chunk_out_dev;
     rs.done_value = ctx->done_value;
     return rs;
 }

@@ -265,11 +265,6 @@ constexpr uint32_t kTailMaxTables = 96;
 // transaction, so a reader that sees the sequence number it waits for has the
 // data that belongs to it, and neither side needs a system-wide fence (those
 // cost more than a microsecond each on the device).
-struct TailChunk {
-    uint64_t data;
-    uint32_t seq;
-    uint32_t pad;
-};
 struct TailBox {
     // host -> device: the challenge that ends round i carries sequence number i + 1; kTailAbort: leave now
     TailChunk chal[4];
@@ -290,24 +285,11 @@ __device__ __forceinline__ unsigned long long global_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-__device__ __forceinline__ void chunk_store(TailChunk* c, uint64_t data, uint32_t seq) {
-    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(c), "r"((uint32_t)data),
-                 "r"((uint32_t)(data >> 32)), "r"(seq), "r"(0u)
-                 : "memory");
-}
 __device__ __forceinline__ void chunk_load(const TailChunk* c, uint64_t& data, uint32_t& seq) {
     uint32_t lo, hi, unused = 0;
     asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(lo), "=r"(hi), "=r"(seq), "+r"(unused) : "l"(c) : "memory");
     data = (uint64_t)lo | ((uint64_t)hi << 32);
 }
-// an element as chunks with one sequence number
-template <class E>
-__device__ __forceinline__ void chunks_store(TailChunk* c, const E& v, uint32_t seq) {
-    const uint64_t* w = (const uint64_t*)&v;
-#pragma unroll
-    for (int i = 0; i < (int)(sizeof(E) / 8); i++) chunk_store(c + i, w[i], seq);
-}
-
 // The kernel can only trade messages with a host that runs while it does.  Under a profiler that serialises
 // launches, or with blocking launches, the launch call returns only when the kernel has ended: the hello never
 // comes, the kernel says so and leaves at once, and the host goes back to one launch per round.

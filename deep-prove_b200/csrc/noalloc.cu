@@ -58,7 +58,7 @@ static void launch_noalloc(cudaStream_t s, const void* const* tables, uint64_t n
     ReduceScratch<F> rs;
     rs.partials = (typename F::E*)scratch;
     rs.counter = (unsigned int*)((char*)scratch + kNoallocCounterOffset);
-    rs.done_flag = nullptr;
+    rs.chunk_out = nullptr;
     rs.done_value = 0;
     fused_product_eval0<F, K, BASE><<<grid, kThreads, 0, s>>>(ptrs, n_pairs, rs, (typename F::E*)out);
 }

@@ -57,19 +57,44 @@ template <class F>
 struct ReduceScratch {
     typename F::E* partials;  // [max_blocks][NACC]
     unsigned int* counter;    // zero between launches
-    // Optional completion flag (mapped host memory): after the result is
-    // written, done_value is stored there so the host can poll for it instead
-    // of synchronising the stream.  nullptr: no flag.
-    unsigned int* done_flag;
+    // Where the host polls for the result (mapped host memory), or nullptr.  The sums are then written there
+    // instead of to `out`, as 16-byte chunks {8 bytes of data, done_value, pad}: a chunk arrives as one
+    // transaction, so a host that sees done_value in every chunk of an element has the element, and the kernel
+    // needs no system-wide fence (each costs more than a microsecond).
+    void* chunk_out;
     unsigned int done_value;
 };
 
-template <class F>
-__device__ __forceinline__ void signal_done(const ReduceScratch<F>& rs) {
-    __threadfence_system();
-    if (rs.done_flag) {
-        *(volatile unsigned int*)rs.done_flag = rs.done_value;
-        __threadfence_system();
+// 16 bytes that travel as one transaction: 8 bytes of data and the sequence number that says which message
+struct TailChunk {
+    uint64_t data;
+    uint32_t seq;
+    uint32_t pad;
+};
+__device__ __forceinline__ void chunk_store(TailChunk* c, uint64_t data, uint32_t seq) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(c), "r"((uint32_t)data),
+                 "r"((uint32_t)(data >> 32)), "r"(seq), "r"(0u)
+                 : "memory");
+}
+// an element as chunks with one sequence number
+template <class E>
+__device__ __forceinline__ void chunks_store(TailChunk* c, const E& v, uint32_t seq) {
+    const uint64_t* w = (const uint64_t*)&v;
+#pragma unroll
+    for (int i = 0; i < (int)(sizeof(E) / 8); i++) chunk_store(c + i, w[i], seq);
+}
+
+// the NACC sums of a launch go to the host's chunk area, or to `out`
+template <class F, int NACC>
+__device__ __forceinline__ void emit_result(const typename F::E (&v)[NACC], const ReduceScratch<F>& rs,
+                                            typename F::E* out) {
+    typedef typename F::E E;
+    if (rs.chunk_out) {
+#pragma unroll
+        for (int i = 0; i < NACC; i++) chunks_store<E>((TailChunk*)rs.chunk_out + i * (sizeof(E) / 8), v[i], rs.done_value);
+    } else {
+#pragma unroll
+        for (int i = 0; i < NACC; i++) out[i] = v[i];
     }
 }
 
@@ -116,11 +141,7 @@ __device__ __forceinline__ void grid_sum_publish(typename F::E (&acc)[NACC], Red
     __shared__ bool is_last;
     block_sum<F, NACC>(acc);
     if (gridDim.x == 1) {
-        if (threadIdx.x == 0) {
-#pragma unroll
-            for (int i = 0; i < NACC; i++) out[i] = acc[i];
-            signal_done<F>(rs);
-        }
+        if (threadIdx.x == 0) emit_result<F, NACC>(acc, rs, out);
         return;
     }
     if (threadIdx.x == 0) {
@@ -150,10 +171,8 @@ __device__ __forceinline__ void grid_sum_publish(typename F::E (&acc)[NACC], Red
     }
     block_sum<F, NACC>(tot);
     if (threadIdx.x == 0) {
-#pragma unroll
-        for (int i = 0; i < NACC; i++) out[i] = tot[i];
+        emit_result<F, NACC>(tot, rs, out);
         *rs.counter = 0;
-        signal_done<F>(rs);
     }
 }
 
