@@ -5,6 +5,8 @@ sumcheck.  Prints one line per measurement with the algorithmic bytes it is
 divided by, so each figure can be read against the HBM peak.
 
     python deep-prove_b200/microbench.py [--field fr|gl] [--log2 22] [--reps 5]
+    python deep-prove_b200/microbench.py --latency      small sumchecks, one C call per proof, both fields,
+                                                        with the resident last-rounds kernel and with one launch per round
 """
 import argparse
 import importlib
@@ -42,14 +44,65 @@ def timed(ctx, fn, reps):
     return best
 
 
+def latency(dpb, prover, ctx):
+    """Time per proof of f*g*h over 2^n entries through dpb_prove_sumcheck (transcript in the library's C++)."""
+    import ctypes
+    rng = np.random.default_rng(1)
+    lib = dpb.lib
+    print("# product sumcheck f*g*h, one C call per proof (mean of 50), microseconds")
+    for field in ("gl", "fr"):
+        fr = field == "fr"
+        fam, base, w = (dpb.FR, dpb.FR, 4) if fr else (dpb.GL_EXT, dpb.GL_BASE, 2)
+        for resident in (True, False):
+            ctx.resident_rounds(resident)
+            for n in (4, 8, 12, 16, 20):
+                if fr:
+                    tabs = rng.integers(0, 2**64, size=(3, 1 << n, 4), dtype=np.uint64)
+                    tabs[:, :, 3] &= np.uint64((1 << 60) - 1)
+                else:
+                    tabs = rng.integers(0, 2**64 - 2**32 + 1, size=(3, 1 << n), dtype=np.uint64)
+                mles = [ctx.upload(tabs[j], base) for j in range(3)]
+                terms = dpb.make_terms([(dpb.one_bytes(fam), [0, 1, 2])], bytes)
+                hs = (ctypes.c_void_p * 3)(*[m.h for m in mles])
+                evals = np.zeros((n, 4, w), dtype=np.uint64)
+                point = np.zeros((n, w), dtype=np.uint64)
+                finals = np.zeros((3, w), dtype=np.uint64)
+                deg = ctypes.c_uint32()
+                tr = prover.Blake3Transcript(fam)
+                eb, pb, fb = dpb._buf(evals), dpb._buf(point), dpb._buf(finals)
+
+                def go():
+                    return lib.dpb_prove_sumcheck(ctx.h, n, hs, 3, terms, len(terms), tr.h, eb, n * 4, pb, fb,
+                                                  ctypes.byref(deg))
+                for _ in range(5):
+                    dpb.check(go())
+                ctx.sync()
+                t0 = time.perf_counter()
+                for _ in range(50):
+                    go()
+                ctx.sync()
+                dt = (time.perf_counter() - t0) / 50
+                mode = "resident last rounds" if resident else "one launch per round"
+                print(f"{field}  n={n:2d}  {mode:22s} {dt * 1e6:8.1f}")
+                tr.free()
+                for m in mles:
+                    m.free()
+    ctx.resident_rounds(True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--field", default="fr", choices=["fr", "gl"])
     ap.add_argument("--log2", type=int, default=22)
     ap.add_argument("--reps", type=int, default=5)
+    ap.add_argument("--latency", action="store_true")
     args = ap.parse_args()
     dpb, prover = load()
     ctx = dpb.Context(0)
+    if args.latency:
+        latency(dpb, prover, ctx)
+        ctx.close()
+        return
     rng = np.random.default_rng(0)
     n, N = args.log2, 1 << args.log2
     fr = args.field == "fr"
