@@ -90,6 +90,13 @@ SIGNATURES = {
     "dpb_logup_free": (None, [_vp]),
     "dpb_product_round_noalloc": (_int, [_vp, _int, _pp, _u32, _u64, _vp]),
     "dpb_einsum_fix_axes": (_int, [_vp, _int, _vp, _int, _vp, _vp, _pp, _vp, _u32, _pp, _pp, _u32, ctypes.POINTER(_u32)]),
+    "dpb_chunking_info_new": (_int, [_u32, _u32, _int, _u32, _u32, _vp]),
+    "dpb_lookup_counts_new": (_int, [_vp, _u32, _pp]),
+    "dpb_lookup_counts_to_host": (_int, [_vp, _vp, _u64]),
+    "dpb_lookup_counts_free": (None, [_vp]),
+    "dpb_lookup_multiplicities": (_int, [_vp, _vp, _int, _pp]),
+    "dpb_lookup_witness": (_int, [_vp, _int, _vp, ctypes.c_int64, ctypes.c_int64, _vp, _int, _vp, _u32, _vp, _int, _u32,
+                                  _vp, _vp, _vp, _vp, _pp, _pp, _u32, ctypes.POINTER(_u32), _pp, _u32, ctypes.POINTER(_u32)]),
     "dpb_comm_unique_id": (_int, [_vp]),
     "dpb_comm_init": (_int, [_vp, _vp, _int, _int]),
     "dpb_comm_rank": (_int, [_vp]),
@@ -301,6 +308,82 @@ class Context:
 
     def logup(self, kind, columns, constant, sep, mult=None):
         return Logup(self, kind, columns, constant, sep, mult)
+
+
+SIGN_POSITIVE, SIGN_NEGATIVE, SIGN_MIXED = 0, 1, 2
+
+
+class ChunkingInfo(ctypes.Structure):
+    """dpb_chunking_info, built by dpb_chunking_info_new (ChunkingInfo::new of the reference)."""
+    _fields_ = [("right_shift", _u32), ("value_chunk_bits", _u32), ("n_value_chunks", _u32), ("n_shifted_chunks", _u32),
+                ("n_zeroing_chunks", _u32), ("table_sign", ctypes.c_int32), ("offset", ctypes.c_int64),
+                ("value_chunk_offset", ctypes.c_int64), ("shifted_chunk_multiplier", ctypes.c_int64),
+                ("top_zeroing_chunk_offset", ctypes.c_int64)]
+
+    @classmethod
+    def new(cls, right_shift, table_bits, table_sign, max_bit_size, n_value_chunks=1):
+        ci = cls()
+        check(lib.dpb_chunking_info_new(right_shift, table_bits, table_sign, max_bit_size, n_value_chunks, ctypes.byref(ci)))
+        return ci
+
+
+class LookupCounts:
+    """dpb_lookup_counts: per-row lookup counters of one table, on the device."""
+
+    def __init__(self, ctx, table_bits):
+        self.ctx, self.bits = ctx, table_bits
+        self.h = ctypes.c_void_p()
+        check(lib.dpb_lookup_counts_new(ctx.h, table_bits, ctypes.byref(self.h)))
+
+    def to_host(self):
+        out = np.empty(1 << self.bits, dtype=np.uint64)
+        check(lib.dpb_lookup_counts_to_host(self.h, _buf(out), out.size))
+        return out
+
+    def multiplicities(self, family_dtype):
+        h = ctypes.c_void_p()
+        check(lib.dpb_lookup_multiplicities(self.ctx.h, self.h, family_dtype, ctypes.byref(h)))
+        return Mle(self.ctx, h)
+
+    def free(self):
+        if self.h:
+            lib.dpb_lookup_counts_free(self.h)
+            self.h = None
+
+
+def lookup_witness(ctx, family_dtype, info, fixed_point_multiplier, padding_value, tensor, value_table_outputs,
+                   num_value_columns, counts=(None, None, None, None), device_tensor=None, device_table=None):
+    """dpb_lookup_witness.  tensor: int64 ndarray (unpadded), or device_tensor = ctx.upload_tensor_i64(...);
+    value_table_outputs: int64 array over the value table's inputs, or None for a one-column table;
+    counts: LookupCounts for the shift-check, value, zero-check and signed zero-check tables (None: not counted);
+    device_table = ctx.upload_tensor_i64(value_table_outputs) uses an output column that is already on the device.
+    Returns (owner, input columns, output columns)."""
+    if device_tensor is not None:
+        mle, tshape = device_tensor
+        src, on_dev = ctypes.c_void_p(lib.dpb_mle_device_ptr(mle.h)), 1
+    else:
+        t = np.ascontiguousarray(tensor, dtype=np.int64)
+        tshape, src, on_dev = t.shape, _buf(t), 0
+    rank = len(tshape)
+    shape = (ctypes.c_uint64 * rank)(*tshape)
+    slices = 1
+    for d in tshape[:-2]:
+        slices *= d
+    cap = slices * 12
+    ins, outs = (ctypes.c_void_p * cap)(), (ctypes.c_void_p * cap)()
+    n_in, n_out, owner = ctypes.c_uint32(), ctypes.c_uint32(), ctypes.c_void_p()
+    tab = None if value_table_outputs is None else np.ascontiguousarray(value_table_outputs, dtype=np.int64)
+    if device_table is not None:
+        tab_ptr, tab_dev = ctypes.c_void_p(lib.dpb_mle_device_ptr(device_table[0].h)), 1
+    else:
+        tab_ptr, tab_dev = (_buf(tab) if tab is not None else None), 0
+    hs = [c.h if c is not None else None for c in counts]
+    check(lib.dpb_lookup_witness(ctx.h, family_dtype, ctypes.byref(info), fixed_point_multiplier, padding_value, src, on_dev,
+                                 shape, rank, tab_ptr, tab_dev, num_value_columns, hs[0], hs[1],
+                                 hs[2], hs[3], ctypes.byref(owner), ins, cap, ctypes.byref(n_in), outs, cap,
+                                 ctypes.byref(n_out)))
+    return (Mle(ctx, owner), [Mle(ctx, ctypes.c_void_p(ins[i])) for i in range(n_in.value)],
+            [Mle(ctx, ctypes.c_void_p(outs[i])) for i in range(n_out.value)])
 
 
 def product_round_noalloc(stream, dtype, table_ptrs, length, out_ptr):

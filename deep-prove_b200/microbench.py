@@ -5,6 +5,7 @@ sumcheck.  Prints one line per measurement with the algorithmic bytes it is
 divided by, so each figure can be read against the HBM peak.
 
     python deep-prove_b200/microbench.py [--field fr|gl] [--log2 22] [--reps 5]
+    python deep-prove_b200/microbench.py --lookup [--field ..] [--log2 ..]   only the lookup witness lines
     python deep-prove_b200/microbench.py --latency      small sumchecks, one C call per proof, both fields,
                                                         with the resident last-rounds kernel and with one launch per round
 """
@@ -90,12 +91,45 @@ def latency(dpb, prover, ctx):
     ctx.resident_rounds(True)
 
 
+def lookup(dpb, ctx, rng, args, fam, s0, report):
+    """Lookup witness generation: a GELU-like lookup over 2^n rescaled values on the device."""
+    n, N = args.log2, 1 << args.log2
+    # 12-bit two-column table, shift 16, 44-bit values: 1 + 1 + 1 input columns and 1 + 1 output columns per entry
+    lk_bits, lk_shift, lk_max = 12, 16, 44
+    ci = dpb.ChunkingInfo.new(lk_shift, lk_bits, dpb.SIGN_MIXED, lk_max)
+    rows = 1 << (n // 2)
+    # activations with a bell shape: about one rescaled value in a hundred falls outside the table's range
+    tens = np.rint(rng.standard_normal((rows, N // rows)) * ((1 << 27) / 181 / 2.6)).astype(np.int64)
+    dt = ctx.upload_tensor_i64(tens)
+    tab_out = np.clip(np.arange(-(1 << (lk_bits - 1)), 1 << (lk_bits - 1), dtype=np.int64), 0, None)
+    d_tab = ctx.upload_tensor_i64(tab_out)
+    cnt = [dpb.LookupCounts(ctx, b) for b in (16, lk_bits, 16, 16)]
+    n_cols = ci.n_shifted_chunks + 1 + ci.n_zeroing_chunks + 1 + ci.n_zeroing_chunks
+
+    def witness(counts):
+        owner, ins, outs = dpb.lookup_witness(ctx, fam, ci, 181, 0, None, tab_out, 2, counts, device_tensor=dt,
+                                              device_table=d_tab)
+        for h in ins + outs:
+            h.free()
+        return owner
+
+    t = timed(ctx, lambda: witness(cnt).free(), args.reps)
+    report(f"lookup witness 2^{n}, {n_cols} columns, counted", t, N * 8 + n_cols * N * s0)
+    t = timed(ctx, lambda: witness((None,) * 4).free(), args.reps)
+    report("  the same without the counters", t, N * 8 + n_cols * N * s0)
+    t = timed(ctx, lambda: cnt[0].multiplicities(fam).free(), args.reps)
+    report("  multiplicities of a 2^16-row table", t, (1 << 16) * (8 + s0))
+    for h in cnt:
+        h.free()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--field", default="fr", choices=["fr", "gl"])
     ap.add_argument("--log2", type=int, default=22)
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--latency", action="store_true")
+    ap.add_argument("--lookup", action="store_true", help="only the lookup witness lines")
     args = ap.parse_args()
     dpb, prover = load()
     ctx = dpb.Context(0)
@@ -123,6 +157,10 @@ def main():
     def report(name, seconds, nbytes):
         print(f"{name:44s} {seconds * 1e3:9.3f} ms  {nbytes / 1e9:8.3f} GB  {nbytes / seconds / 1e9:8.1f} GB/s")
 
+    if args.lookup:
+        lookup(dpb, ctx, rng, args, fam, s0, report)
+        ctx.close()
+        return
     print(f"# field={args.field} log2={n} (one B200, best of {args.reps}, wall clock around a stream sync)")
     pt = chal(n)
     t = timed(ctx, lambda: ctx.eq_table(fam, pt).free(), args.reps)
@@ -183,6 +221,8 @@ def main():
     report("  the same, tensor already on the device", t, x.size * 8)
     t = timed(ctx, lambda: [h.free() for h in ctx.einsum_fix_axes(fam, None, K2, [None, p12], device_tensor=dw)[1]], args.reps)
     report("  the same, tensor already on the device", t, wt.size * 8)
+
+    lookup(dpb, ctx, rng, args, fam, s0, report)
 
     # claim batching of the opening proof: many committed polynomials of mixed sizes, one claim each, all
     # zero-padded to the largest; bytes = sumcheck traffic of every polynomial and its eq table at its own size

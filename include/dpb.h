@@ -298,6 +298,74 @@ int dpb_logup_level(const dpb_logup* lu, uint32_t level, dpb_mle* out_views[4]);
 int dpb_logup_outputs(const dpb_logup* lu, void* out4);
 void dpb_logup_free(dpb_logup* lu);
 
+/* ---- lookup witness generation (zkml/src/lookup/operation, zkml/src/lookup/context.rs) ---- */
+#define DPB_SIGN_POSITIVE 0 /* TableSign::Positive: inputs >= 0 (shift check, zero check) */
+#define DPB_SIGN_NEGATIVE 1 /* TableSign::Negative: inputs <= 0 (exp) */
+#define DPB_SIGN_MIXED 2    /* TableSign::Mixed: both signs (ReLU, GeLU, SiLU, requantise, signed zero check) */
+
+/* The numbers ChunkingInfo holds (zkml/src/lookup/operation/decomposer.rs:12-42). */
+typedef struct dpb_chunking_info {
+    uint32_t right_shift;
+    uint32_t value_chunk_bits; /* the value table's bit size */
+    uint32_t n_value_chunks;
+    uint32_t n_shifted_chunks;
+    uint32_t n_zeroing_chunks;
+    int32_t table_sign;
+    int64_t offset;
+    int64_t value_chunk_offset;
+    int64_t shifted_chunk_multiplier;
+    int64_t top_zeroing_chunk_offset;
+} dpb_chunking_info;
+
+/* ChunkingInfo::new(right_shift, table, max_bit_size, number_of_value_chunks)
+ * (decomposer.rs:182-249); the table enters through its bit size and input sign.  Host only.
+ * DPB_EINVAL for right_shift = 0 (the reference's error), for more than 4 chunks of a kind and
+ * for a bit size outside 1..30. */
+int dpb_chunking_info_new(uint32_t right_shift, uint32_t table_bits, int table_sign, uint32_t max_bit_size,
+                          uint32_t n_value_chunks, dpb_chunking_info* out);
+
+/* How often each row of one table was looked up (the per-table element counts of
+ * LookupWitnessGen, zkml/src/lookup/context.rs:160-200), as 2^table_bits 64-bit counters on
+ * the device, row i being the table's input min_input + i (Table::min_input_value,
+ * zkml/src/lookup/table/mod.rs:135-142).  Counters start at zero and add up over every
+ * dpb_lookup_witness call they are handed to, which is how lookups of several layers into
+ * one table are merged (LookupWitnessGen::consume). */
+typedef struct dpb_lookup_counts dpb_lookup_counts;
+int dpb_lookup_counts_new(dpb_ctx* ctx, uint32_t table_bits, dpb_lookup_counts** out);
+int dpb_lookup_counts_to_host(const dpb_lookup_counts* counts, uint64_t* out, uint64_t len);
+void dpb_lookup_counts_free(dpb_lookup_counts* counts);
+/* The table's multiplicity polynomial (context.rs:313-371): row i holds its count as a field
+ * element.  The rows of the reference's tables are distinct (the input column is a range), so
+ * the division by a row's number of copies (context.rs:349-357) never applies. */
+int dpb_lookup_multiplicities(dpb_ctx* ctx, const dpb_lookup_counts* counts, int family_dtype, dpb_mle** out);
+
+/* LookupOp::generate_witness (zkml/src/lookup/operation/mod.rs:103-160) followed by
+ * LookupOpWitness::{input_mle_evals, output_mle_evals, get_counts} (mod.rs:193-282).
+ * `tensor`: the operation's UNPADDED input, signed 64-bit, row-major, on the host or (with
+ * tensor_on_device) on the device.  Every slice over the last two dimensions is padded to
+ * powers of two with padding_value, every entry becomes x * fixed_point_multiplier +
+ * 2^(right_shift-1) and is decomposed as `info` says.  `value_table_outputs`: the value
+ * table's output column over its inputs min..=max (2^value_chunk_bits entries), or NULL for a
+ * one-column table (requantise), whose output is its input; num_value_columns as
+ * Table::num_columns.
+ * Results, P = padded slice size, per slice in the reference's order:
+ *   input columns:  shifted chunks (least significant first), value chunks when the value
+ *                   table has two columns, zeroing chunks;
+ *   output columns: value chunk outputs, zeroing chunk outputs (zero check: 1 at 0 else 0;
+ *                   the top chunk of a Mixed operation: signum).
+ * Columns are tables of DPB_GL_BASE or DPB_FR elements (negative x -> p - |x|): borrowed
+ * views into *out_owner, as with dpb_einsum_fix_axes.  The four count handles may be NULL
+ * (that table's lookups are not counted); shift, zero and signed-zero counts have 2^16 rows.
+ * DPB_EINVAL with the reference's message when a top zeroing chunk falls outside the signed
+ * zero-check table (an input beyond max_bit_size). */
+int dpb_lookup_witness(dpb_ctx* ctx, int family_dtype, const dpb_chunking_info* info, int64_t fixed_point_multiplier,
+                       int64_t padding_value, const int64_t* tensor, int tensor_on_device, const uint64_t* shape,
+                       uint32_t rank, const int64_t* value_table_outputs, int outputs_on_device,
+                       uint32_t num_value_columns, dpb_lookup_counts* shift_counts, dpb_lookup_counts* value_counts,
+                       dpb_lookup_counts* zero_counts, dpb_lookup_counts* signed_zero_counts, dpb_mle** out_owner,
+                       dpb_mle** out_input_columns, uint32_t in_cap, uint32_t* n_in, dpb_mle** out_output_columns,
+                       uint32_t out_cap, uint32_t* n_out);
+
 #ifdef __cplusplus
 }
 #endif

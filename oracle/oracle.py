@@ -1101,3 +1101,206 @@ def mles_from_tensor(F, tensor_i64, kinds, points):
         vals = cur[start:start + contraction] + [F.zero] * pad
         out.append(scalars_to_array(F, vals))
     return out
+
+
+# ------------------------------------------------- lookup witness generation
+SHIFT_CHECK_TABLE_BIT_SIZE = 16  # zkml/src/lookup/table/mod.rs:20-23
+ZERO_CHECK_TABLE_BIT_SIZE = 16
+COLUMN_SEPARATOR = 1 << 32       # zkml/src/lookup/context.rs:205
+SIGN_POSITIVE, SIGN_NEGATIVE, SIGN_MIXED = 0, 1, 2
+
+
+def table_input_range(table_bits, sign):
+    """Table::min_input_value / max_input_value (zkml/src/lookup/table/mod.rs:126-142)."""
+    if sign == SIGN_POSITIVE:
+        return 0, (1 << table_bits) - 1
+    if sign == SIGN_MIXED:
+        return -(1 << (table_bits - 1)), (1 << (table_bits - 1)) - 1
+    return -(1 << table_bits) + 1, 0
+
+
+class ChunkingInfo:
+    """ChunkingInfo::new (zkml/src/lookup/operation/decomposer.rs:182-249): how a rescaled value is cut into
+    shifted chunks (the bits a right shift drops, 16 at a time), value chunks (looked up in the value table)
+    and zeroing chunks (the bits above, 16 at a time)."""
+
+    def __init__(self, right_shift, table_bits, sign, max_bit_size, n_value_chunks=1):
+        if right_shift <= 0:
+            raise ValueError("Right shift must be greater than zero to decompose value")
+        self.right_shift, self.value_chunk_size, self.sign = right_shift, table_bits, sign
+        self.n_value = n_value_chunks
+        self.n_shifted = -(-right_shift // SHIFT_CHECK_TABLE_BIT_SIZE)
+        self.n_zeroing = -(-max(max_bit_size - (right_shift + table_bits * n_value_chunks), 0) // ZERO_CHECK_TABLE_BIT_SIZE)
+        rem = right_shift % SHIFT_CHECK_TABLE_BIT_SIZE
+        self.shifted_chunk_multiplier = (1 << (SHIFT_CHECK_TABLE_BIT_SIZE - rem)) if rem else 1
+        if sign == SIGN_MIXED:
+            self.value_chunk_offset = 1 << (table_bits - 1)
+            combined = 1 << (table_bits * n_value_chunks - 1)
+            first = max(1 << (max_bit_size - 1), combined << right_shift)
+            self.offset = first + (1 if self.n_zeroing > 0 else 0) * (combined << right_shift)
+        else:
+            self.value_chunk_offset = self.offset = 0
+        if self.n_zeroing > 0 and sign == SIGN_MIXED:
+            self.top_zeroing_chunk_offset = self.offset >> (
+                right_shift + table_bits * n_value_chunks + (self.n_zeroing - 1) * ZERO_CHECK_TABLE_BIT_SIZE)
+        else:
+            self.top_zeroing_chunk_offset = 0
+        self.is_signed = sign == SIGN_MIXED
+
+    def rounding_constant(self):
+        return 1 << (self.right_shift - 1)
+
+    def decompose_input(self, values):
+        """decompose_input (decomposer.rs:252-312) on an int64 array; returns (shifted, value, zeroing), each a
+        list of int64 arrays."""
+        v = np.asarray(values, dtype=np.int64)
+        rem = v + self.offset if self.sign == SIGN_MIXED else (v.copy() if self.sign == SIGN_POSITIVE else -v)
+        shifted, value, zeroing = [], [], []
+        for i in range(self.n_shifted):
+            if i != self.n_shifted - 1 or self.right_shift % SHIFT_CHECK_TABLE_BIT_SIZE == 0:
+                shifted.append(rem & ((1 << SHIFT_CHECK_TABLE_BIT_SIZE) - 1))
+                rem = rem >> SHIFT_CHECK_TABLE_BIT_SIZE
+            else:
+                size = self.right_shift % SHIFT_CHECK_TABLE_BIT_SIZE
+                shifted.append((rem & ((1 << size) - 1)) * self.shifted_chunk_multiplier)
+                rem = rem >> size
+        for _ in range(self.n_value):
+            c = rem & ((1 << self.value_chunk_size) - 1)
+            value.append(c - self.value_chunk_offset if self.sign == SIGN_MIXED else (c if self.sign == SIGN_POSITIVE else -c))
+            rem = rem >> self.value_chunk_size
+        for i in range(self.n_zeroing):
+            c = rem & ((1 << ZERO_CHECK_TABLE_BIT_SIZE) - 1)
+            zeroing.append(c if (i != self.n_zeroing - 1 or not self.is_signed) else c - self.top_zeroing_chunk_offset)
+            rem = rem >> ZERO_CHECK_TABLE_BIT_SIZE
+        return shifted, value, zeroing
+
+    def table_output(self, value, zeroing, value_outputs):
+        """table_output (decomposer.rs:315-383): value chunks go through the value table (`value_outputs` = its
+        output column over min..=max inputs, or None for a one-column table, whose output is its input), zeroing
+        chunks through the zero-check table (1 at 0, else 0), the top chunk of a signed operation through the
+        signed zero-check table (signum; an input outside -2^15..2^15-1 is an error)."""
+        lo, hi = table_input_range(self.value_chunk_size, self.sign)
+        outs = []
+        for c in value:
+            if c.size and (c.min() < lo or c.max() > hi):
+                raise ValueError("value chunk outside its table")
+            outs.append(c.copy() if value_outputs is None else np.asarray(value_outputs, dtype=np.int64)[c - lo])
+        zouts = []
+        for i, c in enumerate(zeroing):
+            if self.is_signed and i == self.n_zeroing - 1:
+                if c.size and (c.min() < -(1 << 15) or c.max() > (1 << 15) - 1):
+                    raise ValueError("out of range for SignedZeroCheckTable")
+                zouts.append(np.sign(c).astype(np.int64))
+            else:
+                zouts.append((c == 0).astype(np.int64))
+        return outs, zouts
+
+    def combine_input_claims(self, F, shifted, value, zeroing):
+        """combine_input_claims (decomposer.rs:431-499) on field scalars: the rescaled input from its chunks."""
+        acc = F.zero
+        for j, c in enumerate(shifted):
+            w = F.from_int(1 << (j * SHIFT_CHECK_TABLE_BIT_SIZE))
+            if j != self.n_shifted - 1 or self.right_shift % SHIFT_CHECK_TABLE_BIT_SIZE == 0:
+                acc = F.add(acc, F.mul(c, w))
+            else:
+                acc = F.add(acc, F.mul(F.mul(c, F.inv(F.from_int(self.shifted_chunk_multiplier))), w))
+        comb = F.zero
+        for j, c in enumerate(value):
+            w = F.from_int(1 << (j * self.value_chunk_size))
+            rec = F.add(c, F.from_int(self.value_chunk_offset)) if self.sign == SIGN_MIXED else (c if self.sign == SIGN_POSITIVE else F.neg(c))
+            comb = F.add(comb, F.mul(rec, w))
+        acc = F.add(acc, F.mul(comb, F.from_int(1 << self.right_shift)))
+        for j, c in enumerate(zeroing):
+            w = F.from_int(1 << (self.value_chunk_size * self.n_value + self.right_shift + j * ZERO_CHECK_TABLE_BIT_SIZE))
+            if j != self.n_zeroing - 1 or not self.is_signed:
+                acc = F.add(acc, F.mul(c, w))
+            else:
+                acc = F.add(acc, F.mul(F.add(c, F.from_int(self.top_zeroing_chunk_offset)), w))
+        if self.sign == SIGN_MIXED:
+            return F.sub(acc, F.from_int(self.offset))
+        return acc if self.sign == SIGN_POSITIVE else F.neg(acc)
+
+
+class LookupOpWitness:
+    """LookupOp::generate_witness (zkml/src/lookup/operation/mod.rs:103-160) and LookupOpWitness
+    (mod.rs:163-283).  `inputs[c]` / `outputs[c]` hold, for the c-th slice over the last two dimensions,
+    (shifted, value, zeroing) and (value outputs, zeroing outputs)."""
+
+    def __init__(self, info, fixed_point_multiplier, padding_value, tensor, value_outputs, num_value_columns):
+        t = np.asarray(tensor, dtype=np.int64)
+        if t.ndim < 1:
+            raise ValueError("Input tensor must have rank at least 1")
+        rows, cols = (1, t.shape[0]) if t.ndim == 1 else t.shape[-2:]
+        prow, pcol = 1 << max(rows - 1, 0).bit_length(), 1 << max(cols - 1, 0).bit_length()
+        rc = info.rounding_constant()
+        self.info, self.num_value_columns = info, num_value_columns
+        self.inputs, self.outputs = [], []
+        for chunk in t.reshape(-1, rows, cols):
+            padded = np.full((prow, pcol), padding_value * fixed_point_multiplier + rc, dtype=np.int64)
+            padded[:rows, :cols] = chunk * fixed_point_multiplier + rc
+            dec = info.decompose_input(padded.reshape(-1))
+            self.inputs.append(dec)
+            self.outputs.append(info.table_output(dec[1], dec[2], value_outputs))
+
+    def input_columns(self):
+        """input_mle_evals (mod.rs:269-274) with ChunkedInput::to_evals (decomposer.rs:71-87), as int64 arrays."""
+        out = []
+        for shifted, value, zeroing in self.inputs:
+            out += list(shifted) + (list(value) if self.num_value_columns != 1 else []) + list(zeroing)
+        return out
+
+    def output_columns(self):
+        """output_mle_evals (mod.rs:276-282)."""
+        out = []
+        for value_out, zero_out in self.outputs:
+            out += list(value_out) + list(zero_out)
+        return out
+
+    def get_counts(self):
+        """get_counts (mod.rs:193-267): how often each (merged) table row is looked up, for the shift-check table,
+        the value table, the zero-check table and the signed zero-check table."""
+        def count(arrays):
+            d = {}
+            for a in arrays:
+                keys, n = np.unique(a, return_counts=True)
+                for k, c in zip(keys.tolist(), n.tolist()):
+                    d[k] = d.get(k, 0) + c
+            return d
+        sep = COLUMN_SEPARATOR
+        shift = count([s for dec in self.inputs for s in dec[0]])
+        if self.num_value_columns == 1:
+            value = count([v for o in self.outputs for v in o[0]])
+        else:
+            value = count([vi + sep * vo for dec, o in zip(self.inputs, self.outputs) for vi, vo in zip(dec[1], o[0])])
+        if not self.info.is_signed:
+            zero = count([zi + sep * zo for dec, o in zip(self.inputs, self.outputs) for zi, zo in zip(dec[2], o[1])])
+            signed = {}
+        else:
+            zero = count([zi + sep * zo for dec, o in zip(self.inputs, self.outputs) for zi, zo in zip(dec[2][:-1], o[1][:-1])])
+            signed = count([zi + sep * zo for dec, o in zip(self.inputs, self.outputs) for zi, zo in zip(dec[2][-1:], o[1][-1:])])
+        return [shift, value, zero, signed]
+
+
+def merged_table_column(table_bits, sign, outputs):
+    """Table::get_merged_table_columns (zkml/src/lookup/table/mod.rs:252-264): input + 2^32 * output per row
+    (the input alone for a one-column table, `outputs` None)."""
+    lo, hi = table_input_range(table_bits, sign)
+    ins = np.arange(lo, hi + 1, dtype=np.int64)
+    return ins if outputs is None else ins + COLUMN_SEPARATOR * np.asarray(outputs, dtype=np.int64)
+
+
+def table_multiplicities(F, merged_column, counts):
+    """The multiplicity polynomial of one table (zkml/src/lookup/context.rs:313-371): per row, the number of
+    lookups of that row divided by the number of times the row occurs in the table."""
+    col = [int(x) for x in merged_column]
+    occurs = {}
+    for x in col:
+        occurs[x] = occurs.get(x, 0) + 1
+    vals = []
+    for x in col:
+        if x in counts:
+            inv = F.inv(F.from_int(occurs[x])) if occurs[x] != 1 else F.one
+            vals.append(F.mul(F.from_int(counts[x]), inv))
+        else:
+            vals.append(F.zero)
+    return scalars_to_array(F, vals)

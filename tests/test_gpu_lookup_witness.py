@@ -1,0 +1,232 @@
+"""Lookup witness generation on the device (dpb_lookup_witness, dpb_lookup_counts_*, dpb_lookup_multiplicities)
+against the oracle's restatement of LookupOp::generate_witness and the multiplicity computation: every chunk column
+and every looked-up column bit for bit, the per-table counts, and that the columns and multiplicities satisfy the
+logup argument they are made for."""
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+from tests.helpers import family_dtype
+
+FIELDS = [orc.FrField, orc.GlField]
+
+
+def test_chunking_info_matches_the_oracle(dpb):
+    """Host-only: the numbers of ChunkingInfo::new over the reference's own test strategy and beyond."""
+    rng = np.random.default_rng(9500)
+    for _ in range(500):
+        right_shift = int(rng.integers(1, 40))
+        bits = int(rng.integers(2, 17))
+        n_value = int(rng.integers(1, 3))
+        sign = int(rng.integers(0, 3))
+        if right_shift + bits * n_value > 60:
+            continue
+        max_bit_size = int(rng.integers(max(right_shift + bits * n_value - 3, 1), 63))
+        want = orc.ChunkingInfo(right_shift, bits, sign, max_bit_size, n_value)
+        if want.n_zeroing > 4 or want.n_shifted > 4:
+            with pytest.raises(dpb.DpbError):
+                dpb.ChunkingInfo.new(right_shift, bits, sign, max_bit_size, n_value)
+            continue
+        got = dpb.ChunkingInfo.new(right_shift, bits, sign, max_bit_size, n_value)
+        assert (got.n_shifted_chunks, got.n_zeroing_chunks, got.offset, got.value_chunk_offset,
+                got.shifted_chunk_multiplier, got.top_zeroing_chunk_offset) == \
+               (want.n_shifted, want.n_zeroing, want.offset, want.value_chunk_offset,
+                want.shifted_chunk_multiplier, want.top_zeroing_chunk_offset)
+    with pytest.raises(dpb.DpbError) as e:
+        dpb.ChunkingInfo.new(0, 8, 2, 40)
+    assert "Right shift must be greater than zero" in str(e.value)
+
+
+def value_table(kind, bits):
+    """(sign, output column or None, columns): integer stand-ins for the reference's tables.  'exp' is a
+    decreasing table over non-positive inputs with the shape of TableType::Exp (tabletype.rs:90-99); its values
+    come from float32 arithmetic here and are data, not part of what is checked."""
+    if kind == "relu":
+        lo, hi = orc.table_input_range(bits, orc.SIGN_MIXED)
+        return orc.SIGN_MIXED, np.clip(np.arange(lo, hi + 1, dtype=np.int64), 0, hi), 2
+    if kind == "requantise":
+        return orc.SIGN_MIXED, None, 1
+    if kind == "exp":
+        lo, hi = orc.table_input_range(bits, orc.SIGN_NEGATIVE)
+        x = np.arange(lo, hi + 1, dtype=np.int64)
+        out = np.rint(np.exp(x.astype(np.float32) / np.float32(1 << (bits - 3))) * np.float32(1 << 20)).astype(np.int64)
+        out[0] = 0
+        return orc.SIGN_NEGATIVE, out, 2
+    if kind == "positive":
+        return orc.SIGN_POSITIVE, (np.arange(1 << bits, dtype=np.int64) * 2654435761) % 1000003 - 500000, 2
+    raise ValueError(kind)
+
+
+def draw_tensor(rng, shape, sign, max_bit_size, fpm):
+    big = (1 << (max_bit_size - 2)) // fpm
+    if sign == orc.SIGN_MIXED:
+        t = rng.integers(-big, big, size=shape, dtype=np.int64)
+    elif sign == orc.SIGN_POSITIVE:
+        t = rng.integers(0, big, size=shape, dtype=np.int64)
+    else:
+        t = -rng.integers(0, big, size=shape, dtype=np.int64)
+    flat = t.reshape(-1)
+    flat[::3] >>= int(rng.integers(10, 30))  # small magnitudes too
+    flat[::7] = 0
+    return t
+
+
+def check_case(dpb, ctx, F, kind, bits, right_shift, max_bit_size, shape, fpm, padding, rng, n_value=1, device_tensor=False):
+    sign, table_out, n_cols = value_table(kind, bits)
+    want_ci = orc.ChunkingInfo(right_shift, bits, sign, max_bit_size, n_value)
+    ci = dpb.ChunkingInfo.new(right_shift, bits, sign, max_bit_size, n_value)
+    t = draw_tensor(rng, shape, sign, max_bit_size, fpm)
+    want = orc.LookupOpWitness(want_ci, fpm, padding, t, table_out, n_cols)
+    counts = [dpb.LookupCounts(ctx, b) for b in (16, bits, 16, 16)]
+    fam = family_dtype(dpb, F)
+    dev = ctx.upload_tensor_i64(t) if device_tensor else None
+    owner, ins, outs = dpb.lookup_witness(ctx, fam, ci, fpm, padding, t, table_out, n_cols, counts, device_tensor=dev)
+    try:
+        want_in, want_out = want.input_columns(), want.output_columns()
+        assert len(ins) == len(want_in) and len(outs) == len(want_out)
+        for got, col in zip(ins + outs, want_in + want_out):
+            assert got.len == col.size
+            assert np.array_equal(got.to_host(), F.table_from_i64(col))
+        # counts: dense rows on the device, merged keys in the oracle
+        shift, value, zero, signed = want.get_counts()
+        lo, _ = orc.table_input_range(bits, sign)
+        got_counts = [c.to_host() for c in counts]
+        sep = orc.COLUMN_SEPARATOR
+
+        def dense(d, n, key_to_row):
+            a = np.zeros(n, dtype=np.uint64)
+            for k, c in d.items():
+                a[key_to_row(k)] += c
+            return a
+
+        def input_of(key):  # merged key = input + 2^32 * output, |input| < 2^31
+            return ((key + (1 << 31)) % sep) - (1 << 31)
+
+        assert np.array_equal(got_counts[0], dense(shift, 1 << 16, lambda k: k))
+        assert np.array_equal(got_counts[1], dense(value, 1 << bits, (lambda k: k - lo) if n_cols == 1 else (lambda k: input_of(k) - lo)))
+        assert np.array_equal(got_counts[2], dense(zero, 1 << 16, input_of))
+        assert np.array_equal(got_counts[3], dense(signed, 1 << 16, lambda k: input_of(k) + (1 << 15)))
+        # multiplicities against the reference's computation over the merged table column
+        m = counts[1].multiplicities(fam)
+        col = orc.merged_table_column(bits, sign, table_out)
+        assert F.table_to_ints(m.to_host()) == orc.array_to_scalars(F, orc.table_multiplicities(F, col, value))
+        m.free()
+    finally:
+        for v in ins + outs:
+            v.free()
+        owner.free()
+        for c in counts:
+            c.free()
+        if dev is not None:
+            dev[0].free()
+    return want
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("F", FIELDS)
+@pytest.mark.parametrize("kind,bits,right_shift,max_bit_size", [
+    ("relu", 10, 13, 44), ("relu", 8, 16, 40), ("relu", 12, 27, 55), ("relu", 9, 12, 21), ("requantise", 10, 32, 60),
+    ("exp", 11, 10, 40), ("exp", 8, 20, 28), ("positive", 9, 17, 50), ("positive", 16, 5, 21)])
+def test_witness_columns_counts_multiplicities(dpb, ctx, F, kind, bits, right_shift, max_bit_size):
+    rng = np.random.default_rng(9600 + bits + right_shift)
+    for shape in [(5,), (3, 7), (2, 3, 5), (2, 2, 4, 8), (1, 1), (33, 65)]:
+        check_case(dpb, ctx, F, kind, bits, right_shift, max_bit_size, shape, 37, 0 if kind != "exp" else -3, rng)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("F", FIELDS)
+def test_two_value_chunks_and_device_tensor(dpb, ctx, F):
+    rng = np.random.default_rng(9700)
+    check_case(dpb, ctx, F, "requantise", 8, 12, 44, (3, 5, 9), 3, 0, rng, n_value=2)
+    check_case(dpb, ctx, F, "relu", 10, 13, 44, (4, 17, 31), 5, 2, rng, device_tensor=True)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("F", FIELDS)
+def test_large_tensor_with_constant_chunks(dpb, ctx, F):
+    """2^20 entries whose zeroing chunks are all equal (the usual case: values far below the declared maximum),
+    which is the case the block-local counters are for."""
+    rng = np.random.default_rng(9800)
+    bits, right_shift, max_bit_size = 12, 16, 60
+    sign, table_out, n_cols = value_table("relu", bits)
+    t = rng.integers(-(1 << 20), 1 << 20, size=(1 << 10, 1 << 10), dtype=np.int64)
+    want_ci = orc.ChunkingInfo(right_shift, bits, sign, max_bit_size)
+    want = orc.LookupOpWitness(want_ci, 1 << 5, 0, t, table_out, n_cols)
+    ci = dpb.ChunkingInfo.new(right_shift, bits, sign, max_bit_size)
+    counts = [dpb.LookupCounts(ctx, b) for b in (16, bits, 16, 16)]
+    fam = family_dtype(dpb, F)
+    for rep in range(2):  # counters add up over calls
+        owner, ins, outs = dpb.lookup_witness(ctx, fam, ci, 1 << 5, 0, t, table_out, n_cols, counts)
+        for got, col in zip(ins + outs, want.input_columns() + want.output_columns()):
+            assert np.array_equal(got.to_host(), F.table_from_i64(col))
+        for v in ins + outs:
+            v.free()
+        owner.free()
+    shift, value, zero, signed = want.get_counts()
+    got = [c.to_host() for c in counts]
+    assert int(got[0].sum()) == 2 * sum(shift.values()) and int(got[1].sum()) == 2 * sum(value.values())
+    assert int(got[2].sum()) == 2 * sum(zero.values()) and int(got[3].sum()) == 2 * sum(signed.values())
+    for k, c in shift.items():
+        assert got[0][k] == 2 * c
+    assert len(zero) == 1 and len(signed) == 1  # one row each: every lookup of those tables hits it
+    for c in counts:
+        c.free()
+
+
+@pytest.mark.gpu
+def test_value_beyond_the_declared_size_is_an_error(dpb, ctx):
+    """The reference fails with the signed zero-check table's range error (tabletype.rs:137-143) when an input is
+    too large for max_bit_size; so does the call."""
+    bits, right_shift, max_bit_size = 10, 13, 44
+    sign, table_out, n_cols = value_table("relu", bits)
+    ci = dpb.ChunkingInfo.new(right_shift, bits, sign, max_bit_size)
+    t = np.array([[1, 2], [3, 3 << 53]], dtype=np.int64)
+    with pytest.raises(ValueError):
+        orc.LookupOpWitness(orc.ChunkingInfo(right_shift, bits, sign, max_bit_size), 1, 0, t, table_out, n_cols)
+    with pytest.raises(dpb.DpbError) as e:
+        dpb.lookup_witness(ctx, dpb.FR, ci, 1, 0, t, table_out, n_cols)
+    assert e.value.code == dpb.EINVAL and "SignedZeroCheckTable" in str(e.value)
+    with pytest.raises(dpb.DpbError):
+        dpb.lookup_witness(ctx, dpb.FR, ci, 1, 0, t, None, 2)  # two columns need the output column
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("F", FIELDS)
+def test_witness_feeds_the_logup_argument(dpb, ctx, F):
+    """The fractions of the lookups (value chunk in, value chunk out) and of the table with the device's
+    multiplicities cancel: sum_lookups 1/(c + in + s*out) = sum_rows m/(c + in + s*out), which is the global check
+    of zkml/src/iop/verifier.rs:543-584 on the trees' outputs."""
+    rng = np.random.default_rng(9900)
+    bits, right_shift, max_bit_size = 8, 12, 40
+    sign, table_out, n_cols = value_table("relu", bits)
+    ci = dpb.ChunkingInfo.new(right_shift, bits, sign, max_bit_size)
+    t = draw_tensor(rng, (2, 16, 32), sign, max_bit_size, 7)
+    counts = dpb.LookupCounts(ctx, bits)
+    fam = family_dtype(dpb, F)
+    owner, ins, outs = dpb.lookup_witness(ctx, fam, ci, 7, 0, t, table_out, n_cols, (None, counts, None, None))
+    n_in_per, n_out_per = len(ins) // 2, len(outs) // 2
+    cst, sep = F.random_scalar(rng), F.random_scalar(rng)
+    c_arr, s_arr = orc.scalars_to_array(F, [cst]), orc.scalars_to_array(F, [sep])
+    fracs = []
+    for s in range(2):
+        vin = ins[s * n_in_per + ci.n_shifted_chunks]
+        vout = outs[s * n_out_per]
+        lu = ctx.logup(0, [vin, vout], c_arr, s_arr)
+        fracs.append(orc.array_to_scalars(F, lu.outputs()))
+        lu.free()
+    lo, hi = orc.table_input_range(bits, sign)
+    tin = ctx.upload(F.table_from_i64(np.arange(lo, hi + 1, dtype=np.int64)), dpb.dtype_of_array(F.table_from_i64(np.arange(2)), F.name))
+    tout = ctx.upload(F.table_from_i64(table_out), tin.dtype)
+    mult = counts.multiplicities(fam)
+    lu = ctx.logup(1, [tin, tout], c_arr, s_arr, mult)
+    fracs.append(orc.array_to_scalars(F, lu.outputs()))
+    lu.free()
+    n, d = F.zero, F.one
+    for n0, n1, d0, d1 in fracs:
+        for nn, dd in ((n0, d0), (n1, d1)):
+            n, d = F.add(F.mul(n, dd), F.mul(d, nn)), F.mul(d, dd)
+    assert n == F.zero and d != F.zero
+    for m in ins + outs + [tin, tout, mult]:
+        m.free()
+    owner.free()
+    counts.free()
