@@ -116,7 +116,7 @@ static int witness_impl(dpb_ctx* ctx, const dpb_chunking_info& ci, int64_t fpm, 
     // few, large blocks: each adds its block-local counters to device memory once
     const uint64_t work = n_slices << p_bits;
     uint64_t blocks = (work + 511) / 512;
-    const uint64_t cap = (uint64_t)ctx->sm_count * (std::is_same<F, FrFam>::value ? 2 : 4);
+    const uint64_t cap = (uint64_t)ctx->sm_count * 2;
     if (blocks > cap) blocks = cap;
     if (e == cudaSuccess) {
         lookup_witness_kernel<F><<<(uint32_t)blocks, 512, smem, ctx->stream>>>(a, in_cols, out_cols);
