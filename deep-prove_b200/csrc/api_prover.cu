@@ -6,6 +6,7 @@
 #include "common.cuh"
 #include "host/claims.hpp"
 #include "host/logup.hpp"
+#include "host/lookup.hpp"
 #include "host/prover.hpp"
 #include "host/transcript.hpp"
 
@@ -242,6 +243,36 @@ int logup_impl(dpb_ctx* ctx, const dpb_logup_input* inputs, uint32_t n_inputs, T
     return DPB_OK;
 }
 
+// inputs/proving.rs:26-114
+template <class F, class T>
+int linking_impl(dpb_ctx* ctx, int variant, const dpb_chunking_info& ci, int64_t out_min, int64_t out_max,
+                 const uint64_t* shape, uint32_t rank, dpb_mle* const* mles, uint32_t n_mles, const void* claim_point,
+                 uint32_t n_claim, const void* logup_point, uint32_t n_logup, T& tr, void* out_evals, uint32_t cap,
+                 void* out_point, void* out_evaluations, void* out_chal, uint32_t chal_cap, uint32_t* n_chal,
+                 uint32_t* out_degree) {
+    typedef typename F::E E;
+    const std::vector<uint64_t> shp(shape, shape + rank);
+    const std::vector<dpb_mle*> tabs(mles, mles + n_mles);
+    for (auto* m : tabs)
+        if (!m || m->ctx != ctx) return fail(DPB_EINVAL, "null or foreign witness table");
+    auto res = zkml::lookup::prove_linking_sumcheck<F>(ctx, (zkml::lookup::LookupVariant)variant, ci, out_min, out_max, shp, tabs,
+                                                       elems<F>(claim_point, n_claim), elems<F>(logup_point, n_logup), tr);
+    const size_t n = res.sumcheck_point.size();
+    if (n * (res.degree + 1) > cap)
+        return fail(DPB_EINVAL, "round-evaluation buffer holds %u elements, %llu needed", cap, (unsigned long long)(n * (res.degree + 1)));
+    if (res.batching_challenges.size() > chal_cap)
+        return fail(DPB_EINVAL, "room for %u batching challenges, %llu needed", chal_cap, (unsigned long long)res.batching_challenges.size());
+    E* o = (E*)out_evals;
+    for (const auto& m : res.sumcheck_proof.proofs)
+        for (const auto& v : m.evaluations) *o++ = v;
+    memcpy(out_point, res.sumcheck_point.data(), n * sizeof(E));
+    memcpy(out_evaluations, res.evaluations.data(), res.evaluations.size() * sizeof(E));
+    memcpy(out_chal, res.batching_challenges.data(), res.batching_challenges.size() * sizeof(E));
+    *n_chal = (uint32_t)res.batching_challenges.size();
+    if (out_degree) *out_degree = res.degree;
+    return DPB_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -424,3 +455,32 @@ int dpb_logup_proof_serialize(const dpb_logup_proof* p, void* buf, size_t cap, s
 void dpb_logup_proof_free(dpb_logup_proof* p) { delete p; }
 
 }  // extern "C"
+
+extern "C" int dpb_lookup_linking_prove(dpb_ctx* ctx, int variant, const dpb_chunking_info* info, int64_t table_min_output,
+                                        int64_t table_max_output, const uint64_t* shape, uint32_t rank, dpb_mle* const* mles,
+                                        uint32_t n_mles, const void* last_claim_point, uint32_t n_claim_coords,
+                                        const void* logup_point, uint32_t n_logup_coords, dpb_transcript* t,
+                                        void* out_round_evals, uint32_t round_evals_cap, void* out_point,
+                                        void* out_evaluations, void* out_batching_challenges, uint32_t chal_cap,
+                                        uint32_t* out_n_challenges, uint32_t* out_degree) {
+    if (!ctx || !info || !shape || !mles || !last_claim_point || !logup_point || !t || !out_round_evals || !out_point ||
+        !out_evaluations || !out_batching_challenges || !out_n_challenges)
+        return fail(DPB_EINVAL, "null argument");
+    if (variant != DPB_VARIANT_STANDARD && variant != DPB_VARIANT_GLU) return fail(DPB_EINVAL, "unknown variant %d", variant);
+    if (rank < 1 || rank > 8) return fail(DPB_EINVAL, "rank %u outside 1..8", rank);
+    for (uint32_t a = 0; a < rank; a++)
+        if (shape[a] == 0) return fail(DPB_EINVAL, "axis %u is empty", a);
+    if (info->n_value_chunks < 1 || info->n_value_chunks > 4 || info->n_zeroing_chunks > 4 || info->value_chunk_bits < 1 ||
+        info->value_chunk_bits * info->n_value_chunks > 62 || info->table_sign < DPB_SIGN_POSITIVE || info->table_sign > DPB_SIGN_MIXED)
+        return fail(DPB_EINVAL, "chunking info out of range");
+    return guarded([&]() {
+        return t->gl ? linking_impl<GlFam>(ctx, variant, *info, table_min_output, table_max_output, shape, rank, mles, n_mles,
+                                           last_claim_point, n_claim_coords, logup_point, n_logup_coords, *t->g, out_round_evals,
+                                           round_evals_cap, out_point, out_evaluations, out_batching_challenges, chal_cap,
+                                           out_n_challenges, out_degree)
+                     : linking_impl<FrFam>(ctx, variant, *info, table_min_output, table_max_output, shape, rank, mles, n_mles,
+                                           last_claim_point, n_claim_coords, logup_point, n_logup_coords, *t->f, out_round_evals,
+                                           round_evals_cap, out_point, out_evaluations, out_batching_challenges, chal_cap,
+                                           out_n_challenges, out_degree);
+    });
+}

@@ -49,6 +49,9 @@ PROVER_SIGNATURES = {
     "dpb_same_poly_prove": (_int, [_vp, _vp, _vp, _u32, _u32, _vp, _vp, _vp, _vp]),
     "dpb_claims_batching_prove": (_int, [_vp, ctypes.POINTER(CommittedPolyStruct), _u32, _vp, _vp, _u32, _vp,
                                          ctypes.POINTER(_u32), _vp, _u32, _vp, _pp]),
+    "dpb_lookup_linking_prove": (_int, [_vp, _int, _vp, ctypes.c_int64, ctypes.c_int64, _vp, _u32, _pp, _u32, _vp, _u32, _vp,
+                                        _u32, _vp, _vp, _u32, _vp, _vp, _vp, _u32, ctypes.POINTER(_u32),
+                                        ctypes.POINTER(_u32)]),
     "dpb_logup_batch_prove": (_int, [_vp, ctypes.POINTER(LogupInputStruct), _u32, _vp, _pp]),
     "dpb_logup_proof_serialize": (_int, [_vp, _vp, _size_t, ctypes.POINTER(_size_t)]),
     "dpb_logup_proof_free": (None, [_vp]),
@@ -228,6 +231,39 @@ def same_poly_prove(ctx, transcript, poly, points):
     ev = np.zeros(w, dtype=np.uint64)
     check(lib.dpb_same_poly_prove(ctx.h, poly.h, _buf(p), m, n, transcript.h, _buf(evals), _buf(point), _buf(ev)))
     return evals, point, ev
+
+
+VARIANT_STANDARD, VARIANT_GLU = 0, 1
+
+
+def lookup_linking_prove(ctx, transcript, variant, info, table_min_output, table_max_output, shape, mles,
+                         last_claim_point, logup_point):
+    """LookupInputConfig::prove_linking_sumcheck (zkml/src/lookup/operation/inputs/proving.rs:26-114), Standard and
+    GLU variants.  info: ChunkingInfo; shape: the operation's unpadded input shape; mles: the witness tables in
+    the expression's order; points: [coords, w].  Returns dict(sumcheck [n, d+1, w], point [n, w],
+    evaluations [len(mles), w], challenges [1 + slices, w])."""
+    w = elem_words(chal_dtype(mles[0].dtype))
+    cp, lp = _scalars(last_claim_point).reshape(-1, w), _scalars(logup_point).reshape(-1, w)
+    n = lp.shape[0]
+    rank = len(shape)
+    shp = (ctypes.c_uint64 * rank)(*shape)
+    slices = 1
+    for d in shape[:-2]:
+        slices *= d
+    hs = (ctypes.c_void_p * len(mles))(*[m.h for m in mles])
+    cap = n * 9  # degree at most 8 factors per term
+    evals = np.zeros((cap, w), dtype=np.uint64)
+    point = np.zeros((n, w), dtype=np.uint64)
+    finals = np.zeros((len(mles), w), dtype=np.uint64)
+    chal = np.zeros((1 + slices, w), dtype=np.uint64)
+    n_chal, degree = ctypes.c_uint32(), ctypes.c_uint32()
+    check(lib.dpb_lookup_linking_prove(ctx.h, variant, ctypes.byref(info), table_min_output, table_max_output, shp, rank, hs,
+                                       len(mles), _buf(cp), cp.shape[0], _buf(lp), n, transcript.h, _buf(evals), cap,
+                                       _buf(point), _buf(finals), _buf(chal), 1 + slices, ctypes.byref(n_chal),
+                                       ctypes.byref(degree)))
+    d = degree.value
+    return dict(sumcheck=evals[: n * (d + 1)].reshape(n, d + 1, w), point=point, evaluations=finals,
+                challenges=chal[: n_chal.value])
 
 
 class CommittedPoly:

@@ -138,6 +138,35 @@ int dpb_logup_batch_prove(dpb_ctx* ctx, const dpb_logup_input* inputs, uint32_t 
 int dpb_logup_proof_serialize(const dpb_logup_proof* p, void* buf, size_t cap, size_t* len);
 void dpb_logup_proof_free(dpb_logup_proof* p);
 
+/* ---- lookup linking sumcheck ---------------------------------------------------- */
+#define DPB_VARIANT_STANDARD 0 /* LookupVariant::Standard */
+#define DPB_VARIANT_GLU 1      /* LookupVariant::GLU: one more witness table per slice, multiplied into the output */
+/* LookupInputConfig::prove_linking_sumcheck (zkml/src/lookup/operation/inputs/proving.rs:26-114)
+ * with LookupVariant::build_full_sumcheck_expression (zkml/src/lookup/operation/variant.rs:55-262)
+ * for the Standard and GLU variants, without a weight table: ties the looked-up outputs of an
+ * operation to the claim on its output tensor and to the logup point,
+ *   sum_x sum_c b_c * ( eq(x, p_out) * (clamping_c(x) + selector_c(x) * value_c(x)) [* glu_c(x)]
+ *                       + eq(x, p_logup) * sum_j s^j * witness_{c,j}(x) ).
+ * shape[rank]: the operation's UNPADDED input shape; a slice c is one index of the leading
+ * rank-2 dimensions, n = the variables of the last two padded dimensions.
+ * mles: per slice its value chunk outputs then its zeroing chunk outputs (the output columns
+ * of dpb_lookup_witness, in order), then for GLU one table per slice; every table 2^n entries.
+ * table_min_output / table_max_output: Table::min_output_value / max_output_value.
+ * last_claim_point: all the padded tensor's variables (Shape::split_point order: the last
+ * dimension first); logup_point: n coordinates.  The transcript gives the challenge "sum";
+ * the slices' coefficients b_c are the eq evaluations of the leading dimensions' coordinates
+ * (Shape::compute_eq_point_and_batching_challenges, zkml/src/shape.rs:565-610).
+ * Outputs: out_round_evals[n * (degree+1)] (capacity round_evals_cap elements),
+ * out_point[n], out_evaluations[n_mles] (the witness tables at the point),
+ * out_batching_challenges[1 + slices] (capacity chal_cap), *out_degree. */
+int dpb_lookup_linking_prove(dpb_ctx* ctx, int variant, const dpb_chunking_info* info, int64_t table_min_output,
+                             int64_t table_max_output, const uint64_t* shape, uint32_t rank, dpb_mle* const* mles,
+                             uint32_t n_mles, const void* last_claim_point, uint32_t n_claim_coords,
+                             const void* logup_point, uint32_t n_logup_coords, dpb_transcript* t, void* out_round_evals,
+                             uint32_t round_evals_cap, void* out_point, void* out_evaluations,
+                             void* out_batching_challenges, uint32_t chal_cap, uint32_t* out_n_challenges,
+                             uint32_t* out_degree);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1304,3 +1304,121 @@ def table_multiplicities(F, merged_column, counts):
         else:
             vals.append(F.zero)
     return scalars_to_array(F, vals)
+
+
+# ------------------------------------------------ lookup linking sumcheck
+VARIANT_STANDARD, VARIANT_GLU = 0, 1
+
+
+def lookup_output_expressions(F, info, chunk, out_min, out_max):
+    """LookupVariant::build_lookup_output_expressions (zkml/src/lookup/operation/variant.rs:73-226) with
+    ValueExpression::new (variant.rs:467-510): (value, prod_selector, clamping_expression, sum) over the witnesses
+    of one chunk, which are its value chunk outputs followed by its zeroing chunk outputs.  out_min / out_max are
+    the value table's extreme outputs (Table::min_output_value / max_output_value)."""
+    one, zero = F.one, F.zero
+    ONE, bits, nz = Expr.const(one), info.value_chunk_size, info.n_zeroing
+    offset = chunk * (info.n_value + nz)
+    if info.n_value == 1:
+        value = Expr.wit(offset)
+        total = Expr.wit(offset) * Expr.chal(0, 1, one, zero)
+        wo, so = offset + 1, 2
+    else:
+        value = Expr.const(F.neg(F.from_int(1 << (info.n_value * bits - 1))))
+        total = Expr.const(zero)
+        for idx in range(info.n_value):
+            c = Expr.wit(offset + idx)
+            value = value + Expr.const(F.from_int(1 << (bits * idx))) * (c + Expr.const(F.from_int(1 << (bits - 1))))
+            total = total + c * Expr.chal(0, idx + 1, one, zero)
+        wo, so = offset + info.n_value, 1 + info.n_value
+    if info.is_signed:
+        prod = ONE
+        for idx in range(max(nz - 1, 0)):
+            c = Expr.wit(wo + idx)
+            prod = prod * c
+            total = total + c * Expr.chal(0, so + idx, one, zero)
+        if info.n_value == 1:
+            cmin, cmax = F.from_int(out_min), F.from_int(out_max)
+        else:
+            full = info.n_value * bits
+            cmin, cmax = F.from_int(-(1 << (full - 1))), F.from_int((1 << (full - 1)) - 1)
+        if nz != 0:
+            last = Expr.wit(wo - 1 + nz)
+            lower = prod
+            one_minus_sq = ONE - last * last
+            prod = prod * one_minus_sq
+            total = total + last * Expr.chal(0, so - 1 + nz, one, zero)
+            half = Expr.const(F.inv(F.from_int(2)))
+            first = last * (last + ONE) * half + (one_minus_sq - lower * one_minus_sq)
+            second = last * (last - ONE) * half
+            clamp = first * Expr.const(cmax) + second * Expr.const(cmin)
+        else:
+            clamp = Expr.const(zero)
+    else:
+        prod = ONE
+        for idx in range(nz):
+            c = Expr.wit(wo + idx)
+            prod = prod * c
+            total = total + c * Expr.chal(0, so + idx, one, zero)
+        if nz != 0:
+            clamp = Expr.const(F.from_int(out_max if info.sign == SIGN_POSITIVE else out_min))
+        else:
+            clamp = ONE
+    return value, prod, clamp, total
+
+
+def lookup_linking_expression(F, variant, total_chunks, info, out_min, out_max):
+    """build_full_sumcheck_expression / sumcheck_expression_for_chunk (variant.rs:55-70, 229-262) for the Standard
+    and GLU variants: sum over chunks of
+        challenge[1 + c] * (eq_out * (clamping + prod_selector * value) [* glu_witness_c] + eq_lookup * sum).
+    Witness ids: the chunks' outputs, then (GLU) one witness per chunk, then eq_out, eq_lookup."""
+    per = info.n_value + info.n_zeroing
+    total_out = total_chunks * per
+    total_wit = total_out + (total_chunks if variant == VARIANT_GLU else 0)
+    eq_out, eq_lk = Expr.wit(total_wit), Expr.wit(total_wit + 1)
+    e = Expr.const(F.zero)
+    for c in range(total_chunks):
+        value, prod, clamp, total = lookup_output_expressions(F, info, c, out_min, out_max)
+        prod_expression = clamp + prod * value
+        out_part = eq_out * prod_expression
+        if variant == VARIANT_GLU:
+            out_part = out_part * Expr.wit(total_out + c)
+        e = e + Expr.chal(1 + c, 1, F.one, F.zero) * (out_part + eq_lk * total)
+    return e
+
+
+def eq_point_and_batching_challenges(F, shape, point):
+    """Shape::compute_eq_point_and_batching_challenges (zkml/src/shape.rs:565-610): the coordinates of the last
+    two (padded) dimensions, and one coefficient per slice over them: the product of eq evaluations of the leading
+    dimensions' coordinates, first dimension outermost, only the unpadded indices."""
+    dims = [1 << max(d - 1, 0).bit_length() for d in shape]
+    if len(point) != sum(d.bit_length() - 1 for d in dims):
+        raise ValueError("Point length %d does not match total variables" % len(point))
+    end, parts = len(point), []
+    for d in dims:  # split_point (shape.rs:475-496): the first dimension takes the last coordinates
+        start = end - (d.bit_length() - 1)
+        parts.append(point[start:end])
+        end = start
+    skip = max(len(shape) - 2, 0)
+    eq_point, chal = [], [F.one]
+    for i, (p, size) in enumerate(zip(parts, shape)):
+        if i < skip:
+            ev = array_to_scalars(F, eq_evals(F, p))[:size]
+            chal = [F.mul(c, e) for c in chal for e in ev]
+        else:
+            eq_point = list(p) + eq_point
+    return eq_point, chal
+
+
+def lookup_linking_prove(F, transcript, variant, info, out_min, out_max, shape, mles, last_claim_point, logup_point):
+    """LookupInputConfig::prove_linking_sumcheck (zkml/src/lookup/operation/inputs/proving.rs:26-114), Standard and
+    GLU variants, without a weight table.  `mles`: the witness tables in the expression's order.  Returns the
+    proof, the tables' evaluations at the sumcheck's point (eq tables left out), the point and the batching
+    challenges."""
+    eq_point, chal = eq_point_and_batching_challenges(F, shape, last_claim_point)
+    sum_challenge = transcript.append_and_sample(b"sum")
+    chal = [sum_challenge] + chal
+    eqs = [eq_evals(F, eq_point), eq_evals(F, logup_point)]
+    expr = lookup_linking_expression(F, variant, len(chal) - 1, info, out_min, out_max)
+    terms = expr_to_terms(F, expr, chal)
+    proof, point, finals = sumcheck_prove(F, len(eq_point), list(mles) + eqs, terms, transcript)
+    return dict(sumcheck=proof, evaluations=finals[:len(mles)], point=point, challenges=chal)

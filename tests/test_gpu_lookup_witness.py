@@ -230,3 +230,102 @@ def test_witness_feeds_the_logup_argument(dpb, ctx, F):
         m.free()
     owner.free()
     counts.free()
+
+
+# ------------------------------------------------------------- linking sumcheck
+@pytest.fixture(scope="module")
+def prover(dpb):
+    import importlib
+    return importlib.import_module("deep_prove_b200.prover")
+
+
+def flat(F, arr):
+    return orc.array_to_scalars(F, np.asarray(arr).reshape(-1, F.elem_words))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("F", FIELDS)
+@pytest.mark.parametrize("kind,bits,right_shift,max_bit_size,n_value,shape", [
+    ("relu", 8, 12, 40, 1, (3, 5, 6)),          # two zeroing chunks, rank 3
+    ("relu", 10, 13, 23, 1, (7, 9)),            # no zeroing chunk, rank 2
+    ("relu", 9, 11, 30, 1, (2, 3, 17, 33)),     # one zeroing chunk, rank 4, 2^11 entries per slice
+    ("requantise", 8, 12, 44, 2, (4, 16, 8)),   # two value chunks
+    ("exp", 8, 10, 34, 1, (2, 12, 12)),         # a table over non-positive inputs
+    ("positive", 9, 17, 26, 1, (11,)),          # no zeroing chunk, unsigned: the reference's 1 + value form
+])
+def test_linking_sumcheck_on_the_device_witness(dpb, ctx, prover, F, kind, bits, right_shift, max_bit_size, n_value, shape):
+    """The witness columns come from dpb_lookup_witness and go straight into dpb_lookup_linking_prove; proof,
+    point, evaluations, batching challenges and the transcript's state afterwards equal the oracle's."""
+    rng = np.random.default_rng(9970 + bits + right_shift)
+    sign, table_out, n_cols = value_table(kind, bits)
+    fpm = 3
+    t = draw_tensor(rng, shape, sign, max_bit_size, fpm)
+    o_ci = orc.ChunkingInfo(right_shift, bits, sign, max_bit_size, n_value)
+    want_w = orc.LookupOpWitness(o_ci, fpm, 0, t, table_out, n_cols)
+    if table_out is None:
+        out_min, out_max = orc.table_input_range(bits, sign)
+    else:
+        out_min, out_max = int(table_out[0]), int(table_out[-1])  # Table::min/max_output_value: the outputs at the ends
+    o_mles = [F.table_from_i64(c) for c in want_w.output_columns()]
+    dims = [1 << max(d - 1, 0).bit_length() for d in shape]
+    total = sum(d.bit_length() - 1 for d in dims)
+    n2d = sum(d.bit_length() - 1 for d in dims[-2:])
+    claim_point = [F.random_scalar(rng) for _ in range(total)]
+    logup_point = [F.random_scalar(rng) for _ in range(n2d)]
+    o_tr = orc.Transcript(F)
+    want = orc.lookup_linking_prove(F, o_tr, orc.VARIANT_STANDARD, o_ci, out_min, out_max, shape, o_mles, claim_point,
+                                    logup_point)
+
+    fam = family_dtype(dpb, F)
+    ci = dpb.ChunkingInfo.new(right_shift, bits, sign, max_bit_size, n_value)
+    owner, ins, outs = dpb.lookup_witness(ctx, fam, ci, fpm, 0, t, table_out, n_cols)
+    tr = prover.Blake3Transcript(fam)
+    got = prover.lookup_linking_prove(ctx, tr, prover.VARIANT_STANDARD, ci, out_min, out_max, shape, outs,
+                                      orc.scalars_to_array(F, claim_point), orc.scalars_to_array(F, logup_point))
+    assert flat(F, got["challenges"]) == want["challenges"]
+    assert flat(F, got["sumcheck"]) == [e for r in want["sumcheck"] for e in r]
+    assert flat(F, got["point"]) == want["point"]
+    assert flat(F, got["evaluations"]) == want["evaluations"]
+    assert tr.state() == (o_tr.state, o_tr.round)
+    for m in ins + outs:
+        m.free()
+    owner.free()
+    tr.free()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("F", FIELDS)
+def test_linking_sumcheck_glu_and_errors(dpb, ctx, prover, F):
+    rng = np.random.default_rng(9980)
+    bits, right_shift, max_bit_size, shape = 8, 12, 40, (2, 6, 8)
+    sign, table_out, n_cols = value_table("relu", bits)
+    t = draw_tensor(rng, shape, sign, max_bit_size, 3)
+    o_ci = orc.ChunkingInfo(right_shift, bits, sign, max_bit_size)
+    w = orc.LookupOpWitness(o_ci, 3, 0, t, table_out, n_cols)
+    glu = [F.random_table_fast(rng, 64) if F is orc.FrField else F.random_table(rng, 64) for _ in range(2)]
+    o_mles = [F.table_from_i64(c) for c in w.output_columns()] + glu
+    claim_point = [F.random_scalar(rng) for _ in range(7)]
+    logup_point = [F.random_scalar(rng) for _ in range(6)]
+    o_tr = orc.Transcript(F)
+    want = orc.lookup_linking_prove(F, o_tr, orc.VARIANT_GLU, o_ci, 0, 127, shape, o_mles, claim_point, logup_point)
+    fam = family_dtype(dpb, F)
+    ci = dpb.ChunkingInfo.new(right_shift, bits, sign, max_bit_size)
+    d_mles = [ctx.upload(np.ascontiguousarray(m), dpb.dtype_of_array(m, F.name)) for m in o_mles]
+    tr = prover.Blake3Transcript(fam)
+    got = prover.lookup_linking_prove(ctx, tr, prover.VARIANT_GLU, ci, 0, 127, shape, d_mles,
+                                      orc.scalars_to_array(F, claim_point), orc.scalars_to_array(F, logup_point))
+    assert flat(F, got["sumcheck"]) == [e for r in want["sumcheck"] for e in r]
+    assert flat(F, got["evaluations"]) == want["evaluations"]
+    assert tr.state() == (o_tr.state, o_tr.round)
+    # a table too few, a claim point of the wrong length (the reference's error text)
+    with pytest.raises(dpb.DpbError) as e:
+        prover.lookup_linking_prove(ctx, tr, prover.VARIANT_GLU, ci, 0, 127, shape, d_mles[:-1],
+                                    orc.scalars_to_array(F, claim_point), orc.scalars_to_array(F, logup_point))
+    assert "witness tables" in str(e.value)
+    with pytest.raises(dpb.DpbError) as e:
+        prover.lookup_linking_prove(ctx, tr, prover.VARIANT_GLU, ci, 0, 127, shape, d_mles,
+                                    orc.scalars_to_array(F, claim_point[:-1]), orc.scalars_to_array(F, logup_point))
+    assert "does not match total variables" in str(e.value)
+    for m in d_mles:
+        m.free()
+    tr.free()

@@ -224,3 +224,111 @@ def test_counts_and_multiplicities(F):
     col = np.array([0, 1, 2, 2], dtype=np.int64)
     m = orc.array_to_scalars(F, orc.table_multiplicities(F, col, {2: 6, 0: 1}))
     assert m == [F.one, F.zero, F.from_int(3), F.from_int(3)]
+
+
+# ------------------------------------------------------------- linking sumcheck
+def padded_2d(a, fill):
+    rows, cols = a.shape
+    prow, pcol = 1 << max(rows - 1, 0).bit_length(), 1 << max(cols - 1, 0).bit_length()
+    out = np.full((prow, pcol), fill, dtype=np.int64)
+    out[:rows, :cols] = a
+    return out
+
+
+def linking_case(F, kind, rng, shape=(3, 5, 6)):
+    """A lookup operation's witness over a rank-3 tensor with everything the linking sumcheck needs."""
+    bits, right_shift, max_bit_size, fpm, padding = 8, 12, 40, 5, 0
+    lo, hi = orc.table_input_range(bits, orc.SIGN_MIXED)
+    if kind == "relu":
+        table_out, n_cols, n_value = np.clip(np.arange(lo, hi + 1, dtype=np.int64), 0, hi), 2, 1
+        out_min, out_max = 0, hi
+    else:  # requantisation over two value chunks
+        table_out, n_cols, n_value = None, 1, 2
+        out_min, out_max = lo, hi
+    ci = orc.ChunkingInfo(right_shift, bits, orc.SIGN_MIXED, max_bit_size, n_value)
+    big = (1 << (max_bit_size - 2)) // fpm
+    t = rng.integers(-big, big, size=shape, dtype=np.int64)
+    t.reshape(-1)[::2] >>= 22
+    w = orc.LookupOpWitness(ci, fpm, padding, t, table_out, n_cols)
+    # what the operation computes (LookupOp::apply, zkml/src/lookup/operation/mod.rs:46-58)
+    full_bits = bits * n_value
+    cl_lo, cl_hi = (0, hi) if kind == "relu" else (-(1 << (full_bits - 1)), (1 << (full_bits - 1)) - 1)
+    op = lambda x: np.clip((x * fpm + ci.rounding_constant()) >> right_shift, cl_lo, cl_hi)
+    outputs = [padded_2d(op(s), int(op(np.int64(padding)))) for s in t]
+    return ci, w, outputs, out_min, out_max
+
+
+@pytest.mark.parametrize("F", [orc.FrField, orc.GlField])
+@pytest.mark.parametrize("kind", ["relu", "requantise2"])
+def test_linking_sumcheck_ties_outputs_and_lookups(F, kind):
+    """What prove_linking_sumcheck's claimed sum must be (debug_linking_sumcheck's check,
+    zkml/src/lookup/operation/inputs/proving.rs:74-84): sum_c b_c * (MLE of the operation's padded output slice c at
+    the claim's point + sum_j s^j * MLE of witness (c, j) at the logup point); and the sumcheck verifies, its final
+    evaluations being the witness tables at its point."""
+    rng = np.random.default_rng(9950)
+    shape = (3, 5, 6)
+    ci, w, outputs, out_min, out_max = linking_case(F, kind, rng, shape)
+    mles = [F.table_from_i64(c) for c in w.output_columns()]
+    n2d = 3 + 3
+    claim_point = [F.random_scalar(rng) for _ in range(n2d + 2)]
+    logup_point = [F.random_scalar(rng) for _ in range(n2d)]
+    res = orc.lookup_linking_prove(F, orc.Transcript(F), orc.VARIANT_STANDARD, ci, out_min, out_max, shape, mles,
+                                   claim_point, logup_point)
+    chal = res["challenges"]
+    s, betas = chal[0], chal[1:]
+    assert len(betas) == 3
+    # the slices' coefficients are the eq evaluations of the leading dimension's coordinates
+    lead = orc.array_to_scalars(F, orc.eq_evals(F, claim_point[n2d:]))
+    assert betas == lead[:3]
+    per = ci.n_value + ci.n_zeroing
+    want = F.zero
+    for c in range(3):
+        out_eval = orc.evaluate(F, F.table_from_i64(outputs[c].reshape(-1)), claim_point[:n2d])
+        lk = F.zero
+        if ci.n_value == 1:
+            powers = [1] + [2 + j for j in range(ci.n_zeroing)]
+        else:
+            powers = [1 + j for j in range(ci.n_value)] + [1 + ci.n_value + j for j in range(ci.n_zeroing)]
+        for j, p in enumerate(powers):
+            lk = F.add(lk, F.mul(F.pow(s, p), orc.evaluate(F, mles[c * per + j], logup_point)))
+        want = F.add(want, F.mul(betas[c], F.add(out_eval, lk)))
+    assert orc.extract_sum(F, res["sumcheck"]) == want
+    # the whole padded output tensor at the claim's point is the first half of that sum
+    full = np.zeros((4, 8, 8), dtype=np.int64)
+    full[:3] = np.stack(outputs)
+    total_out = orc.evaluate(F, F.table_from_i64(full.reshape(-1)), claim_point)
+    part = F.zero
+    for c in range(3):
+        part = F.add(part, F.mul(betas[c], orc.evaluate(F, F.table_from_i64(outputs[c].reshape(-1)), claim_point[:n2d])))
+    assert part == total_out
+    # verifier side: rounds check out, final evaluations are the tables at the point
+    degree = len(res["sumcheck"][0]) - 1
+    tr = orc.Transcript(F)
+    tr.append_and_sample(b"sum")
+    v_point, expected = orc.sumcheck_verify(F, want, res["sumcheck"], n2d, degree, tr)
+    point = res["point"]
+    assert v_point == point
+    assert [orc.evaluate(F, m, point) for m in mles] == res["evaluations"]
+    expr = orc.lookup_linking_expression(F, orc.VARIANT_STANDARD, 3, ci, out_min, out_max)
+    wit = res["evaluations"] + [orc.identity_eval(F, claim_point[:n2d], point), orc.identity_eval(F, logup_point, point)]
+    assert orc.eval_expr(F, expr, wit, chal) == expected
+
+
+def test_eq_point_and_batching_challenges_shapes():
+    F = orc.FrField
+    rng = np.random.default_rng(9960)
+    for shape in [(5,), (3, 7), (2, 3, 5), (2, 3, 4, 8)]:
+        total = sum(max(d - 1, 0).bit_length() for d in shape)
+        pt = [F.random_scalar(rng) for _ in range(total)]
+        eq_point, chal = orc.eq_point_and_batching_challenges(F, shape, pt)
+        n2d = sum(max(d - 1, 0).bit_length() for d in shape[-2:])
+        assert eq_point == pt[:n2d]
+        slices = int(np.prod(shape[:-2])) if len(shape) > 2 else 1
+        assert len(chal) == slices
+        # coefficient of slice (i0, i1, ..) = prod_k eq(bits of i_k, that dimension's coordinates)
+        if len(shape) == 4:
+            d1 = orc.array_to_scalars(F, orc.eq_evals(F, pt[n2d:n2d + 2]))     # second dimension (3 -> 2 vars)
+            d0 = orc.array_to_scalars(F, orc.eq_evals(F, pt[n2d + 2:]))        # first dimension (2 -> 1 var)
+            assert chal == [F.mul(d0[i], d1[j]) for i in range(2) for j in range(3)]
+    with pytest.raises(ValueError):
+        orc.eq_point_and_batching_challenges(F, (3, 7), [F.one])
