@@ -38,14 +38,23 @@ struct ProgGroup {
     uint16_t outer, term_begin, term_end, pad;
 };
 
-// coeff * product of idx[0..n_factors) (the group's outer table is not listed).  Terms of a group with the same
-// coefficient are stored next to each other; the coefficient multiplies their sum, at the term with run_last set.
+// One step of a group's inner sum (the group's outer table is not listed), which is evaluated as a Horner chain:
+//   kOpTerm  adds coeff * product of idx[0..n_factors).  Terms with the same coefficient are stored next to each
+//            other and the coefficient multiplies their sum, at the term with run_last set (neg: the coefficient
+//            is -1 and the sum is subtracted);
+//   kOpConst adds coeff;
+//   kOpFold  multiplies everything added so far by the tables idx[0..n_factors).
+// z*(z*(a - v) + b) + v is thus: const a, term -v, fold z, const b, fold z, term v: two products instead of the
+// four (and three coefficient products) of its monomials.
+constexpr uint8_t kOpTerm = 0, kOpConst = 1, kOpFold = 2;
 template <class F>
 struct ProgTerm {
     typename F::E coeff;
     uint16_t n_factors;
     uint8_t coeff_is_one;
     uint8_t run_last;
+    uint8_t op;
+    uint8_t neg;
     uint16_t idx[DPB_MAX_FACTORS];
 };
 
@@ -85,6 +94,14 @@ __device__ __noinline__ typename F::E eval_program(const Slots<F>& sl, const Pro
         for (uint32_t t = pg.term_begin; t < pg.term_end; t++) {
             const ProgTerm<F>& tm = terms[t];
             const uint32_t nf = tm.n_factors;
+            if (tm.op == kOpFold) {
+                for (uint32_t j = 0; j < nf; j++) inner = F::mul(inner, sl.get(2 * tm.idx[j]));
+                continue;
+            }
+            if (tm.op == kOpConst) {
+                inner = F::add(inner, tm.coeff);
+                continue;
+            }
             E prod;
             if (nf == 0) {
                 prod = F::one();
@@ -94,7 +111,8 @@ __device__ __noinline__ typename F::E eval_program(const Slots<F>& sl, const Pro
             }
             run = F::add(run, prod);
             if (tm.run_last) {
-                inner = F::add(inner, tm.coeff_is_one ? run : F::mul(run, tm.coeff));
+                if (tm.neg) inner = F::sub(inner, run);
+                else inner = F::add(inner, tm.coeff_is_one ? run : F::mul(run, tm.coeff));
                 run = F::zero();
             }
         }
@@ -373,6 +391,14 @@ __device__ __noinline__ typename F::E eval_program_at(const PairSlots<F>& sl, ui
         for (uint32_t t = pg.term_begin; t < pg.term_end; t++) {
             const ProgTerm<F>& tm = terms[t];
             const uint32_t nf = tm.n_factors;
+            if (tm.op == kOpFold) {
+                for (uint32_t j = 0; j < nf; j++) inner = F::mul(inner, sl.at(tm.idx[j], p, x));
+                continue;
+            }
+            if (tm.op == kOpConst) {
+                inner = F::add(inner, tm.coeff);
+                continue;
+            }
             E prod;
             if (nf == 0) {
                 prod = F::one();
@@ -382,7 +408,8 @@ __device__ __noinline__ typename F::E eval_program_at(const PairSlots<F>& sl, ui
             }
             run = F::add(run, prod);
             if (tm.run_last) {
-                inner = F::add(inner, tm.coeff_is_one ? run : F::mul(run, tm.coeff));
+                if (tm.neg) inner = F::sub(inner, run);
+                else inner = F::add(inner, tm.coeff_is_one ? run : F::mul(run, tm.coeff));
                 run = F::zero();
             }
         }
@@ -513,28 +540,130 @@ __global__ void __launch_bounds__(kTailThreads)
 
 // ---- host side ---------------------------------------------------------------
 
+// A monomial of a group's inner sum on the host: coeff * product of f.
+template <class F>
+struct ProgMono {
+    typename F::E coeff;
+    std::vector<uint16_t> f;
+};
+
+// Steps and field multiplications of a monomial list evaluated as it stands: constants summed into one
+// kOpConst, the rest sorted into runs of equal coefficients.
+template <class F>
+inline uint32_t emit_flat(std::vector<ProgMono<F>> monos, std::vector<ProgTerm<F>>& out) {
+    typedef typename F::E E;
+    uint32_t cost = 0;
+    E c = F::zero();
+    bool have_c = false;
+    std::vector<ProgMono<F>> rest;
+    for (auto& m : monos) {
+        if (m.f.empty()) {
+            c = F::add(c, m.coeff);
+            have_c = true;
+        } else {
+            rest.push_back(std::move(m));
+        }
+    }
+    if (have_c && !F::is_zero(c)) {
+        ProgTerm<F> pt;
+        memset(&pt, 0, sizeof pt);
+        pt.coeff = c;
+        pt.op = kOpConst;
+        out.push_back(pt);
+    }
+    // equal coefficients next to each other (stable: otherwise the caller's order), the last of each run marked
+    std::stable_sort(rest.begin(), rest.end(),
+                     [](const ProgMono<F>& x, const ProgMono<F>& y) { return memcmp(&x.coeff, &y.coeff, sizeof(E)) < 0; });
+    for (size_t t = 0; t < rest.size(); t++) {
+        ProgTerm<F> pt;
+        memset(&pt, 0, sizeof pt);
+        pt.coeff = rest[t].coeff;
+        pt.op = kOpTerm;
+        pt.coeff_is_one = F::is_one(pt.coeff) ? 1 : 0;
+        pt.neg = F::is_one(F::neg(pt.coeff)) ? 1 : 0;
+        pt.n_factors = (uint16_t)rest[t].f.size();
+        for (size_t j = 0; j < rest[t].f.size(); j++) pt.idx[j] = rest[t].f[j];
+        pt.run_last = (t + 1 == rest.size() || memcmp(&rest[t].coeff, &rest[t + 1].coeff, sizeof(E)) != 0) ? 1 : 0;
+        cost += pt.n_factors - 1;
+        if (pt.run_last && !pt.coeff_is_one && !pt.neg) cost++;
+        out.push_back(pt);
+    }
+    return cost;
+}
+
+// The cheaper of the list as it stands and  f * (monomials with f, f taken out once) + (monomials without f),
+// f the table in most monomials, the first part planned the same way.  Returns the multiplications per
+// evaluation; appends the steps to `out`.
+template <class F>
+inline uint32_t emit_chain(const std::vector<ProgMono<F>>& monos, uint32_t k, std::vector<ProgTerm<F>>& out) {
+    std::vector<ProgTerm<F>> flat;
+    const uint32_t flat_cost = emit_flat<F>(monos, flat);
+    std::vector<uint32_t> count(k, 0);
+    for (const auto& m : monos)
+        for (size_t j = 0; j < m.f.size(); j++) {
+            bool first = true;
+            for (size_t q = 0; q < j; q++)
+                if (m.f[q] == m.f[j]) first = false;
+            if (first) count[m.f[j]]++;
+        }
+    uint32_t best = 0, best_n = 0;
+    for (uint32_t j = 0; j < k; j++)
+        if (count[j] > best_n) {
+            best_n = count[j];
+            best = j;
+        }
+    if (best_n >= 2 && monos.size() <= 4096) {
+        std::vector<ProgMono<F>> with, without;
+        for (const auto& m : monos) {
+            size_t pos = m.f.size();
+            for (size_t j = 0; j < m.f.size(); j++)
+                if (m.f[j] == best) {
+                    pos = j;
+                    break;
+                }
+            if (pos == m.f.size()) {
+                without.push_back(m);
+            } else {
+                ProgMono<F> r = m;
+                r.f.erase(r.f.begin() + pos);
+                with.push_back(std::move(r));
+            }
+        }
+        std::vector<ProgTerm<F>> chain;
+        uint32_t cost = emit_chain<F>(with, k, chain);
+        ProgTerm<F> fold;
+        memset(&fold, 0, sizeof fold);
+        fold.op = kOpFold;
+        fold.n_factors = 1;
+        fold.idx[0] = (uint16_t)best;
+        chain.push_back(fold);
+        cost += 1 + emit_flat<F>(without, chain);
+        if (cost < flat_cost) {
+            out.insert(out.end(), chain.begin(), chain.end());
+            return cost;
+        }
+    }
+    out.insert(out.end(), flat.begin(), flat.end());
+    return flat_cost;
+}
+
 // Groups terms by a shared table, greedily: the table that occurs in most of the
 // still ungrouped terms (at least two) becomes the outer factor of those terms.
 // Tables listed in `prefer` (eq tables) become outer factors first, whatever their counts.
+// Inside a group the remaining monomials become a Horner chain where that saves multiplications (emit_chain).
 template <class F>
 inline void compile_program(const dpb_term* terms, uint32_t n_terms, uint32_t k, std::vector<ProgGroup>& groups,
                             std::vector<ProgTerm<F>>& prog, const std::vector<bool>& prefer = std::vector<bool>()) {
     typedef typename F::E E;
     std::vector<bool> used(n_terms, false);
     uint32_t left = n_terms;
-    auto emit = [&](uint32_t t, int drop) {  // drop: position of the factor that became the outer table, or -1
-        ProgTerm<F> pt;
-        memset(&pt, 0, sizeof pt);
-        memcpy(&pt.coeff, terms[t].coeff, sizeof(E));
-        pt.coeff_is_one = F::is_one(pt.coeff) ? 1 : 0;
-        uint16_t n = 0;
+    std::vector<ProgMono<F>> monos;
+    auto take = [&](uint32_t t, int drop) {  // drop: position of the factor that became the outer table, or -1
+        ProgMono<F> m;
+        memcpy(&m.coeff, terms[t].coeff, sizeof(E));
         for (uint32_t j = 0; j < terms[t].n_factors; j++)
-            if ((int)j != drop) pt.idx[n++] = terms[t].idx[j];
-        pt.n_factors = n;
-        if (n == 0 && drop >= 0) {
-            // the term was the outer table alone: its inner part is the coefficient itself
-        }
-        prog.push_back(pt);
+            if ((int)j != drop) m.f.push_back(terms[t].idx[j]);
+        monos.push_back(std::move(m));
     };
     while (left > 0) {
         std::vector<uint32_t> count(k, 0);
@@ -561,6 +690,7 @@ inline void compile_program(const dpb_term* terms, uint32_t n_terms, uint32_t k,
         ProgGroup g;
         g.pad = 0;
         g.term_begin = (uint16_t)prog.size();
+        monos.clear();
         if (best_n >= 2) {
             g.outer = (uint16_t)best;
             for (uint32_t t = 0; t < n_terms; t++) {
@@ -572,7 +702,7 @@ inline void compile_program(const dpb_term* terms, uint32_t n_terms, uint32_t k,
                         break;
                     }
                 if (pos < 0) continue;
-                emit(t, pos);
+                take(t, pos);
                 used[t] = true;
                 left--;
             }
@@ -580,17 +710,13 @@ inline void compile_program(const dpb_term* terms, uint32_t n_terms, uint32_t k,
             g.outer = kNoOuter;
             for (uint32_t t = 0; t < n_terms; t++) {
                 if (used[t]) continue;
-                emit(t, -1);
+                take(t, -1);
                 used[t] = true;
                 left--;
             }
         }
+        emit_chain<F>(monos, k, prog);
         g.term_end = (uint16_t)prog.size();
-        // equal coefficients next to each other (stable: otherwise the caller's order), the last of each run marked
-        std::stable_sort(prog.begin() + g.term_begin, prog.begin() + g.term_end,
-                         [](const ProgTerm<F>& a, const ProgTerm<F>& b) { return memcmp(&a.coeff, &b.coeff, sizeof(E)) < 0; });
-        for (uint32_t t = g.term_begin; t < g.term_end; t++)
-            prog[t].run_last = (t + 1 == g.term_end || memcmp(&prog[t].coeff, &prog[t + 1].coeff, sizeof(E)) != 0) ? 1 : 0;
         groups.push_back(g);
     }
 }

@@ -91,7 +91,7 @@ def latency(dpb, prover, ctx):
     ctx.resident_rounds(True)
 
 
-def lookup(dpb, ctx, rng, args, fam, s0, report):
+def lookup(dpb, prover, ctx, rng, args, fam, s0, s1, report):
     """Lookup witness generation: a GELU-like lookup over 2^n rescaled values on the device."""
     n, N = args.log2, 1 << args.log2
     # 12-bit two-column table, shift 16, 44-bit values: 1 + 1 + 1 input columns and 1 + 1 output columns per entry
@@ -121,6 +121,26 @@ def lookup(dpb, ctx, rng, args, fam, s0, report):
     report("  multiplicities of a 2^16-row table", t, (1 << 16) * (8 + s0))
     for h in cnt:
         h.free()
+
+    # the linking sumcheck over that witness (one slice of 2^n entries): value output, zeroing output and the two
+    # eq tables, degree 4; bytes = the sumcheck traffic of the four tables (eq tables counted as tables)
+    owner, ins, outs = dpb.lookup_witness(ctx, fam, ci, 181, 0, None, tab_out, 2, device_tensor=dt, device_table=d_tab)
+    w = 4 if fam == dpb.FR else 2
+    claim_pt = rng.integers(0, 2**62, size=(n, w), dtype=np.uint64)
+    logup_pt = rng.integers(0, 2**62, size=(n, w), dtype=np.uint64)
+
+    def linking():
+        tr = prover.Blake3Transcript(fam)
+        out = prover.lookup_linking_prove(ctx, tr, prover.VARIANT_STANDARD, ci, 0, (1 << (lk_bits - 1)) - 1, tens.shape, outs,
+                                          claim_pt, logup_pt)
+        tr.free()
+        return out
+
+    t = timed(ctx, linking, max(1, args.reps // 2))
+    report(f"lookup linking sumcheck 2^{n}, {len(outs)} + 2 tables", t, (len(outs) * (2 * s0 + 2 * s1) + 2 * 4 * s1) * N)
+    for h in ins + outs:
+        h.free()
+    owner.free()
 
 
 def main():
@@ -158,7 +178,7 @@ def main():
         print(f"{name:44s} {seconds * 1e3:9.3f} ms  {nbytes / 1e9:8.3f} GB  {nbytes / seconds / 1e9:8.1f} GB/s")
 
     if args.lookup:
-        lookup(dpb, ctx, rng, args, fam, s0, report)
+        lookup(dpb, prover, ctx, rng, args, fam, s0, s1, report)
         ctx.close()
         return
     print(f"# field={args.field} log2={n} (one B200, best of {args.reps}, wall clock around a stream sync)")
@@ -222,7 +242,7 @@ def main():
     t = timed(ctx, lambda: [h.free() for h in ctx.einsum_fix_axes(fam, None, K2, [None, p12], device_tensor=dw)[1]], args.reps)
     report("  the same, tensor already on the device", t, wt.size * 8)
 
-    lookup(dpb, ctx, rng, args, fam, s0, report)
+    lookup(dpb, prover, ctx, rng, args, fam, s0, s1, report)
 
     # claim batching of the opening proof: many committed polynomials of mixed sizes, one claim each, all
     # zero-padded to the largest; bytes = sumcheck traffic of every polynomial and its eq table at its own size
