@@ -466,7 +466,8 @@ extern "C" int dpb_lookup_linking_prove(dpb_ctx* ctx, int variant, const dpb_chu
     if (!ctx || !info || !shape || !mles || !last_claim_point || !logup_point || !t || !out_round_evals || !out_point ||
         !out_evaluations || !out_batching_challenges || !out_n_challenges)
         return fail(DPB_EINVAL, "null argument");
-    if (variant != DPB_VARIANT_STANDARD && variant != DPB_VARIANT_GLU) return fail(DPB_EINVAL, "unknown variant %d", variant);
+    if (variant != DPB_VARIANT_STANDARD && variant != DPB_VARIANT_GLU && variant != DPB_VARIANT_SOFTMAX)
+        return fail(DPB_EINVAL, "unknown variant %d", variant);
     if (rank < 1 || rank > 8) return fail(DPB_EINVAL, "rank %u outside 1..8", rank);
     for (uint32_t a = 0; a < rank; a++)
         if (shape[a] == 0) return fail(DPB_EINVAL, "axis %u is empty", a);

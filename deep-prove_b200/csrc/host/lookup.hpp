@@ -1,7 +1,7 @@
 // The lookup linking sumcheck on the GPU, following the reference's in-repo code step for step:
 //   LookupVariant::{build_full_sumcheck_expression, build_lookup_output_expressions,
-//   sumcheck_expression_for_chunk} (Standard and GLU variants), ValueExpression::new
-//                                        zkml/src/lookup/operation/variant.rs:55-262, 467-510
+//   sumcheck_expression_for_chunk} (Standard, GLU and Softmax variants), ValueExpression::new
+//                                        zkml/src/lookup/operation/variant.rs:55-287, 363-379, 467-510
 //   Shape::compute_eq_point_and_batching_challenges, split_point
 //                                        zkml/src/shape.rs:475-496, 565-610
 //   LookupVariant::build_eq_polys        zkml/src/lookup/operation/variant/proving.rs:225-253
@@ -17,7 +17,7 @@ using dp_crypto::check;
 using dp_crypto::Error;
 using dp_crypto::Expression;
 
-enum class LookupVariant { Standard = 0, GLU = 1 };
+enum class LookupVariant { Standard = 0, GLU = 1, Softmax = 2 };
 
 template <class F>
 typename F::E to_field(int64_t x) {
@@ -118,15 +118,17 @@ LookupExpressions<F> build_lookup_output_expressions(const dpb_chunking_info& ci
     return {value, prod, clamp, sum};
 }
 
-// variant.rs:55-70, 229-262
+// variant.rs:55-70, 229-287
 template <class F>
-Expression<F> build_full_sumcheck_expression(LookupVariant variant, size_t total_chunks, const dpb_chunking_info& ci,
-                                             int64_t out_min, int64_t out_max) {
+Expression<F> build_full_sumcheck_expression(LookupVariant variant, size_t total_chunks, size_t final_dim_size,
+                                             const dpb_chunking_info& ci, int64_t out_min, int64_t out_max) {
     typedef Expression<F> X;
     const size_t per = ci.n_value_chunks + ci.n_zeroing_chunks;
     const size_t total_out = total_chunks * per;
     const size_t total_wit = total_out + (variant == LookupVariant::GLU ? total_chunks : 0);
-    if (total_wit + 2 > 0xffff) throw Error(DPB_EINVAL, "too many witness tables for 16-bit ids");
+    if (total_wit + 3 > 0xffff) throw Error(DPB_EINVAL, "too many witness tables for 16-bit ids");
+    size_t final_dim_log = 0;
+    while ((1ull << final_dim_log) < final_dim_size) final_dim_log++;
     const X output_linking_eq = X::WitIn((uint16_t)total_wit), lookup_linking_eq = X::WitIn((uint16_t)(total_wit + 1));
     X acc = X::ZERO();
     for (size_t c = 0; c < total_chunks; c++) {
@@ -134,6 +136,12 @@ Expression<F> build_full_sumcheck_expression(LookupVariant variant, size_t total
         const X prod_expression = e.clamping_expression + e.prod_selector * e.value;
         X out_part = output_linking_eq * prod_expression;
         if (variant == LookupVariant::GLU) out_part = out_part * X::WitIn((uint16_t)(total_out + c));
+        if (variant == LookupVariant::Softmax) {
+            // the normalisation check rides on the same product expression through the third eq table
+            const X normalisation_eq = X::WitIn((uint16_t)(total_wit + 2));
+            const X sum_norm_challenge = X::Challenge((uint16_t)(1 + total_chunks), 1, F::from_u64(1ull << final_dim_log), F::zero());
+            out_part = out_part + sum_norm_challenge * (normalisation_eq * prod_expression);
+        }
         acc = acc + X::Challenge((uint16_t)(1 + c), 1, F::one(), F::zero()) * (out_part + lookup_linking_eq * e.sum);
     }
     return acc;
@@ -204,28 +212,37 @@ LookupSumcheckProof<F> prove_linking_sumcheck(dpb_ctx* ctx, LookupVariant varian
                                     std::to_string(output_eq_point.size()) + " variables");
     const E sum_challenge = transcript.append_and_sample("sum");
     batching.insert(batching.begin(), sum_challenge);
+    // squeeze_sumcheck_challenges (variant.rs:363-379)
+    if (variant == LookupVariant::Softmax) batching.push_back(transcript.append_and_sample("normalisation"));
 
-    // build_eq_polys: eq(output point), eq(logup point), both in one call
+    // build_eq_polys (variant/proving.rs:225-253): eq(output point), eq(logup point) and, for Softmax, eq of
+    // (1/2, .., 1/2, the logup point's coordinates above the last dimension's); all in one call
     const uint32_t n = (uint32_t)output_eq_point.size();
+    const uint32_t n_eq = variant == LookupVariant::Softmax ? 3 : 2;
     std::vector<E> pts(output_eq_point);
     pts.insert(pts.end(), logup_point.begin(), logup_point.end());
-    const uint32_t nv[2] = {n, n};
-    dpb_mle* eqs[2] = {nullptr, nullptr};
+    if (variant == LookupVariant::Softmax) {
+        size_t fdv = 0;
+        while ((1ull << fdv) < unpadded_input_shape.back()) fdv++;
+        const E half = F::inv(F::from_u64(2));
+        for (size_t j = 0; j < n; j++) pts.push_back(j < fdv ? half : logup_point[j]);
+    }
+    const uint32_t nv[3] = {n, n, n};
+    dpb_mle* eqs[3] = {nullptr, nullptr, nullptr};
     dpb_mle* eq_owner = nullptr;
-    check(dpb_eq_tables(ctx, F::kChalDtype, pts.data(), nv, 2, &eq_owner, eqs));
+    check(dpb_eq_tables(ctx, F::kChalDtype, pts.data(), nv, n_eq, &eq_owner, eqs));
     struct G {
         dpb_mle** v;
         dpb_mle*& owner;
         ~G() {
-            dpb_mle_free(v[0]);
-            dpb_mle_free(v[1]);
+            for (int i = 0; i < 3; i++) dpb_mle_free(v[i]);
             dpb_mle_free(owner);
         }
     } g{eqs, eq_owner};
     std::vector<dpb_mle*> all(mles);
-    all.push_back(eqs[0]);
-    all.push_back(eqs[1]);
-    const Expression<F> expression = build_full_sumcheck_expression<F>(variant, total_chunks, ci, out_min, out_max);
+    for (uint32_t i = 0; i < n_eq; i++) all.push_back(eqs[i]);
+    const Expression<F> expression =
+        build_full_sumcheck_expression<F>(variant, total_chunks, unpadded_input_shape.back(), ci, out_min, out_max);
     auto builder = dp_crypto::VirtualPolynomialsBuilder<F>::new_with_mles(1, n, all);
     auto vp = builder.to_virtual_polys({expression}, batching);
     auto res = dp_crypto::IOPProverState<F>::prove(ctx, vp, transcript);

@@ -233,7 +233,7 @@ def same_poly_prove(ctx, transcript, poly, points):
     return evals, point, ev
 
 
-VARIANT_STANDARD, VARIANT_GLU = 0, 1
+VARIANT_STANDARD, VARIANT_GLU, VARIANT_SOFTMAX = 0, 1, 2
 
 
 def lookup_linking_prove(ctx, transcript, variant, info, table_min_output, table_max_output, shape, mles,
@@ -255,11 +255,11 @@ def lookup_linking_prove(ctx, transcript, variant, info, table_min_output, table
     evals = np.zeros((cap, w), dtype=np.uint64)
     point = np.zeros((n, w), dtype=np.uint64)
     finals = np.zeros((len(mles), w), dtype=np.uint64)
-    chal = np.zeros((1 + slices, w), dtype=np.uint64)
+    chal = np.zeros((2 + slices, w), dtype=np.uint64)
     n_chal, degree = ctypes.c_uint32(), ctypes.c_uint32()
     check(lib.dpb_lookup_linking_prove(ctx.h, variant, ctypes.byref(info), table_min_output, table_max_output, shp, rank, hs,
                                        len(mles), _buf(cp), cp.shape[0], _buf(lp), n, transcript.h, _buf(evals), cap,
-                                       _buf(point), _buf(finals), _buf(chal), 1 + slices, ctypes.byref(n_chal),
+                                       _buf(point), _buf(finals), _buf(chal), 2 + slices, ctypes.byref(n_chal),
                                        ctypes.byref(degree)))
     d = degree.value
     return dict(sumcheck=evals[: n * (d + 1)].reshape(n, d + 1, w), point=point, evaluations=finals,

@@ -141,9 +141,12 @@ void dpb_logup_proof_free(dpb_logup_proof* p);
 /* ---- lookup linking sumcheck ---------------------------------------------------- */
 #define DPB_VARIANT_STANDARD 0 /* LookupVariant::Standard */
 #define DPB_VARIANT_GLU 1      /* LookupVariant::GLU: one more witness table per slice, multiplied into the output */
+#define DPB_VARIANT_SOFTMAX 2  /* LookupVariant::Softmax: one more challenge ("normalisation") and a third eq table,
+                                * over (1/2, .., 1/2, the logup point's coordinates above the last dimension's), that
+                                * sums the outputs along the last dimension */
 /* LookupInputConfig::prove_linking_sumcheck (zkml/src/lookup/operation/inputs/proving.rs:26-114)
  * with LookupVariant::build_full_sumcheck_expression (zkml/src/lookup/operation/variant.rs:55-262)
- * for the Standard and GLU variants, without a weight table: ties the looked-up outputs of an
+ * for the Standard, GLU and Softmax variants, without a weight table: ties the looked-up outputs of an
  * operation to the claim on its output tensor and to the logup point,
  *   sum_x sum_c b_c * ( eq(x, p_out) * (clamping_c(x) + selector_c(x) * value_c(x)) [* glu_c(x)]
  *                       + eq(x, p_logup) * sum_j s^j * witness_{c,j}(x) ).
@@ -158,7 +161,7 @@ void dpb_logup_proof_free(dpb_logup_proof* p);
  * (Shape::compute_eq_point_and_batching_challenges, zkml/src/shape.rs:565-610).
  * Outputs: out_round_evals[n * (degree+1)] (capacity round_evals_cap elements),
  * out_point[n], out_evaluations[n_mles] (the witness tables at the point),
- * out_batching_challenges[1 + slices] (capacity chal_cap), *out_degree. */
+ * out_batching_challenges[1 + slices (+ 1 for Softmax)] (capacity chal_cap), *out_degree. */
 int dpb_lookup_linking_prove(dpb_ctx* ctx, int variant, const dpb_chunking_info* info, int64_t table_min_output,
                              int64_t table_max_output, const uint64_t* shape, uint32_t rank, dpb_mle* const* mles,
                              uint32_t n_mles, const void* last_claim_point, uint32_t n_claim_coords,

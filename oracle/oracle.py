@@ -1307,7 +1307,7 @@ def table_multiplicities(F, merged_column, counts):
 
 
 # ------------------------------------------------ lookup linking sumcheck
-VARIANT_STANDARD, VARIANT_GLU = 0, 1
+VARIANT_STANDARD, VARIANT_GLU, VARIANT_SOFTMAX = 0, 1, 2
 
 
 def lookup_output_expressions(F, info, chunk, out_min, out_max):
@@ -1366,11 +1366,13 @@ def lookup_output_expressions(F, info, chunk, out_min, out_max):
     return value, prod, clamp, total
 
 
-def lookup_linking_expression(F, variant, total_chunks, info, out_min, out_max):
-    """build_full_sumcheck_expression / sumcheck_expression_for_chunk (variant.rs:55-70, 229-262) for the Standard
-    and GLU variants: sum over chunks of
-        challenge[1 + c] * (eq_out * (clamping + prod_selector * value) [* glu_witness_c] + eq_lookup * sum).
-    Witness ids: the chunks' outputs, then (GLU) one witness per chunk, then eq_out, eq_lookup."""
+def lookup_linking_expression(F, variant, total_chunks, info, out_min, out_max, final_dim_size=None):
+    """build_full_sumcheck_expression / sumcheck_expression_for_chunk (variant.rs:55-70, 229-287) for the Standard,
+    GLU and Softmax variants: sum over chunks of
+        challenge[1 + c] * (eq_out * P_c [* glu_witness_c] [+ 2^k challenge[1 + chunks] * eq_norm * P_c]
+                            + eq_lookup * sum),   P_c = clamping + prod_selector * value,
+    2^k the padded size of the last dimension.  Witness ids: the chunks' outputs, then (GLU) one witness per chunk,
+    then eq_out, eq_lookup, (Softmax) eq_norm."""
     per = info.n_value + info.n_zeroing
     total_out = total_chunks * per
     total_wit = total_out + (total_chunks if variant == VARIANT_GLU else 0)
@@ -1382,6 +1384,9 @@ def lookup_linking_expression(F, variant, total_chunks, info, out_min, out_max):
         out_part = eq_out * prod_expression
         if variant == VARIANT_GLU:
             out_part = out_part * Expr.wit(total_out + c)
+        if variant == VARIANT_SOFTMAX:
+            pow_two = F.from_int(1 << max(final_dim_size - 1, 0).bit_length())
+            out_part = out_part + Expr.chal(1 + total_chunks, 1, pow_two, F.zero) * (Expr.wit(total_wit + 2) * prod_expression)
         e = e + Expr.chal(1 + c, 1, F.one, F.zero) * (out_part + eq_lk * total)
     return e
 
@@ -1410,15 +1415,22 @@ def eq_point_and_batching_challenges(F, shape, point):
 
 
 def lookup_linking_prove(F, transcript, variant, info, out_min, out_max, shape, mles, last_claim_point, logup_point):
-    """LookupInputConfig::prove_linking_sumcheck (zkml/src/lookup/operation/inputs/proving.rs:26-114), Standard and
-    GLU variants, without a weight table.  `mles`: the witness tables in the expression's order.  Returns the
-    proof, the tables' evaluations at the sumcheck's point (eq tables left out), the point and the batching
-    challenges."""
+    """LookupInputConfig::prove_linking_sumcheck (zkml/src/lookup/operation/inputs/proving.rs:26-114), Standard,
+    GLU and Softmax variants, without a weight table.  `mles`: the witness tables in the expression's order.
+    Returns the proof, the tables' evaluations at the sumcheck's point (eq tables left out), the point and the
+    batching challenges.  Softmax squeezes one more challenge ("normalisation", variant.rs:363-379) and adds the
+    eq table of the point (1/2, .., 1/2, logup point's coordinates above the last dimension's)
+    (build_eq_polys, variant/proving.rs:225-253)."""
     eq_point, chal = eq_point_and_batching_challenges(F, shape, last_claim_point)
     sum_challenge = transcript.append_and_sample(b"sum")
-    chal = [sum_challenge] + chal
+    other = [transcript.append_and_sample(b"normalisation")] if variant == VARIANT_SOFTMAX else []
+    total_chunks = len(chal)
+    chal = [sum_challenge] + chal + other
     eqs = [eq_evals(F, eq_point), eq_evals(F, logup_point)]
-    expr = lookup_linking_expression(F, variant, len(chal) - 1, info, out_min, out_max)
+    if variant == VARIANT_SOFTMAX:
+        fdv = max(shape[-1] - 1, 0).bit_length()
+        eqs.append(eq_evals(F, [F.inv(F.from_int(2))] * fdv + list(logup_point[fdv:])))
+    expr = lookup_linking_expression(F, variant, total_chunks, info, out_min, out_max, shape[-1])
     terms = expr_to_terms(F, expr, chal)
     proof, point, finals = sumcheck_prove(F, len(eq_point), list(mles) + eqs, terms, transcript)
     return dict(sumcheck=proof, evaluations=finals[:len(mles)], point=point, challenges=chal)

@@ -253,7 +253,9 @@ def flat(F, arr):
     ("exp", 8, 10, 34, 1, (2, 12, 12)),         # a table over non-positive inputs
     ("positive", 9, 17, 26, 1, (11,)),          # no zeroing chunk, unsigned: the reference's 1 + value form
 ])
-def test_linking_sumcheck_on_the_device_witness(dpb, ctx, prover, F, kind, bits, right_shift, max_bit_size, n_value, shape):
+@pytest.mark.parametrize("variant", [0, 2])
+def test_linking_sumcheck_on_the_device_witness(dpb, ctx, prover, F, kind, bits, right_shift, max_bit_size, n_value, shape,
+                                                variant):
     """The witness columns come from dpb_lookup_witness and go straight into dpb_lookup_linking_prove; proof,
     point, evaluations, batching challenges and the transcript's state afterwards equal the oracle's."""
     rng = np.random.default_rng(9970 + bits + right_shift)
@@ -273,14 +275,13 @@ def test_linking_sumcheck_on_the_device_witness(dpb, ctx, prover, F, kind, bits,
     claim_point = [F.random_scalar(rng) for _ in range(total)]
     logup_point = [F.random_scalar(rng) for _ in range(n2d)]
     o_tr = orc.Transcript(F)
-    want = orc.lookup_linking_prove(F, o_tr, orc.VARIANT_STANDARD, o_ci, out_min, out_max, shape, o_mles, claim_point,
-                                    logup_point)
+    want = orc.lookup_linking_prove(F, o_tr, variant, o_ci, out_min, out_max, shape, o_mles, claim_point, logup_point)
 
     fam = family_dtype(dpb, F)
     ci = dpb.ChunkingInfo.new(right_shift, bits, sign, max_bit_size, n_value)
     owner, ins, outs = dpb.lookup_witness(ctx, fam, ci, fpm, 0, t, table_out, n_cols)
     tr = prover.Blake3Transcript(fam)
-    got = prover.lookup_linking_prove(ctx, tr, prover.VARIANT_STANDARD, ci, out_min, out_max, shape, outs,
+    got = prover.lookup_linking_prove(ctx, tr, variant, ci, out_min, out_max, shape, outs,
                                       orc.scalars_to_array(F, claim_point), orc.scalars_to_array(F, logup_point))
     assert flat(F, got["challenges"]) == want["challenges"]
     assert flat(F, got["sumcheck"]) == [e for r in want["sumcheck"] for e in r]

@@ -332,3 +332,40 @@ def test_eq_point_and_batching_challenges_shapes():
             assert chal == [F.mul(d0[i], d1[j]) for i in range(2) for j in range(3)]
     with pytest.raises(ValueError):
         orc.eq_point_and_batching_challenges(F, (3, 7), [F.one])
+
+
+@pytest.mark.parametrize("F", [orc.FrField, orc.GlField])
+def test_softmax_variant_adds_the_row_sums(F):
+    """LookupVariant::Softmax (variant.rs:264-287, build_eq_polys variant/proving.rs:238-251): on top of the
+    Standard sum, 2^k * nu * sum_x eq(x, (1/2,..,1/2, r_rows)) P_c(x), which is nu times the sum along the last
+    dimension of the operation's output, taken at the logup point's row coordinates."""
+    rng = np.random.default_rng(9990)
+    shape = (3, 5, 6)
+    ci, w, outputs, out_min, out_max = linking_case(F, "relu", rng, shape)
+    mles = [F.table_from_i64(c) for c in w.output_columns()]
+    n2d, col_vars = 6, 3
+    claim_point = [F.random_scalar(rng) for _ in range(n2d + 2)]
+    logup_point = [F.random_scalar(rng) for _ in range(n2d)]
+    std = orc.lookup_linking_prove(F, orc.Transcript(F), orc.VARIANT_STANDARD, ci, out_min, out_max, shape, mles,
+                                   claim_point, logup_point)
+    soft = orc.lookup_linking_prove(F, orc.Transcript(F), orc.VARIANT_SOFTMAX, ci, out_min, out_max, shape, mles,
+                                    claim_point, logup_point)
+    assert soft["challenges"][:-1] == std["challenges"] and len(soft["challenges"]) == 1 + 3 + 1
+    nu, betas = soft["challenges"][-1], soft["challenges"][1:4]
+    extra = F.zero
+    for c in range(3):
+        row_sums = outputs[c].sum(axis=1)                       # padded rows, summed along the last dimension
+        at_rows = orc.evaluate(F, F.table_from_i64(row_sums), logup_point[col_vars:])
+        extra = F.add(extra, F.mul(betas[c], at_rows))
+    want = F.add(orc.extract_sum(F, std["sumcheck"]), F.mul(nu, extra))
+    assert orc.extract_sum(F, soft["sumcheck"]) == want
+    tr = orc.Transcript(F)
+    tr.append_and_sample(b"sum")
+    tr.append_and_sample(b"normalisation")
+    degree = len(soft["sumcheck"][0]) - 1
+    point, expected = orc.sumcheck_verify(F, want, soft["sumcheck"], n2d, degree, tr)
+    half = F.inv(F.from_int(2))
+    expr = orc.lookup_linking_expression(F, orc.VARIANT_SOFTMAX, 3, ci, out_min, out_max, shape[-1])
+    wit = soft["evaluations"] + [orc.identity_eval(F, claim_point[:n2d], point), orc.identity_eval(F, logup_point, point),
+                                 orc.identity_eval(F, [half] * col_vars + logup_point[col_vars:], point)]
+    assert orc.eval_expr(F, expr, wit, soft["challenges"]) == expected
