@@ -6,6 +6,7 @@ divided by, so each figure can be read against the HBM peak.
 
     python deep-prove_b200/microbench.py [--field fr|gl] [--log2 22] [--reps 5]
     python deep-prove_b200/microbench.py --lookup [--field ..] [--log2 ..]   only the lookup witness lines
+    python deep-prove_b200/microbench.py --mlp          one dense + ReLU layer of the MLP configuration, per step
     python deep-prove_b200/microbench.py --latency      small sumchecks, one C call per proof, both fields,
                                                         with the resident last-rounds kernel and with one launch per round
 """
@@ -143,6 +144,103 @@ def lookup(dpb, prover, ctx, rng, args, fam, s0, s1, report):
     owner.free()
 
 
+def mlp_layer(dpb, prover, ctx):
+    """Time of every step of one dense + ReLU layer of the two-layer MLP configuration (input 1 x 1024 int8, weights
+    1024 x 1024 int8, ReLU through a 12-bit lookup), tensors resident on the device, transcript in the library."""
+    rng = np.random.default_rng(0)
+    print("# dense + ReLU layer of the MLP configuration, per step (best of 20), microseconds")
+    for field in ("fr", "gl"):
+        fam, base, w = (dpb.FR, dpb.FR, 4) if field == "fr" else (dpb.GL_EXT, dpb.GL_BASE, 2)
+        x = rng.integers(-128, 128, size=(1, 1024), dtype=np.int64)
+        wt = rng.integers(-128, 128, size=(1024, 1024), dtype=np.int64)
+        y = x @ wt + rng.integers(-(1 << 15), 1 << 15, size=1024, dtype=np.int64)
+        pt = rng.integers(0, 2**62, size=(10, w), dtype=np.uint64)
+        d_w, d_y = ctx.upload_tensor_i64(wt), ctx.upload_tensor_i64(y)
+        x_tab = ctx.upload_i64(x.reshape(-1), base)
+        K = (dpb.AXIS_CONTRACTED, dpb.AXIS_OUTER)
+        steps = []
+
+        def step(name, fn, keep=False):
+            out = fn()
+            ctx.sync()
+            best = 1e30
+            for _ in range(20):
+                t0 = time.perf_counter()
+                r = fn()
+                ctx.sync()
+                best = min(best, time.perf_counter() - t0)
+                if not keep:
+                    release(r)
+            steps.append((name, best))
+            return out
+
+        def release(r):
+            if isinstance(r, (list, tuple)):
+                for q in r:
+                    release(q)
+            elif hasattr(r, "free"):
+                r.free()
+
+        def fix_axes():
+            owner, views = ctx.einsum_fix_axes(fam, None, K, [None, pt], device_tensor=d_w)
+            return [views, owner]
+
+        (w_views, w_owner) = step("einsum fix_axes W[1024,1024]", fix_axes, keep=True)
+        terms = dpb.make_terms([(dpb.one_bytes(fam), [0, 1])], bytes)
+
+        def dense():
+            tr = prover.Blake3Transcript(fam)
+            st = prover.IOPProverState.prove(ctx, 10, [x_tab, w_views[0]], terms, tr)
+            tr.free()
+            return st
+
+        step("dense sumcheck, 2^10", dense)
+        ci = dpb.ChunkingInfo.new(13, 12, dpb.SIGN_MIXED, 28)
+        relu_in = np.arange(-2048, 2048, dtype=np.int64)
+        relu_out = np.clip(relu_in, 0, None)
+        d_tab = ctx.upload_tensor_i64(relu_out)
+        cnt = [dpb.LookupCounts(ctx, b) for b in (16, 12, 16, 16)]
+
+        def witness():
+            owner, ins, outs = dpb.lookup_witness(ctx, fam, ci, 1, 0, None, relu_out, 2, cnt, device_tensor=d_y,
+                                                  device_table=d_tab)
+            return [ins, outs, owner]
+
+        ins, outs, wit_owner = step("lookup witness, 2^10 entries, 5 columns", witness, keep=True)
+        mult = step("multiplicities, 3 tables", lambda: [cnt[0].multiplicities(fam), cnt[1].multiplicities(fam),
+                                                         cnt[3].multiplicities(fam)], keep=True)
+        up = lambda a: ctx.upload_i64(np.ascontiguousarray(a, dtype=np.int64), base)
+        sz_in = np.arange(-(1 << 15), 1 << 15, dtype=np.int64)
+        tabs = [up(np.arange(1 << 16)), up(sz_in), up(np.sign(sz_in)), up(relu_in), up(relu_out)]
+        ch = rng.integers(0, 2**62, size=(6, w), dtype=np.uint64)
+        t_inputs = [prover.LogUpInput.new_table([tabs[0]], mult[0], ch[0], ch[1]),
+                    prover.LogUpInput.new_table([tabs[1], tabs[2]], mult[2], ch[4], ch[5]),
+                    prover.LogUpInput.new_table([tabs[3], tabs[4]], mult[1], ch[2], ch[3])]
+        l_inputs = [prover.LogUpInput.new_lookup([ins[0]], ch[0], ch[1], 1),
+                    prover.LogUpInput.new_lookup([ins[1], outs[0]], ch[2], ch[3], 2),
+                    prover.LogUpInput.new_lookup([ins[2], outs[1]], ch[4], ch[5], 2)]
+
+        def logup(inputs):
+            tr = prover.Blake3Transcript(fam)
+            out = prover.new_batch_multiple_sizes_prove(ctx, inputs, tr)
+            tr.free()
+            return out
+
+        step("logup-GKR, tables 2^16 + 2^16 + 2^12", lambda: logup(t_inputs))
+        step("logup-GKR, 3 lookups of 2^10", lambda: logup(l_inputs))
+
+        def linking():
+            tr = prover.Blake3Transcript(fam)
+            out = prover.lookup_linking_prove(ctx, tr, prover.VARIANT_STANDARD, ci, 0, 2047, (1, 1024), outs, pt, pt)
+            tr.free()
+            return out
+
+        step("linking sumcheck, 2^10", linking)
+        for name, t in steps:
+            print(f"{field}  {name:44s} {t * 1e6:9.1f}")
+        print(f"{field}  {'layer total':44s} {sum(t for _, t in steps) * 1e6:9.1f}")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--field", default="fr", choices=["fr", "gl"])
@@ -150,11 +248,16 @@ def main():
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--latency", action="store_true")
     ap.add_argument("--lookup", action="store_true", help="only the lookup witness lines")
+    ap.add_argument("--mlp", action="store_true", help="the steps of one dense + ReLU layer of the MLP configuration")
     args = ap.parse_args()
     dpb, prover = load()
     ctx = dpb.Context(0)
     if args.latency:
         latency(dpb, prover, ctx)
+        ctx.close()
+        return
+    if args.mlp:
+        mlp_layer(dpb, prover, ctx)
         ctx.close()
         return
     rng = np.random.default_rng(0)
