@@ -26,7 +26,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 def golden_inputs(F, name):
     """Seeded inputs shared by the generator and the GPU parity tests."""
     seed = {"prod3": 101, "hadamard": 102, "logup_lookup": 103, "logup_table": 104, "fix": 105,
-            "mixed": 106, "claims": 107}[name]
+            "mixed": 106, "claims": 107, "lookup": 108}[name]
     rng = np.random.default_rng(seed)
     if name == "prod3":
         n = 6
@@ -55,6 +55,17 @@ def golden_inputs(F, name):
         return dict(n=n, tables=[F.random_table(rng, 1 << n), F.random_table(rng, 1 << n),
                                  F.random_table(rng, 1 << (n - 2)), F.random_table(rng, 1 << (n - 2))],
                     coeffs=[F.random_scalar(rng) for _ in range(3)])
+    if name == "lookup":
+        # a signed lookup operation (8-bit table of ReLU shape, shift 12, 40-bit values: two zeroing chunks) over a
+        # ragged rank-3 tensor, with the points of its linking sumcheck
+        bits, shape = 8, (2, 3, 5)
+        lo, hi = orc.table_input_range(bits, orc.SIGN_MIXED)
+        t = rng.integers(-(1 << 36), 1 << 36, size=shape, dtype=np.int64)
+        t.reshape(-1)[::2] >>= 20
+        return dict(bits=bits, right_shift=12, max_bit_size=40, fpm=3, padding=1, tensor=t,
+                    table_out=np.clip(np.arange(lo, hi + 1, dtype=np.int64), 0, hi), out_min=0, out_max=hi,
+                    claim_point=[F.random_scalar(rng) for _ in range(2 + 3 + 1)],
+                    logup_point=[F.random_scalar(rng) for _ in range(2 + 3)])
     if name == "claims":
         # committed polynomials (num_vars, chunks, claims): one unchunked with two claims, one in four chunks, one small
         polys = []
@@ -106,6 +117,22 @@ def generate(F):
     out["claims"] = dict(proof=orc.serialize_sumcheck_proof(F, pr["sumcheck"]).hex(), point=hx(pr["point"]),
                          evals=hx(pr["sumcheck_evals"]), rlc_challenges=hx(pr["rlc_challenges"]),
                          rlc=hx(orc.array_to_scalars(F, pr["rlc"])))
+
+    g = golden_inputs(F, "lookup")
+    ci = orc.ChunkingInfo(g["right_shift"], g["bits"], orc.SIGN_MIXED, g["max_bit_size"])
+    wit = orc.LookupOpWitness(ci, g["fpm"], g["padding"], g["tensor"], g["table_out"], 2)
+    cols = wit.input_columns() + wit.output_columns()
+    counts = wit.get_counts()
+    link = orc.lookup_linking_prove(F, orc.Transcript(F), orc.VARIANT_STANDARD, ci, g["out_min"], g["out_max"],
+                                    g["tensor"].shape, [F.table_from_i64(c) for c in wit.output_columns()],
+                                    g["claim_point"], g["logup_point"])
+    out["lookup"] = dict(
+        columns=[[int(v) for v in c] for c in cols],
+        counts=[sorted([int(k), int(v)] for k, v in d.items()) for d in counts],
+        multiplicities=hx(orc.array_to_scalars(F, orc.table_multiplicities(
+            F, orc.merged_table_column(g["bits"], orc.SIGN_MIXED, g["table_out"]), counts[1]))),
+        linking=dict(proof=orc.serialize_sumcheck_proof(F, link["sumcheck"]).hex(), point=hx(link["point"]),
+                     evaluations=hx(link["evaluations"]), challenges=hx(link["challenges"])))
 
     g = golden_inputs(F, "fix")
     out["eq"] = hx(orc.array_to_scalars(F, orc.eq_evals(F, g["point"][:4])))

@@ -330,3 +330,50 @@ def test_linking_sumcheck_glu_and_errors(dpb, ctx, prover, F):
     for m in d_mles:
         m.free()
     tr.free()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("F", FIELDS)
+def test_lookup_golden(dpb, ctx, prover, F):
+    """The committed fixture (tests/golden, made by make_golden.py from the oracle): witness columns, counts,
+    multiplicities and the linking proof of a seeded lookup operation."""
+    import json
+    import os
+    from tests.golden import make_golden
+    with open(os.path.join(os.path.dirname(__file__), "golden", f"oracle_{F.name}.json")) as f:
+        want = json.load(f)["lookup"]
+    g = make_golden.golden_inputs(F, "lookup")
+    fam = family_dtype(dpb, F)
+    ci = dpb.ChunkingInfo.new(g["right_shift"], g["bits"], orc.SIGN_MIXED, g["max_bit_size"])
+    counts = [dpb.LookupCounts(ctx, b) for b in (16, g["bits"], 16, 16)]
+    owner, ins, outs = dpb.lookup_witness(ctx, fam, ci, g["fpm"], g["padding"], g["tensor"], g["table_out"], 2, counts)
+    for got, col in zip(ins + outs, want["columns"]):
+        assert np.array_equal(got.to_host(), F.table_from_i64(np.array(col, dtype=np.int64)))
+    assert len(ins) + len(outs) == len(want["columns"])
+    lo, _ = orc.table_input_range(g["bits"], orc.SIGN_MIXED)
+    sep = orc.COLUMN_SEPARATOR
+    input_of = lambda key: ((key + (1 << 31)) % sep) - (1 << 31)
+    rows = [lambda k: k, lambda k: input_of(k) - lo, input_of, lambda k: input_of(k) + (1 << 15)]
+    for c, pairs, row in zip(counts, want["counts"], rows):
+        dense = np.zeros(1 << c.bits, dtype=np.uint64)
+        for key, n in pairs:
+            dense[row(key)] += n
+        assert np.array_equal(c.to_host(), dense)
+    m = counts[1].multiplicities(fam)
+    assert orc.serialize_scalars(F, F.table_to_ints(m.to_host())).hex() == want["multiplicities"]
+    tr = prover.Blake3Transcript(fam)
+    got = prover.lookup_linking_prove(ctx, tr, prover.VARIANT_STANDARD, ci, g["out_min"], g["out_max"], g["tensor"].shape,
+                                      outs, orc.scalars_to_array(F, g["claim_point"]),
+                                      orc.scalars_to_array(F, g["logup_point"]))
+    hx = lambda a: orc.serialize_scalars(F, flat(F, a)).hex()
+    assert hx(got["point"]) == want["linking"]["point"]
+    assert hx(got["evaluations"]) == want["linking"]["evaluations"]
+    assert hx(got["challenges"]) == want["linking"]["challenges"]
+    proof = [flat(F, r) for r in got["sumcheck"]]
+    assert orc.serialize_sumcheck_proof(F, proof).hex() == want["linking"]["proof"]
+    for h in ins + outs + [m]:
+        h.free()
+    owner.free()
+    tr.free()
+    for c in counts:
+        c.free()
