@@ -249,14 +249,18 @@ int linking_impl(dpb_ctx* ctx, int variant, const dpb_chunking_info& ci, int64_t
                  const uint64_t* shape, uint32_t rank, dpb_mle* const* mles, uint32_t n_mles, const void* claim_point,
                  uint32_t n_claim, const void* logup_point, uint32_t n_logup, T& tr, void* out_evals, uint32_t cap,
                  void* out_point, void* out_evaluations, void* out_chal, uint32_t chal_cap, uint32_t* n_chal,
-                 uint32_t* out_degree) {
+                 uint32_t* out_degree, dpb_mle* weight, void* out_weight_eval) {
     typedef typename F::E E;
     const std::vector<uint64_t> shp(shape, shape + rank);
     const std::vector<dpb_mle*> tabs(mles, mles + n_mles);
     for (auto* m : tabs)
         if (!m || m->ctx != ctx) return fail(DPB_EINVAL, "null or foreign witness table");
-    auto res = zkml::lookup::prove_linking_sumcheck<F>(ctx, (zkml::lookup::LookupVariant)variant, ci, out_min, out_max, shp, tabs,
-                                                       elems<F>(claim_point, n_claim), elems<F>(logup_point, n_logup), tr);
+    if (weight && weight->ctx != ctx) return fail(DPB_EINVAL, "foreign weight table");
+    const bool with_sum = variant == DPB_VARIANT_NORMALISATION_WITH_SUM;
+    const auto v = with_sum ? zkml::lookup::LookupVariant::Normalisation : (zkml::lookup::LookupVariant)variant;
+    auto res = zkml::lookup::prove_linking_sumcheck<F>(ctx, v, ci, out_min, out_max, shp, tabs, elems<F>(claim_point, n_claim),
+                                                       elems<F>(logup_point, n_logup), tr, with_sum, weight);
+    if (res.has_weight_eval && out_weight_eval) memcpy(out_weight_eval, &res.weight_eval, sizeof(E));
     const size_t n = res.sumcheck_point.size();
     if (n * (res.degree + 1) > cap)
         return fail(DPB_EINVAL, "round-evaluation buffer holds %u elements, %llu needed", cap, (unsigned long long)(n * (res.degree + 1)));
@@ -462,12 +466,14 @@ extern "C" int dpb_lookup_linking_prove(dpb_ctx* ctx, int variant, const dpb_chu
                                         const void* logup_point, uint32_t n_logup_coords, dpb_transcript* t,
                                         void* out_round_evals, uint32_t round_evals_cap, void* out_point,
                                         void* out_evaluations, void* out_batching_challenges, uint32_t chal_cap,
-                                        uint32_t* out_n_challenges, uint32_t* out_degree) {
+                                        uint32_t* out_n_challenges, uint32_t* out_degree, dpb_mle* weight,
+                                        void* out_weight_eval) {
     if (!ctx || !info || !shape || !mles || !last_claim_point || !logup_point || !t || !out_round_evals || !out_point ||
         !out_evaluations || !out_batching_challenges || !out_n_challenges)
         return fail(DPB_EINVAL, "null argument");
-    if (variant != DPB_VARIANT_STANDARD && variant != DPB_VARIANT_GLU && variant != DPB_VARIANT_SOFTMAX)
+    if (variant < DPB_VARIANT_STANDARD || variant > DPB_VARIANT_NORMALISATION_WITH_SUM)
         return fail(DPB_EINVAL, "unknown variant %d", variant);
+    if (weight && !out_weight_eval) return fail(DPB_EINVAL, "a weight table needs room for its evaluation");
     if (rank < 1 || rank > 8) return fail(DPB_EINVAL, "rank %u outside 1..8", rank);
     for (uint32_t a = 0; a < rank; a++)
         if (shape[a] == 0) return fail(DPB_EINVAL, "axis %u is empty", a);
@@ -478,10 +484,10 @@ extern "C" int dpb_lookup_linking_prove(dpb_ctx* ctx, int variant, const dpb_chu
         return t->gl ? linking_impl<GlFam>(ctx, variant, *info, table_min_output, table_max_output, shape, rank, mles, n_mles,
                                            last_claim_point, n_claim_coords, logup_point, n_logup_coords, *t->g, out_round_evals,
                                            round_evals_cap, out_point, out_evaluations, out_batching_challenges, chal_cap,
-                                           out_n_challenges, out_degree)
+                                           out_n_challenges, out_degree, weight, out_weight_eval)
                      : linking_impl<FrFam>(ctx, variant, *info, table_min_output, table_max_output, shape, rank, mles, n_mles,
                                            last_claim_point, n_claim_coords, logup_point, n_logup_coords, *t->f, out_round_evals,
                                            round_evals_cap, out_point, out_evaluations, out_batching_challenges, chal_cap,
-                                           out_n_challenges, out_degree);
+                                           out_n_challenges, out_degree, weight, out_weight_eval);
     });
 }

@@ -1,7 +1,7 @@
 // The lookup linking sumcheck on the GPU, following the reference's in-repo code step for step:
 //   LookupVariant::{build_full_sumcheck_expression, build_lookup_output_expressions,
-//   sumcheck_expression_for_chunk} (Standard, GLU and Softmax variants), ValueExpression::new
-//                                        zkml/src/lookup/operation/variant.rs:55-287, 363-379, 467-510
+//   sumcheck_expression_for_chunk} (all four variants), ValueExpression::new
+//                                        zkml/src/lookup/operation/variant.rs:55-346, 363-379, 467-510
 //   Shape::compute_eq_point_and_batching_challenges, split_point
 //                                        zkml/src/shape.rs:475-496, 565-610
 //   LookupVariant::build_eq_polys        zkml/src/lookup/operation/variant/proving.rs:225-253
@@ -17,7 +17,7 @@ using dp_crypto::check;
 using dp_crypto::Error;
 using dp_crypto::Expression;
 
-enum class LookupVariant { Standard = 0, GLU = 1, Softmax = 2 };
+enum class LookupVariant { Standard = 0, GLU = 1, Softmax = 2, Normalisation = 3 };
 
 template <class F>
 typename F::E to_field(int64_t x) {
@@ -46,7 +46,7 @@ std::vector<typename F::E> eq_evals(const typename F::E* point, size_t m) {
 
 template <class F>
 struct LookupExpressions {
-    Expression<F> value, prod_selector, clamping_expression, sum;
+    Expression<F> value, prod_selector, clamping_expression, sum, squared_clamping_expression;
 };
 
 // variant.rs:73-226 with ValueExpression::new (variant.rs:467-510).  The witnesses of chunk c are its value chunk
@@ -78,7 +78,7 @@ LookupExpressions<F> build_lookup_output_expressions(const dpb_chunking_info& ci
         witness_offset = (uint16_t)(offset + nv);
         sum_challenge_offset = 1 + nv;
     }
-    X prod = X::ONE(), clamp;
+    X prod = X::ONE(), clamp, sq_clamp = X::ZERO();  // a squared clamping part exists only in the signed case
     if (ci.table_sign == DPB_SIGN_MIXED) {
         for (size_t idx = 0; idx + 1 < nz; idx++) {
             const X chunk = X::WitIn((uint16_t)(witness_offset + idx));
@@ -104,6 +104,7 @@ LookupExpressions<F> build_lookup_output_expressions(const dpb_chunking_info& ci
             const X first = last * (last + X::ONE()) * half + (one_minus_sq - lower * one_minus_sq);
             const X second = last * (last - X::ONE()) * half;
             clamp = first * X::Constant(cmax) + second * X::Constant(cmin);
+            sq_clamp = first * X::Constant(cmax) * X::Constant(cmax) + second * X::Constant(cmin) * X::Constant(cmin);
         } else {
             clamp = X::ZERO();
         }
@@ -115,18 +116,21 @@ LookupExpressions<F> build_lookup_output_expressions(const dpb_chunking_info& ci
         }
         clamp = nz != 0 ? X::Constant(to_field<F>(ci.table_sign == DPB_SIGN_POSITIVE ? out_max : out_min)) : X::ONE();
     }
-    return {value, prod, clamp, sum};
+    return {value, prod, clamp, sum, sq_clamp};
 }
 
-// variant.rs:55-70, 229-287
+// variant.rs:55-70, 229-346.  Normalisation: two more witnesses per chunk (its input and its scaling), the squared
+// product expression under the third eq table, optionally the sum under it too and a weight table on the output.
 template <class F>
 Expression<F> build_full_sumcheck_expression(LookupVariant variant, size_t total_chunks, size_t final_dim_size,
-                                             const dpb_chunking_info& ci, int64_t out_min, int64_t out_max) {
+                                             const dpb_chunking_info& ci, int64_t out_min, int64_t out_max,
+                                             bool normalised_sum = false, bool has_weight = false) {
     typedef Expression<F> X;
     const size_t per = ci.n_value_chunks + ci.n_zeroing_chunks;
     const size_t total_out = total_chunks * per;
-    const size_t total_wit = total_out + (variant == LookupVariant::GLU ? total_chunks : 0);
-    if (total_wit + 3 > 0xffff) throw Error(DPB_EINVAL, "too many witness tables for 16-bit ids");
+    const size_t extra = variant == LookupVariant::GLU ? 1 : variant == LookupVariant::Normalisation ? 2 : 0;
+    const size_t total_wit = total_out + extra * total_chunks;
+    if (total_wit + 4 > 0xffff) throw Error(DPB_EINVAL, "too many witness tables for 16-bit ids");
     size_t final_dim_log = 0;
     while ((1ull << final_dim_log) < final_dim_size) final_dim_log++;
     const X output_linking_eq = X::WitIn((uint16_t)total_wit), lookup_linking_eq = X::WitIn((uint16_t)(total_wit + 1));
@@ -134,6 +138,20 @@ Expression<F> build_full_sumcheck_expression(LookupVariant variant, size_t total
     for (size_t c = 0; c < total_chunks; c++) {
         const LookupExpressions<F> e = build_lookup_output_expressions<F>(ci, c, out_min, out_max);
         const X prod_expression = e.clamping_expression + e.prod_selector * e.value;
+        if (variant == LookupVariant::Normalisation) {
+            const X normalisation_eq = X::WitIn((uint16_t)(total_wit + 2));
+            const typename F::E pow_two = F::from_u64(1ull << final_dim_log);
+            const X prod_squared = e.squared_clamping_expression + e.prod_selector * e.value * e.value;
+            const X lead = has_weight ? output_linking_eq * X::WitIn((uint16_t)(total_wit + 3)) : output_linking_eq;
+            X out_part = lead * prod_expression;
+            if (normalised_sum)
+                out_part = out_part + X::Challenge((uint16_t)(1 + total_chunks), 2, pow_two, F::zero()) * (normalisation_eq * prod_expression);
+            const X input = X::WitIn((uint16_t)(total_out + c)) * X::WitIn((uint16_t)(total_out + total_chunks + c));
+            acc = acc + X::Challenge((uint16_t)(1 + c), 1, F::one(), F::zero()) *
+                            (out_part + X::Challenge((uint16_t)(1 + total_chunks), 1, pow_two, F::zero()) * (normalisation_eq * prod_squared) +
+                             lookup_linking_eq * (e.sum + X::Challenge((uint16_t)(2 + total_chunks), 1, F::one(), F::zero()) * input));
+            continue;
+        }
         X out_part = output_linking_eq * prod_expression;
         if (variant == LookupVariant::GLU) out_part = out_part * X::WitIn((uint16_t)(total_out + c));
         if (variant == LookupVariant::Softmax) {
@@ -190,21 +208,27 @@ struct LookupSumcheckProof {
     std::vector<typename F::E> evaluations;     // the witness tables at the sumcheck's point, eq tables left out
     std::vector<typename F::E> sumcheck_point;
     std::vector<typename F::E> batching_challenges;
+    bool has_weight_eval = false;
+    typename F::E weight_eval;                  // the weight table at the point, when one was given
     uint32_t degree = 0;
 };
 
-// inputs/proving.rs:26-114 without a weight table.  `mles` in the expression's order.
+// inputs/proving.rs:26-114.  `mles` in the expression's order; weight_mle may be null.
 template <class F, class T>
 LookupSumcheckProof<F> prove_linking_sumcheck(dpb_ctx* ctx, LookupVariant variant, const dpb_chunking_info& ci, int64_t out_min,
                                               int64_t out_max, const std::vector<uint64_t>& unpadded_input_shape,
                                               const std::vector<dpb_mle*>& mles, const std::vector<typename F::E>& last_claim_point,
-                                              const std::vector<typename F::E>& logup_point, T& transcript) {
+                                              const std::vector<typename F::E>& logup_point, T& transcript,
+                                              bool normalised_sum = false, dpb_mle* weight_mle = nullptr) {
     typedef typename F::E E;
     auto pc = compute_eq_point_and_batching_challenges<F>(unpadded_input_shape, last_claim_point);
     const std::vector<E>& output_eq_point = pc.first;
     std::vector<E> batching = pc.second;
     const size_t total_chunks = batching.size();
-    const size_t want = total_chunks * (ci.n_value_chunks + ci.n_zeroing_chunks) + (variant == LookupVariant::GLU ? total_chunks : 0);
+    const size_t extra = variant == LookupVariant::GLU ? 1 : variant == LookupVariant::Normalisation ? 2 : 0;
+    const size_t want = total_chunks * (ci.n_value_chunks + ci.n_zeroing_chunks + extra);
+    if (weight_mle && variant != LookupVariant::Normalisation)
+        throw Error(DPB_EINVAL, "only the normalisation variant's expression has a weight table");
     if (mles.size() != want)
         throw Error(DPB_EINVAL, "the expression has " + std::to_string(want) + " witness tables, " + std::to_string(mles.size()) + " given");
     if (logup_point.size() != output_eq_point.size())
@@ -213,15 +237,17 @@ LookupSumcheckProof<F> prove_linking_sumcheck(dpb_ctx* ctx, LookupVariant varian
     const E sum_challenge = transcript.append_and_sample("sum");
     batching.insert(batching.begin(), sum_challenge);
     // squeeze_sumcheck_challenges (variant.rs:363-379)
-    if (variant == LookupVariant::Softmax) batching.push_back(transcript.append_and_sample("normalisation"));
+    const bool third_eq = variant == LookupVariant::Softmax || variant == LookupVariant::Normalisation;
+    if (third_eq) batching.push_back(transcript.append_and_sample("normalisation"));
+    if (variant == LookupVariant::Normalisation) batching.push_back(transcript.append_and_sample("input"));
 
     // build_eq_polys (variant/proving.rs:225-253): eq(output point), eq(logup point) and, for Softmax, eq of
     // (1/2, .., 1/2, the logup point's coordinates above the last dimension's); all in one call
     const uint32_t n = (uint32_t)output_eq_point.size();
-    const uint32_t n_eq = variant == LookupVariant::Softmax ? 3 : 2;
+    const uint32_t n_eq = third_eq ? 3 : 2;
     std::vector<E> pts(output_eq_point);
     pts.insert(pts.end(), logup_point.begin(), logup_point.end());
-    if (variant == LookupVariant::Softmax) {
+    if (third_eq) {
         size_t fdv = 0;
         while ((1ull << fdv) < unpadded_input_shape.back()) fdv++;
         const E half = F::inv(F::from_u64(2));
@@ -241,15 +267,20 @@ LookupSumcheckProof<F> prove_linking_sumcheck(dpb_ctx* ctx, LookupVariant varian
     } g{eqs, eq_owner};
     std::vector<dpb_mle*> all(mles);
     for (uint32_t i = 0; i < n_eq; i++) all.push_back(eqs[i]);
-    const Expression<F> expression =
-        build_full_sumcheck_expression<F>(variant, total_chunks, unpadded_input_shape.back(), ci, out_min, out_max);
+    if (weight_mle) all.push_back(weight_mle);  // after the eq tables (inputs/proving.rs:66-68)
+    const Expression<F> expression = build_full_sumcheck_expression<F>(variant, total_chunks, unpadded_input_shape.back(), ci,
+                                                                       out_min, out_max, normalised_sum, weight_mle != nullptr);
     auto builder = dp_crypto::VirtualPolynomialsBuilder<F>::new_with_mles(1, n, all);
     auto vp = builder.to_virtual_polys({expression}, batching);
     auto res = dp_crypto::IOPProverState<F>::prove(ctx, vp, transcript);
     LookupSumcheckProof<F> out;
     out.sumcheck_proof = res.first;
     out.evaluations = res.second.get_mle_flatten_final_evaluations();
-    out.evaluations.resize(mles.size());  // drop the eq tables' evaluations
+    if (weight_mle) {
+        out.has_weight_eval = true;
+        out.weight_eval = out.evaluations.back();
+    }
+    out.evaluations.resize(mles.size());  // drop the eq tables' (and the weight's) evaluations
     out.sumcheck_point = res.second.collect_raw_challenges();
     out.batching_challenges = batching;
     out.degree = vp.max_degree;

@@ -51,7 +51,7 @@ PROVER_SIGNATURES = {
                                          ctypes.POINTER(_u32), _vp, _u32, _vp, _pp]),
     "dpb_lookup_linking_prove": (_int, [_vp, _int, _vp, ctypes.c_int64, ctypes.c_int64, _vp, _u32, _pp, _u32, _vp, _u32, _vp,
                                         _u32, _vp, _vp, _u32, _vp, _vp, _vp, _u32, ctypes.POINTER(_u32),
-                                        ctypes.POINTER(_u32)]),
+                                        ctypes.POINTER(_u32), _vp, _vp]),
     "dpb_logup_batch_prove": (_int, [_vp, ctypes.POINTER(LogupInputStruct), _u32, _vp, _pp]),
     "dpb_logup_proof_serialize": (_int, [_vp, _vp, _size_t, ctypes.POINTER(_size_t)]),
     "dpb_logup_proof_free": (None, [_vp]),
@@ -233,15 +233,16 @@ def same_poly_prove(ctx, transcript, poly, points):
     return evals, point, ev
 
 
-VARIANT_STANDARD, VARIANT_GLU, VARIANT_SOFTMAX = 0, 1, 2
+VARIANT_STANDARD, VARIANT_GLU, VARIANT_SOFTMAX, VARIANT_NORMALISATION, VARIANT_NORMALISATION_WITH_SUM = 0, 1, 2, 3, 4
 
 
 def lookup_linking_prove(ctx, transcript, variant, info, table_min_output, table_max_output, shape, mles,
-                         last_claim_point, logup_point):
+                         last_claim_point, logup_point, weight=None):
     """LookupInputConfig::prove_linking_sumcheck (zkml/src/lookup/operation/inputs/proving.rs:26-114), Standard and
     GLU variants.  info: ChunkingInfo; shape: the operation's unpadded input shape; mles: the witness tables in
     the expression's order; points: [coords, w].  Returns dict(sumcheck [n, d+1, w], point [n, w],
-    evaluations [len(mles), w], challenges [1 + slices, w])."""
+    evaluations [len(mles), w], challenges [1 + slices (+ the variant's own), w], weight_eval [w] or None).
+    weight: the Normalisation variant's weight table (an Mle) or None."""
     w = elem_words(chal_dtype(mles[0].dtype))
     cp, lp = _scalars(last_claim_point).reshape(-1, w), _scalars(logup_point).reshape(-1, w)
     n = lp.shape[0]
@@ -255,15 +256,16 @@ def lookup_linking_prove(ctx, transcript, variant, info, table_min_output, table
     evals = np.zeros((cap, w), dtype=np.uint64)
     point = np.zeros((n, w), dtype=np.uint64)
     finals = np.zeros((len(mles), w), dtype=np.uint64)
-    chal = np.zeros((2 + slices, w), dtype=np.uint64)
+    chal = np.zeros((3 + slices, w), dtype=np.uint64)
+    weight_eval = np.zeros(w, dtype=np.uint64)
     n_chal, degree = ctypes.c_uint32(), ctypes.c_uint32()
     check(lib.dpb_lookup_linking_prove(ctx.h, variant, ctypes.byref(info), table_min_output, table_max_output, shp, rank, hs,
                                        len(mles), _buf(cp), cp.shape[0], _buf(lp), n, transcript.h, _buf(evals), cap,
-                                       _buf(point), _buf(finals), _buf(chal), 2 + slices, ctypes.byref(n_chal),
-                                       ctypes.byref(degree)))
+                                       _buf(point), _buf(finals), _buf(chal), 3 + slices, ctypes.byref(n_chal),
+                                       ctypes.byref(degree), weight.h if weight is not None else None, _buf(weight_eval)))
     d = degree.value
     return dict(sumcheck=evals[: n * (d + 1)].reshape(n, d + 1, w), point=point, evaluations=finals,
-                challenges=chal[: n_chal.value])
+                challenges=chal[: n_chal.value], weight_eval=weight_eval if weight is not None else None)
 
 
 class CommittedPoly:

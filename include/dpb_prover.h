@@ -144,9 +144,11 @@ void dpb_logup_proof_free(dpb_logup_proof* p);
 #define DPB_VARIANT_SOFTMAX 2  /* LookupVariant::Softmax: one more challenge ("normalisation") and a third eq table,
                                 * over (1/2, .., 1/2, the logup point's coordinates above the last dimension's), that
                                 * sums the outputs along the last dimension */
+#define DPB_VARIANT_NORMALISATION 3           /* LookupVariant::Normalisation { normalised_sum_value: None, .. } */
+#define DPB_VARIANT_NORMALISATION_WITH_SUM 4  /* the same with normalised_sum_value: Some(..): the sums are tied too */
 /* LookupInputConfig::prove_linking_sumcheck (zkml/src/lookup/operation/inputs/proving.rs:26-114)
  * with LookupVariant::build_full_sumcheck_expression (zkml/src/lookup/operation/variant.rs:55-262)
- * for the Standard, GLU and Softmax variants, without a weight table: ties the looked-up outputs of an
+ * for the Standard, GLU and Softmax variants (the Normalisation variant is described below): ties the looked-up outputs of an
  * operation to the claim on its output tensor and to the logup point,
  *   sum_x sum_c b_c * ( eq(x, p_out) * (clamping_c(x) + selector_c(x) * value_c(x)) [* glu_c(x)]
  *                       + eq(x, p_logup) * sum_j s^j * witness_{c,j}(x) ).
@@ -161,14 +163,20 @@ void dpb_logup_proof_free(dpb_logup_proof* p);
  * (Shape::compute_eq_point_and_batching_challenges, zkml/src/shape.rs:565-610).
  * Outputs: out_round_evals[n * (degree+1)] (capacity round_evals_cap elements),
  * out_point[n], out_evaluations[n_mles] (the witness tables at the point),
- * out_batching_challenges[1 + slices (+ 1 for Softmax)] (capacity chal_cap), *out_degree. */
+ * out_batching_challenges[1 + slices (+ 1 for Softmax, + 2 for Normalisation)] (capacity
+ * chal_cap), *out_degree.
+ * Normalisation (variant.rs:288-346): after the outputs, `mles` holds one input table per slice
+ * and then one scaling table per slice; two more challenges ("normalisation", "input"); the
+ * sums of squares of the outputs along the last dimension ride on the third eq table (and the
+ * sums, with DPB_VARIANT_NORMALISATION_WITH_SUM); `weight` (may be NULL; only this variant takes
+ * one) multiplies the output part (has_weight) and *out_weight_eval receives its evaluation. */
 int dpb_lookup_linking_prove(dpb_ctx* ctx, int variant, const dpb_chunking_info* info, int64_t table_min_output,
                              int64_t table_max_output, const uint64_t* shape, uint32_t rank, dpb_mle* const* mles,
                              uint32_t n_mles, const void* last_claim_point, uint32_t n_claim_coords,
                              const void* logup_point, uint32_t n_logup_coords, dpb_transcript* t, void* out_round_evals,
                              uint32_t round_evals_cap, void* out_point, void* out_evaluations,
                              void* out_batching_challenges, uint32_t chal_cap, uint32_t* out_n_challenges,
-                             uint32_t* out_degree);
+                             uint32_t* out_degree, dpb_mle* weight, void* out_weight_eval);
 
 #ifdef __cplusplus
 }

@@ -1307,16 +1307,17 @@ def table_multiplicities(F, merged_column, counts):
 
 
 # ------------------------------------------------ lookup linking sumcheck
-VARIANT_STANDARD, VARIANT_GLU, VARIANT_SOFTMAX = 0, 1, 2
+VARIANT_STANDARD, VARIANT_GLU, VARIANT_SOFTMAX, VARIANT_NORMALISATION = 0, 1, 2, 3
 
 
 def lookup_output_expressions(F, info, chunk, out_min, out_max):
     """LookupVariant::build_lookup_output_expressions (zkml/src/lookup/operation/variant.rs:73-226) with
-    ValueExpression::new (variant.rs:467-510): (value, prod_selector, clamping_expression, sum) over the witnesses
-    of one chunk, which are its value chunk outputs followed by its zeroing chunk outputs.  out_min / out_max are
+    ValueExpression::new (variant.rs:467-510): (value, prod_selector, clamping_expression, sum,
+    squared_clamping_expression) over the witnesses of one chunk, which are its value chunk outputs followed by its zeroing chunk outputs.  out_min / out_max are
     the value table's extreme outputs (Table::min_output_value / max_output_value)."""
     one, zero = F.one, F.zero
     ONE, bits, nz = Expr.const(one), info.value_chunk_size, info.n_zeroing
+    sq_clamp = Expr.const(zero)  # only the signed case with zeroing chunks has one (variant.rs:163-170, 212-213)
     offset = chunk * (info.n_value + nz)
     if info.n_value == 1:
         value = Expr.wit(offset)
@@ -1351,6 +1352,7 @@ def lookup_output_expressions(F, info, chunk, out_min, out_max):
             first = last * (last + ONE) * half + (one_minus_sq - lower * one_minus_sq)
             second = last * (last - ONE) * half
             clamp = first * Expr.const(cmax) + second * Expr.const(cmin)
+            sq_clamp = first * Expr.const(cmax) * Expr.const(cmax) + second * Expr.const(cmin) * Expr.const(cmin)
         else:
             clamp = Expr.const(zero)
     else:
@@ -1363,24 +1365,44 @@ def lookup_output_expressions(F, info, chunk, out_min, out_max):
             clamp = Expr.const(F.from_int(out_max if info.sign == SIGN_POSITIVE else out_min))
         else:
             clamp = ONE
-    return value, prod, clamp, total
+    return value, prod, clamp, total, sq_clamp
 
 
-def lookup_linking_expression(F, variant, total_chunks, info, out_min, out_max, final_dim_size=None):
+def lookup_linking_expression(F, variant, total_chunks, info, out_min, out_max, final_dim_size=None,
+                              normalised_sum=False, has_weight=False):
     """build_full_sumcheck_expression / sumcheck_expression_for_chunk (variant.rs:55-70, 229-287) for the Standard,
     GLU and Softmax variants: sum over chunks of
         challenge[1 + c] * (eq_out * P_c [* glu_witness_c] [+ 2^k challenge[1 + chunks] * eq_norm * P_c]
                             + eq_lookup * sum),   P_c = clamping + prod_selector * value,
     2^k the padded size of the last dimension.  Witness ids: the chunks' outputs, then (GLU) one witness per chunk,
-    then eq_out, eq_lookup, (Softmax) eq_norm."""
+    then eq_out, eq_lookup, (Softmax) eq_norm.
+    Normalisation (variant.rs:288-346), two more witnesses per chunk (the chunk's input and its scaling):
+        challenge[1 + c] * (eq_out [* weight] * P_c [+ 2^k nu^2 * eq_norm * P_c] + 2^k nu * eq_norm * Q_c
+                            + eq_lookup * (sum + iota * input_c * scaling_c)),
+    Q_c = squared clamping + prod_selector * value^2, nu = challenge[1 + chunks], iota = challenge[2 + chunks];
+    witness ids: outputs, inputs per chunk, scalings per chunk, eq_out, eq_lookup, eq_norm, (weight)."""
     per = info.n_value + info.n_zeroing
     total_out = total_chunks * per
-    total_wit = total_out + (total_chunks if variant == VARIANT_GLU else 0)
+    extra = {VARIANT_GLU: 1, VARIANT_NORMALISATION: 2}.get(variant, 0)
+    total_wit = total_out + total_chunks * extra
     eq_out, eq_lk = Expr.wit(total_wit), Expr.wit(total_wit + 1)
     e = Expr.const(F.zero)
     for c in range(total_chunks):
-        value, prod, clamp, total = lookup_output_expressions(F, info, c, out_min, out_max)
+        value, prod, clamp, total, sq_clamp = lookup_output_expressions(F, info, c, out_min, out_max)
         prod_expression = clamp + prod * value
+        if variant == VARIANT_NORMALISATION:
+            norm_eq = Expr.wit(total_wit + 2)
+            pow_two = F.from_int(1 << max(final_dim_size - 1, 0).bit_length())
+            prod_squared = sq_clamp + prod * value * value
+            lead = eq_out * Expr.wit(total_wit + 3) if has_weight else eq_out
+            out_part = lead * prod_expression
+            if normalised_sum:
+                out_part = out_part + Expr.chal(1 + total_chunks, 2, pow_two, F.zero) * (norm_eq * prod_expression)
+            inp = Expr.wit(total_out + c) * Expr.wit(total_out + total_chunks + c)
+            e = e + Expr.chal(1 + c, 1, F.one, F.zero) * (
+                out_part + Expr.chal(1 + total_chunks, 1, pow_two, F.zero) * (norm_eq * prod_squared)
+                + eq_lk * (total + Expr.chal(2 + total_chunks, 1, F.one, F.zero) * inp))
+            continue
         out_part = eq_out * prod_expression
         if variant == VARIANT_GLU:
             out_part = out_part * Expr.wit(total_out + c)
@@ -1414,7 +1436,8 @@ def eq_point_and_batching_challenges(F, shape, point):
     return eq_point, chal
 
 
-def lookup_linking_prove(F, transcript, variant, info, out_min, out_max, shape, mles, last_claim_point, logup_point):
+def lookup_linking_prove(F, transcript, variant, info, out_min, out_max, shape, mles, last_claim_point, logup_point,
+                         normalised_sum=False, weight=None):
     """LookupInputConfig::prove_linking_sumcheck (zkml/src/lookup/operation/inputs/proving.rs:26-114), Standard,
     GLU and Softmax variants, without a weight table.  `mles`: the witness tables in the expression's order.
     Returns the proof, the tables' evaluations at the sumcheck's point (eq tables left out), the point and the
@@ -1423,14 +1446,22 @@ def lookup_linking_prove(F, transcript, variant, info, out_min, out_max, shape, 
     (build_eq_polys, variant/proving.rs:225-253)."""
     eq_point, chal = eq_point_and_batching_challenges(F, shape, last_claim_point)
     sum_challenge = transcript.append_and_sample(b"sum")
-    other = [transcript.append_and_sample(b"normalisation")] if variant == VARIANT_SOFTMAX else []
+    other = []
+    if variant in (VARIANT_SOFTMAX, VARIANT_NORMALISATION):
+        other.append(transcript.append_and_sample(b"normalisation"))
+    if variant == VARIANT_NORMALISATION:
+        other.append(transcript.append_and_sample(b"input"))
     total_chunks = len(chal)
     chal = [sum_challenge] + chal + other
     eqs = [eq_evals(F, eq_point), eq_evals(F, logup_point)]
-    if variant == VARIANT_SOFTMAX:
+    if variant in (VARIANT_SOFTMAX, VARIANT_NORMALISATION):
         fdv = max(shape[-1] - 1, 0).bit_length()
         eqs.append(eq_evals(F, [F.inv(F.from_int(2))] * fdv + list(logup_point[fdv:])))
-    expr = lookup_linking_expression(F, variant, total_chunks, info, out_min, out_max, shape[-1])
+    if weight is not None:
+        eqs.append(weight)  # the weight table comes after the eq tables (inputs/proving.rs:66-68)
+    expr = lookup_linking_expression(F, variant, total_chunks, info, out_min, out_max, shape[-1], normalised_sum,
+                                     weight is not None)
     terms = expr_to_terms(F, expr, chal)
     proof, point, finals = sumcheck_prove(F, len(eq_point), list(mles) + eqs, terms, transcript)
-    return dict(sumcheck=proof, evaluations=finals[:len(mles)], point=point, challenges=chal)
+    return dict(sumcheck=proof, evaluations=finals[:len(mles)], point=point, challenges=chal,
+                weight_eval=finals[-1] if weight is not None else None)

@@ -377,3 +377,59 @@ def test_lookup_golden(dpb, ctx, prover, F):
     tr.free()
     for c in counts:
         c.free()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("F", FIELDS)
+@pytest.mark.parametrize("with_sum,with_weight,kind,bits,right_shift,max_bit_size,shape", [
+    (False, False, "relu", 8, 12, 40, (3, 5, 6)),      # two zeroing chunks: degree 6 under the third eq table
+    (True, True, "relu", 8, 12, 30, (2, 9, 12)),       # one zeroing chunk, the sum tied too, a weight table
+    (True, False, "relu", 10, 13, 23, (7, 33)),        # no zeroing chunk, 2^9 entries
+    (False, True, "exp", 8, 10, 34, (2, 6, 6)),        # a table over non-positive inputs
+])
+def test_linking_sumcheck_normalisation(dpb, ctx, prover, F, with_sum, with_weight, kind, bits, right_shift, max_bit_size,
+                                        shape):
+    rng = np.random.default_rng(9985 + bits)
+    sign, table_out, n_cols = value_table(kind, bits)
+    t = draw_tensor(rng, shape, sign, max_bit_size, 3)
+    o_ci = orc.ChunkingInfo(right_shift, bits, sign, max_bit_size)
+    w = orc.LookupOpWitness(o_ci, 3, 0, t, table_out, n_cols)
+    out_min, out_max = int(table_out[0]), int(table_out[-1])
+    dims = [1 << max(d - 1, 0).bit_length() for d in shape]
+    total, n2d = sum(d.bit_length() - 1 for d in dims), sum(d.bit_length() - 1 for d in dims[-2:])
+    slices = int(np.prod(shape[:-2])) if len(shape) > 2 else 1
+    P = 1 << n2d
+    rand = lambda: F.random_table_fast(rng, P) if F is orc.FrField else F.random_table(rng, P)
+    extra = [rand() for _ in range(2 * slices)]
+    weight = rand() if with_weight else None
+    o_mles = [F.table_from_i64(c) for c in w.output_columns()] + extra
+    claim_point = [F.random_scalar(rng) for _ in range(total)]
+    logup_point = [F.random_scalar(rng) for _ in range(n2d)]
+    o_tr = orc.Transcript(F)
+    want = orc.lookup_linking_prove(F, o_tr, orc.VARIANT_NORMALISATION, o_ci, out_min, out_max, shape, o_mles, claim_point,
+                                    logup_point, normalised_sum=with_sum, weight=weight)
+    fam = family_dtype(dpb, F)
+    ci = dpb.ChunkingInfo.new(right_shift, bits, sign, max_bit_size)
+    up = lambda m: ctx.upload(np.ascontiguousarray(m), dpb.dtype_of_array(m, F.name))
+    d_mles = [up(m) for m in o_mles]
+    d_weight = up(weight) if with_weight else None
+    tr = prover.Blake3Transcript(fam)
+    variant = prover.VARIANT_NORMALISATION_WITH_SUM if with_sum else prover.VARIANT_NORMALISATION
+    got = prover.lookup_linking_prove(ctx, tr, variant, ci, out_min, out_max, shape, d_mles,
+                                      orc.scalars_to_array(F, claim_point), orc.scalars_to_array(F, logup_point),
+                                      weight=d_weight)
+    assert flat(F, got["challenges"]) == want["challenges"]
+    assert flat(F, got["sumcheck"]) == [e for r in want["sumcheck"] for e in r]
+    assert flat(F, got["point"]) == want["point"]
+    assert flat(F, got["evaluations"]) == want["evaluations"]
+    if with_weight:
+        assert flat(F, got["weight_eval"]) == [want["weight_eval"]]
+    assert tr.state() == (o_tr.state, o_tr.round)
+    if not with_weight:  # a weight table belongs to this variant only
+        with pytest.raises(dpb.DpbError):
+            prover.lookup_linking_prove(ctx, tr, prover.VARIANT_STANDARD, ci, out_min, out_max, shape,
+                                        d_mles[:len(w.output_columns())], orc.scalars_to_array(F, claim_point),
+                                        orc.scalars_to_array(F, logup_point), weight=d_mles[0])
+    for m in d_mles + ([d_weight] if d_weight else []):
+        m.free()
+    tr.free()

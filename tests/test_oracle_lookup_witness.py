@@ -369,3 +369,62 @@ def test_softmax_variant_adds_the_row_sums(F):
     wit = soft["evaluations"] + [orc.identity_eval(F, claim_point[:n2d], point), orc.identity_eval(F, logup_point, point),
                                  orc.identity_eval(F, [half] * col_vars + logup_point[col_vars:], point)]
     assert orc.eval_expr(F, expr, wit, soft["challenges"]) == expected
+
+
+@pytest.mark.parametrize("F", [orc.FrField, orc.GlField])
+@pytest.mark.parametrize("normalised_sum,with_weight", [(False, False), (True, True)])
+def test_normalisation_variant(F, normalised_sum, with_weight):
+    """LookupVariant::Normalisation (variant.rs:288-346): the output part (times the weight table when there is
+    one), nu times the sums of squares along the last dimension (and nu^2 times the sums, when the sum is
+    normalised too) at the logup point's row coordinates, the lookup columns, and iota times the product of each
+    chunk's input and scaling tables at the logup point."""
+    rng = np.random.default_rng(9995)
+    shape = (3, 5, 6)
+    ci, w, outputs, out_min, out_max = linking_case(F, "relu", rng, shape)
+    n2d, col_vars, P = 6, 3, 64
+    small = lambda: F.table_from_i64(rng.integers(-50, 50, size=P, dtype=np.int64))
+    inputs, scalings = [small() for _ in range(3)], [small() for _ in range(3)]
+    w_int = rng.integers(-50, 50, size=P, dtype=np.int64)
+    weight = F.table_from_i64(w_int) if with_weight else None
+    mles = [F.table_from_i64(c) for c in w.output_columns()] + inputs + scalings
+    claim_point = [F.random_scalar(rng) for _ in range(n2d + 2)]
+    logup_point = [F.random_scalar(rng) for _ in range(n2d)]
+    res = orc.lookup_linking_prove(F, orc.Transcript(F), orc.VARIANT_NORMALISATION, ci, out_min, out_max, shape, mles,
+                                   claim_point, logup_point, normalised_sum=normalised_sum, weight=weight)
+    chal = res["challenges"]
+    assert len(chal) == 1 + 3 + 2
+    s, betas, nu, iota = chal[0], chal[1:4], chal[4], chal[5]
+    per = ci.n_value + ci.n_zeroing
+    want = F.zero
+    for c in range(3):
+        out = outputs[c]
+        if with_weight:
+            lead = orc.evaluate(F, F.table_from_i64((out * w_int.reshape(out.shape)).reshape(-1)), claim_point[:n2d])
+        else:
+            lead = orc.evaluate(F, F.table_from_i64(out.reshape(-1)), claim_point[:n2d])
+        rows = logup_point[col_vars:]
+        part = F.add(lead, F.mul(nu, orc.evaluate(F, F.table_from_i64((out * out).sum(axis=1)), rows)))
+        if normalised_sum:
+            part = F.add(part, F.mul(F.mul(nu, nu), orc.evaluate(F, F.table_from_i64(out.sum(axis=1)), rows)))
+        lk = F.zero
+        for j, p in enumerate([1] + [2 + k for k in range(ci.n_zeroing)]):
+            lk = F.add(lk, F.mul(F.pow(s, p), orc.evaluate(F, mles[c * per + j], logup_point)))
+        prod_tab = [F.mul(a, b) for a, b in zip(orc.array_to_scalars(F, orc._widen(F, inputs[c])),
+                                                orc.array_to_scalars(F, orc._widen(F, scalings[c])))]
+        lk = F.add(lk, F.mul(iota, orc.evaluate(F, orc.scalars_to_array(F, prod_tab), logup_point)))
+        want = F.add(want, F.mul(betas[c], F.add(part, lk)))
+    assert orc.extract_sum(F, res["sumcheck"]) == want
+    tr = orc.Transcript(F)
+    for label in (b"sum", b"normalisation", b"input"):
+        tr.append_and_sample(label)
+    degree = len(res["sumcheck"][0]) - 1
+    point, expected = orc.sumcheck_verify(F, want, res["sumcheck"], n2d, degree, tr)
+    half = F.inv(F.from_int(2))
+    expr = orc.lookup_linking_expression(F, orc.VARIANT_NORMALISATION, 3, ci, out_min, out_max, shape[-1],
+                                         normalised_sum, with_weight)
+    wit = res["evaluations"] + [orc.identity_eval(F, claim_point[:n2d], point), orc.identity_eval(F, logup_point, point),
+                                orc.identity_eval(F, [half] * col_vars + logup_point[col_vars:], point)]
+    if with_weight:
+        assert res["weight_eval"] == orc.evaluate(F, weight, point)
+        wit.append(res["weight_eval"])
+    assert orc.eval_expr(F, expr, wit, chal) == expected
