@@ -87,6 +87,7 @@ SIGNATURES = {
     "dpb_logup_num_levels": (_u32, [_vp]),
     "dpb_logup_level": (_int, [_vp, _u32, _pp]),
     "dpb_logup_outputs": (_int, [_vp, _vp]),
+    "dpb_logup_outputs_batch": (_int, [_pp, _u32, _vp]),
     "dpb_logup_free": (None, [_vp]),
     "dpb_product_round_noalloc": (_int, [_vp, _int, _pp, _u32, _u64, _vp]),
     "dpb_einsum_fix_axes": (_int, [_vp, _int, _vp, _int, _vp, _vp, _pp, _vp, _u32, _pp, _pp, _u32, ctypes.POINTER(_u32)]),

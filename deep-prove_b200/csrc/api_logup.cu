@@ -139,6 +139,30 @@ int dpb_logup_outputs(const dpb_logup* lu, void* out4) {
     return DPB_OK;
 }
 
+int dpb_logup_outputs_batch(const dpb_logup* const* lus, uint32_t n, void* out) {
+    if (!lus || !out || n == 0) return fail(DPB_EINVAL, "null argument");
+    for (uint32_t i = 0; i < n; i++)
+        if (!lus[i] || lus[i]->ctx != lus[0]->ctx || lus[i]->gl != lus[0]->gl)
+            return fail(DPB_EINVAL, "tree %u is null, of another context or of another field", i);
+    dpb_ctx* ctx = lus[0]->ctx;
+    const size_t es = lus[0]->gl ? 16 : 32;
+    // gathered on the device, then one copy to the host and one wait, instead of one of each per tree
+    void* gathered = nullptr;
+    DPB_TRY(device_alloc(ctx, (size_t)n * 4 * es, &gathered));
+    cudaError_t e = cudaSuccess;
+    for (uint32_t i = 0; i < n && e == cudaSuccess; i++) {
+        const uint32_t top = lus[i]->m - 1;
+        char* dst = (char*)gathered + (size_t)i * 4 * es;
+        e = cudaMemcpyAsync(dst, lus[i]->num[top - 1], 2 * es, cudaMemcpyDeviceToDevice, ctx->stream);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(dst + 2 * es, lus[i]->den[top - 1], 2 * es, cudaMemcpyDeviceToDevice, ctx->stream);
+    }
+    if (e == cudaSuccess) e = cudaMemcpyAsync(out, gathered, (size_t)n * 4 * es, cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    device_free(ctx, gathered);
+    if (e != cudaSuccess) return fail(DPB_ECUDA, "logup outputs: %s", cudaGetErrorString(e));
+    return DPB_OK;
+}
+
 void dpb_logup_free(dpb_logup* lu) {
     if (!lu) return;
     device_free(lu->ctx, lu->slab);

@@ -71,6 +71,7 @@ struct dpb_sc {
     RoundTab* d_rtab_eq = nullptr;  // [n][k] descriptors of split-eq rounds
     alignas(16) uint8_t lag_w_h[7 * 32] = {0};  // interpolation weights for the nodes 0..d-1
     bool one_pass = false;       // large generic rounds run sc_round_generic
+    bool heavy = false;          // a long term program: small rounds are spread over the terms instead
     bool has_prog = false;       // d_rtab / d_groups / d_prog are laid out (every shape that fits)
     uint32_t tail_start = ~0u;   // first round the resident last-rounds kernel may take over
     bool tail_active = false;    // that kernel is running for this sumcheck
@@ -156,8 +157,12 @@ static void launch_eval_ranged(dpb_sc* sc, uint32_t round) {
 template <class F, int D>
 static void launch_eval(dpb_sc* sc, uint32_t round, uint64_t n_pairs) {
     dpb_ctx* ctx = sc->ctx;
-    sc_eval_generic<F, D><<<grid_for(ctx, n_pairs, 4), kThreads, 0, ctx->stream>>>(
-        sc->d_desc + (size_t)round * sc->k, (const TermDev<F>*)sc->d_terms, sc->n_terms, n_pairs,
+    // enough (pair, slice) items to fill the GPU once, at most one slice per term
+    const uint64_t target = (uint64_t)ctx->sm_count * kThreads * 2;
+    uint64_t n_slices = n_pairs >= target ? 1 : (target + n_pairs - 1) / n_pairs;
+    if (n_slices > sc->n_terms) n_slices = sc->n_terms;
+    sc_eval_generic<F, D><<<grid_for(ctx, n_pairs * n_slices, 4), kThreads, 0, ctx->stream>>>(
+        sc->d_desc + (size_t)round * sc->k, (const TermDev<F>*)sc->d_terms, sc->n_terms, n_pairs, (uint32_t)n_slices,
         reduce_scratch<F>(ctx), (typename F::E*)ctx->round_out);
 }
 
@@ -299,7 +304,12 @@ static void plan_program(dpb_sc* sc, const dpb_term* terms, dpb_mle* const* mles
     std::vector<ProgTerm<F>> prog;
     std::vector<bool> is_eq(sc->k);
     for (uint32_t j = 0; j < sc->k; j++) is_eq[j] = mles[j]->eq_point.size() == (size_t)sc->tr[j].nv * sizeof(E);
-    compile_program<F>(terms, sc->n_terms, sc->k, groups, prog, is_eq);
+    uint32_t mults = 0;
+    compile_program<F>(terms, sc->n_terms, sc->k, groups, prog, is_eq, &mults);
+    // One thread walks the whole program per (pair, point) in the one-pass rounds and in the resident kernel; once
+    // that chain of multiplications takes longer than two more launches, rounds too small to fill the GPU with
+    // pairs are better spread over the terms (sc_fold_generic + sc_eval_generic with slices).
+    sc->heavy = (uint64_t)mults * (sc->d + 1) >= 200u;
     sc->n_groups = (uint32_t)groups.size();
     sc->n_prog_terms = (uint32_t)prog.size();
     h_groups.assign((const uint8_t*)groups.data(), (const uint8_t*)groups.data() + groups.size() * sizeof(ProgGroup));
@@ -819,6 +829,8 @@ static int wait_round_chunks(dpb_ctx* ctx, size_t msg_bytes, void* out) {
     return DPB_OK;
 }
 
+constexpr uint64_t kSpreadPairs = 4096;  // rounds up to this size of a heavy program are spread over its terms
+
 template <class F>
 static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
     typedef typename F::E E;
@@ -847,8 +859,10 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
     }
     if (sc->spliteq && i > 0) spliteq_advance<F>(sc, i, r);
     // the last rounds go to the resident kernel (one per context at a time; not while profiling per launch)
-    bool use_tail = sc->tail_active || (sc->has_prog && ctx->tail_enabled && !sharded && !ctx->profile &&
+    bool use_tail = sc->tail_active || (sc->has_prog && ctx->tail_enabled && !sharded && !ctx->profile && !sc->heavy &&
                                         i >= sc->tail_start && ctx->tail_owner == nullptr);
+    const bool spread = sc->heavy && n_pairs <= kSpreadPairs && sc->fused_shape != kFusedProduct;
+    if (spread && sc->eq_unbound) DPB_TRY(spliteq_materialize<F>(sc, i));
     E raw[kMaxAcc];
     if (use_tail) {
         const int rc = tail_round<F>(sc, i, r, raw);
@@ -867,7 +881,7 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
     }
     bool one_pass = use_tail;
     bool split = false;
-    if (!use_tail && !done && sc->spliteq) {
+    if (!use_tail && !done && !spread && sc->spliteq) {
         int rc = DPB_OK;
         switch (sc->d) {
             case 2: rc = launch_spliteq<F, 2>(sc, i, n_pairs, r); break;
@@ -881,7 +895,7 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
         one_pass = split = true;
         sc->eq_unbound = true;
     }
-    if (!use_tail && !done && !split && sc->one_pass) {
+    if (!use_tail && !done && !split && !spread && sc->one_pass) {
         int rc = DPB_OK;
         switch (sc->d) {
             case 1: rc = launch_one_pass<F, 1>(sc, i, n_pairs, r); break;

@@ -653,7 +653,8 @@ inline uint32_t emit_chain(const std::vector<ProgMono<F>>& monos, uint32_t k, st
 // Inside a group the remaining monomials become a Horner chain where that saves multiplications (emit_chain).
 template <class F>
 inline void compile_program(const dpb_term* terms, uint32_t n_terms, uint32_t k, std::vector<ProgGroup>& groups,
-                            std::vector<ProgTerm<F>>& prog, const std::vector<bool>& prefer = std::vector<bool>()) {
+                            std::vector<ProgTerm<F>>& prog, const std::vector<bool>& prefer = std::vector<bool>(),
+                            uint32_t* mults_per_point = nullptr) {
     typedef typename F::E E;
     std::vector<bool> used(n_terms, false);
     uint32_t left = n_terms;
@@ -715,7 +716,8 @@ inline void compile_program(const dpb_term* terms, uint32_t n_terms, uint32_t k,
                 left--;
             }
         }
-        emit_chain<F>(monos, k, prog);
+        const uint32_t cost = emit_chain<F>(monos, k, prog) + (g.outer != kNoOuter ? 1 : 0);
+        if (mults_per_point) *mults_per_point += cost;
         g.term_end = (uint16_t)prog.size();
         groups.push_back(g);
     }

@@ -100,6 +100,7 @@ class LogUpCircuit {
         check(dpb_logup_outputs(tree_, o.data()));
         return o;
     }
+    const dpb_logup* tree() const { return tree_; }
 
     // Tables of the layer whose halves have `layer_vars` variables, in the
     // order layer_proving_info registers them.  Views stay alive with *this.
@@ -295,7 +296,15 @@ LogUpBatchProof<F> new_batch_multiple_sizes_prove(dpb_ctx* ctx, const std::vecto
 
     LogUpBatchProof<F> proof;
     proof.proof_type = proof_type;
-    for (const auto& c : circuits) proof.circuit_outputs.push_back(c->outputs());
+    {
+        // every circuit's outputs (LogUpCircuit::outputs, circuit.rs:558-560) with one wait for the device
+        std::vector<const dpb_logup*> trees;
+        for (const auto& c : circuits) trees.push_back(c->tree());
+        std::vector<E> flat(4 * trees.size());
+        check(dpb_logup_outputs_batch(trees.data(), (uint32_t)trees.size(), flat.data()));
+        for (size_t i = 0; i < trees.size(); i++)
+            proof.circuit_outputs.emplace_back(flat.begin() + 4 * i, flat.begin() + 4 * i + 4);
+    }
 
     const E count = F::from_u64(circuits.size());
     transcript.append_scalars(&count, 1);

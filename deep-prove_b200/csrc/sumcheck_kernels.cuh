@@ -178,18 +178,23 @@ __device__ __forceinline__ void grid_sum_publish(typename F::E (&acc)[NACC], Red
 
 // Generic round evaluation: any list of product terms over any tables.
 // acc[x] = sum_p sum_t coeff_t * prod_j f_tj(x; p),  f(x; p) = f[2p] + x (f[2p+1] - f[2p]).
+// Work items are (pair, slice): slice s of n_slices takes the terms s, s + n_slices, ..  A round with few pairs
+// and many terms (a batch of many logup instances late in a sumcheck) is spread over the terms as well, instead
+// of leaving one thread per pair to walk the whole list.
 template <class F, int D>
 __global__ void __launch_bounds__(kThreads)
     sc_eval_generic(const MleDesc* __restrict__ mles, const TermDev<F>* __restrict__ terms,
-                    uint32_t n_terms, uint64_t n_pairs, ReduceScratch<F> rs,
+                    uint32_t n_terms, uint64_t n_pairs, uint32_t n_slices, ReduceScratch<F> rs,
                     typename F::E* out) {
     typedef typename F::E E;
     E acc[D + 1];
 #pragma unroll
     for (int x = 0; x <= D; x++) acc[x] = F::zero();
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
-    for (uint64_t p = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; p < n_pairs; p += stride) {
-        for (uint32_t t = 0; t < n_terms; t++) {
+    const uint64_t n_items = n_pairs * n_slices;
+    for (uint64_t w = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; w < n_items; w += stride) {
+        const uint64_t p = w % n_pairs;
+        for (uint32_t t = (uint32_t)(w / n_pairs); t < n_terms; t += n_slices) {
             const TermDev<F>& tm = terms[t];
             E prod[D + 1];
             const uint32_t nf = tm.n_factors;

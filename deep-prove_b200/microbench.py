@@ -316,6 +316,23 @@ def main():
     sc = sum((4 * 2 + 1) * (4 * s1) * (1 << v) for v in range(1, n)) // 2
     report(f"logup-GKR batch prove, 2 x 2^{n} lookups", t, tree + sc)
 
+    # a batch of many small instances (softmax chunks x lookups per chunk): 36 two-column lookups of 2^12, whose
+    # long term list is spread over threads in the small rounds
+    many = [ctx.upload(table(1 << 12), base) for _ in range(72)]
+
+    def logup_many():
+        tr = prover.Blake3Transcript(fam)
+        out = prover.new_batch_multiple_sizes_prove(ctx, [prover.LogUpInput.new_lookup(many, c, sep, 2)], tr)
+        tr.free()
+        return out
+
+    t = timed(ctx, logup_many, max(1, args.reps // 2))
+    m12 = 1 << 12
+    report("logup-GKR batch prove, 36 x 2 columns x 2^12", t,
+           36 * (2 * m12 * s0 + 4 * m12 * s1) + sum((4 * 36 + 1) * (4 * s1) * (1 << v) for v in range(1, 12)) // 2)
+    for h in many:
+        h.free()
+
     # generic sumcheck: two product terms with coefficients over four tables (einsum-like shape)
     tabs = [ctx.upload(table(N), base) for _ in range(4)]
     cb = chal(2)

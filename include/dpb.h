@@ -296,6 +296,8 @@ uint32_t dpb_logup_num_levels(const dpb_logup* lu);
 int dpb_logup_level(const dpb_logup* lu, uint32_t level, dpb_mle* out_views[4]);
 /* [num[0], num[1], den[0], den[1]] of the top level (LogUpCircuit::outputs, :558-560). */
 int dpb_logup_outputs(const dpb_logup* lu, void* out4);
+/* The same for n trees of one context and field with a single wait: out receives 4 elements per tree. */
+int dpb_logup_outputs_batch(const dpb_logup* const* lus, uint32_t n, void* out);
 void dpb_logup_free(dpb_logup* lu);
 
 /* ---- lookup witness generation (zkml/src/lookup/operation, zkml/src/lookup/context.rs) ---- */
