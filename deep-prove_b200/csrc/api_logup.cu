@@ -16,6 +16,8 @@ struct dpb_logup {
 
 namespace dpb {
 
+constexpr uint64_t kSmallLevel = 1024;  // levels of at most this many fractions are finished by one block
+
 template <class F>
 static int build_tree(dpb_logup* lu, int kind, dpb_mle* const* columns, uint32_t n_cols,
                       const dpb_mle* mult, const void* constant_chal, const void* sep_chal) {
@@ -57,6 +59,12 @@ static int build_tree(dpb_logup* lu, int kind, dpb_mle* const* columns, uint32_t
                                                                                    (E*)lu->num[0], (E*)lu->den[0]);
     for (uint32_t l = 2; l <= levels; l++) {
         half = 1ull << (m - l);
+        if (half <= kSmallLevel) {
+            // levels l..levels in one launch (they lie one behind the other in the slab)
+            logup_small_levels<F><<<1, kThreads, 0, ctx->stream>>>((const E*)lu->num[l - 2], (const E*)lu->den[l - 2], half,
+                                                                   (E*)lu->num[l - 1]);
+            break;
+        }
         logup_next_level<F><<<grid_for(ctx, half), kThreads, 0, ctx->stream>>>(
             (const E*)lu->num[l - 2], (const E*)lu->den[l - 2], half, (E*)lu->num[l - 1], (E*)lu->den[l - 1]);
     }

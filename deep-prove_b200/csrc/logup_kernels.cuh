@@ -80,4 +80,26 @@ __global__ void logup_next_level(const typename F::E* __restrict__ num_in,
     }
 }
 
+// The last levels of a tree in one block: level after level from `half` entries down to 2, each level's
+// numerators and denominators stored right behind the previous level's (the tree's layout).  Launched once the
+// levels are small enough that a launch per level costs more than the level.
+template <class F>
+__global__ void __launch_bounds__(kThreads)
+    logup_small_levels(const typename F::E* num_in, const typename F::E* den_in, uint64_t half, typename F::E* num) {
+    typedef typename F::E E;
+    for (; half >= 2; half >>= 1) {
+        E* den = num + half;
+        for (uint64_t i = threadIdx.x; i < half; i += blockDim.x) {
+            const E n1 = F::load(num_in, F::kChalDtype, i), n2 = F::load(num_in, F::kChalDtype, i + half);
+            const E d1 = F::load(den_in, F::kChalDtype, i), d2 = F::load(den_in, F::kChalDtype, i + half);
+            F::store(num, i, F::add(F::mul(n1, d2), F::mul(d1, n2)));
+            F::store(den, i, F::mul(d1, d2));
+        }
+        __syncthreads();  // this level is complete (and visible to the block) before the next one reads it
+        num_in = num;
+        den_in = den;
+        num = den + half;
+    }
+}
+
 }  // namespace dpb
