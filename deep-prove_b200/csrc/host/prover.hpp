@@ -64,7 +64,23 @@ class Expression {
         E a, b;  // Constant: a; Challenge: a = scalar, b = offset
         std::shared_ptr<const Node> l, r;
     };
-    typedef std::map<std::vector<uint16_t>, E> Terms;
+    // A monomial: its table ids in ascending order.  Ordered like a vector of ids (element by element, a prefix
+    // before its extensions), which is the order the terms reach the sumcheck in.
+    struct Mono {
+        uint16_t n = 0;
+        uint16_t id[DPB_MAX_FACTORS] = {0};
+        bool operator<(const Mono& o) const {
+            const uint16_t m = std::min(n, o.n);
+            for (uint16_t i = 0; i < m; i++)
+                if (id[i] != o.id[i]) return id[i] < o.id[i];
+            return n < o.n;
+        }
+        bool operator==(const Mono& o) const { return n == o.n && std::equal(id, id + n, o.id); }
+        size_t size() const { return n; }
+        uint16_t operator[](size_t i) const { return id[i]; }
+    };
+    // Monomial form: (monomial, coefficient) sorted by monomial, no monomial twice, no zero coefficient.
+    typedef std::vector<std::pair<Mono, E>> Terms;
 
     Expression() : n_(leaf(kConstant, 0, 0, F::zero(), F::zero())) {}
     static Expression ZERO() { return Constant(F::zero()); }
@@ -82,6 +98,7 @@ class Expression {
 
     // Monomial form under the given challenge values: {sorted table ids -> coefficient}.
     Terms to_terms(const std::vector<E>& challenges) const { return expand(*n_, challenges); }
+    static void normalise_terms(Terms& t) { normalise(t); }
 
     // eval_by_expr_with_instance with witness values and challenges only.
     E evaluate(const std::vector<E>& wit_evals, const std::vector<E>& challenges) const {
@@ -111,22 +128,55 @@ class Expression {
         if (n.id >= ch.size()) throw Error(DPB_EINVAL, "expression refers to a challenge that was not supplied");
         return F::add(F::mul(n.a, pow_elem<F>(ch[n.id], n.pow)), n.b);
     }
-    static void add_term(Terms& t, const std::vector<uint16_t>& m, const E& c) {
-        auto it = t.find(m);
-        if (it == t.end()) t.emplace(m, c);
-        else it->second = F::add(it->second, c);
+    // sorts by monomial, adds up equal monomials, drops zeros
+    static void normalise(Terms& t) {
+        std::stable_sort(t.begin(), t.end(), [](const std::pair<Mono, E>& x, const std::pair<Mono, E>& y) { return x.first < y.first; });
+        size_t w = 0;
+        for (size_t r = 0; r < t.size();) {
+            Mono m = t[r].first;
+            E c = t[r].second;
+            for (r++; r < t.size() && t[r].first == m; r++) c = F::add(c, t[r].second);
+            if (!F::is_zero(c)) {
+                t[w].first = m;
+                t[w].second = c;
+                w++;
+            }
+        }
+        t.resize(w);
     }
-    static void prune(Terms& t) {
-        for (auto it = t.begin(); it != t.end();) it = F::is_zero(it->second) ? t.erase(it) : std::next(it);
+    // two normalised lists -> their sum, normalised
+    static Terms merge(const Terms& a, const Terms& b) {
+        Terms out;
+        out.reserve(a.size() + b.size());
+        size_t i = 0, j = 0;
+        while (i < a.size() || j < b.size()) {
+            if (j == b.size() || (i < a.size() && a[i].first < b[j].first)) {
+                out.push_back(a[i++]);
+            } else if (i == a.size() || b[j].first < a[i].first) {
+                out.push_back(b[j++]);
+            } else {
+                const E c = F::add(a[i].second, b[j].second);
+                if (!F::is_zero(c)) out.emplace_back(a[i].first, c);
+                i++;
+                j++;
+            }
+        }
+        return out;
     }
     static Terms expand(const Node& n, const std::vector<E>& ch) {
         Terms out;
         switch (n.kind) {
-            case kWitIn: out.emplace(std::vector<uint16_t>{n.id}, F::one()); return out;
-            case kConstant: if (!F::is_zero(n.a)) out.emplace(std::vector<uint16_t>{}, n.a); return out;
+            case kWitIn: {
+                Mono m;
+                m.n = 1;
+                m.id[0] = n.id;
+                out.emplace_back(m, F::one());
+                return out;
+            }
+            case kConstant: if (!F::is_zero(n.a)) out.emplace_back(Mono(), n.a); return out;
             case kChallenge: {
                 const E v = challenge_value(n, ch);
-                if (!F::is_zero(v)) out.emplace(std::vector<uint16_t>{}, v);
+                if (!F::is_zero(v)) out.emplace_back(Mono(), v);
                 return out;
             }
             case kNeg: {
@@ -134,22 +184,19 @@ class Expression {
                 for (auto& kv : out) kv.second = F::neg(kv.second);
                 return out;
             }
-            case kAdd: {
-                out = expand(*n.l, ch);
-                for (const auto& kv : expand(*n.r, ch)) add_term(out, kv.first, kv.second);
-                prune(out);
-                return out;
-            }
+            case kAdd: return merge(expand(*n.l, ch), expand(*n.r, ch));
             case kMul: {
                 const Terms a = expand(*n.l, ch), b = expand(*n.r, ch);
+                out.reserve(a.size() * b.size());
                 for (const auto& x : a)
                     for (const auto& y : b) {
-                        std::vector<uint16_t> m(x.first);
-                        m.insert(m.end(), y.first.begin(), y.first.end());
-                        std::sort(m.begin(), m.end());
-                        add_term(out, m, F::mul(x.second, y.second));
+                        if (x.first.n + y.first.n > DPB_MAX_FACTORS) throw Error(DPB_EINVAL, "product term has too many factors");
+                        Mono m;
+                        m.n = (uint16_t)(x.first.n + y.first.n);
+                        std::merge(x.first.id, x.first.id + x.first.n, y.first.id, y.first.id + y.first.n, m.id);
+                        out.emplace_back(m, F::mul(x.second, y.second));
                     }
-                prune(out);
+                normalise(out);
                 return out;
             }
         }
@@ -202,12 +249,11 @@ class VirtualPolynomialsBuilder {
     VirtualPolynomials<F> to_virtual_polys(const std::vector<Expression<F>>& exprs,
                                            const std::vector<E>& challenges) const {
         typename Expression<F>::Terms all;
-        for (const auto& e : exprs)
-            for (const auto& kv : e.to_terms(challenges)) {
-                auto it = all.find(kv.first);
-                if (it == all.end()) all.emplace(kv.first, kv.second);
-                else it->second = F::add(it->second, kv.second);
-            }
+        for (const auto& e : exprs) {
+            const auto t = e.to_terms(challenges);
+            all.insert(all.end(), t.begin(), t.end());
+        }
+        Expression<F>::normalise_terms(all);
         VirtualPolynomials<F> vp;
         vp.num_vars = num_vars_;
         vp.mles = mles_;
