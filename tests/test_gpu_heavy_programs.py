@@ -45,10 +45,11 @@ def test_long_term_lists(dpb, ctx, F, k, n_terms, n):
 
 
 @pytest.mark.parametrize("F", FIELDS)
-@pytest.mark.parametrize("n_inst,m", [(16, 7), (40, 6), (12, 14)])
+@pytest.mark.parametrize("n_inst,m", [(16, 7), (40, 6), (12, 14), (12, 16)])
 def test_logup_batches_of_many_instances(dpb, ctx, prover, F, n_inst, m):
-    """(12, 14): the top layers start with split-eq rounds and pass to the spread rounds (the eq tables are
-    materialised on the way); (40, 6): more tables than the one-pass rounds take."""
+    """(12, 16): the top layers start with split-eq rounds (8192 pairs and more) and pass to the spread rounds, the
+    eq tables being materialised on the way; (12, 14): spread from the first round; (40, 6): more tables than the
+    one-pass rounds take."""
     rng = np.random.default_rng(8900 + n_inst)
     cols = [F.table_from_i64(rng.integers(0, 1 << 12, size=1 << m, dtype=np.int64)) for _ in range(2 * n_inst)]
     cst, sep = F.random_scalar(rng), F.random_scalar(rng)
