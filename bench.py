@@ -33,16 +33,18 @@ if ROOT not in sys.path:
 GL_MOD = 2**64 - 2**32 + 1
 FALLBACK_HBM_GBS = 6650.0
 
-# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per table entry of a
-# launch's input, from the ncu capture at 2^24 summarised in
-# profiles/sumcheck_goldilocks_product3_2p24_fused_rounds.md.  Traffic grows in
-# proportion to the entries processed, so a full launch is this figure times
-# its input entries.  Keyed by (field, profile label, round).
-NCU_TRAFFIC_BYTES_PER_INPUT_ENTRY = {
-    ("gl", "fused_eval0<base>", 0): (402.744064e6 + 6.582016e6) / (3 << 24),
-    ("gl", "fused_fold_eval<base>", 1): (402.845952e6 + 359.348736e6) / (3 << 24),
-    ("gl", "fused_fold_eval", 2): (402.789632e6 + 169.018880e6) / (3 << 23),
-}
+def load_ncu_traffic():
+    """DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per table entry of a launch's input, taken from an
+    ncu capture at a smaller size; traffic grows in proportion to the entries processed, so a full launch is the
+    figure times its input entries.  Keyed by (field, profile label of the kernel, round)."""
+    path = os.path.join(ROOT, "profiles", "ncu_dram_traffic.json")
+    try:
+        with open(path) as f:
+            rows = json.load(f)["kernels"]
+    except (OSError, ValueError, KeyError):
+        return {}
+    return {(r["field"], r["kernel"], r["round"]): (r["dram_read_bytes"] + r["dram_write_bytes"]) / r["input_entries"]
+            for r in rows}
 
 
 def alg_bytes(field, n, k=3):
@@ -144,9 +146,19 @@ def cpu_prove(orc, F, n, tabs):
     return orc.sumcheck_prove(F, n, tabs, {(0, 1, 2): F.one}, orc.Transcript(F))
 
 
-def cpu_baseline(field, n_sample, seed):
-    """The CPU restatement (oracle) of the same prover on the host cores."""
+def cpu_setup():
+    """The oracle tuned for this host's CPU and on every core this process may use (a launcher such as
+    torch.distributed.run exports OMP_NUM_THREADS=1, which would turn the baseline into one core)."""
     from oracle import oracle as orc
+    native = orc.use_native_build()
+    cores = orc.set_num_threads()
+    return orc, cores, native
+
+
+def cpu_baseline(field, n_sample, seed):
+    """The CPU restatement (oracle) of the same prover on the host cores.  Also returns the tables and the proof
+    of the sample, for the parity check of the GPU path."""
+    orc, cores, native = cpu_setup()
     F = orc.GlField if field == "gl" else orc.FrField
     if field != "gl":
         n_sample = min(n_sample, 22)  # BN254 on the host: 32-byte elements and a slower product
@@ -156,13 +168,14 @@ def cpu_baseline(field, n_sample, seed):
     # whole proofs, one after the other, until about ten seconds of CPU work have been timed
     reps, t0 = 0, time.perf_counter()
     while reps < 16 and (reps == 0 or time.perf_counter() - t0 < 10.0):
-        cpu_prove(orc, F, n_sample, tabs)
+        proof = cpu_prove(orc, F, n_sample, tabs)
         reps += 1
     dt = (time.perf_counter() - t0) / reps
-    return {"value": alg_bytes(field, n_sample) / dt / 1e9, "unit": "GB/s", "cores": orc.lib().orc_num_threads(),
-            "kind": "port", "seconds": dt * reps,
-            "sample": f"{reps} full proofs at 2^{n_sample} entries per table (same shape and field, smaller size), "
-                      "mean; C/OpenMP restatement of the prover, not the reference's Rust binary"}
+    rec = {"value": alg_bytes(field, n_sample) / dt / 1e9, "unit": "GB/s", "cores": cores,
+           "kind": "port", "seconds": dt * reps, "march_native": native,
+           "sample": f"{reps} full proofs at 2^{n_sample} entries per table (same shape and field, smaller size), "
+                     "mean; C/OpenMP restatement of the prover, not the reference's Rust binary"}
+    return rec, (F, n_sample, tabs, proof)
 
 
 def metric_name(field):
@@ -181,12 +194,18 @@ def workload_config(field, n, n_gpus):
 
 
 def run_reference(args):
+    """The reference arm: the CPU prover of the same workload on the host cores.  At one GPU each step is one full
+    proof at the workload's own size; at N GPUs the workload is 2^(n + log2 N) entries per table, and each step
+    proves the 2^n entries one GPU holds (a bounded sample, stated in cpu_baseline.sample; throughput in GB/s does
+    not depend on the size on the CPU)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    from oracle import oracle as orc
+    orc, cores, native = cpu_setup()
+    world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
+    n_global = args.log2_size + world.bit_length() - 1
     F = orc.GlField if args.field == "gl" else orc.FrField
-    n_s = args.cpu_sample_log2 if args.field == "gl" else min(args.cpu_sample_log2, 22)
+    n_s = min(args.log2_size, args.ref_max_log2 if args.field == "gl" else min(args.ref_max_log2, 24))
     rng = np.random.default_rng(args.seed)
     tabs = [F.random_table_fast(rng, 1 << n_s) for _ in range(3)]
     for _ in range(args.warmup):
@@ -196,19 +215,222 @@ def run_reference(args):
         cpu_prove(orc, F, n_s, tabs)
     dt = (time.perf_counter() - t0) / args.steps
     val = alg_bytes(args.field, n_s) / dt / 1e9
-    cores = orc.lib().orc_num_threads()
-    sample = (f"each step is one full proof at 2^{n_s} entries per table (bounded sample of the 2^{args.log2_size} "
-              "workload; throughput is size-independent on the CPU)")
+    if n_s == n_global:
+        sample = f"each step is one full proof of the workload (2^{n_s} entries per table)"
+    else:
+        sample = (f"each step is one full proof at 2^{n_s} entries per table, a bounded sample of the "
+                  f"2^{n_global} workload; GB/s does not depend on the size on the CPU")
     print(json.dumps({
         "impl": "reference", "metric": metric_name(args.field), "value": val, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "u64" if args.field == "gl" else "u256", "data": "synthetic",
-        "config": workload_config(args.field, args.log2_size, args.gpus),
-        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "config": workload_config(args.field, n_global, world),
+        "sample_log2_size": n_s,
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample,
+                         "march_native": native, "omp_num_threads_env": os.environ.get("OMP_NUM_THREADS")},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "the reference's Rust prover cannot be built here (no Rust toolchain, dp-crypto not vendored); "
                 "this is the C/OpenMP restatement in oracle/ on the host cores",
     }))
+
+
+def proof_scalars(orc, F, st):
+    """(rounds, point, final evaluations) of a proof from the library as the oracle's scalars."""
+    flat = lambda a: orc.array_to_scalars(F, np.asarray(a).reshape(-1, F.elem_words))
+    return flat(st.proof), flat(st.collect_raw_challenges()), flat(st.get_mle_flatten_final_evaluations())
+
+
+def parity_check(dpb, prover, ctx, field, case, world, rank, dist):
+    """Outside the timed region: the GPU path proves seeded tables the oracle has proved and the proofs must be
+    equal (rounds, point, final evaluations).  One GPU: the 2^26 sample of the CPU baseline.  Several GPUs: every
+    rank proves its shard of a 2^(22 + log2 N) sumcheck, all ranks' proofs must be equal and rank 0 compares them
+    with the oracle's proof of the whole tables."""
+    from oracle import oracle as orc
+    base_dtype = dpb.GL_BASE if field == "gl" else dpb.FR
+    fam = dpb.GL_EXT if field == "gl" else dpb.FR
+    terms = dpb.make_terms([(dpb.one_bytes(fam), [0, 1, 2])], bytes)
+    if world == 1:
+        F, n, tabs, want = case
+        mles = [ctx.upload(t, base_dtype) for t in tabs]
+        t = prover.Blake3Transcript(fam)
+        st = prover.IOPProverState.prove(ctx, n, mles, terms, t)
+        t.free()
+        for m in mles:
+            m.free()
+        got = proof_scalars(orc, F, st)
+        ok = got[0] == [e for r in want[0] for e in r] and got[1] == want[1] and got[2] == want[2]
+        return {"log2": n, "ok": bool(ok), "against": "oracle proof of the same seeded tables (rounds, point, finals)"}
+    F = orc.GlField if field == "gl" else orc.FrField
+    c = world.bit_length() - 1
+    n = 22 + c
+    rng = np.random.default_rng(12345)
+    tabs = [F.random_table_fast(rng, 1 << n) for _ in range(3)]
+    per = 1 << (n - c)
+    mles = [ctx.upload(np.ascontiguousarray(t[rank * per:(rank + 1) * per]), base_dtype) for t in tabs]
+    t = prover.Blake3Transcript(fam)
+    st = prover.IOPProverState.prove(ctx, n, mles, terms, t, sharded=True)
+    t.free()
+    for m in mles:
+        m.free()
+    got = proof_scalars(orc, F, st)
+    everyone = [None] * world
+    dist.all_gather_object(everyone, got)
+    if rank != 0:
+        return None
+    orc.set_num_threads()
+    want = cpu_prove(orc, F, n, tabs)
+    same = all(g == everyone[0] for g in everyone)
+    ok = same and got[0] == [e for r in want[0] for e in r] and got[1] == want[1] and got[2] == want[2]
+    return {"log2": n, "ok": bool(ok), "ranks_agree": bool(same),
+            "against": "oracle proof of the whole seeded tables; every rank's proof equal to rank 0's"}
+
+
+def device_random_fr(ctx, dpb, torch, n, seed, device):
+    """Three BN254 tables of 2^n entries made on the device (random limbs below the modulus, taken as Montgomery
+    residues): the BN254 record needs no host copy of its 6 GiB of inputs."""
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    keep, mles = [], []
+    for _ in range(3):
+        t = torch.randint(-2**63, 2**63 - 1, (1 << n, 4), dtype=torch.int64, device=device, generator=g)
+        t[:, 3] &= (1 << 60) - 1
+        keep.append(t)
+        mles.append(ctx.wrap_device(t.data_ptr(), dpb.FR, 1 << n))
+    torch.cuda.synchronize()
+    return keep, mles
+
+
+def bn254_record(dpb, prover, ctx, torch, stream, device, steps, n):
+    """The same f*g*h shape over BN254 Fr, the reference's own field: whole-proof GB/s, per-round kernels, and the
+    binding bound.  These rounds are bound by 32-bit multiply-add issue, not by HBM: the roofline entry compares
+    the field products per second of the top kernel with what dpb_issue_rate_probe measures on this GPU."""
+    keep, mles = device_random_fr(ctx, dpb, torch, n, 99, device)
+    terms = dpb.make_terms([(dpb.one_bytes(dpb.FR), [0, 1, 2])], bytes)
+
+    def step():
+        t = prover.Blake3Transcript(dpb.FR)
+        st = prover.IOPProverState.prove(ctx, n, mles, terms, t)
+        t.free()
+        return st
+
+    for _ in range(3):
+        step()
+    ctx.sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        step()
+    e1.record(stream)
+    ctx.sync()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    ctx.profile(True)
+    for _ in range(min(steps, 5)):
+        step()
+    ctx.sync()
+    ctx.profile(False)
+    prof = ctx.profile_read()
+    mul_rate, _ = ctx.issue_rate(ctx.PROBE_FR_MUL)
+    fixed_rate, _ = ctx.issue_rate(ctx.PROBE_FR_MUL_FIXED)
+    mad_rate, _ = ctx.issue_rate(ctx.PROBE_WIDE_MAD)
+    kernels = []
+    for e in sorted(prof, key=lambda e: e["round"])[:6]:
+        per_ms = e["total_ms"] / e["launches"]
+        pairs = 1 << (n - e["round"] - 1)
+        # round 0: samples at 0, 1, inf, -1 of a product of three = 8 products per pair;
+        # later rounds: 6 folds by the challenge (precomputed rows) + 3 samples x 2 products
+        floor_s = pairs * (8 / mul_rate if e["round"] == 0 else 6 / fixed_rate + 6 / mul_rate)
+        kernels.append({"kernel": e["kernel"], "round": e["round"], "ms_per_launch": per_ms,
+                        "GBps": e["alg_bytes_per_launch"] / (per_ms * 1e-3) / 1e9,
+                        "products_per_pair": 8 if e["round"] == 0 else 12,
+                        "frac_of_multiplier_floor": floor_s / (per_ms * 1e-3)})
+    top = max(kernels, key=lambda k: k["ms_per_launch"]) if kernels else None
+    peak, _ = load_peak()
+    rec = {"workload": f"f*g*h, 2^{n} entries per table, BN254 Fr (the reference's field), tables made on the device",
+           "log2_size": n, "value": alg_bytes("fr", n) / (ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms,
+           "steps": steps, "frac_of_hbm_peak": alg_bytes("fr", n) / (ms * 1e-3) / 1e9 / peak, "kernels": kernels,
+           "issue_rate_probe": {"fr_products_per_s": mul_rate, "fr_fixed_products_per_s": fixed_rate,
+                                "wide_multiply_adds_per_s": mad_rate}}
+    if top:
+        ach = (1 << (n - top["round"] - 1)) * top["products_per_pair"] / (top["ms_per_launch"] * 1e-3)
+        rec["roofline"] = {"bound": "imad", "kernel": top["kernel"], "round": top["round"],
+                           "achieved": ach, "unit": "field products/s",
+                           "peak": mul_rate if top["round"] == 0 else 12 / (6 / fixed_rate + 6 / mul_rate),
+                           "frac": top["frac_of_multiplier_floor"],
+                           "peak_source": "dpb_issue_rate_probe on this GPU (chains of the kernels' own product "
+                                          "routines on register operands)"}
+    for m in mles:
+        m.free()
+    del keep
+    torch.cuda.empty_cache()
+    return rec
+
+
+def strong_record(dpb, prover, ctx, torch, dist, stream, mles, terms, fam, n, world, rank, steps):
+    """Strong scaling of the fixed 2^n proof: all ranks prove ONE sumcheck of 2^n entries per table, each holding
+    2^(n - log2 N); rank 0 also proves a 2^n sumcheck alone in the same run, the N = 1 time of the ratio."""
+    c = world.bit_length() - 1
+    per = 1 << (n - c)
+    views = [m.view(0, per) for m in mles]
+
+    def timed(fn, reps):
+        for _ in range(2):
+            fn()
+        dist.barrier()
+        ctx.sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(reps):
+            fn()
+        e1.record(stream)
+        ctx.sync()
+        torch.cuda.synchronize()
+        tt = torch.tensor([e0.elapsed_time(e1) / reps], device="cuda")
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return float(tt.item())
+
+    def sharded():
+        t = prover.Blake3Transcript(fam)
+        prover.IOPProverState.prove(ctx, n, views, terms, t, sharded=True)
+        t.free()
+
+    ms_n = timed(sharded, steps)
+    ctx.profile(True)
+    for _ in range(3):
+        sharded()
+    ctx.sync()
+    ctx.profile(False)
+    prof = ctx.profile_read()
+    kernel_ms = sum(e["total_ms"] / 3 for e in prof)
+    ms_1 = None
+    if rank == 0:
+        def alone():
+            t = prover.Blake3Transcript(fam)
+            prover.IOPProverState.prove(ctx, n, mles, terms, t)
+            t.free()
+        for _ in range(2):
+            alone()
+        ctx.sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            alone()
+        e1.record(stream)
+        ctx.sync()
+        torch.cuda.synchronize()
+        ms_1 = e0.elapsed_time(e1) / steps
+    dist.barrier()
+    for v in views:
+        v.free()
+    if rank != 0:
+        return None
+    return {"workload": f"one f*g*h proof of 2^{n} entries per table over {world} GPUs (2^{n - c} per GPU)",
+            "ms_per_proof": ms_n, "ms_per_proof_one_gpu_same_run": ms_1, "speedup": ms_1 / ms_n,
+            "GBps": alg_bytes("gl" if fam == dpb.GL_EXT else "fr", n) / (ms_n * 1e-3) / 1e9,
+            "local_rounds": n - c, "exchanges_per_proof": n - c + 1,
+            "split_ms": {"round_kernels": kernel_ms, "exchange_launch_host": max(ms_n - kernel_ms, 0.0)},
+            "limiter": "per-round turn-around (launch, exchange of the partial sums between the hosts, transcript) "
+                       "of the local rounds plus the replicated last log2(N) rounds; the kernels scale with 1/N"}
 
 
 def run_ours(args):
@@ -224,11 +446,12 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
     field, n = args.field, args.log2_size
     base_dtype = dpb.GL_BASE if field == "gl" else dpb.FR
     fam = dpb.GL_EXT if field == "gl" else dpb.FR
     ctx = dpb.Context(local_rank)
-    stream = torch.cuda.ExternalStream(ctx.stream, device=torch.device("cuda", local_rank))
+    stream = torch.cuda.ExternalStream(ctx.stream, device=device)
 
     if world > 1:
         # the library's own communicator; torch.distributed only carries the 128-byte id
@@ -288,7 +511,7 @@ def run_ours(args):
     # per-kernel CUDA-event times: the same steps once more with the library's per-round events on
     # (they cost about 10 us per round, so they stay out of the timed region above)
     ctx.profile(True)
-    for _ in range(args.steps):
+    for _ in range(min(args.steps, 20)):
         st = step_device()
     barrier()
     ctx.profile(False)
@@ -302,22 +525,44 @@ def run_ours(args):
     prof = ctx.profile_read()
 
     # ---- end to end: host buffers in, proof out, copies inside the timed region
+    e2e_steps = min(args.steps, 20)
     for _ in range(min(args.warmup, 2)):
         step_e2e()
     barrier()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(e2e_steps):
         st = step_e2e()
     barrier()
-    e2e_s = (time.perf_counter() - t0) / args.steps
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
     words = 2 if field == "gl" else 4
     h2d = world * 3 * (1 << n) * (8 if field == "gl" else 32)
     d2h = (n_global * 4 + n_global + 3) * words * 8
 
+    strong = None
     if world > 1:
         tt = torch.tensor([e2e_s], device="cuda")
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         e2e_s = float(tt.item())
+        if not args.no_strong:
+            strong = strong_record(dpb, prover, ctx, torch, dist, stream, mles, terms, fam, n, world, rank,
+                                   min(args.steps, 20))
+    # ---- parity of the timed path against the oracle, outside the timed region
+    cpu_rec, case = None, None
+    if world == 1 and not args.no_cpu_baseline:
+        cpu_rec, case = cpu_baseline(field, args.cpu_sample_log2, args.seed)
+    parity = None
+    if case is not None or world > 1:
+        parity = parity_check(dpb, prover, ctx, field, case, world, rank, dist)
+    case = None
+    # ---- the same shape over BN254 (one GPU; the Goldilocks buffers are released first)
+    bn254 = None
+    if world == 1 and field == "gl" and not args.no_bn254:
+        for m in mles:
+            m.free()
+        mles = []
+        del pinned, host
+        bn254 = bn254_record(dpb, prover, ctx, torch, stream, device, min(args.steps, 10), args.bn254_log2)
+    if world > 1:
         ctx.comm_free()
         dist.barrier()
         dist.destroy_process_group()
@@ -330,7 +575,7 @@ def run_ours(args):
         per_launch_ms = top["total_ms"] / top["launches"]
         ach = top["alg_bytes_per_launch"] / (per_launch_ms * 1e-3) / 1e9
         traffic = None
-        per_entry = NCU_TRAFFIC_BYTES_PER_INPUT_ENTRY.get((field, top["kernel"], top["round"]))
+        per_entry = load_ncu_traffic().get((field, top["kernel"], top["round"]))
         if per_entry is not None:
             traffic = per_entry * 3 * (1 << (n - max(top["round"] - 1, 0)))
         roofline = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
@@ -350,28 +595,40 @@ def run_ours(args):
         "roofline": roofline,
         "kernels": kernels,
         "e2e": {"value": alg_bytes(field, n_global) / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3},
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3, "steps": e2e_steps},
         # counted by the library on rank 0 over the timed steps (every rank launches the same kernels): one
         # launch per large round, one resident kernel for the last rounds and the final evaluations
         "gpu_launches": launches * world,
         "clocks": clocks,
+        "parity_checked": parity,
     }
-    if world == 1 and not args.no_cpu_baseline:
-        out["cpu_baseline"] = cpu_baseline(field, args.cpu_sample_log2, args.seed)
+    if cpu_rec is not None:
+        out["cpu_baseline"] = cpu_rec
+    if bn254 is not None:
+        out["bn254"] = bn254
+    if strong is not None:
+        out["strong"] = strong
     print(json.dumps(out))
+    if parity is not None and not parity["ok"]:
+        sys.exit("parity check failed: the GPU proof differs from the oracle's")
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--log2-size", type=int, default=28)
     ap.add_argument("--field", default="gl", choices=["gl", "fr"])
     ap.add_argument("--cpu-sample-log2", type=int, default=26)
+    ap.add_argument("--ref-max-log2", type=int, default=28,
+                    help="largest table the reference arm proves per step (it proves min(log2-size, this))")
+    ap.add_argument("--bn254-log2", type=int, default=26)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-bn254", action="store_true")
+    ap.add_argument("--no-strong", action="store_true")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

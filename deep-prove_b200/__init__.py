@@ -55,6 +55,7 @@ SIGNATURES = {
     "dpb_comm_shared_exchange": (_int, [_vp]),
     "dpb_resident_rounds": (_int, [_vp, _int, _u32]),
     "dpb_sumcheck_launches": (_u64, [_vp]),
+    "dpb_issue_rate_probe": (_int, [_vp, _int, _u32, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)]),
     "dpb_profile_enable": (_int, [_vp, _int]),
     "dpb_profile_read": (_int, [_vp, ctypes.POINTER(ProfileEntry), _u32, ctypes.POINTER(_u32)]),
     "dpb_init": (_int, [_int, _pp]),
@@ -201,6 +202,14 @@ class Context:
 
     def sumcheck_launches(self):
         return int(lib.dpb_sumcheck_launches(self.h))
+
+    PROBE_WIDE_MAD, PROBE_FR_MUL, PROBE_FR_MUL_FIXED, PROBE_GL_MAC, PROBE_GL_MUL = range(5)
+
+    def issue_rate(self, kind, iters=4096):
+        """dpb_issue_rate_probe: (operations per second, milliseconds of the timed launch)."""
+        ops, ms = ctypes.c_double(), ctypes.c_double()
+        check(lib.dpb_issue_rate_probe(self.h, kind, iters, ctypes.byref(ops), ctypes.byref(ms)))
+        return ops.value, ms.value
 
     def profile(self, on):
         check(lib.dpb_profile_enable(self.h, 1 if on else 0))

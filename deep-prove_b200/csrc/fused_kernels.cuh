@@ -1,15 +1,13 @@
-// Fused sumcheck rounds for the shape that dominates the byte count: a single
-// product term  f_1 * f_2 * ... * f_K  (coefficient one) over K tables that all
-// have every variable of the sumcheck and share one storage layout.  This is
-// the f*g*h microbenchmark shape and the v1*v2*eq shape of the Hadamard
-// prover (zkml/src/layers/hadamard.rs:106-115).
+// The product shape of a sumcheck: a single term  f_1 * f_2 * ... * f_K
+// (coefficient one) over K tables that all have every variable of the
+// sumcheck and share one storage layout.  This is the f*g*h microbenchmark
+// shape and the v1*v2*eq shape of the Hadamard prover
+// (zkml/src/layers/hadamard.rs:106-115).
 //
-// Round 0 only evaluates.  Every later round reads the previous tables ONCE,
-// binds the previous variable with the challenge, writes the half-size tables
-// and evaluates the new round polynomial from the values it still holds in
-// registers — the minimum traffic a sumcheck with host-side challenges allows:
-// per table 2*s0 + 2*s1 bytes per entry of the input (s0, s1 = entry size
-// before / after the first fold).
+// This header holds the shape detection the sumcheck entry points use and the
+// plain first-round kernel (one thread per pair, evaluations at 0..=K) that the
+// allocation-free entry point launches; the rounds of an ordinary sumcheck of
+// this shape run the sampled kernels of fused_v2.cuh / fused_v4.cuh.
 #pragma once
 #include <functional>
 #include <type_traits>
@@ -30,18 +28,9 @@ struct FusedIn;
 template <>
 struct FusedIn<GlFam, true> {
     typedef uint64_t T;
-    __device__ __forceinline__ static void load4(const void* p, uint64_t q, T (&a)[4]) {
-        const ulonglong2* s = (const ulonglong2*)p + 2 * q;
-        const ulonglong2 u = s[0], v = s[1];
-        a[0] = u.x; a[1] = u.y; a[2] = v.x; a[3] = v.y;
-    }
     __device__ __forceinline__ static void load2(const void* p, uint64_t q, T (&a)[2]) {
         const ulonglong2 u = ((const ulonglong2*)p)[q];
         a[0] = u.x; a[1] = u.y;
-    }
-    __device__ __forceinline__ static Gl2 fold(T a0, T a1, const Gl2& r) {
-        const uint64_t d = gl_sub(a1, a0);
-        return gl2_make(gl_add(a0, gl_mul(r.c0, d)), gl_mul(r.c1, d));
     }
     __device__ __forceinline__ static T add(T a, T b) { return gl_add(a, b); }
     __device__ __forceinline__ static T sub(T a, T b) { return gl_sub(a, b); }
@@ -53,16 +42,9 @@ struct FusedIn<GlFam, true> {
 template <class F>
 struct FusedIn<F, false> {
     typedef typename F::E T;
-    __device__ __forceinline__ static void load4(const void* p, uint64_t q, T (&a)[4]) {
-#pragma unroll
-        for (int i = 0; i < 4; i++) a[i] = F::load(p, F::kChalDtype, 4 * q + i);
-    }
     __device__ __forceinline__ static void load2(const void* p, uint64_t q, T (&a)[2]) {
         a[0] = F::load(p, F::kChalDtype, 2 * q);
         a[1] = F::load(p, F::kChalDtype, 2 * q + 1);
-    }
-    __device__ __forceinline__ static T fold(const T& a0, const T& a1, const T& r) {
-        return F::add(a0, F::mul(r, F::sub(a1, a0)));
     }
     __device__ __forceinline__ static T add(const T& a, const T& b) { return F::add(a, b); }
     __device__ __forceinline__ static T sub(const T& a, const T& b) { return F::sub(a, b); }
@@ -114,48 +96,6 @@ __global__ void __launch_bounds__(kThreads)
 #pragma unroll
     for (int x = 0; x <= K; x++) wide[x] = In::widen(acc[x]);
     grid_sum_publish<F, K + 1>(wide, rs, out);
-}
-
-// Rounds >= 1: bind the previous variable with r, write the folded tables,
-// evaluate the new round polynomial.  One thread per OUTPUT pair: it reads
-// entries 4p..4p+3 of every input table and writes entries 2p, 2p+1.
-template <class F, int K, bool BASE_IN>
-__global__ void __launch_bounds__(kThreads)
-    fused_product_fold_eval(FusedPtrs<K> ptrs, typename F::E r, uint64_t n_pairs,
-                            ReduceScratch<F> rs, typename F::E* out) {
-    typedef FusedIn<F, BASE_IN> In;
-    typedef typename In::T T;
-    typedef typename F::E E;
-    E acc[K + 1];
-#pragma unroll
-    for (int x = 0; x <= K; x++) acc[x] = F::zero();
-    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
-    for (uint64_t p = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; p < n_pairs; p += stride) {
-        E val[K], delta[K];
-#pragma unroll
-        for (int j = 0; j < K; j++) {
-            T a[4];
-            In::load4(ptrs.in[j], p, a);
-            const E f0 = In::fold(a[0], a[1], r);
-            const E f1 = In::fold(a[2], a[3], r);
-            F::store(ptrs.out[j], 2 * p, f0);
-            F::store(ptrs.out[j], 2 * p + 1, f1);
-            val[j] = f0;
-            delta[j] = F::sub(f1, f0);
-        }
-#pragma unroll
-        for (int x = 0; x <= K; x++) {
-            E prod = val[0];
-#pragma unroll
-            for (int j = 1; j < K; j++) prod = F::mul(prod, val[j]);
-            acc[x] = F::add(acc[x], prod);
-            if (x < K) {
-#pragma unroll
-                for (int j = 0; j < K; j++) val[j] = F::add(val[j], delta[j]);
-            }
-        }
-    }
-    grid_sum_publish<F, K + 1>(acc, rs, out);
 }
 
 // ---- host side ---------------------------------------------------------------

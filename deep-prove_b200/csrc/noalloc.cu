@@ -99,6 +99,11 @@ extern "C" int dpb_product_round_noalloc(void* cuda_stream, int dtype, const voi
     void* scratch = nullptr;
     DPB_TRY(noalloc_scratch_for(device, &scratch));
     cudaStream_t s = (cudaStream_t)cuda_stream;
+    // the scratch array is per device: a stream of another GPU would run the kernel there with this GPU's address
+    int stream_device = device;
+    DPB_CUDA(cudaStreamGetDevice(s, &stream_device));
+    if (stream_device != device)
+        return fail(DPB_EINVAL, "the stream belongs to device %d but device %d is current", stream_device, device);
     // the ticket counter must start at zero even if an earlier call was cut short
     DPB_CUDA(cudaMemsetAsync((char*)scratch + kNoallocCounterOffset, 0, 256, s));
     const uint64_t n_pairs = len / 2;

@@ -122,6 +122,16 @@ int dpb_profile_enable(dpb_ctx* ctx, int on);
 /* Copies at most cap entries; *n is the number available. */
 int dpb_profile_read(dpb_ctx* ctx, dpb_profile_entry* out, uint32_t cap, uint32_t* n);
 
+/* Issue-rate probe: runs chains of one arithmetic primitive of the round
+ * kernels on register operands on every SM and reports how many of them the
+ * device completes per second -- the ceiling a kernel bound by the integer
+ * pipes (every BN254 round) is measured against.  kind: 0 = 32x32->64
+ * multiply-add with 64-bit addend, 1 = BN254 Montgomery product, 2 = BN254
+ * product by a per-launch constant (the fold's challenge), 3 = Goldilocks
+ * lazy multiply-accumulate, 4 = Goldilocks product with reduction.  iters =
+ * chain length per thread (1..2^20).  No reference counterpart. */
+int dpb_issue_rate_probe(dpb_ctx* ctx, int kind, uint32_t iters, double* ops_per_second, double* elapsed_ms);
+
 /* The last rounds of a sumcheck (a few hundred pairs or fewer) run in one
  * resident kernel that exchanges round sums and challenges with the host
  * through mapped memory instead of one launch per round.  enable = 0 turns
@@ -272,6 +282,9 @@ void dpb_sumcheck_free(dpb_sc* sc);
  *  - All calls on a device share the scratch array.  Each call zeroes the part
  *    that must start at zero, but two calls whose kernels can overlap on the
  *    GPU (different streams, no ordering between them) race on it: order them.
+ *  - `cuda_stream` must belong to the device that is current when the call is
+ *    made (the scratch array is per device); a stream of another device is
+ *    rejected with DPB_EINVAL.
  *  - It calls no cudaMalloc / cudaFree and no allocating library routine. */
 int dpb_product_round_noalloc(void* cuda_stream, int dtype, const void* const* tables_dev, uint32_t k,
                               uint64_t len, void* out_evals_dev);

@@ -4,10 +4,11 @@ batched logup-GKR prover, einsum axis fixing and the generic (term-list)
 sumcheck.  Prints one line per measurement with the algorithmic bytes it is
 divided by, so each figure can be read against the HBM peak.
 
-    python deep-prove_b200/microbench.py [--field fr|gl] [--log2 22] [--reps 5]
-    python deep-prove_b200/microbench.py --lookup [--field ..] [--log2 ..]   only the lookup witness lines
-    python deep-prove_b200/microbench.py --mlp          one dense + ReLU layer of the MLP configuration, per step
-    python deep-prove_b200/microbench.py --latency      small sumchecks, one C call per proof, both fields,
+    python microbench.py [--field fr|gl] [--log2 22] [--reps 5]
+    python microbench.py --lookup [--field ..] [--log2 ..]   only the lookup witness lines
+    python microbench.py --mlp          one dense + ReLU layer of the MLP configuration, per step
+    python microbench.py --issue-rate   field products per second the integer pipes deliver (dpb_issue_rate_probe)
+    python microbench.py --latency      small sumchecks, one C call per proof, both fields,
                                                         with the resident last-rounds kernel and with one launch per round
 """
 import argparse
@@ -25,8 +26,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 def load():
     name = "deep_prove_b200"
     if name not in sys.modules:
-        spec = importlib.util.spec_from_file_location(name, os.path.join(HERE, "__init__.py"),
-                                                      submodule_search_locations=[HERE])
+        pkg = os.path.join(HERE, "deep-prove_b200")
+        spec = importlib.util.spec_from_file_location(name, os.path.join(pkg, "__init__.py"),
+                                                      submodule_search_locations=[pkg])
         mod = importlib.util.module_from_spec(spec)
         sys.modules[name] = mod
         spec.loader.exec_module(mod)
@@ -44,6 +46,30 @@ def timed(ctx, fn, reps):
         best = min(best, time.perf_counter() - t0)
         del r
     return best
+
+
+def issue_rate(dpb, ctx):
+    """The probes of csrc/issue_rate.cu: chains of the round kernels' own product routines on register operands.
+    Cycles are per warp instruction stream per SM sub-partition at the SM clock read from nvidia-smi."""
+    import subprocess
+    try:
+        mhz = float(subprocess.run(["nvidia-smi", "-i", "0", "--query-gpu=clocks.max.sm", "--format=csv,noheader,nounits"],
+                                   capture_output=True, text=True).stdout.split()[0])
+    except (OSError, IndexError, ValueError):
+        mhz = 1965.0
+    sms = 148
+    names = ["32x32->64 multiply-add (64-bit addend, carry)", "BN254 Montgomery product (frw::mul)",
+             "BN254 product by a per-launch constant (frw::mul_fixed)", "Goldilocks lazy multiply-accumulate (glw::acc_mac)",
+             "Goldilocks product with reduction (glw::mul)"]
+    print(f"# issue-rate probes, {sms} SMs x 4 sub-partitions, cycles at the maximum SM clock {mhz:.0f} MHz")
+    print("# (a lower bound on cycles when the clock under load is lower; each probe: 4 blocks of 256 threads per SM)")
+    for kind, name in enumerate(names):
+        best = 0.0
+        for _ in range(3):
+            ops, ms = ctx.issue_rate(kind, 8192)
+            best = max(best, ops)
+        cyc = sms * 4 * mhz * 1e6 / (best / 32)
+        print(f"{name:58s} {best / 1e9:10.2f} G/s   {cyc:8.1f} cycles per warp-wide operation per sub-partition")
 
 
 def latency(dpb, prover, ctx):
@@ -247,11 +273,16 @@ def main():
     ap.add_argument("--log2", type=int, default=22)
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--latency", action="store_true")
+    ap.add_argument("--issue-rate", action="store_true", help="the integer pipes' product rates (dpb_issue_rate_probe)")
     ap.add_argument("--lookup", action="store_true", help="only the lookup witness lines")
     ap.add_argument("--mlp", action="store_true", help="the steps of one dense + ReLU layer of the MLP configuration")
     args = ap.parse_args()
     dpb, prover = load()
     ctx = dpb.Context(0)
+    if args.issue_rate:
+        issue_rate(dpb, ctx)
+        ctx.close()
+        return
     if args.latency:
         latency(dpb, prover, ctx)
         ctx.close()

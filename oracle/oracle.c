@@ -425,3 +425,12 @@ int orc_num_threads(void) {
 #endif
     return n;
 }
+/* Number of OpenMP threads later parallel regions use (a launcher may have exported OMP_NUM_THREADS=1). */
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    extern void omp_set_num_threads(int);
+    if (n >= 1) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}

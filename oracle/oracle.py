@@ -34,14 +34,35 @@ GL_MOD = 2**64 - 2**32 + 1
 GL_NONRES = 7
 
 
-def build(force=False):
-    """Compiles oracle.c into oracle/_build/liboracle.so with gcc."""
+def _cpu_tag():
+    """Short tag of this host's instruction-set flags: a library tuned for one CPU is never loaded on another."""
+    import hashlib
+    flags = ""
+    try:
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.startswith("flags"):
+                    flags = line
+                    break
+    except OSError:
+        pass
+    return hashlib.sha1(flags.encode()).hexdigest()[:10]
+
+
+def build(force=False, native=False):
+    """Compiles oracle.c into oracle/_build/liboracle.so with gcc.  native=True builds a second library tuned for
+    the CPU it is compiled on (-march=native), named after that CPU's flag set; it is what the timed CPU baseline
+    uses, and it is compiled on the host that runs it."""
     src = os.path.join(HERE, "oracle.c")
-    if not force and os.path.exists(LIB_PATH) and os.path.getmtime(LIB_PATH) >= os.path.getmtime(src):
-        return LIB_PATH
-    os.makedirs(os.path.dirname(LIB_PATH), exist_ok=True)
-    subprocess.run(["gcc", "-O3", "-fopenmp", "-shared", "-fPIC", "-o", LIB_PATH, src], check=True)
-    return LIB_PATH
+    path = os.path.join(HERE, "_build", f"liboracle_native_{_cpu_tag()}.so") if native else LIB_PATH
+    if not force and os.path.exists(path) and os.path.getmtime(path) >= os.path.getmtime(src):
+        return path
+    os.makedirs(os.path.dirname(path), exist_ok=True)
+    flags = ["-O3", "-fopenmp", "-shared", "-fPIC"] + (["-march=native"] if native else [])
+    tmp = f"{path}.{os.getpid()}.tmp"
+    subprocess.run(["gcc", *flags, "-o", tmp, src], check=True)
+    os.replace(tmp, path)
+    return path
 
 
 _lib = None
@@ -50,9 +71,27 @@ _lib = None
 def lib():
     global _lib
     if _lib is None:
-        build()
-        _lib = ctypes.CDLL(LIB_PATH)
+        _lib = ctypes.CDLL(build())
     return _lib
+
+
+def use_native_build():
+    """Switches this process to the -march=native library (timed CPU baseline); falls back to the portable one
+    when the compiler is missing.  Returns True when the native library is in use."""
+    global _lib
+    try:
+        _lib = ctypes.CDLL(build(native=True))
+        return True
+    except (OSError, subprocess.CalledProcessError):
+        return False
+
+
+def set_num_threads(n=None):
+    """OpenMP threads of the C routines; default: every core this process may run on."""
+    if n is None:
+        n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().orc_set_num_threads(int(n))
+    return lib().orc_num_threads()
 
 
 class OrcTerm(ctypes.Structure):

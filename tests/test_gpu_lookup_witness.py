@@ -143,13 +143,14 @@ def test_two_value_chunks_and_device_tensor(dpb, ctx, F):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("F", FIELDS)
-def test_large_tensor_with_constant_chunks(dpb, ctx, F):
-    """2^20 entries whose zeroing chunks are all equal (the usual case: values far below the declared maximum),
+@pytest.mark.parametrize("side", [10, 11])
+def test_large_tensor_with_constant_chunks(dpb, ctx, F, side):
+    """2^20 and 2^22 entries whose zeroing chunks are all equal (the usual case: values far below the declared maximum),
     which is the case the block-local counters are for."""
     rng = np.random.default_rng(9800)
     bits, right_shift, max_bit_size = 12, 16, 60
     sign, table_out, n_cols = value_table("relu", bits)
-    t = rng.integers(-(1 << 20), 1 << 20, size=(1 << 10, 1 << 10), dtype=np.int64)
+    t = rng.integers(-(1 << 20), 1 << 20, size=(1 << side, 1 << side), dtype=np.int64)
     want_ci = orc.ChunkingInfo(right_shift, bits, sign, max_bit_size)
     want = orc.LookupOpWitness(want_ci, 1 << 5, 0, t, table_out, n_cols)
     ci = dpb.ChunkingInfo.new(right_shift, bits, sign, max_bit_size)

@@ -114,6 +114,43 @@ def test_product_sumcheck(dpb, ctx, F, n, k):
             m.free()
 
 
+@pytest.mark.parametrize("F,n,k", [(orc.GlField, 20, 2), (orc.GlField, 20, 3), (orc.GlField, 20, 4),
+                                   (orc.GlField, 21, 3), (orc.GlField, 22, 3), (orc.FrField, 20, 2),
+                                   (orc.FrField, 20, 3), (orc.FrField, 20, 4)])
+def test_product_sumcheck_large(dpb, ctx, F, n, k):
+    """The sizes at which the launcher picks the staged kernels (a launch with at least two items per thread of a
+    full grid, i.e. 2^20 entries and up on a 148-SM part): round 0 over base or extension tables, round 1 with base
+    or extension input, later rounds staged until they become too small, then the unstaged kernels and the resident
+    one.  Every round message, the point and the final evaluations against the oracle."""
+    rng = np.random.default_rng(7000 + 10 * n + k)
+    for ext in ([False, True] if F is orc.GlField else [False]):
+        tabs = product_case(F, rng, n, k, ext)
+        terms = {tuple(range(k)): F.one}
+        want = orc.sumcheck_prove(F, n, tabs, terms, orc.Transcript(F))
+        mles = [upload(dpb, ctx, F, t) for t in tabs]
+        got = gpu_sumcheck_prove(dpb, ctx, F, n, mles, terms, orc.Transcript(F))
+        assert got[0] == want[0]
+        assert got[1:] == want[1:]
+        for m, t in zip(mles, tabs):
+            assert (m.to_host() == t).all()
+            m.free()
+
+
+@pytest.mark.parametrize("F", FIELDS)
+@pytest.mark.parametrize("k", [1, 10, 22])
+def test_fix_high_low_large(dpb, ctx, F, k):
+    """2^22 entries: several passes of up to five variables, grids larger than one wave."""
+    n = 22
+    rng = np.random.default_rng(7100 + k)
+    t = F.random_table_fast(rng, 1 << n)
+    pt = [F.random_scalar(rng) for _ in range(k)]
+    m = upload(dpb, ctx, F, t)
+    pa = orc.scalars_to_array(F, pt)
+    assert (ctx.fix_high(m, pa).to_host() == orc.fix_high_variables(F, t, pt)).all()
+    assert (ctx.fix_low(m, pa).to_host() == orc.fix_low_variables(F, t, pt)).all()
+    m.free()
+
+
 @pytest.mark.parametrize("F", FIELDS)
 def test_product_sumcheck_golden(dpb, ctx, F):
     g = make_golden.golden_inputs(F, "prod3")
