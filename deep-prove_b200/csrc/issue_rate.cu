@@ -27,19 +27,23 @@ __device__ __forceinline__ uint32_t probe_seed(uint32_t salt) {
     return x;
 }
 
-// kind 0: dependent 32x32->64 multiply-adds with a 64-bit addend (eight chains per thread)
+// kind 0: 32x32->64 multiply-adds into a 64-bit accumulator (mad.lo.cc + madc.hi on one aligned word pair, the
+// form every product routine here is built from); eight independent accumulators per thread
 __global__ void __launch_bounds__(kProbeThreads) probe_wide_mad(uint32_t iters, uint32_t* out) {
-    uint32_t lo[8], hi[8];
+    uint32_t lo[8], hi[8], a[8];
     const uint32_t m = probe_seed(7) | 1u;
 #pragma unroll
     for (int c = 0; c < 8; c++) {
         lo[c] = probe_seed(c);
         hi[c] = probe_seed(c + 8);
+        a[c] = probe_seed(c + 16);
     }
     for (uint32_t it = 0; it < iters; it++) {
 #pragma unroll
         for (int c = 0; c < 8; c++)
-            asm volatile("mad.lo.cc.u32 %0, %0, %2, %1; madc.hi.u32 %1, %0, %2, %1;" : "+r"(lo[c]), "+r"(hi[c]) : "r"(m));
+            asm volatile("mad.lo.cc.u32 %0, %2, %3, %0; madc.hi.u32 %1, %2, %3, %1;"
+                         : "+r"(lo[c]), "+r"(hi[c])
+                         : "r"(a[c]), "r"(m));
     }
     uint32_t x = 0;
 #pragma unroll
