@@ -97,6 +97,7 @@ SIGNATURES = {
     "dpb_lookup_counts_to_host": (_int, [_vp, _vp, _u64]),
     "dpb_lookup_counts_free": (None, [_vp]),
     "dpb_lookup_multiplicities": (_int, [_vp, _vp, _int, _pp]),
+    "dpb_lookup_counts_add_rows": (_int, [_vp, _vp, _vp, _int, _u64]),
     "dpb_lookup_witness": (_int, [_vp, _int, _vp, ctypes.c_int64, ctypes.c_int64, _vp, _int, _vp, _u32, _vp, _int, _u32,
                                   _vp, _vp, _vp, _vp, _pp, _pp, _u32, ctypes.POINTER(_u32), _pp, _u32, ctypes.POINTER(_u32)]),
     "dpb_comm_unique_id": (_int, [_vp]),
@@ -349,6 +350,11 @@ class LookupCounts:
         out = np.empty(1 << self.bits, dtype=np.uint64)
         check(lib.dpb_lookup_counts_to_host(self.h, _buf(out), out.size))
         return out
+
+    def add_rows(self, rows):
+        """dpb_lookup_counts_add_rows: rows is an int64 array of row indices (host memory)."""
+        r = np.ascontiguousarray(rows, dtype=np.int64)
+        check(lib.dpb_lookup_counts_add_rows(self.ctx.h, self.h, _buf(r), 0, r.size))
 
     def multiplicities(self, family_dtype):
         h = ctypes.c_void_p()

@@ -227,6 +227,66 @@ extern "C" void dpb_lookup_counts_free(dpb_lookup_counts* c) {
     delete c;
 }
 
+namespace dpb {
+
+// counters[rows[i]] += 1 for i < n; equal rows of a warp are merged into one atomic
+__global__ void __launch_bounds__(kThreads)
+    lookup_count_rows_kernel(const int64_t* rows, uint64_t n, uint64_t n_rows, unsigned long long* counters,
+                             unsigned int* bad) {
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    // whole warps iterate together so that the match below sees every lane of the warp
+    const uint64_t n_up = (n + 31) & ~(uint64_t)31;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_up; i += stride) {
+        const bool live = i < n;
+        const int64_t r = live ? rows[i] : -1;
+        const bool ok = live && r >= 0 && (uint64_t)r < n_rows;
+        if (live && !ok) atomicAdd(bad, 1u);
+        const unsigned long long key = ok ? (unsigned long long)r : ~0ull;
+        const unsigned peers = __match_any_sync(0xffffffffu, key);
+        if (ok && (unsigned)(__ffs(peers) - 1) == (threadIdx.x & 31u))
+            atomicAdd(&counters[r], (unsigned long long)__popc(peers));
+    }
+}
+
+}  // namespace dpb
+
+extern "C" int dpb_lookup_counts_add_rows(dpb_ctx* ctx, dpb_lookup_counts* c, const int64_t* rows, int rows_on_device,
+                                          uint64_t n) {
+    if (!ctx || !c || (!rows && n)) return fail(DPB_EINVAL, "null argument");
+    if (c->ctx != ctx) return fail(DPB_EINVAL, "the counters belong to another context");
+    if (n == 0) return DPB_OK;
+    const int64_t* dev = rows;
+    void* tmp = nullptr;
+    if (!rows_on_device) {
+        DPB_TRY(device_alloc(ctx, n * sizeof(int64_t), &tmp));
+        cudaError_t e = cudaMemcpyAsync(tmp, rows, n * sizeof(int64_t), cudaMemcpyHostToDevice, ctx->stream);
+        if (e != cudaSuccess) {
+            device_free(ctx, tmp);
+            return fail(DPB_ECUDA, "copying rows: %s", cudaGetErrorString(e));
+        }
+        dev = (const int64_t*)tmp;
+    }
+    unsigned int* bad = nullptr;
+    int rc = device_alloc(ctx, sizeof(unsigned int), (void**)&bad);
+    if (rc != DPB_OK) {
+        device_free(ctx, tmp);
+        return rc;
+    }
+    unsigned int h_bad = 0;
+    cudaError_t e = cudaMemsetAsync(bad, 0, sizeof(unsigned int), ctx->stream);
+    if (e == cudaSuccess) {
+        lookup_count_rows_kernel<<<grid_for(ctx, n), kThreads, 0, ctx->stream>>>(dev, n, 1ull << c->bits, c->dev, bad);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&h_bad, bad, sizeof(unsigned int), cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    device_free(ctx, bad);
+    device_free(ctx, tmp);
+    if (e != cudaSuccess) return fail(DPB_ECUDA, "counting rows: %s", cudaGetErrorString(e));
+    if (h_bad) return fail(DPB_EINVAL, "%u rows lie outside the table's 2^%u rows (they were not counted)", h_bad, c->bits);
+    return DPB_OK;
+}
+
 extern "C" int dpb_lookup_multiplicities(dpb_ctx* ctx, const dpb_lookup_counts* c, int family_dtype, dpb_mle** out) {
     if (!ctx || !c || !out) return fail(DPB_EINVAL, "null argument");
     if (!valid_dtype(family_dtype)) return fail(DPB_EINVAL, "unknown dtype %d", family_dtype);

@@ -349,6 +349,14 @@ typedef struct dpb_lookup_counts dpb_lookup_counts;
 int dpb_lookup_counts_new(dpb_ctx* ctx, uint32_t table_bits, dpb_lookup_counts** out);
 int dpb_lookup_counts_to_host(const dpb_lookup_counts* counts, uint64_t* out, uint64_t len);
 void dpb_lookup_counts_free(dpb_lookup_counts* counts);
+/* Adds one to counter rows[i] for every i < n: lookups that need no decomposition, such as the
+ * 16-bit range-check chunks of the logits layer, which go straight into the shift-check table
+ * (Logits::build_lookup_input, zkml/src/layers/transformer/logits.rs:300-345).  `rows` are row
+ * indices (input - min_input), in host memory or (rows_on_device != 0) device memory.  A row
+ * outside the table is not counted and the call returns DPB_EINVAL. */
+int dpb_lookup_counts_add_rows(dpb_ctx* ctx, dpb_lookup_counts* counts, const int64_t* rows, int rows_on_device,
+                               uint64_t n);
+
 /* The table's multiplicity polynomial (context.rs:313-371): row i holds its count as a field
  * element.  The rows of the reference's tables are distinct (the input column is a range), so
  * the division by a row's number of copies (context.rs:349-357) never applies. */

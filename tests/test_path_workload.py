@@ -1,0 +1,90 @@
+"""The transformer path workload (deep-prove_b200/workloads.py): the same walk of sumcheck / fold / logup-GKR calls
+on the CPU restatement (oracle/path_backend.py) and on the GPU library, compared call by call.
+
+CPU part: the walk itself (call list, shapes, determinism) on the oracle backend.  GPU part: every call's payload
+(round messages, points, final evaluations, logup proofs, batching challenges) and the transcript's final state are
+equal between the two backends, for BN254 and for Goldilocks, at a reduced shape with every call of the full
+graph: embeddings, positions, one block (two normalisations, QKV / QK^T / AV / output / FFN einsums with stacked
+heads, attention mask, softmax, GELU, three requantisations, two claim merges), final normalisation, LM head,
+argmax range check and linking, the tables' logup proof and the claim batching over every committed polynomial."""
+import importlib
+
+import pytest
+
+from oracle.path_backend import OracleBackend
+
+
+@pytest.fixture(scope="module")
+def wl(dpb):
+    return importlib.import_module("deep_prove_b200.workloads")
+
+
+def load_workloads_without_gpu():
+    """The walk is plain Python over a backend; it loads without the CUDA library."""
+    import importlib.util
+    import os
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    name = "_dpb_workloads_cpu"
+    if name in sys.modules:
+        return sys.modules[name]
+    spec = importlib.util.spec_from_file_location(name, os.path.join(root, "deep-prove_b200", "workloads.py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+EXPECTED_KINDS = {"einsum": 7, "logup": 10, "linking": 8, "same_poly": 2, "attention_mask": 1, "embeddings": 1,
+                  "positional": 1, "argmax_linking": 1, "claim_batching": 1, "state": 1}
+
+
+def test_walk_on_the_cpu_backend_is_complete_and_deterministic():
+    wl = load_workloads_without_gpu()
+    a, timer = wl.transformer_path(OracleBackend("fr"), wl.TINY, seed=3)
+    b, _ = wl.transformer_path(OracleBackend("fr"), wl.TINY, seed=3)
+    assert a == b
+    kinds = {}
+    for _, kind, payload in a:
+        kinds[kind] = kinds.get(kind, 0) + 1
+        assert isinstance(payload, bytes) and len(payload) > 0
+    assert kinds == EXPECTED_KINDS
+    c, _ = wl.transformer_path(OracleBackend("fr"), wl.TINY, seed=4)
+    assert [r[0] for r in c] == [r[0] for r in a] and c != a
+    # every kind of call was timed
+    assert {"einsum_fix_axes", "einsum_sumcheck", "lookup_witness", "lookup_logup", "lookup_linking", "same_poly",
+            "attention_mask", "embeddings", "positional", "argmax_logup", "argmax_linking", "tables_logup",
+            "claim_batching"} == set(timer.by_kind)
+
+
+def test_gpt2_shape_call_sizes():
+    """The sizes BASELINE's GPT-2 configuration gives the calls (hot-path table of the survey): contraction over
+    768 -> 10 variables, 3072 -> 12, head dimension 64 -> 6, sequence 512 -> 9; softmax slices of 2^18, GELU 2^21,
+    normalisation 2^19, logits 2^25, embeddings 2^26."""
+    wl = load_workloads_without_gpu()
+    g = wl.GPT2_SMALL
+    lg = wl.ceil_log2
+    assert (lg(g.d_model), lg(g.ffn), lg(g.head_dim), lg(g.seq)) == (10, 12, 6, 9)
+    assert 2 * lg(g.seq) == 18 and lg(g.seq) + lg(g.ffn) == 21 and lg(g.seq) + lg(g.d_model) == 19
+    assert lg(g.seq) + lg(g.vocab) == 25 and lg(g.vocab) + lg(g.d_model) == 26
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("field", ["fr", "gl"])
+def test_gpu_walk_equals_the_cpu_walk(dpb, ctx, wl, field):
+    prover = importlib.import_module("deep_prove_b200.prover")
+    want, _ = wl.transformer_path(OracleBackend(field), wl.TINY, seed=7)
+    got = wl.run_transformer_path(dpb, prover, ctx, wl.TINY, field=field, seed=7)
+    assert [r[:2] for r in got["records"]] == [r[:2] for r in want]
+    for (name, kind, g), (_, _, w) in zip(got["records"], want):
+        assert g == w, f"{name} ({kind}) differs from the CPU restatement"
+    assert got["tokens_per_s"] > 0 and set(got["by_kind"]) == set(got["calls"])
+
+
+@pytest.mark.gpu
+def test_gpu_walk_two_blocks_without_head(dpb, ctx, wl):
+    """Two blocks, nothing after them: the counters and kept witness columns of a longer walk."""
+    prover = importlib.import_module("deep_prove_b200.prover")
+    want, _ = wl.transformer_path(OracleBackend("fr"), wl.TINY, seed=9, blocks=2, with_final=False)
+    got = wl.run_transformer_path(dpb, prover, ctx, wl.TINY, field="fr", seed=9, blocks=2, with_final=False)
+    assert [r for r in got["records"]] == want
