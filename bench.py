@@ -440,8 +440,10 @@ def workload_record(dpb, prover, ctx, args):
     a bounded sample of the same call list (one block at a reduced shape) and the GPU walks that sample too."""
     wl = importlib.import_module("deep_prove_b200.workloads")
     shape = wl.GPT2_SMALL
-    # warm-up: one block and the head, so that kernels are loaded and the memory pool has grown
-    wl.run_transformer_path(dpb, prover, ctx, shape, field="fr", seed=args.seed + 1, blocks=1, with_final=True)
+    # warm-up: one whole walk, so that kernels are loaded and the stream-ordered memory pool has grown to the
+    # walk's largest allocation (the claim batching's fold buffers); a prover process is in this state after its
+    # first proof
+    wl.run_transformer_path(dpb, prover, ctx, shape, field="fr", seed=args.seed + 1)
     got = wl.run_transformer_path(dpb, prover, ctx, shape, field="fr", seed=args.seed)
     rec = {"workload": "GPT-2-small (12 layers, d_model 768, 12 heads, FFN 3072, vocab 50257), 512 tokens: every "
                        "sumcheck / fold / logup-GKR call of the forward graph, BN254 Fr, seeded synthetic integer "
