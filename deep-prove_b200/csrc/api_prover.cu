@@ -5,6 +5,7 @@
 
 #include "common.cuh"
 #include "host/claims.hpp"
+#include "host/evals.hpp"
 #include "host/logup.hpp"
 #include "host/lookup.hpp"
 #include "host/prover.hpp"
@@ -367,6 +368,53 @@ int dpb_expr_eval(int family_dtype, const dpb_expr_node* nodes, uint32_t n_nodes
             memcpy(out, &v, sizeof v);
         }
         return DPB_OK;
+    });
+}
+
+int dpb_lookup_padding_evaluation(int family_dtype, const void* padding_value, const uint64_t* shape, uint32_t rank,
+                                  const void* point, uint32_t n_point, void* out) {
+    if (!padding_value || !shape || !out || (!point && n_point)) return fail(DPB_EINVAL, "null argument");
+    if (!valid_dtype(family_dtype)) return fail(DPB_EINVAL, "unknown dtype %d", family_dtype);
+    return guarded([&] {
+        if (is_gl(family_dtype)) {
+            Gl2 pv;
+            memcpy(&pv, padding_value, sizeof pv);
+            const Gl2 v = zkml::compute_lookup_padding_evaluation<GlFam>(pv, shape, rank, (const Gl2*)point, n_point);
+            memcpy(out, &v, sizeof v);
+        } else {
+            Fr pv;
+            memcpy(&pv, padding_value, sizeof pv);
+            const Fr v = zkml::compute_lookup_padding_evaluation<FrFam>(pv, shape, rank, (const Fr*)point, n_point);
+            memcpy(out, &v, sizeof v);
+        }
+        return DPB_OK;
+    });
+}
+
+int dpb_bias_evaluation(int family_dtype, const uint64_t* output_shape, uint32_t rank, const uint8_t* axis_in_bias,
+                        const uint32_t* bias_axis_position, const void* point, uint32_t n_point, const void* bias_eval,
+                        void* out_eval, void* out_bias_point, uint32_t bias_point_cap, uint32_t* n_bias_point) {
+    if (!output_shape || !axis_in_bias || !bias_eval || !out_eval || (!point && n_point))
+        return fail(DPB_EINVAL, "null argument");
+    if (!valid_dtype(family_dtype)) return fail(DPB_EINVAL, "unknown dtype %d", family_dtype);
+    return guarded([&] {
+        auto run = [&](auto fam) {
+            typedef decltype(fam) F;
+            typedef typename F::E E;
+            E be;
+            memcpy(&be, bias_eval, sizeof be);
+            std::vector<E> bp;
+            const E v = zkml::compute_bias_evaluation<F>(output_shape, rank, axis_in_bias, bias_axis_position,
+                                                         (const E*)point, n_point, be, bias_axis_position ? &bp : nullptr);
+            memcpy(out_eval, &v, sizeof v);
+            if (n_bias_point) *n_bias_point = (uint32_t)bp.size();
+            if (out_bias_point && bias_axis_position) {
+                if (bp.size() > bias_point_cap) throw dp_crypto::Error(DPB_EINVAL, "bias point buffer too small");
+                if (!bp.empty()) memcpy(out_bias_point, bp.data(), bp.size() * sizeof(E));
+            }
+            return DPB_OK;
+        };
+        return is_gl(family_dtype) ? run(GlFam()) : run(FrFam());
     });
 }
 

@@ -41,6 +41,8 @@ PROVER_SIGNATURES = {
     "dpb_expr_to_terms": (_int, [_int, ctypes.POINTER(ExprNode), _u32, _vp, _u32, ctypes.POINTER(Term), _u32,
                                  ctypes.POINTER(_u32)]),
     "dpb_expr_eval": (_int, [_int, ctypes.POINTER(ExprNode), _u32, _vp, _u32, _vp, _u32, _vp]),
+    "dpb_lookup_padding_evaluation": (_int, [_int, _vp, _vp, _u32, _vp, _u32, _vp]),
+    "dpb_bias_evaluation": (_int, [_int, _vp, _u32, _vp, _vp, _vp, _u32, _vp, _vp, _vp, _u32, ctypes.POINTER(_u32)]),
     "dpb_prove_sumcheck": (_int, [_vp, _u32, _pp, _u32, ctypes.POINTER(Term), _u32, _vp, _vp, _u32, _vp, _vp,
                                   ctypes.POINTER(_u32)]),
     "dpb_prove_sumcheck_sharded": (_int, [_vp, _u32, _pp, _u32, ctypes.POINTER(Term), _u32, _vp, _vp, _u32, _vp, _vp,
@@ -206,6 +208,33 @@ class IOPProverState:
 
     def extract_sum(self):
         raise NotImplementedError("add proof[0][0] and proof[0][1] in the field of your choice")
+
+
+def lookup_padding_evaluation(family_dtype, padding_value, shape, point):
+    """compute_lookup_padding_evaluation (zkml/src/lookup/operation/mod.rs:289-340); host arithmetic."""
+    w = elem_words(chal_dtype(family_dtype))
+    pv, pt = _scalars(padding_value).reshape(w), _scalars(point).reshape(-1, w)
+    shp = (ctypes.c_uint64 * len(shape))(*shape)
+    out = np.zeros(w, dtype=np.uint64)
+    check(lib.dpb_lookup_padding_evaluation(family_dtype, _buf(pv), shp, len(shape), _buf(pt) if pt.size else None,
+                                            pt.shape[0], _buf(out)))
+    return out
+
+
+def bias_evaluation(family_dtype, output_shape, axis_in_bias, bias_axis_position, point, bias_eval):
+    """AxesMapping::compute_bias_evaluation (zkml/src/layers/einsum/axis.rs:655-720) -> (evaluation, bias point)."""
+    w = elem_words(chal_dtype(family_dtype))
+    pt, be = _scalars(point).reshape(-1, w), _scalars(bias_eval).reshape(w)
+    rank = len(output_shape)
+    shp = (ctypes.c_uint64 * rank)(*output_shape)
+    pres = (ctypes.c_uint8 * rank)(*[1 if a else 0 for a in axis_in_bias])
+    pos = (ctypes.c_uint32 * rank)(*[int(p) for p in bias_axis_position])
+    out = np.zeros(w, dtype=np.uint64)
+    bp = np.zeros((max(pt.shape[0], 1), w), dtype=np.uint64)
+    n = ctypes.c_uint32()
+    check(lib.dpb_bias_evaluation(family_dtype, shp, rank, pres, pos, _buf(pt) if pt.size else None, pt.shape[0], _buf(be),
+                                  _buf(out), _buf(bp), bp.shape[0], ctypes.byref(n)))
+    return out, bp[: n.value]
 
 
 def hadamard_prove(ctx, transcript, claim_point, v1, v2):

@@ -60,6 +60,24 @@ int dpb_expr_to_terms(int family_dtype, const dpb_expr_node* nodes, uint32_t n_n
 int dpb_expr_eval(int family_dtype, const dpb_expr_node* nodes, uint32_t n_nodes, const void* wit_evals,
                   uint32_t n_wit, const void* challenges, uint32_t n_challenges, void* out);
 
+/* ---- closed-form evaluations between layers (host arithmetic, no device work) ---- */
+/* compute_lookup_padding_evaluation (zkml/src/lookup/operation/mod.rs:289-340): the evaluation, at `point`
+ * (over the PADDED shape, Shape::split_point order: the last dimension owns the first coordinates), of the
+ * tensor that is zero inside the unpadded last two dimensions of `shape` and `padding_value` in their padding,
+ * repeated over the unpadded leading indices -- what a lookup layer subtracts from its input claim.
+ * padding_value, point and out are challenge elements of `family_dtype`.  DPB_EINVAL with the reference's
+ * message when the point's length does not match the padded shape. */
+int dpb_lookup_padding_evaluation(int family_dtype, const void* padding_value, const uint64_t* shape, uint32_t rank,
+                                  const void* point, uint32_t n_point, void* out);
+/* AxesMapping::compute_bias_evaluation and bias_evaluation_point (zkml/src/layers/einsum/axis.rs:583-720):
+ * axis_in_bias[d] != 0 when output dimension d is an axis of the bias, bias_axis_position[d] its position in the
+ * bias tensor (may be NULL: no bias point is produced).  out_eval = bias_eval times the less-than polynomial of
+ * every output dimension the bias is broadcast along; out_bias_point (when given) = the point at which the
+ * caller evaluates the bias tensor itself. */
+int dpb_bias_evaluation(int family_dtype, const uint64_t* output_shape, uint32_t rank, const uint8_t* axis_in_bias,
+                        const uint32_t* bias_axis_position, const void* point, uint32_t n_point, const void* bias_eval,
+                        void* out_eval, void* out_bias_point, uint32_t bias_point_cap, uint32_t* n_bias_point);
+
 /* ---- IOPProverState::prove -------------------------------------------------- */
 /* Runs all num_vars rounds (zkml/src/layers/hadamard.rs:115-130).  Outputs, all
  * challenge elements: out_round_evals[num_vars * (degree+1)] (IOPProof),

@@ -1475,6 +1475,101 @@ def eq_point_and_batching_challenges(F, shape, point):
     return eq_point, chal
 
 
+def eval_zeroifier_mle(F, column_point, row_point):
+    """eval_zeroifier_mle (zkml/src/lib.rs:131-138): the MLE of the matrix with ones where column <= row (indices
+    little-endian) at (column_point, row_point).  With row_point the bits of n - 1 it is the "less than n"
+    polynomial of a dimension of size n at column_point."""
+    acc = F.one
+    two = F.from_int(2)
+    for c, r in zip(column_point, row_point):
+        acc = F.add(F.mul(acc, F.add(F.sub(F.sub(F.one, c), r), F.mul(two, F.mul(c, r)))), F.mul(F.sub(F.one, c), r))
+    return acc
+
+
+def evaluate_dim_lt_poly(F, point, size):
+    """evaluate_dim_lt_poly (zkml/src/lookup/operation/variant/verifying.rs:6-22)."""
+    bits = max(size - 1, 0).bit_length()
+    if len(point) != bits:
+        raise ValueError("Row point length %d does not match unpadded seq len log2 %d" % (len(point), bits))
+    return eval_zeroifier_mle(F, point, [F.from_int(((size - 1) >> b) & 1) for b in range(bits)])
+
+
+def split_point(shape, point):
+    """Shape::split_point (zkml/src/shape.rs:475-496) on the PADDED shape: one slice of coordinates per dimension,
+    the last dimension taking the first coordinates."""
+    dims = [1 << max(d - 1, 0).bit_length() for d in shape]
+    if len(point) != sum(d.bit_length() - 1 for d in dims):
+        raise ValueError("Point length %d does not match total variables" % len(point))
+    end, parts = len(point), []
+    for d in dims:
+        start = end - (d.bit_length() - 1)
+        parts.append(list(point[start:end]))
+        end = start
+    return parts
+
+
+def broadcasting_evaluation(F, shape, dim_points, unbroadcast_shape):
+    """Shape::broadcasting_evaluation (zkml/src/shape.rs:516-562): the product of the less-than polynomials of the
+    dimensions that a tensor of shape `unbroadcast_shape` (size one there) is broadcast along."""
+    if len(unbroadcast_shape) != len(shape) or len(dim_points) != len(shape):
+        raise ValueError("shape ranks differ")
+    ev = F.one
+    for full, small, pt in zip(shape, unbroadcast_shape, dim_points):
+        if small == 1:
+            ev = F.mul(ev, eval_zeroifier_mle(F, pt, [F.from_int(((full - 1) >> b) & 1) for b in range(len(pt))]))
+        elif small != full:
+            raise ValueError("Dimension size %d does not match unbroadcasted dimension size %d" % (full, small))
+    return ev
+
+
+def compute_lookup_padding_evaluation(F, padding_value, shape, dim_points):
+    """compute_lookup_padding_evaluation (zkml/src/lookup/operation/mod.rs:289-340): the evaluation of the tensor
+    that is zero inside the unpadded last two dimensions and `padding_value` in their padding, repeated over the
+    leading dimensions' unpadded indices."""
+    rank = len(shape)
+    is_pow2 = lambda d: d & (d - 1) == 0
+    if all(is_pow2(d) for d in shape[max(rank - 2, 0):]):
+        return F.zero
+    unbroadcast = [1 if i < max(rank - 2, 0) else d for i, d in enumerate(shape)]
+    leading = broadcasting_evaluation(F, shape, dim_points, unbroadcast)
+    second_last, last = (shape[rank - 2], shape[rank - 1]) if rank >= 2 else (1, shape[0])
+    last_lt = F.zero if is_pow2(last) else F.sub(F.one, evaluate_dim_lt_poly(F, dim_points[rank - 1], last))
+    if second_last == 1 or is_pow2(second_last):
+        ev = F.mul(leading, last_lt)
+    else:
+        sl = evaluate_dim_lt_poly(F, dim_points[rank - 2], second_last)
+        ev = F.mul(leading, F.add(F.mul(sl, last_lt), F.sub(F.one, sl)))
+    return F.mul(ev, padding_value)
+
+
+def bias_evaluation_point(output_axes, bias_axes, claim_point):
+    """AxesMapping::bias_evaluation_point (zkml/src/layers/einsum/axis.rs:583-637).  Axes are labels (one character
+    each); claim_point holds one slice per output dimension (split_point order).  The bias's point is its
+    dimensions' slices, last dimension first."""
+    slices = [None] * len(bias_axes)
+    for a in bias_axes:
+        if a not in output_axes:
+            raise ValueError("Bias tensor has an axis %s that is not present in the output tensor" % a)
+    for pos, a in enumerate(output_axes):
+        if a in bias_axes:
+            slices[bias_axes.index(a)] = claim_point[pos]
+    out = []
+    for sl in reversed(slices):
+        out += list(sl)
+    return out
+
+
+def compute_bias_evaluation(F, output_axes, bias_axes, claim_point, bias_eval, output_shape):
+    """AxesMapping::compute_bias_evaluation (axis.rs:655-720): the bias's evaluation times the less-than polynomial
+    of every output dimension the bias is broadcast along."""
+    ev = bias_eval
+    for pos, a in enumerate(output_axes):
+        if a not in bias_axes:
+            sl, size = claim_point[pos], output_shape[pos]
+            ev = F.mul(ev, eval_zeroifier_mle(F, sl, [F.from_int(((size - 1) >> b) & 1) for b in range(len(sl))]))
+    return ev, bias_evaluation_point(output_axes, bias_axes, claim_point)
+
+
 def lookup_linking_prove(F, transcript, variant, info, out_min, out_max, shape, mles, last_claim_point, logup_point,
                          normalised_sum=False, weight=None):
     """LookupInputConfig::prove_linking_sumcheck (zkml/src/lookup/operation/inputs/proving.rs:26-114), Standard,

@@ -107,3 +107,48 @@ def test_malformed_expression_is_rejected(dpb, prover):
     with pytest.raises(dpb.DpbError) as e:
         bad.to_terms(dpb.FR, np.zeros((0, 4), np.uint64))
     assert e.value.code == dpb.EINVAL
+
+
+# ------------------------------------------------------- closed-form evaluations between layers
+@pytest.mark.parametrize("F", FIELDS)
+def test_lookup_padding_evaluation_matches_the_oracle(dpb, prover, F):
+    """dpb_lookup_padding_evaluation against the oracle's restatement, which tests/test_oracle_pins.py pins with
+    the reference's own test (zkml/src/lookup/operation/mod.rs:354-415); ranks 1..4, power-of-two and ragged
+    dimensions, and the reference's error for a point of the wrong length."""
+    rng = np.random.default_rng(5100)
+    f = fam(dpb, F)
+    for _ in range(40):
+        rank = int(rng.integers(1, 5))
+        shape = [int(rng.integers(1, 12)) for _ in range(rank)]
+        n_vars = sum(max(d - 1, 0).bit_length() for d in shape)
+        point = [F.random_scalar(rng) for _ in range(n_vars)]
+        pad = F.random_scalar(rng)
+        want = orc.compute_lookup_padding_evaluation(F, pad, shape, orc.split_point(shape, point))
+        pt = orc.scalars_to_array(F, point) if n_vars else np.zeros((0, F.elem_words), np.uint64)
+        got = prover.lookup_padding_evaluation(f, orc.scalars_to_array(F, [pad]), shape, pt)
+        assert orc.array_to_scalars(F, got)[0] == want
+    with pytest.raises(dpb.DpbError) as e:
+        prover.lookup_padding_evaluation(f, orc.scalars_to_array(F, [F.one]), [3, 5], orc.scalars_to_array(F, [F.one] * 4))
+    assert "does not match total variables" in str(e.value)
+
+
+@pytest.mark.parametrize("F", FIELDS)
+def test_bias_evaluation_matches_the_oracle(dpb, prover, F):
+    """dpb_bias_evaluation for output C(ijl) with BIAS(il), BIAS(l), BIAS(li) and BIAS(ijl)
+    (zkml/src/layers/einsum/axis.rs:583-720; the first is the shape of the reference's test at axis.rs:1529)."""
+    rng = np.random.default_rng(5200)
+    f = fam(dpb, F)
+    for bias_axes in ("il", "l", "li", "ijl"):
+        for _ in range(8):
+            shape = [int(rng.integers(1, 10)), int(rng.integers(2, 10)), int(rng.integers(1, 10))]
+            n_vars = sum(max(d - 1, 0).bit_length() for d in shape)
+            point = [F.random_scalar(rng) for _ in range(n_vars)]
+            bias_eval = F.random_scalar(rng)
+            split = orc.split_point(shape, point)
+            want, want_pt = orc.compute_bias_evaluation(F, "ijl", bias_axes, split, bias_eval, shape)
+            present = [a in bias_axes for a in "ijl"]
+            pos = [bias_axes.index(a) if a in bias_axes else 0 for a in "ijl"]
+            pt = orc.scalars_to_array(F, point) if n_vars else np.zeros((0, F.elem_words), np.uint64)
+            got, got_pt = prover.bias_evaluation(f, shape, present, pos, pt, orc.scalars_to_array(F, [bias_eval]))
+            assert orc.array_to_scalars(F, got)[0] == want
+            assert (orc.array_to_scalars(F, got_pt) if len(want_pt) else []) == want_pt

@@ -391,3 +391,54 @@ def test_golden_fixture(F):
     with open(os.path.join(GOLDEN, f"oracle_{F.name}.json")) as f:
         want = json.load(f)
     assert make_golden.generate(F) == want
+
+
+# ------------------------------------------------------- padding and broadcast evaluations
+def _pad_pow2(a, value=0):
+    shape = [1 << max(d - 1, 0).bit_length() for d in a.shape]
+    out = np.full(shape, value, dtype=np.int64)
+    out[tuple(slice(0, d) for d in a.shape)] = a
+    return out
+
+
+@pytest.mark.parametrize("F", FIELDS)
+def test_padding_eval_function(F):
+    """zkml/src/lookup/operation/mod.rs:354-415, the reference's own test of compute_lookup_padding_evaluation:
+    zero sub-tensors over the last two dimensions padded with the padding value, repeated over the unpadded
+    leading indices, zero elsewhere; the MLE's evaluation at a random point equals the closed form."""
+    rng = np.random.default_rng(4100)
+    padding_value = 1
+    for _ in range(30):
+        rank = int(rng.integers(1, 5))
+        shape = [int(rng.integers(1, 10)) for _ in range(rank)]
+        lead = shape[: max(rank - 2, 0)]
+        sub = _pad_pow2(np.zeros(shape[max(rank - 2, 0):], dtype=np.int64), padding_value)
+        inter = np.broadcast_to(sub, tuple(lead) + sub.shape).copy()
+        tensor = _pad_pow2(inter, 0)
+        n_vars = sum(max(d - 1, 0).bit_length() for d in tensor.shape)
+        point = [F.random_scalar(rng) for _ in range(n_vars)]
+        mle_eval = orc.evaluate(F, F.table_from_i64(tensor.reshape(-1)), point)
+        dim_points = orc.split_point(list(tensor.shape), point)
+        got = orc.compute_lookup_padding_evaluation(F, F.from_int(padding_value), shape, dim_points)
+        assert got == mle_eval, (shape, rank)
+
+
+@pytest.mark.parametrize("F", FIELDS)
+def test_broadcasted_bias_eval(F):
+    """zkml/src/layers/einsum/axis.rs:1529-1590 for "A(ijk)@B(ikl)->C(ijl)+BIAS(il)": the bias broadcast along j,
+    padded, evaluated at a random point equals compute_bias_evaluation of the bias's own evaluation."""
+    rng = np.random.default_rng(4200)
+    for _ in range(20):
+        i, j, l = int(rng.integers(1, 10)), int(rng.integers(2, 10)), int(rng.integers(1, 10))
+        out_shape = [i, j, l]
+        bias = rng.integers(-1000, 1000, size=(i, l), dtype=np.int64)
+        broadcast = np.broadcast_to(bias[:, None, :], (i, j, l)).copy()
+        padded_b, padded_bias = _pad_pow2(broadcast), _pad_pow2(bias)
+        n_vars = sum(max(d - 1, 0).bit_length() for d in padded_b.shape)
+        point = [F.random_scalar(rng) for _ in range(n_vars)]
+        want = orc.evaluate(F, F.table_from_i64(padded_b.reshape(-1)), point)
+        split = orc.split_point(out_shape, point)
+        bias_point = orc.bias_evaluation_point("ijl", "il", split)
+        bias_eval = orc.evaluate(F, F.table_from_i64(padded_bias.reshape(-1)), bias_point)
+        got, pt = orc.compute_bias_evaluation(F, "ijl", "il", split, bias_eval, out_shape)
+        assert got == want and pt == bias_point
