@@ -21,6 +21,7 @@
 
 #include <atomic>
 #include <chrono>
+#include <random>
 #include <thread>
 
 #include "comm.cuh"
@@ -130,7 +131,10 @@ static int xch_setup(dpb_ctx* ctx, const void* unique_id) {
     DPB_TRY(all_ranks_agree(ctx, host_fingerprint(), &same_host));
     bool ok = same_host;
     void* map = MAP_FAILED;
-    const size_t bytes = (xch_bytes_for(ctx->nranks) + 4095) & ~(size_t)4095;
+    // the slots, then one 64-byte line that holds a nonce rank 0 draws for this segment
+    const size_t nonce_off = (xch_bytes_for(ctx->nranks) + 63) & ~(size_t)63;
+    const size_t bytes = (nonce_off + 64 + 4095) & ~(size_t)4095;
+    uint64_t nonce = 0;
     char name[64];
     {
         uint64_t h = 1469598103934665603ull;
@@ -162,6 +166,25 @@ static int xch_setup(dpb_ctx* ctx, const void* unique_id) {
             close(fd);
         }
         ok = map != MAP_FAILED;
+        if (ok) {
+            // Which segment did this rank map?  Rank 0 marks the one it created with a random non-zero word; the
+            // others wait (bounded) for a mark to appear.  A rank that opened a leftover segment of the same name
+            // before rank 0 unlinked it reads another value, and the agreement below then fails for everybody.
+            volatile uint64_t* mark = (volatile uint64_t*)((char*)map + nonce_off);
+            if (ctx->rank == 0) {
+                std::random_device rd;
+                do nonce = ((uint64_t)rd() << 32) ^ rd() ^ (uint64_t)std::chrono::steady_clock::now().time_since_epoch().count();
+                while (nonce == 0);
+                *mark = nonce;
+                std::atomic_thread_fence(std::memory_order_seq_cst);
+            } else {
+                const auto t0 = std::chrono::steady_clock::now();
+                while ((nonce = *mark) == 0 &&
+                       std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() < 10.0)
+                    std::this_thread::sleep_for(std::chrono::milliseconds(1));
+                ok = nonce != 0;
+            }
+        }
     }
     bool registered = false;
     void* dev = nullptr;
@@ -171,8 +194,9 @@ static int xch_setup(dpb_ctx* ctx, const void* unique_id) {
         ok = registered && cudaHostGetDevicePointer(&dev, map, 0) == cudaSuccess;
         if (!ok) cudaGetLastError();  // clear the sticky-free error of a refused registration
     }
+    // every rank reports the mark of the segment it mapped (0: it has none): equal non-zero marks = one segment
     bool all_ok = false;
-    int rc = all_ranks_agree(ctx, ok ? 1 : 0, &all_ok);
+    int rc = all_ranks_agree(ctx, ok ? nonce : 0, &all_ok);
     if (ctx->rank == 0 && same_host) shm_unlink(name);  // every rank that could has mapped it by now
     if (rc == DPB_OK && ok && all_ok) {
         ctx->xch_host = map;
