@@ -295,6 +295,18 @@ int dpb_init(int device, dpb_ctx** out) {
     DPB_CUDA(cudaDeviceGetDefaultMemPool(&pool, device));
     uint64_t thresh = UINT64_MAX;
     DPB_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &thresh));
+    // The resident last-rounds kernel needs the host to answer while it runs.  When launches are known to block the
+    // launching thread (CUDA_LAUNCH_BLOCKING, or a tool injected into the process that serialises kernels) it is
+    // not started at all; otherwise the first one still finds out by itself (its bounded wait for the host's first
+    // sign of life) and the context falls back then.
+    {
+        const char* blocking = getenv("CUDA_LAUNCH_BLOCKING");
+        const char* injected = getenv("CUDA_INJECTION64_PATH");
+        const char* assume_async = getenv("DPB_ASSUME_ASYNC_LAUNCHES");  // skips this check (the kernel's own stays)
+        if (!(assume_async && assume_async[0] == '1') &&
+            ((blocking && blocking[0] && strcmp(blocking, "0") != 0) || (injected && injected[0])))
+            ctx->tail_enabled = false;
+    }
     ctx->max_blocks = (uint32_t)ctx->sm_count * 8;
     DPB_CUDA(cudaMalloc(&ctx->partials, (size_t)ctx->max_blocks * kMaxAcc * sizeof(Fr)));
     DPB_CUDA(cudaMalloc((void**)&ctx->counter, 256));

@@ -127,10 +127,13 @@ def test_host_that_is_held_up(dpb, ctx, F):
     assert (proof, point, finals) == want
 
 
-def test_blocking_launches_fall_back_to_one_launch_per_round():
+@pytest.mark.parametrize("detect_at_init", [True, False])
+def test_blocking_launches_fall_back_to_one_launch_per_round(detect_at_init):
     """With launches that block the host (CUDA_LAUNCH_BLOCKING=1; a profiler that serialises kernels behaves the
-    same) the resident kernel cannot talk to the host: it notices within 50 ms, leaves, and the context runs one
-    launch per round.  Results are unchanged and nothing waits for a time-out."""
+    same) the resident kernel cannot talk to the host.  The context sees the setting when it is created and never
+    starts the kernel; with that check switched off (DPB_ASSUME_ASYNC_LAUNCHES=1) the kernel itself notices
+    within 50 ms, leaves, and the context runs one launch per round from then on.  Results are unchanged and
+    nothing waits for a time-out."""
     import os
     import subprocess
     import sys
@@ -158,5 +161,7 @@ assert time.perf_counter() - t0 < 3.0
 print('FALLBACK-OK')
 """.format(root=root)
     env = dict(os.environ, CUDA_LAUNCH_BLOCKING="1")
+    if not detect_at_init:
+        env["DPB_ASSUME_ASYNC_LAUNCHES"] = "1"
     out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
     assert "FALLBACK-OK" in out.stdout, out.stdout + out.stderr
