@@ -16,6 +16,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libdpb.so")
 
 GL_BASE, GL_EXT, FR = 0, 1, 2
+GL_I64, GL_I32, FR_I64, FR_I32 = 3, 4, 5, 6  # integer tables (the integers themselves, 8 or 4 bytes per entry)
+INT_DTYPES = {GL_I64: np.int64, GL_I32: np.int32, FR_I64: np.int64, FR_I32: np.int32}
 FORM_NATIVE, FORM_CANONICAL, FORM_I64 = 0, 1, 2
 LOGUP_LOOKUP, LOGUP_TABLE = 0, 1
 AXIS_CONTRACTED, AXIS_OUTER, AXIS_STACKED = 0, 1, 2
@@ -134,11 +136,12 @@ def check(rc):
 
 
 def elem_words(dtype):
+    """64-bit words per entry of a field layout (integer layouts are described by INT_DTYPES)."""
     return {GL_BASE: 1, GL_EXT: 2, FR: 4}[dtype]
 
 
 def chal_dtype(dtype):
-    return FR if dtype == FR else GL_EXT
+    return FR if dtype in (FR, FR_I64, FR_I32) else GL_EXT
 
 
 FR_MODULUS = 21888242871839275222246405745257275088548364400416034343698204186575808495617
@@ -230,6 +233,13 @@ class Context:
         n = a.shape[0]
         h = ctypes.c_void_p()
         check(lib.dpb_mle_from_host(self.h, dtype, _buf(a), n, form, ctypes.byref(h)))
+        return Mle(self, h)
+
+    def upload_ints(self, array, dtype):
+        """An integer table (GL_I64 / GL_I32 / FR_I64 / FR_I32): the integers stay integers on the device."""
+        a = np.ascontiguousarray(array, dtype=INT_DTYPES[dtype])
+        h = ctypes.c_void_p()
+        check(lib.dpb_mle_from_host(self.h, dtype, _buf(a), a.size, FORM_NATIVE, ctypes.byref(h)))
         return Mle(self, h)
 
     def upload_i64(self, array, dtype):
@@ -432,6 +442,10 @@ class Mle:
 
     def to_host(self, form=FORM_NATIVE, n=None):
         n = self.len if n is None else n
+        if self.dtype in INT_DTYPES:
+            out = np.empty(n, dtype=INT_DTYPES[self.dtype])
+            check(lib.dpb_mle_to_host(self.h, _buf(out), n, FORM_NATIVE))
+            return out
         w = elem_words(self.dtype)
         out = np.empty((n, w) if w > 1 else (n,), dtype=np.uint64)
         check(lib.dpb_mle_to_host(self.h, _buf(out), n, form))

@@ -401,6 +401,8 @@ int dpb_mle_from_host(dpb_ctx* ctx, int dtype, const void* evals, uint64_t len, 
     if (form == DPB_FORM_I64 && dtype == DPB_GL_EXT)
         return fail(DPB_EINVAL, "i64 input yields base-field or Fr tables");
     if (form < DPB_FORM_NATIVE || form > DPB_FORM_I64) return fail(DPB_EINVAL, "unknown form %d", form);
+    if (is_int_dtype(dtype) && form != DPB_FORM_NATIVE)
+        return fail(DPB_EINVAL, "integer tables take their integers as they are (DPB_FORM_NATIVE)");
     dpb_mle* m = nullptr;
     DPB_TRY(new_mle(ctx, dtype, len, &m));
     int rc = DPB_OK;
@@ -595,6 +597,24 @@ int dpb_mle_evaluate(dpb_ctx* ctx, const dpb_mle* mle, const void* point, uint32
                     (unsigned long long)mle->len);
     if (n == 0) {
         // a constant: widen the single entry
+        if (is_int_dtype(mle->dtype)) {
+            int64_t x = 0;
+            int32_t x32 = 0;
+            const bool narrow = dtype_size(mle->dtype) == 4;
+            DPB_CUDA(cudaMemcpyAsync(narrow ? (void*)&x32 : (void*)&x, mle->ptr, narrow ? 4 : 8, cudaMemcpyDeviceToHost,
+                                     ctx->stream));
+            DPB_CUDA(cudaStreamSynchronize(ctx->stream));
+            if (narrow) x = x32;
+            if (is_gl(mle->dtype)) {
+                const uint64_t mag = x < 0 ? (uint64_t)0 - (uint64_t)x : (uint64_t)x;
+                const Gl2 v = gl2_make(x < 0 ? (GL_P - mag % GL_P) % GL_P : mag % GL_P, 0);
+                memcpy(out, &v, sizeof v);
+            } else {
+                const Fr v = fr_from_i64(x);
+                memcpy(out, &v, sizeof v);
+            }
+            return DPB_OK;
+        }
         if (mle->dtype == DPB_GL_BASE) {
             uint64_t v[2] = {0, 0};
             DPB_CUDA(cudaMemcpyAsync(v, mle->ptr, 8, cudaMemcpyDeviceToHost, ctx->stream));

@@ -14,6 +14,7 @@
 #include "fused_v2.cuh"
 #include "fused_v3.cuh"
 #include "fused_v4.cuh"
+#include "fused_int.cuh"
 #include "generic_round.cuh"
 #include "comm.cuh"
 
@@ -774,6 +775,19 @@ static void launch_fused_fr(dpb_ctx* ctx, const MleDesc* desc, const FoldDesc* f
     for (int j = 0; j < K; j++) {
         ptrs.in[j] = round == 0 ? desc[j].ptr : folds[j].in;
         ptrs.out[j] = round == 0 ? nullptr : folds[j].out;
+    }
+    // integer tables (DPB_FR_I32, K <= 3): round 0 in integer arithmetic, round 1 folds integers (fused_int.cuh)
+    if constexpr (K <= 3) {
+        if (round == 0 && desc[0].dtype == DPB_FR_I32) {
+            v2_eval0_fr_i32<K><<<grid, kThreads, 0, ctx->stream>>>(ptrs, n_pairs, rs, out);
+            return;
+        }
+        if (round > 0 && folds[0].dtype_in == DPB_FR_I32) {
+            IntFoldKey key;
+            int_fold_key(r, key);
+            v2_fold_eval_fr_i32<K, 2><<<grid, kThreads, 0, ctx->stream>>>(ptrs, key, n_pairs, rs, out);
+            return;
+        }
     }
     // two resident blocks per SM: these kernels wait on their multiply chains, more warps hide that
     if (round == 0) {

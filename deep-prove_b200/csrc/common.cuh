@@ -32,9 +32,19 @@ int fail(int code, const char* fmt, ...);
         if (rc__ != DPB_OK) return rc__; \
     } while (0)
 
-inline bool is_gl(int dtype) { return dtype == DPB_GL_BASE || dtype == DPB_GL_EXT; }
-inline bool valid_dtype(int dtype) { return dtype >= DPB_GL_BASE && dtype <= DPB_FR; }
-inline size_t dtype_size(int dtype) { return dtype == DPB_GL_BASE ? 8 : dtype == DPB_GL_EXT ? 16 : 32; }
+inline bool is_gl(int dtype) {
+    return dtype == DPB_GL_BASE || dtype == DPB_GL_EXT || dtype == DPB_GL_I64 || dtype == DPB_GL_I32;
+}
+inline bool valid_dtype(int dtype) { return dtype >= DPB_GL_BASE && dtype <= DPB_FR_I32; }
+inline bool is_int_dtype(int dtype) { return dtype >= DPB_GL_I64 && dtype <= DPB_FR_I32; }
+inline size_t dtype_size(int dtype) {
+    switch (dtype) {
+        case DPB_GL_BASE: case DPB_GL_I64: case DPB_FR_I64: return 8;
+        case DPB_GL_EXT: return 16;
+        case DPB_GL_I32: case DPB_FR_I32: return 4;
+        default: return 32;
+    }
+}
 inline int chal_dtype(int dtype) { return is_gl(dtype) ? DPB_GL_EXT : DPB_FR; }
 inline bool is_pow2(uint64_t x) { return x && !(x & (x - 1)); }
 inline uint32_t log2u(uint64_t x) {

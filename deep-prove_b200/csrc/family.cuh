@@ -70,10 +70,18 @@ struct GlFam {
     __device__ __forceinline__ static void fold_key_block(const E& r, FoldKey* out) {
         if (threadIdx.x == 0) *out = r;
     }
+    // a signed integer as a canonical base element: negative x -> p - |x|
+    __device__ __forceinline__ static uint64_t base_from_int(int64_t x) {
+        return x < 0 ? GL_P - ((uint64_t)0 - (uint64_t)x) % GL_P : (uint64_t)x % GL_P;
+    }
     __device__ __forceinline__ static E load(const void* p, int dtype, uint64_t i) {
         if (dtype == DPB_GL_BASE) return gl2_from_base(((const uint64_t*)p)[i]);
-        const ulonglong2 v = ((const ulonglong2*)p)[i];
-        return gl2_make(v.x, v.y);
+        if (dtype == DPB_GL_EXT) {
+            const ulonglong2 v = ((const ulonglong2*)p)[i];
+            return gl2_make(v.x, v.y);
+        }
+        if (dtype == DPB_GL_I32) return gl2_from_base(base_from_int(((const int32_t*)p)[i]));
+        return gl2_from_base(base_from_int(((const int64_t*)p)[i]));
     }
     // entries 2i and 2i+1
     __device__ __forceinline__ static void load_pair(const void* p, int dtype, uint64_t i, E& a,
@@ -82,11 +90,19 @@ struct GlFam {
             const ulonglong2 v = ((const ulonglong2*)p)[i];
             a = gl2_from_base(v.x);
             b = gl2_from_base(v.y);
-        } else {
+        } else if (dtype == DPB_GL_EXT) {
             const ulonglong2 v0 = ((const ulonglong2*)p)[2 * i];
             const ulonglong2 v1 = ((const ulonglong2*)p)[2 * i + 1];
             a = gl2_make(v0.x, v0.y);
             b = gl2_make(v1.x, v1.y);
+        } else if (dtype == DPB_GL_I64) {
+            const longlong2 v = ((const longlong2*)p)[i];
+            a = gl2_from_base(base_from_int(v.x));
+            b = gl2_from_base(base_from_int(v.y));
+        } else {
+            const int2 v = ((const int2*)p)[i];
+            a = gl2_from_base(base_from_int(v.x));
+            b = gl2_from_base(base_from_int(v.y));
         }
     }
     __device__ __forceinline__ static void store(void* p, uint64_t i, const E& v) {
@@ -127,7 +143,9 @@ struct FrFam {
     __device__ __forceinline__ static void fold_key_block(const E& r, FoldKey* out) {
         if (threadIdx.x < 8) fr_fixed_row(r, (int)threadIdx.x, out->c[threadIdx.x]);
     }
-    __device__ __forceinline__ static E load(const void* p, int, uint64_t i) {
+    __device__ __forceinline__ static E load(const void* p, int dtype, uint64_t i) {
+        if (dtype == DPB_FR_I64) return fr_from_i64(((const int64_t*)p)[i]);
+        if (dtype == DPB_FR_I32) return fr_from_i64((int64_t)((const int32_t*)p)[i]);
         const ulonglong2* q = (const ulonglong2*)p + 2 * i;
         const ulonglong2 a = q[0], b = q[1];
         E r;

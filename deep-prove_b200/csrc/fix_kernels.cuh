@@ -46,13 +46,18 @@ struct WSum<GlFam> {
             const glw::W xw = glw::make_w((uint32_t)x, (uint32_t)(x >> 32));
             glw::acc_mac(a.s0, xw, k.c0);
             glw::acc_mac(a.s1, xw, k.c1);
-        } else {
+        } else if (dtype == DPB_GL_EXT) {
             const uint4 v = ((const uint4*)in)[i];
             const glw::W x0 = glw::make_w(v.x, v.y), x1 = glw::make_w(v.z, v.w);
             glw::acc_mac(a.s0, x0, k.c0);
             glw::acc_mac(a.s0, x1, k.c1x7);
             glw::acc_mac(a.s1, x0, k.c1);
             glw::acc_mac(a.s1, x1, k.c0);
+        } else {  // integer tables: the base element the integer stands for
+            const uint64_t x = GlFam::load(in, dtype, i).c0;
+            const glw::W xw = glw::make_w((uint32_t)x, (uint32_t)(x >> 32));
+            glw::acc_mac(a.s0, xw, k.c0);
+            glw::acc_mac(a.s1, xw, k.c1);
         }
     }
     // acc += key0 * entry i + key1 * entry i + 1 of a base table, i even: one 16-byte load

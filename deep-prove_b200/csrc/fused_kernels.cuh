@@ -112,6 +112,9 @@ inline int detect_fused_shape(const MleDesc*, size_t k, uint32_t num_vars, const
         seen[id] = true;
         if (nv(j) != num_vars || dtype(j) != dtype(0)) return kFusedNone;
     }
+    // integer tables: only 32-bit integers of the BN254 family have fused rounds (products of up to three)
+    if (dtype(0) == DPB_GL_I64 || dtype(0) == DPB_GL_I32 || dtype(0) == DPB_FR_I64) return kFusedNone;
+    if (dtype(0) == DPB_FR_I32 && k > 3) return kFusedNone;
     if (gl) {
         Gl2 c;
         memcpy(&c, terms[0].coeff, sizeof c);

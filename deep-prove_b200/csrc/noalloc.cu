@@ -83,6 +83,7 @@ extern "C" int dpb_product_round_noalloc(void* cuda_stream, int dtype, const voi
                                          uint64_t len, void* out_evals_dev) {
     if (!tables_dev || !out_evals_dev) return fail(DPB_EINVAL, "null argument");
     if (!valid_dtype(dtype)) return fail(DPB_EINVAL, "unknown dtype %d", dtype);
+    if (is_int_dtype(dtype)) return fail(DPB_EINVAL, "this entry point takes field tables, not integer tables (dtype %d)", dtype);
     if (k < 2 || k > kNoallocMaxTables)
         return fail(DPB_EINVAL, "table count %u outside 2..%u", k, kNoallocMaxTables);
     if (!is_pow2(len) || len < 2) return fail(DPB_EINVAL, "length %llu is not a power of two >= 2", (unsigned long long)len);

@@ -48,6 +48,17 @@ extern "C" {
 #define DPB_GL_BASE 0
 #define DPB_GL_EXT 1
 #define DPB_FR 2
+/* Integer tables: the quantised tensors and lookup columns of the reference are small signed integers
+ * (Element = i64, zkml/src/quantization/mod.rs:220-267; Tensor::to_field, zkml/src/layers/einsum/prove.rs:66-91).
+ * A table of one of these layouts holds the integers themselves (8 or 4 bytes per entry) and stands for the
+ * field elements they map to (negative x -> p - |x|) in the Goldilocks or in the BN254 family.  Every sumcheck
+ * entry point, the folds, evaluate, the linear combination and the logup tree accept them; results are
+ * bit-identical to those of the converted table, because the arithmetic is exact.  The product sumcheck over
+ * DPB_FR_I32 tables runs its first round in integer arithmetic and its first fold through two precomputed rows. */
+#define DPB_GL_I64 3
+#define DPB_GL_I32 4
+#define DPB_FR_I64 5
+#define DPB_FR_I32 6
 
 /* forms accepted by dpb_mle_from_host for DPB_FR tables */
 #define DPB_FORM_NATIVE 0    /* already in the layout of `dtype` */
