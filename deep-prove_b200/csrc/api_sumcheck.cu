@@ -999,7 +999,8 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
         const char* name;
         if (i == 0) {
             for (uint32_t j = 0; j < sc->k; j++) bytes += dtype_size(sc->tr[j].dtype) << sc->tr[j].nv;
-            name = done ? (sc->tr[0].dtype == DPB_GL_BASE ? "fused_eval0<base>" : "fused_eval0")
+            name = done ? (sc->tr[0].dtype == DPB_GL_BASE ? "fused_eval0<base>"
+                           : sc->tr[0].dtype == DPB_FR_I32 ? "fused_eval0<i32>" : "fused_eval0")
                         : split ? "sc_round_spliteq" : one_pass ? "sc_round_generic" : "sc_eval_generic";
         } else {
             const FoldDesc* fd = sc->h_fold.data() + (size_t)i * sc->k;
@@ -1007,7 +1008,8 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
                 bytes += fd[j].n_out * (2 * dtype_size(fd[j].dtype_in) + sizeof(E));
             for (uint32_t j = 0; j < sc->k; j++)
                 if (sc->h_desc[(size_t)i * sc->k + j].shift >= 0) bytes += dtype_size(sc->tr[j].dtype) << sc->tr[j].nv;
-            name = done ? (fd[0].dtype_in == DPB_GL_BASE ? "fused_fold_eval<base>" : "fused_fold_eval")
+            name = done ? (fd[0].dtype_in == DPB_GL_BASE ? "fused_fold_eval<base>"
+                           : fd[0].dtype_in == DPB_FR_I32 ? "fused_fold_eval<i32>" : "fused_fold_eval")
                         : split ? "sc_round_spliteq" : one_pass ? "sc_round_generic" : "sc_fold_generic+sc_eval_generic";
         }
         bool found = false;
