@@ -144,8 +144,8 @@ struct FrFam {
         if (threadIdx.x < 8) fr_fixed_row(r, (int)threadIdx.x, out->c[threadIdx.x]);
     }
     __device__ __forceinline__ static E load(const void* p, int dtype, uint64_t i) {
-        if (dtype == DPB_FR_I64) return fr_from_i64(((const int64_t*)p)[i]);
-        if (dtype == DPB_FR_I32) return fr_from_i64((int64_t)((const int32_t*)p)[i]);
+        if (dtype == DPB_FR_I64) return fr_from_int_rows(((const int64_t*)p)[i]);
+        if (dtype == DPB_FR_I32) return fr_from_int_rows((int64_t)((const int32_t*)p)[i]);
         const ulonglong2* q = (const ulonglong2*)p + 2 * i;
         const ulonglong2 a = q[0], b = q[1];
         E r;

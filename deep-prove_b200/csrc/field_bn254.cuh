@@ -224,6 +224,23 @@ __device__ __forceinline__ Fr fr_intacc_finish(const FrIntAcc& acc) {
     return fr_add(a, b);
 }
 
+// Integer -> Montgomery form without a full product: |x| = lo + 2^32 hi, and x R = lo * (+-R) + hi * (+-2^32 R)
+// mod r; the rows below hold those four constants times 2^64 (what frw::lin2_rows divides out again).
+static __device__ __constant__ const uint32_t kIntRowOnePos[8] = {0x7c5fb586u, 0xb4c6edf9u, 0xbfeb93beu, 0x708c8d50u,
+                                                                  0x04f7e0efu, 0x9ffd1de4u, 0x9a392866u, 0x215b02acu};
+static __device__ __constant__ const uint32_t kIntRowOneNeg[8] = {0x73a04a7bu, 0x8f1b079au, 0xb9cddcd2u, 0xb7a75af7u,
+                                                                  0x7c89776du, 0x185327d2u, 0x46f877c3u, 0x0f094bc6u};
+static __device__ __constant__ const uint32_t kIntRowHiPos[8] = {0xaf8b5a7au, 0x54c81065u, 0x97aa45f6u, 0x2b82a1efu,
+                                                                 0x330a5a6du, 0xbe492693u, 0x8229aff4u, 0x1847e486u};
+static __device__ __constant__ const uint32_t kIntRowHiNeg[8] = {0x4074a587u, 0xef19e52eu, 0xe20f2a9au, 0xfcb14658u,
+                                                                 0x4e76fdefu, 0xfa071f23u, 0x5f07f034u, 0x181c69ecu};
+__device__ __forceinline__ Fr fr_from_int_rows(int64_t x) {
+    const uint64_t mag = x < 0 ? (uint64_t)0 - (uint64_t)x : (uint64_t)x;
+    const bool neg = x < 0;
+    return frw::to_fr(frw::lin2_rows((uint32_t)mag, neg ? kIntRowOneNeg : kIntRowOnePos, (uint32_t)(mag >> 32),
+                                     neg ? kIntRowHiNeg : kIntRowHiPos));
+}
+
 // 2^(32 i + 64) mod r as a plain integer, i = 0..7
 DPB_HD Fr fr_fixed_power(int i) {
     Fr x;

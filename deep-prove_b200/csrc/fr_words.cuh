@@ -191,6 +191,33 @@ __device__ __forceinline__ F8 mul_fixed(const F8& a, const FixedMul& k) {
     return reduce_once(s);
 }
 
+// Two small integers times two rows, the reduction of mul_fixed: what turns an integer, or the fold of two
+// integers by a challenge, into a field element for a fraction of a product's cost.
+// (ma * row_a + md * row_d) / 2^64 mod p, ma and md below 2^32
+__device__ __forceinline__ F8 lin2_rows(uint32_t ma, const uint32_t* ra, uint32_t md, const uint32_t* rd) {
+    uint32_t E[12], O[12];  // pairs at even / odd positions, as in mul_fixed
+#pragma unroll
+    for (int i = 0; i < 12; i++) E[i] = O[i] = 0;
+    chain_mul(E, E[8], ra[0], ra[2], ra[4], ra[6], ma);
+    chain_mul(O + 1, O[9], ra[1], ra[3], ra[5], ra[7], ma);
+    chain_mul(E, E[8], rd[0], rd[2], rd[4], rd[6], md);
+    chain_mul(O + 1, O[9], rd[1], rd[3], rd[5], rd[7], md);
+    const uint32_t m0 = E[0] * DPB_FRW_INV;
+    chain_mod_even(E, E[8], m0);
+    chain_mod_odd<false>(O + 1, O[9], m0, 0);
+    const uint32_t m1 = (O[1] + E[1]) * DPB_FRW_INV;
+    chain_mod_even(O + 1, O[9], m1);
+    chain_mod_odd<true>(E + 2, E[10], m1, E[1]);
+    F8 s;
+    asm("add.cc.u32 %0, %8, %16; addc.cc.u32 %1, %9, %17; addc.cc.u32 %2, %10, %18; addc.cc.u32 %3, %11, %19;\n\t"
+        "addc.cc.u32 %4, %12, %20; addc.cc.u32 %5, %13, %21; addc.cc.u32 %6, %14, %22; addc.u32 %7, %15, %23;"
+        : "=&r"(s.w[0]), "=&r"(s.w[1]), "=&r"(s.w[2]), "=&r"(s.w[3]), "=&r"(s.w[4]), "=&r"(s.w[5]), "=&r"(s.w[6]),
+          "=&r"(s.w[7])
+        : "r"(E[2]), "r"(E[3]), "r"(E[4]), "r"(E[5]), "r"(E[6]), "r"(E[7]), "r"(E[8]), "r"(E[9]), "r"(O[2]),
+          "r"(O[3]), "r"(O[4]), "r"(O[5]), "r"(O[6]), "r"(O[7]), "r"(O[8]), "r"(O[9]));
+    return reduce_once(s);
+}
+
 // Sum of (64-bit integer) * (field element) products kept as one unreduced integer: what the contraction of an
 // integer tensor against eq weights is made of.  A term is 16 wide multiply-adds and no reduction; the sum of up to
 // 2^24 terms stays below 2^352 and is reduced once (two Montgomery products).  Layout as in mul: E holds word pairs

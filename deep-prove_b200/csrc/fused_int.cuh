@@ -72,37 +72,12 @@ struct IntFoldKey {
     uint32_t one_pos[8], one_neg[8], r_pos[8], r_neg[8];
 };
 
-// (ma * row_a + md * row_d) / 2^64 mod p, ma and md below 2^32
-__device__ __forceinline__ frw::F8 lin2_rows(uint32_t ma, const uint32_t* ra, uint32_t md, const uint32_t* rd) {
-    uint32_t E[12], O[12];  // pairs at even / odd positions, as in frw::mul_fixed
-#pragma unroll
-    for (int i = 0; i < 12; i++) E[i] = O[i] = 0;
-    frw::chain_mul(E, E[8], ra[0], ra[2], ra[4], ra[6], ma);
-    frw::chain_mul(O + 1, O[9], ra[1], ra[3], ra[5], ra[7], ma);
-    frw::chain_mul(E, E[8], rd[0], rd[2], rd[4], rd[6], md);
-    frw::chain_mul(O + 1, O[9], rd[1], rd[3], rd[5], rd[7], md);
-    const uint32_t m0 = E[0] * DPB_FRW_INV;
-    frw::chain_mod_even(E, E[8], m0);
-    frw::chain_mod_odd<false>(O + 1, O[9], m0, 0);
-    const uint32_t m1 = (O[1] + E[1]) * DPB_FRW_INV;
-    frw::chain_mod_even(O + 1, O[9], m1);
-    frw::chain_mod_odd<true>(E + 2, E[10], m1, E[1]);
-    frw::F8 s;
-    asm("add.cc.u32 %0, %8, %16; addc.cc.u32 %1, %9, %17; addc.cc.u32 %2, %10, %18; addc.cc.u32 %3, %11, %19;\n\t"
-        "addc.cc.u32 %4, %12, %20; addc.cc.u32 %5, %13, %21; addc.cc.u32 %6, %14, %22; addc.u32 %7, %15, %23;"
-        : "=&r"(s.w[0]), "=&r"(s.w[1]), "=&r"(s.w[2]), "=&r"(s.w[3]), "=&r"(s.w[4]), "=&r"(s.w[5]), "=&r"(s.w[6]),
-          "=&r"(s.w[7])
-        : "r"(E[2]), "r"(E[3]), "r"(E[4]), "r"(E[5]), "r"(E[6]), "r"(E[7]), "r"(E[8]), "r"(E[9]), "r"(O[2]),
-          "r"(O[3]), "r"(O[4]), "r"(O[5]), "r"(O[6]), "r"(O[7]), "r"(O[8]), "r"(O[9]));
-    return frw::reduce_once(s);
-}
-
 // a0 + r (a1 - a0) for integers a0, a1 of 32 bits
 __device__ __forceinline__ Fr fold_i32(const IntFoldKey& k, int32_t a0, int32_t a1) {
     const int64_t d = (int64_t)a1 - (int64_t)a0;  // below 2^32 in magnitude
     const uint32_t ma = a0 < 0 ? (uint32_t)0 - (uint32_t)a0 : (uint32_t)a0;
     const uint32_t md = d < 0 ? (uint32_t)(-d) : (uint32_t)d;
-    return frw::to_fr(lin2_rows(ma, a0 < 0 ? k.one_neg : k.one_pos, md, d < 0 ? k.r_neg : k.r_pos));
+    return frw::to_fr(frw::lin2_rows(ma, a0 < 0 ? k.one_neg : k.one_pos, md, d < 0 ? k.r_neg : k.r_pos));
 }
 
 // Round 1 over int32 tables: fold by the challenge (integers in, field elements out), then the usual samples.

@@ -462,8 +462,13 @@ class GpuBackend:
     """The walk's calls on the GPU library: every method is one or a few C-ABI calls (device tensors stay on the
     device; the transcript and the expression algebra run in the library's host code)."""
 
-    def __init__(self, dpb, prover, ctx, field="fr"):
+    def __init__(self, dpb, prover, ctx, field="fr", int_tables=True):
         self.dpb, self.prover, self.ctx = dpb, prover, ctx
+        # int_tables: integer tensors (weights, activations, fixed 0/1 tables) stay 32- or 64-bit integers on the
+        # device instead of being converted to field elements at upload; every result is the same
+        self.int_tables = int_tables
+        self.i32 = dpb.FR_I32 if field == "fr" else dpb.GL_I32
+        self.i64 = dpb.FR_I64 if field == "fr" else dpb.GL_I64
         self.fam = dpb.FR if field == "fr" else dpb.GL_EXT
         self.base = dpb.FR if field == "fr" else dpb.GL_BASE
         self.w = dpb.elem_words(self.fam)
@@ -534,7 +539,11 @@ class GpuBackend:
 
     # -- tables
     def int_table(self, arr):
-        return self.ctx.upload_i64(np.ascontiguousarray(arr, dtype=np.int64), self.base)
+        a = np.ascontiguousarray(arr, dtype=np.int64)
+        if not self.int_tables:
+            return self.ctx.upload_i64(a, self.base)
+        fits32 = a.size == 0 or (int(a.min()) >= -2**31 and int(a.max()) < 2**31)
+        return self.ctx.upload_ints(a, self.i32 if fits32 else self.i64)
 
     def tensor(self, arr):
         return self.ctx.upload_tensor_i64(arr)
@@ -655,9 +664,10 @@ class GpuBackend:
         return payload
 
 
-def run_transformer_path(dpb, prover, ctx, shape=GPT2_SMALL, field="fr", seed=0, blocks=None, with_final=True):
+def run_transformer_path(dpb, prover, ctx, shape=GPT2_SMALL, field="fr", seed=0, blocks=None, with_final=True,
+                         int_tables=True):
     """One walk on the GPU.  Returns dict(seconds, tokens_per_s, by_kind, calls, records)."""
-    be = GpuBackend(dpb, prover, ctx, field)
+    be = GpuBackend(dpb, prover, ctx, field, int_tables)
     ctx.sync()
     t0 = time.perf_counter()
     rec, timer = transformer_path(be, shape, seed, blocks, with_final)

@@ -71,10 +71,12 @@ def test_gpt2_shape_call_sizes():
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("field", ["fr", "gl"])
-def test_gpu_walk_equals_the_cpu_walk(dpb, ctx, wl, field):
+@pytest.mark.parametrize("int_tables", [True, False])
+def test_gpu_walk_equals_the_cpu_walk(dpb, ctx, wl, field, int_tables):
+    """int_tables: the integer tensors stay integers on the device (the default) or become field tables at upload."""
     prover = importlib.import_module("deep_prove_b200.prover")
     want, _ = wl.transformer_path(OracleBackend(field), wl.TINY, seed=7)
-    got = wl.run_transformer_path(dpb, prover, ctx, wl.TINY, field=field, seed=7)
+    got = wl.run_transformer_path(dpb, prover, ctx, wl.TINY, field=field, seed=7, int_tables=int_tables)
     assert [r[:2] for r in got["records"]] == [r[:2] for r in want]
     for (name, kind, g), (_, _, w) in zip(got["records"], want):
         assert g == w, f"{name} ({kind}) differs from the CPU restatement"
