@@ -1,0 +1,334 @@
+// C ABI: multi-scalar multiplication over BN254 G1, the arithmetic of the commitment scheme's commit
+// (HyperKZG commits to a multilinear polynomial as sum_i evals[i] * G_i over the SRS's G1 points;
+// CommittedPolynomial::batch_commit, zkml/src/poly_commit/context.rs:56-90, one MSM per chunk of at most 2^20
+// evaluations).
+//
+// Bucket method (Pippenger) with windows of c bits:
+//   1. msm_count      per scalar and window: which bucket it goes to (its c-bit digit; zero digits are skipped);
+//                     a histogram of the (window, bucket) keys
+//   2. msm_scan       exclusive prefix sums of the histogram: where every bucket's list starts
+//   3. msm_scatter    the point indices, grouped by bucket
+//   4. msm_buckets    one thread per bucket adds its points up (mixed Jacobian + affine additions)
+//   5. msm_reduce     per window sum_b b * B_b: a thread takes a run of 64 buckets (running sums from the top, plus
+//                     the run's offset times its total), a block adds its 256 runs up in shared memory
+//   6. host           the blocks' partial sums per window (a handful of points), the windows combined by c
+//                     doublings each, one inversion for the affine result.
+// Integer tables (DPB_FR_I32 / DPB_FR_I64) enter as magnitudes: a negative scalar adds the negated point, and only
+// the one to four windows their bits reach are ever touched: committing to quantised tensors and 16-bit lookup
+// columns costs a fraction of a commit to full-width scalars.
+#include <vector>
+
+#include "common.cuh"
+#include "g1_bn254.cuh"
+
+struct dpb_g1_bases {
+    dpb_ctx* ctx = nullptr;
+    uint64_t n = 0;
+    dpb::G1Affine* dev = nullptr;
+};
+
+namespace dpb {
+
+constexpr int kMsmRun = 64;         // buckets a reduction thread walks
+constexpr int kMsmReduceThreads = 256;
+
+struct MsmScalars {
+    const void* ptr;
+    int dtype;  // DPB_FR (Montgomery), DPB_FR_I32, DPB_FR_I64
+};
+
+// the scalar as a 256-bit magnitude (canonical integer below r) and a sign
+__device__ __forceinline__ void msm_scalar(const MsmScalars& s, uint64_t i, uint64_t (&mag)[4], bool& neg) {
+    neg = false;
+    if (s.dtype == DPB_FR) {
+        const Fr v = fr_from_mont(FrFam::load(s.ptr, DPB_FR, i));
+        mag[0] = v.l[0];
+        mag[1] = v.l[1];
+        mag[2] = v.l[2];
+        mag[3] = v.l[3];
+        return;
+    }
+    const int64_t x = s.dtype == DPB_FR_I32 ? (int64_t)((const int32_t*)s.ptr)[i] : ((const int64_t*)s.ptr)[i];
+    neg = x < 0;
+    mag[0] = neg ? (uint64_t)0 - (uint64_t)x : (uint64_t)x;
+    mag[1] = mag[2] = mag[3] = 0;
+}
+__device__ __forceinline__ uint32_t msm_digit(const uint64_t (&mag)[4], uint32_t w, uint32_t c) {
+    const uint32_t bit = w * c, limb = bit >> 6, off = bit & 63;
+    if (limb >= 4) return 0;
+    uint64_t v = mag[limb] >> off;
+    if (off + c > 64 && limb + 1 < 4) v |= mag[limb + 1] << (64 - off);
+    return (uint32_t)(v & ((1ull << c) - 1));
+}
+
+__global__ void __launch_bounds__(kThreads)
+    msm_count(MsmScalars s, uint64_t n, uint32_t c, uint32_t windows, uint32_t* __restrict__ counts) {
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        uint64_t mag[4];
+        bool neg;
+        msm_scalar(s, i, mag, neg);
+        for (uint32_t w = 0; w < windows; w++) {
+            const uint32_t d = msm_digit(mag, w, c);
+            if (d) atomicAdd(&counts[((size_t)w << c) + d], 1u);
+        }
+    }
+}
+
+// exclusive scan of `n` counters by one block (n is at most a few million; the scan is a sliver of the MSM)
+__global__ void __launch_bounds__(1024) msm_scan(const uint32_t* __restrict__ counts, uint32_t* __restrict__ offsets, uint64_t n) {
+    __shared__ uint32_t part[1024];
+    const uint64_t per = (n + blockDim.x - 1) / blockDim.x;
+    const uint64_t lo = (uint64_t)threadIdx.x * per, hi = lo + per < n ? lo + per : n;
+    uint32_t sum = 0;
+    for (uint64_t i = lo; i < hi; i++) sum += counts[i];
+    part[threadIdx.x] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t run = 0;
+        for (uint32_t t = 0; t < blockDim.x; t++) {
+            const uint32_t v = part[t];
+            part[t] = run;
+            run += v;
+        }
+    }
+    __syncthreads();
+    uint32_t run = part[threadIdx.x];
+    for (uint64_t i = lo; i < hi; i++) {
+        offsets[i] = run;
+        run += counts[i];
+    }
+}
+
+__global__ void __launch_bounds__(kThreads)
+    msm_scatter(MsmScalars s, uint64_t n, uint32_t c, uint32_t windows, const uint32_t* __restrict__ offsets,
+                uint32_t* __restrict__ cursor, uint32_t* __restrict__ items) {
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        uint64_t mag[4];
+        bool neg;
+        msm_scalar(s, i, mag, neg);
+        for (uint32_t w = 0; w < windows; w++) {
+            const uint32_t d = msm_digit(mag, w, c);
+            if (!d) continue;
+            const size_t key = ((size_t)w << c) + d;
+            const uint32_t at = atomicAdd(&cursor[key], 1u);
+            items[offsets[key] + at] = (uint32_t)i | (neg ? 0x80000000u : 0u);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kThreads)
+    msm_buckets(const G1Affine* __restrict__ bases, const uint32_t* __restrict__ offsets,
+                const uint32_t* __restrict__ counts, const uint32_t* __restrict__ items, uint64_t n_keys,
+                G1Jac* __restrict__ buckets) {
+    const uint64_t key = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (key >= n_keys) return;
+    G1Jac acc = g1_infinity();
+    const uint32_t lo = offsets[key], cnt = counts[key];
+    for (uint32_t j = 0; j < cnt; j++) {
+        const uint32_t it = items[lo + j];
+        G1Affine p = bases[it & 0x7fffffffu];
+        if (it & 0x80000000u) p = g1_affine_neg(p);
+        acc = g1_add_mixed(acc, p);
+    }
+    buckets[key] = acc;
+}
+
+// out[w * blocks_per_window + blk] = sum over the block's buckets b of b * B_b
+__global__ void __launch_bounds__(kMsmReduceThreads)
+    msm_reduce(const G1Jac* __restrict__ buckets, uint32_t c, uint32_t blocks_per_window, G1Jac* __restrict__ out) {
+    __shared__ G1Jac sh[kMsmReduceThreads];
+    const uint32_t w = blockIdx.x / blocks_per_window, blk = blockIdx.x % blocks_per_window;
+    const uint64_t n_b = 1ull << c;
+    const uint64_t run_id = (uint64_t)blk * kMsmReduceThreads + threadIdx.x;
+    const uint64_t b_lo = run_id * kMsmRun;  // first bucket of this thread's run
+    G1Jac total = g1_infinity();
+    if (b_lo < n_b) {
+        const uint64_t b_hi = b_lo + kMsmRun < n_b ? b_lo + kMsmRun : n_b;
+        const G1Jac* B = buckets + ((size_t)w << c);
+        G1Jac running = g1_infinity(), sum = g1_infinity();
+        for (uint64_t b = b_hi; b-- > b_lo;) {  // sum = sum_b (b - b_lo + 1) B_b
+            running = g1_add(running, B[b]);
+            sum = g1_add(sum, running);
+        }
+        // sum_b b B_b = sum + (b_lo - 1) * running; bucket 0 is empty, so for b_lo = 0 the term (-1) * running
+        // is cancelled by counting one copy less: walk it as sum - running
+        if (b_lo == 0) {
+            G1Jac neg = running;
+            neg.Y = fq_neg(neg.Y);
+            total = g1_add(sum, neg);
+        } else {
+            total = g1_add(sum, g1_mul_small(running, (uint32_t)(b_lo - 1)));
+        }
+    }
+    sh[threadIdx.x] = total;
+    __syncthreads();
+    for (uint32_t s = kMsmReduceThreads / 2; s > 0; s >>= 1) {
+        if (threadIdx.x < s) sh[threadIdx.x] = g1_add(sh[threadIdx.x], sh[threadIdx.x + s]);
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = sh[0];
+}
+
+__global__ void __launch_bounds__(kThreads) msm_bases_to_mont(G1Affine* p, uint64_t n, unsigned int* bad) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    G1Affine a = p[i];
+    if (!g1_affine_is_infinity(a)) {
+        if (fq_geq_q(a.x) || fq_geq_q(a.y)) {
+            atomicAdd(bad, 1u);
+            return;
+        }
+        a.x = fq_to_mont(a.x);
+        a.y = fq_to_mont(a.y);
+        if (!g1_affine_on_curve(a)) atomicAdd(bad, 1u);
+    }
+    p[i] = a;
+}
+
+static uint32_t msm_window_bits(uint64_t n) {
+    uint32_t lg = 0;
+    while ((1ull << lg) < n) lg++;
+    if (lg >= 18) return 16;
+    if (lg >= 14) return 13;
+    if (lg >= 10) return 10;
+    return 8;
+}
+
+}  // namespace dpb
+
+using namespace dpb;
+
+extern "C" {
+
+int dpb_g1_bases_from_host(dpb_ctx* ctx, const void* affine_xy, uint64_t n, dpb_g1_bases** out) {
+    if (!ctx || !affine_xy || !out) return fail(DPB_EINVAL, "null argument");
+    if (n == 0 || n > (1ull << 31)) return fail(DPB_EINVAL, "number of points %llu outside 1..2^31", (unsigned long long)n);
+    dpb_g1_bases* b = new (std::nothrow) dpb_g1_bases();
+    if (!b) return fail(DPB_ENOMEM, "host allocation failed");
+    b->ctx = ctx;
+    b->n = n;
+    void* p = nullptr;
+    int rc = device_alloc(ctx, n * sizeof(G1Affine), &p);
+    if (rc != DPB_OK) {
+        delete b;
+        return rc;
+    }
+    b->dev = (G1Affine*)p;
+    unsigned int* bad = nullptr;
+    rc = device_alloc(ctx, sizeof(unsigned int), (void**)&bad);
+    unsigned int h_bad = 0;
+    cudaError_t e = cudaSuccess;
+    if (rc == DPB_OK) {
+        e = cudaMemcpyAsync(p, affine_xy, n * sizeof(G1Affine), cudaMemcpyHostToDevice, ctx->stream);
+        if (e == cudaSuccess) e = cudaMemsetAsync(bad, 0, sizeof(unsigned int), ctx->stream);
+        if (e == cudaSuccess) {
+            msm_bases_to_mont<<<(uint32_t)((n + kThreads - 1) / kThreads), kThreads, 0, ctx->stream>>>(b->dev, n, bad);
+            e = cudaGetLastError();
+        }
+        if (e == cudaSuccess) e = cudaMemcpyAsync(&h_bad, bad, sizeof(unsigned int), cudaMemcpyDeviceToHost, ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    }
+    device_free(ctx, bad);
+    if (rc == DPB_OK && e != cudaSuccess) rc = fail(DPB_ECUDA, "uploading G1 points: %s", cudaGetErrorString(e));
+    if (rc == DPB_OK && h_bad) rc = fail(DPB_EINVAL, "%u points are not on the curve or have coordinates >= q", h_bad);
+    if (rc != DPB_OK) {
+        device_free(ctx, p);
+        delete b;
+        return rc;
+    }
+    *out = b;
+    return DPB_OK;
+}
+
+uint64_t dpb_g1_bases_len(const dpb_g1_bases* b) { return b ? b->n : 0; }
+
+void dpb_g1_bases_free(dpb_g1_bases* b) {
+    if (!b) return;
+    device_free(b->ctx, b->dev);
+    delete b;
+}
+
+int dpb_msm_g1(dpb_ctx* ctx, const dpb_g1_bases* bases, const dpb_mle* scalars, void* out_affine_xy) {
+    if (!ctx || !bases || !scalars || !out_affine_xy) return fail(DPB_EINVAL, "null argument");
+    if (bases->ctx != ctx || scalars->ctx != ctx) return fail(DPB_EINVAL, "bases or scalars belong to another context");
+    if (scalars->dtype != DPB_FR && scalars->dtype != DPB_FR_I32 && scalars->dtype != DPB_FR_I64)
+        return fail(DPB_EINVAL, "scalars must be a BN254 table (DPB_FR, DPB_FR_I32 or DPB_FR_I64), not dtype %d", scalars->dtype);
+    const uint64_t n = scalars->len;
+    if (n > bases->n)
+        return fail(DPB_EINVAL, "%llu scalars but only %llu points", (unsigned long long)n, (unsigned long long)bases->n);
+    const uint32_t c = msm_window_bits(n);
+    const uint32_t scalar_bits = scalars->dtype == DPB_FR ? 254 : scalars->dtype == DPB_FR_I32 ? 32 : 64;
+    const uint32_t windows = (scalar_bits + c - 1) / c;
+    const size_t n_keys = (size_t)windows << c;
+    const uint32_t runs = (uint32_t)(((1ull << c) + kMsmRun - 1) / kMsmRun);
+    const uint32_t blocks_per_window = (runs + kMsmReduceThreads - 1) / kMsmReduceThreads;
+    const size_t n_partials = (size_t)windows * blocks_per_window;
+    // one block of device memory: [counts | offsets | cursor | items | buckets | partials]
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        const size_t o = off;
+        off = (off + bytes + 255) & ~(size_t)255;
+        return o;
+    };
+    const size_t o_counts = take(n_keys * 4), o_offsets = take(n_keys * 4), o_cursor = take(n_keys * 4),
+                 o_items = take((size_t)n * windows * 4), o_buckets = take(n_keys * sizeof(G1Jac)),
+                 o_part = take(n_partials * sizeof(G1Jac));
+    void* slab = nullptr;
+    DPB_TRY(device_alloc(ctx, off, &slab));
+    char* base = (char*)slab;
+    uint32_t* counts = (uint32_t*)(base + o_counts);
+    uint32_t* offsets = (uint32_t*)(base + o_offsets);
+    uint32_t* cursor = (uint32_t*)(base + o_cursor);
+    uint32_t* items = (uint32_t*)(base + o_items);
+    G1Jac* buckets = (G1Jac*)(base + o_buckets);
+    G1Jac* partials = (G1Jac*)(base + o_part);
+    MsmScalars s;
+    s.ptr = scalars->ptr;
+    s.dtype = scalars->dtype;
+    std::vector<G1Jac> h_part(n_partials);
+    cudaError_t e = cudaMemsetAsync(counts, 0, o_items - o_counts, ctx->stream);  // counts, offsets, cursor
+    if (e == cudaSuccess) {
+        msm_count<<<grid_for(ctx, n), kThreads, 0, ctx->stream>>>(s, n, c, windows, counts);
+        msm_scan<<<1, 1024, 0, ctx->stream>>>(counts, offsets, n_keys);
+        msm_scatter<<<grid_for(ctx, n), kThreads, 0, ctx->stream>>>(s, n, c, windows, offsets, cursor, items);
+        msm_buckets<<<(uint32_t)((n_keys + kThreads - 1) / kThreads), kThreads, 0, ctx->stream>>>(
+            bases->dev, offsets, counts, items, n_keys, buckets);
+        msm_reduce<<<(uint32_t)n_partials, kMsmReduceThreads, 0, ctx->stream>>>(buckets, c, blocks_per_window, partials);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(h_part.data(), partials, n_partials * sizeof(G1Jac), cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    device_free(ctx, slab);
+    if (e != cudaSuccess) return fail(DPB_ECUDA, "msm: %s", cudaGetErrorString(e));
+    // windows from the top: total = 2^c * total + window sum
+    G1Jac total = g1_infinity();
+    for (uint32_t w = windows; w-- > 0;) {
+        for (uint32_t d = 0; d < c; d++) total = g1_double(total);
+        for (uint32_t k = 0; k < blocks_per_window; k++) total = g1_add(total, h_part[(size_t)w * blocks_per_window + k]);
+    }
+    const G1Affine a = g1_to_affine(total);
+    Fq xy[2];
+    if (g1_affine_is_infinity(a)) {
+        xy[0] = xy[1] = fq_zero();
+    } else {
+        xy[0] = fq_from_mont(a.x);
+        xy[1] = fq_from_mont(a.y);
+    }
+    memcpy(out_affine_xy, xy, sizeof xy);
+    return DPB_OK;
+}
+
+int dpb_pcs_batch_commit(dpb_ctx* ctx, const dpb_g1_bases* bases, dpb_mle* const* polys, uint32_t n_polys,
+                         void* out_affine_xy) {
+    if (!ctx || !bases || !polys || !out_affine_xy) return fail(DPB_EINVAL, "null argument");
+    for (uint32_t i = 0; i < n_polys; i++) {
+        if (!polys[i]) return fail(DPB_EINVAL, "polynomial %u is null", i);
+        DPB_TRY(dpb_msm_g1(ctx, bases, polys[i], (char*)out_affine_xy + (size_t)i * 64));
+    }
+    return DPB_OK;
+}
+
+}  // extern "C"
