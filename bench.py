@@ -485,17 +485,23 @@ def workload_record(dpb, prover, ctx, args):
     # warm-up: one whole walk, so that kernels are loaded and the stream-ordered memory pool has grown to the
     # walk's largest allocation (the claim batching's fold buffers); a prover process is in this state after its
     # first proof
-    wl.run_transformer_path(dpb, prover, ctx, shape, field="fr", seed=args.seed + 1)
-    got = wl.run_transformer_path(dpb, prover, ctx, shape, field="fr", seed=args.seed)
+    wl.run_transformer_path(dpb, prover, ctx, shape, field="fr", seed=args.seed + 1, with_commit=True)
+    got = wl.run_transformer_path(dpb, prover, ctx, shape, field="fr", seed=args.seed, with_commit=True)
     rec = {"workload": "GPT-2-small (12 layers, d_model 768, 12 heads, FFN 3072, vocab 50257), 512 tokens: every "
                        "sumcheck / fold / logup-GKR call of the forward graph, BN254 Fr, seeded synthetic integer "
                        "tensors resident on the device (BASELINE.json configs[2] shapes)",
            "field": "bn254", "ms": got["seconds"] * 1e3, "tokens_per_s": got["tokens_per_s"],
            "by_kind_ms": {k: v * 1e3 for k, v in sorted(got["by_kind"].items(), key=lambda kv: -kv[1])},
            "calls": got["calls"], "wall_seconds_with_input_generation": got["wall_seconds"],
+           "witness_commit": {
+               "ms": got["commit_seconds"] * 1e3,
+               "what": "every lookup layer's witness columns committed: one BN254 G1 multi-scalar multiplication "
+                       "per chunk of at most 2^20 evaluations against device-made stand-in bases "
+                       "(zkml/src/lookup/context.rs:420-422); not part of the path, reported beside it",
+               "tokens_per_s_path_plus_witness_commit": shape.seq / (got["seconds"] + got["commit_seconds"])},
            "timing": "wall clock per call with a device synchronisation on both sides, summed; generation and upload "
                      "of the synthetic tensors are outside",
-           "excludes": "inference, HyperKZG commit/open and host orchestration of the reference's prove_full; the "
+           "excludes": "inference, HyperKZG opening and host orchestration of the reference's prove_full; the "
                        "reference's published 1.12 tokens/s (24-core EPYC, whole prover) is a different scope"}
     sample = wl.CPU_SAMPLE
     gpu_s = wl.run_transformer_path(dpb, prover, ctx, sample, field="fr", seed=args.seed)

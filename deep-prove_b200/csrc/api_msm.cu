@@ -8,7 +8,9 @@
 //                     a histogram of the (window, bucket) keys
 //   2. msm_scan       exclusive prefix sums of the histogram: where every bucket's list starts
 //   3. msm_scatter    the point indices, grouped by bucket
-//   4. msm_buckets    one thread per bucket adds its points up (mixed Jacobian + affine additions)
+//   4. msm_buckets    one thread per bucket adds its points up (mixed Jacobian + affine additions); a bucket with
+//                     more than 96 points (small integers crowd a wide window's low buckets) goes to a list that
+//                     msm_heavy_buckets works off with one block per bucket
 //   5. msm_reduce     per window sum_b b * B_b: a thread takes a run of 64 buckets (running sums from the top, plus
 //                     the run's offset times its total), a block adds its 256 runs up in shared memory
 //   6. host           the blocks' partial sums per window (a handful of points), the windows combined by c
@@ -118,14 +120,20 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
+constexpr uint32_t kMsmHeavy = 96;  // a bucket with more points than this is summed by a whole block
+
 __global__ void __launch_bounds__(kThreads)
     msm_buckets(const G1Affine* __restrict__ bases, const uint32_t* __restrict__ offsets,
                 const uint32_t* __restrict__ counts, const uint32_t* __restrict__ items, uint64_t n_keys,
-                G1Jac* __restrict__ buckets) {
+                G1Jac* __restrict__ buckets, uint32_t* __restrict__ heavy_list, uint32_t* __restrict__ heavy_count) {
     const uint64_t key = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (key >= n_keys) return;
-    G1Jac acc = g1_infinity();
     const uint32_t lo = offsets[key], cnt = counts[key];
+    if (cnt > kMsmHeavy) {  // skewed digits (small integers in a wide window): left to msm_heavy_buckets
+        heavy_list[atomicAdd(heavy_count, 1u)] = (uint32_t)key;
+        return;
+    }
+    G1Jac acc = g1_infinity();
     for (uint32_t j = 0; j < cnt; j++) {
         const uint32_t it = items[lo + j];
         G1Affine p = bases[it & 0x7fffffffu];
@@ -133,6 +141,35 @@ __global__ void __launch_bounds__(kThreads)
         acc = g1_add_mixed(acc, p);
     }
     buckets[key] = acc;
+}
+
+// one block per heavy bucket: every thread adds a strided share of the bucket's points, then a tree in shared memory
+__global__ void __launch_bounds__(kMsmReduceThreads)
+    msm_heavy_buckets(const G1Affine* __restrict__ bases, const uint32_t* __restrict__ offsets,
+                      const uint32_t* __restrict__ counts, const uint32_t* __restrict__ items,
+                      const uint32_t* __restrict__ heavy_list, const uint32_t* __restrict__ heavy_count,
+                      G1Jac* __restrict__ buckets) {
+    __shared__ G1Jac sh[kMsmReduceThreads];
+    const uint32_t n_heavy = *heavy_count;
+    for (uint32_t h = blockIdx.x; h < n_heavy; h += gridDim.x) {
+        const uint32_t key = heavy_list[h];
+        const uint32_t lo = offsets[key], cnt = counts[key];
+        G1Jac acc = g1_infinity();
+        for (uint32_t j = threadIdx.x; j < cnt; j += blockDim.x) {
+            const uint32_t it = items[lo + j];
+            G1Affine p = bases[it & 0x7fffffffu];
+            if (it & 0x80000000u) p = g1_affine_neg(p);
+            acc = g1_add_mixed(acc, p);
+        }
+        sh[threadIdx.x] = acc;
+        __syncthreads();
+        for (uint32_t s = kMsmReduceThreads / 2; s > 0; s >>= 1) {
+            if (threadIdx.x < s) sh[threadIdx.x] = g1_add(sh[threadIdx.x], sh[threadIdx.x + s]);
+            __syncthreads();
+        }
+        if (threadIdx.x == 0) buckets[key] = sh[0];
+        __syncthreads();
+    }
 }
 
 // out[w * blocks_per_window + blk] = sum over the block's buckets b of b * B_b
@@ -185,6 +222,20 @@ __global__ void __launch_bounds__(kThreads) msm_bases_to_mont(G1Affine* p, uint6
         if (!g1_affine_on_curve(a)) atomicAdd(bad, 1u);
     }
     p[i] = a;
+}
+
+// point i = (first + i) * G for the generator G = (1, 2): valid, distinct points for benchmarks and tests
+__global__ void __launch_bounds__(kThreads) msm_synthetic_bases(G1Affine* out, uint64_t n, uint32_t first) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    G1Affine g;
+    Fq one, two;
+    one.l[0] = 1;
+    two.l[0] = 2;
+    one.l[1] = one.l[2] = one.l[3] = two.l[1] = two.l[2] = two.l[3] = 0;
+    g.x = fq_to_mont(one);
+    g.y = fq_to_mont(two);
+    out[i] = g1_to_affine(g1_mul_small(g1_from_affine(g), first + (uint32_t)i));
 }
 
 static uint32_t msm_window_bits(uint64_t n) {
@@ -242,6 +293,33 @@ int dpb_g1_bases_from_host(dpb_ctx* ctx, const void* affine_xy, uint64_t n, dpb_
     return DPB_OK;
 }
 
+int dpb_g1_bases_synthetic(dpb_ctx* ctx, uint64_t n, uint32_t first_multiple, dpb_g1_bases** out) {
+    if (!ctx || !out) return fail(DPB_EINVAL, "null argument");
+    if (n == 0 || first_multiple == 0 || n + first_multiple > (1ull << 31))
+        return fail(DPB_EINVAL, "multiples %u .. %llu of the generator are outside 1..2^31", first_multiple,
+                    (unsigned long long)(n + first_multiple - 1));
+    dpb_g1_bases* b = new (std::nothrow) dpb_g1_bases();
+    if (!b) return fail(DPB_ENOMEM, "host allocation failed");
+    b->ctx = ctx;
+    b->n = n;
+    void* p = nullptr;
+    int rc = device_alloc(ctx, n * sizeof(G1Affine), &p);
+    if (rc != DPB_OK) {
+        delete b;
+        return rc;
+    }
+    b->dev = (G1Affine*)p;
+    msm_synthetic_bases<<<(uint32_t)((n + kThreads - 1) / kThreads), kThreads, 0, ctx->stream>>>(b->dev, n, first_multiple);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        device_free(ctx, p);
+        delete b;
+        return fail(DPB_ECUDA, "synthetic bases: %s", cudaGetErrorString(e));
+    }
+    *out = b;
+    return DPB_OK;
+}
+
 uint64_t dpb_g1_bases_len(const dpb_g1_bases* b) { return b ? b->n : 0; }
 
 void dpb_g1_bases_free(dpb_g1_bases* b) {
@@ -273,7 +351,7 @@ int dpb_msm_g1(dpb_ctx* ctx, const dpb_g1_bases* bases, const dpb_mle* scalars, 
         return o;
     };
     const size_t o_counts = take(n_keys * 4), o_offsets = take(n_keys * 4), o_cursor = take(n_keys * 4),
-                 o_items = take((size_t)n * windows * 4), o_buckets = take(n_keys * sizeof(G1Jac)),
+                 o_heavy_count = take(256), o_items = take((size_t)n * windows * 4), o_heavy = take(n_keys * 4), o_buckets = take(n_keys * sizeof(G1Jac)),
                  o_part = take(n_partials * sizeof(G1Jac));
     void* slab = nullptr;
     DPB_TRY(device_alloc(ctx, off, &slab));
@@ -282,19 +360,29 @@ int dpb_msm_g1(dpb_ctx* ctx, const dpb_g1_bases* bases, const dpb_mle* scalars, 
     uint32_t* offsets = (uint32_t*)(base + o_offsets);
     uint32_t* cursor = (uint32_t*)(base + o_cursor);
     uint32_t* items = (uint32_t*)(base + o_items);
+    uint32_t* heavy_list = (uint32_t*)(base + o_heavy);
+    uint32_t* heavy_count = (uint32_t*)(base + o_heavy_count);
     G1Jac* buckets = (G1Jac*)(base + o_buckets);
     G1Jac* partials = (G1Jac*)(base + o_part);
     MsmScalars s;
     s.ptr = scalars->ptr;
     s.dtype = scalars->dtype;
     std::vector<G1Jac> h_part(n_partials);
-    cudaError_t e = cudaMemsetAsync(counts, 0, o_items - o_counts, ctx->stream);  // counts, offsets, cursor
+    cudaError_t e = cudaMemsetAsync(counts, 0, o_items - o_counts, ctx->stream);  // counts, offsets, cursor, heavy count
     if (e == cudaSuccess) {
         msm_count<<<grid_for(ctx, n), kThreads, 0, ctx->stream>>>(s, n, c, windows, counts);
         msm_scan<<<1, 1024, 0, ctx->stream>>>(counts, offsets, n_keys);
         msm_scatter<<<grid_for(ctx, n), kThreads, 0, ctx->stream>>>(s, n, c, windows, offsets, cursor, items);
         msm_buckets<<<(uint32_t)((n_keys + kThreads - 1) / kThreads), kThreads, 0, ctx->stream>>>(
-            bases->dev, offsets, counts, items, n_keys, buckets);
+            bases->dev, offsets, counts, items, n_keys, buckets, heavy_list, heavy_count);
+        {
+            // at most n * windows / kMsmHeavy buckets can be heavy; idle blocks leave at once
+            uint64_t max_heavy = (uint64_t)n * windows / kMsmHeavy + 1;
+            if (max_heavy > n_keys) max_heavy = n_keys;
+            const uint32_t cap = (uint32_t)ctx->sm_count * 16;
+            msm_heavy_buckets<<<(uint32_t)(max_heavy < cap ? max_heavy : cap), kMsmReduceThreads, 0, ctx->stream>>>(
+                bases->dev, offsets, counts, items, heavy_list, heavy_count, buckets);
+        }
         msm_reduce<<<(uint32_t)n_partials, kMsmReduceThreads, 0, ctx->stream>>>(buckets, c, blocks_per_window, partials);
         e = cudaGetLastError();
     }

@@ -156,8 +156,9 @@ DPB_HD Fq fq_from_mont(const Fq& a) {
     one.l[1] = one.l[2] = one.l[3] = 0;
     return fq_mul(a, one);
 }
-// a^(q - 2): the inverse (host: once per MSM, for the affine result)
-inline Fq fq_inv(const Fq& a) {
+// a^(q - 2): the inverse (once per MSM on the host, for the affine result; once per point when synthetic bases
+// are made on the device)
+DPB_HD Fq fq_inv(const Fq& a) {
     const uint64_t e[4] = {DPB_FQ_Q0 - 2, DPB_FQ_Q1, DPB_FQ_Q2, DPB_FQ_Q3};
     Fq r = fq_one();
     for (int i = 255; i >= 0; i--) {

@@ -110,8 +110,8 @@ DPB_HD G1Jac g1_mul_small(const G1Jac& p, uint32_t k) {
     return r;
 }
 
-// affine coordinates (host: one inversion)
-inline G1Affine g1_to_affine(const G1Jac& p) {
+// affine coordinates (one inversion)
+DPB_HD G1Affine g1_to_affine(const G1Jac& p) {
     G1Affine r;
     if (g1_is_infinity(p)) {
         r.x = r.y = fq_zero();

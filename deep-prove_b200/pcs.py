@@ -9,6 +9,7 @@ from . import _buf, _int, _pp, _u32, _u64, _vp, check, lib
 
 PCS_SIGNATURES = {
     "dpb_g1_bases_from_host": (_int, [_vp, _vp, _u64, _pp]),
+    "dpb_g1_bases_synthetic": (_int, [_vp, _u64, _u32, _pp]),
     "dpb_g1_bases_len": (_u64, [_vp]),
     "dpb_g1_bases_free": (None, [_vp]),
     "dpb_msm_g1": (_int, [_vp, _vp, _vp, _vp]),
@@ -38,12 +39,22 @@ def array_to_points(arr):
 class G1Bases:
     """dpb_g1_bases: the points an MSM multiplies (HyperKZG's prover setup)."""
 
-    def __init__(self, ctx, points):
+    def __init__(self, ctx, points, _h=None):
         self.ctx = ctx
+        if _h is not None:
+            self.h = _h
+            return
         arr = points if isinstance(points, np.ndarray) else points_to_array(points)
         arr = np.ascontiguousarray(arr, dtype=np.uint64).reshape(-1, 8)
         self.h = ctypes.c_void_p()
         check(lib.dpb_g1_bases_from_host(ctx.h, _buf(arr), arr.shape[0], ctypes.byref(self.h)))
+
+    @staticmethod
+    def synthetic(ctx, n, first_multiple=1):
+        """dpb_g1_bases_synthetic: point i = (first_multiple + i) * G, made on the device."""
+        h = ctypes.c_void_p()
+        check(lib.dpb_g1_bases_synthetic(ctx.h, n, first_multiple, ctypes.byref(h)))
+        return G1Bases(ctx, None, _h=h)
 
     def __len__(self):
         return lib.dpb_g1_bases_len(self.h)

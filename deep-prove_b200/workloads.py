@@ -146,10 +146,13 @@ class PathTimer:
         return _Span()
 
 
-def transformer_path(be, shape, seed=0, blocks=None, with_final=True):
+def transformer_path(be, shape, seed=0, blocks=None, with_final=True, with_commit=False):
     """Walks the path calls of `shape` on backend `be`.  Returns (records, timer): records is a list of
     (name, kind, payload bytes); timer.by_kind holds seconds per kind of call.  `blocks` limits the number of
-    transformer blocks walked (default: all); `with_final=False` leaves out everything after the last block."""
+    transformer blocks walked (default: all); `with_final=False` leaves out everything after the last block.
+    with_commit: every lookup layer also commits to its witness columns (one multi-scalar multiplication per
+    chunk of at most 2^commit_chunk_log2 evaluations, zkml/src/lookup/context.rs:420-422), timed as its own kind
+    "witness_commit": the commitment scheme's share of a proof, next to the path's."""
     rng = np.random.default_rng(seed)
     T = be.new_transcript()
     timer = PathTimer(be)
@@ -166,6 +169,7 @@ def transformer_path(be, shape, seed=0, blocks=None, with_final=True):
     for k in ("requant", "gelu", "exp", "norm"):
         counts[k] = be.new_counts(bits)
     committed = []  # (name, table handle, num entries): everything the claim batching at the end opens
+    srs = be.commit_setup(1 << shape.commit_chunk_log2) if with_commit else None
 
     act_bits = bits + 2
     specs = {
@@ -267,6 +271,11 @@ def transformer_path(be, shape, seed=0, blocks=None, with_final=True):
         # the witness columns are committed polynomials: they are opened at the end
         for j, col in enumerate(ins + outs):
             committed.append((f"{name}.w{j}", col, 1 << n2d))
+        if with_commit:
+            n_chunks = 1 << max(n2d - shape.commit_chunk_log2, 0)
+            with timer("witness_commit"):
+                chunks = [c_ for col in ins + outs for c_ in be.chunks(col, n_chunks)]
+                rec.append((name + ".commit", "commit", be.commit(srs, chunks)))
         be.free(*extra_owner)
         be.keep(wit["owner"])
 
@@ -442,6 +451,7 @@ def transformer_path(be, shape, seed=0, blocks=None, with_final=True):
                 polys.append((be.chunks(tab, n_chunks), [(point, ev)]))
             rec.append(("claim_batching", "claim_batching", be.claims_batching(T, polys)))
     rec.append(("transcript", "state", be.transcript_state(T)))
+    be.free(srs)
     be.release()
     return rec, timer
 
@@ -536,6 +546,16 @@ class GpuBackend:
 
     def _pt(self, point):
         return np.ascontiguousarray(np.stack(point) if len(point) else np.zeros((0, self.w), np.uint64), dtype=np.uint64)
+
+    # -- commitments
+    def commit_setup(self, n):
+        import importlib
+        self.pcs = importlib.import_module("deep_prove_b200.pcs")
+        return self.pcs.G1Bases.synthetic(self.ctx, n, 1)
+
+    def commit(self, srs, tables):
+        pts = self.pcs.batch_commit(self.ctx, srs, tables)
+        return b"".join(int(x).to_bytes(32, "little") + int(y).to_bytes(32, "little") for x, y in pts)
 
     # -- tables
     def int_table(self, arr):
@@ -665,14 +685,17 @@ class GpuBackend:
 
 
 def run_transformer_path(dpb, prover, ctx, shape=GPT2_SMALL, field="fr", seed=0, blocks=None, with_final=True,
-                         int_tables=True):
-    """One walk on the GPU.  Returns dict(seconds, tokens_per_s, by_kind, calls, records)."""
+                         int_tables=True, with_commit=False):
+    """One walk on the GPU.  Returns dict(seconds, tokens_per_s, by_kind, calls, records); `seconds` and
+    `tokens_per_s` count the path's calls only, `commit_seconds` is the witness commitments' time (with_commit)."""
     be = GpuBackend(dpb, prover, ctx, field, int_tables)
     ctx.sync()
     t0 = time.perf_counter()
-    rec, timer = transformer_path(be, shape, seed, blocks, with_final)
+    rec, timer = transformer_path(be, shape, seed, blocks, with_final, with_commit)
     ctx.sync()
     wall = time.perf_counter() - t0
-    path_s = sum(timer.by_kind.values())
-    return dict(seconds=path_s, wall_seconds=wall, tokens_per_s=shape.seq / path_s if path_s else None,
+    commit_s = timer.by_kind.get("witness_commit", 0.0)
+    path_s = sum(timer.by_kind.values()) - commit_s
+    return dict(seconds=path_s, commit_seconds=commit_s, wall_seconds=wall,
+                tokens_per_s=shape.seq / path_s if path_s else None,
                 by_kind=dict(timer.by_kind), calls=dict(timer.calls), records=rec)

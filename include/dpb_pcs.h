@@ -29,6 +29,10 @@ typedef struct dpb_g1_bases dpb_g1_bases;
 /* The SRS's G1 points (HyperKZG's prover setup), kept on the device.  affine_xy: n points of 64 bytes.
  * Every point is checked to lie on y^2 = x^3 + 3 with coordinates below q; DPB_EINVAL otherwise. */
 int dpb_g1_bases_from_host(dpb_ctx* ctx, const void* affine_xy, uint64_t n, dpb_g1_bases** out);
+/* n valid, distinct points made on the device: point i = (first_multiple + i) * G for the generator G = (1, 2).
+ * A stand-in for an SRS in benchmarks and tests (an MSM treats its points as opaque); no reference counterpart:
+ * the reference loads or samples its setup on the host. */
+int dpb_g1_bases_synthetic(dpb_ctx* ctx, uint64_t n, uint32_t first_multiple, dpb_g1_bases** out);
 uint64_t dpb_g1_bases_len(const dpb_g1_bases* bases);
 void dpb_g1_bases_free(dpb_g1_bases* bases);
 

@@ -8,6 +8,7 @@ divided by, so each figure can be read against the HBM peak.
     python microbench.py --lookup [--field ..] [--log2 ..]   only the lookup witness lines
     python microbench.py --mlp          one dense + ReLU layer of the MLP configuration, per step
     python microbench.py --issue-rate   field products per second the integer pipes deliver (dpb_issue_rate_probe)
+    python microbench.py --msm          commit throughput (BN254 G1 multi-scalar multiplication)
     python microbench.py --latency      small sumchecks, one C call per proof, both fields,
                                                         with the resident last-rounds kernel and with one launch per round
 """
@@ -70,6 +71,35 @@ def issue_rate(dpb, ctx):
             best = max(best, ops)
         cyc = sms * 4 * mhz * 1e6 / (best / 32)
         print(f"{name:58s} {best / 1e9:10.2f} G/s   {cyc:8.1f} cycles per warp-wide operation per sub-partition")
+
+
+def msm_bench(dpb, ctx):
+    """Commit throughput: one MSM over 2^n G1 points, full-width field scalars and 32-bit integer tables."""
+    import importlib
+    pcs = importlib.import_module("deep_prove_b200.pcs")
+    from oracle import g1  # only to make a handful of valid points; the timing below is the library's alone
+    pts = pcs.points_to_array(g1.synthetic_bases(256, seed=1))
+    rng = np.random.default_rng(3)
+    print("# dpb_msm_g1: one commitment over 2^n points (mean of 5 after a warm-up), milliseconds and M points/s")
+    for n in (16, 18, 20):
+        N = 1 << n
+        bases = pcs.G1Bases(ctx, np.tile(pts, (N // 256, 1)))
+        t = rng.integers(0, 2**64, size=(N, 4), dtype=np.uint64)
+        t[:, 3] &= np.uint64((1 << 60) - 1)
+        tabs = {"field scalars (254 bits)": ctx.upload(t, dpb.FR),
+                "int32 table (quantised tensor)": ctx.upload_ints(rng.integers(-2**31, 2**31, size=N, dtype=np.int64), dpb.FR_I32),
+                "int32 table of 16-bit values (lookup column)": ctx.upload_ints(rng.integers(0, 2**16, size=N, dtype=np.int64), dpb.FR_I32)}
+        for name, m in tabs.items():
+            pcs.msm(ctx, bases, m)
+            ctx.sync()
+            t0 = time.perf_counter()
+            for _ in range(5):
+                pcs.msm(ctx, bases, m)
+            ctx.sync()
+            dt = (time.perf_counter() - t0) / 5
+            print(f"2^{n} {name:46s} {dt * 1e3:9.3f} ms  {N / dt / 1e6:9.1f} M points/s")
+            m.free()
+        bases.free()
 
 
 def latency(dpb, prover, ctx):
@@ -273,6 +303,7 @@ def main():
     ap.add_argument("--log2", type=int, default=22)
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--latency", action="store_true")
+    ap.add_argument("--msm", action="store_true", help="commit (G1 multi-scalar multiplication) throughput")
     ap.add_argument("--issue-rate", action="store_true", help="the integer pipes' product rates (dpb_issue_rate_probe)")
     ap.add_argument("--lookup", action="store_true", help="only the lookup witness lines")
     ap.add_argument("--mlp", action="store_true", help="the steps of one dense + ReLU layer of the MLP configuration")
@@ -281,6 +312,10 @@ def main():
     ctx = dpb.Context(0)
     if args.issue_rate:
         issue_rate(dpb, ctx)
+        ctx.close()
+        return
+    if args.msm:
+        msm_bench(dpb, ctx)
         ctx.close()
         return
     if args.latency:

@@ -69,6 +69,24 @@ class OracleBackend:
     def inv2(self):
         return self.F.inv(self.F.from_int(2))
 
+    # -- commitments: the synthetic bases are the multiples 1 G, 2 G, ... of the generator, so
+    # sum_i s_i * (i + 1) G = (sum_i s_i (i + 1) mod r) G: one scalar multiplication checks a whole MSM
+    def commit_setup(self, n):
+        return n
+
+    def commit(self, srs, tables):
+        from . import g1
+        if self.F is not orc.FrField:
+            raise ValueError("commitments are over BN254")
+        out = b""
+        for t in tables:
+            vals = self.F.table_to_ints(t)
+            assert len(vals) <= srs
+            k = sum(v * (i + 1) for i, v in enumerate(vals)) % g1.R_ORDER
+            x, y = g1.boundary(g1.mul(k, g1.GENERATOR))
+            out += int(x).to_bytes(32, "little") + int(y).to_bytes(32, "little")
+        return out
+
     # -- tables
     def int_table(self, arr):
         return self.F.table_from_i64(np.ascontiguousarray(arr, dtype=np.int64))

@@ -90,3 +90,15 @@ def test_gpu_walk_two_blocks_without_head(dpb, ctx, wl):
     want, _ = wl.transformer_path(OracleBackend("fr"), wl.TINY, seed=9, blocks=2, with_final=False)
     got = wl.run_transformer_path(dpb, prover, ctx, wl.TINY, field="fr", seed=9, blocks=2, with_final=False)
     assert [r for r in got["records"]] == want
+
+
+@pytest.mark.gpu
+def test_gpu_walk_with_witness_commitments(dpb, ctx, wl):
+    """The walk with every lookup layer's witness columns committed (one G1 multi-scalar multiplication per chunk):
+    the commitments equal the CPU restatement's, which gets each of them from ONE scalar multiplication because the
+    synthetic bases are consecutive multiples of the generator."""
+    prover = importlib.import_module("deep_prove_b200.prover")
+    want, _ = wl.transformer_path(OracleBackend("fr"), wl.TINY, seed=5, with_final=False, with_commit=True)
+    got = wl.run_transformer_path(dpb, prover, ctx, wl.TINY, field="fr", seed=5, with_final=False, with_commit=True)
+    assert got["records"] == want
+    assert sum(1 for r in want if r[1] == "commit") == 7 and got["commit_seconds"] > 0
