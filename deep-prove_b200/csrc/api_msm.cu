@@ -6,12 +6,12 @@
 // Bucket method (Pippenger) with windows of c bits:
 //   1. msm_count      per scalar and window: which bucket it goes to (its c-bit digit; zero digits are skipped);
 //                     a histogram of the (window, bucket) keys
-//   2. msm_scan       exclusive prefix sums of the histogram: where every bucket's list starts
+//   2. msm_scan_*     exclusive prefix sums of the histogram: where every bucket's list starts
 //   3. msm_scatter    the point indices, grouped by bucket
 //   4. msm_buckets    one thread per bucket adds its points up (mixed Jacobian + affine additions); a bucket with
 //                     more than 96 points (small integers crowd a wide window's low buckets) goes to a list that
 //                     msm_heavy_buckets works off with one block per bucket
-//   5. msm_reduce     per window sum_b b * B_b: a thread takes a run of 64 buckets (running sums from the top, plus
+//   5. msm_reduce     per window sum_b b * B_b: a thread takes a run of 16 buckets (running sums from the top, plus
 //                     the run's offset times its total), a block adds its 256 runs up in shared memory
 //   6. host           the blocks' partial sums per window (a handful of points), the windows combined by c
 //                     doublings each, one inversion for the affine result.
@@ -31,7 +31,7 @@ struct dpb_g1_bases {
 
 namespace dpb {
 
-constexpr int kMsmRun = 64;         // buckets a reduction thread walks
+constexpr int kMsmRun = 16;         // buckets a reduction thread walks
 constexpr int kMsmReduceThreads = 256;
 
 struct MsmScalars {
@@ -77,13 +77,35 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
-// exclusive scan of `n` counters by one block (n is at most a few million; the scan is a sliver of the MSM)
-__global__ void __launch_bounds__(1024) msm_scan(const uint32_t* __restrict__ counts, uint32_t* __restrict__ offsets, uint64_t n) {
-    __shared__ uint32_t part[1024];
-    const uint64_t per = (n + blockDim.x - 1) / blockDim.x;
-    const uint64_t lo = (uint64_t)threadIdx.x * per, hi = lo + per < n ? lo + per : n;
+// Exclusive scan of the histogram in three small launches: sums of tiles of 4096 counters, a scan of the tile sums
+// by one block, and the scan inside every tile (all global accesses coalesced, the serial part in shared memory).
+constexpr uint32_t kScanTile = 4096, kScanThreads = 256, kScanPer = kScanTile / kScanThreads;
+
+__global__ void __launch_bounds__(kScanThreads)
+    msm_scan_tile_sums(const uint32_t* __restrict__ counts, uint64_t n, uint32_t* __restrict__ tile_sums) {
+    __shared__ uint32_t sh[kScanThreads];
+    const uint64_t base = (uint64_t)blockIdx.x * kScanTile;
     uint32_t sum = 0;
-    for (uint64_t i = lo; i < hi; i++) sum += counts[i];
+    for (uint32_t j = 0; j < kScanPer; j++) {
+        const uint64_t i = base + (uint64_t)j * kScanThreads + threadIdx.x;
+        if (i < n) sum += counts[i];
+    }
+    sh[threadIdx.x] = sum;
+    __syncthreads();
+    for (uint32_t s = kScanThreads / 2; s > 0; s >>= 1) {
+        if (threadIdx.x < s) sh[threadIdx.x] += sh[threadIdx.x + s];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) tile_sums[blockIdx.x] = sh[0];
+}
+
+// in place: tile_sums[t] becomes the sum of the tiles before t (n_tiles is at most a few thousand)
+__global__ void __launch_bounds__(1024) msm_scan_tiles(uint32_t* __restrict__ tile_sums, uint32_t n_tiles) {
+    __shared__ uint32_t part[1024];
+    const uint32_t per = (n_tiles + blockDim.x - 1) / blockDim.x;
+    const uint32_t lo = threadIdx.x * per, hi = lo + per < n_tiles ? lo + per : n_tiles;
+    uint32_t sum = 0;
+    for (uint32_t i = lo; i < hi; i++) sum += tile_sums[i];
     part[threadIdx.x] = sum;
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -96,9 +118,48 @@ __global__ void __launch_bounds__(1024) msm_scan(const uint32_t* __restrict__ co
     }
     __syncthreads();
     uint32_t run = part[threadIdx.x];
-    for (uint64_t i = lo; i < hi; i++) {
-        offsets[i] = run;
-        run += counts[i];
+    for (uint32_t i = lo; i < hi; i++) {
+        const uint32_t v = tile_sums[i];
+        tile_sums[i] = run;
+        run += v;
+    }
+}
+
+__global__ void __launch_bounds__(kScanThreads)
+    msm_scan_in_tiles(const uint32_t* __restrict__ counts, const uint32_t* __restrict__ tile_offsets, uint64_t n,
+                      uint32_t* __restrict__ offsets) {
+    __shared__ uint32_t vals[kScanTile];
+    __shared__ uint32_t part[kScanThreads];
+    const uint64_t base = (uint64_t)blockIdx.x * kScanTile;
+    for (uint32_t j = 0; j < kScanPer; j++) {
+        const uint32_t k = j * kScanThreads + threadIdx.x;
+        vals[k] = base + k < n ? counts[base + k] : 0u;
+    }
+    __syncthreads();
+    uint32_t sum = 0;
+    for (uint32_t j = 0; j < kScanPer; j++) sum += vals[threadIdx.x * kScanPer + j];
+    part[threadIdx.x] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t run = tile_offsets[blockIdx.x];
+        for (uint32_t t = 0; t < kScanThreads; t++) {
+            const uint32_t v = part[t];
+            part[t] = run;
+            run += v;
+        }
+    }
+    __syncthreads();
+    uint32_t run = part[threadIdx.x];
+    for (uint32_t j = 0; j < kScanPer; j++) {
+        const uint32_t k = threadIdx.x * kScanPer + j;
+        const uint32_t v = vals[k];
+        vals[k] = run;
+        run += v;
+    }
+    __syncthreads();
+    for (uint32_t j = 0; j < kScanPer; j++) {
+        const uint32_t k = j * kScanThreads + threadIdx.x;
+        if (base + k < n) offsets[base + k] = vals[k];
     }
 }
 
@@ -351,7 +412,8 @@ int dpb_msm_g1(dpb_ctx* ctx, const dpb_g1_bases* bases, const dpb_mle* scalars, 
         return o;
     };
     const size_t o_counts = take(n_keys * 4), o_offsets = take(n_keys * 4), o_cursor = take(n_keys * 4),
-                 o_heavy_count = take(256), o_items = take((size_t)n * windows * 4), o_heavy = take(n_keys * 4), o_buckets = take(n_keys * sizeof(G1Jac)),
+                 o_heavy_count = take(256), o_items = take((size_t)n * windows * 4), o_heavy = take(n_keys * 4),
+                 o_tiles = take(((n_keys + kScanTile - 1) / kScanTile) * 4), o_buckets = take(n_keys * sizeof(G1Jac)),
                  o_part = take(n_partials * sizeof(G1Jac));
     void* slab = nullptr;
     DPB_TRY(device_alloc(ctx, off, &slab));
@@ -362,6 +424,8 @@ int dpb_msm_g1(dpb_ctx* ctx, const dpb_g1_bases* bases, const dpb_mle* scalars, 
     uint32_t* items = (uint32_t*)(base + o_items);
     uint32_t* heavy_list = (uint32_t*)(base + o_heavy);
     uint32_t* heavy_count = (uint32_t*)(base + o_heavy_count);
+    uint32_t* tile_sums = (uint32_t*)(base + o_tiles);
+    const uint32_t n_tiles = (uint32_t)((n_keys + kScanTile - 1) / kScanTile);
     G1Jac* buckets = (G1Jac*)(base + o_buckets);
     G1Jac* partials = (G1Jac*)(base + o_part);
     MsmScalars s;
@@ -371,7 +435,9 @@ int dpb_msm_g1(dpb_ctx* ctx, const dpb_g1_bases* bases, const dpb_mle* scalars, 
     cudaError_t e = cudaMemsetAsync(counts, 0, o_items - o_counts, ctx->stream);  // counts, offsets, cursor, heavy count
     if (e == cudaSuccess) {
         msm_count<<<grid_for(ctx, n), kThreads, 0, ctx->stream>>>(s, n, c, windows, counts);
-        msm_scan<<<1, 1024, 0, ctx->stream>>>(counts, offsets, n_keys);
+        msm_scan_tile_sums<<<n_tiles, kScanThreads, 0, ctx->stream>>>(counts, n_keys, tile_sums);
+        msm_scan_tiles<<<1, 1024, 0, ctx->stream>>>(tile_sums, n_tiles);
+        msm_scan_in_tiles<<<n_tiles, kScanThreads, 0, ctx->stream>>>(counts, tile_sums, n_keys, offsets);
         msm_scatter<<<grid_for(ctx, n), kThreads, 0, ctx->stream>>>(s, n, c, windows, offsets, cursor, items);
         msm_buckets<<<(uint32_t)((n_keys + kThreads - 1) / kThreads), kThreads, 0, ctx->stream>>>(
             bases->dev, offsets, counts, items, n_keys, buckets, heavy_list, heavy_count);

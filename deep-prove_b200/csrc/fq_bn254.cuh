@@ -18,6 +18,29 @@ struct alignas(16) Fq {
 #define DPB_FQ_Q3 0x30644e72e131a029ULL
 #define DPB_FQ_INV 0x87d20782e4866389ULL  // -q^{-1} mod 2^64
 
+}  // namespace dpb
+#if defined(__CUDACC__)
+#include "fq_words.cuh"
+namespace dpb {
+__device__ __forceinline__ frw::F8 fq_words(const Fq& a) {
+    frw::F8 r;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        r.w[2 * i] = (uint32_t)a.l[i];
+        r.w[2 * i + 1] = (uint32_t)(a.l[i] >> 32);
+    }
+    return r;
+}
+__device__ __forceinline__ Fq fq_from_words(const frw::F8& a) {
+    Fq r;
+#pragma unroll
+    for (int i = 0; i < 4; i++) r.l[i] = (uint64_t)a.w[2 * i] | ((uint64_t)a.w[2 * i + 1] << 32);
+    return r;
+}
+}  // namespace dpb
+#endif
+namespace dpb {
+
 // (hi, lo) = a * b + c + d; never overflows 128 bits
 DPB_HD void fq_mac(uint64_t a, uint64_t b, uint64_t c, uint64_t d, uint64_t& lo, uint64_t& hi) {
 #if defined(__CUDA_ARCH__)
@@ -89,6 +112,9 @@ DPB_HD Fq fq_sub_q(const Fq& a) {
     return r;
 }
 DPB_HD Fq fq_add(const Fq& a, const Fq& b) {
+#if defined(__CUDA_ARCH__)
+    return fq_from_words(fqw::add(fq_words(a), fq_words(b)));
+#endif
     Fq r;
     uint64_t carry = 0;
     for (int i = 0; i < 4; i++) {
@@ -100,6 +126,9 @@ DPB_HD Fq fq_add(const Fq& a, const Fq& b) {
     return fq_geq_q(r) ? fq_sub_q(r) : r;  // a + b < 2q < 2^255: no carry out
 }
 DPB_HD Fq fq_sub(const Fq& a, const Fq& b) {
+#if defined(__CUDA_ARCH__)
+    return fq_from_words(fqw::sub(fq_words(a), fq_words(b)));
+#endif
     const uint64_t q[4] = {DPB_FQ_Q0, DPB_FQ_Q1, DPB_FQ_Q2, DPB_FQ_Q3};
     Fq r;
     uint64_t borrow = 0;
@@ -125,6 +154,9 @@ DPB_HD Fq fq_dbl(const Fq& a) { return fq_add(a, a); }
 
 // Montgomery product a b / 2^256 mod q (coarsely integrated operand scanning on 64-bit limbs)
 DPB_HD Fq fq_mul(const Fq& a, const Fq& b) {
+#if defined(__CUDA_ARCH__)
+    return fq_from_words(fqw::mul(fq_words(a), fq_words(b)));  // the word-level product of fq_words.cuh
+#endif
     const uint64_t q[4] = {DPB_FQ_Q0, DPB_FQ_Q1, DPB_FQ_Q2, DPB_FQ_Q3};
     uint64_t t[6] = {0, 0, 0, 0, 0, 0};
     for (int i = 0; i < 4; i++) {
