@@ -336,6 +336,17 @@ extern "C" int dpb_lookup_witness(dpb_ctx* ctx, int family_dtype, const dpb_chun
     for (int h = 0; h < 4; h++)
         if (counts[h] && (counts[h]->bits != want_bits[h] || counts[h]->ctx != ctx))
             return fail(DPB_EINVAL, "counter %d has 2^%u rows, its table 2^%u (or another context)", h, counts[h]->bits, want_bits[h]);
+    if (is_int_dtype(family_dtype)) {  // integer columns: the chunks as they are, eight bytes each
+        return is_gl(family_dtype)
+                   ? witness_impl<IntColumns<GlFam>>(ctx, ci, fixed_point_multiplier, padding_value, tensor, tensor_on_device,
+                                                     shape, rank, value_table_outputs, outputs_on_device, num_value_columns,
+                                                     counts, out_owner, out_input_columns, in_cap, n_in, out_output_columns,
+                                                     out_cap, n_out)
+                   : witness_impl<IntColumns<FrFam>>(ctx, ci, fixed_point_multiplier, padding_value, tensor, tensor_on_device,
+                                                     shape, rank, value_table_outputs, outputs_on_device, num_value_columns,
+                                                     counts, out_owner, out_input_columns, in_cap, n_in, out_output_columns,
+                                                     out_cap, n_out);
+    }
     return is_gl(family_dtype)
                ? witness_impl<GlFam>(ctx, ci, fixed_point_multiplier, padding_value, tensor, tensor_on_device, shape, rank,
                                      value_table_outputs, outputs_on_device, num_value_columns, counts, out_owner,

@@ -125,6 +125,23 @@ struct SmallToField<FrFam> {
     __device__ __forceinline__ static void store(T* p, uint64_t i, const T& v) { FrFam::store(p, i, v); }
 };
 
+// Columns that stay integers (DPB_GL_I64 / DPB_FR_I64 tables): what the witness kernel writes is the chunk itself.
+// Eight bytes per entry instead of 32 for BN254, and a commitment to such a column is a multi-scalar multiplication
+// over one or two windows instead of sixteen (a negative chunk as a field element has all its bits set).
+template <class F>
+struct IntColumns {};
+template <class F>
+struct SmallToField<IntColumns<F>> {
+    typedef int64_t T;
+    static constexpr int kDtype = std::is_same<F, GlFam>::value ? DPB_GL_I64 : DPB_FR_I64;
+    struct Shared {
+        int unused;
+    };
+    __device__ static void init(Shared&) {}
+    __device__ __forceinline__ static T conv(const Shared&, int64_t v) { return v; }
+    __device__ __forceinline__ static void store(T* p, uint64_t i, T v) { p[i] = v; }
+};
+
 // Dynamic shared memory: [conversion tables | caches | value histogram (direct_rows words)].
 template <class F>
 size_t lookup_witness_smem(uint32_t direct_rows) {

@@ -645,8 +645,8 @@ class GpuBackend:
 
     def lookup_witness(self, tensor, shape, spec, table_out, n_cols, counts):
         info = self.dpb.ChunkingInfo.new(spec.right_shift, spec.bits, spec.sign, spec.max_bit_size, spec.n_value)
-        owner, ins, outs = self.dpb.lookup_witness(self.ctx, self.fam, info, spec.fpm, spec.padding, None, table_out, n_cols,
-                                                   counts, device_tensor=tensor)
+        owner, ins, outs = self.dpb.lookup_witness(self.ctx, self.i64 if self.int_tables else self.fam, info, spec.fpm,
+                                                   spec.padding, None, table_out, n_cols, counts, device_tensor=tensor)
         tensor[0].free()
         return dict(owner=owner, ins=ins, outs=outs, n_shifted=info.n_shifted_chunks, n_zeroing=info.n_zeroing_chunks)
 

@@ -391,7 +391,9 @@ int dpb_lookup_multiplicities(dpb_ctx* ctx, const dpb_lookup_counts* counts, int
  * views into *out_owner, as with dpb_einsum_fix_axes.  The four count handles may be NULL
  * (that table's lookups are not counted); shift, zero and signed-zero counts have 2^16 rows.
  * DPB_EINVAL with the reference's message when a top zeroing chunk falls outside the signed
- * zero-check table (an input beyond max_bit_size). */
+ * zero-check table (an input beyond max_bit_size).  * family_dtype may also be an integer layout (DPB_FR_I64 / DPB_GL_I64): the columns then hold the chunks as
+ * 64-bit integers (8 bytes per entry), which every sumcheck entry point, the logup tree and dpb_msm_g1 accept.
+ */
 int dpb_lookup_witness(dpb_ctx* ctx, int family_dtype, const dpb_chunking_info* info, int64_t fixed_point_multiplier,
                        int64_t padding_value, const int64_t* tensor, int tensor_on_device, const uint64_t* shape,
                        uint32_t rank, const int64_t* value_table_outputs, int outputs_on_device,

@@ -135,6 +135,31 @@ def test_witness_columns_counts_multiplicities(dpb, ctx, F, kind, bits, right_sh
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("F", FIELDS)
+def test_integer_columns(dpb, ctx, F):
+    """family_dtype = an integer layout: the columns are the chunks themselves (64-bit integers), equal to the
+    oracle's integer columns, and the counters are the same as with field columns."""
+    rng = np.random.default_rng(9650)
+    for kind, bits, right_shift, max_bit_size, shape in [("relu", 10, 13, 44, (3, 7, 9)), ("exp", 8, 10, 34, (2, 12, 12)),
+                                                         ("requantise", 10, 32, 60, (33, 65))]:
+        sign, table_out, n_cols = value_table(kind, bits)
+        t = draw_tensor(rng, shape, sign, max_bit_size, 5)
+        want = orc.LookupOpWitness(orc.ChunkingInfo(right_shift, bits, sign, max_bit_size), 5, 0, t, table_out, n_cols)
+        ci = dpb.ChunkingInfo.new(right_shift, bits, sign, max_bit_size)
+        dt = dpb.FR_I64 if F is orc.FrField else dpb.GL_I64
+        counts = [dpb.LookupCounts(ctx, b) for b in (16, bits, 16, 16)]
+        counts_f = [dpb.LookupCounts(ctx, b) for b in (16, bits, 16, 16)]
+        owner, ins, outs = dpb.lookup_witness(ctx, dt, ci, 5, 0, t, table_out, n_cols, counts)
+        owner_f, ins_f, outs_f = dpb.lookup_witness(ctx, family_dtype(dpb, F), ci, 5, 0, t, table_out, n_cols, counts_f)
+        for got, col in zip(ins + outs, want.input_columns() + want.output_columns()):
+            assert got.dtype == dt and np.array_equal(got.to_host(), col)
+        for a, b in zip(counts, counts_f):
+            assert np.array_equal(a.to_host(), b.to_host())
+        for h in ins + outs + ins_f + outs_f + [owner, owner_f] + counts + counts_f:
+            h.free()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("F", FIELDS)
 def test_two_value_chunks_and_device_tensor(dpb, ctx, F):
     rng = np.random.default_rng(9700)
     check_case(dpb, ctx, F, "requantise", 8, 12, 44, (3, 5, 9), 3, 0, rng, n_value=2)
