@@ -523,6 +523,23 @@ def workload_record(dpb, prover, ctx, args):
     return rec
 
 
+def run_only(args):
+    """One sub-record of the default line by itself (one GPU)."""
+    import torch
+    from __graft_entry__ import load_package
+    dpb = load_package()
+    prover = importlib.import_module("deep_prove_b200.prover")
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    ctx = dpb.Context(0)
+    stream = torch.cuda.ExternalStream(ctx.stream, device=device)
+    if args.only == "bn254":
+        rec = bn254_record(dpb, prover, ctx, torch, stream, device, min(args.steps, 10), args.bn254_log2)
+    else:
+        rec = workload_record(dpb, prover, ctx, args)
+    print(json.dumps({args.only: rec}))
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -728,11 +745,15 @@ def main():
     ap.add_argument("--no-bn254", action="store_true")
     ap.add_argument("--no-strong", action="store_true")
     ap.add_argument("--no-workload", action="store_true", help="skip the GPT-2 seq-512 path workload")
+    ap.add_argument("--only", default=None, choices=["bn254", "workload"],
+                    help="run one sub-record alone and print it (profiling captures of its kernels)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
+    elif args.only:
+        run_only(args)
     else:
         run_ours(args)
 
