@@ -77,13 +77,11 @@ def msm_bench(dpb, ctx):
     """Commit throughput: one MSM over 2^n G1 points, full-width field scalars and 32-bit integer tables."""
     import importlib
     pcs = importlib.import_module("deep_prove_b200.pcs")
-    from oracle import g1  # only to make a handful of valid points; the timing below is the library's alone
-    pts = pcs.points_to_array(g1.synthetic_bases(256, seed=1))
     rng = np.random.default_rng(3)
     print("# dpb_msm_g1: one commitment over 2^n points (mean of 5 after a warm-up), milliseconds and M points/s")
     for n in (16, 18, 20):
         N = 1 << n
-        bases = pcs.G1Bases(ctx, np.tile(pts, (N // 256, 1)))
+        bases = pcs.G1Bases.synthetic(ctx, N, 1)  # the multiples 1 G .. N G of the generator, made on the device
         t = rng.integers(0, 2**64, size=(N, 4), dtype=np.uint64)
         t[:, 3] &= np.uint64((1 << 60) - 1)
         tabs = {"field scalars (254 bits)": ctx.upload(t, dpb.FR),
