@@ -58,6 +58,8 @@ SIGNATURES = {
     "dpb_resident_rounds": (_int, [_vp, _int, _u32]),
     "dpb_sumcheck_launches": (_u64, [_vp]),
     "dpb_issue_rate_probe": (_int, [_vp, _int, _u32, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)]),
+    "dpb_trace_enable": (_int, [_int]),
+    "dpb_trace_read": (_int, [ctypes.c_char_p, ctypes.c_size_t, ctypes.POINTER(ctypes.c_size_t)]),
     "dpb_profile_enable": (_int, [_vp, _int]),
     "dpb_profile_read": (_int, [_vp, ctypes.POINTER(ProfileEntry), _u32, ctypes.POINTER(_u32)]),
     "dpb_init": (_int, [_int, _pp]),
@@ -111,6 +113,24 @@ SIGNATURES = {
 }
 
 COMM_ID_BYTES = 128
+
+
+def trace(on):
+    """dpb_trace_enable: host-side phase timers of the whole-protocol entry points."""
+    check(lib.dpb_trace_enable(1 if on else 0))
+
+
+def trace_read():
+    """{phase: (milliseconds, calls)} since trace(True)."""
+    n = ctypes.c_size_t()
+    check(lib.dpb_trace_read(None, 0, ctypes.byref(n)))
+    buf = ctypes.create_string_buffer(n.value)
+    check(lib.dpb_trace_read(buf, n.value, ctypes.byref(n)))
+    out = {}
+    for line in buf.value.decode().splitlines():
+        name, ms, calls = line.split("\t")
+        out[name] = (float(ms), int(calls))
+    return out
 
 
 def comm_unique_id():

@@ -1,6 +1,8 @@
 // C ABI: context, table handles, layout conversion, eq tables and partial
 // evaluation (fix_high / fix_low / evaluate).
 #include <algorithm>
+#include <atomic>
+#include <mutex>
 
 #include "common.cuh"
 #include "fix_kernels.cuh"
@@ -11,6 +13,21 @@ namespace dpb {
 std::string& last_error_slot() {
     static thread_local std::string s;
     return s;
+}
+
+static std::atomic<bool> g_trace{false};
+static std::mutex g_trace_mu;
+static std::vector<std::pair<std::string, std::pair<double, uint64_t>>> g_trace_log;
+bool trace_on() { return g_trace.load(std::memory_order_relaxed); }
+void trace_add(const char* phase, double seconds) {
+    std::lock_guard<std::mutex> lock(g_trace_mu);
+    for (auto& e : g_trace_log)
+        if (e.first == phase) {
+            e.second.first += seconds;
+            e.second.second++;
+            return;
+        }
+    g_trace_log.push_back({phase, {seconds, 1}});
 }
 
 int fail(int code, const char* fmt, ...) {
@@ -335,6 +352,7 @@ int dpb_init(int device, dpb_ctx** out) {
 void dpb_shutdown(dpb_ctx* ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
+    if (ctx->slab_cache) cudaFreeAsync(ctx->slab_cache, ctx->stream);
     cudaStreamSynchronize(ctx->stream);
     cudaStreamSynchronize(ctx->tail_stream);
     cudaStreamDestroy(ctx->tail_stream);
@@ -374,6 +392,30 @@ int dpb_profile_enable(dpb_ctx* ctx, int on) {
     if (!ctx) return fail(DPB_EINVAL, "null context");
     if (on) ctx->prof_log.clear();
     ctx->profile = on != 0;
+    return DPB_OK;
+}
+
+int dpb_trace_enable(int on) {
+    std::lock_guard<std::mutex> lock(g_trace_mu);
+    if (on) g_trace_log.clear();
+    g_trace.store(on != 0);
+    return DPB_OK;
+}
+
+int dpb_trace_read(char* out, size_t cap, size_t* needed) {
+    if (!needed) return fail(DPB_EINVAL, "null argument");
+    std::string text;
+    {
+        std::lock_guard<std::mutex> lock(g_trace_mu);
+        char line[160];
+        for (const auto& e : g_trace_log) {
+            snprintf(line, sizeof line, "%s\t%.6f\t%llu\n", e.first.c_str(), e.second.first * 1e3,
+                     (unsigned long long)e.second.second);
+            text += line;
+        }
+    }
+    *needed = text.size() + 1;
+    if (out && cap >= text.size() + 1) memcpy(out, text.c_str(), text.size() + 1);
     return DPB_OK;
 }
 

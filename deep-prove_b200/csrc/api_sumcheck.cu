@@ -20,6 +20,7 @@
 
 namespace dpb {
 
+constexpr size_t kSlabCacheMax = (size_t)4 << 30;  // larger blocks (claim batching over a whole model) are not kept
 constexpr int kOnePassMaxSmem = 200 * 1024;  // dynamic shared memory the one-pass generic rounds may use
 
 struct MleTrack {
@@ -844,6 +845,7 @@ static int wait_round_chunks(dpb_ctx* ctx, size_t msg_bytes, void* out) {
 }
 
 constexpr uint64_t kSpreadPairs = 4096;  // rounds up to this size of a heavy program are spread over its terms
+constexpr uint64_t kSpreadLightPairs = 16384;  // and of any other program (measured: 14-15 % off a logup batch)
 
 template <class F>
 static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
@@ -875,7 +877,13 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
     // the last rounds go to the resident kernel (one per context at a time; not while profiling per launch)
     bool use_tail = sc->tail_active || (sc->has_prog && ctx->tail_enabled && !sharded && !ctx->profile && !sc->heavy &&
                                         i >= sc->tail_start && ctx->tail_owner == nullptr);
-    const bool spread = sc->heavy && n_pairs <= kSpreadPairs && sc->fused_shape != kFusedProduct;
+    // Rounds too small to fill the GPU with one thread per pair run as a fold launch plus an evaluation spread over
+    // (pair, slice of the term list) items: a thread's chain of dependent field products is what such a round
+    // waits for, and the spread form makes it several times shorter.  Heavy programs: up to kSpreadPairs pairs;
+    // every other program: between the resident kernel's rounds and kSpreadLightPairs.
+    const bool spread = ((sc->heavy && n_pairs <= kSpreadPairs) ||
+                         (!use_tail && !sc->ranged && sc->has_prog && n_pairs <= kSpreadLightPairs)) &&
+                        sc->fused_shape != kFusedProduct;
     if (spread && sc->eq_unbound) DPB_TRY(spliteq_materialize<F>(sc, i));
     E raw[kMaxAcc];
     if (use_tail) {
@@ -1148,6 +1156,7 @@ int dpb_sumcheck_begin(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, ui
     // host-side plan, then ONE device allocation and ONE upload:
     // [fold buffers | table descriptors | fold descriptors | terms | final values | round tables | groups | program]
     std::vector<uint8_t> h_terms, h_groups, h_prog;
+    TracePhase t_plan("sumcheck.begin.plan");
     if (gl) {
         build_terms<GlFam>(sc, terms, h_terms);
         if (!sc->ranged) plan_program<GlFam>(sc, terms, mles, h_groups, h_prog);
@@ -1191,11 +1200,30 @@ int dpb_sumcheck_begin(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, ui
                  o_groups = take(h_groups.size()), o_prog = take(h_prog.size()),
                  o_tiles = take(h_tile_prefix.size() * 8), o_pairs = take(h_term_pairs.size() * 8),
                  o_rtab_eq = take(sc->spliteq ? nk * sizeof(RoundTab) : 0);
-    int rc = device_alloc(ctx, off, &sc->slab);
+    t_plan.stop();
+    TracePhase t_alloc("sumcheck.begin.alloc");
+    // Sumchecks of one context run one after the other, each with one block of device memory for its fold buffers
+    // and descriptors.  The context keeps the last block (up to kSlabCacheMax) and hands it to the next sumcheck that
+    // fits: no trip through the allocator per tree level of a logup batch.
+    int rc = DPB_OK;
+    if (ctx->slab_cache && !ctx->slab_cache_busy && off <= ctx->slab_cache_bytes) {
+        sc->slab = ctx->slab_cache;
+        ctx->slab_cache_busy = true;
+    } else {
+        rc = device_alloc(ctx, off, &sc->slab);
+        if (rc == DPB_OK && !ctx->slab_cache_busy && off <= kSlabCacheMax) {
+            device_free(ctx, ctx->slab_cache);  // smaller than what was asked for (or absent)
+            ctx->slab_cache = sc->slab;
+            ctx->slab_cache_bytes = off;
+            ctx->slab_cache_busy = true;
+        }
+    }
+    t_alloc.stop();
     if (rc != DPB_OK) {
         delete sc;
         return rc;
     }
+    TracePhase t_desc("sumcheck.begin.descriptors_upload");
     {
         char* base = (char*)sc->slab;
         sc->d_desc = (MleDesc*)(base + o_desc);
@@ -1373,7 +1401,9 @@ void dpb_sumcheck_free(dpb_sc* sc) {
     if (sc->tail) dpb_sumcheck_free(sc->tail);
     for (auto* m : sc->tail_mles) dpb_mle_free(m);
     device_free(sc->ctx, sc->tail_dev);
-    device_free(sc->ctx, sc->slab);  // the fold buffers and every descriptor array live in this one block
+    // the fold buffers and every descriptor array live in this one block
+    if (sc->slab && sc->slab == sc->ctx->slab_cache) sc->ctx->slab_cache_busy = false;
+    else device_free(sc->ctx, sc->slab);
     delete sc;
 }
 

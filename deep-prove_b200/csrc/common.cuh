@@ -3,6 +3,7 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <chrono>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -55,6 +56,25 @@ inline uint32_t log2u(uint64_t x) {
 
 constexpr int kMaxAcc = 8;  // round-polynomial evaluations per launch (degree <= 7)
 
+// Opt-in host-side phase timers (dpb_trace_enable): wall time per named phase of the whole-protocol entry points,
+// summed over calls -- where a logup batch or a sumcheck spends its host time (the counterpart of the reference's
+// timed_instrument spans, zkml/src/layers/activation.rs:620).  Off: one relaxed load per phase.
+bool trace_on();
+void trace_add(const char* phase, double seconds);
+struct TracePhase {
+    const char* name;
+    bool on;
+    std::chrono::steady_clock::time_point t0;
+    explicit TracePhase(const char* n) : name(n), on(trace_on()) {
+        if (on) t0 = std::chrono::steady_clock::now();
+    }
+    void stop() {
+        if (on) trace_add(name, std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count());
+        on = false;
+    }
+    ~TracePhase() { stop(); }
+};
+
 }  // namespace dpb
 
 struct dpb_ctx {
@@ -106,6 +126,10 @@ struct dpb_ctx {
     cudaEvent_t up_ev[kStageSlots] = {};
     bool up_used[kStageSlots] = {};
     int up_next = 0;
+    // the block of device memory the last sumcheck used, kept for the next one (dpb_sumcheck_begin)
+    void* slab_cache = nullptr;
+    size_t slab_cache_bytes = 0;
+    bool slab_cache_busy = false;
     bool tail_enabled = true;
     uint64_t sumcheck_launches = 0;  // kernels launched by the sumcheck entry points
     unsigned long long tail_wait_ns = 1ull * 1000 * 1000 * 1000;

@@ -271,6 +271,7 @@ LogUpBatchProof<F> new_batch_multiple_sizes_prove(dpb_ctx* ctx, const std::vecto
         if (in.kind != proof_type) throw Error(DPB_EINVAL, "Not all proof types matched");
 
     // structs.rs:241-272
+    dpb::TracePhase t_trees("logup.trees");
     std::vector<std::unique_ptr<LogUpCircuit<F>>> circuits;
     for (const auto& in : input) {
         if (in.kind == ProofType::Table) {
@@ -296,7 +297,9 @@ LogUpBatchProof<F> new_batch_multiple_sizes_prove(dpb_ctx* ctx, const std::vecto
 
     LogUpBatchProof<F> proof;
     proof.proof_type = proof_type;
+    t_trees.stop();
     {
+        dpb::TracePhase t_out("logup.outputs");
         // every circuit's outputs (LogUpCircuit::outputs, circuit.rs:558-560) with one wait for the device
         std::vector<const dpb_logup*> trees;
         for (const auto& c : circuits) trees.push_back(c->tree());
@@ -324,6 +327,7 @@ LogUpBatchProof<F> new_batch_multiple_sizes_prove(dpb_ctx* ctx, const std::vecto
         if (wit_evals.empty())
             throw Error(DPB_EINVAL, "Proving failed: No previous evals and no evals for this number of variables");
 
+        dpb::TracePhase t_expr("logup.layer_expressions");
         std::vector<dpb_mle*> mles;
         std::vector<dpb_mle*> eq_mles;
         std::vector<X> group_exprs;
@@ -350,7 +354,10 @@ LogUpBatchProof<F> new_batch_multiple_sizes_prove(dpb_ctx* ctx, const std::vecto
                 claim_expr = claim_expr + mult * le.claim;
             }
             dpb_mle* eq = nullptr;
-            check(dpb_eq_table(ctx, F::kChalDtype, point.data() + (point.size() - layer_vars), (uint32_t)layer_vars, &eq));
+            {
+                dpb::TracePhase t_eq("logup.eq_tables");
+                check(dpb_eq_table(ctx, F::kChalDtype, point.data() + (point.size() - layer_vars), (uint32_t)layer_vars, &eq));
+            }
             eq_mles.push_back(eq);
             group_exprs.push_back(group);
         }
@@ -362,7 +369,10 @@ LogUpBatchProof<F> new_batch_multiple_sizes_prove(dpb_ctx* ctx, const std::vecto
         std::vector<dpb_mle*> all(mles);
         all.insert(all.end(), eq_mles.begin(), eq_mles.end());
         auto builder = dp_crypto::VirtualPolynomialsBuilder<F>::new_with_mles(1, (uint32_t)v, all);
+        dpb::TracePhase t_expand("logup.expand_terms");
         auto vp = builder.to_virtual_polys({full}, {alpha, lambda});
+        t_expand.stop();
+        t_expr.stop();
         auto res = dp_crypto::IOPProverState<F>::prove(ctx, vp, transcript);
         point = res.second.collect_raw_challenges();
         const auto& finals = res.second.get_mle_flatten_final_evaluations();

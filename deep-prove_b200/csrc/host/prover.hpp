@@ -304,9 +304,12 @@ class IOPProverState {
         IOPProverState st;
         IOPProof<F> proof;
         dpb_sc* sc = nullptr;
+        dpb::TracePhase t_begin("sumcheck.begin");
         // sharded: the tables are this rank's slices and every rank runs this same loop
         check((sharded ? dpb_sumcheck_begin_sharded : dpb_sumcheck_begin)(
             ctx, vp.num_vars, vp.mles.data(), (uint32_t)vp.mles.size(), vp.terms.data(), (uint32_t)vp.terms.size(), &sc));
+        t_begin.stop();
+        dpb::TracePhase t_rounds("sumcheck.rounds");
         struct Guard {
             dpb_sc* s;
             ~Guard() { dpb_sumcheck_free(s); }
@@ -325,6 +328,8 @@ class IOPProverState {
             st.challenges_.push_back(r);
             proof.proofs.push_back(std::move(msg));
         }
+        t_rounds.stop();
+        dpb::TracePhase t_finish("sumcheck.finish");
         st.final_evals_.resize(vp.mles.size());
         check(dpb_sumcheck_finish(sc, &r, st.final_evals_.data()));
         return {std::move(proof), std::move(st)};

@@ -133,6 +133,14 @@ int dpb_profile_enable(dpb_ctx* ctx, int on);
 /* Copies at most cap entries; *n is the number available. */
 int dpb_profile_read(dpb_ctx* ctx, dpb_profile_entry* out, uint32_t cap, uint32_t* n);
 
+/* Host-side phase timers (no counterpart in the reference beyond its timed_instrument spans,
+ * zkml/src/layers/activation.rs:620): when enabled, the whole-protocol entry points add the wall time of their
+ * phases (tree builds, expression expansion, eq tables, sumcheck begin / rounds / finish, ...) to a process-wide log.
+ * dpb_trace_read writes one line "phase<TAB>milliseconds<TAB>calls" per phase into `out` (NUL-terminated) when
+ * `cap` suffices; *needed is the size required.  on != 0 clears the log. */
+int dpb_trace_enable(int on);
+int dpb_trace_read(char* out, size_t cap, size_t* needed);
+
 /* Issue-rate probe: runs chains of one arithmetic primitive of the round
  * kernels on register operands on every SM and reports how many of them the
  * device completes per second -- the ceiling a kernel bound by the integer

@@ -203,3 +203,21 @@ def test_logup_errors(dpb, ctx, prover):
         prover.new_batch_multiple_sizes_prove(ctx, [prover.LogUpInput.new_lookup([big, small], S(F.one), S(F.one), 2)], t())
     with pytest.raises(dpb.DpbError, match="Multiplicities length"):
         prover.new_batch_multiple_sizes_prove(ctx, [prover.LogUpInput.new_table([big], small, S(F.one), S(F.one))], t())
+
+
+def test_phase_timers(dpb, ctx, prover):
+    """dpb_trace_enable / dpb_trace_read: the whole-protocol entry points report where their host time goes."""
+    F = orc.FrField
+    rng = np.random.default_rng(77)
+    assert dpb.trace_read() == {} or isinstance(dpb.trace_read(), dict)
+    dpb.trace(True)
+    cols = [ctx.upload(F.random_table_fast(rng, 1 << 9), dpb.FR) for _ in range(2)]
+    one = orc.scalars_to_array(F, [F.one])
+    d_in = prover.LogUpInput.new_lookup(cols, one, one, 1)
+    prover.new_batch_multiple_sizes_prove(ctx, [d_in], prover.Blake3Transcript(dpb.FR))
+    got = dpb.trace_read()
+    dpb.trace(False)
+    for phase in ("logup.trees", "logup.outputs", "logup.layer_expressions", "logup.eq_tables", "sumcheck.begin",
+                  "sumcheck.rounds", "sumcheck.finish"):
+        assert phase in got and got[phase][0] >= 0 and got[phase][1] >= 1
+    assert got["sumcheck.begin"][1] == 8  # one sumcheck per tree level of a 2^9 instance
