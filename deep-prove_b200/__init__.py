@@ -104,6 +104,7 @@ SIGNATURES = {
     "dpb_lookup_counts_add_rows": (_int, [_vp, _vp, _vp, _int, _u64]),
     "dpb_lookup_witness": (_int, [_vp, _int, _vp, ctypes.c_int64, ctypes.c_int64, _vp, _int, _vp, _u32, _vp, _int, _u32,
                                   _vp, _vp, _vp, _vp, _pp, _pp, _u32, ctypes.POINTER(_u32), _pp, _u32, ctypes.POINTER(_u32)]),
+    "dpb_eq_table_shard": (_int, [_vp, _int, _vp, _u32, _pp]),
     "dpb_comm_unique_id": (_int, [_vp]),
     "dpb_comm_init": (_int, [_vp, _vp, _int, _int]),
     "dpb_comm_rank": (_int, [_vp]),
@@ -284,6 +285,14 @@ class Context:
         m = p.shape[0] if p.size else 0
         h = ctypes.c_void_p()
         check(lib.dpb_eq_table(self.h, family_dtype, _buf(p) if m else None, m, ctypes.byref(h)))
+        return Mle(self, h)
+
+    def eq_table_shard(self, family_dtype, point_array):
+        """dpb_eq_table_shard: this rank's slice of the eq table of the point."""
+        p = np.ascontiguousarray(point_array, dtype=np.uint64)
+        m = p.shape[0] if p.size else 0
+        h = ctypes.c_void_p()
+        check(lib.dpb_eq_table_shard(self.h, family_dtype, _buf(p) if m else None, m, ctypes.byref(h)))
         return Mle(self, h)
 
     def fix_high(self, mle, point_array):

@@ -214,6 +214,25 @@ static int xch_setup(dpb_ctx* ctx, const void* unique_id) {
 
 using namespace dpb;
 
+// eq(x, point) restricted to this rank's shard of the hypercube: x = (x_low, rank bits).  The shard is the eq table
+// of the low coordinates times prod_b eq(rank_b, point[m - c + b]).
+template <class F>
+static int eq_table_shard_impl(dpb_ctx* ctx, const void* point, uint32_t m, uint32_t c, dpb_mle** out) {
+    typedef typename F::E E;
+    const E* pt = (const E*)point;
+    E scale = F::one();
+    for (uint32_t b = 0; b < c; b++) {
+        const E q = pt[m - c + b];
+        scale = F::mul(scale, ((ctx->rank >> b) & 1) ? q : F::sub(F::one(), q));
+    }
+    dpb_mle* low = nullptr;
+    DPB_TRY(dpb_eq_table(ctx, F::kChalDtype, point, m - c, &low));
+    dpb_mle* one_tab[1] = {low};
+    const int rc = dpb_linear_combination(ctx, one_tab, &scale, 1, out);
+    dpb_mle_free(low);
+    return rc;
+}
+
 extern "C" {
 
 int dpb_comm_unique_id(void* out_id) {
@@ -246,6 +265,16 @@ int dpb_comm_init(dpb_ctx* ctx, const void* id, int rank, int nranks) {
     DPB_CUDA(cudaHostAlloc(&ctx->gather_host, ctx->gather_bytes, cudaHostAllocDefault));
     if (nranks > 1 && !getenv("DPB_NO_SHARED_EXCHANGE")) DPB_TRY(xch_setup(ctx, id));
     return DPB_OK;
+}
+
+int dpb_eq_table_shard(dpb_ctx* ctx, int family_dtype, const void* point, uint32_t m, dpb_mle** out) {
+    if (!ctx || !out || (!point && m)) return fail(DPB_EINVAL, "null argument");
+    if (!valid_dtype(family_dtype)) return fail(DPB_EINVAL, "unknown dtype %d", family_dtype);
+    uint32_t c = 0;
+    while ((1 << c) < ctx->nranks) c++;
+    if (m < c) return fail(DPB_EINVAL, "a point of %u coordinates cannot be sharded over %d ranks", m, ctx->nranks);
+    return is_gl(family_dtype) ? eq_table_shard_impl<GlFam>(ctx, point, m, c, out)
+                               : eq_table_shard_impl<FrFam>(ctx, point, m, c, out);
 }
 
 int dpb_comm_shared_exchange(const dpb_ctx* ctx) { return ctx && ctx->xch_host ? 1 : 0; }

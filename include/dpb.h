@@ -107,6 +107,11 @@ void* dpb_stream(dpb_ctx* ctx);
 int dpb_comm_unique_id(void* out_id);
 /* ncclCommInitRank on the context's device; collective over all ranks.  nranks a power of two. */
 int dpb_comm_init(dpb_ctx* ctx, const void* id, int rank, int nranks);
+/* This rank's shard of the eq table of `point` (m coordinates), for sharded sumchecks with an eq factor (the
+ * hadamard, same_poly and linking shapes): entries [rank * 2^(m-c), (rank+1) * 2^(m-c)) of dpb_eq_table's result,
+ * c = log2(ranks), computed as the eq table of the low m - c coordinates times the eq value of the rank's bits at
+ * the top c coordinates -- no rank ever holds the whole table.  Without a communicator it is dpb_eq_table. */
+int dpb_eq_table_shard(dpb_ctx* ctx, int family_dtype, const void* point, uint32_t m, dpb_mle** out);
 /* 1 when the ranks of this context's communicator exchange the per-round sums
  * through a shared host segment (all on one host), 0 when they use
  * ncclAllGather.  The environment variable DPB_NO_SHARED_EXCHANGE, set on every

@@ -70,6 +70,58 @@ def run_gpu(field, n, seed, rank, world, out):
         json.dump(res, f)
 
 
+def linking_case(F, n, seed):
+    """Tables and terms of the shape of a linking / hadamard sumcheck: an eq table as a factor of every term."""
+    rng = np.random.default_rng(seed + 1000)
+    tabs = [F.random_table_fast(rng, 1 << n) for _ in range(3)]
+    point = [F.random_scalar(rng) for _ in range(n)]
+    c = [F.random_scalar(rng) for _ in range(2)]
+    terms = {(3, 0, 1): F.one, (3, 1, 2, 2): c[0], (3, 0): c[1]}
+    return tabs, point, terms
+
+
+def run_gpu_eq(field, n, seed, rank, world, out):
+    """The library's sharded sumcheck over a term list with an eq factor; every rank builds only its shard of the
+    eq table (dpb_eq_table_shard)."""
+    from tests.conftest import load_package
+    import importlib
+    dpb = load_package()
+    prover = importlib.import_module("deep_prove_b200.prover")
+    F = orc.FIELDS[field]
+    ctx = dpb.Context(rank)
+    id_path = out + ".id"
+    if rank == 0:
+        uid = dpb.comm_unique_id()
+        with open(id_path + ".tmp", "wb") as f:
+            f.write(uid)
+        os.replace(id_path + ".tmp", id_path)
+    else:
+        t0 = time.time()
+        while not os.path.exists(id_path):
+            if time.time() - t0 > 60:
+                raise SystemExit("rank 0 never published the communicator id")
+            time.sleep(0.01)
+        with open(id_path, "rb") as f:
+            uid = f.read()
+    ctx.comm_init(uid, rank, world)
+    tabs, point, terms = linking_case(F, n, seed)
+    base = dpb.FR if field == "fr" else dpb.GL_BASE
+    fam = dpb.FR if field == "fr" else dpb.GL_EXT
+    mles = [ctx.upload(shard(t, rank, world), base) for t in tabs]
+    eq = ctx.eq_table_shard(fam, orc.scalars_to_array(F, point))
+    want_eq = shard(orc.eq_evals(F, point), rank, world)
+    assert (eq.to_host() == want_eq).all(), "eq shard differs from the slice of the whole eq table"
+    arr = dpb.make_terms([(c, list(m)) for m, c in sorted(terms.items())], F.to_native)
+    st = prover.IOPProverState.prove(ctx, n, mles + [eq], arr, prover.Blake3Transcript(fam), sharded=True)
+    flat = lambda a: orc.serialize_scalars(F, orc.array_to_scalars(F, np.asarray(a).reshape(-1, F.elem_words))).hex()
+    res = dict(proof=flat(st.proof), point=flat(st.collect_raw_challenges()),
+               finals=flat(st.get_mle_flatten_final_evaluations()))
+    ctx.comm_free()
+    ctx.close()
+    with open(f"{out}.{rank}.json", "w") as f:
+        json.dump(res, f)
+
+
 def run_cpu(field, n, seed, rank, world, out):
     import torch
     import torch.distributed as dist
@@ -122,4 +174,4 @@ def run_cpu(field, n, seed, rank, world, out):
 
 if __name__ == "__main__":
     mode, field, n, seed, rank, world, out = sys.argv[1:8]
-    (run_gpu if mode == "gpu" else run_cpu)(field, int(n), int(seed), int(rank), int(world), out)
+    {"gpu": run_gpu, "gpu_eq": run_gpu_eq, "cpu": run_cpu}[mode](field, int(n), int(seed), int(rank), int(world), out)

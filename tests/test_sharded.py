@@ -80,3 +80,24 @@ def test_sharded_sumcheck_on_gpus(field, n, exchange):
         if exchange == "nccl":
             assert not shared
         assert got == want
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("field", ["gl", "fr"])
+@pytest.mark.parametrize("n", [5, 13])
+def test_sharded_sumcheck_with_an_eq_factor_on_gpus(field, n):
+    """A term list of the linking / hadamard shape (every term led by an eq table, a squared factor, coefficients)
+    sharded over the GPUs of the box: each rank builds only its shard of the eq table (dpb_eq_table_shard, checked
+    against the slice of the whole table) and all ranks produce the oracle's proof of the whole tables."""
+    import torch
+    g = torch.cuda.device_count()
+    world = 8 if g >= 8 else 4 if g >= 4 else 2 if g >= 2 else 0
+    if world == 0:
+        pytest.skip("needs at least 2 GPUs")
+    F = orc.FIELDS[field]
+    tabs, point, terms = W.linking_case(F, n, 21)
+    proof, pt, finals = orc.sumcheck_prove(F, n, tabs + [orc.eq_evals(F, point)], terms, orc.Transcript(F))
+    hx = lambda v: orc.serialize_scalars(F, v).hex()
+    want = dict(proof=orc.serialize_sumcheck_proof(F, proof).hex(), point=hx(pt), finals=hx(finals))
+    for got in launch("gpu_eq", field, n, 21, world):
+        assert got == want
