@@ -523,6 +523,40 @@ def workload_record(dpb, prover, ctx, args):
     return rec
 
 
+def more_workloads(dpb, prover, ctx, args, which):
+    """The other model configurations BASELINE.json names, walked like the GPT-2 one: the dense network
+    (configs[0]; "tokens" are input rows), the Gemma-3-1B-style model (configs[3]) and two Llama-2-7B-style blocks
+    (configs[4]), each on ONE GPU.  Warm-up: one whole walk (three for the dense network), which also grows the
+    stream-ordered memory pool to the walk's largest working set (the claim batching: one eq table per committed
+    chunk polynomial, tens of GB at these sizes) as a prover process has it after its first proof."""
+    import torch
+    wl = importlib.import_module("deep_prove_b200.workloads")
+    table = {"mlp": (wl.MLP_2LAYER, "BASELINE.json configs[0] shapes: 1 x 1024 input, 1024 x 1024 and 1024 x 10 weights, "
+                                    "ReLU through a lookup, argmax"),
+             "gemma3_1b_seq512": (wl.GEMMA3_1B, "BASELINE.json configs[3] shapes: 26 layers, d_model 1152, 4 query heads / "
+                                                "1 KV head x 256, GeGLU 6912, RoPE, vocab 262144, 512 tokens"),
+             "llama2_7b_2blocks_seq1024": (wl.LLAMA2_7B_2BLOCKS, "BASELINE.json configs[4] shapes: 2 blocks, d_model 4096, 32 "
+                                                                 "heads x 128, SwiGLU 11008, RoPE, vocab 32000, 1024 tokens; "
+                                                                 "walked on one GPU")}
+    out = {}
+    for key in which:
+        shape, what = table[key]
+        if isinstance(shape, wl.MlpShape):
+            for i in range(3):
+                wl.run_transformer_path(dpb, prover, ctx, shape, field="fr", seed=args.seed + 1 + i)
+        else:
+            wl.run_transformer_path(dpb, prover, ctx, shape, field="fr", seed=args.seed + 1)
+        got = wl.run_transformer_path(dpb, prover, ctx, shape, field="fr", seed=args.seed)
+        free_b, total_b = torch.cuda.mem_get_info()
+        out[key] = {"workload": what + "; every sumcheck / fold / logup-GKR call of the forward graph, BN254 Fr, seeded "
+                                       "synthetic integer tensors resident on the device",
+                    "field": "bn254", "ms": got["seconds"] * 1e3, "tokens_per_s": got["tokens_per_s"],
+                    "by_kind_ms": {k: v * 1e3 for k, v in sorted(got["by_kind"].items(), key=lambda kv: -kv[1])},
+                    "calls": got["calls"], "wall_seconds_with_input_generation": got["wall_seconds"],
+                    "device_memory_held_after_GB": (total_b - free_b) / 1e9}
+    return out
+
+
 def run_only(args):
     """One sub-record of the default line by itself (one GPU)."""
     import torch
@@ -535,8 +569,10 @@ def run_only(args):
     stream = torch.cuda.ExternalStream(ctx.stream, device=device)
     if args.only == "bn254":
         rec = bn254_record(dpb, prover, ctx, torch, stream, device, min(args.steps, 10), args.bn254_log2)
-    else:
+    elif args.only == "workload":
         rec = workload_record(dpb, prover, ctx, args)
+    else:
+        rec = more_workloads(dpb, prover, ctx, args, [args.only])[args.only]
     print(json.dumps({args.only: rec}))
 
 
@@ -675,6 +711,7 @@ def run_ours(args):
             m.free()
         mles = []
         workloads = {"gpt2_seq512": workload_record(dpb, prover, ctx, args)}
+        workloads.update(more_workloads(dpb, prover, ctx, args, ["mlp", "llama2_7b_2blocks_seq1024", "gemma3_1b_seq512"]))
     if world > 1:
         ctx.comm_free()
         dist.barrier()
@@ -745,7 +782,8 @@ def main():
     ap.add_argument("--no-bn254", action="store_true")
     ap.add_argument("--no-strong", action="store_true")
     ap.add_argument("--no-workload", action="store_true", help="skip the GPT-2 seq-512 path workload")
-    ap.add_argument("--only", default=None, choices=["bn254", "workload"],
+    ap.add_argument("--only", default=None,
+                    choices=["bn254", "workload", "mlp", "gemma3_1b_seq512", "llama2_7b_2blocks_seq1024"],
                     help="run one sub-record alone and print it (profiling captures of its kernels)")
     args = ap.parse_args()
     if args.warmup < 3:

@@ -82,6 +82,7 @@ SIGNATURES = {
     "dpb_eq_table": (_int, [_vp, _int, _vp, _u32, _pp]),
     "dpb_fix_high": (_int, [_vp, _vp, _vp, _u32, _pp]),
     "dpb_fix_low": (_int, [_vp, _vp, _vp, _u32, _pp]),
+    "dpb_rope_permuted_eq": (_int, [_vp, _vp, _int, _u64, _pp]),
     "dpb_mle_evaluate": (_int, [_vp, _vp, _vp, _u32, _vp]),
     "dpb_sumcheck_begin": (_int, [_vp, _u32, _pp, _u32, ctypes.POINTER(Term), _u32, _pp]),
     "dpb_sumcheck_degree": (_u32, [_vp]),
@@ -509,6 +510,16 @@ def eq_tables(ctx, family_dtype, points):
     outs = (ctypes.c_void_p * n)()
     check(lib.dpb_eq_tables(ctx.h, family_dtype, _buf(flat), nv, n, ctypes.byref(owner), outs))
     return Mle(ctx, owner), [Mle(ctx, ctypes.c_void_p(outs[i])) for i in range(n)]
+
+
+ROPE_ADJACENT, ROPE_ROTATE_HALF = 0, 1
+
+
+def rope_permuted_eq(ctx, eq, layout=ROPE_ADJACENT, row_size=0):
+    """RopeLayout::permuted_eq_poly (zkml/src/layers/transformer/positional/rope.rs:238-258) of an eq table."""
+    h = ctypes.c_void_p()
+    check(lib.dpb_rope_permuted_eq(ctx.h, eq.h, layout, row_size, ctypes.byref(h)))
+    return Mle(ctx, h)
 
 
 def linear_combination(ctx, mles, coeffs):

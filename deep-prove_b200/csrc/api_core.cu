@@ -571,6 +571,31 @@ int dpb_linear_combination(dpb_ctx* ctx, dpb_mle* const* mles, const void* coeff
     return DPB_OK;
 }
 
+int dpb_rope_permuted_eq(dpb_ctx* ctx, const dpb_mle* eq, int layout, uint64_t row_size, dpb_mle** out) {
+    if (!ctx || !eq || !out) return fail(DPB_EINVAL, "null argument");
+    if (eq->ctx != ctx) return fail(DPB_EINVAL, "table of another context");
+    if (eq->dtype != DPB_FR && eq->dtype != DPB_GL_EXT) return fail(DPB_EINVAL, "an eq table holds challenge elements");
+    if (layout != 0 && layout != 1) return fail(DPB_EINVAL, "layout is 0 (adjacent pairs) or 1 (rotate half)");
+    if (eq->len < 2 || (eq->len & 1)) return fail(DPB_EINVAL, "table length must be even");
+    if (layout == 1 && (row_size < 2 || (row_size & 1) || eq->len % row_size))
+        return fail(DPB_EINVAL, "rotate half: the row size must be even and divide the table length");
+    dpb_mle* res = nullptr;
+    DPB_TRY(new_mle(ctx, eq->dtype, eq->len, &res));
+    if (eq->dtype == DPB_FR)
+        rope_permuted_eq_kernel<FrFam><<<grid_for(ctx, eq->len), kThreads, 0, ctx->stream>>>(
+            (const Fr*)eq->ptr, eq->len, layout, row_size, (Fr*)res->ptr);
+    else
+        rope_permuted_eq_kernel<GlFam><<<grid_for(ctx, eq->len), kThreads, 0, ctx->stream>>>(
+            (const Gl2*)eq->ptr, eq->len, layout, row_size, (Gl2*)res->ptr);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        dpb_mle_free(res);
+        return fail(DPB_ECUDA, "permuted eq: %s", cudaGetErrorString(e));
+    }
+    *out = res;
+    return DPB_OK;
+}
+
 int dpb_mle_free(dpb_mle* mle) {
     if (!mle) return DPB_OK;
     if (mle->owns) device_free(mle->ctx, mle->ptr);

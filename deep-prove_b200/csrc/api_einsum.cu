@@ -25,7 +25,7 @@ static int einsum_impl(dpb_ctx* ctx, const int64_t* tensor, int tensor_on_device
     uint64_t S = 1, C = 1, O = 1;
     for (uint32_t a = 0; a < rank; a++) {
         if (kind[a] == DPB_AXIS_OUTER) {
-            if (!points[a]) return fail(DPB_EINVAL, "outer axis %u has no point", a);
+            if (!points[a] && shape[a] > 1) return fail(DPB_EINVAL, "outer axis %u has no point", a);
             if ((1ull << point_len[a]) < shape[a])
                 return fail(DPB_EINVAL, "axis %u of size %llu needs more than %u variables", a, (unsigned long long)shape[a], point_len[a]);
             outer_dims[n_outer] = shape[a];

@@ -140,6 +140,31 @@ struct LinCombSrc {
     int32_t pad;
 };
 
+// The eq table of a rotary layer with its entries moved and negated the way the rotation pairs them
+// (RopeLayout::permuted_eq_poly, zkml/src/layers/transformer/positional/rope.rs:238-258).
+// layout 0 (adjacent pairs): out[i] = eq[i + 1] for even i, -eq[i - 1] for odd i.
+// layout 1 (rotate half, rows of `row` entries): out[i] = eq[i + row/2] in a row's first half, -eq[i - row/2] in its second.
+template <class F>
+__global__ void __launch_bounds__(kThreads)
+    rope_permuted_eq_kernel(const typename F::E* __restrict__ eq, uint64_t len, int layout, uint64_t row,
+                            typename F::E* __restrict__ out) {
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < len; i += stride) {
+        bool first;
+        uint64_t src;
+        if (layout == 0) {
+            first = (i & 1) == 0;
+            src = i ^ 1;
+        } else {
+            const uint64_t half = row >> 1, c = i % row;
+            first = c < half;
+            src = first ? i + half : i - half;
+        }
+        const typename F::E v = eq[src];
+        out[i] = first ? v : F::neg(v);
+    }
+}
+
 // out[i] = sum_j coeff[j] * table_j[i], tables shorter than the output read as zero beyond their length.
 // Consecutive threads read consecutive entries of each table in turn.
 template <class F>

@@ -46,13 +46,40 @@ class TransformerShape:
     table_bits: int = 12        # activation / requantisation tables (ZKML_BIT_LEN's default, quantization/mod.rs:28-33)
     commit_chunk_log2: int = 20  # committed polynomials are cut into chunks of at most 2^20 (poly_commit/context.rs:103-118)
     range_check_chunks: int = 2  # 16-bit chunks of the logits' max - logit difference (logits.rs:286-298)
+    kv_heads: int = 0            # 0: as many as query heads; fewer: grouped-query attention (K and V shared by groups)
+    glu: bool = False            # gated feed-forward (GeGLU / SwiGLU): two up projections and a GLU linking sumcheck
+    rope: bool = False           # rotary positions on Q and K per block instead of one absolute-position layer
+
+
+@dataclass(frozen=True)
+class MlpShape:
+    """A dense network: layer widths, ReLU through a lookup after every layer but the last, argmax at the end."""
+    name: str
+    widths: tuple
+    batch: int = 1
+    table_bits: int = 12
+    commit_chunk_log2: int = 20
+    range_check_chunks: int = 2
 
 
 GPT2_SMALL = TransformerShape("gpt2-small", layers=12, seq=512, d_model=768, heads=12, head_dim=64, ffn=3072,
                               vocab=50257)
-# the same graph at a size a CPU restatement proves in seconds: every call of the walk, one block
+# BASELINE.json configs[3]: 26 layers, d_model 1152, 4 query heads / 1 KV head, head_dim 256, GeGLU 6912, RMSNorm,
+# RoPE, vocab 262144, 512 tokens
+GEMMA3_1B = TransformerShape("gemma3-1b-style", layers=26, seq=512, d_model=1152, heads=4, head_dim=256, ffn=6912,
+                             vocab=262144, kv_heads=1, glu=True, rope=True)
+# BASELINE.json configs[4]: two blocks of d_model 4096, 32 heads x 128, SwiGLU 11008, RMSNorm, RoPE, vocab 32000,
+# 1024 tokens
+LLAMA2_7B_2BLOCKS = TransformerShape("llama2-7b-style-2-blocks", layers=2, seq=1024, d_model=4096, heads=32,
+                                     head_dim=128, ffn=11008, vocab=32000, glu=True, rope=True)
+# BASELINE.json configs[0]: input 1 x 1024, 1024 x 1024 and 1024 x 10 weights, ReLU through a lookup, argmax
+MLP_2LAYER = MlpShape("mlp-1024-1024-10", widths=(1024, 1024, 10))
+# the same graphs at sizes a CPU restatement proves in seconds: every call of the walk, one block
 TINY = TransformerShape("tiny", layers=1, seq=24, d_model=48, heads=3, head_dim=16, ffn=80, vocab=200, table_bits=8,
                         commit_chunk_log2=8, range_check_chunks=2)
+TINY_GLU_ROPE = TransformerShape("tiny-glu-rope-gqa", layers=1, seq=20, d_model=40, heads=4, head_dim=8, ffn=56,
+                                 vocab=150, table_bits=8, commit_chunk_log2=8, kv_heads=2, glu=True, rope=True)
+TINY_MLP = MlpShape("tiny-mlp", widths=(48, 40, 10), table_bits=8, commit_chunk_log2=8)
 
 
 # one block at a size the CPU restatement walks in some tens of seconds: the bounded sample bench.py times on the host
@@ -92,7 +119,7 @@ def value_table(table, bits):
     arithmetic (tabletype.rs:83-125); they are data to the path, not part of it."""
     if table == "requant":
         return SIGN_MIXED, None, 1
-    if table in ("gelu", "norm"):
+    if table in ("gelu", "norm", "relu"):
         lo, hi = table_input_range(bits, SIGN_MIXED)
         x = np.arange(lo, hi + 1, dtype=np.int64)
         # gelu-like: x * sigmoid(1.702 x) at the table's scale, rounded; norm: a plain clamp at zero
@@ -146,81 +173,84 @@ class PathTimer:
         return _Span()
 
 
-def transformer_path(be, shape, seed=0, blocks=None, with_final=True, with_commit=False):
-    """Walks the path calls of `shape` on backend `be`.  Returns (records, timer): records is a list of
-    (name, kind, payload bytes); timer.by_kind holds seconds per kind of call.  `blocks` limits the number of
-    transformer blocks walked (default: all); `with_final=False` leaves out everything after the last block.
-    with_commit: every lookup layer also commits to its witness columns (one multi-scalar multiplication per
-    chunk of at most 2^commit_chunk_log2 evaluations, zkml/src/lookup/context.rs:420-422), timed as its own kind
-    "witness_commit": the commitment scheme's share of a proof, next to the path's."""
-    rng = np.random.default_rng(seed)
-    T = be.new_transcript()
-    timer = PathTimer(be)
-    rec = []
-    s, e, h, dh, f, V = shape.seq, shape.d_model, shape.heads, shape.head_dim, shape.ffn, shape.vocab
-    bits = shape.table_bits
-    lg = ceil_log2
-    n_blocks = shape.layers if blocks is None else blocks
+class PathWalk:
+    """The calls of the path, one method per kind of layer, over one backend and one transcript.  A model's walk
+    (transformer_path, mlp_path) strings them together in forward order; `records` collects (name, kind, payload)."""
 
-    # ---- per-table logup challenges (ChallengeStorage, zkml/src/iop/mod.rs:174-187) and lookup counters
-    table_keys = ["shift", "zero", "signed", "requant", "gelu", "exp", "norm"]
-    chal = {k: tuple(be.squeeze(T, 2)) for k in table_keys}
-    counts = {"shift": be.new_counts(16), "zero": be.new_counts(16), "signed": be.new_counts(16)}
-    for k in ("requant", "gelu", "exp", "norm"):
-        counts[k] = be.new_counts(bits)
-    committed = []  # (name, table handle, num entries): everything the claim batching at the end opens
-    srs = be.commit_setup(1 << shape.commit_chunk_log2) if with_commit else None
+    TABLE_KEYS = ["shift", "zero", "signed", "requant", "gelu", "exp", "norm", "relu"]
 
-    act_bits = bits + 2
-    specs = {
-        "requant": LookupSpec("requant", bits, right_shift=bits + 1, max_bit_size=2 * bits + 4, sign=SIGN_MIXED),
-        "gelu": LookupSpec("gelu", bits, right_shift=bits + 1, max_bit_size=2 * bits + 4, sign=SIGN_MIXED),
-        "exp": LookupSpec("exp", bits, right_shift=bits - 2, max_bit_size=2 * bits + 10, sign=SIGN_NEGATIVE),
-        "norm": LookupSpec("norm", bits, right_shift=bits, max_bit_size=2 * bits + 2, sign=SIGN_MIXED),
-    }
+    def __init__(self, be, bits, commit_chunk_log2, range_check_chunks, seed, with_commit):
+        self.be, self.bits, self.chunk_log2, self.range_chunks = be, bits, commit_chunk_log2, range_check_chunks
+        self.rng = np.random.default_rng(seed)
+        self.T = be.new_transcript()
+        self.timer = PathTimer(be)
+        self.rec = []
+        self.with_commit = with_commit
+        # per-table logup challenges (ChallengeStorage, zkml/src/iop/mod.rs:174-187) and lookup counters
+        self.chal = {k: tuple(be.squeeze(self.T, 2)) for k in self.TABLE_KEYS}
+        self.counts = {"shift": be.new_counts(16), "zero": be.new_counts(16), "signed": be.new_counts(16)}
+        for k in ("requant", "gelu", "exp", "norm", "relu"):
+            self.counts[k] = be.new_counts(bits)
+        self.used_tables = set()
+        self.committed = []  # (name, table handle, entries): everything the claim batching at the end opens
+        self.srs = be.commit_setup(1 << commit_chunk_log2) if with_commit else None
+        self.act_bits = bits + 2
+        self.specs = {
+            "requant": LookupSpec("requant", bits, right_shift=bits + 1, max_bit_size=2 * bits + 4, sign=SIGN_MIXED),
+            "gelu": LookupSpec("gelu", bits, right_shift=bits + 1, max_bit_size=2 * bits + 4, sign=SIGN_MIXED),
+            "relu": LookupSpec("relu", bits, right_shift=bits + 1, max_bit_size=2 * bits + 4, sign=SIGN_MIXED),
+            "exp": LookupSpec("exp", bits, right_shift=bits - 2, max_bit_size=2 * bits + 10, sign=SIGN_NEGATIVE),
+            "norm": LookupSpec("norm", bits, right_shift=bits, max_bit_size=2 * bits + 2, sign=SIGN_MIXED),
+        }
 
-    def small(shape_):
-        return rng.integers(-(1 << (act_bits - 1)), 1 << (act_bits - 1), size=shape_, dtype=np.int64)
+    # ------------------------------------------------------------------ synthetic data
+    def small(self, shape_):
+        return self.rng.integers(-(1 << (self.act_bits - 1)), 1 << (self.act_bits - 1), size=shape_, dtype=np.int64)
 
-    def weights(shape_):
-        return rng.integers(-(1 << (bits - 1)), 1 << (bits - 1), size=shape_, dtype=np.int64)
+    def weights(self, shape_):
+        return self.rng.integers(-(1 << (self.bits - 1)), 1 << (self.bits - 1), size=shape_, dtype=np.int64)
 
-    def commit_weight(name, w):
-        """A weight matrix as a committed polynomial: padded to powers of two per dimension, as field elements."""
-        dims = [1 << lg(d) for d in w.shape]
+    def draw(self, shape_, table):
+        return draw_tensor(self.rng, shape_, self.specs[table])
+
+    def commit_weight(self, name, w):
+        """A weight matrix as a committed polynomial: padded to powers of two per dimension."""
+        dims = [1 << ceil_log2(d) for d in w.shape]
         padded = np.zeros(dims, dtype=np.int64)
         padded[tuple(slice(0, d) for d in w.shape)] = w
-        committed.append((name, be.int_table(padded.reshape(-1)), padded.size))
+        self.committed.append((name, self.be.int_table(padded.reshape(-1)), padded.size))
 
     # ------------------------------------------------------------------ the calls
-    def einsum(name, lhs, lhs_kinds, rhs, rhs_kinds):
-        """EinSum::prove_internal: fix the outer axes of both tensors at the output claim's point, keep the
-        stacked axes as one table each, sumcheck over the contracted axis
-        sum_t coef_t * lhs_t * rhs_t with the stacking coefficients eq(r_stack, t) (einsum/axis.rs:1043-1062)."""
+    def einsum(self, name, lhs, lhs_kinds, rhs, rhs_kinds, rhs_stack_repeat=1):
+        """EinSum::prove_internal: fix the outer axes of both tensors at the output claim's point, keep the stacked
+        axes as one table each, sumcheck over the contracted axis  sum_t coef_t * lhs_t * rhs_t  with the stacking
+        coefficients eq(r_stack, t) (einsum/axis.rs:1043-1062).  rhs_stack_repeat > 1: grouped-query attention,
+        every right-hand table serves that many consecutive left-hand ones."""
+        be, T, lg = self.be, self.T, ceil_log2
         lhs_dev, rhs_dev = be.tensor(lhs), be.tensor(rhs)  # resident before the clock starts
-        with timer("einsum_fix_axes"):
+        with self.timer("einsum_fix_axes"):
             lp = [be.squeeze(T, lg(d)) if k == AX_OUTER else None for d, k in zip(lhs.shape, lhs_kinds)]
             rp = [be.squeeze(T, lg(d)) if k == AX_OUTER else None for d, k in zip(rhs.shape, rhs_kinds)]
             lt_owner, lt = be.fix_axes(lhs_dev, lhs_kinds, lp)
             rt_owner, rt = be.fix_axes(rhs_dev, rhs_kinds, rp)
         H = len(lt)
-        assert len(rt) == H
-        with timer("einsum_sumcheck"):
-            if H > 1:
-                coef = be.eq_values(be.squeeze(T, lg(H)))[:H]
-            else:
-                coef = [None]
+        assert len(rt) * rhs_stack_repeat == H
+        with self.timer("einsum_sumcheck"):
+            coef = be.eq_values(be.squeeze(T, lg(H)))[:H] if H > 1 else [None]
             n = be.num_vars(lt[0])
-            payload, point, finals = be.sumcheck(T, n, lt + rt, [(coef[t], [t, H + t]) for t in range(H)])
-        rec.append((name, "einsum", payload))
+            terms = [(coef[t], [t, H + t // rhs_stack_repeat]) for t in range(H)]
+            payload, point, finals = be.sumcheck(T, n, lt + rt, terms)
+        self.rec.append((name, "einsum", payload))
         be.free(lt_owner, rt_owner)
 
-    def lookup_layer(name, tensor, spec, variant=VARIANT_STANDARD, weight=None):
+    def lookup_layer(self, name, tensor, table, variant=VARIANT_STANDARD, weight=None, glu=False):
         """prove_lookup_op: witness columns -> batched logup-GKR over the lookups -> linking sumcheck."""
+        be, T, lg, spec = self.be, self.T, ceil_log2, self.specs[table]
         sign, table_out, n_cols = value_table(spec.table, spec.bits)
+        self.used_tables.update(("shift", "zero", "signed", table))
         tensor_dev = be.tensor(tensor)
-        with timer("lookup_witness"):
-            cs = [counts["shift"], counts[spec.table], counts["zero"], counts["signed"]]
+        with self.timer("lookup_witness"):
+            cs = [self.counts["shift"], self.counts[table], self.counts["zero"], self.counts["signed"]]
             wit = be.lookup_witness(tensor_dev, tensor.shape, spec, table_out, n_cols, cs)
             ins, outs = wit["ins"], wit["outs"]
         slices = int(np.prod(tensor.shape[:-2])) if tensor.ndim > 2 else 1
@@ -228,25 +258,25 @@ def transformer_path(be, shape, seed=0, blocks=None, with_final=True, with_commi
         per_in = n_sh + (spec.n_value if n_cols != 1 else 0) + n_z
         per_out = spec.n_value + n_z
         signed = sign == SIGN_MIXED
-        groups = {"shift": [], spec.table: [], "zero": [], "signed": []}
+        groups = {"shift": [], table: [], "zero": [], "signed": []}
         for c in range(slices):
             i0, o0 = c * per_in, c * per_out
             groups["shift"] += ins[i0:i0 + n_sh]
             for v in range(spec.n_value):
                 if n_cols != 1:
-                    groups[spec.table] += [ins[i0 + n_sh + v], outs[o0 + v]]
+                    groups[table] += [ins[i0 + n_sh + v], outs[o0 + v]]
                 else:
-                    groups[spec.table] += [outs[o0 + v]]
+                    groups[table] += [outs[o0 + v]]
             zi0 = i0 + n_sh + (spec.n_value if n_cols != 1 else 0)
             for z in range(n_z):
                 key = "signed" if (signed and z == n_z - 1) else "zero"
                 groups[key] += [ins[zi0 + z], outs[o0 + spec.n_value + z]]
         inputs = []
-        for key, cpi in (("shift", 1), (spec.table, 2 if n_cols != 1 else 1), ("zero", 2), ("signed", 2)):
+        for key, cpi in (("shift", 1), (table, 2 if n_cols != 1 else 1), ("zero", 2), ("signed", 2)):
             if groups[key]:
-                inputs.append(("lookup", groups[key], cpi, None, chal[key][0], chal[key][1]))
-        with timer("lookup_logup"):
-            rec.append((name + ".logup", "logup", be.logup(T, inputs)))
+                inputs.append(("lookup", groups[key], cpi, None, self.chal[key][0], self.chal[key][1]))
+        with self.timer("lookup_logup"):
+            self.rec.append((name + ".logup", "logup", be.logup(T, inputs)))
         dims = [1 << lg(d) for d in tensor.shape]
         total = sum(lg(d) for d in dims)
         n2d = sum(lg(d) for d in dims[-2:]) if tensor.ndim > 1 else lg(dims[-1])
@@ -256,45 +286,49 @@ def transformer_path(be, shape, seed=0, blocks=None, with_final=True, with_commi
             out_min, out_max = int(table_out[0]), int(table_out[-1])
         mles = list(outs)
         extra_owner = []
+        P = 1 << n2d
         if variant in (VARIANT_NORMALISATION, VARIANT_NORMALISATION_WITH_SUM):
             # one input table and one scaling table per slice (variant.rs:288-346)
-            P = 1 << n2d
             for _ in range(2 * slices):
-                tab = be.int_table(small(P))
+                tab = be.int_table(self.small(P))
                 extra_owner.append(tab)
                 mles.append(tab)
-        with timer("lookup_linking"):
+        if glu:
+            # the gate's partner: one witness table per slice multiplies the looked-up value (variant.rs:229-287)
+            variant = VARIANT_GLU
+            for _ in range(slices):
+                tab = be.int_table(self.small(P))
+                extra_owner.append(tab)
+                mles.append(tab)
+        with self.timer("lookup_linking"):
             claim_point = be.squeeze(T, total)
             logup_point = be.squeeze(T, n2d)
             payload = be.linking(T, variant, spec, out_min, out_max, tensor.shape, mles, claim_point, logup_point, weight)
-        rec.append((name + ".linking", "linking", payload))
+        self.rec.append((name + ".linking", "linking", payload))
         # the witness columns are committed polynomials: they are opened at the end
         for j, col in enumerate(ins + outs):
-            committed.append((f"{name}.w{j}", col, 1 << n2d))
-        if with_commit:
-            n_chunks = 1 << max(n2d - shape.commit_chunk_log2, 0)
-            with timer("witness_commit"):
+            self.committed.append((f"{name}.w{j}", col, 1 << n2d))
+        if self.with_commit:
+            n_chunks = 1 << max(n2d - self.chunk_log2, 0)
+            with self.timer("witness_commit"):
                 chunks = [c_ for col in ins + outs for c_ in be.chunks(col, n_chunks)]
-                rec.append((name + ".commit", "commit", be.commit(srs, chunks)))
+                self.rec.append((name + ".commit", "commit", be.commit(self.srs, chunks)))
         be.free(*extra_owner)
         be.keep(wit["owner"])
 
-    def same_poly(name, n_entries, n_claims):
-        """Two claims on the residual stream merged into one (flatten_and_merge_claims, iop/prover.rs:1064-1101)."""
-        tab = be.int_table(small(n_entries))
-        with timer("same_poly"):
-            pts = [be.squeeze(T, lg(n_entries)) for _ in range(n_claims)]
-            rec.append((name, "same_poly", be.same_poly(T, tab, pts)))
+    def same_poly(self, name, n_entries, n_claims):
+        """Claims on one tensor merged into one (flatten_and_merge_claims, iop/prover.rs:1064-1101)."""
+        be, T = self.be, self.T
+        tab = be.int_table(self.small(n_entries))
+        with self.timer("same_poly"):
+            pts = [be.squeeze(T, ceil_log2(n_entries)) for _ in range(n_claims)]
+            self.rec.append((name, "same_poly", be.same_poly(T, tab, pts)))
         be.free(tab)
 
-    def expr_sumcheck(name, kind, n, tables, expr, challenges):
-        with timer(kind):
-            payload, point, finals = be.expr_sumcheck(T, n, tables, expr, challenges)
-        rec.append((name, kind, payload))
-
-    def attention_mask(name, batch, seq):
+    def attention_mask(self, name, batch, seq):
         """AttentionMask::prove_internal: eq * row_lt * col_lt * sum_j chi_j (mask * in_j + NEG (1 - mask)),
         tables eq, mask, row_lt, col_lt, then one input table per head (attention_mask/mod.rs:115-159)."""
+        be, T, lg = self.be, self.T, ceil_log2
         ps = 1 << lg(seq)
         n = 2 * lg(seq)
         i = np.arange(ps)
@@ -302,11 +336,11 @@ def transformer_path(be, shape, seed=0, blocks=None, with_final=True, with_commi
         row_lt = np.repeat((i < seq).astype(np.int64), ps)
         col_lt = np.tile((i < seq).astype(np.int64), ps)
         fixed = [be.int_table(mask.reshape(-1)), be.int_table(row_lt), be.int_table(col_lt)]
-        fixed += [be.int_table(small(ps * ps)) for _ in range(batch)]
-        with timer("attention_mask"):
+        fixed += [be.int_table(self.small(ps * ps)) for _ in range(batch)]
+        with self.timer("attention_mask"):
             tabs = [be.eq_table(be.squeeze(T, n))] + fixed
             chi = be.eq_values(be.squeeze(T, lg(batch)))[:batch] if batch > 1 else [be.scalar(1)]
-            neg = be.const(be.scalar(-(1 << (2 * bits))))
+            neg = be.const(be.scalar(-(1 << (2 * self.bits))))
             lead = be.wit(0) * (be.wit(2) * be.wit(3))
             one_minus = be.const(be.scalar(1)) - be.wit(1)
             e_ = None
@@ -314,77 +348,68 @@ def transformer_path(be, shape, seed=0, blocks=None, with_final=True, with_commi
                 term = lead * be.chal(j) * (be.wit(1) * be.wit(4 + j) + neg * one_minus)
                 e_ = term if e_ is None else e_ + term
             payload, point, finals = be.expr_sumcheck(T, n, tabs, e_, chi)
-        rec.append((name, "attention_mask", payload))
+        self.rec.append((name, "attention_mask", payload))
         be.free(*tabs)
 
-    # ------------------------------------------------------------------ embeddings and positions
-    if with_final:
-        pv, pe = 1 << lg(V), 1 << lg(e)
-        wte = np.zeros((pv, pe), dtype=np.int64)
-        wte[:V, :e] = weights((V, e))
+    def embeddings(self, wte, V, e):
+        """Embeddings::prove: bind the column variables of the padded matrix, then sum_v onehot(v) * E(v)
+        (transformer/embeddings.rs:395-445)."""
+        be, T, lg = self.be, self.T, ceil_log2
+        pv, pe = wte.shape
         wte_tab = be.int_table(wte.reshape(-1))
-        committed.append(("wte", wte_tab, wte.size))
-        one_hot = be.int_table(rng.integers(0, 3, size=pv, dtype=np.int64))
-        with timer("embeddings"):
-            # Embeddings::prove: bind the column variables of the padded matrix, then sum_v onehot(v) * E(v)
+        self.committed.append(("wte", wte_tab, wte.size))
+        one_hot = be.int_table(self.rng.integers(0, 3, size=pv, dtype=np.int64))
+        with self.timer("embeddings"):
             col_point = be.squeeze(T, lg(pe))
             fixed = be.fix_low(wte_tab, col_point)
             payload, point, finals = be.sumcheck(T, lg(pv), [one_hot, fixed], [(None, [0, 1])])
-            rec.append(("embeddings", "embeddings", payload))
+            self.rec.append(("embeddings", "embeddings", payload))
         be.free(fixed, one_hot)
-        # Positional (absolute): fixed_positional * lt * column_eq over the embedding columns
+
+    def positional(self, e):
+        """Positional (absolute): fixed_positional * lt * column_eq over the embedding columns
+        (positional/absolute.rs:290-330)."""
+        be, T, lg = self.be, self.T, ceil_log2
         ps_ = 1 << lg(e)
-        tabs = [be.int_table(small(ps_)), be.int_table((np.arange(ps_) < e).astype(np.int64))]
-        with timer("positional"):
+        tabs = [be.int_table(self.small(ps_)), be.int_table((np.arange(ps_) < e).astype(np.int64))]
+        with self.timer("positional"):
             tabs.append(be.eq_table(be.squeeze(T, lg(ps_))))
             payload, point, finals = be.sumcheck(T, lg(ps_), tabs, [(None, [0, 1, 2])])
-            rec.append(("positional", "positional", payload))
+            self.rec.append(("positional", "positional", payload))
         be.free(*tabs)
 
-    # ------------------------------------------------------------------ transformer blocks
-    for b in range(n_blocks):
-        pre = f"block{b}."
-        x = small((s, e))
-        gamma = be.int_table(np.tile(np.pad(weights(e), (0, (1 << lg(e)) - e)), 1 << lg(s)))
-        lookup_layer(pre + "ln1", draw_tensor(rng, (s, e), specs["norm"]), specs["norm"], VARIANT_NORMALISATION, gamma)
-        w_qkv = weights((e, 3 * e))
-        commit_weight(pre + "w_qkv", w_qkv)
-        einsum(pre + "qkv", x, (AX_OUTER, AX_CONTRACTED), w_qkv, (AX_CONTRACTED, AX_OUTER))
-        lookup_layer(pre + "qkv.requant", draw_tensor(rng, (s, 3 * e), specs["requant"]), specs["requant"])
-        q, k_, v_ = small((h, s, dh)), small((h, s, dh)), small((h, s, dh))
-        einsum(pre + "qk", q, (AX_STACKED, AX_OUTER, AX_CONTRACTED), k_, (AX_STACKED, AX_OUTER, AX_CONTRACTED))
-        attention_mask(pre + "mask", h, s)
-        lookup_layer(pre + "softmax", draw_tensor(rng, (h, s, s), specs["exp"]), specs["exp"], VARIANT_SOFTMAX)
-        a = small((h, s, s))
-        einsum(pre + "av", a, (AX_STACKED, AX_OUTER, AX_CONTRACTED), v_, (AX_STACKED, AX_CONTRACTED, AX_OUTER))
-        lookup_layer(pre + "av.requant", draw_tensor(rng, (s, e), specs["requant"]), specs["requant"])
-        w_o = weights((e, e))
-        commit_weight(pre + "w_o", w_o)
-        einsum(pre + "out", x, (AX_OUTER, AX_CONTRACTED), w_o, (AX_CONTRACTED, AX_OUTER))
-        same_poly(pre + "residual1", (1 << lg(s)) * (1 << lg(e)), 2)
-        lookup_layer(pre + "ln2", draw_tensor(rng, (s, e), specs["norm"]), specs["norm"], VARIANT_NORMALISATION, gamma)
-        w_up = weights((e, f))
-        commit_weight(pre + "w_up", w_up)
-        einsum(pre + "ffn_up", x, (AX_OUTER, AX_CONTRACTED), w_up, (AX_CONTRACTED, AX_OUTER))
-        lookup_layer(pre + "gelu", draw_tensor(rng, (s, f), specs["gelu"]), specs["gelu"])
-        w_down = weights((f, e))
-        commit_weight(pre + "w_down", w_down)
-        einsum(pre + "ffn_down", small((s, f)), (AX_OUTER, AX_CONTRACTED), w_down, (AX_CONTRACTED, AX_OUTER))
-        lookup_layer(pre + "ffn_down.requant", draw_tensor(rng, (s, e), specs["requant"]), specs["requant"])
-        same_poly(pre + "residual2", (1 << lg(s)) * (1 << lg(e)), 2)
-        be.free(gamma)
+    def rope(self, name, heads, seq, dh):
+        """Rotary positions (positional/rope.rs:526-590): bind the head variables of the input (fix_high), then
+        input * lt * (eq * cos + permuted_eq * sin) over the (position, head dimension) variables."""
+        be, T, lg = self.be, self.T, ceil_log2
+        ph, ps_, pd = 1 << lg(heads), 1 << lg(seq), 1 << lg(dh)
+        n = lg(ps_) + lg(pd)
+        x = np.zeros((ph, ps_, pd), dtype=np.int64)
+        x[:heads, :seq, :dh] = self.small((heads, seq, dh))
+        inp = be.int_table(x.reshape(-1))
+        cos, sin = be.int_table(self.small(ps_ * pd)), be.int_table(self.small(ps_ * pd))
+        lt = be.int_table(np.repeat((np.arange(ps_) < seq).astype(np.int64), pd))
+        with self.timer("rope"):
+            fix_point = be.squeeze(T, lg(ph))
+            beta = be.squeeze(T, n)
+            fixed = be.fix_high(inp, fix_point) if lg(ph) else inp
+            eq = be.eq_table(beta)
+            peq = be.permuted_eq(eq)
+            tabs = [fixed, cos, sin, eq, peq, lt]
+            expr = be.wit(0) * be.wit(5) * (be.wit(3) * be.wit(1) + be.wit(4) * be.wit(2))
+            payload, point, finals = be.expr_sumcheck(T, n, tabs, expr, [])
+        self.rec.append((name, "rope", payload))
+        be.free(inp, cos, sin, lt, eq, peq)
+        if lg(ph):
+            be.free(fixed)
 
-    # ------------------------------------------------------------------ head
-    if with_final:
-        gamma = be.int_table(np.tile(np.pad(weights(e), (0, (1 << lg(e)) - e)), 1 << lg(s)))
-        lookup_layer("ln_f", draw_tensor(rng, (s, e), specs["norm"]), specs["norm"], VARIANT_NORMALISATION, gamma)
-        be.free(gamma)
-        einsum("lm_head", small((s, e)), (AX_OUTER, AX_CONTRACTED), wte[:V, :e].T.copy(), (AX_CONTRACTED, AX_OUTER))
-        # Logits (argmax): the range check of max - logit over range_check_chunks 16-bit chunks, then the linking
-        # sumcheck  sum_eq (max - C onehot input) + chi input_eq lt (max - input)   (logits.rs:531-670)
-        ps_, pv_ = 1 << lg(s), 1 << lg(V)
+    def argmax(self, rows, V):
+        """Logits (argmax): the range check of max - logit over range_check_chunks 16-bit chunks, then the linking
+        sumcheck  sum_eq (max - C onehot input) + chi input_eq lt (max - input)   (logits.rs:531-670)."""
+        be, T, lg, rng = self.be, self.T, ceil_log2, self.rng
+        ps_, pv_ = 1 << lg(rows), 1 << lg(V)
         n = lg(ps_) + lg(pv_)
-        logits = small((ps_, pv_))
+        logits = self.small((ps_, pv_))
         logits[:, V:] = 0
         arg = logits[:, :V].argmax(axis=1)
         one_hot = np.zeros((ps_, pv_), dtype=np.int64)
@@ -392,17 +417,18 @@ def transformer_path(be, shape, seed=0, blocks=None, with_final=True, with_commi
         mx = np.repeat(logits[np.arange(ps_), arg], pv_)
         lt = np.tile((np.arange(pv_) < V).astype(np.int64), ps_)
         diff = (mx - logits.reshape(-1)) * lt          # max - logit, zero in the padding
-        chunk_ints = [(diff >> (16 * c_)) & 0xFFFF for c_ in range(shape.range_check_chunks)]
+        chunk_ints = [(diff >> (16 * c_)) & 0xFFFF for c_ in range(self.range_chunks)]
         cols = [be.int_table(c_) for c_ in chunk_ints]
-        with timer("argmax_logup"):
+        self.used_tables.add("shift")
+        with self.timer("argmax_logup"):
             for c_ in chunk_ints:
-                be.count_rows(counts["shift"], c_)
-            rec.append(("argmax.logup", "logup",
-                        be.logup(T, [("lookup", cols, 1, None, chal["shift"][0], chal["shift"][1])])))
+                be.count_rows(self.counts["shift"], c_)
+            self.rec.append(("argmax.logup", "logup",
+                             be.logup(T, [("lookup", cols, 1, None, self.chal["shift"][0], self.chal["shift"][1])])))
         tabs = [be.int_table(logits.reshape(-1)), be.int_table(mx), be.int_table(one_hot.reshape(-1)), None, None,
                 be.int_table(lt)]
-        del diff, chunk_ints
-        with timer("argmax_linking"):
+        del diff, chunk_ints, logits, one_hot, mx, lt
+        with self.timer("argmax_linking"):
             row_point = be.squeeze(T, lg(ps_))
             sum_eq_point = [be.inv2()] * lg(pv_) + list(row_point)
             tabs[3] = be.eq_table(sum_eq_point)
@@ -412,48 +438,154 @@ def transformer_path(be, shape, seed=0, blocks=None, with_final=True, with_commi
             second = be.wit(4) * be.wit(5) * (be.wit(1) - be.wit(0))
             expr = first + be.chal(0) * second
             payload, point, finals = be.expr_sumcheck(T, n, tabs, expr, be.squeeze(T, 1))
-            rec.append(("argmax.linking", "argmax_linking", payload))
+            self.rec.append(("argmax.linking", "argmax_linking", payload))
         for c_ in cols:
-            committed.append(("argmax.chunk", c_, ps_ * pv_))
+            self.committed.append(("argmax.chunk", c_, ps_ * pv_))
         be.free(*tabs)
 
-        # ---------------------------------------------------------------- tables' logup-GKR (prove_tables)
-        inputs = []
+    def tables_logup(self):
+        """prove_tables (zkml/src/iop/prover.rs:220-274): one logup-GKR batch over every table that was looked up,
+        with the multiplicities the lookups left in the counters."""
+        be, T, bits = self.be, self.T, self.bits
         t16 = np.arange(1 << 16, dtype=np.int64)
         s16 = np.arange(-(1 << 15), 1 << 15, dtype=np.int64)
         table_cols = {"shift": [t16], "zero": [t16, (t16 == 0).astype(np.int64)], "signed": [s16, np.sign(s16)]}
-        for key in ("requant", "gelu", "exp", "norm"):
+        for key in ("requant", "gelu", "exp", "norm", "relu"):
             sign, out, n_cols = value_table(key, bits)
             lo, hi = table_input_range(bits, sign)
             ins_ = np.arange(lo, hi + 1, dtype=np.int64)
             table_cols[key] = [ins_] if out is None else [ins_, out]
-        owners = []
-        dev_cols = {key: [be.int_table(c_) for c_ in table_cols[key]] for key in table_keys}
-        with timer("tables_logup"):
-            for key in table_keys:
-                mult = be.multiplicities(counts[key], table_cols[key], value_table(key, bits)[0] if key in specs else None)
+        keys = [k for k in self.TABLE_KEYS if k in self.used_tables]
+        dev_cols = {key: [be.int_table(c_) for c_ in table_cols[key]] for key in keys}
+        owners, inputs = [], []
+        with self.timer("tables_logup"):
+            for key in keys:
+                mult = be.multiplicities(self.counts[key], table_cols[key], None)
                 owners += dev_cols[key] + [mult]
-                inputs.append(("table", dev_cols[key], len(dev_cols[key]), mult, chal[key][0], chal[key][1]))
+                inputs.append(("table", dev_cols[key], len(dev_cols[key]), mult, self.chal[key][0], self.chal[key][1]))
             # a batch is ordered by non-increasing size (prover.rs:95-140)
             inputs.sort(key=lambda i_: -be.num_vars(i_[1][0]))
-            rec.append(("tables.logup", "logup", be.logup(T, inputs)))
+            self.rec.append(("tables.logup", "logup", be.logup(T, inputs)))
         be.free(*owners)
 
-        # ---------------------------------------------------------------- claim batching over every committed polynomial
-        with timer("claim_batching"):
+    def claim_batching(self):
+        """CommitmentProver::claims_batching_sumcheck + the linear combination over every committed polynomial
+        (zkml/src/poly_commit/prover.rs:113-131, 140-255), one claim per polynomial."""
+        be, T = self.be, self.T
+        with self.timer("claim_batching"):
             polys = []
-            cmax = shape.commit_chunk_log2
-            for name, tab, entries in committed:
-                nv = lg(entries)
-                n_chunks = 1 << max(nv - cmax, 0)
+            for name, tab, entries in self.committed:
+                nv = ceil_log2(entries)
+                n_chunks = 1 << max(nv - self.chunk_log2, 0)
                 point = be.squeeze(T, nv)
                 ev = be.squeeze(T, 1)[0]
                 polys.append((be.chunks(tab, n_chunks), [(point, ev)]))
-            rec.append(("claim_batching", "claim_batching", be.claims_batching(T, polys)))
-    rec.append(("transcript", "state", be.transcript_state(T)))
-    be.free(srs)
-    be.release()
-    return rec, timer
+            self.rec.append(("claim_batching", "claim_batching", be.claims_batching(T, polys)))
+
+    def finish(self):
+        be = self.be
+        self.rec.append(("transcript", "state", be.transcript_state(self.T)))
+        be.free(self.srs)
+        be.release()
+        return self.rec, self.timer
+
+
+def transformer_path(be, shape, seed=0, blocks=None, with_final=True, with_commit=False):
+    """Walks the path calls of `shape` on backend `be`.  Returns (records, timer): records is a list of
+    (name, kind, payload bytes); timer.by_kind holds seconds per kind of call.  `blocks` limits the number of
+    transformer blocks walked (default: all); `with_final=False` leaves out everything after the last block.
+    with_commit: every lookup layer also commits to its witness columns (one multi-scalar multiplication per
+    chunk of at most 2^commit_chunk_log2 evaluations, zkml/src/lookup/context.rs:420-422), timed as its own kind
+    "witness_commit": the commitment scheme's share of a proof, next to the path's."""
+    w = PathWalk(be, shape.table_bits, shape.commit_chunk_log2, shape.range_check_chunks, seed, with_commit)
+    s, e, h, dh, f, V = shape.seq, shape.d_model, shape.heads, shape.head_dim, shape.ffn, shape.vocab
+    kv = shape.kv_heads or h
+    lg = ceil_log2
+    n_blocks = shape.layers if blocks is None else blocks
+    O, C, S = AX_OUTER, AX_CONTRACTED, AX_STACKED
+
+    def gamma_table():
+        return be.int_table(np.tile(np.pad(w.weights(e), (0, (1 << lg(e)) - e)), 1 << lg(s)))
+
+    wte = None
+    if with_final:
+        pv, pe = 1 << lg(V), 1 << lg(e)
+        wte = np.zeros((pv, pe), dtype=np.int64)
+        wte[:V, :e] = w.weights((V, e))
+        w.embeddings(wte, V, e)
+        if not shape.rope:
+            w.positional(e)
+
+    for b in range(n_blocks):
+        pre = f"block{b}."
+        x = w.small((s, e))
+        gamma = gamma_table()
+        w.lookup_layer(pre + "norm1", w.draw((s, e), "norm"), "norm", VARIANT_NORMALISATION, gamma)
+        qkv_cols = (h + 2 * kv) * dh
+        w_qkv = w.weights((e, qkv_cols))
+        w.commit_weight(pre + "w_qkv", w_qkv)
+        w.einsum(pre + "qkv", x, (O, C), w_qkv, (C, O))
+        w.lookup_layer(pre + "qkv.requant", w.draw((s, qkv_cols), "requant"), "requant")
+        if shape.rope:
+            w.rope(pre + "rope_q", h, s, dh)
+            w.rope(pre + "rope_k", kv, s, dh)
+        q, k_, v_ = w.small((h, s, dh)), w.small((kv, s, dh)), w.small((kv, s, dh))
+        w.einsum(pre + "qk", q, (S, O, C), k_, (S, O, C), rhs_stack_repeat=h // kv)
+        w.attention_mask(pre + "mask", h, s)
+        w.lookup_layer(pre + "softmax", w.draw((h, s, s), "exp"), "exp", VARIANT_SOFTMAX)
+        w.einsum(pre + "av", w.small((h, s, s)), (S, O, C), v_, (S, C, O), rhs_stack_repeat=h // kv)
+        w.lookup_layer(pre + "av.requant", w.draw((s, h * dh), "requant"), "requant")
+        w_o = w.weights((h * dh, e))
+        w.commit_weight(pre + "w_o", w_o)
+        w.einsum(pre + "out", w.small((s, h * dh)), (O, C), w_o, (C, O))
+        w.same_poly(pre + "residual1", (1 << lg(s)) * (1 << lg(e)), 2)
+        w.lookup_layer(pre + "norm2", w.draw((s, e), "norm"), "norm", VARIANT_NORMALISATION, gamma)
+        w_up = w.weights((e, f))
+        w.commit_weight(pre + "w_up", w_up)
+        w.einsum(pre + "ffn_up", x, (O, C), w_up, (C, O))
+        if shape.glu:
+            w_gate = w.weights((e, f))
+            w.commit_weight(pre + "w_gate", w_gate)
+            w.einsum(pre + "ffn_gate", x, (O, C), w_gate, (C, O))
+            w.lookup_layer(pre + "glu", w.draw((s, f), "gelu"), "gelu", glu=True)
+        else:
+            w.lookup_layer(pre + "gelu", w.draw((s, f), "gelu"), "gelu")
+        w_down = w.weights((f, e))
+        w.commit_weight(pre + "w_down", w_down)
+        w.einsum(pre + "ffn_down", w.small((s, f)), (O, C), w_down, (C, O))
+        w.lookup_layer(pre + "ffn_down.requant", w.draw((s, e), "requant"), "requant")
+        w.same_poly(pre + "residual2", (1 << lg(s)) * (1 << lg(e)), 2)
+        be.free(gamma)
+
+    if with_final:
+        gamma = gamma_table()
+        w.lookup_layer("norm_f", w.draw((s, e), "norm"), "norm", VARIANT_NORMALISATION, gamma)
+        be.free(gamma)
+        w.einsum("lm_head", w.small((s, e)), (O, C), wte[:V, :e].T.copy(), (C, O))
+        w.argmax(s, V)
+        w.tables_logup()
+        w.claim_batching()
+    return w.finish()
+
+
+def mlp_path(be, shape, seed=0, with_commit=False):
+    """The dense network of BASELINE's first configuration: per layer the einsum's axis fixing and sumcheck, then
+    (all but the last layer) ReLU with requantisation through a lookup: witness, logup-GKR, linking sumcheck; at the
+    end the argmax, the tables' logup proof and the claim batching."""
+    w = PathWalk(be, shape.table_bits, shape.commit_chunk_log2, shape.range_check_chunks, seed, with_commit)
+    O, C = AX_OUTER, AX_CONTRACTED
+    widths = shape.widths
+    for i in range(len(widths) - 1):
+        x = w.small((shape.batch, widths[i]))
+        wt = w.weights((widths[i], widths[i + 1]))
+        w.commit_weight(f"layer{i}.w", wt)
+        w.einsum(f"layer{i}.dense", x, (O, C), wt, (C, O))
+        if i < len(widths) - 2:
+            w.lookup_layer(f"layer{i}.relu", w.draw((shape.batch, widths[i + 1]), "relu"), "relu")
+    w.argmax(shape.batch, widths[-1])
+    w.tables_logup()
+    w.claim_batching()
+    return w.finish()
 
 
 # ------------------------------------------------------------------------------ GPU backend
@@ -597,6 +729,12 @@ class GpuBackend:
     def fix_low(self, table, point):
         return self.ctx.fix_low(table, self._pt(point))
 
+    def fix_high(self, table, point):
+        return self.ctx.fix_high(table, self._pt(point))
+
+    def permuted_eq(self, eq):
+        return self.dpb.rope_permuted_eq(self.ctx, eq)
+
     def evaluate(self, table, point):
         return self.ctx.evaluate(table, self._pt(point))
 
@@ -686,16 +824,20 @@ class GpuBackend:
 
 def run_transformer_path(dpb, prover, ctx, shape=GPT2_SMALL, field="fr", seed=0, blocks=None, with_final=True,
                          int_tables=True, with_commit=False):
-    """One walk on the GPU.  Returns dict(seconds, tokens_per_s, by_kind, calls, records); `seconds` and
-    `tokens_per_s` count the path's calls only, `commit_seconds` is the witness commitments' time (with_commit)."""
+    """One walk on the GPU (a TransformerShape or an MlpShape).  Returns dict(seconds, tokens_per_s, by_kind, calls,
+    records); `seconds` and `tokens_per_s` count the path's calls only, `commit_seconds` is the witness
+    commitments' time (with_commit).  For an MlpShape "tokens" are input rows."""
     be = GpuBackend(dpb, prover, ctx, field, int_tables)
     ctx.sync()
     t0 = time.perf_counter()
-    rec, timer = transformer_path(be, shape, seed, blocks, with_final, with_commit)
+    if isinstance(shape, MlpShape):
+        rec, timer = mlp_path(be, shape, seed, with_commit)
+    else:
+        rec, timer = transformer_path(be, shape, seed, blocks, with_final, with_commit)
     ctx.sync()
     wall = time.perf_counter() - t0
     commit_s = timer.by_kind.get("witness_commit", 0.0)
     path_s = sum(timer.by_kind.values()) - commit_s
     return dict(seconds=path_s, commit_seconds=commit_s, wall_seconds=wall,
-                tokens_per_s=shape.seq / path_s if path_s else None,
+                tokens_per_s=(shape.batch if isinstance(shape, MlpShape) else shape.seq) / path_s if path_s else None,
                 by_kind=dict(timer.by_kind), calls=dict(timer.calls), records=rec)

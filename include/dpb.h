@@ -215,6 +215,14 @@ int dpb_eq_table(dpb_ctx* ctx, int family_dtype, const void* point, uint32_t m, 
  * zkml/src/iop/same_poly.rs:90). */
 int dpb_eq_tables(dpb_ctx* ctx, int family_dtype, const void* points, const uint32_t* num_vars, uint32_t n,
                   dpb_mle** out_owner, dpb_mle** out_tables);
+/* The second eq table of a rotary-position layer: the entries of `eq` (challenge
+ * elements) moved and negated the way the rotation pairs its inputs
+ * (RopeLayout::permuted_eq_poly, zkml/src/layers/transformer/positional/rope.rs:238-258;
+ * call site rope.rs:559).  layout 0, adjacent pairs: out[i] = eq[i+1] for even i,
+ * -eq[i-1] for odd i.  layout 1, rotate half over rows of row_size entries:
+ * out[i] = eq[i + row_size/2] in the first half of a row, -eq[i - row_size/2] in
+ * the second (row_size is ignored for layout 0). */
+int dpb_rope_permuted_eq(dpb_ctx* ctx, const dpb_mle* eq, int layout, uint64_t row_size, dpb_mle** out);
 
 /* Binds the top k variables (variable n-k+j := point[j]) -> table of len/2^k.
  * DensePolynomial::fix_high_variables{,_parallel}

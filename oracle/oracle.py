@@ -472,6 +472,23 @@ def fix_low_variables(F, table, point):
     return t
 
 
+def rope_permuted_eq(F, eq, layout=0, row_size=0):
+    """RopeLayout::permuted_eq_poly (zkml/src/layers/transformer/positional/rope.rs:238-258).  layout 0 (Adjacent):
+    pairs (a, b) -> (b, -a).  layout 1 (RotateHalf): each row of row_size entries -> second half, then the negated
+    first half."""
+    v = array_to_scalars(F, eq)
+    out = []
+    if layout == 0:
+        for i in range(0, len(v), 2):
+            out += [v[i + 1], F.neg(v[i])]
+    else:
+        half = row_size // 2
+        for r in range(0, len(v), row_size):
+            row = v[r:r + row_size]
+            out += row[half:] + [F.neg(e) for e in row[:half]]
+    return scalars_to_array(F, out)
+
+
 def fix_high_variables(F, table, point):
     """DensePolynomial::fix_high_variables: the top len(point) variables, with
     point[j] the value of variable n - len(point) + j

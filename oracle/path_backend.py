@@ -113,6 +113,12 @@ class OracleBackend:
     def fix_low(self, table, point):
         return orc.fix_low_variables(self.F, table, list(point))
 
+    def fix_high(self, table, point):
+        return orc.fix_high_variables(self.F, table, list(point))
+
+    def permuted_eq(self, eq):
+        return orc.rope_permuted_eq(self.F, eq)
+
     def evaluate(self, table, point):
         return orc.evaluate(self.F, table, list(point))
 

@@ -83,6 +83,57 @@ def test_gpu_walk_equals_the_cpu_walk(dpb, ctx, wl, field, int_tables):
     assert got["tokens_per_s"] > 0 and set(got["by_kind"]) == set(got["calls"])
 
 
+def test_variant_walks_on_the_cpu_backend():
+    """The gated / rotary / grouped-query block (Gemma- and Llama-style) and the dense network: the calls each adds."""
+    wl = load_workloads_without_gpu()
+    rec, timer = wl.transformer_path(OracleBackend("fr"), wl.TINY_GLU_ROPE, seed=3)
+    names = [r[0] for r in rec]
+    assert "block0.rope_q" in names and "block0.rope_k" in names and "block0.ffn_gate" in names
+    assert "block0.glu.linking" in names and "positional" not in names
+    assert "rope" in timer.by_kind and timer.calls["rope"] == 2
+    rec, timer = wl.mlp_path(OracleBackend("gl"), wl.TINY_MLP, seed=3)
+    assert [r[1] for r in rec] == ["einsum", "logup", "linking", "einsum", "logup", "argmax_linking", "logup",
+                                   "claim_batching", "state"]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("field", ["fr", "gl"])
+@pytest.mark.parametrize("shape", ["TINY_GLU_ROPE", "TINY_MLP"])
+def test_gpu_variant_walks_equal_the_cpu_walks(dpb, ctx, wl, field, shape):
+    """Gated FFN (GLU linking), rotary positions on Q and K, grouped-query attention; the dense network."""
+    prover = importlib.import_module("deep_prove_b200.prover")
+    shape = getattr(wl, shape)
+    if isinstance(shape, wl.MlpShape):
+        want, _ = wl.mlp_path(OracleBackend(field), shape, seed=11)
+    else:
+        want, _ = wl.transformer_path(OracleBackend(field), shape, seed=11)
+    got = wl.run_transformer_path(dpb, prover, ctx, shape, field=field, seed=11)
+    assert [r[:2] for r in got["records"]] == [r[:2] for r in want]
+    for (name, kind, g), (_, _, w) in zip(got["records"], want):
+        assert g == w, f"{name} ({kind}) differs from the CPU restatement"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("field", ["fr", "gl"])
+def test_rope_permuted_eq(dpb, ctx, field):
+    """dpb_rope_permuted_eq against the restated RopeLayout::permuted_eq_poly, both layouts."""
+    import numpy as np
+    from oracle import oracle as orc
+    F = orc.FrField if field == "fr" else orc.GlField
+    fam = dpb.FR if field == "fr" else dpb.GL_BASE
+    rng = np.random.default_rng(5)
+    point = [F.random_scalar(rng) for _ in range(7)]
+    pt = np.ascontiguousarray(orc.scalars_to_array(F, point), dtype=np.uint64)
+    eq = ctx.eq_table(fam, pt)
+    want_eq = orc.eq_evals(F, point)
+    for layout, row in ((0, 0), (1, 16), (1, 128)):
+        got = dpb.rope_permuted_eq(ctx, eq, layout, row).to_host()
+        want = np.asarray(orc.rope_permuted_eq(F, want_eq, layout, row), dtype=np.uint64)
+        assert np.array_equal(got.reshape(want.shape), want)
+    with pytest.raises(dpb.DpbError):
+        dpb.rope_permuted_eq(ctx, eq, 1, 6)  # does not divide 128
+
+
 @pytest.mark.gpu
 def test_gpu_walk_two_blocks_without_head(dpb, ctx, wl):
     """Two blocks, nothing after them: the counters and kept witness columns of a longer walk."""
