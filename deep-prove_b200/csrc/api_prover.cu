@@ -5,6 +5,7 @@
 
 #include "common.cuh"
 #include "host/claims.hpp"
+#include "host/einsum.hpp"
 #include "host/evals.hpp"
 #include "host/logup.hpp"
 #include "host/lookup.hpp"
@@ -24,6 +25,10 @@ struct dpb_transcript {
 };
 
 struct dpb_logup_proof {
+    std::vector<uint8_t> bytes;
+};
+
+struct dpb_einsum_proof {
     std::vector<uint8_t> bytes;
 };
 
@@ -240,6 +245,85 @@ int logup_impl(dpb_ctx* ctx, const dpb_logup_input* inputs, uint32_t n_inputs, T
     auto proof = new_batch_multiple_sizes_prove<F>(ctx, in, tr);
     dpb_logup_proof* p = new dpb_logup_proof();
     p->bytes = proof.serialize();
+    *out = p;
+    return DPB_OK;
+}
+
+// einsum/prove.rs:48-335
+template <class F, class T>
+int einsum_impl(dpb_ctx* ctx, const dpb_einsum_operand* lhs, const dpb_einsum_operand* rhs, uint32_t n_rhs,
+                dpb_mle* lhs_padded, T& tr, dpb_einsum_proof** out) {
+    typedef typename F::E E;
+    using namespace zkml::einsum;
+    auto convert = [&](const dpb_einsum_operand& s, const char* side, uint32_t i) {
+        if (!s.tensor || !s.shape || !s.axis_kind || s.rank == 0)
+            throw dp_crypto::Error(DPB_EINVAL, std::string(side) + " operand " + std::to_string(i) + " has a null field");
+        Operand<F> op;
+        op.tensor = s.tensor;
+        op.on_device = s.tensor_on_device != 0;
+        op.shape.assign(s.shape, s.shape + s.rank);
+        op.kind.assign(s.axis_kind, s.axis_kind + s.rank);
+        op.points.resize(s.rank);
+        for (uint32_t a = 0; a < s.rank; a++) {
+            const uint32_t len = s.axis_point_len ? s.axis_point_len[a] : 0;
+            if (op.kind[a] != DPB_AXIS_CONTRACTED && len) {
+                if (!s.axis_points || !s.axis_points[a])
+                    throw dp_crypto::Error(DPB_EINVAL, std::string(side) + " operand " + std::to_string(i) +
+                                                           ": an axis has a point length but no point");
+                op.points[a] = elems<F>(s.axis_points[a], len);
+            }
+            if (op.kind[a] != DPB_AXIS_CONTRACTED && (1ull << len) < op.shape[a])
+                throw dp_crypto::Error(DPB_EINVAL, std::string(side) + " operand " + std::to_string(i) +
+                                                       ": an outer or stacked axis needs ceil_log2(size) coordinates");
+        }
+        return op;
+    };
+    std::vector<Operand<F>> l, r;
+    for (uint32_t i = 0; i < n_rhs; i++) l.push_back(convert(lhs[i], "left", i));
+    for (uint32_t i = 0; i < n_rhs; i++) r.push_back(convert(rhs[i], "right", i));
+    if (lhs_padded && lhs_padded->ctx != ctx) return fail(DPB_EINVAL, "the padded left tensor belongs to another context");
+    const EinsumProof<F> pr = prove<F>(ctx, l, r, lhs_padded, tr);
+
+    dpb_einsum_proof* p = new dpb_einsum_proof();
+    auto& b = p->bytes;
+    auto u32 = [&](uint64_t v) {
+        const uint32_t x = (uint32_t)v;
+        b.insert(b.end(), (const uint8_t*)&x, (const uint8_t*)&x + 4);
+    };
+    auto scal = [&](const E& v) {
+        uint8_t c[32];
+        dpb::to_canonical(v, c);
+        b.insert(b.end(), c, c + dpb::canonical_size(v));
+    };
+    auto sumcheck = [&](const dp_crypto::IOPProof<F>& sp) {
+        u32(sp.proofs.size());
+        for (const auto& m : sp.proofs) {
+            u32(m.evaluations.size());
+            for (const auto& v : m.evaluations) scal(v);
+        }
+    };
+    auto claim = [&](const std::vector<E>& pt, const E& ev) {
+        u32(pt.size());
+        for (const auto& v : pt) scal(v);
+        scal(ev);
+    };
+    u32(n_rhs);
+    u32(pr.stacking_coeffs[0].size());
+    scal(pr.batching_challenge);
+    for (const auto& cs : pr.stacking_coeffs)
+        for (const auto& v : cs) scal(v);
+    sumcheck(pr.sumcheck);
+    u32(pr.point.size());
+    for (const auto& v : pr.point) scal(v);
+    u32(pr.evaluations.size());
+    for (const auto& v : pr.evaluations) scal(v);
+    for (uint32_t i = 0; i < n_rhs; i++) claim(pr.rhs_points[i], pr.rhs_evals[i]);
+    claim(pr.lhs_point, pr.lhs_eval);
+    u32(pr.aggregated ? 1 : 0);
+    if (pr.aggregated) {
+        scal(pr.input_batching_challenge);
+        sumcheck(pr.aggregation);
+    }
     *out = p;
     return DPB_OK;
 }
@@ -503,6 +587,25 @@ int dpb_logup_proof_serialize(const dpb_logup_proof* p, void* buf, size_t cap, s
     if (cap >= p->bytes.size()) memcpy(buf, p->bytes.data(), p->bytes.size());
     return DPB_OK;
 }
+
+int dpb_einsum_prove(dpb_ctx* ctx, const dpb_einsum_operand* lhs_fixes, const dpb_einsum_operand* rhs, uint32_t n_rhs,
+                     dpb_mle* lhs_padded, dpb_transcript* t, dpb_einsum_proof** out) {
+    if (!ctx || !t || !out || !lhs_fixes || !rhs) return fail(DPB_EINVAL, "null argument");
+    if (n_rhs == 0) return fail(DPB_EINVAL, "an einsum has at least one right tensor");
+    return guarded([&] {
+        return t->gl ? einsum_impl<GlFam>(ctx, lhs_fixes, rhs, n_rhs, lhs_padded, *t->g, out)
+                     : einsum_impl<FrFam>(ctx, lhs_fixes, rhs, n_rhs, lhs_padded, *t->f, out);
+    });
+}
+
+int dpb_einsum_proof_serialize(const dpb_einsum_proof* p, void* buf, size_t cap, size_t* len) {
+    if (!p || !len || (!buf && cap)) return fail(DPB_EINVAL, "null argument");
+    *len = p->bytes.size();
+    if (cap >= p->bytes.size()) memcpy(buf, p->bytes.data(), p->bytes.size());
+    return DPB_OK;
+}
+
+void dpb_einsum_proof_free(dpb_einsum_proof* p) { delete p; }
 
 void dpb_logup_proof_free(dpb_logup_proof* p) { delete p; }
 

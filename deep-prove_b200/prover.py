@@ -29,6 +29,12 @@ class CommittedPolyStruct(ctypes.Structure):
                 ("claim_points", ctypes.c_void_p), ("claim_evals", ctypes.c_void_p)]
 
 
+class EinsumOperandStruct(ctypes.Structure):
+    _fields_ = [("tensor", ctypes.c_void_p), ("tensor_on_device", ctypes.c_int32), ("rank", ctypes.c_uint32),
+                ("shape", ctypes.c_void_p), ("axis_kind", ctypes.c_void_p), ("axis_points", ctypes.c_void_p),
+                ("axis_point_len", ctypes.c_void_p)]
+
+
 _size_t = ctypes.c_size_t
 PROVER_SIGNATURES = {
     "dpb_transcript_new": (_int, [_int, _vp, _size_t, _pp]),
@@ -57,6 +63,10 @@ PROVER_SIGNATURES = {
     "dpb_logup_batch_prove": (_int, [_vp, ctypes.POINTER(LogupInputStruct), _u32, _vp, _pp]),
     "dpb_logup_proof_serialize": (_int, [_vp, _vp, _size_t, ctypes.POINTER(_size_t)]),
     "dpb_logup_proof_free": (None, [_vp]),
+    "dpb_einsum_prove": (_int, [_vp, ctypes.POINTER(EinsumOperandStruct), ctypes.POINTER(EinsumOperandStruct), _u32, _vp,
+                                _vp, _pp]),
+    "dpb_einsum_proof_serialize": (_int, [_vp, _vp, _size_t, ctypes.POINTER(_size_t)]),
+    "dpb_einsum_proof_free": (None, [_vp]),
 }
 for _name, (_res, _args) in PROVER_SIGNATURES.items():
     _fn = getattr(lib, _name)
@@ -383,3 +393,60 @@ def new_batch_multiple_sizes_prove(ctx, inputs, transcript):
         return bytes(buf)
     finally:
         lib.dpb_logup_proof_free(h)
+
+
+class EinsumOperand:
+    """One tensor of an einsum and what happens to its axes (dpb_einsum_operand).  tensor: int64 ndarray (unpadded)
+    or, with device_tensor = ctx.upload_tensor_i64(...), a tensor already on the device; kinds[a] in AXIS_*;
+    points[a]: challenge elements uint64[len, words] for outer and stacked axes, None for contracted ones."""
+
+    def __init__(self, tensor, kinds, points, device_tensor=None):
+        if device_tensor is not None:
+            mle, shape = device_tensor
+            self._keep = [mle]
+            self.ptr, self.on_device = lib.dpb_mle_device_ptr(mle.h), 1
+        else:
+            t = np.ascontiguousarray(tensor, dtype=np.int64)
+            shape = t.shape
+            self._keep = [t]
+            self.ptr, self.on_device = t.ctypes.data, 0
+        rank = len(shape)
+        self.shape = (ctypes.c_uint64 * rank)(*shape)
+        self.kinds = (ctypes.c_uint8 * rank)(*kinds)
+        pts = [np.ascontiguousarray(p, dtype=np.uint64) if p is not None else None for p in points]
+        self._keep.append(pts)
+        self.points = (ctypes.c_void_p * rank)(*[p.ctypes.data if p is not None and p.size else None for p in pts])
+        self.lens = (ctypes.c_uint32 * rank)(*[0 if p is None or not p.size else p.shape[0] for p in pts])
+        self.rank = rank
+
+    def fill(self, s):
+        s.tensor, s.tensor_on_device, s.rank = self.ptr, self.on_device, self.rank
+        s.shape = ctypes.cast(self.shape, ctypes.c_void_p)
+        s.axis_kind = ctypes.cast(self.kinds, ctypes.c_void_p)
+        s.axis_points = ctypes.cast(self.points, ctypes.c_void_p)
+        s.axis_point_len = ctypes.cast(self.lens, ctypes.c_void_p)
+
+
+def einsum_prove(ctx, lhs_fixes, rhs, transcript, lhs_padded=None):
+    """EinSum::prove_internal (zkml/src/layers/einsum/prove.rs:48-335) below the axis mapping: lhs_fixes[i] is the
+    left tensor with output i's fixes, rhs[i] the right tensor of output i (EinsumOperand each); lhs_padded (an
+    Mle, the left tensor padded to powers of two per axis) is needed when there are several outputs.  Returns the
+    flat canonical encoding of the proof (see include/dpb_prover.h)."""
+    n = len(rhs)
+    if len(lhs_fixes) != n:
+        raise ValueError("one fix of the left tensor per right tensor")
+    la, ra = (EinsumOperandStruct * n)(), (EinsumOperandStruct * n)()
+    for i in range(n):
+        lhs_fixes[i].fill(la[i])
+        rhs[i].fill(ra[i])
+    h = ctypes.c_void_p()
+    check(lib.dpb_einsum_prove(ctx.h, la, ra, n, lhs_padded.h if lhs_padded is not None else None, transcript.h,
+                               ctypes.byref(h)))
+    try:
+        sz = ctypes.c_size_t()
+        check(lib.dpb_einsum_proof_serialize(h, None, 0, ctypes.byref(sz)))
+        buf = (ctypes.c_uint8 * sz.value)()
+        check(lib.dpb_einsum_proof_serialize(h, buf, sz.value, ctypes.byref(sz)))
+        return bytes(buf)
+    finally:
+        lib.dpb_einsum_proof_free(h)

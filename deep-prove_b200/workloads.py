@@ -221,27 +221,20 @@ class PathWalk:
         self.committed.append((name, self.be.int_table(padded.reshape(-1)), padded.size))
 
     # ------------------------------------------------------------------ the calls
-    def einsum(self, name, lhs, lhs_kinds, rhs, rhs_kinds, rhs_stack_repeat=1):
-        """EinSum::prove_internal: fix the outer axes of both tensors at the output claim's point, keep the stacked
-        axes as one table each, sumcheck over the contracted axis  sum_t coef_t * lhs_t * rhs_t  with the stacking
-        coefficients eq(r_stack, t) (einsum/axis.rs:1043-1062).  rhs_stack_repeat > 1: grouped-query attention,
-        every right-hand table serves that many consecutive left-hand ones."""
+    def einsum(self, name, lhs, lhs_kinds, rhs, rhs_kinds):
+        """EinSum::prove_internal (zkml/src/layers/einsum/prove.rs:48-335) with one right tensor: the outer axes of
+        both tensors are bound to (squeezed stand-ins for) the output claim's coordinates, the stacked axes (heads)
+        share one point that gives the stacking coefficients, and the sumcheck runs over the contracted axis."""
         be, T, lg = self.be, self.T, ceil_log2
         lhs_dev, rhs_dev = be.tensor(lhs), be.tensor(rhs)  # resident before the clock starts
-        with self.timer("einsum_fix_axes"):
-            lp = [be.squeeze(T, lg(d)) if k == AX_OUTER else None for d, k in zip(lhs.shape, lhs_kinds)]
-            rp = [be.squeeze(T, lg(d)) if k == AX_OUTER else None for d, k in zip(rhs.shape, rhs_kinds)]
-            lt_owner, lt = be.fix_axes(lhs_dev, lhs_kinds, lp)
-            rt_owner, rt = be.fix_axes(rhs_dev, rhs_kinds, rp)
-        H = len(lt)
-        assert len(rt) * rhs_stack_repeat == H
-        with self.timer("einsum_sumcheck"):
-            coef = be.eq_values(be.squeeze(T, lg(H)))[:H] if H > 1 else [None]
-            n = be.num_vars(lt[0])
-            terms = [(coef[t], [t, H + t // rhs_stack_repeat]) for t in range(H)]
-            payload, point, finals = be.sumcheck(T, n, lt + rt, terms)
+        with self.timer("einsum"):
+            lp = [be.squeeze(T, lg(d)) if k != AX_CONTRACTED else None for d, k in zip(lhs.shape, lhs_kinds)]
+            stacked = [p for p, k in zip(lp, lhs_kinds) if k == AX_STACKED]
+            rp = []
+            for d, k in zip(rhs.shape, rhs_kinds):
+                rp.append(stacked.pop(0) if k == AX_STACKED else be.squeeze(T, lg(d)) if k == AX_OUTER else None)
+            payload = be.einsum_prove(T, lhs_dev, lhs.shape, lhs_kinds, lp, rhs_dev, rhs.shape, rhs_kinds, rp)
         self.rec.append((name, "einsum", payload))
-        be.free(lt_owner, rt_owner)
 
     def lookup_layer(self, name, tensor, table, variant=VARIANT_STANDARD, weight=None, glu=False):
         """prove_lookup_op: witness columns -> batched logup-GKR over the lookups -> linking sumcheck."""
@@ -529,11 +522,14 @@ def transformer_path(be, shape, seed=0, blocks=None, with_final=True, with_commi
         if shape.rope:
             w.rope(pre + "rope_q", h, s, dh)
             w.rope(pre + "rope_k", kv, s, dh)
-        q, k_, v_ = w.small((h, s, dh)), w.small((kv, s, dh)), w.small((kv, s, dh))
-        w.einsum(pre + "qk", q, (S, O, C), k_, (S, O, C), rhs_stack_repeat=h // kv)
+        # grouped-query attention: every K / V head serves h // kv query heads; the proof sees them repeated
+        q = w.small((h, s, dh))
+        k_ = np.repeat(w.small((kv, s, dh)), h // kv, axis=0)
+        v_ = np.repeat(w.small((kv, s, dh)), h // kv, axis=0)
+        w.einsum(pre + "qk", q, (S, O, C), k_, (S, O, C))
         w.attention_mask(pre + "mask", h, s)
         w.lookup_layer(pre + "softmax", w.draw((h, s, s), "exp"), "exp", VARIANT_SOFTMAX)
-        w.einsum(pre + "av", w.small((h, s, s)), (S, O, C), v_, (S, C, O), rhs_stack_repeat=h // kv)
+        w.einsum(pre + "av", w.small((h, s, s)), (S, O, C), v_, (S, C, O))
         w.lookup_layer(pre + "av.requant", w.draw((s, h * dh), "requant"), "requant")
         w_o = w.weights((h * dh, e))
         w.commit_weight(pre + "w_o", w_o)
@@ -710,6 +706,15 @@ class GpuBackend:
         views = [table.view(i * per, per) for i in range(n_chunks)]
         self._kept += views
         return views
+
+    def einsum_prove(self, T, lhs, lhs_shape, lhs_kinds, lhs_points, rhs, rhs_shape, rhs_kinds, rhs_points):
+        pt = lambda ps: [self._pt(p) if p is not None else None for p in ps]
+        lo = self.prover.EinsumOperand(None, lhs_kinds, pt(lhs_points), device_tensor=lhs)
+        ro = self.prover.EinsumOperand(None, rhs_kinds, pt(rhs_points), device_tensor=rhs)
+        payload = self.prover.einsum_prove(self.ctx, [lo], [ro], T)
+        lhs[0].free()
+        rhs[0].free()
+        return payload
 
     def fix_axes(self, tensor, kinds, points):
         pts = [self._pt(p) if p is not None else None for p in points]

@@ -156,6 +156,41 @@ int dpb_logup_batch_prove(dpb_ctx* ctx, const dpb_logup_input* inputs, uint32_t 
 int dpb_logup_proof_serialize(const dpb_logup_proof* p, void* buf, size_t cap, size_t* len);
 void dpb_logup_proof_free(dpb_logup_proof* p);
 
+/* ---- einsum layer ------------------------------------------------------------- */
+/* One tensor of an einsum with what happens to each of its axes: DPB_AXIS_OUTER axes are bound to their point,
+ * DPB_AXIS_STACKED axes are kept (one table per index) and their point gives the stacking coefficients,
+ * DPB_AXIS_CONTRACTED axes are summed over by the sumcheck (no point).  `tensor` as for dpb_einsum_fix_axes. */
+typedef struct dpb_einsum_operand {
+    const int64_t* tensor;
+    int32_t tensor_on_device;
+    uint32_t rank;
+    const uint64_t* shape;            /* unpadded extents */
+    const uint8_t* axis_kind;         /* DPB_AXIS_* per axis */
+    const void* const* axis_points;   /* per axis: challenge elements on the host, or NULL */
+    const uint32_t* axis_point_len;
+} dpb_einsum_operand;
+typedef struct dpb_einsum_proof dpb_einsum_proof;
+/* EinSum::prove_internal (zkml/src/layers/einsum/prove.rs:48-335) below the axis mapping and without biases (a
+ * bias claim is an evaluation, dpb_bias_evaluation; it does not touch the transcript): n_rhs right tensors, one
+ * output each; lhs_fixes[i] is the LEFT tensor with the fixes of output i (FixedAxesMapping::lhs_fixes,
+ * einsum/axis.rs:1043-1075; the same tensor in every entry), rhs[i] the right tensor of output i.  Steps: axis
+ * fixing of every operand, stacking coefficients prod evals(point)[..size] over the stacked axes (first stacked
+ * axis slowest), gamma = append_and_sample("batching_challenge"), the sumcheck
+ *   sum_i gamma^i sum_t coef[i][t] * lhs[i][t] * rhs[i][t]        (einsum/op_info.rs:159-195)
+ * and the input claims (reconstruct_full_point, prove.rs:338-361).  With n_rhs > 1 the claims on the left tensor
+ * are merged by the sumcheck  input * sum_i c^i eq_i  over `lhs_padded`, the left tensor padded to powers of two
+ * per axis (prove.rs:260-288; c = append_and_sample("input_batching_challenge")); lhs_padded may be NULL when
+ * n_rhs == 1. */
+int dpb_einsum_prove(dpb_ctx* ctx, const dpb_einsum_operand* lhs_fixes, const dpb_einsum_operand* rhs, uint32_t n_rhs,
+                     dpb_mle* lhs_padded, dpb_transcript* t, dpb_einsum_proof** out);
+/* Flat encoding (u32 counts, canonical scalars): n_rhs, S, gamma, the n_rhs x S stacking coefficients, the sumcheck
+ * (rounds, then per round its count and evaluations), the sumcheck point (count first), the final evaluations
+ * (count first: the left tables of every output, then the right tables), per right tensor its claim (point count,
+ * point, evaluation), the left tensor's claim in the same form, 1 or 0 for a merged left claim and, when 1, c and
+ * the merging sumcheck.  Writes at most cap bytes; *len is the size needed. */
+int dpb_einsum_proof_serialize(const dpb_einsum_proof* p, void* buf, size_t cap, size_t* len);
+void dpb_einsum_proof_free(dpb_einsum_proof* p);
+
 /* ---- lookup linking sumcheck ---------------------------------------------------- */
 #define DPB_VARIANT_STANDARD 0 /* LookupVariant::Standard */
 #define DPB_VARIANT_GLU 1      /* LookupVariant::GLU: one more witness table per slice, multiplied into the output */

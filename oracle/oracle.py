@@ -1117,6 +1117,36 @@ def serialize_logup_proof(F, p):
     return bytes(out)
 
 
+def serialize_einsum_proof(F, p):
+    """The flat encoding of einsum_prove's result that the library's dpb_einsum_proof_serialize writes."""
+    out = bytearray()
+    u32 = lambda x: int(x).to_bytes(4, "little")
+
+    def sumcheck(sp):
+        b = u32(len(sp))
+        for ev in sp:
+            b += u32(len(ev)) + serialize_scalars(F, ev)
+        return b
+
+    def claim(c):
+        return u32(len(c[0])) + serialize_scalars(F, c[0]) + serialize_scalars(F, [c[1]])
+    out += u32(len(p["stacking_coeffs"])) + u32(len(p["stacking_coeffs"][0]))
+    out += serialize_scalars(F, [p["batching_challenge"]])
+    for cs in p["stacking_coeffs"]:
+        out += serialize_scalars(F, cs)
+    out += sumcheck(p["sumcheck"])
+    out += u32(len(p["point"])) + serialize_scalars(F, p["point"])
+    out += u32(len(p["evaluations"])) + serialize_scalars(F, p["evaluations"])
+    for c in p["rhs_claims"]:
+        out += claim(c)
+    out += claim(p["lhs_claim"])
+    if p["aggregation"] is None:
+        out += u32(0)
+    else:
+        out += u32(1) + serialize_scalars(F, [p["aggregation"]["challenge"]]) + sumcheck(p["aggregation"]["sumcheck"])
+    return bytes(out)
+
+
 # ------------------------------------------------------------ einsum axis fixing
 AXIS_CONTRACTED, AXIS_OUTER, AXIS_STACKED = 0, 1, 2
 
@@ -1156,6 +1186,97 @@ def mles_from_tensor(F, tensor_i64, kinds, points):
     for start in range(0, len(cur), contraction):
         vals = cur[start:start + contraction] + [F.zero] * pad
         out.append(scalars_to_array(F, vals))
+    return out
+
+
+def stacking_coefficients(F, shape, kinds, points):
+    """FixedAxesMapping::lhs_fixes / stacking_coefficients (zkml/src/layers/einsum/axis.rs:1043-1062, 1077-1100):
+    the product over the Stacked axes of evals(point)[..size], the FIRST stacked axis the slowest index."""
+    acc = [F.one]
+    for axis in reversed(range(len(shape))):
+        if kinds[axis] != AXIS_STACKED:
+            continue
+        beta = array_to_scalars(F, eq_evals(F, points[axis]))[:shape[axis]]
+        acc = [F.mul(a, b) for b in beta for a in acc]
+    return acc
+
+
+def reconstruct_full_point(kinds, points, sumcheck_point, padded_shape):
+    """reconstruct_full_point (zkml/src/layers/einsum/prove.rs:338-361): the axes from last to first; Outer and
+    Stacked axes give their own point, a Contracted axis the next ceil_log2(dim) sumcheck coordinates."""
+    out, skip = [], 0
+    for axis in reversed(range(len(kinds))):
+        if kinds[axis] == AXIS_CONTRACTED:
+            n = max(int(padded_shape[axis]) - 1, 0).bit_length()
+            out += list(sumcheck_point[skip:skip + n])
+            skip += n
+        else:
+            out += list(points[axis])
+    return out
+
+
+def einsum_prove(F, transcript, lhs, lhs_fixes, rhs, lhs_padded=None):
+    """EinSum::prove_internal (zkml/src/layers/einsum/prove.rs:48-335) below the axis mapping and without biases
+    (a bias claim is an evaluation, prove.rs:190-213; it does not touch the transcript).
+
+    lhs: the left tensor (int64 array, unpadded); lhs_fixes[i] = (kinds, points) fixes it for output i;
+    rhs[i] = (tensor, kinds, points) is the right tensor of output i.  Outer and Stacked axes carry points.
+    The sumcheck proves  sum_i gamma^i sum_t coef_{i,t} lhs_{i,t} rhs_{i,t}  with gamma sampled under the label
+    "batching_challenge" (prove.rs:157; expression: op_info.rs:159-195).  With more than one output the claims on
+    the left tensor are merged by a second sumcheck  input * sum_i c^i eq_i  over the padded left tensor
+    `lhs_padded` (prove.rs:260-288), c sampled under "input_batching_challenge"."""
+    R = len(rhs)
+    assert len(lhs_fixes) == R and R >= 1
+    lhs = np.asarray(lhs, dtype=np.int64)
+    lhs_tabs, coeffs = [], []
+    for kinds, points in lhs_fixes:
+        lhs_tabs.append(mles_from_tensor(F, lhs, tuple(kinds), list(points)))
+        coeffs.append(stacking_coefficients(F, lhs.shape, kinds, points))
+    rhs_tabs = [mles_from_tensor(F, np.asarray(t, dtype=np.int64), tuple(k), list(p)) for t, k, p in rhs]
+    S = len(coeffs[0])
+    assert all(len(t) == S for t in lhs_tabs + rhs_tabs)
+    gamma = transcript.append_and_sample(b"batching_challenge")
+    e = None
+    for i in range(R):
+        off, roff = i * S, R * S + i * S
+        inner = Expr.const(coeffs[i][0]) * Expr.wit(off) * Expr.wit(roff)
+        for j in range(1, S):
+            inner = Expr.const(coeffs[i][j]) * Expr.wit(off + j) * Expr.wit(roff + j) + inner
+        term = Expr.chal(0, i, F.one, F.zero) * inner
+        e = term if e is None else e + term
+    terms = expr_to_terms(F, e, [gamma])
+    tables = [t for ts in lhs_tabs for t in ts] + [t for ts in rhs_tabs for t in ts]
+    n = table_len(tables[0]).bit_length() - 1
+    proof, point, finals = sumcheck_prove(F, n, tables, terms, transcript)
+
+    def pad(shape):
+        return [1 << max(int(d) - 1, 0).bit_length() for d in shape]
+
+    def comb(c, ev):
+        acc = F.zero
+        for a, b in zip(c, ev):
+            acc = F.add(acc, F.mul(a, b))
+        return acc
+    rhs_claims = []
+    for i, (t, kinds, points) in enumerate(rhs):
+        full = reconstruct_full_point(kinds, points, point, pad(np.asarray(t).shape))
+        rhs_claims.append((full, comb(coeffs[i], finals[R * S + i * S:R * S + (i + 1) * S])))
+    out = dict(batching_challenge=gamma, stacking_coeffs=coeffs, sumcheck=proof, point=point, evaluations=finals,
+               rhs_claims=rhs_claims, aggregation=None)
+    if R == 1:
+        kinds, points = lhs_fixes[0]
+        out["lhs_claim"] = (reconstruct_full_point(kinds, points, point, pad(lhs.shape)), comb(coeffs[0], finals[:S]))
+        return out
+    eqs = [eq_evals(F, reconstruct_full_point(k, p, point, pad(lhs.shape))) for k, p in lhs_fixes]
+    c = transcript.append_and_sample(b"input_batching_challenge")
+    agg = None
+    for i in range(R):
+        term = Expr.wit(0) * Expr.wit(i + 1) * Expr.chal(0, i, F.one, F.zero)
+        agg = term if agg is None else agg + term
+    nv = table_len(lhs_padded).bit_length() - 1
+    a_proof, a_point, a_finals = sumcheck_prove(F, nv, [lhs_padded] + eqs, expr_to_terms(F, agg, [c]), transcript)
+    out["aggregation"] = dict(challenge=c, sumcheck=a_proof, point=a_point)
+    out["lhs_claim"] = (a_point, a_finals[0])
     return out
 
 

@@ -101,6 +101,11 @@ class OracleBackend:
         per = orc.table_len(table) // n_chunks
         return [table[i * per:(i + 1) * per] for i in range(n_chunks)]
 
+    def einsum_prove(self, T, lhs, lhs_shape, lhs_kinds, lhs_points, rhs, rhs_shape, rhs_kinds, rhs_points):
+        got = orc.einsum_prove(self.F, T, lhs.reshape(lhs_shape), [(tuple(lhs_kinds), list(lhs_points))],
+                               [(rhs.reshape(rhs_shape), tuple(rhs_kinds), list(rhs_points))])
+        return orc.serialize_einsum_proof(self.F, got)
+
     def fix_axes(self, tensor, kinds, points):
         return None, orc.mles_from_tensor(self.F, tensor, tuple(kinds), list(points))
 

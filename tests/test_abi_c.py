@@ -42,7 +42,10 @@ static void layouts(void) {
     END(); printf(", ");
     SZ(dpb_logup_input); OFF(dpb_logup_input, kind); OFF(dpb_logup_input, columns); OFF(dpb_logup_input, n_columns);
     OFF(dpb_logup_input, columns_per_instance); OFF(dpb_logup_input, multiplicities);
-    OFF(dpb_logup_input, constant_challenge); OFF(dpb_logup_input, column_separation_challenge); END();
+    OFF(dpb_logup_input, constant_challenge); OFF(dpb_logup_input, column_separation_challenge); END(); printf(", ");
+    SZ(dpb_einsum_operand); OFF(dpb_einsum_operand, tensor); OFF(dpb_einsum_operand, tensor_on_device);
+    OFF(dpb_einsum_operand, rank); OFF(dpb_einsum_operand, shape); OFF(dpb_einsum_operand, axis_kind);
+    OFF(dpb_einsum_operand, axis_points); OFF(dpb_einsum_operand, axis_point_len); END();
     printf("}\n");
 }
 
@@ -133,6 +136,9 @@ def test_headers_compile_as_c_and_layouts_match_the_bindings(dpb, c_program):
                                                                              "columns_per_instance", "multiplicities",
                                                                              "constant_challenge",
                                                                              "column_separation_challenge"])
+    assert got["dpb_einsum_operand"] == ctypes_layout(prover.EinsumOperandStruct, ["tensor", "tensor_on_device", "rank",
+                                                                                   "shape", "axis_kind", "axis_points",
+                                                                                   "axis_point_len"])
 
 
 @pytest.mark.gpu

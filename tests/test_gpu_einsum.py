@@ -116,3 +116,43 @@ def test_fix_axes_errors(dpb, ctx):
     with pytest.raises(dpb.DpbError) as e:
         ctx.einsum_fix_axes(dpb.FR, t, (C, 7), [None, None])
     assert e.value.code == dpb.EINVAL
+
+
+@pytest.mark.parametrize("F", FIELDS)
+def test_einsum_prove_matches_oracle(dpb, ctx, F):
+    """dpb_einsum_prove (axis fixing, stacking coefficients, batching challenge, sumcheck, input claims and, with two
+    outputs, the merging sumcheck over the padded left tensor) byte for byte against the restated
+    EinSum::prove_internal, with host and device tensors; the transcripts end in the same state."""
+    import importlib
+    from tests.test_oracle_pins import _padded_mle, einsum_cases
+    prover = importlib.import_module("deep_prove_b200.prover")
+    fam = family_dtype(dpb, F)
+    rng = np.random.default_rng(33)
+
+    def arr(p):
+        return None if p is None else np.ascontiguousarray(orc.scalars_to_array(F, p), dtype=np.uint64).reshape(len(p), -1)
+    for name, lhs, fixes, rhs, _, _ in einsum_cases(F, rng):
+        for on_device in (False, True):
+            To = orc.Transcript(F)
+            want = orc.serialize_einsum_proof(F, orc.einsum_prove(F, To, lhs, fixes, rhs, lhs_padded=_padded_mle(F, lhs)))
+            Tg = prover.Blake3Transcript(fam)
+            dev = (lambda t: ctx.upload_tensor_i64(np.ascontiguousarray(t, dtype=np.int64))) if on_device else (lambda t: None)
+            lops = [prover.EinsumOperand(lhs, k, [arr(p) for p in pts], device_tensor=dev(lhs)) for k, pts in fixes]
+            rops = [prover.EinsumOperand(t, k, [arr(p) for p in pts], device_tensor=dev(t)) for t, k, pts in rhs]
+            padded = ctx.upload(np.asarray(_padded_mle(F, lhs)), fam if F is orc.FrField else dpb.GL_BASE) \
+                if len(rhs) > 1 else None
+            got = prover.einsum_prove(ctx, lops, rops, Tg, lhs_padded=padded)
+            assert got == want, (name, on_device)
+            assert Tg.state() == (To.state, To.round), name
+    # an outer axis of more than one entry needs its point; the stacked axes must span the same number of tables
+    x = np.ones((2, 2), dtype=np.int64)
+    with pytest.raises(dpb.DpbError):
+        prover.einsum_prove(ctx, [prover.EinsumOperand(x, (O, C), [None, None])],
+                            [prover.EinsumOperand(x, (C, C), [None, None])], prover.Blake3Transcript(fam))
+    one = arr([F.random_scalar(rng)])
+    with pytest.raises(dpb.DpbError):
+        prover.einsum_prove(ctx, [prover.EinsumOperand(x, (S, C), [one, None])],
+                            [prover.EinsumOperand(x, (C, C), [None, None])], prover.Blake3Transcript(fam))
+    with pytest.raises(ValueError):
+        op = prover.EinsumOperand(x, (C, C), [None, None])
+        prover.einsum_prove(ctx, [op], [op, op], prover.Blake3Transcript(fam))

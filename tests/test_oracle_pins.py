@@ -442,3 +442,73 @@ def test_broadcasted_bias_eval(F):
         bias_eval = orc.evaluate(F, F.table_from_i64(padded_bias.reshape(-1)), bias_point)
         got, pt = orc.compute_bias_evaluation(F, "ijl", "il", split, bias_eval, out_shape)
         assert got == want and pt == bias_point
+
+
+def _padded_mle(F, t):
+    """The tensor zero-padded to powers of two per axis, as a table (last axis lowest variables)."""
+    dims = [1 << max(d - 1, 0).bit_length() for d in t.shape]
+    p = np.zeros(dims, dtype=np.int64)
+    p[tuple(slice(0, d) for d in t.shape)] = t
+    return F.table_from_i64(p.reshape(-1))
+
+
+def einsum_cases(F, rng):
+    """(name, lhs, lhs_fixes, rhs, subscripts per output, output points) of the layer shapes the path uses."""
+    C, O, S = orc.AXIS_CONTRACTED, orc.AXIS_OUTER, orc.AXIS_STACKED
+    lg = lambda d: max(d - 1, 0).bit_length()
+    pt = lambda d: [F.random_scalar(rng) for _ in range(lg(d))]
+    cases = []
+    # dense layer: x[m, k] w[k, n]
+    x, w = rng.integers(-99, 99, (6, 10)), rng.integers(-99, 99, (10, 5))
+    rp, cp = pt(6), pt(5)
+    cases.append(("dense", x, [((O, C), [rp, None])], [(w, (C, O), [None, cp])], ["mk,kn->mn"], [cp + rp]))
+    # attention scores: q[h, s, d] k[h, t, d], stacked heads
+    q, k = rng.integers(-9, 9, (3, 5, 4)), rng.integers(-9, 9, (3, 6, 4))
+    hp, sp, tp = pt(3), pt(5), pt(6)
+    cases.append(("qk", q, [((S, O, C), [hp, sp, None])], [(k, (S, O, C), [hp, tp, None])], ["hsd,htd->hst"],
+                  [tp + sp + hp]))
+    # one left tensor, two right tensors (a fused projection): two outputs, the left claims are merged
+    w2 = rng.integers(-99, 99, (10, 3))
+    rp2, cp2 = pt(6), pt(3)
+    cases.append(("two outputs", x, [((O, C), [rp, None]), ((O, C), [rp2, None])],
+                  [(w, (C, O), [None, cp]), (w2, (C, O), [None, cp2])], ["mk,kn->mn", "mk,kn->mn"],
+                  [cp + rp, cp2 + rp2]))
+    return cases
+
+
+@pytest.mark.parametrize("F", FIELDS)
+def test_einsum_prove_claims(F):
+    """einsum_prove (EinSum::prove_internal restated): the sumcheck's claimed sum is the gamma-combination of the
+    outputs' MLEs at their claim points (what EinSum::verify checks first, zkml/src/layers/einsum/verify.rs), the
+    sumcheck verifies, and every input claim it hands on is true of the padded input tensor."""
+    rng = np.random.default_rng(21)
+    for name, lhs, fixes, rhs, subs, out_points in einsum_cases(F, rng):
+        T = orc.Transcript(F)
+        got = orc.einsum_prove(F, T, lhs, fixes, rhs, lhs_padded=_padded_mle(F, lhs))
+        gamma = got["batching_challenge"]
+        want, g = F.zero, F.one
+        for (t, _, _), sub, pt in zip(rhs, subs, out_points):
+            out = np.einsum(sub, lhs, t)
+            want = F.add(want, F.mul(g, orc.evaluate(F, _padded_mle(F, out), pt)))
+            g = F.mul(g, gamma)
+        assert orc.extract_sum(F, got["sumcheck"]) == want, name
+        V = orc.Transcript(F)
+        assert V.append_and_sample(b"batching_challenge") == gamma
+        n = len(got["point"])
+        point, expected = orc.sumcheck_verify(F, want, got["sumcheck"], n, 2, V)
+        assert point == got["point"], name
+        # the last round's value is the expression at the final evaluations (left tables first, then right)
+        R, S = len(rhs), len(got["stacking_coeffs"][0])
+        ev, acc, g = got["evaluations"], F.zero, F.one
+        for i in range(R):
+            inner = F.zero
+            for j in range(S):
+                inner = F.add(inner, F.mul(got["stacking_coeffs"][i][j], F.mul(ev[i * S + j], ev[R * S + i * S + j])))
+            acc = F.add(acc, F.mul(g, inner))
+            g = F.mul(g, gamma)
+        assert acc == expected, name
+        for (t, _, _), (pt, ev) in zip(rhs, got["rhs_claims"]):
+            assert orc.evaluate(F, _padded_mle(F, t), pt) == ev, name
+        pt, ev = got["lhs_claim"]
+        assert orc.evaluate(F, _padded_mle(F, lhs), pt) == ev, name
+        assert (got["aggregation"] is not None) == (len(rhs) > 1)

@@ -52,7 +52,7 @@ def test_walk_on_the_cpu_backend_is_complete_and_deterministic():
     c, _ = wl.transformer_path(OracleBackend("fr"), wl.TINY, seed=4)
     assert [r[0] for r in c] == [r[0] for r in a] and c != a
     # every kind of call was timed
-    assert {"einsum_fix_axes", "einsum_sumcheck", "lookup_witness", "lookup_logup", "lookup_linking", "same_poly",
+    assert {"einsum", "lookup_witness", "lookup_logup", "lookup_linking", "same_poly",
             "attention_mask", "embeddings", "positional", "argmax_logup", "argmax_linking", "tables_logup",
             "claim_batching"} == set(timer.by_kind)
 
