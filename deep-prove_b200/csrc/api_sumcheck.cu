@@ -87,6 +87,12 @@ struct dpb_sc {
     uint32_t n_groups = 0;
     uint32_t op_threads = 0;
     size_t op_smem = 0;
+    bool seg_ok = false;         // the program splits into segments over few tables each: sc_round_seg runs the large rounds
+    void* d_segs = nullptr;
+    void* d_seg_prog = nullptr;
+    uint32_t n_segs = 0;
+    size_t seg_smem = 0;
+    uint32_t seg_inner_slot = 0;  // first of the slots that hold a group's running sums
     alignas(16) uint8_t prev_evals[7 * 32] = {0};  // previous round message (one-pass rounds derive s(1) from it)
     alignas(16) uint8_t lag_w[7 * 32] = {0};       // interpolation weights for the nodes 0..d
     alignas(16) uint8_t prev_coeffs[5 * 32] = {0};  // previous round polynomial, low to high (fused rounds)
@@ -168,9 +174,48 @@ static void launch_eval(dpb_sc* sc, uint32_t round, uint64_t n_pairs) {
         reduce_scratch<F>(ctx), (typename F::E*)ctx->round_out);
 }
 
+// The one-pass round over the segmented program (sc_round_seg): degrees 2..4.
+template <class F, int D, bool SPLIT>
+static int launch_seg(dpb_sc* sc, uint32_t round, uint64_t n_pairs, const typename F::E& r, const SplitEqArgs<F>& eq) {
+    typedef typename F::E E;
+    dpb_ctx* ctx = sc->ctx;
+    const bool skip = round > 0;
+    // rounds that do not fill the GPU with blocks of 256 run blocks of 128 or 64 on more SMs
+    uint32_t threads = kThreads;
+    while (threads > 64 && n_pairs < (uint64_t)ctx->sm_count * threads) threads /= 2;
+    const size_t smem = sc->seg_smem / kThreads * threads;
+    uint64_t blocks = (n_pairs + threads - 1) / threads;
+    const uint64_t per_sm = std::max<uint64_t>(1, std::min<uint64_t>(2 * (kThreads / threads), (uint64_t)kOnePassMaxSmem / smem));
+    if (blocks > (uint64_t)ctx->sm_count * per_sm) blocks = (uint64_t)ctx->sm_count * per_sm;
+    if (blocks > ctx->max_blocks) blocks = ctx->max_blocks;
+    const RoundTab* tabs = (SPLIT ? sc->d_rtab_eq : sc->d_rtab) + (size_t)round * sc->k;
+    const typename F::FoldKey rk = F::fold_key(r);
+    if (skip) {
+        DPB_CUDA(cudaFuncSetAttribute(sc_round_seg<F, D, true, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kOnePassMaxSmem));
+        sc_round_seg<F, D, true, SPLIT><<<(uint32_t)blocks, threads, smem, ctx->stream>>>(
+            tabs, (const SegDesc*)sc->d_segs, sc->n_segs, (const ProgTerm<F>*)sc->d_seg_prog, rk, eq, n_pairs,
+            sc->seg_inner_slot, reduce_scratch<F>(ctx), (E*)ctx->round_out);
+    } else {
+        DPB_CUDA(cudaFuncSetAttribute(sc_round_seg<F, D, false, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kOnePassMaxSmem));
+        sc_round_seg<F, D, false, SPLIT><<<(uint32_t)blocks, threads, smem, ctx->stream>>>(
+            tabs, (const SegDesc*)sc->d_segs, sc->n_segs, (const ProgTerm<F>*)sc->d_seg_prog, rk, eq, n_pairs,
+            sc->seg_inner_slot, reduce_scratch<F>(ctx), (E*)ctx->round_out);
+    }
+    return DPB_OK;
+}
+
 template <class F, int D>
 static int launch_one_pass(dpb_sc* sc, uint32_t round, uint64_t n_pairs, const typename F::E& r) {
     dpb_ctx* ctx = sc->ctx;
+    if constexpr (D >= 2 && D <= 4) {
+        if (sc->seg_ok) {
+            SplitEqArgs<F> none;
+            memset(&none, 0, sizeof none);
+            return launch_seg<F, D, false>(sc, round, n_pairs, r, none);
+        }
+    }
     const bool skip = round > 0;
     if (skip)
         DPB_CUDA(cudaFuncSetAttribute(sc_round_generic<F, D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -299,7 +344,7 @@ static void plan_spliteq(dpb_sc* sc, dpb_mle* const* mles, const std::vector<Pro
 // program, launch shapes and shared-memory layouts.  No device work.
 template <class F>
 static void plan_program(dpb_sc* sc, const dpb_term* terms, dpb_mle* const* mles, std::vector<uint8_t>& h_groups,
-                         std::vector<uint8_t>& h_prog) {
+                         std::vector<uint8_t>& h_prog, std::vector<uint8_t>& h_segs, std::vector<uint8_t>& h_seg_prog) {
     typedef typename F::E E;
     if (sc->k > 4096) return;  // very many tables: the two-pass kernels run every round
     std::vector<ProgGroup> groups;
@@ -307,7 +352,8 @@ static void plan_program(dpb_sc* sc, const dpb_term* terms, dpb_mle* const* mles
     std::vector<bool> is_eq(sc->k);
     for (uint32_t j = 0; j < sc->k; j++) is_eq[j] = mles[j]->eq_point.size() == (size_t)sc->tr[j].nv * sizeof(E);
     uint32_t mults = 0;
-    compile_program<F>(terms, sc->n_terms, sc->k, groups, prog, is_eq, &mults);
+    std::vector<std::vector<ProgMono<F>>> group_monos;
+    compile_program<F>(terms, sc->n_terms, sc->k, groups, prog, is_eq, &mults, &group_monos);
     // One thread walks the whole program per (pair, point) in the one-pass rounds and in the resident kernel; once
     // that chain of multiplications takes longer than two more launches, rounds too small to fill the GPU with
     // pairs are better spread over the terms (sc_fold_generic + sc_eval_generic with slices).
@@ -325,6 +371,23 @@ static void plan_program(dpb_sc* sc, const dpb_term* terms, dpb_mle* const* mles
         sc->op_threads = threads;
         sc->op_smem = per_thread * threads;
         sc->one_pass = sc->fused_shape == kFusedNone;
+    }
+    // the same rounds over segments of the program, when it falls apart into independent parts over few tables
+    // (also when the tables are too many for the unsegmented kernels' slots: the segments need few)
+    if (sc->fused_shape == kFusedNone && sc->d >= 2 && sc->d <= 4 && !getenv("DPB_NO_SEGMENTS")) {
+        std::vector<SegDesc> segs;
+        std::vector<ProgTerm<F>> seg_prog;
+        uint32_t widest = 0;
+        if (compile_segments<F>(groups, group_monos, sc->k, segs, seg_prog, &widest)) {
+            sc->seg_ok = true;
+            sc->one_pass = true;
+            sc->n_segs = (uint32_t)segs.size();
+            sc->seg_inner_slot = 2 * widest;
+            sc->seg_smem = (size_t)(2 * widest + sc->d + 1) * sizeof(E) * kThreads;
+            h_segs.assign((const uint8_t*)segs.data(), (const uint8_t*)segs.data() + segs.size() * sizeof(SegDesc));
+            h_seg_prog.assign((const uint8_t*)seg_prog.data(),
+                              (const uint8_t*)seg_prog.data() + seg_prog.size() * sizeof(ProgTerm<F>));
+        }
     }
     // interpolation weights per degree, computed once per process (field inversions are slow on the host)
     static E weights[7][7];
@@ -435,6 +498,9 @@ static int launch_spliteq(dpb_sc* sc, uint32_t round, uint64_t n_pairs, const ty
         eq.stride_log2[eq.n_eq] = ip + 1;
         eq.scale[eq.n_eq] = F::mul(S, iz);
         eq.n_eq++;
+    }
+    if constexpr (D >= 2 && D <= 4) {
+        if (sc->seg_ok) return launch_seg<F, D, true>(sc, round, n_pairs, r, eq);
     }
     const bool skip = round > 0;
     if (skip)
@@ -1005,11 +1071,13 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
         // minimum traffic of this round: every table read once, folded tables written once
         uint64_t bytes = 0;
         const char* name;
+        const bool seg = sc->seg_ok && sc->d >= 2 && sc->d <= 4;
         if (i == 0) {
             for (uint32_t j = 0; j < sc->k; j++) bytes += dtype_size(sc->tr[j].dtype) << sc->tr[j].nv;
             name = done ? (sc->tr[0].dtype == DPB_GL_BASE ? "fused_eval0<base>"
                            : sc->tr[0].dtype == DPB_FR_I32 ? "fused_eval0<i32>" : "fused_eval0")
-                        : split ? "sc_round_spliteq" : one_pass ? "sc_round_generic" : "sc_eval_generic";
+                        : split ? (seg ? "sc_round_seg<spliteq>" : "sc_round_spliteq")
+                        : one_pass ? (seg ? "sc_round_seg" : "sc_round_generic") : "sc_eval_generic";
         } else {
             const FoldDesc* fd = sc->h_fold.data() + (size_t)i * sc->k;
             for (uint32_t j = 0; j < sc->n_fold[i]; j++)
@@ -1018,7 +1086,8 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
                 if (sc->h_desc[(size_t)i * sc->k + j].shift >= 0) bytes += dtype_size(sc->tr[j].dtype) << sc->tr[j].nv;
             name = done ? (fd[0].dtype_in == DPB_GL_BASE ? "fused_fold_eval<base>"
                            : fd[0].dtype_in == DPB_FR_I32 ? "fused_fold_eval<i32>" : "fused_fold_eval")
-                        : split ? "sc_round_spliteq" : one_pass ? "sc_round_generic" : "sc_fold_generic+sc_eval_generic";
+                        : split ? (seg ? "sc_round_seg<spliteq>" : "sc_round_spliteq")
+                        : one_pass ? (seg ? "sc_round_seg" : "sc_round_generic") : "sc_fold_generic+sc_eval_generic";
         }
         bool found = false;
         for (auto& e : ctx->prof_log) {
@@ -1155,14 +1224,14 @@ int dpb_sumcheck_begin(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, ui
                                                       [&](uint32_t j) { return sc->tr[j].dtype; });
     // host-side plan, then ONE device allocation and ONE upload:
     // [fold buffers | table descriptors | fold descriptors | terms | final values | round tables | groups | program]
-    std::vector<uint8_t> h_terms, h_groups, h_prog;
+    std::vector<uint8_t> h_terms, h_groups, h_prog, h_segs, h_seg_prog;
     TracePhase t_plan("sumcheck.begin.plan");
     if (gl) {
         build_terms<GlFam>(sc, terms, h_terms);
-        if (!sc->ranged) plan_program<GlFam>(sc, terms, mles, h_groups, h_prog);
+        if (!sc->ranged) plan_program<GlFam>(sc, terms, mles, h_groups, h_prog, h_segs, h_seg_prog);
     } else {
         build_terms<FrFam>(sc, terms, h_terms);
-        if (!sc->ranged) plan_program<FrFam>(sc, terms, mles, h_groups, h_prog);
+        if (!sc->ranged) plan_program<FrFam>(sc, terms, mles, h_groups, h_prog, h_segs, h_seg_prog);
     }
     // ranged evaluation: per round and term, the pairs to visit and the tiles that cover them
     std::vector<uint64_t> h_tile_prefix, h_term_pairs;
@@ -1199,7 +1268,8 @@ int dpb_sumcheck_begin(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, ui
                  o_final = take(k * es), o_rtab = take(sc->has_prog ? nk * sizeof(RoundTab) : 0),
                  o_groups = take(h_groups.size()), o_prog = take(h_prog.size()),
                  o_tiles = take(h_tile_prefix.size() * 8), o_pairs = take(h_term_pairs.size() * 8),
-                 o_rtab_eq = take(sc->spliteq ? nk * sizeof(RoundTab) : 0);
+                 o_rtab_eq = take(sc->spliteq ? nk * sizeof(RoundTab) : 0), o_segs = take(h_segs.size()),
+                 o_seg_prog = take(h_seg_prog.size());
     t_plan.stop();
     TracePhase t_alloc("sumcheck.begin.alloc");
     // Sumchecks of one context run one after the other, each with one block of device memory for its fold buffers
@@ -1234,6 +1304,8 @@ int dpb_sumcheck_begin(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, ui
         sc->d_groups = base + o_groups;
         sc->d_prog = base + o_prog;
         sc->d_rtab_eq = (RoundTab*)(base + o_rtab_eq);
+        sc->d_segs = base + o_segs;
+        sc->d_seg_prog = base + o_seg_prog;
         sc->d_tile_prefix = (uint64_t*)(base + o_tiles);
         sc->d_term_pairs = (uint64_t*)(base + o_pairs);
         // ping-pong fold buffers of every table, at the front of the block
@@ -1320,6 +1392,8 @@ int dpb_sumcheck_begin(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, ui
         }
         put(o_groups, h_groups.data(), h_groups.size());
         put(o_prog, h_prog.data(), h_prog.size());
+        put(o_segs, h_segs.data(), h_segs.size());
+        put(o_seg_prog, h_seg_prog.data(), h_seg_prog.size());
         put(o_tiles, h_tile_prefix.data(), h_tile_prefix.size() * 8);
         put(o_pairs, h_term_pairs.data(), h_term_pairs.size() * 8);
         rc = upload_small(ctx, (char*)sc->slab + o_desc, blob.data(), blob.size());

@@ -18,6 +18,8 @@
 //    multiplies the group's sum once per point instead of once per term.
 // Results are exact field sums, so they equal the two-pass kernels' bit for bit.
 #pragma once
+#include <algorithm>
+
 #include "sumcheck_kernels.cuh"
 
 namespace dpb {
@@ -260,6 +262,162 @@ __global__ void __launch_bounds__(kThreads)
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
         F::store(out, i, F::mul(scale, F::load(in, dtype_in, i << stride_log2)));
+}
+
+// ---- one-pass rounds over a program cut into segments ------------------------------
+//
+// The kernels above keep (value, difference) of EVERY table in a thread's shared-memory slots, so a program over
+// many tables leaves room for few threads per SM (13 BN254 tables: one block of 128), and one thread's chain of
+// dependent products is then what the round waits for.  Most long programs are sums of independent parts, though:
+// the instances of a logup batch, the heads of a stacked einsum.  Inside a group (terms sharing an outer table) the
+// host finds the connected components of "terms that share a table"; each becomes a segment with its own few
+// tables and its own Horner-chained term list over local table numbers.  A thread then walks the segments one
+// after the other, reusing the same few slots: load (bind, store) the segment's tables, evaluate its terms at
+// every point into the group's running sums, and multiply by the outer table once per group and point.  Same
+// field sums as the unsegmented kernels, so the same messages.
+constexpr int kSegTables = 6;
+struct SegDesc {
+    uint16_t group;                 // program group (bit of SplitEqArgs::const_groups)
+    uint16_t outer;                 // the group's outer table, or kNoOuter
+    uint16_t n_tabs;
+    uint16_t term_begin, term_end;  // steps in the segmented program; their idx[] number the segment's tables
+    uint8_t first, last;            // first / last segment of its group
+    uint16_t tab[kSegTables];
+};
+
+// a group's inner sum over the steps [begin, end) at the slots' current values
+template <class F>
+__device__ __noinline__ typename F::E eval_steps(const Slots<F>& sl, const ProgTerm<F>* __restrict__ terms,
+                                                 uint32_t begin, uint32_t end) {
+    typedef typename F::E E;
+    E inner = F::zero(), run = F::zero();
+    for (uint32_t t = begin; t < end; t++) {
+        const ProgTerm<F>& tm = terms[t];
+        const uint32_t nf = tm.n_factors;
+        if (tm.op == kOpFold) {
+            for (uint32_t j = 0; j < nf; j++) inner = F::mul(inner, sl.get(2 * tm.idx[j]));
+            continue;
+        }
+        if (tm.op == kOpConst) {
+            inner = F::add(inner, tm.coeff);
+            continue;
+        }
+        E prod;
+        if (nf == 0) {
+            prod = F::one();
+        } else {
+            prod = sl.get(2 * tm.idx[0]);
+            for (uint32_t j = 1; j < nf; j++) prod = F::mul(prod, sl.get(2 * tm.idx[j]));
+        }
+        run = F::add(run, prod);
+        if (tm.run_last) {
+            if (tm.neg) inner = F::sub(inner, run);
+            else inner = F::add(inner, tm.coeff_is_one ? run : F::mul(run, tm.coeff));
+            run = F::zero();
+        }
+    }
+    return inner;
+}
+
+// (value at 0, difference) of table t for pair p; binds the previous challenge and stores when the round folds
+template <class F>
+__device__ __forceinline__ void seg_load(const RoundTab& t, uint64_t p, const typename F::FoldKey& rk,
+                                         typename F::E& f0, typename F::E& df) {
+    typedef typename F::E E;
+    E f1;
+    if (t.out) {
+        E a0, a1, b0, b1;
+        F::load_pair(t.in, t.dtype_in, 2 * p, a0, a1);
+        F::load_pair(t.in, t.dtype_in, 2 * p + 1, b0, b1);
+        f0 = F::add(a0, F::mul_key(rk, F::sub(a1, a0)));
+        f1 = F::add(b0, F::mul_key(rk, F::sub(b1, b0)));
+        F::store(t.out, 2 * p, f0);
+        F::store(t.out, 2 * p + 1, f1);
+    } else if (t.shift < 0) {
+        F::load_pair(t.in, t.dtype_in, p, f0, f1);
+    } else {
+        f0 = F::load(t.in, t.dtype_in, p >> t.shift);
+        df = F::zero();
+        return;
+    }
+    df = F::sub(f1, f0);
+}
+
+// SPLIT: the sums of sc_round_spliteq (H at 0..D-1, then C); otherwise those of sc_round_generic (0..D).
+template <class F, int D, bool SKIP_ONE, bool SPLIT>
+__global__ void __launch_bounds__(kThreads, 2)
+    sc_round_seg(const RoundTab* __restrict__ tabs, const SegDesc* __restrict__ segs, uint32_t n_segs,
+                 const ProgTerm<F>* __restrict__ terms, typename F::FoldKey rk, SplitEqArgs<F> eq, uint64_t n_pairs,
+                 uint32_t inner_slot, ReduceScratch<F> rs, typename F::E* out) {
+    typedef typename F::E E;
+    constexpr int NP = SPLIT ? D : D + 1;  // evaluation points per pair; the group's running sums live in the
+                                           // slots inner_slot .. inner_slot + NP - 1 (registers are for the products)
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    Slots<F> sl;
+    sl.base = (uint4*)smem_raw;
+    E acc[D + 1];
+#pragma unroll
+    for (int x = 0; x <= D; x++) acc[x] = F::zero();
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t p = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; p < n_pairs; p += stride) {
+        for (uint32_t s = 0; s < n_segs; s++) {
+            const SegDesc sd = segs[s];
+            for (uint32_t j = 0; j < sd.n_tabs; j++) {
+                E f0, df;
+                seg_load<F>(tabs[sd.tab[j]], p, rk, f0, df);
+                sl.put(2 * j, f0);
+                sl.put(2 * j + 1, df);
+            }
+            if (sd.term_begin == sd.term_end && sd.outer == kNoOuter) continue;  // tables no term uses: bound, stored
+            const bool cg = SPLIT && ((eq.const_groups >> (sd.group & 31)) & 1u);  // the group does not move this round
+            if (sd.first) {
+#pragma unroll
+                for (int x = 0; x < NP; x++) sl.put(inner_slot + x, F::zero());
+            }
+            if (sd.term_begin != sd.term_end) {
+#pragma unroll
+                for (int x = 0; x < NP; x++) {
+                    if (cg && x > 0) break;
+                    if (!(SKIP_ONE && x == 1))
+                        sl.put(inner_slot + x, F::add(sl.get(inner_slot + x), eval_steps<F>(sl, terms, sd.term_begin, sd.term_end)));
+                    if (x < NP - 1 && !cg)
+                        for (uint32_t j = 0; j < sd.n_tabs; j++) sl.put(2 * j, F::add(sl.get(2 * j), sl.get(2 * j + 1)));
+                }
+            }
+            if (!sd.last) continue;
+            if (sd.outer == kNoOuter) {
+                if (cg) {
+                    acc[D] = F::add(acc[D], sl.get(inner_slot));
+                } else {
+#pragma unroll
+                    for (int x = 0; x < NP; x++) acc[x] = F::add(acc[x], sl.get(inner_slot + x));
+                }
+                continue;
+            }
+            E o, od;
+            int e = -1;
+            if (SPLIT)
+                for (uint32_t q = 0; q < eq.n_eq; q++)
+                    if (eq.table[q] == sd.outer) e = (int)q;
+            if (e >= 0) {
+                const RoundTab t = tabs[sd.outer];
+                o = F::mul(eq.scale[e], F::load(t.in, t.dtype_in, p << eq.stride_log2[e]));
+                od = F::zero();
+            } else {
+                seg_load<F>(tabs[sd.outer], p, rk, o, od);
+            }
+            if (cg) {
+                acc[D] = F::add(acc[D], F::mul(sl.get(inner_slot), o));
+            } else {
+#pragma unroll
+                for (int x = 0; x < NP; x++) {
+                    if (!(SKIP_ONE && x == 1)) acc[x] = F::add(acc[x], F::mul(sl.get(inner_slot + x), o));
+                    if (x < NP - 1 && e < 0) o = F::add(o, od);
+                }
+            }
+        }
+    }
+    grid_sum_publish<F, D + 1>(acc, rs, out);
 }
 
 // ---- resident kernel for the last rounds ---------------------------------------
@@ -654,7 +812,8 @@ inline uint32_t emit_chain(const std::vector<ProgMono<F>>& monos, uint32_t k, st
 template <class F>
 inline void compile_program(const dpb_term* terms, uint32_t n_terms, uint32_t k, std::vector<ProgGroup>& groups,
                             std::vector<ProgTerm<F>>& prog, const std::vector<bool>& prefer = std::vector<bool>(),
-                            uint32_t* mults_per_point = nullptr) {
+                            uint32_t* mults_per_point = nullptr,
+                            std::vector<std::vector<ProgMono<F>>>* group_monos = nullptr) {
     typedef typename F::E E;
     std::vector<bool> used(n_terms, false);
     uint32_t left = n_terms;
@@ -716,11 +875,107 @@ inline void compile_program(const dpb_term* terms, uint32_t n_terms, uint32_t k,
                 left--;
             }
         }
+        if (group_monos) group_monos->push_back(monos);
         const uint32_t cost = emit_chain<F>(monos, k, prog) + (g.outer != kNoOuter ? 1 : 0);
         if (mults_per_point) *mults_per_point += cost;
         g.term_end = (uint16_t)prog.size();
         groups.push_back(g);
     }
+}
+
+// Cuts the groups compile_program made into segments for sc_round_seg: inside a group, the connected components of
+// "monomials that share a table", in the order of their first monomial; a group's constants form a component
+// without tables.  Every table no term touches gets a place in a segment without steps, so that it is still bound
+// and stored.  Returns false when a component has more than kSegTables tables (the caller keeps the unsegmented
+// kernels) or when nothing would be gained (a single segment holds every table).
+template <class F>
+inline bool compile_segments(const std::vector<ProgGroup>& groups, const std::vector<std::vector<ProgMono<F>>>& group_monos,
+                             uint32_t k, std::vector<SegDesc>& segs, std::vector<ProgTerm<F>>& prog, uint32_t* max_tabs) {
+    if (groups.size() != group_monos.size() || groups.size() > 32) return false;
+    std::vector<bool> covered(k, false);
+    uint32_t widest = 1;
+    for (size_t g = 0; g < groups.size(); g++) {
+        const auto& monos = group_monos[g];
+        if (groups[g].outer != kNoOuter) covered[groups[g].outer] = true;
+        // union-find over the tables of this group's monomials
+        std::vector<int> parent(k);
+        for (uint32_t j = 0; j < k; j++) parent[j] = (int)j;
+        auto find = [&](int x) {
+            while (parent[x] != x) x = parent[x] = parent[parent[x]];
+            return x;
+        };
+        for (const auto& m : monos)
+            for (size_t j = 1; j < m.f.size(); j++) parent[find(m.f[j])] = find(m.f[0]);
+        std::vector<int> comp_of_root(k, -1);
+        std::vector<std::vector<ProgMono<F>>> comp_monos;
+        int const_comp = -1;
+        for (const auto& m : monos) {
+            int c;
+            if (m.f.empty()) {
+                if (const_comp < 0) {
+                    const_comp = (int)comp_monos.size();
+                    comp_monos.emplace_back();
+                }
+                c = const_comp;
+            } else {
+                const int root = find(m.f[0]);
+                if (comp_of_root[root] < 0) {
+                    comp_of_root[root] = (int)comp_monos.size();
+                    comp_monos.emplace_back();
+                }
+                c = comp_of_root[root];
+            }
+            comp_monos[c].push_back(m);
+        }
+        if (comp_monos.empty()) comp_monos.emplace_back();  // a group of nothing but its outer table cannot occur; keep a segment
+        for (size_t c = 0; c < comp_monos.size(); c++) {
+            std::vector<uint16_t> tabs;
+            for (const auto& m : comp_monos[c])
+                for (uint16_t t : m.f)
+                    if (std::find(tabs.begin(), tabs.end(), t) == tabs.end()) tabs.push_back(t);
+            if (tabs.size() > (size_t)kSegTables) return false;
+            std::sort(tabs.begin(), tabs.end());
+            std::vector<ProgMono<F>> local = comp_monos[c];
+            for (auto& m : local)
+                for (auto& t : m.f) t = (uint16_t)(std::find(tabs.begin(), tabs.end(), t) - tabs.begin());
+            if (prog.size() + 4 * local.size() + 8 > 65535) return false;
+            SegDesc sd;
+            memset(&sd, 0, sizeof sd);
+            sd.group = (uint16_t)g;
+            sd.outer = groups[g].outer;
+            sd.n_tabs = (uint16_t)tabs.size();
+            for (size_t j = 0; j < tabs.size(); j++) {
+                sd.tab[j] = tabs[j];
+                covered[tabs[j]] = true;
+            }
+            sd.term_begin = (uint16_t)prog.size();
+            emit_chain<F>(local, (uint32_t)tabs.size(), prog);
+            sd.term_end = (uint16_t)prog.size();
+            sd.first = c == 0;
+            sd.last = c + 1 == comp_monos.size();
+            widest = std::max<uint32_t>(widest, (uint32_t)tabs.size());
+            segs.push_back(sd);
+        }
+    }
+    // tables outside every term: bound and stored by segments without steps
+    SegDesc rest;
+    memset(&rest, 0, sizeof rest);
+    rest.outer = kNoOuter;
+    for (uint32_t j = 0; j < k; j++) {
+        if (covered[j]) continue;
+        rest.tab[rest.n_tabs++] = (uint16_t)j;
+        if (rest.n_tabs == kSegTables) {
+            segs.push_back(rest);
+            widest = std::max<uint32_t>(widest, rest.n_tabs);
+            rest.n_tabs = 0;
+        }
+    }
+    if (rest.n_tabs) {
+        segs.push_back(rest);
+        widest = std::max<uint32_t>(widest, rest.n_tabs);
+    }
+    *max_tabs = widest;
+    return segs.size() > 1 && (uint32_t)(2 * widest) <= k;
 }
 
 // Value at x of the polynomial of degree <= D with the given values at 0..D.
