@@ -112,6 +112,7 @@ SIGNATURES = {
     "dpb_comm_size": (_int, [_vp]),
     "dpb_comm_free": (_int, [_vp]),
     "dpb_sumcheck_begin_sharded": (_int, [_vp, _u32, _pp, _u32, ctypes.POINTER(Term), _u32, _pp]),
+    "dpb_sumcheck_begin_partial": (_int, [_vp, _u32, _pp, _u32, ctypes.POINTER(Term), _u32, _pp]),
 }
 
 COMM_ID_BYTES = 128
@@ -555,7 +556,9 @@ class Sumcheck:
         k = len(mles)
         hs = (ctypes.c_void_p * k)(*[m.h for m in mles])
         h = ctypes.c_void_p()
-        begin = lib.dpb_sumcheck_begin_sharded if sharded else lib.dpb_sumcheck_begin
+        # sharded: True = this rank's slices of the tables; "partial" = this rank's part of the terms over whole tables
+        begin = lib.dpb_sumcheck_begin_partial if sharded == "partial" else \
+            lib.dpb_sumcheck_begin_sharded if sharded else lib.dpb_sumcheck_begin
         check(begin(ctx.h, num_vars, hs, k, term_array, len(term_array), ctypes.byref(h)))
         self.h = h
         self.k = k

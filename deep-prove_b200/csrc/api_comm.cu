@@ -24,6 +24,8 @@
 #include <random>
 #include <thread>
 
+#include <algorithm>
+
 #include "comm.cuh"
 
 namespace dpb {
@@ -208,6 +210,25 @@ static int xch_setup(dpb_ctx* ctx, const void* unique_id) {
     if (registered) cudaHostUnregister(map);
     if (map != MAP_FAILED) munmap(map, bytes);
     return rc;
+}
+
+int comm_allgather_host(dpb_ctx* ctx, const void* in, size_t bytes, void* out) {
+    if (ctx->nranks <= 1) {
+        memcpy(out, in, bytes);
+        return DPB_OK;
+    }
+    if (!ctx->nccl_comm) return fail(DPB_ESTATE, "the context has no communicator (dpb_comm_init)");
+    // in pieces that fit the exchange buffer
+    const size_t piece_max = ctx->gather_bytes / (size_t)ctx->nranks / 16 * 16;
+    for (size_t done = 0; done < bytes; done += piece_max) {
+        const size_t piece = std::min(piece_max, bytes - done);
+        char* slot = (char*)ctx->gather_dev + (size_t)ctx->rank * piece;
+        DPB_CUDA(cudaMemcpyAsync(slot, (const char*)in + done, piece, cudaMemcpyHostToDevice, ctx->stream));
+        DPB_TRY(allgather_to_host(ctx, slot, piece));
+        for (int q = 0; q < ctx->nranks; q++)
+            memcpy((char*)out + (size_t)q * bytes + done, (const char*)ctx->gather_host + (size_t)q * piece, piece);
+    }
+    return DPB_OK;
 }
 
 }  // namespace dpb

@@ -224,7 +224,8 @@ int claims_impl(dpb_ctx* ctx, const dpb_committed_poly* polys, uint32_t n_polys,
 }
 
 template <class F, class T>
-int logup_impl(dpb_ctx* ctx, const dpb_logup_input* inputs, uint32_t n_inputs, T& tr, dpb_logup_proof** out) {
+int logup_impl(dpb_ctx* ctx, const dpb_logup_input* inputs, uint32_t n_inputs, T& tr, dpb_logup_proof** out,
+               bool partial = false) {
     typedef typename F::E E;
     using namespace zkml::logup_gkr;
     std::vector<LogUpInput<F>> in;
@@ -242,7 +243,7 @@ int logup_impl(dpb_ctx* ctx, const dpb_logup_input* inputs, uint32_t n_inputs, T
         else if (s.kind == DPB_LOGUP_LOOKUP) in.push_back(LogUpInput<F>::new_lookup(cols, cst, sep, s.columns_per_instance));
         else return fail(DPB_EINVAL, "input %u has unknown kind %d", i, s.kind);
     }
-    auto proof = new_batch_multiple_sizes_prove<F>(ctx, in, tr);
+    auto proof = new_batch_multiple_sizes_prove<F>(ctx, in, tr, partial);
     dpb_logup_proof* p = new dpb_logup_proof();
     p->bytes = proof.serialize();
     *out = p;
@@ -578,6 +579,16 @@ int dpb_logup_batch_prove(dpb_ctx* ctx, const dpb_logup_input* inputs, uint32_t 
     return guarded([&] {
         return t->gl ? logup_impl<GlFam>(ctx, inputs, n_inputs, *t->g, out)
                      : logup_impl<FrFam>(ctx, inputs, n_inputs, *t->f, out);
+    });
+}
+
+int dpb_logup_batch_prove_partial(dpb_ctx* ctx, const dpb_logup_input* inputs, uint32_t n_inputs, dpb_transcript* t,
+                                  dpb_logup_proof** out) {
+    if (!ctx || !t || !out || (!inputs && n_inputs)) return fail(DPB_EINVAL, "null argument");
+    if (n_inputs == 0) return fail(DPB_EINVAL, "No inputs provided for LogUp");
+    return guarded([&] {
+        return t->gl ? logup_impl<GlFam>(ctx, inputs, n_inputs, *t->g, out, true)
+                     : logup_impl<FrFam>(ctx, inputs, n_inputs, *t->f, out, true);
     });
 }
 

@@ -98,6 +98,7 @@ struct dpb_sc {
     alignas(16) uint8_t prev_coeffs[5 * 32] = {0};  // previous round polynomial, low to high (fused rounds)
     // sharded sumchecks: the local part has n variables, the whole sumcheck n + log2_ranks
     uint32_t log2_ranks = 0;
+    bool partial = false;  // this rank holds some of the TERMS (whole tables): every round's sums are added over the ranks
     uint32_t global_round = 0;
     std::vector<dpb_term> terms_copy;
     dpb_sc* tail = nullptr;             // the last log2_ranks rounds, identical on every rank
@@ -924,7 +925,7 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
 
     // A sharded sumcheck publishes into this rank's slot of the exchange area (in-place all-gather).
     const size_t msg_bytes = (sc->d + 1) * sizeof(E);
-    const bool sharded = sc->log2_ranks > 0;
+    const bool sharded = sc->log2_ranks > 0 || sc->partial;
     const bool shared_xch = sharded && ctx->xch_host != nullptr;
     if (shared_xch) {
         // this rank's slot of the shared host segment: the kernel's last block writes the sums, then the sequence number
@@ -1426,6 +1427,18 @@ int dpb_sumcheck_begin_sharded(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* 
     sc->log2_ranks = c;
     sc->spliteq = false;  // the shards of an eq table are not eq tables
     sc->terms_copy.assign(terms, terms + n_terms);
+    *out = sc;
+    return DPB_OK;
+}
+
+int dpb_sumcheck_begin_partial(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, uint32_t k,
+                               const dpb_term* terms, uint32_t n_terms, dpb_sc** out) {
+    if (!ctx || !mles || !terms || !out) return fail(DPB_EINVAL, "null argument");
+    if (ctx->nranks <= 1) return dpb_sumcheck_begin(ctx, num_vars, mles, k, terms, n_terms, out);
+    if (!ctx->nccl_comm) return fail(DPB_ESTATE, "the context has no communicator (dpb_comm_init)");
+    dpb_sc* sc = nullptr;
+    DPB_TRY(dpb_sumcheck_begin(ctx, num_vars, mles, k, terms, n_terms, &sc));
+    sc->partial = true;
     *out = sc;
     return DPB_OK;
 }

@@ -181,4 +181,8 @@ int new_mle(dpb_ctx* ctx, int dtype, uint64_t len, dpb_mle** out);
 // copies `n` challenge elements from host memory to the staging area and returns the device pointer
 int stage_to_device(dpb_ctx* ctx, const void* host, size_t bytes, size_t offset, void** dev);
 
+// Every rank contributes `bytes` of host data; out receives nranks * bytes in rank order (api_comm.cu).  With one
+// rank: a copy.  Bounded wait; DPB_EINVAL when nranks * bytes exceeds the context's exchange buffer.
+int comm_allgather_host(dpb_ctx* ctx, const void* in, size_t bytes, void* out);
+
 }  // namespace dpb

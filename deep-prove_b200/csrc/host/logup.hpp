@@ -259,12 +259,27 @@ struct LogUpBatchProof {
     }
 };
 
-// prover.rs:91-344
+// prover.rs:91-344.
+// partial: the instances of the batch are spread over the ranks of ctx's communicator.  Every rank passes its own
+// instances, of the same kinds, sizes and column counts on every rank; local instance i of rank g is instance
+// i * G + g of the whole batch (so the batch stays ordered by size).  Each rank builds only its own trees and runs
+// its own part of every layer's sumcheck (dpb_sumcheck_begin_partial adds the round sums over the ranks); the
+// outputs and the final evaluations of each layer are gathered, every rank feeds the same transcript, and every
+// rank returns the proof of the WHOLE batch.
 template <class F, class T>
 LogUpBatchProof<F> new_batch_multiple_sizes_prove(dpb_ctx* ctx, const std::vector<LogUpInput<F>>& input,
-                                                  T& transcript) {
+                                                  T& transcript, bool partial = false) {
     typedef typename F::E E;
     typedef Expression<F> X;
+    const size_t G = partial ? (size_t)std::max(dpb_comm_size(ctx), 1) : 1;
+    const size_t g_rank = G > 1 ? (size_t)dpb_comm_rank(ctx) : 0;
+    partial = G > 1;
+    // rank-order gather of equal-sized host vectors; out[q] = rank q's
+    auto gather = [&](const std::vector<E>& mine) {
+        std::vector<E> all(mine.size() * G);
+        check(dpb::comm_allgather_host(ctx, mine.data(), mine.size() * sizeof(E), all.data()));
+        return all;
+    };
     if (input.empty()) throw Error(DPB_EINVAL, "No inputs provided for LogUp");
     const ProofType proof_type = input[0].kind;
     for (const auto& in : input)
@@ -305,11 +320,29 @@ LogUpBatchProof<F> new_batch_multiple_sizes_prove(dpb_ctx* ctx, const std::vecto
         for (const auto& c : circuits) trees.push_back(c->tree());
         std::vector<E> flat(4 * trees.size());
         check(dpb_logup_outputs_batch(trees.data(), (uint32_t)trees.size(), flat.data()));
-        for (size_t i = 0; i < trees.size(); i++)
-            proof.circuit_outputs.emplace_back(flat.begin() + 4 * i, flat.begin() + 4 * i + 4);
+        if (partial) {
+            // every rank must hold the same shapes: compare a signature before anything depends on it
+            std::vector<E> sig;
+            for (const auto& c : circuits)
+                sig.push_back(F::from_u64(((uint64_t)c->num_vars() << 32) | ((uint64_t)c->denominator_column_count() << 1) |
+                                          (c->final_eval_count() != 2 * c->denominator_column_count() ? 1u : 0u)));
+            sig.push_back(F::from_u64(circuits.size()));
+            const std::vector<E> sigs = gather(sig);
+            for (size_t q = 0; q < G; q++)
+                if (memcmp(sigs.data() + q * sig.size(), sig.data(), sig.size() * sizeof(E)) != 0)
+                    throw Error(DPB_EINVAL, "the ranks of a partial logup batch must hold instances of the same shapes");
+            const std::vector<E> all = gather(flat);
+            for (size_t i = 0; i < trees.size(); i++)
+                for (size_t q = 0; q < G; q++)
+                    proof.circuit_outputs.emplace_back(all.begin() + q * flat.size() + 4 * i,
+                                                       all.begin() + q * flat.size() + 4 * i + 4);
+        } else {
+            for (size_t i = 0; i < trees.size(); i++)
+                proof.circuit_outputs.emplace_back(flat.begin() + 4 * i, flat.begin() + 4 * i + 4);
+        }
     }
 
-    const E count = F::from_u64(circuits.size());
+    const E count = F::from_u64(circuits.size() * G);
     transcript.append_scalars(&count, 1);
     for (const auto& o : proof.circuit_outputs) transcript.append_scalars(o);
     E rho = transcript.append_and_sample("initial_batching");
@@ -323,7 +356,9 @@ LogUpBatchProof<F> new_batch_multiple_sizes_prove(dpb_ctx* ctx, const std::vecto
         if (!proof.round_evaluations.empty()) wit_evals = proof.round_evaluations.back();
         for (size_t i = 0; i < circuits.size(); i++)
             if (circuits[i]->num_vars() == remaining)
-                wit_evals.insert(wit_evals.end(), proof.circuit_outputs[i].begin(), proof.circuit_outputs[i].end());
+                for (size_t q = 0; q < G; q++)
+                    wit_evals.insert(wit_evals.end(), proof.circuit_outputs[i * G + q].begin(),
+                                     proof.circuit_outputs[i * G + q].end());
         if (wit_evals.empty())
             throw Error(DPB_EINVAL, "Proving failed: No previous evals and no evals for this number of variables");
 
@@ -345,13 +380,18 @@ LogUpBatchProof<F> new_batch_multiple_sizes_prove(dpb_ctx* ctx, const std::vecto
             X group = X::ZERO();
             for (auto& c : circuits) {
                 if (c->num_vars() != size) continue;
-                auto le = c->layer_exprs(layer_vars, layer_count, wit_off);
-                auto lm = c->layer_mles(layer_vars);
-                mles.insert(mles.end(), lm.begin(), lm.end());
-                layer_count++;
-                wit_off = (uint16_t)(wit_off + le.num_witnesses);
-                group = group + le.sumcheck;
-                claim_expr = claim_expr + mult * le.claim;
+                // the whole batch holds this instance once per rank, next to each other; only this rank's takes
+                // part in its sumcheck, all of them in the claim
+                for (size_t q = 0; q < G; q++) {
+                    auto le = c->layer_exprs(layer_vars, layer_count, wit_off);
+                    layer_count++;
+                    claim_expr = claim_expr + mult * le.claim;
+                    if (q != g_rank) continue;
+                    auto lm = c->layer_mles(layer_vars);
+                    mles.insert(mles.end(), lm.begin(), lm.end());
+                    wit_off = (uint16_t)(wit_off + le.num_witnesses);
+                    group = group + le.sumcheck;
+                }
             }
             dpb_mle* eq = nullptr;
             {
@@ -373,10 +413,29 @@ LogUpBatchProof<F> new_batch_multiple_sizes_prove(dpb_ctx* ctx, const std::vecto
         auto vp = builder.to_virtual_polys({full}, {alpha, lambda});
         t_expand.stop();
         t_expr.stop();
-        auto res = dp_crypto::IOPProverState<F>::prove(ctx, vp, transcript);
+        auto res = dp_crypto::IOPProverState<F>::prove(ctx, vp, transcript, partial ? 2 : 0);
         point = res.second.collect_raw_challenges();
         const auto& finals = res.second.get_mle_flatten_final_evaluations();
         std::vector<E> evals(finals.begin(), finals.begin() + wit_off);
+        if (partial) {
+            // the whole batch's evaluations: per instance of this layer (sizes in the order above), rank by rank
+            const std::vector<E> all = gather(evals);
+            std::vector<E> merged;
+            merged.reserve(all.size());
+            size_t at = 0;
+            for (size_t size : sizes) {
+                if (size < remaining) continue;
+                const size_t layer_vars = size - remaining + 1;
+                for (auto& c : circuits) {
+                    if (c->num_vars() != size) continue;
+                    const size_t n = layer_vars == c->num_vars() ? c->final_eval_count() : 4;
+                    for (size_t q = 0; q < G; q++)
+                        merged.insert(merged.end(), all.begin() + q * evals.size() + at, all.begin() + q * evals.size() + at + n);
+                    at += n;
+                }
+            }
+            evals.swap(merged);
+        }
 
         rho = transcript.append_and_sample("logup_batching");
         if (v != total_layers) {
@@ -392,14 +451,16 @@ LogUpBatchProof<F> new_batch_multiple_sizes_prove(dpb_ctx* ctx, const std::vecto
     const auto& last = proof.round_evaluations.back();
     size_t skip = 0;
     for (const auto& c : circuits) {
-        const size_t n = c->final_eval_count();
-        if (skip + n > last.size()) throw Error(DPB_EINVAL, "final evaluations are short");
-        auto ev = c->combine_final_evals(last.data() + skip, n, rho);
-        skip += n;
-        std::vector<E> pt(point.end() - (c->num_vars() + 1), point.end());
-        for (const auto& e : ev) proof.output_claims.push_back({pt, e});
-        proof.num_vars_per_instance.push_back(c->num_vars());
-        proof.num_denominator_columns_per_instance.push_back(c->denominator_column_count());
+        for (size_t q = 0; q < G; q++) {
+            const size_t n = c->final_eval_count();
+            if (skip + n > last.size()) throw Error(DPB_EINVAL, "final evaluations are short");
+            auto ev = c->combine_final_evals(last.data() + skip, n, rho);
+            skip += n;
+            std::vector<E> pt(point.end() - (c->num_vars() + 1), point.end());
+            for (const auto& e : ev) proof.output_claims.push_back({pt, e});
+            proof.num_vars_per_instance.push_back(c->num_vars());
+            proof.num_denominator_columns_per_instance.push_back(c->denominator_column_count());
+        }
     }
     return proof;
 }

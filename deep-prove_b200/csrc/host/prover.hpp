@@ -299,14 +299,15 @@ class IOPProverState {
     // Runs every round on the GPU behind `ctx`; the transcript is only touched here, on the host.
     template <class T>
     static std::pair<IOPProof<F>, IOPProverState> prove(dpb_ctx* ctx, const VirtualPolynomials<F>& vp,
-                                                        T& transcript, bool sharded = false) {
+                                                        T& transcript, int sharded = 0) {
         if (vp.terms.empty()) throw Error(DPB_EINVAL, "virtual polynomial has no terms");
         IOPProverState st;
         IOPProof<F> proof;
         dpb_sc* sc = nullptr;
         dpb::TracePhase t_begin("sumcheck.begin");
-        // sharded: the tables are this rank's slices and every rank runs this same loop
-        check((sharded ? dpb_sumcheck_begin_sharded : dpb_sumcheck_begin)(
+        // sharded = 1: the tables are this rank's slices; 2: this rank's part of the terms over whole tables; every
+        // rank runs this same loop
+        check((sharded == 2 ? dpb_sumcheck_begin_partial : sharded ? dpb_sumcheck_begin_sharded : dpb_sumcheck_begin)(
             ctx, vp.num_vars, vp.mles.data(), (uint32_t)vp.mles.size(), vp.terms.data(), (uint32_t)vp.terms.size(), &sc));
         t_begin.stop();
         dpb::TracePhase t_rounds("sumcheck.rounds");

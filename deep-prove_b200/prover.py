@@ -61,6 +61,7 @@ PROVER_SIGNATURES = {
                                         _u32, _vp, _vp, _u32, _vp, _vp, _vp, _u32, ctypes.POINTER(_u32),
                                         ctypes.POINTER(_u32), _vp, _vp]),
     "dpb_logup_batch_prove": (_int, [_vp, ctypes.POINTER(LogupInputStruct), _u32, _vp, _pp]),
+    "dpb_logup_batch_prove_partial": (_int, [_vp, ctypes.POINTER(LogupInputStruct), _u32, _vp, _pp]),
     "dpb_logup_proof_serialize": (_int, [_vp, _vp, _size_t, ctypes.POINTER(_size_t)]),
     "dpb_logup_proof_free": (None, [_vp]),
     "dpb_einsum_prove": (_int, [_vp, ctypes.POINTER(EinsumOperandStruct), ctypes.POINTER(EinsumOperandStruct), _u32, _vp,
@@ -368,9 +369,10 @@ class LogUpInput:
         return LogUpInput(LOGUP_TABLE, columns, constant, sep, len(columns), multiplicities)
 
 
-def new_batch_multiple_sizes_prove(ctx, inputs, transcript):
+def new_batch_multiple_sizes_prove(ctx, inputs, transcript, partial=False):
     """zkml/src/lookup/logup_gkr/prover.rs:91-344.  Returns the flat canonical
-    encoding of the LogUpBatchProof (see include/dpb_prover.h)."""
+    encoding of the LogUpBatchProof (see include/dpb_prover.h).  partial: `inputs` are this rank's instances of a
+    batch spread over the communicator's ranks (dpb_logup_batch_prove_partial); the proof is the whole batch's."""
     arr = (LogupInputStruct * max(len(inputs), 1))()
     keep = []
     for i, inp in enumerate(inputs):
@@ -384,7 +386,8 @@ def new_batch_multiple_sizes_prove(ctx, inputs, transcript):
         arr[i].constant_challenge = inp.constant.ctypes.data
         arr[i].column_separation_challenge = inp.sep.ctypes.data
     h = ctypes.c_void_p()
-    check(lib.dpb_logup_batch_prove(ctx.h, arr, len(inputs), transcript.h, ctypes.byref(h)))
+    fn = lib.dpb_logup_batch_prove_partial if partial else lib.dpb_logup_batch_prove
+    check(fn(ctx.h, arr, len(inputs), transcript.h, ctypes.byref(h)))
     try:
         n = ctypes.c_size_t()
         check(lib.dpb_logup_proof_serialize(h, None, 0, ctypes.byref(n)))

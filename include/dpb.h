@@ -275,6 +275,13 @@ int dpb_sumcheck_begin(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, ui
  * dpb_sumcheck_begin. */
 int dpb_sumcheck_begin_sharded(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, uint32_t k,
                                const dpb_term* terms, uint32_t n_terms, dpb_sc** out);
+/* A sumcheck whose TERMS are spread over the ranks of the context's communicator (the instances of a batch, the
+ * heads of a stacked product): every rank passes whole tables and its own part of the term list, of the same
+ * degree on every rank; each round's sums are added over the ranks (same exchange as the sharded form), all ranks
+ * feed the same transcript, and dpb_sumcheck_finish returns the final evaluations of THIS rank's tables.  The
+ * messages equal those of one sumcheck over the union of the term lists.  With one rank: dpb_sumcheck_begin. */
+int dpb_sumcheck_begin_partial(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, uint32_t k,
+                               const dpb_term* terms, uint32_t n_terms, dpb_sc** out);
 /* Degree of the round polynomial (max factors per term). */
 uint32_t dpb_sumcheck_degree(const dpb_sc* sc);
 /* One prover round.  `prev_challenge` is NULL on the first round, otherwise the

@@ -150,6 +150,15 @@ typedef struct dpb_logup_proof dpb_logup_proof;
 /* new_batch_multiple_sizes_prove (zkml/src/lookup/logup_gkr/prover.rs:91-344) */
 int dpb_logup_batch_prove(dpb_ctx* ctx, const dpb_logup_input* inputs, uint32_t n_inputs, dpb_transcript* t,
                           dpb_logup_proof** out);
+/* The same batch with its INSTANCES spread over the ranks of ctx's communicator: every rank passes its own
+ * instances, of the same kinds, sizes and column counts on every rank (DPB_EINVAL otherwise), and a transcript in the
+ * same state.  Local instance i of rank g is instance i * G + g of the whole batch.  A rank builds only its own
+ * fraction trees and runs its own part of each layer's sumcheck (dpb_sumcheck_begin_partial); the trees' outputs and
+ * each layer's final evaluations are gathered over NCCL.  Every rank returns the proof of the whole batch, equal
+ * byte for byte to dpb_logup_batch_prove of all instances in that order on one GPU.  Splitting a column of 2^m rows
+ * into G instances of 2^m / G rows is how one large lookup is spread; the claims then speak about the slices. */
+int dpb_logup_batch_prove_partial(dpb_ctx* ctx, const dpb_logup_input* inputs, uint32_t n_inputs, dpb_transcript* t,
+                                  dpb_logup_proof** out);
 /* Flat encoding of LogUpBatchProof (field order of
  * zkml/src/lookup/logup_gkr/structs.rs:561-578): u32 counts and canonical
  * scalars.  Writes at most cap bytes; *len is the size needed. */

@@ -295,6 +295,59 @@ def mlp_layer(dpb, prover, ctx):
         print(f"{field}  {'layer total':44s} {sum(t for _, t in steps) * 1e6:9.1f}")
 
 
+def lookup_layer_logup(dpb, prover, ctx, field):
+    """The logup-GKR call of one lookup layer at the GELU size of GPT-2 (512 x 3072 entries, 12-bit table: one
+    shifted-chunk instance and two two-column instances of 2^21 rows): wall time, where the host's time goes
+    (dpb_trace_*), and the round kernels by (kernel, round, size) with launches timed one by one (dpb_profile_*;
+    the resident last-rounds kernel is off while profiling, so its rounds appear as launches)."""
+    import importlib
+    wl = importlib.import_module("deep_prove_b200.workloads")
+    be = wl.GpuBackend(dpb, prover, ctx, field)
+    rng = np.random.default_rng(0)
+    T = be.new_transcript()
+    bits = 12
+    spec = wl.LookupSpec("gelu", bits, right_shift=bits + 1, max_bit_size=2 * bits + 4, sign=wl.SIGN_MIXED)
+    chal = {k: tuple(be.squeeze(T, 2)) for k in ("shift", "gelu", "zero", "signed")}
+    sign, table_out, n_cols = wl.value_table("gelu", bits)
+    t = wl.draw_tensor(rng, (512, 3072), spec)
+    wit = be.lookup_witness(be.tensor(t), t.shape, spec, table_out, n_cols, [None] * 4)
+    ins, outs, n_sh, n_z = wit["ins"], wit["outs"], wit["n_shifted"], wit["n_zeroing"]
+    groups = {"shift": ins[:n_sh], "gelu": [ins[n_sh], outs[0]], "zero": [], "signed": []}
+    for z in range(n_z):
+        groups["signed" if z == n_z - 1 else "zero"] += [ins[n_sh + 1 + z], outs[1 + z]]
+    inputs = [("lookup", groups[k], cpi, None, chal[k][0], chal[k][1])
+              for k, cpi in (("shift", 1), ("gelu", 2), ("zero", 2), ("signed", 2)) if groups[k]]
+    print(f"# {field}: instances (columns, columns per instance): {[(len(i[1]), i[2]) for i in inputs]}")
+    for _ in range(3):
+        be.logup(T, inputs)
+    ctx.sync()
+    t0 = time.perf_counter()
+    for _ in range(5):
+        be.logup(T, inputs)
+    ctx.sync()
+    print(f"wall per call {(time.perf_counter() - t0) / 5 * 1e3:.3f} ms")
+    dpb.trace(True)
+    be.logup(T, inputs)
+    ctx.sync()
+    tr = dpb.trace_read()
+    dpb.trace(False)
+    for k, (ms, calls) in sorted(tr.items(), key=lambda kv: -kv[1][0]):
+        print(f"   host phase {k:36s} {ms:8.3f} ms  {calls} calls")
+    ctx.profile(True)
+    be.logup(T, inputs)
+    ctx.sync()
+    ctx.profile(False)
+    prof = ctx.profile_read()
+    print(f"round kernels, one launch per round: {sum(e['total_ms'] for e in prof):.3f} ms in "
+          f"{sum(e['launches'] for e in prof)} launches")
+    for e in sorted(prof, key=lambda e: -e["total_ms"])[:16]:
+        per = e["total_ms"] / e["launches"]
+        print(f"   {e['kernel']:34s} round {e['round']:2d} x{e['launches']:2d} {e['total_ms']:8.3f} ms "
+              f"{e['alg_bytes_per_launch'] / 1e6:9.2f} MB {e['alg_bytes_per_launch'] / 1e6 / max(per, 1e-9):8.1f} GB/s")
+    small = [e for e in prof if e["alg_bytes_per_launch"] < 4e6]
+    print(f"   launches under 4 MB: {sum(e['launches'] for e in small)} launches, {sum(e['total_ms'] for e in small):.3f} ms")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--field", default="fr", choices=["fr", "gl"])
@@ -305,6 +358,8 @@ def main():
     ap.add_argument("--issue-rate", action="store_true", help="the integer pipes' product rates (dpb_issue_rate_probe)")
     ap.add_argument("--lookup", action="store_true", help="only the lookup witness lines")
     ap.add_argument("--mlp", action="store_true", help="the steps of one dense + ReLU layer of the MLP configuration")
+    ap.add_argument("--lookup-layer-logup", action="store_true",
+                    help="the logup-GKR call of a GELU-sized lookup layer: wall, host phases, round kernels")
     args = ap.parse_args()
     dpb, prover = load()
     ctx = dpb.Context(0)
@@ -322,6 +377,10 @@ def main():
         return
     if args.mlp:
         mlp_layer(dpb, prover, ctx)
+        ctx.close()
+        return
+    if args.lookup_layer_logup:
+        lookup_layer_logup(dpb, prover, ctx, args.field)
         ctx.close()
         return
     rng = np.random.default_rng(0)

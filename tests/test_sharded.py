@@ -101,3 +101,41 @@ def test_sharded_sumcheck_with_an_eq_factor_on_gpus(field, n):
     want = dict(proof=orc.serialize_sumcheck_proof(F, proof).hex(), point=hx(pt), finals=hx(finals))
     for got in launch("gpu_eq", field, n, 21, world):
         assert got == want
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("field", ["gl", "fr"])
+@pytest.mark.parametrize("n", [6, 16])
+def test_logup_batch_spread_over_gpus(field, n):
+    """dpb_logup_batch_prove_partial: the instances of a batch (two sizes, one- and two-column lookups) spread over
+    the GPUs of the box.  Every rank returns the same bytes, equal to the oracle's proof of the whole batch and to
+    the single-GPU proof; n = 16 reaches the segmented one-pass rounds, n = 6 runs in the resident kernel's range
+    (which partial sumchecks do not use)."""
+    import torch
+    g = torch.cuda.device_count()
+    world = 8 if g >= 8 else 4 if g >= 4 else 2 if g >= 2 else 0
+    if world == 0:
+        pytest.skip("needs at least 2 GPUs")
+    F = orc.FIELDS[field]
+    _, whole = W.logup_batch_case(F, n, 31, world)
+    o_in = [orc.LogUpInput(F, 0, [F.table_from_i64(c) for c in cols], c0, s0, columns_per_instance=cpi)
+            for cols, cpi, c0, s0 in whole]
+    want = orc.serialize_logup_proof(F, orc.logup_batch_prove(F, o_in, orc.Transcript(F))).hex()
+    for r, got in enumerate(launch("gpu_logup", field, n, 31, world)):
+        assert got["proof"] == want, f"rank {r}"
+        if r == 0:
+            assert got["single_gpu_equal"]
+
+
+@pytest.mark.parametrize("field", ["gl", "fr"])
+@pytest.mark.parametrize("world", [2, 4])
+def test_logup_batch_spread_protocol_on_cpu_gloo(field, world):
+    """The protocol of the instance-spread logup prover with gloo ranks on CPU: every rank ends with the oracle's
+    proof of the whole batch (local instance i of rank g at position i * world + g)."""
+    F = orc.FIELDS[field]
+    _, whole = W.logup_batch_case(F, 5, 41, world)
+    o_in = [orc.LogUpInput(F, 0, [F.table_from_i64(c) for c in cols], c0, s0, columns_per_instance=cpi)
+            for cols, cpi, c0, s0 in whole]
+    want = orc.serialize_logup_proof(F, orc.logup_batch_prove(F, o_in, orc.Transcript(F))).hex()
+    for r, got in enumerate(launch("cpu_logup", field, 5, 41, world)):
+        assert got["proof"] == want, f"rank {r}"
