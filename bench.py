@@ -475,6 +475,74 @@ def strong_record(dpb, prover, ctx, torch, dist, stream, mles, terms, fam, n, wo
                        "of the local rounds plus the replicated last log2(N) rounds; the kernels scale with 1/N"}
 
 
+def logup_spread_record(dpb, prover, ctx, torch, dist, world, rank, steps, seed):
+    """A logup-GKR batch spread over the GPUs by instance (dpb_logup_batch_prove_partial): 24 two-column lookup
+    instances of 2^18 rows (two attention layers' worth of softmax columns), BN254, integer columns resident on the
+    device; instance j lives on rank j mod N.  Rank 0 also proves the whole batch alone in the same run, and the
+    bytes of the two proofs are compared."""
+    import numpy as np
+    total, rows = 24, 1 << 18
+    rng = np.random.default_rng(seed + 5)
+    cst, sep = [rng.integers(1, 2**62, size=4, dtype=np.uint64) for _ in range(2)]
+    cst[3] = sep[3] = 0
+    cols = [[rng.integers(-(1 << 11), 1 << 11, size=rows, dtype=np.int64) for _ in range(2)] for _ in range(total)]
+
+    def lookups(idx):
+        dev = [ctx.upload_ints(c, dpb.FR_I64) for j in idx for c in cols[j]]
+        return prover.LogUpInput.new_lookup(dev, cst.reshape(1, 4), sep.reshape(1, 4), 2), dev
+
+    mine, mine_dev = lookups([j for j in range(total) if j % world == rank])
+
+    def spread():
+        t = prover.Blake3Transcript(dpb.FR)
+        out = prover.new_batch_multiple_sizes_prove(ctx, [mine], t, partial=True)
+        t.free()
+        return out
+
+    def wall(fn, reps, collective):
+        for _ in range(2):
+            got = fn()
+        if collective:
+            dist.barrier()
+        ctx.sync()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            got = fn()
+        ctx.sync()
+        dt = (time.perf_counter() - t0) / reps * 1e3
+        if collective:
+            tt = torch.tensor([dt], device="cuda")
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            dt = float(tt.item())
+        return dt, got
+
+    ms_n, got = wall(spread, steps, True)
+    ms_1, equal = None, None
+    if rank == 0:
+        whole, whole_dev = lookups(range(total))
+
+        def alone():
+            t = prover.Blake3Transcript(dpb.FR)
+            out = prover.new_batch_multiple_sizes_prove(ctx, [whole], t)
+            t.free()
+            return out
+        ms_1, want = wall(alone, steps, False)
+        equal = want == got
+        for m in whole_dev:
+            m.free()
+    dist.barrier()
+    for m in mine_dev:
+        m.free()
+    if rank != 0:
+        return None
+    return {"workload": f"logup-GKR batch of {total} two-column lookup instances of 2^18 rows, BN254, over {world} GPUs "
+                        f"({total // world} instances per GPU)",
+            "ms_per_proof": ms_n, "ms_per_proof_one_gpu_same_run": ms_1, "speedup": ms_1 / ms_n,
+            "proof_equals_single_gpu": equal,
+            "timing": "wall clock around the call between device synchronisations, max over ranks",
+            "exchanges": "per round the partial sums (shared host segment), per layer the final evaluations (NCCL)"}
+
+
 def workload_record(dpb, prover, ctx, args):
     """The GPT-2-small seq-512 path workload (deep-prove_b200/workloads.py) over BN254, tensors resident on the
     device: tokens/s = sequence length / time of the path's calls, the reference's definition of token/sec
@@ -689,6 +757,9 @@ def run_ours(args):
         if not args.no_strong:
             strong = strong_record(dpb, prover, ctx, torch, dist, stream, mles, terms, fam, n, world, rank,
                                    min(args.steps, 20))
+            spread = logup_spread_record(dpb, prover, ctx, torch, dist, world, rank, min(args.steps, 10), args.seed)
+            if strong is not None:
+                strong["logup_batch"] = spread
     # ---- parity of the timed path against the oracle, outside the timed region
     cpu_rec, case = None, None
     if world == 1 and not args.no_cpu_baseline:
