@@ -554,13 +554,17 @@ def workload_record(dpb, prover, ctx, args):
     # walk's largest allocation (the claim batching's fold buffers); a prover process is in this state after its
     # first proof
     wl.run_transformer_path(dpb, prover, ctx, shape, field="fr", seed=args.seed + 1, with_commit=True)
+    dpb.trace(True)
     got = wl.run_transformer_path(dpb, prover, ctx, shape, field="fr", seed=args.seed, with_commit=True)
+    phases = {k: {"ms": v[0], "calls": v[1]} for k, v in sorted(dpb.trace_read().items(), key=lambda kv: -kv[1][0])[:12]}
+    dpb.trace(False)
     rec = {"workload": "GPT-2-small (12 layers, d_model 768, 12 heads, FFN 3072, vocab 50257), 512 tokens: every "
                        "sumcheck / fold / logup-GKR call of the forward graph, BN254 Fr, seeded synthetic integer "
                        "tensors resident on the device (BASELINE.json configs[2] shapes)",
            "field": "bn254", "ms": got["seconds"] * 1e3, "tokens_per_s": got["tokens_per_s"],
            "by_kind_ms": {k: v * 1e3 for k, v in sorted(got["by_kind"].items(), key=lambda kv: -kv[1])},
            "calls": got["calls"], "wall_seconds_with_input_generation": got["wall_seconds"],
+           "host_phases_ms": phases,
            "witness_commit": {
                "ms": got["commit_seconds"] * 1e3,
                "what": "every lookup layer's witness columns committed: one BN254 G1 multi-scalar multiplication "
@@ -781,8 +785,11 @@ def run_ours(args):
         for m in mles:
             m.free()
         mles = []
-        workloads = {"gpt2_seq512": workload_record(dpb, prover, ctx, args)}
-        workloads.update(more_workloads(dpb, prover, ctx, args, ["mlp", "llama2_7b_2blocks_seq1024", "gemma3_1b_seq512"]))
+        which = [w for w in args.workloads.split(",") if w]
+        workloads = {}
+        if "gpt2_seq512" in which:
+            workloads["gpt2_seq512"] = workload_record(dpb, prover, ctx, args)
+        workloads.update(more_workloads(dpb, prover, ctx, args, [w for w in which if w != "gpt2_seq512"]))
     if world > 1:
         ctx.comm_free()
         dist.barrier()
@@ -852,7 +859,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-bn254", action="store_true")
     ap.add_argument("--no-strong", action="store_true")
-    ap.add_argument("--no-workload", action="store_true", help="skip the GPT-2 seq-512 path workload")
+    ap.add_argument("--no-workload", action="store_true", help="skip the model-shaped path workloads")
+    ap.add_argument("--workloads", default="gpt2_seq512,mlp,llama2_7b_2blocks_seq1024,gemma3_1b_seq512",
+                    help="which path workloads the default line walks (comma-separated)")
     ap.add_argument("--only", default=None,
                     choices=["bn254", "workload", "mlp", "gemma3_1b_seq512", "llama2_7b_2blocks_seq1024"],
                     help="run one sub-record alone and print it (profiling captures of its kernels)")

@@ -40,13 +40,68 @@ int fail(int code, const char* fmt, ...) {
     return code;
 }
 
+constexpr size_t kBlockCacheMin = 256 * 1024;            // smaller requests go straight to the allocator
+constexpr size_t kBlockCacheMaxBytes = (size_t)24 << 30;  // freed bytes kept per context
+constexpr size_t kBlockCacheMaxBlocks = 512;
+
+static void block_cache_release(dpb_ctx* ctx, size_t keep_bytes) {
+    // oldest first
+    size_t i = 0;
+    while (i < ctx->block_free.size() && (ctx->block_free_bytes > keep_bytes || ctx->block_free.size() > kBlockCacheMaxBlocks)) {
+        cudaFreeAsync(ctx->block_free[i].p, ctx->stream);
+        ctx->block_free_bytes -= ctx->block_free[i].bytes;
+        i++;
+    }
+    ctx->block_free.erase(ctx->block_free.begin(), ctx->block_free.begin() + i);
+}
+
 int device_alloc(dpb_ctx* ctx, size_t bytes, void** out) {
     if (bytes == 0) bytes = 16;
-    DPB_CUDA(cudaMallocAsync(out, bytes, ctx->stream));
+    if (bytes < kBlockCacheMin) {
+        DPB_CUDA(cudaMallocAsync(out, bytes, ctx->stream));
+        return DPB_OK;
+    }
+    std::lock_guard<std::mutex> lock(ctx->block_mu);
+    for (size_t i = ctx->block_free.size(); i-- > 0;) {  // newest first
+        if (ctx->block_free[i].bytes != bytes) continue;
+        *out = ctx->block_free[i].p;
+        ctx->block_free_bytes -= bytes;
+        ctx->block_free.erase(ctx->block_free.begin() + i);
+        ctx->block_live[*out] = bytes;
+        return DPB_OK;
+    }
+    cudaError_t e = cudaMallocAsync(out, bytes, ctx->stream);
+    if (e == cudaErrorMemoryAllocation && !ctx->block_free.empty()) {
+        // the kept blocks are what stands in the way: give them back and ask again
+        cudaGetLastError();
+        block_cache_release(ctx, 0);
+        e = cudaMallocAsync(out, bytes, ctx->stream);
+    }
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(e == cudaErrorMemoryAllocation ? DPB_ENOMEM : DPB_ECUDA, "device allocation of %zu bytes: %s", bytes,
+                    cudaGetErrorString(e));
+    }
+    ctx->block_live[*out] = bytes;
     return DPB_OK;
 }
 void device_free(dpb_ctx* ctx, void* p) {
-    if (p) cudaFreeAsync(p, ctx->stream);
+    if (!p) return;
+    std::lock_guard<std::mutex> lock(ctx->block_mu);
+    auto it = ctx->block_live.find(p);
+    if (it == ctx->block_live.end()) {
+        cudaFreeAsync(p, ctx->stream);
+        return;
+    }
+    const size_t bytes = it->second;
+    ctx->block_live.erase(it);
+    if (bytes > kBlockCacheMaxBytes / 4) {  // one very large block would push everything else out
+        cudaFreeAsync(p, ctx->stream);
+        return;
+    }
+    ctx->block_free.push_back({p, bytes});
+    ctx->block_free_bytes += bytes;
+    block_cache_release(ctx, kBlockCacheMaxBytes);
 }
 
 int upload_small(dpb_ctx* ctx, void* dst, const void* src, size_t bytes) {
@@ -352,7 +407,11 @@ int dpb_init(int device, dpb_ctx** out) {
 void dpb_shutdown(dpb_ctx* ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
-    if (ctx->slab_cache) cudaFreeAsync(ctx->slab_cache, ctx->stream);
+    if (ctx->slab_cache) device_free(ctx, ctx->slab_cache);
+    {
+        std::lock_guard<std::mutex> lock(ctx->block_mu);
+        block_cache_release(ctx, 0);
+    }
     cudaStreamSynchronize(ctx->stream);
     cudaStreamSynchronize(ctx->tail_stream);
     cudaStreamDestroy(ctx->tail_stream);

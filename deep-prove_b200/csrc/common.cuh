@@ -8,6 +8,8 @@
 #include <cstdio>
 #include <cstring>
 #include <string>
+#include <mutex>
+#include <unordered_map>
 #include <vector>
 
 #include "family.cuh"
@@ -126,6 +128,19 @@ struct dpb_ctx {
     cudaEvent_t up_ev[kStageSlots] = {};
     bool up_used[kStageSlots] = {};
     int up_next = 0;
+    // Freed blocks of 256 KiB and more, kept by exact size for the next request of that size (device_alloc /
+    // device_free): a proof asks for the same few sizes layer after layer (fraction trees, witness columns, eq
+    // tables), and the stream-ordered allocator was measured to take milliseconds per large block once its pool
+    // is fragmented by earlier work of the process.  Every allocation of a context is used on its one stream, so
+    // handing a freed block to the next request is as safe as the allocator's own stream-ordered reuse.
+    struct Block {
+        void* p;
+        size_t bytes;
+    };
+    std::mutex block_mu;
+    std::unordered_map<void*, size_t> block_live;  // live large allocations -> size
+    std::vector<Block> block_free;                  // oldest first
+    size_t block_free_bytes = 0;
     // the block of device memory the last sumcheck used, kept for the next one (dpb_sumcheck_begin)
     void* slab_cache = nullptr;
     size_t slab_cache_bytes = 0;

@@ -565,7 +565,7 @@ def transformer_path(be, shape, seed=0, blocks=None, with_final=True, with_commi
 
 
 def mlp_path(be, shape, seed=0, with_commit=False):
-    """The dense network of BASELINE's first configuration: per layer the einsum's axis fixing and sumcheck, then
+    """The dense network (a 2-layer MLP with ReLU through a lookup and an argmax output): per layer the einsum's axis fixing and sumcheck, then
     (all but the last layer) ReLU with requantisation through a lookup: witness, logup-GKR, linking sumcheck; at the
     end the argmax, the tables' logup proof and the claim batching."""
     w = PathWalk(be, shape.table_bits, shape.commit_chunk_log2, shape.range_check_chunks, seed, with_commit)
