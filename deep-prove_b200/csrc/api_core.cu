@@ -41,8 +41,15 @@ int fail(int code, const char* fmt, ...) {
 }
 
 constexpr size_t kBlockCacheMin = 256 * 1024;            // smaller requests go straight to the allocator
-constexpr size_t kBlockCacheMaxBytes = (size_t)24 << 30;  // freed bytes kept per context
 constexpr size_t kBlockCacheMaxBlocks = 512;
+// freed bytes kept per context: 64 GiB of the 180 (DPB_BLOCK_CACHE_GB overrides; 0 keeps nothing)
+static size_t block_cache_max_bytes() {
+    static const size_t v = [] {
+        const char* e = getenv("DPB_BLOCK_CACHE_GB");
+        return (size_t)(e ? strtoull(e, nullptr, 10) : 64) << 30;
+    }();
+    return v;
+}
 
 static void block_cache_release(dpb_ctx* ctx, size_t keep_bytes) {
     // oldest first
@@ -95,13 +102,13 @@ void device_free(dpb_ctx* ctx, void* p) {
     }
     const size_t bytes = it->second;
     ctx->block_live.erase(it);
-    if (bytes > kBlockCacheMaxBytes / 4) {  // one very large block would push everything else out
+    if (bytes > block_cache_max_bytes() / 2) {  // one very large block would push everything else out
         cudaFreeAsync(p, ctx->stream);
         return;
     }
     ctx->block_free.push_back({p, bytes});
     ctx->block_free_bytes += bytes;
-    block_cache_release(ctx, kBlockCacheMaxBytes);
+    block_cache_release(ctx, block_cache_max_bytes());
 }
 
 int upload_small(dpb_ctx* ctx, void* dst, const void* src, size_t bytes) {

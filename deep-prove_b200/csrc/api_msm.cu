@@ -10,7 +10,8 @@
 //   3. msm_scatter    the point indices, grouped by bucket
 //   4. msm_buckets    one thread per bucket adds its points up (mixed Jacobian + affine additions); a bucket with
 //                     more than 96 points (small integers crowd a wide window's low buckets) goes to a list that
-//                     msm_heavy_buckets works off with one block per bucket
+//                     msm_heavy_plan / msm_heavy_chunks / msm_heavy_combine work off in chunks of 2048 points, one
+//                     block per chunk
 //   5. msm_reduce     per window sum_b b * B_b: a thread takes a run of 16 buckets (running sums from the top, plus
 //                     the run's offset times its total), a block adds its 256 runs up in shared memory
 //   6. host           the blocks' partial sums per window (a handful of points), the windows combined by c
@@ -63,16 +64,33 @@ __device__ __forceinline__ uint32_t msm_digit(const uint64_t (&mag)[4], uint32_t
     return (uint32_t)(v & ((1ull << c) - 1));
 }
 
+// Lanes of a warp that hold the same key add their count with one atomic (a column of a few distinct values would
+// otherwise send a million atomics to the same few counters).  Returns the lane's rank among them and, in every
+// lane of the group, the value the leader's atomicAdd returned.
+__device__ __forceinline__ uint32_t msm_group_add(uint32_t* counter, uint64_t key, bool take, unsigned active,
+                                                  uint32_t& rank) {
+    const unsigned peers = __match_any_sync(active, take ? key : ~0ull);
+    const int leader = __ffs(peers) - 1;
+    const unsigned lane = threadIdx.x & 31;
+    rank = __popc(peers & ((1u << lane) - 1));
+    uint32_t base = 0;
+    if (take && (int)lane == leader) base = atomicAdd(counter, (uint32_t)__popc(peers));
+    return __shfl_sync(peers, base, leader);
+}
+
 __global__ void __launch_bounds__(kThreads)
     msm_count(MsmScalars s, uint64_t n, uint32_t c, uint32_t windows, uint32_t* __restrict__ counts) {
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const unsigned active = __activemask();
         uint64_t mag[4];
         bool neg;
         msm_scalar(s, i, mag, neg);
         for (uint32_t w = 0; w < windows; w++) {
             const uint32_t d = msm_digit(mag, w, c);
-            if (d) atomicAdd(&counts[((size_t)w << c) + d], 1u);
+            const size_t key = ((size_t)w << c) + d;
+            uint32_t rank;
+            msm_group_add(&counts[key], key, d != 0, active, rank);
         }
     }
 }
@@ -168,15 +186,16 @@ __global__ void __launch_bounds__(kThreads)
                 uint32_t* __restrict__ cursor, uint32_t* __restrict__ items) {
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const unsigned active = __activemask();
         uint64_t mag[4];
         bool neg;
         msm_scalar(s, i, mag, neg);
         for (uint32_t w = 0; w < windows; w++) {
             const uint32_t d = msm_digit(mag, w, c);
-            if (!d) continue;
             const size_t key = ((size_t)w << c) + d;
-            const uint32_t at = atomicAdd(&cursor[key], 1u);
-            items[offsets[key] + at] = (uint32_t)i | (neg ? 0x80000000u : 0u);
+            uint32_t rank;
+            const uint32_t at = msm_group_add(&cursor[key], key, d != 0, active, rank);
+            if (d) items[offsets[key] + at + rank] = (uint32_t)i | (neg ? 0x80000000u : 0u);
         }
     }
 }
@@ -204,20 +223,65 @@ __global__ void __launch_bounds__(kThreads)
     buckets[key] = acc;
 }
 
-// one block per heavy bucket: every thread adds a strided share of the bucket's points, then a tree in shared memory
+// Heavy buckets are cut into chunks of kHeavyChunk points so that a bucket of a million points (16-bit values in a
+// 13-bit window leave seven such buckets in the second window) is work for the whole GPU instead of one block.
+// msm_heavy_plan: chunk_first[h] = number of chunks before heavy bucket h (one block; the list has at most
+// n * windows / kMsmHeavy entries).
+constexpr uint32_t kHeavyChunk = 2048;
+__global__ void __launch_bounds__(1024)
+    msm_heavy_plan(const uint32_t* __restrict__ counts, const uint32_t* __restrict__ heavy_list,
+                   const uint32_t* __restrict__ heavy_count, uint32_t* __restrict__ chunk_first) {
+    __shared__ uint32_t part[1024];
+    const uint32_t n_heavy = *heavy_count;
+    const uint32_t per = (n_heavy + blockDim.x - 1) / blockDim.x;
+    const uint32_t lo = threadIdx.x * per < n_heavy ? threadIdx.x * per : n_heavy;
+    const uint32_t hi = lo + per < n_heavy ? lo + per : n_heavy;
+    uint32_t sum = 0;
+    for (uint32_t h = lo; h < hi; h++) sum += (counts[heavy_list[h]] + kHeavyChunk - 1) / kHeavyChunk;
+    part[threadIdx.x] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t run = 0;
+        for (uint32_t t = 0; t < blockDim.x; t++) {
+            const uint32_t v = part[t];
+            part[t] = run;
+            run += v;
+        }
+        chunk_first[n_heavy] = run;  // total
+    }
+    __syncthreads();
+    uint32_t run = part[threadIdx.x];
+    for (uint32_t h = lo; h < hi; h++) {
+        chunk_first[h] = run;
+        run += (counts[heavy_list[h]] + kHeavyChunk - 1) / kHeavyChunk;
+    }
+}
+
+// one block per chunk (grid-stride): every thread adds a strided share of the chunk's points, then a tree in shared
+// memory; chunk_sums[g] = the chunk's sum
 __global__ void __launch_bounds__(kMsmReduceThreads)
-    msm_heavy_buckets(const G1Affine* __restrict__ bases, const uint32_t* __restrict__ offsets,
-                      const uint32_t* __restrict__ counts, const uint32_t* __restrict__ items,
-                      const uint32_t* __restrict__ heavy_list, const uint32_t* __restrict__ heavy_count,
-                      G1Jac* __restrict__ buckets) {
+    msm_heavy_chunks(const G1Affine* __restrict__ bases, const uint32_t* __restrict__ offsets,
+                     const uint32_t* __restrict__ counts, const uint32_t* __restrict__ items,
+                     const uint32_t* __restrict__ heavy_list, const uint32_t* __restrict__ heavy_count,
+                     const uint32_t* __restrict__ chunk_first, G1Jac* __restrict__ chunk_sums) {
     __shared__ G1Jac sh[kMsmReduceThreads];
     const uint32_t n_heavy = *heavy_count;
-    for (uint32_t h = blockIdx.x; h < n_heavy; h += gridDim.x) {
-        const uint32_t key = heavy_list[h];
-        const uint32_t lo = offsets[key], cnt = counts[key];
+    const uint32_t total = chunk_first[n_heavy];
+    for (uint32_t g = blockIdx.x; g < total; g += gridDim.x) {
+        // the heavy bucket this chunk belongs to: last h with chunk_first[h] <= g
+        uint32_t lo_h = 0, hi_h = n_heavy;
+        while (hi_h - lo_h > 1) {
+            const uint32_t mid = (lo_h + hi_h) >> 1;
+            if (chunk_first[mid] <= g) lo_h = mid;
+            else hi_h = mid;
+        }
+        const uint32_t key = heavy_list[lo_h];
+        const uint32_t first = offsets[key] + (g - chunk_first[lo_h]) * kHeavyChunk;
+        const uint32_t end_all = offsets[key] + counts[key];
+        const uint32_t end = first + kHeavyChunk < end_all ? first + kHeavyChunk : end_all;
         G1Jac acc = g1_infinity();
-        for (uint32_t j = threadIdx.x; j < cnt; j += blockDim.x) {
-            const uint32_t it = items[lo + j];
+        for (uint32_t j = first + threadIdx.x; j < end; j += blockDim.x) {
+            const uint32_t it = items[j];
             G1Affine p = bases[it & 0x7fffffffu];
             if (it & 0x80000000u) p = g1_affine_neg(p);
             acc = g1_add_mixed(acc, p);
@@ -228,7 +292,33 @@ __global__ void __launch_bounds__(kMsmReduceThreads)
             if (threadIdx.x < s) sh[threadIdx.x] = g1_add(sh[threadIdx.x], sh[threadIdx.x + s]);
             __syncthreads();
         }
-        if (threadIdx.x == 0) buckets[key] = sh[0];
+        if (threadIdx.x == 0) chunk_sums[g] = sh[0];
+        __syncthreads();
+    }
+}
+
+// one block per heavy bucket (grid-stride): the sum of its chunks' sums
+__global__ void __launch_bounds__(kMsmReduceThreads)
+    msm_heavy_combine(const uint32_t* __restrict__ heavy_list, const uint32_t* __restrict__ heavy_count,
+                      const uint32_t* __restrict__ chunk_first, const G1Jac* __restrict__ chunk_sums,
+                      G1Jac* __restrict__ buckets) {
+    __shared__ G1Jac sh[kMsmReduceThreads];
+    const uint32_t n_heavy = *heavy_count;
+    for (uint32_t h = blockIdx.x; h < n_heavy; h += gridDim.x) {
+        const uint32_t first = chunk_first[h], end = chunk_first[h + 1];
+        if (end - first == 1) {  // the usual case: a bucket of a few hundred points
+            if (threadIdx.x == 0) buckets[heavy_list[h]] = chunk_sums[first];
+            continue;
+        }
+        G1Jac acc = g1_infinity();
+        for (uint32_t g = first + threadIdx.x; g < end; g += blockDim.x) acc = g1_add(acc, chunk_sums[g]);
+        sh[threadIdx.x] = acc;
+        __syncthreads();
+        for (uint32_t s = kMsmReduceThreads / 2; s > 0; s >>= 1) {
+            if (threadIdx.x < s) sh[threadIdx.x] = g1_add(sh[threadIdx.x], sh[threadIdx.x + s]);
+            __syncthreads();
+        }
+        if (threadIdx.x == 0) buckets[heavy_list[h]] = sh[0];
         __syncthreads();
     }
 }
@@ -415,6 +505,11 @@ int dpb_msm_g1(dpb_ctx* ctx, const dpb_g1_bases* bases, const dpb_mle* scalars, 
                  o_heavy_count = take(256), o_items = take((size_t)n * windows * 4), o_heavy = take(n_keys * 4),
                  o_tiles = take(((n_keys + kScanTile - 1) / kScanTile) * 4), o_buckets = take(n_keys * sizeof(G1Jac)),
                  o_part = take(n_partials * sizeof(G1Jac));
+    // heavy buckets: at most n * windows / kMsmHeavy of them, cut into at most that many + n * windows / kHeavyChunk chunks
+    uint64_t max_heavy = (uint64_t)n * windows / kMsmHeavy + 1;
+    if (max_heavy > n_keys) max_heavy = n_keys;
+    const uint64_t max_chunks = max_heavy + (uint64_t)n * windows / kHeavyChunk + 1;
+    const size_t o_chunk_first = take((max_heavy + 1) * 4), o_chunk_sums = take(max_chunks * sizeof(G1Jac));
     void* slab = nullptr;
     DPB_TRY(device_alloc(ctx, off, &slab));
     char* base = (char*)slab;
@@ -442,12 +537,15 @@ int dpb_msm_g1(dpb_ctx* ctx, const dpb_g1_bases* bases, const dpb_mle* scalars, 
         msm_buckets<<<(uint32_t)((n_keys + kThreads - 1) / kThreads), kThreads, 0, ctx->stream>>>(
             bases->dev, offsets, counts, items, n_keys, buckets, heavy_list, heavy_count);
         {
-            // at most n * windows / kMsmHeavy buckets can be heavy; idle blocks leave at once
-            uint64_t max_heavy = (uint64_t)n * windows / kMsmHeavy + 1;
-            if (max_heavy > n_keys) max_heavy = n_keys;
+            // idle blocks leave at once
+            uint32_t* chunk_first = (uint32_t*)(base + o_chunk_first);
+            G1Jac* chunk_sums = (G1Jac*)(base + o_chunk_sums);
             const uint32_t cap = (uint32_t)ctx->sm_count * 16;
-            msm_heavy_buckets<<<(uint32_t)(max_heavy < cap ? max_heavy : cap), kMsmReduceThreads, 0, ctx->stream>>>(
-                bases->dev, offsets, counts, items, heavy_list, heavy_count, buckets);
+            msm_heavy_plan<<<1, 1024, 0, ctx->stream>>>(counts, heavy_list, heavy_count, chunk_first);
+            msm_heavy_chunks<<<(uint32_t)(max_chunks < cap ? max_chunks : cap), kMsmReduceThreads, 0, ctx->stream>>>(
+                bases->dev, offsets, counts, items, heavy_list, heavy_count, chunk_first, chunk_sums);
+            msm_heavy_combine<<<(uint32_t)(max_heavy < cap ? max_heavy : cap), kMsmReduceThreads, 0, ctx->stream>>>(
+                heavy_list, heavy_count, chunk_first, chunk_sums, buckets);
         }
         msm_reduce<<<(uint32_t)n_partials, kMsmReduceThreads, 0, ctx->stream>>>(buckets, c, blocks_per_window, partials);
         e = cudaGetLastError();

@@ -84,7 +84,11 @@ typedef struct dpb_term {
 
 /* ---- context ----------------------------------------------------------- */
 /* Creates a context on CUDA device `device`.  Fails with DPB_ECUDA when no
- * usable GPU is present: there is no CPU fallback. */
+ * usable GPU is present: there is no CPU fallback.
+ * Device memory: tables and scratch come from the device's default stream-ordered pool (release threshold
+ * raised so that the pool keeps what it has grown to); blocks of 256 KiB and more that the library frees are kept
+ * per context, up to 64 GiB (environment variable DPB_BLOCK_CACHE_GB; 0 keeps nothing), and handed to the next
+ * request of exactly that size; they go back to the pool when an allocation fails, and at dpb_shutdown. */
 int dpb_init(int device, dpb_ctx** out);
 void dpb_shutdown(dpb_ctx* ctx);
 const char* dpb_last_error(void);

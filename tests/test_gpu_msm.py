@@ -119,3 +119,23 @@ def test_commit_is_linear_at_the_full_chunk_size(dpb, ctx, pcs, points):
     neg = dpb.linear_combination(ctx, [ctx.upload(f, dpb.FR)], orc.scalars_to_array(F, [F.neg(F.one)]))
     assert g1.add(point(cf), point(pcs.msm(ctx, bases, neg))) is None
     bases.free()
+
+
+@pytest.mark.parametrize("values", ["few", "int16"])
+def test_msm_crowded_buckets(dpb, ctx, pcs, values):
+    """Columns of few distinct values (signs, zero checks) and 16-bit chunks put tens of thousands of points into a
+    handful of buckets: those are summed in chunks of 2048 points by many blocks.  The bases are the consecutive
+    multiples of the generator, so sum_i s_i (i + 1) G is ONE scalar multiplication on the CPU side."""
+    rng = np.random.default_rng(6400)
+    n = 1 << 17
+    if values == "few":
+        x = rng.choice(np.array([0, 1, -1, 2, 255], dtype=np.int64), size=n)
+    else:
+        x = rng.integers(0, 1 << 16, size=n, dtype=np.int64)  # 13-bit window: the second window has 7 huge buckets
+    bases = pcs.G1Bases.synthetic(ctx, n)
+    k = int(sum(int(v) * (i + 1) for i, v in enumerate(x)) % g1.R_ORDER)
+    want = g1.boundary(g1.mul(k, g1.GENERATOR))
+    for dt in (dpb.FR_I32, dpb.FR_I64):
+        assert pcs.msm(ctx, bases, ctx.upload_ints(x, dt)) == want
+    assert pcs.msm(ctx, bases, ctx.upload(F.table_from_i64(x), dpb.FR)) == want
+    bases.free()
