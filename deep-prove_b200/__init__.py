@@ -57,6 +57,7 @@ SIGNATURES = {
     "dpb_comm_shared_exchange": (_int, [_vp]),
     "dpb_resident_rounds": (_int, [_vp, _int, _u32]),
     "dpb_sumcheck_launches": (_u64, [_vp]),
+    "dpb_trim": (_int, [_vp]),
     "dpb_issue_rate_probe": (_int, [_vp, _int, _u32, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)]),
     "dpb_trace_enable": (_int, [_int]),
     "dpb_trace_read": (_int, [ctypes.c_char_p, ctypes.c_size_t, ctypes.POINTER(ctypes.c_size_t)]),
@@ -202,6 +203,10 @@ class Context:
         if self.h:
             lib.dpb_shutdown(self.h)
             self.h = None
+
+    def trim(self):
+        """dpb_trim: kept device memory goes back to the pool and the pool's unused memory to the device."""
+        check(lib.dpb_trim(self.h))
 
     def sync(self):
         check(lib.dpb_sync(self.h))

@@ -87,9 +87,13 @@ typedef struct dpb_term {
  * usable GPU is present: there is no CPU fallback.
  * Device memory: tables and scratch come from the device's default stream-ordered pool (release threshold
  * raised so that the pool keeps what it has grown to); blocks of 256 KiB and more that the library frees are kept
- * per context, up to 64 GiB (environment variable DPB_BLOCK_CACHE_GB; 0 keeps nothing), and handed to the next
+ * per context, up to 8 GiB (environment variable DPB_BLOCK_CACHE_GB; 0 keeps nothing), and handed to the next
  * request of exactly that size; they go back to the pool when an allocation fails, and at dpb_shutdown. */
 int dpb_init(int device, dpb_ctx** out);
+/* Gives the device memory the context keeps for reuse (freed blocks, the last sumcheck's block) back to the pool and
+ * the pool's unused memory back to the device; waits for the context's stream.  For a process that moves on to a
+ * job of different sizes, or shares the GPU's memory with another library. */
+int dpb_trim(dpb_ctx* ctx);
 void dpb_shutdown(dpb_ctx* ctx);
 const char* dpb_last_error(void);
 /* Blocks until all work queued on the context's stream has finished. */
