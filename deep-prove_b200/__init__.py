@@ -58,6 +58,7 @@ SIGNATURES = {
     "dpb_resident_rounds": (_int, [_vp, _int, _u32]),
     "dpb_sumcheck_launches": (_u64, [_vp]),
     "dpb_trim": (_int, [_vp]),
+    "dpb_mle_evaluate_many": (_int, [_vp, _pp, _u32, _vp, _u32, _vp]),
     "dpb_issue_rate_probe": (_int, [_vp, _int, _u32, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)]),
     "dpb_trace_enable": (_int, [_int]),
     "dpb_trace_read": (_int, [ctypes.c_char_p, ctypes.c_size_t, ctypes.POINTER(ctypes.c_size_t)]),
@@ -516,6 +517,17 @@ def eq_tables(ctx, family_dtype, points):
     outs = (ctypes.c_void_p * n)()
     check(lib.dpb_eq_tables(ctx.h, family_dtype, _buf(flat), nv, n, ctypes.byref(owner), outs))
     return Mle(ctx, owner), [Mle(ctx, ctypes.c_void_p(outs[i])) for i in range(n)]
+
+
+def evaluate_many(ctx, mles, point_array):
+    """dpb_mle_evaluate_many: every table (zero-padded to the point's number of variables) at one point."""
+    p = np.ascontiguousarray(point_array, dtype=np.uint64)
+    n = len(mles)
+    w = elem_words(chal_dtype(mles[0].dtype))
+    hs = (ctypes.c_void_p * n)(*[m.h for m in mles])
+    out = np.zeros((n, w), dtype=np.uint64)
+    check(lib.dpb_mle_evaluate_many(ctx.h, hs, n, _buf(p) if p.size else None, p.shape[0] if p.size else 0, _buf(out)))
+    return out
 
 
 ROPE_ADJACENT, ROPE_ROTATE_HALF = 0, 1

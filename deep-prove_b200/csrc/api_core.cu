@@ -53,15 +53,46 @@ static size_t block_cache_max_bytes() {
     return v;
 }
 
-static void block_cache_release(dpb_ctx* ctx, size_t keep_bytes) {
-    // oldest first
-    size_t i = 0;
-    while (i < ctx->block_free.size() && (ctx->block_free_bytes > keep_bytes || ctx->block_free.size() > kBlockCacheMaxBlocks)) {
-        cudaFreeAsync(ctx->block_free[i].p, ctx->stream);
-        ctx->block_free_bytes -= ctx->block_free[i].bytes;
-        i++;
+// Two classes of kept blocks.  Ordinary ones (fraction trees, columns, eq tables: up to 4 GiB each) share the
+// budget above.  Huge ones (the fold buffers and eq tables of a claim batching over a whole model: tens of GB in one
+// block, 170 ms in the allocator each time) are few: the last three, up to 96 GiB together.
+constexpr size_t kBlockHuge = (size_t)4 << 30;
+constexpr size_t kBlockHugeMaxBytes = (size_t)96 << 30;
+constexpr size_t kBlockHugeMaxCount = 3;
+
+// frees the oldest kept blocks until the ordinary ones hold at most keep_bytes and the huge ones at most keep_huge
+static void block_cache_release(dpb_ctx* ctx, size_t keep_bytes, size_t keep_huge = 0) {
+    size_t small_bytes = 0, huge_bytes = 0, small_n = 0, huge_n = 0;
+    for (const auto& b : ctx->block_free) {
+        if (b.bytes >= kBlockHuge) {
+            huge_bytes += b.bytes;
+            huge_n++;
+        } else {
+            small_bytes += b.bytes;
+            small_n++;
+        }
     }
-    ctx->block_free.erase(ctx->block_free.begin(), ctx->block_free.begin() + i);
+    std::vector<dpb_ctx::Block> kept;
+    kept.reserve(ctx->block_free.size());
+    for (const auto& b : ctx->block_free) {  // oldest first
+        const bool huge = b.bytes >= kBlockHuge;
+        const bool drop = huge ? (huge_bytes > keep_huge || huge_n > kBlockHugeMaxCount)
+                               : (small_bytes > keep_bytes || small_n > kBlockCacheMaxBlocks);
+        if (!drop) {
+            kept.push_back(b);
+            continue;
+        }
+        cudaFreeAsync(b.p, ctx->stream);
+        ctx->block_free_bytes -= b.bytes;
+        if (huge) {
+            huge_bytes -= b.bytes;
+            huge_n--;
+        } else {
+            small_bytes -= b.bytes;
+            small_n--;
+        }
+    }
+    ctx->block_free.swap(kept);
 }
 
 int device_alloc(dpb_ctx* ctx, size_t bytes, void** out) {
@@ -104,13 +135,13 @@ void device_free(dpb_ctx* ctx, void* p) {
     }
     const size_t bytes = it->second;
     ctx->block_live.erase(it);
-    if (bytes > block_cache_max_bytes() / 2) {  // one very large block would push everything else out
-        cudaFreeAsync(p, ctx->stream);
+    if (block_cache_max_bytes() == 0 || (bytes < kBlockHuge && bytes > block_cache_max_bytes() / 2)) {
+        cudaFreeAsync(p, ctx->stream);  // nothing is kept, or one block would push everything else out
         return;
     }
     ctx->block_free.push_back({p, bytes});
     ctx->block_free_bytes += bytes;
-    block_cache_release(ctx, block_cache_max_bytes());
+    block_cache_release(ctx, block_cache_max_bytes(), kBlockHugeMaxBytes);
 }
 
 int upload_small(dpb_ctx* ctx, void* dst, const void* src, size_t bytes) {
@@ -788,6 +819,95 @@ int dpb_mle_evaluate(dpb_ctx* ctx, const dpb_mle* mle, const void* point, uint32
     DPB_TRY(fix_common(ctx, mle, point, n, false, &res));
     int rc = dpb_mle_to_host(res, out, 1, DPB_FORM_NATIVE);
     dpb_mle_free(res);
+    return rc;
+}
+
+int dpb_mle_evaluate_many(dpb_ctx* ctx, dpb_mle* const* mles, uint32_t n, const void* point, uint32_t num_vars,
+                          void* out) {
+    if (!ctx || !mles || !out || (!point && num_vars)) return fail(DPB_EINVAL, "null argument");
+    if (n == 0) return DPB_OK;
+    if (num_vars > 40) return fail(DPB_EINVAL, "a point of %u coordinates", num_vars);
+    const bool gl = mles[0] && is_gl(mles[0]->dtype);
+    const size_t es = gl ? 16 : 32;
+    // per number of variables m: the eq table of the first m coordinates and prod_{j >= m} (1 - point[j])
+    std::vector<dpb_mle*> eq(num_vars + 1, nullptr);
+    auto free_eq = [&]() {
+        for (auto* m : eq) dpb_mle_free(m);
+    };
+    std::vector<EvalManySrc> src(n);
+    std::vector<uint8_t> scale((size_t)n * es);
+    for (uint32_t t = 0; t < n; t++) {
+        const dpb_mle* m = mles[t];
+        if (!m || m->ctx != ctx || !valid_dtype(m->dtype) || is_gl(m->dtype) != gl || m->len == 0 || (m->len & (m->len - 1)) ||
+            m->len > (1ull << num_vars)) {
+            free_eq();
+            return fail(DPB_EINVAL, "table %u is null, foreign, of another field, not a power of two or longer than 2^%u", t, num_vars);
+        }
+        uint32_t mv = 0;
+        while ((1ull << mv) < m->len) mv++;
+        if (!eq[mv]) {
+            const int rc = dpb_eq_table(ctx, gl ? DPB_GL_EXT : DPB_FR, point, mv, &eq[mv]);
+            if (rc != DPB_OK) {
+                free_eq();
+                return rc;
+            }
+        }
+        src[t].ptr = m->ptr;
+        src[t].eq = eq[mv]->ptr;
+        src[t].len = m->len;
+        src[t].dtype = m->dtype;
+        src[t].pad = 0;
+        if (gl) {
+            Gl2 sc = GlFam::one();
+            for (uint32_t j = mv; j < num_vars; j++) sc = GlFam::mul(sc, GlFam::sub(GlFam::one(), ((const Gl2*)point)[j]));
+            memcpy(scale.data() + (size_t)t * es, &sc, es);
+        } else {
+            Fr sc = FrFam::one();
+            for (uint32_t j = mv; j < num_vars; j++) sc = FrFam::mul(sc, FrFam::sub(FrFam::one(), ((const Fr*)point)[j]));
+            memcpy(scale.data() + (size_t)t * es, &sc, es);
+        }
+    }
+    uint64_t longest = 0;
+    for (const auto& t : src) longest = std::max(longest, t.len);
+    // enough blocks to fill the GPU a few times over, at most one slice per 256 entries of the longest table
+    uint32_t slices = (uint32_t)std::max<uint64_t>(1, std::min<uint64_t>((longest + kThreads - 1) / kThreads,
+                                                                         ((uint64_t)ctx->sm_count * 8 + n - 1) / n));
+    void *d_src = nullptr, *d_scale = nullptr, *d_partial = nullptr, *d_out = nullptr;
+    int rc = device_alloc(ctx, (size_t)n * sizeof(EvalManySrc), &d_src);
+    if (rc == DPB_OK) rc = device_alloc(ctx, (size_t)n * es, &d_scale);
+    if (rc == DPB_OK) rc = device_alloc(ctx, (size_t)n * slices * es, &d_partial);
+    if (rc == DPB_OK) rc = device_alloc(ctx, (size_t)n * es, &d_out);
+    if (rc == DPB_OK) rc = upload_small(ctx, d_src, src.data(), (size_t)n * sizeof(EvalManySrc));
+    if (rc == DPB_OK) rc = upload_small(ctx, d_scale, scale.data(), (size_t)n * es);
+    if (rc == DPB_OK) {
+        // the grid's second dimension holds at most 65535 blocks
+        for (uint32_t first = 0; first < n; first += 65535) {
+            const uint32_t cnt = std::min<uint32_t>(65535, n - first);
+            const dim3 grid(slices, cnt);
+            if (gl)
+                evaluate_many_kernel<GlFam><<<grid, kThreads, 0, ctx->stream>>>((const EvalManySrc*)d_src + first, slices,
+                                                                                 (Gl2*)d_partial + (size_t)first * slices);
+            else
+                evaluate_many_kernel<FrFam><<<grid, kThreads, 0, ctx->stream>>>((const EvalManySrc*)d_src + first, slices,
+                                                                                 (Fr*)d_partial + (size_t)first * slices);
+        }
+        const uint32_t blocks = (n + kThreads - 1) / kThreads;
+        if (gl)
+            evaluate_many_finish<GlFam><<<blocks, kThreads, 0, ctx->stream>>>((const Gl2*)d_partial, slices, (const Gl2*)d_scale, n,
+                                                                                (Gl2*)d_out);
+        else
+            evaluate_many_finish<FrFam><<<blocks, kThreads, 0, ctx->stream>>>((const Fr*)d_partial, slices, (const Fr*)d_scale, n,
+                                                                                (Fr*)d_out);
+        cudaError_t e = cudaGetLastError();
+        if (e == cudaSuccess) e = cudaMemcpyAsync(out, d_out, (size_t)n * es, cudaMemcpyDeviceToHost, ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess) rc = fail(DPB_ECUDA, "evaluate many: %s", cudaGetErrorString(e));
+    }
+    device_free(ctx, d_src);
+    device_free(ctx, d_scale);
+    device_free(ctx, d_partial);
+    device_free(ctx, d_out);
+    free_eq();
     return rc;
 }
 

@@ -1,7 +1,7 @@
 // Claim batching of the opening proof on the GPU, following the reference's
 // in-repo code step for step:
-//   ChunkedCommitment helpers, build_sumcheck_expression, identity_eval
-//                                        zkml/src/poly_commit/mod.rs:32-148, 184-192
+//   ChunkedCommitment helpers, identity_eval, and build_sumcheck_expression's polynomial (summed in a form
+//   that is linear-combined per claim first)   zkml/src/poly_commit/mod.rs:32-148, 184-192
 //   CommitmentProver::claims_batching_sumcheck and the random linear combination
 //   of the committed polynomials that CommitmentProver::prove builds before it
 //   calls the commitment scheme        zkml/src/poly_commit/prover.rs:113-131, 140-255
@@ -79,30 +79,6 @@ struct CommittedPoly {
     }
 };
 
-// mod.rs:96-148
-template <class F>
-Expression<F> build_sumcheck_expression(const std::vector<CommittedPoly<F>>& polys,
-                                        const std::vector<std::vector<std::vector<typename F::E>>>& coeffs) {
-    typedef Expression<F> X;
-    size_t eq_offset = 0;
-    for (const auto& p : polys) eq_offset += p.num_chunks();
-    X expr = X::Constant(F::zero());
-    size_t total_terms = 0, total_polys = 0;
-    for (size_t pi = 0; pi < polys.size(); pi++) {
-        for (size_t i = 0; i < coeffs[pi].size(); i++) {
-            if (coeffs[pi][i].size() != polys[pi].num_chunks()) throw Error(DPB_EINVAL, "wrong number of chunk challenges");
-            X inner = X::Constant(F::zero());
-            for (size_t c = 0; c < coeffs[pi][i].size(); c++)
-                inner = inner + X::Constant(coeffs[pi][i][c]) * X::WitIn((uint16_t)(total_polys + c));
-            expr = expr + X::Challenge(0, total_terms + i, F::one(), F::zero()) * inner *
-                              X::WitIn((uint16_t)(total_terms + i + eq_offset));
-        }
-        total_terms += coeffs[pi].size();
-        total_polys += polys[pi].num_chunks();
-    }
-    return expr;
-}
-
 template <class F>
 struct ClaimsBatchingProof {
     typedef typename F::E E;
@@ -154,7 +130,31 @@ ClaimsBatchingProof<F> claims_batching_sumcheck(dpb_ctx* ctx, const std::vector<
                         eq_polys.data()));
     for (auto* m : eq_polys) owned.push_back(m);
     owned.push_back(eq_owner);  // freed last
-    const Expression<F> expr = build_sumcheck_expression<F>(polys, coeffs);
+    // The expression (build_sumcheck_expression, mod.rs:96-148) is  sum_t gamma^t (sum_c coef_{t,c} chunk_c) eq_t
+    // over the claims t: LINEAR in the chunk tables.  The sumcheck therefore runs over one table per claim,
+    // L_t = sum_c coef_{t,c} chunk_c (the chunk itself when the polynomial has one chunk), instead of over every
+    // chunk: the same polynomial is summed, so the round messages are the same field elements, and the prover
+    // binds and stores 2 tables per claim instead of (chunks + 1).  What the proof hands on, every chunk at the
+    // sumcheck's point, comes from one pass over the chunks afterwards (dpb_mle_evaluate_many).
+    std::vector<dpb_mle*> term_tables;
+    for (size_t pi = 0; pi < polys.size(); pi++) {
+        const auto& p = polys[pi];
+        for (size_t i = 0; i < coeffs[pi].size(); i++) {
+            if (coeffs[pi][i].size() != p.num_chunks()) throw Error(DPB_EINVAL, "wrong number of chunk challenges");
+            if (p.num_chunks() == 1 && F::is_one(coeffs[pi][i][0])) {
+                term_tables.push_back(p.chunks[0]);
+                continue;
+            }
+            dpb_mle* l = nullptr;
+            check(dpb_linear_combination(ctx, p.chunks.data(), coeffs[pi][i].data(), (uint32_t)p.num_chunks(), &l));
+            owned.push_back(l);
+            term_tables.push_back(l);
+        }
+    }
+    typedef Expression<F> X;
+    X expr = X::Constant(F::zero());
+    for (size_t t = 0; t < total_claims; t++)
+        expr = expr + X::Challenge(0, t, F::one(), F::zero()) * X::WitIn((uint16_t)t) * X::WitIn((uint16_t)(total_claims + t));
     // every table enters as a zero-padded view of max_num_vars variables (prover.rs:214-226)
     std::vector<dpb_mle*> views;
     auto add_view = [&](dpb_mle* m) {
@@ -163,16 +163,17 @@ ClaimsBatchingProof<F> claims_batching_sumcheck(dpb_ctx* ctx, const std::vector<
         owned.push_back(v);
         views.push_back(v);
     };
-    for (auto* m : out.committed_polys) add_view(m);
+    for (auto* m : term_tables) add_view(m);
     for (auto* m : eq_polys) add_view(m);
     const E challenge = transcript.append_and_sample("model_batching");
     auto builder = dp_crypto::VirtualPolynomialsBuilder<F>::new_with_mles(1, (uint32_t)out.max_num_vars, views);
     auto vp = builder.to_virtual_polys({expr}, {challenge});
     auto res = dp_crypto::IOPProverState<F>::prove(ctx, vp, transcript);
-    const auto& finals = res.second.get_mle_flatten_final_evaluations();
-    out.sumcheck_evals.assign(finals.begin(), finals.begin() + total_chunks);
     out.sumcheck_point = res.second.collect_raw_challenges();
     out.sumcheck_proof = std::move(res.first);
+    out.sumcheck_evals.resize(total_chunks);
+    check(dpb_mle_evaluate_many(ctx, out.committed_polys.data(), (uint32_t)total_chunks, out.sumcheck_point.data(),
+                                (uint32_t)out.max_num_vars, out.sumcheck_evals.data()));
     return out;
 }
 

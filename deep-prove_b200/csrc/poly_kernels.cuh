@@ -132,6 +132,40 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
+// Many tables evaluated at one point: table t (2^m_t entries, any layout of its family) against the eq table of the
+// point's first m_t coordinates: partial[t * slices + s] = sum over slice s of table_t[x] * eq_{m_t}[x].
+struct EvalManySrc {
+    const void* ptr;
+    const void* eq;  // eq table over this table's variables (challenge elements)
+    uint64_t len;
+    int32_t dtype;
+    int32_t pad;
+};
+template <class F>
+__global__ void __launch_bounds__(kThreads)
+    evaluate_many_kernel(const EvalManySrc* __restrict__ src, uint32_t slices, typename F::E* __restrict__ partial) {
+    typedef typename F::E E;
+    const EvalManySrc t = src[blockIdx.y];
+    E acc[1] = {F::zero()};
+    const uint64_t stride = (uint64_t)slices * blockDim.x;
+    for (uint64_t x = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; x < t.len; x += stride)
+        acc[0] = F::add(acc[0], F::mul(F::load(t.ptr, t.dtype, x), ((const E*)t.eq)[x]));
+    block_sum<F, 1>(acc);
+    if (threadIdx.x == 0) partial[(size_t)blockIdx.y * slices + blockIdx.x] = acc[0];
+}
+// out[t] = scale[t] * sum_s partial[t * slices + s]
+template <class F>
+__global__ void __launch_bounds__(kThreads)
+    evaluate_many_finish(const typename F::E* __restrict__ partial, uint32_t slices, const typename F::E* __restrict__ scale,
+                         uint32_t n, typename F::E* __restrict__ out) {
+    typedef typename F::E E;
+    const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= n) return;
+    E acc = F::zero();
+    for (uint32_t s = 0; s < slices; s++) acc = F::add(acc, partial[(size_t)t * slices + s]);
+    out[t] = F::mul(acc, scale[t]);
+}
+
 // One source table of a linear combination.
 struct LinCombSrc {
     const void* ptr;

@@ -227,12 +227,13 @@ class PathWalk:
         share one point that gives the stacking coefficients, and the sumcheck runs over the contracted axis."""
         be, T, lg = self.be, self.T, ceil_log2
         lhs_dev, rhs_dev = be.tensor(lhs), be.tensor(rhs)  # resident before the clock starts
+        # the output claim's coordinates: stand-ins, drawn before the clock starts
+        lp = [be.squeeze(T, lg(d)) if k != AX_CONTRACTED else None for d, k in zip(lhs.shape, lhs_kinds)]
+        stacked = [p for p, k in zip(lp, lhs_kinds) if k == AX_STACKED]
+        rp = []
+        for d, k in zip(rhs.shape, rhs_kinds):
+            rp.append(stacked.pop(0) if k == AX_STACKED else be.squeeze(T, lg(d)) if k == AX_OUTER else None)
         with self.timer("einsum"):
-            lp = [be.squeeze(T, lg(d)) if k != AX_CONTRACTED else None for d, k in zip(lhs.shape, lhs_kinds)]
-            stacked = [p for p, k in zip(lp, lhs_kinds) if k == AX_STACKED]
-            rp = []
-            for d, k in zip(rhs.shape, rhs_kinds):
-                rp.append(stacked.pop(0) if k == AX_STACKED else be.squeeze(T, lg(d)) if k == AX_OUTER else None)
             payload = be.einsum_prove(T, lhs_dev, lhs.shape, lhs_kinds, lp, rhs_dev, rhs.shape, rhs_kinds, rp)
         self.rec.append((name, "einsum", payload))
 
@@ -293,9 +294,9 @@ class PathWalk:
                 tab = be.int_table(self.small(P))
                 extra_owner.append(tab)
                 mles.append(tab)
+        claim_point = be.squeeze(T, total)
+        logup_point = be.squeeze(T, n2d)
         with self.timer("lookup_linking"):
-            claim_point = be.squeeze(T, total)
-            logup_point = be.squeeze(T, n2d)
             payload = be.linking(T, variant, spec, out_min, out_max, tensor.shape, mles, claim_point, logup_point, weight)
         self.rec.append((name + ".linking", "linking", payload))
         # the witness columns are committed polynomials: they are opened at the end
@@ -465,14 +466,15 @@ class PathWalk:
         """CommitmentProver::claims_batching_sumcheck + the linear combination over every committed polynomial
         (zkml/src/poly_commit/prover.rs:113-131, 140-255), one claim per polynomial."""
         be, T = self.be, self.T
+        # the claims themselves stand in for what the layers' proofs hand on: drawn before the clock starts
+        polys = []
+        for name, tab, entries in self.committed:
+            nv = ceil_log2(entries)
+            n_chunks = 1 << max(nv - self.chunk_log2, 0)
+            point = be.squeeze(T, nv)
+            ev = be.squeeze(T, 1)[0]
+            polys.append((be.chunks(tab, n_chunks), [(point, ev)]))
         with self.timer("claim_batching"):
-            polys = []
-            for name, tab, entries in self.committed:
-                nv = ceil_log2(entries)
-                n_chunks = 1 << max(nv - self.chunk_log2, 0)
-                point = be.squeeze(T, nv)
-                ev = be.squeeze(T, 1)[0]
-                polys.append((be.chunks(tab, n_chunks), [(point, ev)]))
             self.rec.append(("claim_batching", "claim_batching", be.claims_batching(T, polys)))
 
     def finish(self):

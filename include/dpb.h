@@ -87,8 +87,8 @@ typedef struct dpb_term {
  * usable GPU is present: there is no CPU fallback.
  * Device memory: tables and scratch come from the device's default stream-ordered pool (release threshold
  * raised so that the pool keeps what it has grown to); blocks of 256 KiB and more that the library frees are kept
- * per context, up to 8 GiB (environment variable DPB_BLOCK_CACHE_GB; 0 keeps nothing), and handed to the next
- * request of exactly that size; they go back to the pool when an allocation fails, and at dpb_shutdown. */
+ * per context, up to 8 GiB plus the last three blocks of 4 GiB and more (environment variable DPB_BLOCK_CACHE_GB
+ * sets the 8; 0 keeps nothing), and handed to the next request of exactly that size; they go back to the pool when an allocation fails, and at dpb_shutdown. */
 int dpb_init(int device, dpb_ctx** out);
 /* Gives the device memory the context keeps for reuse (freed blocks, the last sumcheck's block) back to the pool and
  * the pool's unused memory back to the device; waits for the context's stream.  For a process that moves on to a
@@ -243,6 +243,13 @@ int dpb_fix_low(dpb_ctx* ctx, const dpb_mle* mle, const void* point, uint32_t k,
 /* Full evaluation at an n-variable point (DensePolynomial::evaluate,
  * zkml/src/iop/mod.rs:196-207).  Result: one challenge element on the host. */
 int dpb_mle_evaluate(dpb_ctx* ctx, const dpb_mle* mle, const void* point, uint32_t n, void* out);
+/* n tables at ONE point of num_vars coordinates, in one pass over their entries: table t of 2^m_t <= 2^num_vars
+ * entries counts as zero-padded (dpb_mle_zero_padded's convention: a function of the FIRST m_t variables times
+ * (1 - x_j) for every further one), so out[t] = sum_x table_t[x] * eq(point[..m_t], x) * prod_{j >= m_t} (1 - point[j]).
+ * What the claim batching hands on as the committed chunks' evaluations (zkml/src/poly_commit/prover.rs:246-251).
+ * out: n challenge elements on the host. */
+int dpb_mle_evaluate_many(dpb_ctx* ctx, dpb_mle* const* mles, uint32_t n, const void* point, uint32_t num_vars,
+                          void* out);
 
 /* ---- einsum axis fixing --------------------------------------------------- */
 #define DPB_AXIS_CONTRACTED 0 /* summed over by the sumcheck: kept */

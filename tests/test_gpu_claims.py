@@ -166,3 +166,23 @@ def test_claims_batching_argument_errors(dpb, ctx):
         prover.claims_batching_prove(ctx, tr, [prover.CommittedPoly([a, a, a], [(pt, ev)])])
     assert e.value.code == dpb.EINVAL
     tr.free()
+
+
+@pytest.mark.parametrize("F", FIELDS)
+def test_evaluate_many_zero_padded(dpb, ctx, F):
+    """dpb_mle_evaluate_many: tables of several sizes and layouts (field, base, integers) at one point, each as its
+    zero-padded extension (the convention of dpb_mle_zero_padded), against the oracle."""
+    rng = np.random.default_rng(91)
+    n = 9
+    point = [F.random_scalar(rng) for _ in range(n)]
+    tabs, mles = [], []
+    for m in (9, 9, 6, 3, 0):
+        ints = rng.integers(-(1 << 40), 1 << 40, size=1 << m, dtype=np.int64)
+        tabs.append(F.table_from_i64(ints))
+        mles.append(ctx.upload_ints(ints, dpb.FR_I64 if F is orc.FrField else dpb.GL_I64))
+        t = F.random_table_fast(rng, 1 << m) if F is orc.FrField else F.random_table(rng, 1 << m)
+        tabs.append(t)
+        mles.append(upload(dpb, ctx, F, t))
+    got = orc.array_to_scalars(F, dpb.evaluate_many(ctx, mles, orc.scalars_to_array(F, point)))
+    want = [orc.evaluate(F, orc.zero_pad_table(F, t, n), point) for t in tabs]
+    assert got == want
