@@ -40,108 +40,170 @@ int fail(int code, const char* fmt, ...) {
     return code;
 }
 
-constexpr size_t kBlockCacheMin = 256 * 1024;            // smaller requests go straight to the allocator
-constexpr size_t kBlockCacheMaxBlocks = 512;
-// freed bytes kept per context: 8 GiB (DPB_BLOCK_CACHE_GB overrides; 0 keeps nothing).  Measured on the model walks:
-// without it the fraction trees of a GPT-2-sized proof cost 1.6 s in the allocator, with 8 GiB 0.03 s; with 64 GiB
-// the walks that fill most of the device's memory slow down again, the kept blocks standing in the pool's way.
-static size_t block_cache_max_bytes() {
-    static const size_t v = [] {
-        const char* e = getenv("DPB_BLOCK_CACHE_GB");
-        return (size_t)(e ? strtoull(e, nullptr, 10) : 8) << 30;
+constexpr size_t kArenaBytes = (size_t)8 << 30;   // what the library takes from the pool at a time
+constexpr size_t kBigBlock = (size_t)2 << 30;     // requests of this size and more get a block of their own
+constexpr size_t kBigKeepCount = 16;              // freed big blocks kept for a request of the same size
+constexpr size_t kBigKeepBytes = (size_t)96 << 30;
+constexpr size_t kAllocAlign = 256;
+
+// DPB_ARENA=0: every request goes to the stream-ordered allocator itself (for comparison; see the bench notes)
+static bool arena_enabled() {
+    static const bool v = [] {
+        const char* e = getenv("DPB_ARENA");
+        return !(e && e[0] == '0');
     }();
     return v;
 }
 
-// Two classes of kept blocks.  Ordinary ones (fraction trees, columns, eq tables: up to 4 GiB each) share the
-// budget above.  Huge ones (the fold buffers and eq tables of a claim batching over a whole model: tens of GB in one
-// block, 170 ms in the allocator each time) are few: the last three, up to 96 GiB together.
-constexpr size_t kBlockHuge = (size_t)4 << 30;
-constexpr size_t kBlockHugeMaxBytes = (size_t)96 << 30;
-constexpr size_t kBlockHugeMaxCount = 3;
+// gives unused memory back to the pool: arenas nothing lives in, and the kept big blocks
+static void arena_release_unused(dpb_ctx* ctx) {
+    for (auto& a : ctx->arenas) {
+        if (a.base && a.used == 0) {
+            cudaFreeAsync(a.base, ctx->stream);
+            a.base = nullptr;
+            a.bytes = 0;
+            a.free_ranges.clear();
+        }
+    }
+    for (const auto& b : ctx->big_free) cudaFreeAsync(b.p, ctx->stream);
+    ctx->big_free.clear();
+}
 
-// frees the oldest kept blocks until the ordinary ones hold at most keep_bytes and the huge ones at most keep_huge
-static void block_cache_release(dpb_ctx* ctx, size_t keep_bytes, size_t keep_huge = 0) {
-    size_t small_bytes = 0, huge_bytes = 0, small_n = 0, huge_n = 0;
-    for (const auto& b : ctx->block_free) {
-        if (b.bytes >= kBlockHuge) {
-            huge_bytes += b.bytes;
-            huge_n++;
-        } else {
-            small_bytes += b.bytes;
-            small_n++;
-        }
+static cudaError_t pool_alloc(dpb_ctx* ctx, size_t bytes, void** out) {
+    cudaError_t e = cudaMallocAsync(out, bytes, ctx->stream);
+    if (e == cudaErrorMemoryAllocation) {
+        // what the library keeps may be what stands in the way: give it back and ask again
+        cudaGetLastError();
+        arena_release_unused(ctx);
+        e = cudaMallocAsync(out, bytes, ctx->stream);
     }
-    std::vector<dpb_ctx::Block> kept;
-    kept.reserve(ctx->block_free.size());
-    for (const auto& b : ctx->block_free) {  // oldest first
-        const bool huge = b.bytes >= kBlockHuge;
-        const bool drop = huge ? (huge_bytes > keep_huge || huge_n > kBlockHugeMaxCount)
-                               : (small_bytes > keep_bytes || small_n > kBlockCacheMaxBlocks);
-        if (!drop) {
-            kept.push_back(b);
-            continue;
-        }
-        cudaFreeAsync(b.p, ctx->stream);
-        ctx->block_free_bytes -= b.bytes;
-        if (huge) {
-            huge_bytes -= b.bytes;
-            huge_n--;
-        } else {
-            small_bytes -= b.bytes;
-            small_n--;
-        }
-    }
-    ctx->block_free.swap(kept);
+    if (e != cudaSuccess) cudaGetLastError();
+    return e;
 }
 
 int device_alloc(dpb_ctx* ctx, size_t bytes, void** out) {
     if (bytes == 0) bytes = 16;
-    if (bytes < kBlockCacheMin) {
-        DPB_CUDA(cudaMallocAsync(out, bytes, ctx->stream));
-        return DPB_OK;
-    }
+    bytes = (bytes + kAllocAlign - 1) & ~(kAllocAlign - 1);
     std::lock_guard<std::mutex> lock(ctx->block_mu);
-    for (size_t i = ctx->block_free.size(); i-- > 0;) {  // newest first
-        if (ctx->block_free[i].bytes != bytes) continue;
-        *out = ctx->block_free[i].p;
-        ctx->block_free_bytes -= bytes;
-        ctx->block_free.erase(ctx->block_free.begin() + i);
-        ctx->block_live[*out] = bytes;
+    if (!arena_enabled()) {
+        const cudaError_t e = pool_alloc(ctx, bytes, out);
+        if (e != cudaSuccess)
+            return fail(e == cudaErrorMemoryAllocation ? DPB_ENOMEM : DPB_ECUDA, "device allocation of %zu bytes: %s", bytes,
+                        cudaGetErrorString(e));
         return DPB_OK;
     }
-    cudaError_t e = cudaMallocAsync(out, bytes, ctx->stream);
-    if (e == cudaErrorMemoryAllocation && !ctx->block_free.empty()) {
-        // the kept blocks are what stands in the way: give them back and ask again
-        cudaGetLastError();
-        block_cache_release(ctx, 0);
-        e = cudaMallocAsync(out, bytes, ctx->stream);
+    if (bytes >= kBigBlock) {
+        for (size_t i = ctx->big_free.size(); i-- > 0;) {  // newest first
+            if (ctx->big_free[i].bytes != bytes) continue;
+            *out = ctx->big_free[i].p;
+            ctx->big_free.erase(ctx->big_free.begin() + i);
+            ctx->block_live[*out] = {-1, bytes};
+            return DPB_OK;
+        }
+        const cudaError_t e = pool_alloc(ctx, bytes, out);
+        if (e != cudaSuccess)
+            return fail(e == cudaErrorMemoryAllocation ? DPB_ENOMEM : DPB_ECUDA, "device allocation of %zu bytes: %s", bytes,
+                        cudaGetErrorString(e));
+        ctx->block_live[*out] = {-1, bytes};
+        return DPB_OK;
     }
-    if (e != cudaSuccess) {
-        cudaGetLastError();
-        return fail(e == cudaErrorMemoryAllocation ? DPB_ENOMEM : DPB_ECUDA, "device allocation of %zu bytes: %s", bytes,
-                    cudaGetErrorString(e));
+    // first fit by address over the arenas
+    for (int pass = 0; pass < 2; pass++) {
+        for (size_t ai = 0; ai < ctx->arenas.size(); ai++) {
+            auto& a = ctx->arenas[ai];
+            if (!a.base || a.bytes - a.used < bytes) continue;
+            for (auto it = a.free_ranges.begin(); it != a.free_ranges.end(); ++it) {
+                if (it->second < bytes) continue;
+                const size_t off = it->first, len = it->second;
+                a.free_ranges.erase(it);
+                if (len > bytes) a.free_ranges[off + bytes] = len - bytes;
+                a.used += bytes;
+                *out = a.base + off;
+                ctx->block_live[*out] = {(int32_t)ai, bytes};
+                return DPB_OK;
+            }
+        }
+        if (pass == 1) break;
+        // a new arena: 8 GiB, less when the device cannot give that much (never less than the request)
+        size_t want = kArenaBytes;
+        void* base = nullptr;
+        cudaError_t e = cudaErrorMemoryAllocation;
+        while (want >= bytes) {
+            e = cudaMallocAsync(&base, want, ctx->stream);
+            if (e == cudaSuccess) break;
+            cudaGetLastError();
+            if (e != cudaErrorMemoryAllocation) break;
+            if (want == bytes) break;
+            want = std::max(bytes, want / 2);
+        }
+        if (e != cudaSuccess) {
+            arena_release_unused(ctx);
+            want = std::max(bytes, (size_t)256 << 20);
+            e = cudaMallocAsync(&base, want, ctx->stream);
+            if (e != cudaSuccess) {
+                cudaGetLastError();
+                return fail(e == cudaErrorMemoryAllocation ? DPB_ENOMEM : DPB_ECUDA, "device allocation of %zu bytes: %s", bytes,
+                            cudaGetErrorString(e));
+            }
+        }
+        dpb_ctx::Arena* slot = nullptr;
+        for (auto& a : ctx->arenas)
+            if (!a.base) {
+                slot = &a;
+                break;
+            }
+        if (!slot) {
+            ctx->arenas.emplace_back();
+            slot = &ctx->arenas.back();
+        }
+        slot->base = (char*)base;
+        slot->bytes = want;
+        slot->used = 0;
+        slot->free_ranges.clear();
+        slot->free_ranges[0] = want;
     }
-    ctx->block_live[*out] = bytes;
-    return DPB_OK;
+    return fail(DPB_ENOMEM, "device allocation of %zu bytes: no arena could hold it", bytes);
 }
+
 void device_free(dpb_ctx* ctx, void* p) {
     if (!p) return;
     std::lock_guard<std::mutex> lock(ctx->block_mu);
     auto it = ctx->block_live.find(p);
     if (it == ctx->block_live.end()) {
-        cudaFreeAsync(p, ctx->stream);
+        cudaFreeAsync(p, ctx->stream);  // not from the arenas (DPB_ARENA=0)
         return;
     }
-    const size_t bytes = it->second;
+    const dpb_ctx::Live live = it->second;
     ctx->block_live.erase(it);
-    if (block_cache_max_bytes() == 0 || (bytes < kBlockHuge && bytes > block_cache_max_bytes() / 2)) {
-        cudaFreeAsync(p, ctx->stream);  // nothing is kept, or one block would push everything else out
+    if (live.arena < 0) {
+        ctx->big_free.push_back({p, live.bytes});
+        size_t total = 0;
+        for (const auto& b : ctx->big_free) total += b.bytes;
+        while (ctx->big_free.size() > kBigKeepCount || total > kBigKeepBytes) {
+            cudaFreeAsync(ctx->big_free.front().p, ctx->stream);
+            total -= ctx->big_free.front().bytes;
+            ctx->big_free.erase(ctx->big_free.begin());
+        }
         return;
     }
-    ctx->block_free.push_back({p, bytes});
-    ctx->block_free_bytes += bytes;
-    block_cache_release(ctx, block_cache_max_bytes(), kBlockHugeMaxBytes);
+    auto& a = ctx->arenas[live.arena];
+    size_t off = (size_t)((char*)p - a.base), len = live.bytes;
+    a.used -= len;
+    // merge with the free range after and the one before
+    auto next = a.free_ranges.lower_bound(off);
+    if (next != a.free_ranges.end() && next->first == off + len) {
+        len += next->second;
+        next = a.free_ranges.erase(next);
+    }
+    if (next != a.free_ranges.begin()) {
+        auto prev = std::prev(next);
+        if (prev->first + prev->second == off) {
+            off = prev->first;
+            len += prev->second;
+            a.free_ranges.erase(prev);
+        }
+    }
+    a.free_ranges[off] = len;
 }
 
 int upload_small(dpb_ctx* ctx, void* dst, const void* src, size_t bytes) {
@@ -449,8 +511,16 @@ void dpb_shutdown(dpb_ctx* ctx) {
     cudaSetDevice(ctx->device);
     if (ctx->slab_cache) device_free(ctx, ctx->slab_cache);
     {
+        // tables the caller never freed die with the context
         std::lock_guard<std::mutex> lock(ctx->block_mu);
-        block_cache_release(ctx, 0);
+        for (auto& a : ctx->arenas)
+            if (a.base) cudaFreeAsync(a.base, ctx->stream);
+        ctx->arenas.clear();
+        for (const auto& kv : ctx->block_live)
+            if (kv.second.arena < 0) cudaFreeAsync(kv.first, ctx->stream);
+        ctx->block_live.clear();
+        for (const auto& b : ctx->big_free) cudaFreeAsync(b.p, ctx->stream);
+        ctx->big_free.clear();
     }
     cudaStreamSynchronize(ctx->stream);
     cudaStreamSynchronize(ctx->tail_stream);
@@ -473,18 +543,14 @@ void dpb_shutdown(dpb_ctx* ctx) {
 int dpb_trim(dpb_ctx* ctx) {
     if (!ctx) return fail(DPB_EINVAL, "null context");
     DPB_CUDA(cudaSetDevice(ctx->device));
-    {
-        std::lock_guard<std::mutex> lock(ctx->block_mu);
-        block_cache_release(ctx, 0);
-    }
     if (ctx->slab_cache && !ctx->slab_cache_busy) {
-        cudaFreeAsync(ctx->slab_cache, ctx->stream);
-        {
-            std::lock_guard<std::mutex> lock(ctx->block_mu);
-            ctx->block_live.erase(ctx->slab_cache);
-        }
+        device_free(ctx, ctx->slab_cache);
         ctx->slab_cache = nullptr;
         ctx->slab_cache_bytes = 0;
+    }
+    {
+        std::lock_guard<std::mutex> lock(ctx->block_mu);
+        arena_release_unused(ctx);
     }
     DPB_CUDA(cudaStreamSynchronize(ctx->stream));
     cudaMemPool_t pool;

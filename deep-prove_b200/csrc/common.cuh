@@ -8,6 +8,7 @@
 #include <cstdio>
 #include <cstring>
 #include <string>
+#include <map>
 #include <mutex>
 #include <unordered_map>
 #include <vector>
@@ -128,19 +129,30 @@ struct dpb_ctx {
     cudaEvent_t up_ev[kStageSlots] = {};
     bool up_used[kStageSlots] = {};
     int up_next = 0;
-    // Freed blocks of 256 KiB and more, kept by exact size for the next request of that size (device_alloc /
-    // device_free): a proof asks for the same few sizes layer after layer (fraction trees, witness columns, eq
-    // tables), and the stream-ordered allocator was measured to take milliseconds per large block once its pool
-    // is fragmented by earlier work of the process.  Every allocation of a context is used on its one stream, so
-    // handing a freed block to the next request is as safe as the allocator's own stream-ordered reuse.
+    // Device memory of the context (device_alloc / device_free, api_core.cu).  Requests below 2 GiB are cut out of
+    // arenas of 8 GiB that the library takes from the stream-ordered pool and keeps (first fit by address, freed
+    // ranges merged with their neighbours); larger requests get a block of their own, and the last of those (up to
+    // 16 blocks, 96 GiB) are kept for a request of the same size.  Why: a proof asks for the same few hundred sizes layer after layer,
+    // and the stream-ordered allocator was measured to take milliseconds per block of 128 MB..1 GiB in that pattern
+    // (1.6 s of a 3.3 s GPT-2 walk), differently from run to run.  Every allocation of a context is used on its one
+    // stream, so handing a freed range to the next request is as safe as the pool's own stream-ordered reuse.
+    struct Arena {
+        char* base = nullptr;  // nullptr: released
+        size_t bytes = 0, used = 0;
+        std::map<size_t, size_t> free_ranges;  // offset -> length
+    };
+    struct Live {
+        int32_t arena;  // index into arenas, or -1: a block of its own
+        size_t bytes;
+    };
     struct Block {
         void* p;
         size_t bytes;
     };
     std::mutex block_mu;
-    std::unordered_map<void*, size_t> block_live;  // live large allocations -> size
-    std::vector<Block> block_free;                  // oldest first
-    size_t block_free_bytes = 0;
+    std::vector<Arena> arenas;
+    std::unordered_map<void*, Live> block_live;
+    std::vector<Block> big_free;  // kept blocks of 2 GiB and more, oldest first
     // the block of device memory the last sumcheck used, kept for the next one (dpb_sumcheck_begin)
     void* slab_cache = nullptr;
     size_t slab_cache_bytes = 0;

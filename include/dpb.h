@@ -85,10 +85,11 @@ typedef struct dpb_term {
 /* ---- context ----------------------------------------------------------- */
 /* Creates a context on CUDA device `device`.  Fails with DPB_ECUDA when no
  * usable GPU is present: there is no CPU fallback.
- * Device memory: tables and scratch come from the device's default stream-ordered pool (release threshold
- * raised so that the pool keeps what it has grown to); blocks of 256 KiB and more that the library frees are kept
- * per context, up to 8 GiB plus the last three blocks of 4 GiB and more (environment variable DPB_BLOCK_CACHE_GB
- * sets the 8; 0 keeps nothing), and handed to the next request of exactly that size; they go back to the pool when an allocation fails, and at dpb_shutdown. */
+ * Device memory: tables and scratch are cut out of arenas of 8 GiB that the context takes from the device's
+ * default stream-ordered pool and keeps (requests of 2 GiB and more get a block of their own; the last such blocks,
+ * up to 16 and 96 GiB, are kept for a request of the same size).  Unused arenas and kept blocks go back to the pool when an
+ * allocation fails, on dpb_trim and at dpb_shutdown.  The environment variable DPB_ARENA=0 sends every request to
+ * the pool instead. */
 int dpb_init(int device, dpb_ctx** out);
 /* Gives the device memory the context keeps for reuse (freed blocks, the last sumcheck's block) back to the pool and
  * the pool's unused memory back to the device; waits for the context's stream.  For a process that moves on to a
