@@ -524,6 +524,14 @@ void dpb_shutdown(dpb_ctx* ctx) {
     }
     cudaStreamSynchronize(ctx->stream);
     cudaStreamSynchronize(ctx->tail_stream);
+    for (int i = 0; i < dpb_ctx::kMsmStreams; i++)
+        if (ctx->msm_stream[i]) {
+            cudaStreamSynchronize(ctx->msm_stream[i]);
+            cudaStreamDestroy(ctx->msm_stream[i]);
+        }
+    for (int i = 0; i <= dpb_ctx::kMsmStreams; i++)
+        if (ctx->msm_ev[i]) cudaEventDestroy(ctx->msm_ev[i]);
+    if (ctx->msm_host) cudaFreeHost(ctx->msm_host);
     cudaStreamDestroy(ctx->tail_stream);
     cudaEventDestroy(ctx->tail_ev[0]);
     cudaEventDestroy(ctx->tail_ev[1]);

@@ -21,6 +21,7 @@
 // columns costs a fraction of a commit to full-width scalars.
 #include <vector>
 
+#include "../../include/dpb_pcs.h"
 #include "common.cuh"
 #include "g1_bn254.cuh"
 
@@ -398,6 +399,128 @@ static uint32_t msm_window_bits(uint64_t n) {
     return 8;
 }
 
+constexpr uint32_t kMsmGroup = 16;               // commitments of a batch in flight together
+constexpr size_t kMsmHostBytes = 1 << 20;         // pinned staging for their window sums
+
+// One commitment: its layout in one block of device memory [counts | offsets | cursor | heavy count | items |
+// heavy list | scan tiles | buckets | window sums | heavy chunk table | heavy chunk sums].
+struct MsmJob {
+    uint64_t n = 0;
+    uint32_t c = 0, windows = 0, blocks_per_window = 0, n_tiles = 0;
+    size_t n_keys = 0, n_partials = 0, host_off = 0;
+    uint64_t max_heavy = 0, max_chunks = 0;
+    size_t o_counts = 0, o_offsets = 0, o_cursor = 0, o_heavy_count = 0, o_items = 0, o_heavy = 0, o_tiles = 0, o_buckets = 0,
+           o_part = 0, o_chunk_first = 0, o_chunk_sums = 0;
+    void* slab = nullptr;
+};
+
+static int msm_plan(dpb_ctx* ctx, const dpb_g1_bases* bases, const dpb_mle* scalars, MsmJob& job) {
+    if (scalars->dtype != DPB_FR && scalars->dtype != DPB_FR_I32 && scalars->dtype != DPB_FR_I64)
+        return fail(DPB_EINVAL, "scalars must be a BN254 table (DPB_FR, DPB_FR_I32 or DPB_FR_I64), not dtype %d", scalars->dtype);
+    const uint64_t n = scalars->len;
+    if (n > bases->n)
+        return fail(DPB_EINVAL, "%llu scalars but only %llu points", (unsigned long long)n, (unsigned long long)bases->n);
+    job.n = n;
+    job.c = msm_window_bits(n);
+    const uint32_t scalar_bits = scalars->dtype == DPB_FR ? 254 : scalars->dtype == DPB_FR_I32 ? 32 : 64;
+    job.windows = (scalar_bits + job.c - 1) / job.c;
+    job.n_keys = (size_t)job.windows << job.c;
+    const uint32_t runs = (uint32_t)(((1ull << job.c) + kMsmRun - 1) / kMsmRun);
+    job.blocks_per_window = (runs + kMsmReduceThreads - 1) / kMsmReduceThreads;
+    job.n_partials = (size_t)job.windows * job.blocks_per_window;
+    job.n_tiles = (uint32_t)((job.n_keys + kScanTile - 1) / kScanTile);
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        const size_t o = off;
+        off = (off + bytes + 255) & ~(size_t)255;
+        return o;
+    };
+    job.o_counts = take(job.n_keys * 4);
+    job.o_offsets = take(job.n_keys * 4);
+    job.o_cursor = take(job.n_keys * 4);
+    job.o_heavy_count = take(256);
+    job.o_items = take((size_t)n * job.windows * 4);
+    job.o_heavy = take(job.n_keys * 4);
+    job.o_tiles = take((size_t)job.n_tiles * 4);
+    job.o_buckets = take(job.n_keys * sizeof(G1Jac));
+    job.o_part = take(job.n_partials * sizeof(G1Jac));
+    // heavy buckets: at most n * windows / kMsmHeavy of them, cut into at most that many + n * windows / kHeavyChunk chunks
+    job.max_heavy = (uint64_t)n * job.windows / kMsmHeavy + 1;
+    if (job.max_heavy > job.n_keys) job.max_heavy = job.n_keys;
+    job.max_chunks = job.max_heavy + (uint64_t)n * job.windows / kHeavyChunk + 1;
+    job.o_chunk_first = take((job.max_heavy + 1) * 4);
+    job.o_chunk_sums = take(job.max_chunks * sizeof(G1Jac));
+    return device_alloc(ctx, off, &job.slab);
+}
+
+// every kernel of one commitment and the copy of its window sums to `h_part` (pinned), on stream `st`
+static cudaError_t msm_launch(dpb_ctx* ctx, const dpb_g1_bases* bases, const dpb_mle* scalars, const MsmJob& job,
+                              cudaStream_t st, G1Jac* h_part) {
+    char* base = (char*)job.slab;
+    uint32_t* counts = (uint32_t*)(base + job.o_counts);
+    uint32_t* offsets = (uint32_t*)(base + job.o_offsets);
+    uint32_t* cursor = (uint32_t*)(base + job.o_cursor);
+    uint32_t* items = (uint32_t*)(base + job.o_items);
+    uint32_t* heavy_list = (uint32_t*)(base + job.o_heavy);
+    uint32_t* heavy_count = (uint32_t*)(base + job.o_heavy_count);
+    uint32_t* tile_sums = (uint32_t*)(base + job.o_tiles);
+    uint32_t* chunk_first = (uint32_t*)(base + job.o_chunk_first);
+    G1Jac* chunk_sums = (G1Jac*)(base + job.o_chunk_sums);
+    G1Jac* buckets = (G1Jac*)(base + job.o_buckets);
+    G1Jac* partials = (G1Jac*)(base + job.o_part);
+    MsmScalars s;
+    s.ptr = scalars->ptr;
+    s.dtype = scalars->dtype;
+    const uint64_t n = job.n;
+    const uint32_t c = job.c, windows = job.windows;
+    const size_t n_keys = job.n_keys;
+    cudaError_t e = cudaMemsetAsync(counts, 0, job.o_items - job.o_counts, st);  // counts, offsets, cursor, heavy count
+    if (e != cudaSuccess) return e;
+    msm_count<<<grid_for(ctx, n), kThreads, 0, st>>>(s, n, c, windows, counts);
+    msm_scan_tile_sums<<<job.n_tiles, kScanThreads, 0, st>>>(counts, n_keys, tile_sums);
+    msm_scan_tiles<<<1, 1024, 0, st>>>(tile_sums, job.n_tiles);
+    msm_scan_in_tiles<<<job.n_tiles, kScanThreads, 0, st>>>(counts, tile_sums, n_keys, offsets);
+    msm_scatter<<<grid_for(ctx, n), kThreads, 0, st>>>(s, n, c, windows, offsets, cursor, items);
+    msm_buckets<<<(uint32_t)((n_keys + kThreads - 1) / kThreads), kThreads, 0, st>>>(
+        bases->dev, offsets, counts, items, n_keys, buckets, heavy_list, heavy_count);
+    const uint32_t cap = (uint32_t)ctx->sm_count * 16;  // idle blocks leave at once
+    msm_heavy_plan<<<1, 1024, 0, st>>>(counts, heavy_list, heavy_count, chunk_first);
+    msm_heavy_chunks<<<(uint32_t)(job.max_chunks < cap ? job.max_chunks : cap), kMsmReduceThreads, 0, st>>>(
+        bases->dev, offsets, counts, items, heavy_list, heavy_count, chunk_first, chunk_sums);
+    msm_heavy_combine<<<(uint32_t)(job.max_heavy < cap ? job.max_heavy : cap), kMsmReduceThreads, 0, st>>>(
+        heavy_list, heavy_count, chunk_first, chunk_sums, buckets);
+    msm_reduce<<<(uint32_t)job.n_partials, kMsmReduceThreads, 0, st>>>(buckets, c, job.blocks_per_window, partials);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    return cudaMemcpyAsync(h_part, partials, job.n_partials * sizeof(G1Jac), cudaMemcpyDeviceToHost, st);
+}
+
+// host: windows from the top, total = 2^c * total + window sum; one inversion for the affine result
+static void msm_finish(const MsmJob& job, const G1Jac* h_part, void* out_affine_xy) {
+    G1Jac total = g1_infinity();
+    for (uint32_t w = job.windows; w-- > 0;) {
+        for (uint32_t d = 0; d < job.c; d++) total = g1_double(total);
+        for (uint32_t k = 0; k < job.blocks_per_window; k++)
+            total = g1_add(total, h_part[(size_t)w * job.blocks_per_window + k]);
+    }
+    const G1Affine a = g1_to_affine(total);
+    Fq xy[2];
+    if (g1_affine_is_infinity(a)) {
+        xy[0] = xy[1] = fq_zero();
+    } else {
+        xy[0] = fq_from_mont(a.x);
+        xy[1] = fq_from_mont(a.y);
+    }
+    memcpy(out_affine_xy, xy, sizeof xy);
+}
+
+static int msm_side_streams(dpb_ctx* ctx) {
+    if (ctx->msm_stream[0]) return DPB_OK;
+    for (int q = 0; q < dpb_ctx::kMsmStreams; q++) DPB_CUDA(cudaStreamCreateWithFlags(&ctx->msm_stream[q], cudaStreamNonBlocking));
+    for (int q = 0; q <= dpb_ctx::kMsmStreams; q++) DPB_CUDA(cudaEventCreateWithFlags(&ctx->msm_ev[q], cudaEventDisableTiming));
+    return DPB_OK;
+}
+
 }  // namespace dpb
 
 using namespace dpb;
@@ -480,105 +603,63 @@ void dpb_g1_bases_free(dpb_g1_bases* b) {
 }
 
 int dpb_msm_g1(dpb_ctx* ctx, const dpb_g1_bases* bases, const dpb_mle* scalars, void* out_affine_xy) {
-    if (!ctx || !bases || !scalars || !out_affine_xy) return fail(DPB_EINVAL, "null argument");
-    if (bases->ctx != ctx || scalars->ctx != ctx) return fail(DPB_EINVAL, "bases or scalars belong to another context");
-    if (scalars->dtype != DPB_FR && scalars->dtype != DPB_FR_I32 && scalars->dtype != DPB_FR_I64)
-        return fail(DPB_EINVAL, "scalars must be a BN254 table (DPB_FR, DPB_FR_I32 or DPB_FR_I64), not dtype %d", scalars->dtype);
-    const uint64_t n = scalars->len;
-    if (n > bases->n)
-        return fail(DPB_EINVAL, "%llu scalars but only %llu points", (unsigned long long)n, (unsigned long long)bases->n);
-    const uint32_t c = msm_window_bits(n);
-    const uint32_t scalar_bits = scalars->dtype == DPB_FR ? 254 : scalars->dtype == DPB_FR_I32 ? 32 : 64;
-    const uint32_t windows = (scalar_bits + c - 1) / c;
-    const size_t n_keys = (size_t)windows << c;
-    const uint32_t runs = (uint32_t)(((1ull << c) + kMsmRun - 1) / kMsmRun);
-    const uint32_t blocks_per_window = (runs + kMsmReduceThreads - 1) / kMsmReduceThreads;
-    const size_t n_partials = (size_t)windows * blocks_per_window;
-    // one block of device memory: [counts | offsets | cursor | items | buckets | partials]
-    size_t off = 0;
-    auto take = [&](size_t bytes) {
-        const size_t o = off;
-        off = (off + bytes + 255) & ~(size_t)255;
-        return o;
-    };
-    const size_t o_counts = take(n_keys * 4), o_offsets = take(n_keys * 4), o_cursor = take(n_keys * 4),
-                 o_heavy_count = take(256), o_items = take((size_t)n * windows * 4), o_heavy = take(n_keys * 4),
-                 o_tiles = take(((n_keys + kScanTile - 1) / kScanTile) * 4), o_buckets = take(n_keys * sizeof(G1Jac)),
-                 o_part = take(n_partials * sizeof(G1Jac));
-    // heavy buckets: at most n * windows / kMsmHeavy of them, cut into at most that many + n * windows / kHeavyChunk chunks
-    uint64_t max_heavy = (uint64_t)n * windows / kMsmHeavy + 1;
-    if (max_heavy > n_keys) max_heavy = n_keys;
-    const uint64_t max_chunks = max_heavy + (uint64_t)n * windows / kHeavyChunk + 1;
-    const size_t o_chunk_first = take((max_heavy + 1) * 4), o_chunk_sums = take(max_chunks * sizeof(G1Jac));
-    void* slab = nullptr;
-    DPB_TRY(device_alloc(ctx, off, &slab));
-    char* base = (char*)slab;
-    uint32_t* counts = (uint32_t*)(base + o_counts);
-    uint32_t* offsets = (uint32_t*)(base + o_offsets);
-    uint32_t* cursor = (uint32_t*)(base + o_cursor);
-    uint32_t* items = (uint32_t*)(base + o_items);
-    uint32_t* heavy_list = (uint32_t*)(base + o_heavy);
-    uint32_t* heavy_count = (uint32_t*)(base + o_heavy_count);
-    uint32_t* tile_sums = (uint32_t*)(base + o_tiles);
-    const uint32_t n_tiles = (uint32_t)((n_keys + kScanTile - 1) / kScanTile);
-    G1Jac* buckets = (G1Jac*)(base + o_buckets);
-    G1Jac* partials = (G1Jac*)(base + o_part);
-    MsmScalars s;
-    s.ptr = scalars->ptr;
-    s.dtype = scalars->dtype;
-    std::vector<G1Jac> h_part(n_partials);
-    cudaError_t e = cudaMemsetAsync(counts, 0, o_items - o_counts, ctx->stream);  // counts, offsets, cursor, heavy count
-    if (e == cudaSuccess) {
-        msm_count<<<grid_for(ctx, n), kThreads, 0, ctx->stream>>>(s, n, c, windows, counts);
-        msm_scan_tile_sums<<<n_tiles, kScanThreads, 0, ctx->stream>>>(counts, n_keys, tile_sums);
-        msm_scan_tiles<<<1, 1024, 0, ctx->stream>>>(tile_sums, n_tiles);
-        msm_scan_in_tiles<<<n_tiles, kScanThreads, 0, ctx->stream>>>(counts, tile_sums, n_keys, offsets);
-        msm_scatter<<<grid_for(ctx, n), kThreads, 0, ctx->stream>>>(s, n, c, windows, offsets, cursor, items);
-        msm_buckets<<<(uint32_t)((n_keys + kThreads - 1) / kThreads), kThreads, 0, ctx->stream>>>(
-            bases->dev, offsets, counts, items, n_keys, buckets, heavy_list, heavy_count);
-        {
-            // idle blocks leave at once
-            uint32_t* chunk_first = (uint32_t*)(base + o_chunk_first);
-            G1Jac* chunk_sums = (G1Jac*)(base + o_chunk_sums);
-            const uint32_t cap = (uint32_t)ctx->sm_count * 16;
-            msm_heavy_plan<<<1, 1024, 0, ctx->stream>>>(counts, heavy_list, heavy_count, chunk_first);
-            msm_heavy_chunks<<<(uint32_t)(max_chunks < cap ? max_chunks : cap), kMsmReduceThreads, 0, ctx->stream>>>(
-                bases->dev, offsets, counts, items, heavy_list, heavy_count, chunk_first, chunk_sums);
-            msm_heavy_combine<<<(uint32_t)(max_heavy < cap ? max_heavy : cap), kMsmReduceThreads, 0, ctx->stream>>>(
-                heavy_list, heavy_count, chunk_first, chunk_sums, buckets);
-        }
-        msm_reduce<<<(uint32_t)n_partials, kMsmReduceThreads, 0, ctx->stream>>>(buckets, c, blocks_per_window, partials);
-        e = cudaGetLastError();
-    }
-    if (e == cudaSuccess)
-        e = cudaMemcpyAsync(h_part.data(), partials, n_partials * sizeof(G1Jac), cudaMemcpyDeviceToHost, ctx->stream);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
-    device_free(ctx, slab);
-    if (e != cudaSuccess) return fail(DPB_ECUDA, "msm: %s", cudaGetErrorString(e));
-    // windows from the top: total = 2^c * total + window sum
-    G1Jac total = g1_infinity();
-    for (uint32_t w = windows; w-- > 0;) {
-        for (uint32_t d = 0; d < c; d++) total = g1_double(total);
-        for (uint32_t k = 0; k < blocks_per_window; k++) total = g1_add(total, h_part[(size_t)w * blocks_per_window + k]);
-    }
-    const G1Affine a = g1_to_affine(total);
-    Fq xy[2];
-    if (g1_affine_is_infinity(a)) {
-        xy[0] = xy[1] = fq_zero();
-    } else {
-        xy[0] = fq_from_mont(a.x);
-        xy[1] = fq_from_mont(a.y);
-    }
-    memcpy(out_affine_xy, xy, sizeof xy);
-    return DPB_OK;
+    dpb_mle* one[1] = {const_cast<dpb_mle*>(scalars)};
+    if (!scalars) return fail(DPB_EINVAL, "null argument");
+    return dpb_pcs_batch_commit(ctx, bases, one, 1, out_affine_xy);
 }
 
 int dpb_pcs_batch_commit(dpb_ctx* ctx, const dpb_g1_bases* bases, dpb_mle* const* polys, uint32_t n_polys,
                          void* out_affine_xy) {
     if (!ctx || !bases || !polys || !out_affine_xy) return fail(DPB_EINVAL, "null argument");
+    if (bases->ctx != ctx) return fail(DPB_EINVAL, "the bases belong to another context");
     for (uint32_t i = 0; i < n_polys; i++) {
         if (!polys[i]) return fail(DPB_EINVAL, "polynomial %u is null", i);
-        DPB_TRY(dpb_msm_g1(ctx, bases, polys[i], (char*)out_affine_xy + (size_t)i * 64));
+        if (polys[i]->ctx != ctx) return fail(DPB_EINVAL, "polynomial %u belongs to another context", i);
+    }
+    if (n_polys > 1) DPB_TRY(msm_side_streams(ctx));
+    // groups of commitments in flight together: their kernels are short chains of curve additions that leave most
+    // of the GPU idle one at a time
+    for (uint32_t first = 0; first < n_polys; first += kMsmGroup) {
+        const uint32_t cnt = std::min<uint32_t>(kMsmGroup, n_polys - first);
+        std::vector<MsmJob> jobs(cnt);
+        int rc = DPB_OK;
+        size_t host_off = 0;
+        for (uint32_t j = 0; j < cnt && rc == DPB_OK; j++) {
+            rc = msm_plan(ctx, bases, polys[first + j], jobs[j]);
+            jobs[j].host_off = host_off;
+            host_off += jobs[j].n_partials * sizeof(G1Jac);
+        }
+        if (rc == DPB_OK && host_off > kMsmHostBytes) rc = fail(DPB_EINVAL, "commitment staging of %zu bytes", host_off);
+        cudaError_t e = cudaSuccess;
+        if (rc == DPB_OK) {
+            if (!ctx->msm_host) e = cudaHostAlloc(&ctx->msm_host, kMsmHostBytes, cudaHostAllocDefault);
+            const bool side = cnt > 1;
+            if (e == cudaSuccess && side) {
+                // the side streams start after everything this context has queued (the scalars' producers included)
+                e = cudaEventRecord(ctx->msm_ev[dpb_ctx::kMsmStreams], ctx->stream);
+                for (int q = 0; q < dpb_ctx::kMsmStreams && e == cudaSuccess; q++)
+                    e = cudaStreamWaitEvent(ctx->msm_stream[q], ctx->msm_ev[dpb_ctx::kMsmStreams], 0);
+            }
+            for (uint32_t j = 0; j < cnt && e == cudaSuccess; j++) {
+                cudaStream_t st = side ? ctx->msm_stream[j % dpb_ctx::kMsmStreams] : ctx->stream;
+                e = msm_launch(ctx, bases, polys[first + j], jobs[j], st, (G1Jac*)((char*)ctx->msm_host + jobs[j].host_off));
+            }
+            if (side) {
+                // ... and this context's stream goes on after them (even when a launch failed: the slabs are freed below)
+                for (int q = 0; q < dpb_ctx::kMsmStreams; q++) {
+                    cudaEventRecord(ctx->msm_ev[q], ctx->msm_stream[q]);
+                    cudaStreamWaitEvent(ctx->stream, ctx->msm_ev[q], 0);
+                }
+            }
+            const cudaError_t es = cudaStreamSynchronize(ctx->stream);
+            if (e == cudaSuccess) e = es;
+        }
+        for (auto& job : jobs) device_free(ctx, job.slab);
+        if (rc != DPB_OK) return rc;
+        if (e != cudaSuccess) return fail(DPB_ECUDA, "msm: %s", cudaGetErrorString(e));
+        for (uint32_t j = 0; j < cnt; j++)
+            msm_finish(jobs[j], (const G1Jac*)((const char*)ctx->msm_host + jobs[j].host_off),
+                       (char*)out_affine_xy + (size_t)(first + j) * 64);
     }
     return DPB_OK;
 }

@@ -153,6 +153,11 @@ struct dpb_ctx {
     std::vector<Arena> arenas;
     std::unordered_map<void*, Live> block_live;
     std::vector<Block> big_free;  // kept blocks of 2 GiB and more, oldest first
+    // side streams of dpb_pcs_batch_commit (the commitments of a batch run next to each other), made on first use
+    static constexpr int kMsmStreams = 4;
+    cudaStream_t msm_stream[kMsmStreams] = {};
+    cudaEvent_t msm_ev[kMsmStreams + 1] = {};
+    void* msm_host = nullptr;  // pinned: the window sums of the commitments in flight
     // the block of device memory the last sumcheck used, kept for the next one (dpb_sumcheck_begin)
     void* slab_cache = nullptr;
     size_t slab_cache_bytes = 0;

@@ -43,7 +43,9 @@ void dpb_g1_bases_free(dpb_g1_bases* bases);
 int dpb_msm_g1(dpb_ctx* ctx, const dpb_g1_bases* bases, const dpb_mle* scalars, void* out_affine_xy);
 
 /* PCS::batch_commit over already chunked polynomials (zkml/src/poly_commit/context.rs:72): one commitment per
- * table, out_affine_xy holds n_polys x 64 bytes in the tables' order. */
+ * table, out_affine_xy holds n_polys x 64 bytes in the tables' order.  Up to 16 commitments are in flight together
+ * (on side streams of the context that start after everything queued on its stream and that its stream waits for):
+ * one commitment's kernels are short chains of curve additions that leave most of the GPU idle. */
 int dpb_pcs_batch_commit(dpb_ctx* ctx, const dpb_g1_bases* bases, dpb_mle* const* polys, uint32_t n_polys,
                          void* out_affine_xy);
 
