@@ -373,9 +373,20 @@ LogUpBatchProof<F> new_batch_multiple_sizes_prove(dpb_ctx* ctx, const std::vecto
             std::vector<dpb_mle*>& v;
             ~EqGuard() { for (auto* m : v) dpb_mle_free(m); }
         } eq_guard{eq_mles};
+        // Every layer but the last is an inner layer of every instance it touches (an instance reaches its input
+        // layer when one variable remains, all of them together).  Its expression is known in closed form,
+        //   alpha_j * (n_lo d_hi + n_hi d_lo + lambda d_lo d_hi) * eq        (circuit.rs:231-296),
+        // so the three product terms per instance and the claim are written down directly; only the last layer,
+        // whose expression depends on the instances' columns, goes through the expression builder.
+        const bool inner = remaining != 1;
+        dp_crypto::VirtualPolynomials<F> vp;
+        E current_claim = F::zero();
+        std::vector<uint32_t> term_group;  // per direct term: the size group whose eq table closes it
+        E alpha_pow = F::one();            // alpha^layer_count
         for (size_t size : sizes) {
             if (size < remaining) continue;
-            const X mult = X::Constant(F::from_u64(1ull << (total_layers - size)));
+            const E mult_e = F::from_u64(1ull << (total_layers - size));
+            const X mult = X::Constant(mult_e);
             const size_t layer_vars = size - remaining + 1;
             X group = X::ZERO();
             for (auto& c : circuits) {
@@ -383,6 +394,37 @@ LogUpBatchProof<F> new_batch_multiple_sizes_prove(dpb_ctx* ctx, const std::vecto
                 // the whole batch holds this instance once per rank, next to each other; only this rank's takes
                 // part in its sumcheck, all of them in the claim
                 for (size_t q = 0; q < G; q++) {
+                    if (inner) {
+                        const size_t b = layer_count * 4;
+                        if (b + 3 >= wit_evals.size()) throw Error(DPB_EINVAL, "Proving failed: evaluations of the layer above are short");
+                        const E &w0 = wit_evals[b], &w1 = wit_evals[b + 1], &w2 = wit_evals[b + 2], &w3 = wit_evals[b + 3];
+                        const E num = F::add(F::mul(rho, F::sub(w1, w0)), w0), den = F::add(F::mul(rho, F::sub(w3, w2)), w2);
+                        current_claim = F::add(current_claim, F::mul(mult_e, F::mul(alpha_pow, F::add(num, F::mul(lambda, den)))));
+                        if (q == g_rank) {
+                            auto lm = c->layer_mles(layer_vars);
+                            mles.insert(mles.end(), lm.begin(), lm.end());
+                            const E al = F::mul(alpha_pow, lambda);
+                            const uint16_t w = wit_off;
+                            auto term = [&](const E& coef, uint16_t x, uint16_t y) {
+                                if (F::is_zero(coef)) return;
+                                dpb_term t;
+                                memset(&t, 0, sizeof t);
+                                memcpy(t.coeff, &coef, sizeof(E));
+                                t.n_factors = 3;
+                                t.idx[0] = x;
+                                t.idx[1] = y;
+                                vp.terms.push_back(t);
+                                term_group.push_back((uint32_t)group_exprs.size());
+                            };
+                            term(alpha_pow, w, (uint16_t)(w + 3));       // n_lo d_hi
+                            term(alpha_pow, (uint16_t)(w + 1), (uint16_t)(w + 2));  // n_hi d_lo
+                            term(al, (uint16_t)(w + 2), (uint16_t)(w + 3));         // lambda d_lo d_hi
+                            wit_off = (uint16_t)(wit_off + 4);
+                        }
+                        layer_count++;
+                        alpha_pow = F::mul(alpha_pow, alpha);
+                        continue;
+                    }
                     auto le = c->layer_exprs(layer_vars, layer_count, wit_off);
                     layer_count++;
                     claim_expr = claim_expr + mult * le.claim;
@@ -401,17 +443,24 @@ LogUpBatchProof<F> new_batch_multiple_sizes_prove(dpb_ctx* ctx, const std::vecto
             eq_mles.push_back(eq);
             group_exprs.push_back(group);
         }
-        const E current_claim = claim_expr.evaluate(wit_evals, {alpha, lambda, rho});
+        if (!inner) current_claim = claim_expr.evaluate(wit_evals, {alpha, lambda, rho});
         transcript.append_scalars(&current_claim, 1);
 
-        X full = X::ZERO();
-        for (size_t i = 0; i < group_exprs.size(); i++) full = full + group_exprs[i] * X::WitIn((uint16_t)(wit_off + i));
         std::vector<dpb_mle*> all(mles);
         all.insert(all.end(), eq_mles.begin(), eq_mles.end());
-        auto builder = dp_crypto::VirtualPolynomialsBuilder<F>::new_with_mles(1, (uint32_t)v, all);
-        dpb::TracePhase t_expand("logup.expand_terms");
-        auto vp = builder.to_virtual_polys({full}, {alpha, lambda});
-        t_expand.stop();
+        if (inner) {
+            if (vp.terms.empty()) throw Error(DPB_EINVAL, "virtual polynomial has no terms");
+            for (size_t t = 0; t < vp.terms.size(); t++) vp.terms[t].idx[2] = (uint16_t)(wit_off + term_group[t]);
+            vp.num_vars = (uint32_t)v;
+            vp.mles = all;
+            vp.max_degree = 3;
+        } else {
+            X full = X::ZERO();
+            for (size_t i = 0; i < group_exprs.size(); i++) full = full + group_exprs[i] * X::WitIn((uint16_t)(wit_off + i));
+            auto builder = dp_crypto::VirtualPolynomialsBuilder<F>::new_with_mles(1, (uint32_t)v, all);
+            dpb::TracePhase t_expand("logup.expand_terms");
+            vp = builder.to_virtual_polys({full}, {alpha, lambda});
+        }
         t_expr.stop();
         auto res = dp_crypto::IOPProverState<F>::prove(ctx, vp, transcript, partial ? 2 : 0);
         point = res.second.collect_raw_challenges();
