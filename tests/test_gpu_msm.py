@@ -139,3 +139,24 @@ def test_msm_crowded_buckets(dpb, ctx, pcs, values):
         assert pcs.msm(ctx, bases, ctx.upload_ints(x, dt)) == want
     assert pcs.msm(ctx, bases, ctx.upload(F.table_from_i64(x), dpb.FR)) == want
     bases.free()
+
+
+def test_batch_commit_many_polynomials(dpb, ctx, pcs):
+    """More polynomials than are in flight together (16), of mixed sizes and layouts: batch_commit returns what one
+    commitment at a time returns, and what one scalar multiplication gives on the CPU side."""
+    rng = np.random.default_rng(6500)
+    bases = pcs.G1Bases.synthetic(ctx, 1 << 12)
+    polys, want = [], []
+    for i in range(40):
+        n = 1 << int(rng.integers(0, 13))
+        x = rng.integers(-(1 << 20), 1 << 20, size=n, dtype=np.int64)
+        if i % 3 == 0:
+            polys.append(ctx.upload(F.table_from_i64(x), dpb.FR))
+        else:
+            polys.append(ctx.upload_ints(x, dpb.FR_I32 if i % 3 == 1 else dpb.FR_I64))
+        k = int(sum(int(v) * (j + 1) for j, v in enumerate(x)) % g1.R_ORDER)
+        want.append(g1.boundary(g1.mul(k, g1.GENERATOR)) if k else (0, 0))
+    got = pcs.batch_commit(ctx, bases, polys)
+    assert list(got) == want
+    assert [pcs.msm(ctx, bases, p) for p in polys[:5]] == want[:5]
+    bases.free()
