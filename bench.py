@@ -576,6 +576,11 @@ def workload_record(dpb, prover, ctx, args):
                      "of the synthetic tensors are outside",
            "excludes": "inference, HyperKZG opening and host orchestration of the reference's prove_full; the "
                        "reference's published 1.12 tokens/s (24-core EPYC, whole prover) is a different scope"}
+    # the same walk over Goldilocks (base tables, extension challenges): the field of the standalone benchmark
+    wl.run_transformer_path(dpb, prover, ctx, shape, field="gl", seed=args.seed + 1)
+    gl = wl.run_transformer_path(dpb, prover, ctx, shape, field="gl", seed=args.seed)
+    rec["goldilocks"] = {"ms": gl["seconds"] * 1e3, "tokens_per_s": gl["tokens_per_s"],
+                         "by_kind_ms": {k: v * 1e3 for k, v in sorted(gl["by_kind"].items(), key=lambda kv: -kv[1])}}
     sample = wl.CPU_SAMPLE
     gpu_s = wl.run_transformer_path(dpb, prover, ctx, sample, field="fr", seed=args.seed)
     gpu_s = wl.run_transformer_path(dpb, prover, ctx, sample, field="fr", seed=args.seed)

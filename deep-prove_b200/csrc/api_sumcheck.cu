@@ -365,9 +365,19 @@ static void plan_program(dpb_sc* sc, const dpb_term* terms, dpb_mle* const* mles
     h_prog.assign((const uint8_t*)prog.data(), (const uint8_t*)prog.data() + prog.size() * sizeof(ProgTerm<F>));
     sc->has_prog = true;
     // one-pass rounds: every thread keeps (value, difference) of every table in shared memory
+    // block size: the one that keeps most warps on an SM, between the shared memory of the slots and the kernels'
+    // registers (about 124 per thread: two blocks of 256 threads, four of 128); ties go to the larger block
     const size_t per_thread = (size_t)sc->k * 2 * sizeof(E);
-    uint32_t threads = 256;
-    while (threads >= 64 && per_thread * threads > (size_t)kOnePassMaxSmem) threads /= 2;
+    uint32_t threads = 0, best_warps = 0;
+    for (uint32_t t = 256; t >= 64; t /= 2) {
+        if (per_thread * t > (size_t)kOnePassMaxSmem) continue;
+        const uint32_t by_smem = (uint32_t)((size_t)kOnePassMaxSmem / (per_thread * t)), by_regs = 512 / t;
+        const uint32_t warps = std::min(by_smem, by_regs) * t / 32;
+        if (warps > best_warps) {
+            best_warps = warps;
+            threads = t;
+        }
+    }
     if (threads >= 64) {
         sc->op_threads = threads;
         sc->op_smem = per_thread * threads;
