@@ -87,6 +87,10 @@ struct dpb_sc {
     uint32_t n_groups = 0;
     uint32_t op_threads = 0;
     size_t op_smem = 0;
+    bool logup_ok = false;       // a usable hint of the logup prover: sc_round_logup runs the large rounds
+    void* d_logup = nullptr;     // [LogupConsts[n] | LogupInst[n]] (own allocation)
+    uint32_t logup_n = 0, logup_eq = 0;
+    alignas(16) uint8_t logup_lambda[32] = {0};
     bool seg_ok = false;         // the program splits into segments over few tables each: sc_round_seg runs the large rounds
     void* d_segs = nullptr;
     void* d_seg_prog = nullptr;
@@ -488,6 +492,35 @@ static void spliteq_advance(dpb_sc* sc, uint32_t i, const typename F::E& r) {
     }
 }
 
+// The large rounds of a logup layer from the layer's own formula (see sumcheck_hint_logup).
+template <class F>
+static int launch_logup(dpb_sc* sc, uint32_t round, uint64_t n_pairs, const typename F::E& r, const SplitEqArgs<F>& eq) {
+    typedef typename F::E E;
+    dpb_ctx* ctx = sc->ctx;
+    const uint32_t threads = 128;
+    uint64_t blocks = (n_pairs + threads - 1) / threads;
+    const uint64_t per_sm = sizeof(E) == 16 ? 4 : 3;  // resident blocks: 126 registers per thread (Goldilocks), 168 (BN254)
+    if (blocks > (uint64_t)ctx->sm_count * per_sm) blocks = (uint64_t)ctx->sm_count * per_sm;
+    if (blocks > ctx->max_blocks) blocks = ctx->max_blocks;
+    const RoundTab* tabs = sc->d_rtab_eq + (size_t)round * sc->k;
+    const typename F::FoldKey rk = F::fold_key(r);
+    E lam;
+    memcpy(&lam, sc->logup_lambda, sizeof(E));
+    const typename F::FoldKey lamk = F::fold_key(lam);
+    const LogupConsts<F>* consts = (const LogupConsts<F>*)sc->d_logup;
+    const LogupInst* inst = (const LogupInst*)((const char*)sc->d_logup + (size_t)sc->logup_n * sizeof(LogupConsts<F>));
+    const size_t smem = (size_t)sc->logup_n * (sizeof(LogupConsts<F>) + sizeof(LogupInst));
+    if (round > 0)
+        sc_round_logup<F, true><<<(uint32_t)blocks, threads, smem, ctx->stream>>>(
+            tabs, inst, consts, sc->logup_n, rk, lamk, sc->logup_eq, eq.scale[0], eq.stride_log2[0], n_pairs,
+            reduce_scratch<F>(ctx), (E*)ctx->round_out);
+    else
+        sc_round_logup<F, false><<<(uint32_t)blocks, threads, smem, ctx->stream>>>(
+            tabs, inst, consts, sc->logup_n, rk, lamk, sc->logup_eq, eq.scale[0], eq.stride_log2[0], n_pairs,
+            reduce_scratch<F>(ctx), (E*)ctx->round_out);
+    return DPB_OK;
+}
+
 template <class F, int D>
 static int launch_spliteq(dpb_sc* sc, uint32_t round, uint64_t n_pairs, const typename F::E& r) {
     typedef typename F::E E;
@@ -509,6 +542,10 @@ static int launch_spliteq(dpb_sc* sc, uint32_t round, uint64_t n_pairs, const ty
         eq.stride_log2[eq.n_eq] = ip + 1;
         eq.scale[eq.n_eq] = F::mul(S, iz);
         eq.n_eq++;
+    }
+    if constexpr (D == 3) {
+        if (sc->logup_ok && eq.n_eq == 1 && eq.const_groups == 0 && eq.table[0] == sc->logup_eq)
+            return launch_logup<F>(sc, round, n_pairs, r, eq);
     }
     if constexpr (D >= 2 && D <= 4) {
         if (sc->seg_ok) return launch_seg<F, D, true>(sc, round, n_pairs, r, eq);
@@ -1087,7 +1124,7 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
             for (uint32_t j = 0; j < sc->k; j++) bytes += dtype_size(sc->tr[j].dtype) << sc->tr[j].nv;
             name = done ? (sc->tr[0].dtype == DPB_GL_BASE ? "fused_eval0<base>"
                            : sc->tr[0].dtype == DPB_FR_I32 ? "fused_eval0<i32>" : "fused_eval0")
-                        : split ? (seg ? "sc_round_seg<spliteq>" : "sc_round_spliteq")
+                        : split ? (sc->logup_ok && sc->d == 3 ? "sc_round_logup" : seg ? "sc_round_seg<spliteq>" : "sc_round_spliteq")
                         : one_pass ? (seg ? "sc_round_seg" : "sc_round_generic") : "sc_eval_generic";
         } else {
             const FoldDesc* fd = sc->h_fold.data() + (size_t)i * sc->k;
@@ -1097,7 +1134,7 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
                 if (sc->h_desc[(size_t)i * sc->k + j].shift >= 0) bytes += dtype_size(sc->tr[j].dtype) << sc->tr[j].nv;
             name = done ? (fd[0].dtype_in == DPB_GL_BASE ? "fused_fold_eval<base>"
                            : fd[0].dtype_in == DPB_FR_I32 ? "fused_fold_eval<i32>" : "fused_fold_eval")
-                        : split ? (seg ? "sc_round_seg<spliteq>" : "sc_round_spliteq")
+                        : split ? (sc->logup_ok && sc->d == 3 ? "sc_round_logup" : seg ? "sc_round_seg<spliteq>" : "sc_round_spliteq")
                         : one_pass ? (seg ? "sc_round_seg" : "sc_round_generic") : "sc_fold_generic+sc_eval_generic";
         }
         bool found = false;
@@ -1441,6 +1478,78 @@ int dpb_sumcheck_begin_sharded(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* 
     return DPB_OK;
 }
 
+}  // extern "C"
+
+namespace dpb {
+
+template <class F>
+static void hint_logup_impl(dpb_sc* sc, const LogupHintInst* inst, uint32_t n_inst, const void* lambda, uint32_t eq_table) {
+    typedef typename F::E E;
+    std::vector<LogupConsts<F>> consts(n_inst);
+    std::vector<LogupInst> di(n_inst);
+    memset(consts.data(), 0, consts.size() * sizeof(LogupConsts<F>));
+    for (uint32_t i = 0; i < n_inst; i++) {
+        E a, s, c;
+        memcpy(&a, inst[i].alpha, sizeof(E));
+        memcpy(&s, inst[i].sep, sizeof(E));
+        memcpy(&c, inst[i].constant, sizeof(E));
+        consts[i].alpha = F::fold_key(a);
+        consts[i].sep = F::fold_key(s);
+        consts[i].c = c;
+        di[i].kind = (uint16_t)inst[i].kind;
+        di[i].first = (uint16_t)inst[i].first;
+        di[i].ncol = (uint16_t)inst[i].ncol;
+        di[i].pad = 0;
+    }
+    const size_t bytes = n_inst * (sizeof(LogupConsts<F>) + sizeof(LogupInst));
+    if (bytes > 96 * 1024) return;
+    void* d = nullptr;
+    if (device_alloc(sc->ctx, bytes, &d) != DPB_OK) return;
+    std::vector<uint8_t> blob(bytes);
+    memcpy(blob.data(), consts.data(), n_inst * sizeof(LogupConsts<F>));
+    memcpy(blob.data() + n_inst * sizeof(LogupConsts<F>), di.data(), n_inst * sizeof(LogupInst));
+    if (upload_small(sc->ctx, d, blob.data(), bytes) != DPB_OK) {
+        device_free(sc->ctx, d);
+        return;
+    }
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(sc_round_logup<F, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaFuncSetAttribute(sc_round_logup<F, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        attr_set = true;
+    }
+    sc->d_logup = d;
+    sc->logup_n = n_inst;
+    sc->logup_eq = eq_table;
+    memcpy(sc->logup_lambda, lambda, sizeof(E));
+    sc->logup_ok = true;
+}
+
+void sumcheck_hint_logup(dpb_sc* sc, const LogupHintInst* inst, uint32_t n_inst, const void* lambda, uint32_t eq_table) {
+    if (!sc || !inst || !lambda || n_inst == 0 || n_inst > kLogupMaxInst || sc->logup_ok || getenv("DPB_NO_LOGUP_KERNEL")) return;
+    // usable only by a degree-3 sumcheck in split-eq form whose one eq table is the hint's and whose other tables are
+    // exactly the instances', in order
+    if (!sc->spliteq || sc->d != 3 || sc->eq_leads.size() != 1 || sc->eq_leads[0].table != eq_table ||
+        sc->eq_leads[0].first_active != 0 || sc->log2_ranks != 0)
+        return;
+    uint32_t next = 0;
+    for (uint32_t i = 0; i < n_inst; i++) {
+        const LogupHintInst& h = inst[i];
+        if (h.first != next) return;
+        if (h.kind == kLogupInner) next += 4;
+        else if ((h.kind == kLogupLookup || h.kind == kLogupTable) && (h.ncol == 1 || h.ncol == 2))
+            next += 2 * h.ncol + (h.kind == kLogupTable ? 2 : 0);
+        else return;
+    }
+    if (next != eq_table || next + 1 != sc->k) return;
+    if (sc->gl) hint_logup_impl<GlFam>(sc, inst, n_inst, lambda, eq_table);
+    else hint_logup_impl<FrFam>(sc, inst, n_inst, lambda, eq_table);
+}
+
+}  // namespace dpb
+
+extern "C" {
+
 int dpb_sumcheck_begin_partial(dpb_ctx* ctx, uint32_t num_vars, dpb_mle* const* mles, uint32_t k,
                                const dpb_term* terms, uint32_t n_terms, dpb_sc** out) {
     if (!ctx || !mles || !terms || !out) return fail(DPB_EINVAL, "null argument");
@@ -1498,6 +1607,7 @@ void dpb_sumcheck_free(dpb_sc* sc) {
     if (sc->tail) dpb_sumcheck_free(sc->tail);
     for (auto* m : sc->tail_mles) dpb_mle_free(m);
     device_free(sc->ctx, sc->tail_dev);
+    device_free(sc->ctx, sc->d_logup);
     // the fold buffers and every descriptor array live in this one block
     if (sc->slab && sc->slab == sc->ctx->slab_cache) sc->ctx->slab_cache_busy = false;
     else device_free(sc->ctx, sc->slab);

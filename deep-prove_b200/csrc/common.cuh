@@ -217,4 +217,17 @@ int stage_to_device(dpb_ctx* ctx, const void* host, size_t bytes, size_t offset,
 // rank: a copy.  Bounded wait; DPB_EINVAL when nranks * bytes exceeds the context's exchange buffer.
 int comm_allgather_host(dpb_ctx* ctx, const void* in, size_t bytes, void* out);
 
+// What the batched logup prover knows about a layer sumcheck it is about to run (host/logup.hpp): the instances in the
+// order of the sumcheck's tables, and the layer's constants.  sumcheck_hint_logup hands it to a sumcheck right after
+// dpb_sumcheck_begin; when the sumcheck runs in split-eq form with that single eq table, its large rounds then use
+// the layer's own formula (sc_round_logup) instead of the term list.  The hint must describe the polynomial the term
+// list describes; a hint the sumcheck cannot use is ignored.
+struct LogupHintInst {
+    int kind;        // 0 inner layer (4 tables), 1 lookup input layer (2 * ncol tables), 2 table input layer (2 + 2 * ncol)
+    uint32_t first;  // index of its first table
+    uint32_t ncol;
+    alignas(16) uint8_t alpha[32], constant[32], sep[32];  // challenge elements: alpha_j, and for input layers c and s
+};
+void sumcheck_hint_logup(dpb_sc* sc, const LogupHintInst* inst, uint32_t n_inst, const void* lambda, uint32_t eq_table);
+
 }  // namespace dpb

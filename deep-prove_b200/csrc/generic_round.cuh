@@ -420,6 +420,122 @@ __global__ void __launch_bounds__(kThreads, 2)
     grid_sum_publish<F, D + 1>(acc, rs, out);
 }
 
+// ---- one-pass rounds of a logup-GKR layer, from the layer's own formula -------------
+//
+// The layer sumcheck of the batched logup prover (zkml/src/lookup/logup_gkr/circuit.rs:231-412) sums, per instance j,
+//   alpha_j * eq * (n_lo d_hi + n_hi d_lo + lambda d_lo d_hi),
+// where in an instance's input layer d = c + sum_i s^i column_i, the numerators of a lookup are -1 and those of a table
+// its multiplicities.  As a list of product terms that is five products per instance and point (input layer of a
+// two-column lookup: nine monomials); written as  A D + C (B + lambda D)  it is two, with lambda D, and then alpha_j
+// times the sum, as products by per-launch constants.  Every table sits in registers as (value, difference), one
+// instance after the other: no interpreter, no shared-memory slots.  The sums are those of sc_round_spliteq for
+// degree 3 (H at 0, 1, 2, then C = 0), so the host side of the round is unchanged and so are the messages.
+constexpr int kLogupInner = 0, kLogupLookup = 1, kLogupTable = 2;
+constexpr uint32_t kLogupMaxInst = 64;
+struct LogupInst {
+    uint16_t kind;   // kLogup*
+    uint16_t first;  // inner: n_lo, n_hi, d_lo, d_hi at first..first+3; lookup: ncol low halves, then ncol high halves;
+                     // table: multiplicities' low and high halves, then the columns as for a lookup
+    uint16_t ncol;   // input layers: 1 or 2 columns
+    uint16_t pad;
+};
+template <class F>
+struct LogupConsts {
+    typename F::FoldKey alpha;  // alpha_j
+    typename F::FoldKey sep;    // s (input layers with two columns)
+    typename F::E c;            // the constant challenge (input layers)
+};
+
+template <class F, bool SKIP_ONE>
+__global__ void __launch_bounds__(128, 3)
+    sc_round_logup(const RoundTab* __restrict__ tabs, const LogupInst* __restrict__ inst_g,
+                   const LogupConsts<F>* __restrict__ consts_g, uint32_t n_inst, typename F::FoldKey rk,
+                   typename F::FoldKey lamk, uint32_t eq_table, typename F::E eq_scale, uint32_t eq_stride_log2,
+                   uint64_t n_pairs, ReduceScratch<F> rs, typename F::E* out) {
+    typedef typename F::E E;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    LogupConsts<F>* consts = (LogupConsts<F>*)smem_raw;
+    LogupInst* inst = (LogupInst*)(smem_raw + (size_t)n_inst * sizeof(LogupConsts<F>));
+    {
+        const uint32_t words = n_inst * (uint32_t)(sizeof(LogupConsts<F>) / 4);
+        for (uint32_t i = threadIdx.x; i < words; i += blockDim.x) ((uint32_t*)consts)[i] = ((const uint32_t*)consts_g)[i];
+        for (uint32_t i = threadIdx.x; i < n_inst * (uint32_t)(sizeof(LogupInst) / 4); i += blockDim.x)
+            ((uint32_t*)inst)[i] = ((const uint32_t*)inst_g)[i];
+    }
+    __syncthreads();
+    E acc[4];
+#pragma unroll
+    for (int x = 0; x < 4; x++) acc[x] = F::zero();
+    const RoundTab eqt = tabs[eq_table];
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t p = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; p < n_pairs; p += stride) {
+        E g0 = F::zero(), g1 = F::zero(), g2 = F::zero();
+        for (uint32_t i = 0; i < n_inst; i++) {
+            const LogupInst in = inst[i];
+            const LogupConsts<F>& k = consts[i];
+            E a0, da, c0, dc, d0, dd, u0, du;  // A, C, D and U = B + lambda D (lookups: lambda D - 1), each (value, difference)
+            if (in.kind == kLogupInner) {
+                seg_load<F>(tabs[in.first + 3], p, rk, d0, dd);
+                seg_load<F>(tabs[in.first + 1], p, rk, u0, du);
+                u0 = F::add(u0, F::mul_key(lamk, d0));
+                du = F::add(du, F::mul_key(lamk, dd));
+                seg_load<F>(tabs[in.first + 2], p, rk, c0, dc);
+                seg_load<F>(tabs[in.first], p, rk, a0, da);
+            } else {
+                const uint32_t col = in.first + (in.kind == kLogupTable ? 2u : 0u);
+                seg_load<F>(tabs[col], p, rk, c0, dc);
+                seg_load<F>(tabs[col + in.ncol], p, rk, d0, dd);
+                if (in.ncol == 2) {
+                    E v, dv;
+                    seg_load<F>(tabs[col + 1], p, rk, v, dv);
+                    c0 = F::add(c0, F::mul_key(k.sep, v));
+                    dc = F::add(dc, F::mul_key(k.sep, dv));
+                    seg_load<F>(tabs[col + 3], p, rk, v, dv);
+                    d0 = F::add(d0, F::mul_key(k.sep, v));
+                    dd = F::add(dd, F::mul_key(k.sep, dv));
+                }
+                c0 = F::add(c0, k.c);
+                d0 = F::add(d0, k.c);
+                u0 = F::mul_key(lamk, d0);
+                du = F::mul_key(lamk, dd);
+                if (in.kind == kLogupTable) {
+                    E v, dv;
+                    seg_load<F>(tabs[in.first + 1], p, rk, v, dv);
+                    u0 = F::add(u0, v);
+                    du = F::add(du, dv);
+                    seg_load<F>(tabs[in.first], p, rk, a0, da);
+                } else {
+                    u0 = F::sub(u0, F::one());  // numerators -1: C (lambda D - 1) - D
+                    a0 = da = F::zero();
+                }
+            }
+            const bool lookup = in.kind == kLogupLookup;
+#pragma unroll
+            for (int x = 0; x < 3; x++) {
+                if (!(SKIP_ONE && x == 1)) {
+                    E g = F::mul(c0, u0);
+                    g = lookup ? F::sub(g, d0) : F::add(g, F::mul(a0, d0));
+                    g = F::mul_key(k.alpha, g);
+                    if (x == 0) g0 = F::add(g0, g);
+                    else if (x == 1) g1 = F::add(g1, g);
+                    else g2 = F::add(g2, g);
+                }
+                if (x < 2) {
+                    c0 = F::add(c0, dc);
+                    d0 = F::add(d0, dd);
+                    u0 = F::add(u0, du);
+                    if (!lookup) a0 = F::add(a0, da);
+                }
+            }
+        }
+        const E e = F::mul(eq_scale, F::load(eqt.in, eqt.dtype_in, p << eq_stride_log2));
+        acc[0] = F::add(acc[0], F::mul(e, g0));
+        if (!SKIP_ONE) acc[1] = F::add(acc[1], F::mul(e, g1));
+        acc[2] = F::add(acc[2], F::mul(e, g2));
+    }
+    grid_sum_publish<F, 4>(acc, rs, out);
+}
+
 // ---- resident kernel for the last rounds ---------------------------------------
 //
 // Once a round has only a few hundred pairs, launching a kernel per round costs

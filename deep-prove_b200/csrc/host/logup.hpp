@@ -171,6 +171,19 @@ class LogUpCircuit {
         return {alpha_j * (-d_hi - d_lo + lam * d_lo * d_hi), claim, (uint16_t)(2 * ncol)};
     }
 
+    // the input layer as sc_round_logup takes it (kinds 1 and 2 of dpb::LogupHintInst)
+    dpb::LogupHintInst input_layer_hint(uint16_t wit0, const E& alpha_j) const {
+        dpb::LogupHintInst h;
+        memset(&h, 0, sizeof h);
+        h.kind = kind_ == ProofType::Table ? 2 : 1;
+        h.first = wit0;
+        h.ncol = (uint32_t)cols_.size();
+        memcpy(h.alpha, &alpha_j, sizeof(E));
+        memcpy(h.constant, &constant_, sizeof(E));
+        memcpy(h.sep, &sep_, sizeof(E));
+        return h;
+    }
+
     // circuit.rs:442-500
     std::vector<E> combine_final_evals(const E* evals, size_t n, const E& rho) const {
         if (n != final_eval_count()) throw Error(DPB_EINVAL, "wrong number of final evaluations");
@@ -382,6 +395,7 @@ LogUpBatchProof<F> new_batch_multiple_sizes_prove(dpb_ctx* ctx, const std::vecto
         dp_crypto::VirtualPolynomials<F> vp;
         E current_claim = F::zero();
         std::vector<uint32_t> term_group;  // per direct term: the size group whose eq table closes it
+        std::vector<dpb::LogupHintInst> hint;  // this rank's instances as the round kernel of a logup layer wants them
         E alpha_pow = F::one();            // alpha^layer_count
         for (size_t size : sizes) {
             if (size < remaining) continue;
@@ -416,6 +430,12 @@ LogUpBatchProof<F> new_batch_multiple_sizes_prove(dpb_ctx* ctx, const std::vecto
                                 vp.terms.push_back(t);
                                 term_group.push_back((uint32_t)group_exprs.size());
                             };
+                            dpb::LogupHintInst h;
+                            memset(&h, 0, sizeof h);
+                            h.kind = 0;
+                            h.first = w;
+                            memcpy(h.alpha, &alpha_pow, sizeof(E));
+                            hint.push_back(h);
                             term(alpha_pow, w, (uint16_t)(w + 3));       // n_lo d_hi
                             term(alpha_pow, (uint16_t)(w + 1), (uint16_t)(w + 2));  // n_hi d_lo
                             term(al, (uint16_t)(w + 2), (uint16_t)(w + 3));         // lambda d_lo d_hi
@@ -426,6 +446,8 @@ LogUpBatchProof<F> new_batch_multiple_sizes_prove(dpb_ctx* ctx, const std::vecto
                         continue;
                     }
                     auto le = c->layer_exprs(layer_vars, layer_count, wit_off);
+                    if (q == g_rank) hint.push_back(c->input_layer_hint(wit_off, alpha_pow));
+                    alpha_pow = F::mul(alpha_pow, alpha);
                     layer_count++;
                     claim_expr = claim_expr + mult * le.claim;
                     if (q != g_rank) continue;
@@ -462,7 +484,10 @@ LogUpBatchProof<F> new_batch_multiple_sizes_prove(dpb_ctx* ctx, const std::vecto
             vp = builder.to_virtual_polys({full}, {alpha, lambda});
         }
         t_expr.stop();
-        auto res = dp_crypto::IOPProverState<F>::prove(ctx, vp, transcript, partial ? 2 : 0);
+        // one size group: one eq table, right after the instances' tables
+        const bool hinted = group_exprs.size() == 1;
+        auto res = dp_crypto::IOPProverState<F>::prove(ctx, vp, transcript, partial ? 2 : 0, hinted ? &hint : nullptr, &lambda,
+                                                       (uint32_t)wit_off);
         point = res.second.collect_raw_challenges();
         const auto& finals = res.second.get_mle_flatten_final_evaluations();
         std::vector<E> evals(finals.begin(), finals.begin() + wit_off);

@@ -299,7 +299,9 @@ class IOPProverState {
     // Runs every round on the GPU behind `ctx`; the transcript is only touched here, on the host.
     template <class T>
     static std::pair<IOPProof<F>, IOPProverState> prove(dpb_ctx* ctx, const VirtualPolynomials<F>& vp,
-                                                        T& transcript, int sharded = 0) {
+                                                        T& transcript, int sharded = 0,
+                                                        const std::vector<dpb::LogupHintInst>* logup_hint = nullptr,
+                                                        const E* logup_lambda = nullptr, uint32_t logup_eq = 0) {
         if (vp.terms.empty()) throw Error(DPB_EINVAL, "virtual polynomial has no terms");
         IOPProverState st;
         IOPProof<F> proof;
@@ -309,6 +311,9 @@ class IOPProverState {
         // rank runs this same loop
         check((sharded == 2 ? dpb_sumcheck_begin_partial : sharded ? dpb_sumcheck_begin_sharded : dpb_sumcheck_begin)(
             ctx, vp.num_vars, vp.mles.data(), (uint32_t)vp.mles.size(), vp.terms.data(), (uint32_t)vp.terms.size(), &sc));
+        // the logup prover says what its layer looks like: the large rounds then run from the layer's formula
+        if (logup_hint && logup_lambda && !logup_hint->empty())
+            dpb::sumcheck_hint_logup(sc, logup_hint->data(), (uint32_t)logup_hint->size(), logup_lambda, logup_eq);
         t_begin.stop();
         dpb::TracePhase t_rounds("sumcheck.rounds");
         struct Guard {
