@@ -310,9 +310,77 @@ inline Fr fr_pow(Fr a, const uint64_t e[4]) {
     }
     return r;
 }
+// Host-side inverse (Montgomery form in and out) by the binary extended Euclidean algorithm: about 500 shift /
+// subtract steps on four words instead of the 380 Montgomery products of a^(r-2): every sumcheck that runs in
+// split-eq form inverts once when it begins.  inv(0) = 0, as with the power.
 inline Fr fr_inv(const Fr& a) {
-    const uint64_t e[4] = {DPB_FR_P0 - 2, DPB_FR_P1, DPB_FR_P2, DPB_FR_P3};
-    return fr_pow(a, e);
+    typedef unsigned __int128 u128;
+    struct U {
+        uint64_t w[4];
+    };
+    const U P = {{DPB_FR_P0, DPB_FR_P1, DPB_FR_P2, DPB_FR_P3}};
+    auto is_zero = [](const U& x) { return (x.w[0] | x.w[1] | x.w[2] | x.w[3]) == 0; };
+    auto is_one = [](const U& x) { return x.w[0] == 1 && (x.w[1] | x.w[2] | x.w[3]) == 0; };
+    auto geq = [](const U& x, const U& y) {
+        for (int i = 3; i >= 0; i--)
+            if (x.w[i] != y.w[i]) return x.w[i] > y.w[i];
+        return true;
+    };
+    auto add = [](U& x, const U& y) {
+        u128 c = 0;
+        for (int i = 0; i < 4; i++) {
+            c += (u128)x.w[i] + y.w[i];
+            x.w[i] = (uint64_t)c;
+            c >>= 64;
+        }
+    };
+    auto sub = [](U& x, const U& y) {
+        uint64_t b = 0;
+        for (int i = 0; i < 4; i++) {
+            const u128 d = (u128)x.w[i] - y.w[i] - b;
+            x.w[i] = (uint64_t)d;
+            b = (uint64_t)(d >> 64) & 1;
+        }
+    };
+    auto shr1 = [](U& x) {
+        for (int i = 0; i < 3; i++) x.w[i] = (x.w[i] >> 1) | (x.w[i + 1] << 63);
+        x.w[3] >>= 1;
+    };
+    auto halve = [&](U& x) {  // x / 2 mod r for x < r (r < 2^254: x + r does not overflow)
+        if (x.w[0] & 1) add(x, P);
+        shr1(x);
+    };
+    auto sub_mod = [&](U& x, const U& y) {  // x - y mod r for x, y < r
+        if (!geq(x, y)) add(x, P);
+        sub(x, y);
+    };
+    U u = {{a.l[0], a.l[1], a.l[2], a.l[3]}}, v = P, x1 = {{1, 0, 0, 0}}, x2 = {{0, 0, 0, 0}};
+    if (is_zero(u)) return a;
+    while (!is_one(u) && !is_one(v)) {
+        while (!(u.w[0] & 1)) {
+            shr1(u);
+            halve(x1);
+        }
+        while (!(v.w[0] & 1)) {
+            shr1(v);
+            halve(x2);
+        }
+        if (geq(u, v)) {
+            sub(u, v);
+            sub_mod(x1, x2);
+        } else {
+            sub(v, u);
+            sub_mod(x2, x1);
+        }
+    }
+    const U& y = is_one(u) ? x1 : x2;  // (a R)^-1 as a plain integer
+    Fr r;
+    r.l[0] = y.w[0];
+    r.l[1] = y.w[1];
+    r.l[2] = y.w[2];
+    r.l[3] = y.w[3];
+    // Montgomery products by R^2 lift it: (a R)^-1 -> a^-1 -> a^-1 R
+    return fr_mul(fr_mul(r, fr_rr()), fr_rr());
 }
 
 }  // namespace dpb
