@@ -431,7 +431,7 @@ __global__ void __launch_bounds__(kThreads, 2)
 // instance after the other: no interpreter, no shared-memory slots.  The sums are those of sc_round_spliteq for
 // degree 3 (H at 0, 1, 2, then C = 0), so the host side of the round is unchanged and so are the messages.
 constexpr int kLogupInner = 0, kLogupLookup = 1, kLogupTable = 2;
-constexpr uint32_t kLogupMaxInst = 64;
+constexpr uint32_t kLogupMaxInst = 128;
 struct LogupInst {
     uint16_t kind;   // kLogup*
     uint16_t first;  // inner: n_lo, n_hi, d_lo, d_hi at first..first+3; lookup: ncol low halves, then ncol high halves;
