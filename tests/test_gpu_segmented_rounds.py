@@ -63,19 +63,37 @@ def test_logup_batch_of_large_instances(dpb, ctx, prover, F, cpi):
 
 
 @pytest.mark.parametrize("F", FIELDS)
-def test_table_instance_with_multiplicities(dpb, ctx, prover, F):
-    """A table of 2^17 rows with two columns and its multiplicities (the numerators are tables too)."""
-    rng = np.random.default_rng(75)
+@pytest.mark.parametrize("ncols", [1, 2])
+def test_table_instance_with_multiplicities(dpb, ctx, prover, F, ncols):
+    """A table of 2^17 rows with one or two columns and its multiplicities (the numerators are tables too)."""
+    rng = np.random.default_rng(75 + ncols)
     rows = 1 << 17
     base = dpb.FR if F is orc.FrField else dpb.GL_BASE
     t_in = np.arange(rows, dtype=np.int64) - rows // 2
-    t_out = np.maximum(t_in, 0)
+    cols = [t_in, np.maximum(t_in, 0)][:ncols]
     mult = rng.integers(0, 50, size=rows, dtype=np.int64)
     cst, sep = F.random_scalar(rng), F.random_scalar(rng)
     S = lambda v: orc.scalars_to_array(F, [v])
     T = F.table_from_i64
-    o_t = orc.LogUpInput(F, 1, [T(t_in), T(t_out)], cst, sep, mult=T(mult))
+    o_t = orc.LogUpInput(F, 1, [T(c) for c in cols], cst, sep, mult=T(mult))
     want = orc.serialize_logup_proof(F, orc.logup_batch_prove(F, [o_t], orc.Transcript(F)))
-    d_t = prover.LogUpInput.new_table([ctx.upload_i64(t_in, base), ctx.upload_i64(t_out, base)],
-                                      ctx.upload_i64(mult, base), S(cst), S(sep))
+    d_t = prover.LogUpInput.new_table([ctx.upload_i64(c, base) for c in cols], ctx.upload_i64(mult, base), S(cst), S(sep))
     assert prover.new_batch_multiple_sizes_prove(ctx, [d_t], prover.Blake3Transcript(family_dtype(dpb, F))) == want
+
+
+@pytest.mark.parametrize("F", FIELDS)
+def test_many_instances_and_three_columns(dpb, ctx, prover, F):
+    """70 single-column instances of 2^16 rows (more than 64: still the layer kernel) and one three-column instance
+    (more columns than the layer kernel takes: the segmented kernel), each batch against the oracle."""
+    rng = np.random.default_rng(79)
+    rows = 1 << 16
+    base = dpb.FR if F is orc.FrField else dpb.GL_BASE
+    S = lambda v: orc.scalars_to_array(F, [v])
+    fam = family_dtype(dpb, F)
+    for n_cols, cpi in ((70, 1), (3, 3)):
+        cols = [rng.integers(0, 1 << 12, size=rows, dtype=np.int64) for _ in range(n_cols)]
+        cst, sep = F.random_scalar(rng), F.random_scalar(rng)
+        o_in = orc.LogUpInput(F, 0, [F.table_from_i64(c) for c in cols], cst, sep, columns_per_instance=cpi)
+        want = orc.serialize_logup_proof(F, orc.logup_batch_prove(F, [o_in], orc.Transcript(F)))
+        d_in = prover.LogUpInput.new_lookup([ctx.upload_i64(c, base) for c in cols], S(cst), S(sep), cpi)
+        assert prover.new_batch_multiple_sizes_prove(ctx, [d_in], prover.Blake3Transcript(fam)) == want, (n_cols, cpi)
