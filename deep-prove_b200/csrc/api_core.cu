@@ -46,7 +46,7 @@ constexpr size_t kBigKeepCount = 16;              // freed big blocks kept for a
 constexpr size_t kBigKeepBytes = (size_t)96 << 30;
 constexpr size_t kAllocAlign = 256;
 
-// DPB_ARENA=0: every request goes to the stream-ordered allocator itself (for comparison; see the bench notes)
+// DPB_ARENA=0: every request goes to the stream-ordered allocator itself (to compare the two)
 static bool arena_enabled() {
     static const bool v = [] {
         const char* e = getenv("DPB_ARENA");
