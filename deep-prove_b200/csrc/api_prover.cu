@@ -476,6 +476,23 @@ int dpb_lookup_padding_evaluation(int family_dtype, const void* padding_value, c
     });
 }
 
+int dpb_scalar_inverse(int family_dtype, const void* a, void* out) {
+    if (!a || !out) return fail(DPB_EINVAL, "null argument");
+    if (!valid_dtype(family_dtype)) return fail(DPB_EINVAL, "unknown dtype %d", family_dtype);
+    if (is_gl(family_dtype)) {
+        Gl2 x;
+        memcpy(&x, a, sizeof x);
+        const Gl2 y = GlFam::is_zero(x) ? x : GlFam::inv(x);
+        memcpy(out, &y, sizeof y);
+    } else {
+        Fr x;
+        memcpy(&x, a, sizeof x);
+        const Fr y = FrFam::inv(x);
+        memcpy(out, &y, sizeof y);
+    }
+    return DPB_OK;
+}
+
 int dpb_bias_evaluation(int family_dtype, const uint64_t* output_shape, uint32_t rank, const uint8_t* axis_in_bias,
                         const uint32_t* bias_axis_position, const void* point, uint32_t n_point, const void* bias_eval,
                         void* out_eval, void* out_bias_point, uint32_t bias_point_cap, uint32_t* n_bias_point) {

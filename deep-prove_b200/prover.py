@@ -48,6 +48,7 @@ PROVER_SIGNATURES = {
                                  ctypes.POINTER(_u32)]),
     "dpb_expr_eval": (_int, [_int, ctypes.POINTER(ExprNode), _u32, _vp, _u32, _vp, _u32, _vp]),
     "dpb_lookup_padding_evaluation": (_int, [_int, _vp, _vp, _u32, _vp, _u32, _vp]),
+    "dpb_scalar_inverse": (_int, [_int, _vp, _vp]),
     "dpb_bias_evaluation": (_int, [_int, _vp, _u32, _vp, _vp, _vp, _u32, _vp, _vp, _vp, _u32, ctypes.POINTER(_u32)]),
     "dpb_prove_sumcheck": (_int, [_vp, _u32, _pp, _u32, ctypes.POINTER(Term), _u32, _vp, _vp, _u32, _vp, _vp,
                                   ctypes.POINTER(_u32)]),
@@ -229,6 +230,14 @@ def lookup_padding_evaluation(family_dtype, padding_value, shape, point):
     out = np.zeros(w, dtype=np.uint64)
     check(lib.dpb_lookup_padding_evaluation(family_dtype, _buf(pv), shp, len(shape), _buf(pt) if pt.size else None,
                                             pt.shape[0], _buf(out)))
+    return out
+
+
+def scalar_inverse(family_dtype, a):
+    """dpb_scalar_inverse: 1 / a for a challenge element (0 -> 0)."""
+    x = _scalars(a).reshape(elem_words(chal_dtype(family_dtype)))
+    out = np.zeros_like(x)
+    check(lib.dpb_scalar_inverse(family_dtype, _buf(x), _buf(out)))
     return out
 
 

@@ -69,6 +69,10 @@ int dpb_expr_eval(int family_dtype, const dpb_expr_node* nodes, uint32_t n_nodes
  * message when the point's length does not match the padded shape. */
 int dpb_lookup_padding_evaluation(int family_dtype, const void* padding_value, const uint64_t* shape, uint32_t rank,
                                   const void* point, uint32_t n_point, void* out);
+/* The inverse of a challenge element (host arithmetic; 0 maps to 0): what the host side of the split-eq rounds uses,
+ * exported for callers that normalise by a challenge (e.g. 1 / 2 in the argmax linking's eq point,
+ * zkml/src/layers/transformer/logits.rs:600-610). */
+int dpb_scalar_inverse(int family_dtype, const void* a, void* out);
 /* AxesMapping::compute_bias_evaluation and bias_evaluation_point (zkml/src/layers/einsum/axis.rs:583-720):
  * axis_in_bias[d] != 0 when output dimension d is an axis of the bias, bias_axis_position[d] its position in the
  * bias tensor (may be NULL: no bias point is produced).  out_eval = bias_eval times the less-than polynomial of

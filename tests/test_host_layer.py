@@ -152,3 +152,18 @@ def test_bias_evaluation_matches_the_oracle(dpb, prover, F):
             got, got_pt = prover.bias_evaluation(f, shape, present, pos, pt, orc.scalars_to_array(F, [bias_eval]))
             assert orc.array_to_scalars(F, got)[0] == want
             assert (orc.array_to_scalars(F, got_pt) if len(want_pt) else []) == want_pt
+
+
+@pytest.mark.parametrize("F", FIELDS)
+def test_scalar_inverse_matches_the_oracle(dpb, prover, F):
+    """dpb_scalar_inverse (the host inverse the split-eq planning uses; BN254: binary extended Euclid) against the
+    oracle's inverse, on random values and on the edges 1, -1, 2, 0."""
+    rng = np.random.default_rng(17)
+    fam = dpb.FR if F is orc.FrField else dpb.GL_EXT
+    vals = [F.one, F.neg(F.one), F.from_int(2), F.from_int(-7)] + [F.random_scalar(rng) for _ in range(300)]
+    for v in vals:
+        got = orc.array_to_scalars(F, prover.scalar_inverse(fam, orc.scalars_to_array(F, [v])).reshape(1, -1))[0]
+        assert got == F.inv(v)
+        assert F.mul(got, v) == F.one
+    zero = orc.array_to_scalars(F, prover.scalar_inverse(fam, orc.scalars_to_array(F, [F.zero])).reshape(1, -1))[0]
+    assert zero == F.zero
