@@ -497,11 +497,23 @@ template <class F>
 static int launch_logup(dpb_sc* sc, uint32_t round, uint64_t n_pairs, const typename F::E& r, const SplitEqArgs<F>& eq) {
     typedef typename F::E E;
     dpb_ctx* ctx = sc->ctx;
-    const uint32_t threads = 128;
-    uint64_t blocks = (n_pairs + threads - 1) / threads;
     const uint64_t per_sm = sizeof(E) == 16 ? 4 : 3;  // resident blocks: 126 registers per thread (Goldilocks), 168 (BN254)
-    if (blocks > (uint64_t)ctx->sm_count * per_sm) blocks = (uint64_t)ctx->sm_count * per_sm;
-    if (blocks > ctx->max_blocks) blocks = ctx->max_blocks;
+    // blocks of 128 threads, of 64 when the pairs do not fill the GPU even then; and when they still do not, the
+    // instances are cut into slices that run as blocks of their own
+    uint32_t threads = 128;
+    if (n_pairs < (uint64_t)ctx->sm_count * threads) threads = 64;
+    uint64_t blocks_x = (n_pairs + threads - 1) / threads;
+    const uint64_t room = (uint64_t)ctx->sm_count * per_sm * (128 / threads);
+    if (blocks_x > room) blocks_x = room;
+    uint32_t slices = 1;
+    if (blocks_x < room) slices = (uint32_t)std::min<uint64_t>(sc->logup_n, room / blocks_x);
+    const uint32_t inst_per_slice = (sc->logup_n + slices - 1) / slices;
+    slices = (sc->logup_n + inst_per_slice - 1) / inst_per_slice;
+    uint64_t blocks = blocks_x * slices;
+    if (blocks > ctx->max_blocks) {
+        slices = 1;
+        blocks = blocks_x = std::min<uint64_t>(blocks_x, ctx->max_blocks);
+    }
     const RoundTab* tabs = sc->d_rtab_eq + (size_t)round * sc->k;
     const typename F::FoldKey rk = F::fold_key(r);
     E lam;
@@ -513,11 +525,11 @@ static int launch_logup(dpb_sc* sc, uint32_t round, uint64_t n_pairs, const type
     if (round > 0)
         sc_round_logup<F, true><<<(uint32_t)blocks, threads, smem, ctx->stream>>>(
             tabs, inst, consts, sc->logup_n, rk, lamk, sc->logup_eq, eq.scale[0], eq.stride_log2[0], n_pairs,
-            reduce_scratch<F>(ctx), (E*)ctx->round_out);
+            (uint32_t)blocks_x, slices == 1 ? sc->logup_n : inst_per_slice, reduce_scratch<F>(ctx), (E*)ctx->round_out);
     else
         sc_round_logup<F, false><<<(uint32_t)blocks, threads, smem, ctx->stream>>>(
             tabs, inst, consts, sc->logup_n, rk, lamk, sc->logup_eq, eq.scale[0], eq.stride_log2[0], n_pairs,
-            reduce_scratch<F>(ctx), (E*)ctx->round_out);
+            (uint32_t)blocks_x, slices == 1 ? sc->logup_n : inst_per_slice, reduce_scratch<F>(ctx), (E*)ctx->round_out);
     return DPB_OK;
 }
 
@@ -959,6 +971,7 @@ static int wait_round_chunks(dpb_ctx* ctx, size_t msg_bytes, void* out) {
 }
 
 constexpr uint64_t kSpreadPairs = 4096;  // rounds up to this size of a heavy program are spread over its terms
+constexpr uint64_t kLogupMinPairs = 4096;  // rounds above this size of a hinted logup layer run sc_round_logup
 constexpr uint64_t kSpreadLightPairs = 16384;  // and of any other program (measured: 14-15 % off a logup batch)
 
 template <class F>
@@ -995,7 +1008,11 @@ static int run_round(dpb_sc* sc, const void* prev_challenge, void* out_evals) {
     // (pair, slice of the term list) items: a thread's chain of dependent field products is what such a round
     // waits for, and the spread form makes it several times shorter.  Heavy programs: up to kSpreadPairs pairs;
     // every other program: between the resident kernel's rounds and kSpreadLightPairs.
-    const bool spread = ((sc->heavy && n_pairs <= kSpreadPairs) ||
+    // a logup layer with its own round kernel spreads over instances inside that kernel instead
+    // (down to kLogupMinPairs pairs; measured: a 36-instance batch of 2^18 rows 18.7 -> 17.0 ms, below that no gain)
+    const bool logup_round = sc->logup_ok && sc->spliteq && !use_tail && n_pairs > kLogupMinPairs;
+    const bool spread = !logup_round &&
+                        ((sc->heavy && n_pairs <= kSpreadPairs) ||
                          (!use_tail && !sc->ranged && sc->has_prog && n_pairs <= kSpreadLightPairs)) &&
                         sc->fused_shape != kFusedProduct;
     if (spread && sc->eq_unbound) DPB_TRY(spliteq_materialize<F>(sc, i));

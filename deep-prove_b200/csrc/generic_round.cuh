@@ -451,7 +451,8 @@ __global__ void __launch_bounds__(128, 3)
     sc_round_logup(const RoundTab* __restrict__ tabs, const LogupInst* __restrict__ inst_g,
                    const LogupConsts<F>* __restrict__ consts_g, uint32_t n_inst, typename F::FoldKey rk,
                    typename F::FoldKey lamk, uint32_t eq_table, typename F::E eq_scale, uint32_t eq_stride_log2,
-                   uint64_t n_pairs, ReduceScratch<F> rs, typename F::E* out) {
+                   uint64_t n_pairs, uint32_t blocks_x, uint32_t inst_per_slice, ReduceScratch<F> rs,
+                   typename F::E* out) {
     typedef typename F::E E;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     LogupConsts<F>* consts = (LogupConsts<F>*)smem_raw;
@@ -467,10 +468,14 @@ __global__ void __launch_bounds__(128, 3)
 #pragma unroll
     for (int x = 0; x < 4; x++) acc[x] = F::zero();
     const RoundTab eqt = tabs[eq_table];
-    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
-    for (uint64_t p = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; p < n_pairs; p += stride) {
+    // The grid is blocks_x blocks over the pairs times slices of inst_per_slice instances: a round with few pairs
+    // still fills the GPU, and a thread's chain of products is one slice long (the sums are linear in the instances).
+    const uint32_t slice = blockIdx.x / blocks_x, bx = blockIdx.x % blocks_x;
+    const uint32_t i_begin = slice * inst_per_slice, i_end = min(n_inst, i_begin + inst_per_slice);
+    const uint64_t stride = (uint64_t)blocks_x * blockDim.x;
+    for (uint64_t p = (uint64_t)bx * blockDim.x + threadIdx.x; p < n_pairs; p += stride) {
         E g0 = F::zero(), g1 = F::zero(), g2 = F::zero();
-        for (uint32_t i = 0; i < n_inst; i++) {
+        for (uint32_t i = i_begin; i < i_end; i++) {
             const LogupInst in = inst[i];
             const LogupConsts<F>& k = consts[i];
             E a0, da, c0, dc, d0, dd, u0, du;  // A, C, D and U = B + lambda D (lookups: lambda D - 1), each (value, difference)
