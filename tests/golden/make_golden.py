@@ -26,7 +26,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 def golden_inputs(F, name):
     """Seeded inputs shared by the generator and the GPU parity tests."""
     seed = {"prod3": 101, "hadamard": 102, "logup_lookup": 103, "logup_table": 104, "fix": 105,
-            "mixed": 106, "claims": 107, "lookup": 108}[name]
+            "mixed": 106, "claims": 107, "lookup": 108, "einsum": 109}[name]
     rng = np.random.default_rng(seed)
     if name == "prod3":
         n = 6
@@ -66,6 +66,19 @@ def golden_inputs(F, name):
                     table_out=np.clip(np.arange(lo, hi + 1, dtype=np.int64), 0, hi), out_min=0, out_max=hi,
                     claim_point=[F.random_scalar(rng) for _ in range(2 + 3 + 1)],
                     logup_point=[F.random_scalar(rng) for _ in range(2 + 3)])
+    if name == "einsum":
+        # (left tensor, its fixes per output, right tensors with their fixes): stacked heads with one output, and one
+        # left tensor with two right tensors (two outputs: the left claims are merged by a second sumcheck)
+        C, O, S = orc.AXIS_CONTRACTED, orc.AXIS_OUTER, orc.AXIS_STACKED
+        lg = lambda d: max(d - 1, 0).bit_length()
+        pt = lambda d: [F.random_scalar(rng) for _ in range(lg(d))]
+        q, k = rng.integers(-9, 9, (3, 5, 4)), rng.integers(-9, 9, (3, 6, 4))
+        hp, sp, tp = pt(3), pt(5), pt(6)
+        x, w, w2 = rng.integers(-99, 99, (6, 10)), rng.integers(-99, 99, (10, 5)), rng.integers(-99, 99, (10, 3))
+        rp, cp, rp2, cp2 = pt(6), pt(5), pt(6), pt(3)
+        return [dict(lhs=q, fixes=[((S, O, C), [hp, sp, None])], rhs=[(k, (S, O, C), [hp, tp, None])]),
+                dict(lhs=x, fixes=[((O, C), [rp, None]), ((O, C), [rp2, None])],
+                     rhs=[(w, (C, O), [None, cp]), (w2, (C, O), [None, cp2])])]
     if name == "claims":
         # committed polynomials (num_vars, chunks, claims): one unchunked with two claims, one in four chunks, one small
         polys = []
@@ -133,6 +146,15 @@ def generate(F):
             F, orc.merged_table_column(g["bits"], orc.SIGN_MIXED, g["table_out"]), counts[1]))),
         linking=dict(proof=orc.serialize_sumcheck_proof(F, link["sumcheck"]).hex(), point=hx(link["point"]),
                      evaluations=hx(link["evaluations"]), challenges=hx(link["challenges"])))
+
+    out["einsum"] = []
+    for g in golden_inputs(F, "einsum"):
+        dims = [1 << max(d - 1, 0).bit_length() for d in g["lhs"].shape]
+        padded = np.zeros(dims, dtype=np.int64)
+        padded[tuple(slice(0, d) for d in g["lhs"].shape)] = g["lhs"]
+        pr = orc.einsum_prove(F, orc.Transcript(F), g["lhs"], g["fixes"], g["rhs"],
+                              lhs_padded=F.table_from_i64(padded.reshape(-1)))
+        out["einsum"].append(orc.serialize_einsum_proof(F, pr).hex())
 
     g = golden_inputs(F, "fix")
     out["eq"] = hx(orc.array_to_scalars(F, orc.eq_evals(F, g["point"][:4])))

@@ -156,3 +156,28 @@ def test_einsum_prove_matches_oracle(dpb, ctx, F):
     with pytest.raises(ValueError):
         op = prover.EinsumOperand(x, (C, C), [None, None])
         prover.einsum_prove(ctx, [op], [op, op], prover.Blake3Transcript(fam))
+
+
+@pytest.mark.parametrize("F", FIELDS)
+def test_einsum_golden(dpb, ctx, F):
+    """dpb_einsum_prove against the committed fixture (stacked heads; two outputs with the merging sumcheck)."""
+    import importlib
+    import json
+    import os
+    from tests.golden import make_golden
+    prover = importlib.import_module("deep_prove_b200.prover")
+    with open(os.path.join(os.path.dirname(__file__), "golden", f"oracle_{F.name}.json")) as f:
+        want = json.load(f)["einsum"]
+    fam = family_dtype(dpb, F)
+
+    def arr(p):
+        return None if p is None else np.ascontiguousarray(orc.scalars_to_array(F, p), dtype=np.uint64).reshape(len(p), -1)
+    for g, w in zip(make_golden.golden_inputs(F, "einsum"), want):
+        lops = [prover.EinsumOperand(g["lhs"], k, [arr(p) for p in pts]) for k, pts in g["fixes"]]
+        rops = [prover.EinsumOperand(t, k, [arr(p) for p in pts]) for t, k, pts in g["rhs"]]
+        dims = [1 << max(d - 1, 0).bit_length() for d in g["lhs"].shape]
+        padded = np.zeros(dims, dtype=np.int64)
+        padded[tuple(slice(0, d) for d in g["lhs"].shape)] = g["lhs"]
+        pm = ctx.upload_ints(padded.reshape(-1), dpb.FR_I64 if F is orc.FrField else dpb.GL_I64)
+        got = prover.einsum_prove(ctx, lops, rops, prover.Blake3Transcript(fam), lhs_padded=pm)
+        assert got.hex() == w
